@@ -1,0 +1,149 @@
+"""Library surface: ``Model`` and ``generate_plain``.
+
+Mirrors the reference's model façade (src/model.rs:185-405 ``Model::{load, prefill, decode,
+capture, reset, embed, ...}``, ``generate_plain`` :89-127, ``GenerationOutput``) on top of the
+batched engine: the single-sequence calls operate on an implicit "current" sequence, the batched
+calls (``generate_batch``) expose continuous batching.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import torch
+
+from .config import ModelSpec, Settings, named_shape, read_model_spec
+from .engine.engine import Engine, Sequence
+from .models.decoder import DecoderModel
+from .models.weights import TPInfo, random_decoder_weights
+from .planner.plan import plan_engine
+from .utils.log import log_json
+
+
+@dataclass
+class GenerationOutput:
+    ids: list[int]
+    prefill_ms: float = 0.0
+    capture_ms: float = 0.0
+    decode_ms: float = 0.0
+    decode_steps: int = 0
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def decode_tok_s(self) -> float:
+        return 1000.0 * self.decode_steps / self.decode_ms if self.decode_ms > 0 else 0.0
+
+
+class Model:
+    """A loaded model bound to one device (or one tensor/expert-parallel rank)."""
+
+    def __init__(self, engine: Engine, spec: ModelSpec, settings: Settings, tokenizer=None, name: str | None = None):
+        self.engine, self.spec, self.settings = engine, spec, settings
+        self.tokenizer = tokenizer
+        self.name = name or spec.name
+        self._seq: Sequence | None = None
+        self.load_ms = 0.0
+
+    # -- construction ------------------------------------------------------------------------
+    @classmethod
+    def load(cls, model: str, settings: Settings | None = None, device: str | torch.device | None = None,
+             random_init: bool | None = None, seed: int = 0, comm=None, ep=None) -> "Model":
+        """Load a checkpoint directory, or a named shape with seeded random weights
+        (``random_init``; implied when ``model`` names a shape rather than a directory)."""
+        t0 = time.perf_counter()
+        settings = settings or Settings()
+        if device is None:
+            device = f"cuda:{settings.device}" if torch.cuda.is_available() else "cpu"
+        device = torch.device(device)
+        tokenizer = None
+        path = Path(model)
+        tp = TPInfo(comm.rank, comm.size) if comm is not None else TPInfo()
+        epi = TPInfo(ep.rank, ep.size) if ep is not None else TPInfo()
+        if path.is_dir() and not random_init:
+            from .loaders.checkpoint import load_decoder_weights
+            from .loaders.tokenizer import load_tokenizer
+            spec = read_model_spec(path)
+            weights = load_decoder_weights(path, spec, device, tp, epi)
+            tokenizer = load_tokenizer(path)
+            name = path.name
+        else:
+            spec = read_model_spec(path) if path.is_dir() else named_shape(model)
+            weights = random_decoder_weights(spec, seed, device, tp, epi)
+            name = spec.name
+        if spec.mla is not None:
+            from .models.deepseek import DeepseekModel
+            net = DeepseekModel(weights, comm=comm)
+        else:
+            net = DecoderModel(weights, comm=comm)
+        if ep is not None:
+            net.ep = ep
+        plan = plan_engine(spec, settings, device, weights_bytes=weights.nbytes(), tp=tp.size)
+        log_json("prefill_memory_plan", verbose_only=True, **plan.to_json())
+        engine = Engine(net, spec, settings, plan.kv_blocks, device, max_prefill_rows=plan.prefill_chunk)
+        m = cls(engine, spec, settings, tokenizer, name)
+        m.load_ms = (time.perf_counter() - t0) * 1e3
+        log_json("backend_device", verbose_only=True, device=str(device), model=name, load_ms=m.load_ms)
+        return m
+
+    # -- single-sequence surface -------------------------------------------------------------
+    def reset(self) -> None:
+        self.engine.reset()
+        self._seq = None
+
+    def prefill(self, ids: list[int]) -> int:
+        """Start a sequence with ``ids``; returns the first generated token."""
+        if self._seq is not None:
+            self.engine.free_sequence(self._seq.seq_id)
+        self._seq = self.engine.add_sequence(ids)
+        return self.engine.prefill([self._seq])[0]
+
+    def decode(self) -> int:
+        """One greedy decode step for the current sequence."""
+        assert self._seq is not None, "prefill first"
+        return self.engine.decode([self._seq])[0]
+
+    def capture(self) -> float:
+        """Capture the batch-1 decode graph ahead of time; returns milliseconds spent."""
+        t0 = time.perf_counter()
+        if self.engine.use_graph:
+            self.engine.capture(1)
+        return (time.perf_counter() - t0) * 1e3
+
+    def graph_decode(self) -> bool:
+        return self.engine.use_graph
+
+    # -- generation --------------------------------------------------------------------------
+    def generate_batch(self, prompts: list[list[int]], max_new_tokens: int, ignore_eos: bool = True,
+                       on_token=None) -> list[list[int]]:
+        return self.engine.generate(prompts, max_new_tokens, self.spec.eos_token_id, ignore_eos, on_token)
+
+
+def generate_plain(model: Model, ids: list[int], count: int, ignore_eos: bool = False, graph: bool = True,
+                   on_token=None) -> GenerationOutput:
+    """Greedy loop: prefill -> optional graph capture -> decode until EOS or ``count`` tokens.
+    ``ids[0]`` of the result is the token emitted by prefill."""
+    eng = model.engine
+    eng.use_graph = graph and eng.device.type == "cuda"
+    sync = (lambda: torch.cuda.synchronize(eng.device)) if eng.device.type == "cuda" else (lambda: None)
+    t0 = time.perf_counter()
+    first = model.prefill(ids)
+    sync()
+    t1 = time.perf_counter()
+    out = [first]
+    if on_token:
+        on_token(first)
+    cap_ms = model.capture() if eng.use_graph else 0.0
+    t2 = time.perf_counter()
+    eos = model.spec.eos_token_id
+    steps = 0
+    while len(out) < count and not (not ignore_eos and eos is not None and out[-1] == eos):
+        tok = model.decode()
+        steps += 1
+        out.append(tok)
+        if on_token:
+            on_token(tok)
+    sync()
+    t3 = time.perf_counter()
+    return GenerationOutput(ids=out, prefill_ms=(t1 - t0) * 1e3, capture_ms=cap_ms, decode_ms=(t3 - t2) * 1e3,
+                            decode_steps=steps)

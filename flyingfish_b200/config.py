@@ -1,0 +1,286 @@
+"""Model geometry and engine settings.
+
+``ModelSpec`` is the normalised description of a decoder that the rest of the framework works
+from (the counterpart of the reference's ``ModelSpec`` / ``Config``: src/model_spec.rs:8-104,
+469-510; src/config.rs:5-104). It can be read from a Hugging Face ``config.json`` or taken from
+the table of named benchmark shapes below. ``Settings`` carries the engine options of the CLI
+(src/backend/mod.rs:196-224).
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any
+
+
+@dataclass
+class MoeSpec:
+    num_experts: int
+    top_k: int
+    expert_ffn: int
+    score: str = "softmax"            # softmax | sigmoid | noaux | sqrtsoftplus
+    n_shared: int = 0                 # shared experts (each of width shared_ffn)
+    shared_ffn: int = 0
+    n_groups: int = 1
+    topk_groups: int = 1
+    routed_scaling: float = 1.0
+    renormalize: bool = True
+    first_dense_layers: int = 0       # leading layers with a dense FFN
+    dense_ffn: int = 0
+    shared_gate: bool = False         # sigmoid gate on the shared expert (Qwen-style)
+    expert_format: str = "bf16"       # bf16 | fp8_block | nvfp4
+
+
+@dataclass
+class MlaSpec:
+    q_lora_rank: int
+    kv_lora_rank: int
+    qk_nope_dim: int
+    qk_rope_dim: int
+    v_head_dim: int
+
+
+@dataclass
+class ModelSpec:
+    name: str
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe
+    layers: int
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    ffn: int
+    vocab: int
+    rope_theta: float = 10000.0
+    rms_eps: float = 1e-6
+    dtype: str = "bf16"               # storage / compute dtype of dense weights
+    linear_format: str = "bf16"       # bf16 | fp8_block | nvfp4
+    tie_embeddings: bool = False
+    qk_norm: bool = False
+    swiglu_mode: int = 0
+    max_position: int = 131072
+    eos_token_id: int | None = None
+    moe: MoeSpec | None = None
+    mla: MlaSpec | None = None
+    mtp_layers: int = 0               # multi-token-prediction heads shipped with the checkpoint
+    extra: dict[str, Any] = field(default_factory=dict)
+
+    @property
+    def q_dim(self) -> int:
+        return self.heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.kv_heads * self.head_dim
+
+    @property
+    def qkv_dim(self) -> int:
+        return self.q_dim + 2 * self.kv_dim
+
+    def dense_param_count(self) -> int:
+        per_layer = self.hidden * self.qkv_dim + self.q_dim * self.hidden + 3 * self.hidden * self.ffn + 2 * self.hidden
+        return self.layers * per_layer + (1 if self.tie_embeddings else 2) * self.vocab * self.hidden + self.hidden
+
+    def decode_weight_bytes(self) -> int:
+        """Bytes of weights read by one decode step (embedding row gathers excluded, lm_head
+        included) -- the numerator of the reference's decode roofline (src/bench.rs:137-160)."""
+        per_layer = self.hidden * self.qkv_dim + self.q_dim * self.hidden + 3 * self.hidden * self.ffn + 2 * self.hidden
+        return 2 * (self.layers * per_layer + self.vocab * self.hidden + self.hidden)
+
+    def to_json(self) -> dict[str, Any]:
+        return dataclasses.asdict(self)
+
+
+# ------------------------------------------------------------------------------------------
+# named shapes (the benchmark configurations; random-init, no checkpoint needed)
+# ------------------------------------------------------------------------------------------
+def tiny_moe() -> ModelSpec:
+    return ModelSpec(
+        name="tiny-moe", arch="tiny_moe", layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, ffn=512,
+        vocab=1024, rope_theta=1e4, rms_eps=1e-6, dtype="fp32",
+        moe=MoeSpec(num_experts=8, top_k=2, expert_ffn=512, score="softmax", n_shared=1, shared_ffn=512))
+
+
+def tiny_llama() -> ModelSpec:
+    """Small dense shape with the production head geometry (head_dim 128, GQA 4:1) for tests."""
+    return ModelSpec(name="tiny-llama", arch="llama", layers=2, hidden=512, heads=4, kv_heads=1, head_dim=128,
+                     ffn=1024, vocab=2048, rope_theta=5e5, rms_eps=1e-5)
+
+
+def llama3_8b() -> ModelSpec:
+    return ModelSpec(name="llama3-8b-shape", arch="llama", layers=32, hidden=4096, heads=32, kv_heads=8,
+                     head_dim=128, ffn=14336, vocab=128256, rope_theta=5e5, rms_eps=1e-5)
+
+
+def llama3_70b() -> ModelSpec:
+    return ModelSpec(name="llama3-70b-shape", arch="llama", layers=80, hidden=8192, heads=64, kv_heads=8,
+                     head_dim=128, ffn=28672, vocab=128256, rope_theta=5e5, rms_eps=1e-5)
+
+
+def deepseek_v3() -> ModelSpec:
+    return ModelSpec(
+        name="deepseek-v3-shape", arch="deepseek_v3", layers=61, hidden=7168, heads=128, kv_heads=128, head_dim=128,
+        ffn=18432, vocab=129280, rope_theta=1e4, rms_eps=1e-6, linear_format="fp8_block", mtp_layers=1,
+        mla=MlaSpec(q_lora_rank=1536, kv_lora_rank=512, qk_nope_dim=128, qk_rope_dim=64, v_head_dim=128),
+        moe=MoeSpec(num_experts=256, top_k=8, expert_ffn=2048, score="noaux", n_shared=1, shared_ffn=2048,
+                    n_groups=8, topk_groups=4, routed_scaling=2.5, first_dense_layers=3, dense_ffn=18432,
+                    expert_format="fp8_block"))
+
+
+def deepseek_v3_tiny() -> ModelSpec:
+    """Same structure as :func:`deepseek_v3` (MLA + grouped noaux routing + MTP head) at test size."""
+    return ModelSpec(
+        name="deepseek-v3-tiny", arch="deepseek_v3", layers=3, hidden=256, heads=4, kv_heads=4, head_dim=128,
+        ffn=512, vocab=1024, rope_theta=1e4, rms_eps=1e-6, mtp_layers=1,
+        mla=MlaSpec(q_lora_rank=96, kv_lora_rank=64, qk_nope_dim=32, qk_rope_dim=16, v_head_dim=32),
+        moe=MoeSpec(num_experts=16, top_k=4, expert_ffn=128, score="noaux", n_shared=1, shared_ffn=128,
+                    n_groups=4, topk_groups=2, routed_scaling=2.5, first_dense_layers=1, dense_ffn=512))
+
+
+def qwen3_moe_235b() -> ModelSpec:
+    return ModelSpec(
+        name="qwen3-moe-235b-shape", arch="qwen3_moe", layers=94, hidden=4096, heads=64, kv_heads=4, head_dim=128,
+        ffn=12288, vocab=151936, rope_theta=1e6, rms_eps=1e-6, qk_norm=True,
+        moe=MoeSpec(num_experts=128, top_k=8, expert_ffn=1536, score="softmax", expert_format="nvfp4"))
+
+
+def qwen3_moe_tiny() -> ModelSpec:
+    return ModelSpec(
+        name="qwen3-moe-tiny", arch="qwen3_moe", layers=2, hidden=512, heads=4, kv_heads=1, head_dim=128, ffn=1024,
+        vocab=2048, rope_theta=1e6, rms_eps=1e-6, qk_norm=True,
+        moe=MoeSpec(num_experts=16, top_k=4, expert_ffn=256, score="softmax"))
+
+
+NAMED_SHAPES = {
+    "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
+    "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny,
+    "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
+}
+
+
+def named_shape(name: str) -> ModelSpec:
+    if name not in NAMED_SHAPES:
+        raise KeyError(f"unknown shape {name!r}; known: {sorted(NAMED_SHAPES)}")
+    return NAMED_SHAPES[name]()
+
+
+# ------------------------------------------------------------------------------------------
+# config.json normalisation
+# ------------------------------------------------------------------------------------------
+class ConfigError(ValueError):
+    pass
+
+
+_ARCH_MAP = {
+    "LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "Qwen2ForCausalLM": "qwen3",
+    "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "DeepseekV3ForCausalLM": "deepseek_v3",
+    "DeepseekV2ForCausalLM": "deepseek_v3",
+}
+
+
+def spec_from_hf_config(cfg: dict[str, Any], name: str = "model") -> ModelSpec:
+    """Normalise a Hugging Face ``config.json``. Hard checks mirror the reference's: SiLU
+    activation only, 16-bit or 32-bit floats, no unsupported rope scaling for plain Llama."""
+    archs = cfg.get("architectures") or []
+    arch = next((_ARCH_MAP[a] for a in archs if a in _ARCH_MAP), None)
+    if arch is None:
+        raise ConfigError(f"unsupported architectures {archs}")
+    act = cfg.get("hidden_act", "silu")
+    if act not in ("silu", "swish"):
+        raise ConfigError(f"unsupported activation {act!r}")
+    td = cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))
+    dtype = {"bfloat16": "bf16", "float16": "f16", "float32": "fp32"}.get(td)
+    if dtype is None:
+        raise ConfigError(f"unsupported torch_dtype {td!r}")
+    hidden = int(cfg["hidden_size"])
+    heads = int(cfg["num_attention_heads"])
+    kv_heads = int(cfg.get("num_key_value_heads", heads))
+    head_dim = int(cfg.get("head_dim") or hidden // heads)
+    if heads % kv_heads:
+        raise ConfigError("num_attention_heads must be a multiple of num_key_value_heads")
+    scaling = cfg.get("rope_scaling")
+    extra: dict[str, Any] = {}
+    if scaling:
+        kind = scaling.get("rope_type", scaling.get("type"))
+        if kind not in ("llama3", "yarn", "default", None):
+            raise ConfigError(f"unsupported rope scaling {kind!r}")
+        extra["rope_scaling"] = scaling
+    quant = cfg.get("quantization_config") or {}
+    linear_format = "bf16"
+    if quant.get("quant_method") == "fp8" and quant.get("weight_block_size") == [128, 128]:
+        linear_format = "fp8_block"
+    elif quant.get("quant_algo") == "NVFP4" or quant.get("quant_method") == "modelopt":
+        linear_format = "nvfp4"
+    moe = None
+    if arch == "qwen3_moe":
+        moe = MoeSpec(num_experts=int(cfg["num_experts"]), top_k=int(cfg["num_experts_per_tok"]),
+                      expert_ffn=int(cfg["moe_intermediate_size"]), score="softmax",
+                      renormalize=bool(cfg.get("norm_topk_prob", True)),
+                      expert_format=linear_format if linear_format != "bf16" else "bf16")
+    mla = None
+    if arch == "deepseek_v3":
+        moe = MoeSpec(num_experts=int(cfg["n_routed_experts"]), top_k=int(cfg["num_experts_per_tok"]),
+                      expert_ffn=int(cfg["moe_intermediate_size"]),
+                      score="noaux" if cfg.get("topk_method", "noaux_tc") == "noaux_tc" else "softmax",
+                      n_shared=int(cfg.get("n_shared_experts", 0)),
+                      shared_ffn=int(cfg["moe_intermediate_size"]) * int(cfg.get("n_shared_experts", 0) or 0),
+                      n_groups=int(cfg.get("n_group", 1)), topk_groups=int(cfg.get("topk_group", 1)),
+                      routed_scaling=float(cfg.get("routed_scaling_factor", 1.0)),
+                      renormalize=bool(cfg.get("norm_topk_prob", True)),
+                      first_dense_layers=int(cfg.get("first_k_dense_replace", 0)),
+                      dense_ffn=int(cfg["intermediate_size"]),
+                      expert_format=linear_format)
+        mla = MlaSpec(q_lora_rank=int(cfg.get("q_lora_rank") or 0), kv_lora_rank=int(cfg["kv_lora_rank"]),
+                      qk_nope_dim=int(cfg["qk_nope_head_dim"]), qk_rope_dim=int(cfg["qk_rope_head_dim"]),
+                      v_head_dim=int(cfg["v_head_dim"]))
+    eos = cfg.get("eos_token_id")
+    if isinstance(eos, list):
+        extra["eos_token_ids"] = eos
+        eos = eos[0] if eos else None
+    return ModelSpec(
+        name=name, arch=arch, layers=int(cfg["num_hidden_layers"]), hidden=hidden, heads=heads, kv_heads=kv_heads,
+        head_dim=head_dim, ffn=int(cfg.get("intermediate_size", 0)), vocab=int(cfg["vocab_size"]),
+        rope_theta=float(cfg.get("rope_theta", 10000.0)), rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), dtype=dtype,
+        linear_format=linear_format, tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        qk_norm=arch in ("qwen3", "qwen3_moe"), max_position=int(cfg.get("max_position_embeddings", 131072)),
+        eos_token_id=eos, moe=moe, mla=mla, mtp_layers=int(cfg.get("num_nextn_predict_layers", 0)), extra=extra)
+
+
+def read_model_spec(model_dir: str | Path) -> ModelSpec:
+    p = Path(model_dir)
+    cfg = json.loads((p / "config.json").read_text())
+    return spec_from_hf_config(cfg, name=p.name)
+
+
+# ------------------------------------------------------------------------------------------
+# engine settings
+# ------------------------------------------------------------------------------------------
+@dataclass
+class Settings:
+    """Engine options shared by every entry point (CLI flags of the same names)."""
+    device: int = 0
+    capacity: int = 4096                  # tokens of KV per sequence the engine plans for
+    chunk: int | None = None              # prefill chunk rows (planner-derived when None)
+    device_budget_gib: float | None = None
+    draft_model: str | None = None
+    tree_builder: str = "waves"           # waves | serial
+    spec_budget: str = "chain"            # chain | tree16 | tree32 | tree64
+    spec_graph: bool = True
+    prefix_cache: bool = False
+    kv_format: str = "bf16"               # bf16 | affine8
+    runtime_dir: str | None = None
+    dram_gb_s: float = 6550.0             # roofline denominators (measured on the target box)
+    gemm_tflops: float = 1385.0
+    verbose: bool = False
+    tp: int = 1
+    ep: int = 1
+    max_batch: int = 64
+    kv_block: int = 64
+    graph: bool = True
+
+    def resolved_runtime_dir(self) -> Path:
+        import os
+        d = self.runtime_dir or os.environ.get("FLYINGFISH_RUNTIME_DIR") or str(Path.home() / ".flyingfish")
+        return Path(d)

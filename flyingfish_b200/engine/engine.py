@@ -1,0 +1,304 @@
+"""Device engine: owns the weights, the paged KV cache, the packed step metadata and the
+CUDA graphs, and exposes prefill / decode / verify steps over sets of sequences.
+
+This is the counterpart of the reference's ``Engine`` (src/backend/cuda/engine.rs:699-777:
+``prefill`` :4009, ``decode`` :4262, ``capture`` :4401) re-designed for many concurrent
+sequences: chunked prefill over a block cache, decode batches replayed from one CUDA graph per
+batch bucket (the reference captures one graph for its single sequence), one pinned
+host-to-device copy of the step metadata and one device-to-host read of the sampled ids per step.
+
+Failure policy follows the reference's poisoning rule (engine.rs:1941-1944): an exception inside
+a step marks the engine poisoned and every later entry point refuses until ``reset``.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import ops
+from ..config import ModelSpec, Settings
+from ..utils.log import log_json
+from .batch import BatchLayout, ForwardBatch
+from .kv_cache import OutOfBlocks, PagedKVCache
+
+
+class EnginePoisoned(RuntimeError):
+    pass
+
+
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def bucket_for(n: int) -> int:
+    for b in DECODE_BUCKETS:
+        if n <= b:
+            return b
+    raise ValueError(f"decode batch {n} exceeds the largest bucket {DECODE_BUCKETS[-1]}")
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt: list[int]
+    output: list[int] = field(default_factory=list)
+    prefilled: int = 0                 # prompt tokens whose KV is committed
+    pending: int | None = None         # token sampled but not yet fed through the model
+    finished: bool = False
+
+    @property
+    def all_tokens(self) -> list[int]:
+        return self.prompt + self.output
+
+
+class _Graph:
+    def __init__(self):
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.batch: ForwardBatch | None = None
+        self.out: torch.Tensor | None = None
+
+
+class Engine:
+    def __init__(self, model, spec: ModelSpec, settings: Settings, num_blocks: int, device: torch.device | str,
+                 max_prefill_rows: int = 8192):
+        self.model, self.spec, self.settings = model, spec, settings
+        self.device = torch.device(device)
+        tp = model.w.tp.size
+        hkv = max(1, spec.kv_heads // tp)
+        dtype = model.w.embed.dtype
+        self.kv = PagedKVCache(spec.layers, hkv, spec.head_dim, num_blocks, settings.kv_block, dtype, self.device)
+        self.max_blocks = (settings.capacity + settings.kv_block - 1) // settings.kv_block
+        self.max_batch = max(settings.max_batch, 1)
+        self.max_prefill_rows = max_prefill_rows
+        self.prefill_batch = ForwardBatch(BatchLayout(self.max_batch, max(max_prefill_rows, self.max_batch),
+                                                      self.max_blocks), self.device)
+        self.graphs: dict[tuple[int, int], _Graph] = {}
+        self.eager_decode_batch: dict[int, ForwardBatch] = {}
+        self.seqs: dict[int, Sequence] = {}
+        self._next_id = 0
+        self.poisoned = False
+        self.use_graph = settings.graph and self.device.type == "cuda"
+        self.stats = {"prefill_tokens": 0, "decode_steps": 0, "decode_tokens": 0, "graph_replays": 0,
+                      "captures": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+        self.fail_next_step = False      # host-side fault injection hook for tests
+
+    # -- sequence management ---------------------------------------------------------------
+    def add_sequence(self, prompt: list[int]) -> Sequence:
+        self._check()
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt) + 1 > self.settings.capacity:
+            raise ValueError(f"prompt of {len(prompt)} tokens exceeds the KV capacity {self.settings.capacity}")
+        sid = self._next_id
+        self._next_id += 1
+        s = Sequence(sid, list(prompt))
+        self.seqs[sid] = s
+        self.kv.add_sequence(sid)
+        return s
+
+    def free_sequence(self, seq_id: int) -> None:
+        self.seqs.pop(seq_id, None)
+        if seq_id in self.kv.seqs:
+            self.kv.free_sequence(seq_id)
+
+    def reset(self) -> None:
+        for sid in list(self.kv.seqs):
+            self.kv.free_sequence(sid)
+        self.seqs.clear()
+        self.poisoned = False
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            ops.read_status(self.device)
+
+    def _check(self) -> None:
+        if self.poisoned:
+            raise EnginePoisoned("engine is poisoned by an earlier failure; call reset()")
+
+    # -- prefill -----------------------------------------------------------------------------
+    def prefill(self, seqs: list[Sequence], chunk: int | None = None) -> list[int]:
+        """Prefill the given sequences to the end of their prompts (chunked) and return the first
+        generated token of each. Sequences are packed row-wise into chunks of at most ``chunk``
+        rows; only the chunk that contains a sequence's last prompt token computes its logits."""
+        self._check()
+        chunk = min(chunk or self.settings.chunk or self.max_prefill_rows, self.max_prefill_rows)
+        first: dict[int, int] = {}
+        try:
+            pending = [s for s in seqs if s.prefilled < len(s.prompt)]
+            while pending:
+                rows_left = chunk
+                part: list[tuple[Sequence, int]] = []
+                for s in pending:
+                    if rows_left <= 0 or len(part) >= self.max_batch:
+                        break
+                    take = min(len(s.prompt) - s.prefilled, rows_left)
+                    part.append((s, take))
+                    rows_left -= take
+                toks = self._prefill_chunk(part)
+                for (s, take), t in zip(part, toks):
+                    if s.prefilled == len(s.prompt):
+                        first[s.seq_id] = t
+                        s.pending = t
+                        s.output.append(t)
+                pending = [s for s in pending if s.prefilled < len(s.prompt)]
+        except Exception:
+            self.poisoned = True
+            raise
+        return [first[s.seq_id] for s in seqs if s.seq_id in first]
+
+    def _prefill_chunk(self, part: list[tuple[Sequence, int]]) -> list[int]:
+        fb = self.prefill_batch
+        ids, positions, slots, q_lens, ctx_lens, block_rows, logit_rows = [], [], [], [], [], [], []
+        row = 0
+        for s, take in part:
+            kvs = self.kv.seqs[s.seq_id]
+            sl = self.kv.reserve(s.seq_id, take)
+            ids += s.prompt[s.prefilled: s.prefilled + take]
+            positions += list(range(kvs.length, kvs.length + take))
+            slots += sl
+            q_lens.append(take)
+            ctx_lens.append(kvs.length + take)
+            block_rows.append(list(kvs.blocks))
+            logit_rows.append(row + take - 1)
+            row += take
+        fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
+                logit_rows=logit_rows, is_decode=False)
+        fb.upload()
+        out = self.model.forward(fb, self.kv)
+        toks = [int(t) for t in out.cpu().tolist()]
+        self._after_sync()
+        for s, take in part:
+            self.kv.commit(s.seq_id, take)
+            s.prefilled += take
+        self.stats["prefill_tokens"] += row
+        return toks
+
+    # -- decode ------------------------------------------------------------------------------
+    def _fill_decode(self, fb: ForwardBatch, seqs: list[Sequence], bucket: int) -> None:
+        ids, positions, slots, q_lens, ctx_lens, block_rows = [], [], [], [], [], []
+        for s in seqs:
+            kvs = self.kv.seqs[s.seq_id]
+            sl = self.kv.reserve(s.seq_id, 1)
+            ids.append(s.pending)
+            positions.append(kvs.length)
+            slots += sl
+            q_lens.append(1)
+            ctx_lens.append(kvs.length + 1)
+            block_rows.append(list(kvs.blocks))
+        pad = bucket - len(seqs)
+        ids += [0] * pad; positions += [0] * pad; slots += [-1] * pad
+        q_lens += [1] * pad; ctx_lens += [0] * pad; block_rows += [[]] * pad
+        fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
+                logit_rows=list(range(bucket)), is_decode=True, nq=1)
+        fb.max_ctx = self.settings.capacity      # fixed launch geometry (graph-stable)
+
+    def _decode_batch(self, bucket: int) -> ForwardBatch:
+        fb = self.eager_decode_batch.get(bucket)
+        if fb is None:
+            fb = ForwardBatch(BatchLayout(bucket, bucket, self.max_blocks), self.device)
+            self.eager_decode_batch[bucket] = fb
+        return fb
+
+    def capture(self, bucket: int) -> _Graph:
+        """Capture the decode step for a batch bucket: one eager warm-up on padding rows (which
+        write no KV), then stream capture of the same step."""
+        key = (bucket, 1)
+        g = self.graphs.get(key)
+        if g is not None:
+            return g
+        t0 = time.perf_counter()
+        g = _Graph()
+        fb = self._decode_batch(bucket)
+        fb.fill(ids=[0] * bucket, positions=[0] * bucket, slots=[-1] * bucket, q_lens=[1] * bucket,
+                ctx_lens=[0] * bucket, block_rows=[[]] * bucket, logit_rows=list(range(bucket)), is_decode=True)
+        fb.max_ctx = self.settings.capacity
+        fb.upload()
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.model.forward(fb, self.kv)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.model.forward(fb, self.kv)
+        g.graph, g.batch, g.out = graph, fb, out
+        self.graphs[key] = g
+        self.stats["captures"] += 1
+        log_json("graph_capture", bucket=bucket, ms=(time.perf_counter() - t0) * 1e3, verbose_only=True)
+        return g
+
+    def decode(self, seqs: list[Sequence]) -> list[int]:
+        """One decode step for the given sequences (each must have a pending token)."""
+        self._check()
+        if self.fail_next_step:
+            self.fail_next_step = False
+            self.poisoned = True
+            raise RuntimeError("injected step failure")
+        try:
+            n = len(seqs)
+            bucket = bucket_for(n)
+            for s in seqs:
+                if self.kv.seqs[s.seq_id].length + 1 > self.settings.capacity:
+                    raise OutOfBlocks(f"sequence {s.seq_id} reached the KV capacity {self.settings.capacity}")
+            if self.use_graph:
+                g = self.capture(bucket)
+                fb = g.batch
+                self._fill_decode(fb, seqs, bucket)
+                fb.upload()
+                g.graph.replay()
+                out = g.out
+                self.stats["graph_replays"] += 1
+            else:
+                fb = self._decode_batch(bucket)
+                self._fill_decode(fb, seqs, bucket)
+                fb.upload()
+                out = self.model.forward(fb, self.kv)
+            toks = [int(t) for t in out[:n].cpu().tolist()]
+            self.stats["h2d_bytes"] += fb.h2d_bytes()
+            self.stats["d2h_bytes"] += 4 * bucket
+            self._after_sync()
+            for s, t in zip(seqs, toks):
+                self.kv.commit(s.seq_id, 1)
+                s.pending = t
+                s.output.append(t)
+            self.stats["decode_steps"] += 1
+            self.stats["decode_tokens"] += n
+            return toks
+        except Exception:
+            self.poisoned = True
+            raise
+
+    def _after_sync(self) -> None:
+        """Runs right after a device-to-host read (an existing sync point): surface device status."""
+        if self.device.type == "cuda":
+            code = ops.read_status(self.device)
+            if code[0] != 0:
+                raise ops.DeviceStatusError(*code)
+
+    # -- convenience ---------------------------------------------------------------------------
+    def generate(self, prompts: list[list[int]], max_new_tokens: int, eos: int | None = None,
+                 ignore_eos: bool = True, on_token=None) -> list[list[int]]:
+        """Greedy generation for a batch of prompts; returns the generated ids per prompt
+        (``generated[0]`` is the token emitted by prefill, as in the reference's ``generate``)."""
+        seqs = [self.add_sequence(p) for p in prompts]
+        try:
+            self.prefill(seqs)
+            if on_token:
+                for s in seqs:
+                    on_token(s.seq_id, s.output[-1])
+            live = list(seqs)
+            while live:
+                live = [s for s in live if len(s.output) < max_new_tokens and
+                        not (not ignore_eos and eos is not None and s.output[-1] == eos)]
+                if not live:
+                    break
+                toks = self.decode(live)
+                if on_token:
+                    for s, t in zip(live, toks):
+                        on_token(s.seq_id, t)
+            return [list(s.output) for s in seqs]
+        finally:
+            for s in seqs:
+                self.free_sequence(s.seq_id)

@@ -1,0 +1,135 @@
+"""GQA decoder (Llama / Qwen3 / tiny-MoE / Qwen3-MoE shapes) on the operator API.
+
+Layer program (the reference's dense Llama program, src/backend/cuda/engine.rs:2776-3330):
+
+    embed+rmsnorm -> per layer { QKV linear -> RoPE + paged KV write -> attention -> O linear
+    -> add+rmsnorm -> gate/up linear (+SwiGLU in the epilogue) -> down linear -> add+rmsnorm }
+    -> lm_head on the selected rows -> argmax
+
+The residual stream and the normalised activations are separate buffers; with tensor
+parallelism the row-parallel projections (O, down) end in an all-reduce supplied by the
+``comm`` object (fused into the GEMM kernel when the symmetric-memory path is active), the
+QKV / gate-up / lm_head projections are column-parallel and the final argmax merges
+vocabulary shards.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from ..config import ModelSpec
+from ..engine.batch import ForwardBatch
+from ..engine.kv_cache import PagedKVCache
+from .weights import ModelWeights
+from . import moe as moe_mod
+
+
+class NoComm:
+    """Single-rank stand-in for the tensor-parallel communicator."""
+    rank, size = 0, 1
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def row_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, w)
+
+    def all_gather_cat(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+
+class DecoderModel:
+    def __init__(self, weights: ModelWeights, comm=None, trace=None):
+        self.w = weights
+        self.spec: ModelSpec = weights.spec
+        self.comm = comm or NoComm()
+        tp = weights.tp.size
+        self.hq = self.spec.heads // tp
+        self.hkv = max(1, self.spec.kv_heads // tp)
+        self.d = self.spec.head_dim
+        self.scale = 1.0 / math.sqrt(self.d)
+        self.trace = trace           # optional flyingfish_b200.utils.trace.Trace
+        self.capture_taps: dict[int, int] = {}    # layer index -> tap slot for draft-model hidden taps
+        self.capture_slab: torch.Tensor | None = None
+
+    # -- pieces ----------------------------------------------------------------------------
+    def _attention(self, i: int, n: torch.Tensor, b: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
+        lw, s = self.w.layers[i], self.spec
+        qkv = ops.linear(n, lw.wqkv)
+        if s.qk_norm:
+            self._qk_norm(qkv, lw)
+        ops.rope_kv_paged(qkv, b.positions, b.slots, kv.k[i], kv.v[i], self.hq, self.hkv, self.d, s.rope_theta)
+        if b.is_decode:
+            a = ops.attn_decode(qkv, kv.k[i], kv.v[i], b.block_table, b.ctx_lens, self.hq, self.hkv, self.d,
+                                self.scale, nq=b.nq, tree_mask=b.tree_mask, max_ctx=b.max_ctx)
+        else:
+            a = ops.attn_prefill(qkv, kv.k[i], kv.v[i], b.block_table, b.q_start, b.q_lens, b.ctx_lens, b.max_q_len,
+                                 self.hq, self.hkv, self.d, self.scale)
+        if self.trace is not None:
+            self.trace.record(f"layer.{i}.attn", a)
+        return self.comm.row_linear(a, lw.wo)
+
+    def _qk_norm(self, qkv: torch.Tensor, lw) -> None:
+        rows = qkv.shape[0]
+        q = qkv[:, : self.hq * self.d].reshape(rows * self.hq, self.d)
+        k = qkv[:, self.hq * self.d: (self.hq + self.hkv) * self.d].reshape(rows * self.hkv, self.d)
+        qn = ops.rmsnorm(q.contiguous(), lw.q_norm, self.spec.rms_eps)
+        kn = ops.rmsnorm(k.contiguous(), lw.k_norm, self.spec.rms_eps)
+        qkv[:, : self.hq * self.d] = qn.view(rows, -1)
+        qkv[:, self.hq * self.d: (self.hq + self.hkv) * self.d] = kn.view(rows, -1)
+
+    def _ffn(self, i: int, n: torch.Tensor) -> torch.Tensor:
+        lw = self.w.layers[i]
+        if lw.router is not None:
+            return moe_mod.moe_ffn(self, i, n)
+        if lw.wgu_interleaved:
+            hmid = ops.linear_swiglu(n, lw.wgu, mode=self.spec.swiglu_mode)
+        else:
+            hmid = ops.silu_mul(ops.linear(n, lw.wgu), mode=self.spec.swiglu_mode)
+        return self.comm.row_linear(hmid, lw.wdown)
+
+    # -- forward ---------------------------------------------------------------------------
+    def hidden_states(self, b: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
+        """Runs all layers; returns the final-normed activations [rows, hidden]."""
+        w, s = self.w, self.spec
+        x, n = ops.embed_rmsnorm(b.ids, w.embed, w.layers[0].input_ln, s.rms_eps)
+        if self.trace is not None:
+            self.trace.record("embed", x)
+        for i in range(s.layers):
+            lw = w.layers[i]
+            o = self._attention(i, n, b, kv)
+            n = ops.add_rmsnorm(o, x, lw.post_ln, s.rms_eps)
+            dn = self._ffn(i, n)
+            next_w = w.layers[i + 1].input_ln if i + 1 < s.layers else w.final_norm
+            cap = None
+            if i in self.capture_taps and self.capture_slab is not None:
+                cap = self.capture_slab[: x.shape[0], self.capture_taps[i]]
+            n = ops.add_rmsnorm(dn, x, next_w, s.rms_eps, capture=cap)
+            if self.trace is not None:
+                self.trace.record(f"layer.{i}", x)
+        self.last_residual = x
+        return n
+
+    def logits(self, n: torch.Tensor, b: ForwardBatch) -> torch.Tensor:
+        """lm_head on the rows named by ``b.logit_rows`` -> [n_rows, local vocab]."""
+        sel = n.index_select(0, b.logit_rows.long()) if b.n_logit_rows != n.shape[0] else n
+        return ops.linear(sel.contiguous(), self.w.lm_head)
+
+    def greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        tp = self.w.tp
+        if tp.size == 1:
+            return ops.argmax_rows(logits)
+        vals = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+        ids = ops.argmax_rows(logits, id_offset=self.w.vocab_shard[0], out_vals=vals)
+        return self.comm.argmax_merge(vals, ids)
+
+    def forward(self, b: ForwardBatch, kv: PagedKVCache, return_logits: bool = False) -> torch.Tensor:
+        n = self.hidden_states(b, kv)
+        lg = self.logits(n, b)
+        if self.trace is not None:
+            self.trace.record("logits", lg)
+        if return_logits:
+            return self.comm.all_gather_cat(lg) if self.w.tp.size > 1 else lg
+        return self.greedy(lg)

@@ -1,0 +1,38 @@
+"""Mixture-of-experts feed-forward block at model level.
+
+Routing -> expert FFNs -> deterministic combine (+ shared expert). The semantics follow the
+reference's MoE row oracle (src/backend/cuda/moe/reference.rs:332-605): top-k with ties to the
+lower expert id, FP32 renormalised weights, contributions summed in ascending expert id and
+rounded once, shared expert added afterwards. With expert parallelism the ``ep`` communicator of
+the model dispatches token rows to the ranks that own the selected experts and combines their
+outputs (see :mod:`flyingfish_b200.parallel.ep`).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import moe_ops
+
+
+def moe_ffn(model, layer: int, n: torch.Tensor) -> torch.Tensor:
+    lw = model.w.layers[layer]
+    moe = model.spec.moe
+    weights, ids = moe_ops.route(n, lw.router, moe.top_k, moe.score, lw.router_bias, moe.n_groups, moe.topk_groups,
+                                 moe.routed_scaling, moe.renormalize)
+    if getattr(model, "route_hook", None) is not None:
+        model.route_hook(layer, ids, weights)
+    ep = getattr(model, "ep", None)
+    if ep is not None and ep.size > 1:
+        routed = ep.dispatch_ffn_combine(n, weights, ids, lw, model.spec.swiglu_mode)
+    else:
+        provider = getattr(model, "expert_provider", None)
+        if provider is not None:
+            routed = provider.forward(layer, n, weights, ids)
+        else:
+            routed = moe_ops.experts_forward(n, weights, ids, lw.experts_gu, lw.experts_down, model.spec.swiglu_mode)
+    if lw.shared_gu is not None:
+        sh = ops.silu_mul(ops.linear(n, lw.shared_gu), mode=model.spec.swiglu_mode)
+        shared = model.comm.row_linear(sh, lw.shared_down)
+        routed = moe_ops.add_shared(routed, shared)
+    return routed

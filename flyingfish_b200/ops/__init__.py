@@ -1,0 +1,409 @@
+"""Operator API of the framework.
+
+Every function takes PyTorch tensors. On a CUDA device the hand-written sm_100a kernel runs
+(through ``_ff_kernels.so``; a missing library is an error, never a silent fallback); on a CPU
+tensor the plain PyTorch oracle from :mod:`flyingfish_b200.ops.ref` runs, which is how the tiny
+host-only configuration and the CPU test-suite execute the same model code.
+
+Host-side contract checks (shapes, strides, dtypes, alignment) happen here before a launch, in
+the spirit of the reference's typed tensor views (src/backend/cuda/contracts.rs:81-139); the
+kernels report what only the device can see (bad token ids, bad block ids, timed-out waits)
+through the status word (:func:`flyingfish_b200.ops.lib.check_status`).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from . import ref
+from .lib import DeviceStatusError, KernelError, check, check_status, kernels, ptr, read_status, status_tensor, stream_ptr
+
+__all__ = [
+    "linear", "linear_swiglu", "rmsnorm", "add_rmsnorm", "embed_rmsnorm", "embed", "rope_kv_paged", "silu_mul",
+    "attn_decode", "attn_prefill", "argmax_rows", "sample_rows", "residual_add", "softcap", "check_status",
+    "read_status", "KernelError", "DeviceStatusError", "launch_count", "reset_launch_count",
+]
+
+BF16 = torch.bfloat16
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of kernel launches issued through this module since the last reset."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def _count(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def _is_cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _rows2d(t: torch.Tensor) -> tuple[int, int]:
+    _require(t.dim() == 2 and t.stride(1) == 1, "expected a 2-D tensor with unit inner stride")
+    return t.shape[0], t.stride(0)
+
+
+# ------------------------------------------------------------------------------------------
+# workspace (split-K partials, attention split partials): one per device, grown outside of
+# graph capture only
+# ------------------------------------------------------------------------------------------
+class _Workspace:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.gemm_scratch = torch.empty(8 << 20, dtype=torch.float32, device=device)      # 32 MiB
+        self.gemm_counters = torch.zeros(4096, dtype=torch.int32, device=device)
+        self.attn_o = torch.empty(4 << 20, dtype=torch.float32, device=device)             # 16 MiB
+        self.attn_ml = torch.empty(1 << 18, dtype=torch.float32, device=device)
+
+    def ensure(self, name: str, numel: int) -> torch.Tensor:
+        t = getattr(self, name)
+        if t.numel() < numel:
+            _require(not torch.cuda.is_current_stream_capturing(), f"workspace {name} too small during graph capture")
+            t = torch.empty(int(numel * 1.25), dtype=t.dtype, device=self.device)
+            setattr(self, name, t)
+        return t
+
+
+_workspaces: dict[int, _Workspace] = {}
+
+
+def workspace(device: torch.device) -> _Workspace:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None:
+        ws = _Workspace(torch.device("cuda", idx))
+        _workspaces[idx] = ws
+    return ws
+
+
+# ------------------------------------------------------------------------------------------
+# linear
+# ------------------------------------------------------------------------------------------
+SKINNY_MAX_M = 128
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+           out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``y[M,N] = x[M,K] @ w[N,K].T`` (BF16 operands, FP32 accumulation).
+
+    CUDA path: tcgen05 kernels of ``csrc/gemm_bf16.cu`` -- the swap-AB split-K kernel for
+    M <= 128, the persistent 128x256x64 kernel otherwise."""
+    if not _is_cuda(x):
+        y = ref.linear(x, w, out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    _require(x.dtype == BF16 and w.dtype == BF16, "linear: BF16 operands required on CUDA")
+    m, ldx = _rows2d(x)
+    n, ldw = _rows2d(w)
+    k = x.shape[1]
+    _require(w.shape[1] == k, "linear: inner dimensions differ")
+    odt = out_dtype or BF16
+    if out is None:
+        out = torch.empty(m, n, dtype=odt, device=x.device)
+    _require(out.shape == (m, n) and out.stride(1) == 1 and out.dtype == odt, "linear: bad output tensor")
+    lib = kernels()
+    st = status_tensor(x.device)
+    if m <= SKINNY_MAX_M and odt == BF16:
+        scratch_b, counter_b = c_longlong(0), c_longlong(0)
+        splits = lib.ff_gemm_skinny_plan(m, n, k, ctypes.byref(scratch_b), ctypes.byref(counter_b))
+        ws = workspace(x.device)
+        scratch = ws.ensure("gemm_scratch", scratch_b.value // 4) if splits > 1 else None
+        _require(counter_b.value // 4 <= ws.gemm_counters.numel(), "linear: too many column tiles for counters")
+        rc = lib.ff_gemm_skinny(ptr(x), ptr(w), ptr(out), m, n, k, ldx, ldw, out.stride(0), splits, ptr(scratch),
+                                ptr(ws.gemm_counters), ptr(st), stream_ptr())
+        check(rc, "ff_gemm_skinny")
+    else:
+        epi = 0 if odt == BF16 else 2
+        _require(odt in (BF16, torch.float32), "linear: output dtype must be bf16 or fp32")
+        rc = lib.ff_gemm_bf16(ptr(x), ptr(w), ptr(out), m, n, k, ldx, ldw, out.stride(0), epi, ptr(st), stream_ptr())
+        check(rc, "ff_gemm_bf16")
+    _count()
+    return out
+
+
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor | None = None,
+                  mode: int = 0) -> torch.Tensor:
+    """Gate/up projection with the SwiGLU activation fused into the GEMM epilogue. The weight is
+    the per-128 interleaved ``[2f, h]`` matrix built by :func:`ref.interleave_gate_up`."""
+    if not _is_cuda(x):
+        return ref.linear_swiglu(x, w_interleaved, mode)
+    m, ldx = _rows2d(x)
+    n, ldw = _rows2d(w_interleaved)
+    k = x.shape[1]
+    _require(n % 256 == 0 and mode == 0, "linear_swiglu: N must be a multiple of 256 and mode 0")
+    if m <= SKINNY_MAX_M:
+        # decode shapes: two small kernels beat a 128-row tile that is mostly padding
+        gu = linear(x, w_interleaved)
+        return silu_mul_interleaved(gu, out)
+    if out is None:
+        out = torch.empty(m, n // 2, dtype=BF16, device=x.device)
+    rc = kernels().ff_gemm_bf16(ptr(x), ptr(w_interleaved), ptr(out), m, n, k, ldx, ldw, out.stride(0), 1,
+                                ptr(status_tensor(x.device)), stream_ptr())
+    check(rc, "ff_gemm_bf16(swiglu)")
+    _count()
+    return out
+
+
+def silu_mul_interleaved(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """SwiGLU on the per-128 interleaved gate/up layout produced by the fused weight."""
+    m, n = gu.shape
+    g = gu.view(m, n // 256, 2, 128)
+    # strided views: gate = g[:, :, 0], up = g[:, :, 1]; materialise as [gate | up] then reuse silu_mul
+    packed = torch.cat([g[:, :, 0].reshape(m, n // 2), g[:, :, 1].reshape(m, n // 2)], dim=1)
+    return silu_mul(packed, out=out)
+
+
+# ------------------------------------------------------------------------------------------
+# norms / embedding
+# ------------------------------------------------------------------------------------------
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, unit_offset: bool = False,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    if not _is_cuda(x):
+        return ref.rmsnorm(x, w, eps, unit_offset)
+    rows, ldx = _rows2d(x)
+    hidden = x.shape[1]
+    _require(x.dtype == BF16 and w.dtype == BF16 and w.numel() == hidden, "rmsnorm: bad operands")
+    if out is None:
+        out = torch.empty(rows, hidden, dtype=BF16, device=x.device)
+    rc = kernels().ff_rmsnorm(ptr(x), ptr(w), ptr(out), rows, hidden, ldx, c_float(eps), int(unit_offset),
+                              ptr(status_tensor(x.device)), stream_ptr())
+    check(rc, "ff_rmsnorm")
+    _count()
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, res: torch.Tensor, w: torch.Tensor, eps: float, unit_offset: bool = False,
+                out: torch.Tensor | None = None, capture: torch.Tensor | None = None) -> torch.Tensor:
+    """``res += x`` (rounded to the storage dtype, in place) and returns ``rmsnorm(res) * w``.
+    ``capture`` ([rows, hidden] view of a ``[rows, taps, hidden]`` slab) also receives the new
+    residual for a draft model's hidden-state taps."""
+    if not _is_cuda(x):
+        new_res, n = ref.add_rmsnorm(x, res, w, eps, unit_offset)
+        res.copy_(new_res)
+        if capture is not None:
+            capture.copy_(new_res)
+        return n
+    rows, ldx = _rows2d(x)
+    hidden = x.shape[1]
+    _require(res.is_contiguous() and res.shape == (rows, hidden), "add_rmsnorm: residual must be contiguous")
+    if out is None:
+        out = torch.empty(rows, hidden, dtype=BF16, device=x.device)
+    cstride = capture.stride(0) if capture is not None else 0
+    rc = kernels().ff_add_rmsnorm(ptr(x), ptr(res), ptr(w), ptr(out), ptr(capture), cstride, rows, hidden, ldx,
+                                  c_float(eps), int(unit_offset), ptr(status_tensor(x.device)), stream_ptr())
+    check(rc, "ff_add_rmsnorm")
+    _count()
+    return out
+
+
+def embed_rmsnorm(ids: torch.Tensor, table: torch.Tensor, w: torch.Tensor, eps: float, unit_offset: bool = False
+                  ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Embedding gather fused with the first layer's RMSNorm: returns (residual, normalised)."""
+    if not _is_cuda(table):
+        return ref.embed_rmsnorm(ids, table, w, eps, unit_offset)
+    rows = ids.numel()
+    vocab, hidden = table.shape
+    _require(ids.dtype == torch.int32 and ids.is_contiguous(), "embed_rmsnorm: ids must be contiguous int32")
+    res = torch.empty(rows, hidden, dtype=BF16, device=table.device)
+    out = torch.empty(rows, hidden, dtype=BF16, device=table.device)
+    rc = kernels().ff_embed_rmsnorm(ptr(ids), ptr(table), ptr(w), ptr(res), ptr(out), rows, hidden, vocab,
+                                    c_float(eps), int(unit_offset), ptr(status_tensor(table.device)), stream_ptr())
+    check(rc, "ff_embed_rmsnorm")
+    _count()
+    return res, out
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    if not _is_cuda(table):
+        x = table[ids.long()]
+        return x if scale == 1.0 else (x.to(torch.float32) * scale).to(table.dtype)
+    rows = ids.numel()
+    vocab, hidden = table.shape
+    out = torch.empty(rows, hidden, dtype=BF16, device=table.device)
+    rc = kernels().ff_embed(ptr(ids), ptr(table), ptr(out), rows, hidden, vocab, c_float(scale),
+                            ptr(status_tensor(table.device)), stream_ptr())
+    check(rc, "ff_embed")
+    _count()
+    return out
+
+
+def residual_add(res: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    if not _is_cuda(res):
+        res.copy_((res.to(torch.float32) + x.to(torch.float32)).to(res.dtype))
+        return res
+    _require(res.is_contiguous() and x.is_contiguous() and res.numel() == x.numel(), "residual_add: contiguous only")
+    check(kernels().ff_residual_add(ptr(res), ptr(x), c_longlong(res.numel()), stream_ptr()), "ff_residual_add")
+    _count()
+    return res
+
+
+# ------------------------------------------------------------------------------------------
+# rope + kv write, activation
+# ------------------------------------------------------------------------------------------
+def rope_kv_paged(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, kcache: torch.Tensor,
+                  vcache: torch.Tensor, hq: int, hkv: int, dim: int, theta: float, rot_dim: int | None = None,
+                  inv_freq: torch.Tensor | None = None) -> None:
+    """In place on ``qkv`` ([rows, (hq+2*hkv)*dim], Q and K rotated) and the paged cache."""
+    if not _is_cuda(qkv):
+        ref.rope_kv_paged(qkv, positions, slots, kcache, vcache, hq, hkv, dim, theta, rot_dim, inv_freq)
+        return
+    rows, ld = _rows2d(qkv)
+    _require(qkv.shape[1] >= (hq + 2 * hkv) * dim, "rope_kv_paged: packed row too short")
+    _require(positions.dtype == torch.int32 and slots.dtype == torch.int32, "rope_kv_paged: int32 metadata")
+    _require(kcache.is_contiguous() and vcache.is_contiguous() and kcache.dim() == 4, "rope_kv_paged: cache layout")
+    nb, ch, bs, cd = kcache.shape
+    _require(ch == hkv and cd == dim, "rope_kv_paged: cache geometry differs from the heads")
+    rc = kernels().ff_rope_kv_paged(ptr(qkv), ptr(positions), ptr(slots), ptr(kcache), ptr(vcache), ptr(inv_freq),
+                                    rows, hq, hkv, dim, rot_dim or dim, bs, nb, c_float(theta), ld,
+                                    ptr(status_tensor(qkv.device)), stream_ptr())
+    check(rc, "ff_rope_kv_paged")
+    _count()
+
+
+def silu_mul(gu: torch.Tensor, mode: int = 0, limit: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    if not _is_cuda(gu):
+        return ref.silu_mul(gu, mode, limit)
+    rows, ld = _rows2d(gu)
+    f = gu.shape[1] // 2
+    if out is None:
+        out = torch.empty(rows, f, dtype=BF16, device=gu.device)
+    rc = kernels().ff_silu_mul(ptr(gu), ptr(out), rows, f, ld, out.stride(0), mode, c_float(limit), stream_ptr())
+    check(rc, "ff_silu_mul")
+    _count()
+    return out
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    if not _is_cuda(x):
+        return ref.softcap(x, cap)
+    _require(x.is_contiguous() and x.dtype == BF16, "softcap: contiguous bf16")
+    check(kernels().ff_softcap(ptr(x), c_longlong(x.numel()), c_float(cap), stream_ptr()), "ff_softcap")
+    _count()
+    return x
+
+
+# ------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------
+def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                ctx_lens: torch.Tensor, hq: int, hkv: int, dim: int, scale: float, nq: int = 1,
+                tree_mask: torch.Tensor | None = None, max_ctx: int | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """Decode / multi-row verify attention. ``q`` holds ``batch * nq`` rows (heads at columns
+    ``h*dim``; it may be the packed QKV buffer). ``ctx_lens[b]`` counts the keys visible to the last
+    of the ``nq`` rows. Returns ``[batch*nq, hq*dim]``."""
+    batch = block_table.shape[0]
+    if not _is_cuda(q):
+        q_start = torch.arange(batch, dtype=torch.int32) * nq
+        q_lens = torch.full((batch,), nq, dtype=torch.int32)
+        return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale,
+                                   tree_mask)
+    rows, ldq = _rows2d(q)
+    _require(rows == batch * nq, "attn_decode: q rows must equal batch * nq")
+    _require(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attn_decode: block table int32")
+    _require(ctx_lens.dtype == torch.int32, "attn_decode: ctx_lens int32")
+    nb = kcache.shape[0]
+    _require(kcache.shape[2] == 64 and kcache.shape[3] == dim == 128, "attn_decode: block 64 / head_dim 128 only")
+    if max_ctx is None:
+        max_ctx = block_table.shape[1] * 64
+    lib = kernels()
+    po, pml = c_longlong(0), c_longlong(0)
+    nsplit = lib.ff_attn_decode_plan(batch, hq, hkv, nq, max_ctx, ctypes.byref(po), ctypes.byref(pml))
+    ws = workspace(q.device)
+    part_o = ws.ensure("attn_o", po.value // 4) if nsplit > 1 else None
+    part_ml = ws.ensure("attn_ml", pml.value // 4) if nsplit > 1 else None
+    if out is None:
+        out = torch.empty(rows, hq * dim, dtype=BF16, device=q.device)
+    if tree_mask is not None:
+        _require(tree_mask.dtype == torch.int64 and tree_mask.numel() == batch * nq, "attn_decode: tree mask int64")
+    rc = lib.ff_attn_decode(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(tree_mask),
+                            ptr(out), ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, nq, ldq, block_table.shape[1],
+                            nb, nsplit, c_float(scale), ptr(status_tensor(q.device)), stream_ptr())
+    check(rc, "ff_attn_decode")
+    _count(2 if nsplit > 1 else 1)
+    return out
+
+
+def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                 q_start: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, max_q_len: int, hq: int,
+                 hkv: int, dim: int, scale: float, window: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal chunked-prefill attention of packed query rows against the paged cache."""
+    if not _is_cuda(q):
+        return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale,
+                                   None, window)
+    rows, ldq = _rows2d(q)
+    batch = block_table.shape[0]
+    if out is None:
+        out = torch.empty(rows, hq * dim, dtype=BF16, device=q.device)
+    nb = kcache.shape[0]
+    _require(kcache.shape[2] == 64 and dim == 128, "attn_prefill: block 64 / head_dim 128 only")
+    rc = kernels().ff_attn_prefill(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(q_start), ptr(q_lens),
+                                   ptr(ctx_lens), ptr(out), batch, max_q_len, hq, hkv, dim, ldq, out.stride(0),
+                                   block_table.shape[1], nb, c_float(scale), window, ptr(status_tensor(q.device)),
+                                   stream_ptr())
+    check(rc, "ff_attn_prefill")
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# sampling
+# ------------------------------------------------------------------------------------------
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor | None = None, id_offset: int = 0,
+                out_vals: torch.Tensor | None = None) -> torch.Tensor:
+    """Greedy token per row, ties -> lower id. ``out_vals`` additionally receives the row maxima
+    (for merging vocab-parallel shards)."""
+    if not _is_cuda(logits):
+        ids = ref.argmax_rows(logits) + id_offset
+        if out_vals is not None:
+            out_vals.copy_(logits.to(torch.float32).max(-1).values)
+        return ids
+    rows, ld = _rows2d(logits)
+    vocab = logits.shape[1]
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    dt = 0 if logits.dtype == BF16 else 1
+    _require(logits.dtype in (BF16, torch.float32), "argmax_rows: bf16 or fp32 logits")
+    rc = kernels().ff_argmax_rows(ptr(logits), ptr(out), ptr(out_vals), rows, vocab, ld, dt, id_offset, None,
+                                  ptr(status_tensor(logits.device)), stream_ptr())
+    check(rc, "ff_argmax_rows")
+    _count()
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int, step: int,
+                rep_penalty: float = 1.0, history: torch.Tensor | None = None) -> torch.Tensor:
+    """Stochastic sampler (temperature, top-k, top-p, repetition penalty, Philox4x32-10)."""
+    if not _is_cuda(logits):
+        return torch.tensor([ref.sample_row(logits[r], temperature, top_k, top_p, seed, step, r, rep_penalty,
+                                            None if history is None else history[r])
+                             for r in range(logits.shape[0])], dtype=torch.int32)
+    lg = logits.to(torch.float32).contiguous()
+    rows, vocab = lg.shape
+    work = torch.empty_like(lg)
+    out = torch.empty(rows, dtype=torch.int32, device=lg.device)
+    hl = 0 if history is None else history.shape[1]
+    rc = kernels().ff_sample_rows(ptr(lg), ptr(out), ptr(work), rows, vocab, c_float(temperature), top_k,
+                                  c_float(top_p), c_float(rep_penalty), ptr(history), hl, c_ulonglong(seed),
+                                  c_ulonglong(step), stream_ptr())
+    check(rc, "ff_sample_rows")
+    _count()
+    return out

@@ -1,0 +1,100 @@
+// Host-side helpers shared by the launchers: TMA tensor-map encoding through the driver
+// entry point (no link-time dependency on libcuda), launch error mapping, device queries.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace ff {
+
+// Launcher return codes (negative = host-side refusal, positive = cudaError_t).
+enum HostErr : int {
+  FF_HOST_OK = 0,
+  FF_HOST_BAD_SHAPE = -1,
+  FF_HOST_BAD_ALIGN = -2,
+  FF_HOST_NO_DRIVER = -3,
+  FF_HOST_TMAP_FAIL = -4,
+  FF_HOST_TOO_LARGE = -5,
+  FF_HOST_UNSUPPORTED = -6,
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [outer, inner] with `row_bytes` pitch; box [box_outer, box_inner];
+// 128-byte swizzle when the box's inner extent is exactly 128 bytes, none otherwise.
+inline int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
+                        uint64_t inner, uint64_t outer, uint64_t row_bytes, uint32_t box_inner,
+                        uint32_t box_outer, bool swizzle128 = true) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return FF_HOST_NO_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_bytes & 15)) return FF_HOST_BAD_ALIGN;
+  if (box_inner * elem_bytes > 128 && swizzle128) return FF_HOST_BAD_SHAPE;
+  if (box_outer > 256 || box_inner > 256) return FF_HOST_BAD_SHAPE;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FF_HOST_OK : FF_HOST_TMAP_FAIL;
+}
+
+// 3-D tensor [d2, d1, d0] (d0 innermost) with byte strides for d1 and d2.
+inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
+                        uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes, uint64_t stride2_bytes,
+                        uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128 = true) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return FF_HOST_NO_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (stride1_bytes & 15) || (stride2_bytes & 15)) return FF_HOST_BAD_ALIGN;
+  if (b0 * elem_bytes > 128 && swizzle128) return FF_HOST_BAD_SHAPE;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FF_HOST_OK : FF_HOST_TMAP_FAIL;
+}
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+inline int launch_result() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FF_HOST_OK : static_cast<int>(e);
+}
+
+template <typename K>
+inline int opt_in_smem(K kernel, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  return e == cudaSuccess ? FF_HOST_OK : static_cast<int>(e);
+}
+
+}  // namespace ff
+
+#define FF_EXPORT extern "C" __attribute__((visibility("default")))

@@ -1,0 +1,111 @@
+"""ctypes binding of the native libraries.
+
+``kernels()`` returns the handle of ``_ff_kernels.so`` (CUDA launchers), ``host()`` the handle of
+``_ff_host.so`` (CPU expert FFN, direct-IO reader). Both are built in-tree by
+:mod:`flyingfish_b200.ops.build`; if a library is missing it is compiled on first use, and if that
+is impossible on a machine that has a GPU the import fails loudly -- there is no silent PyTorch
+fallback for the CUDA path.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+_lock = threading.Lock()
+_kernels: ctypes.CDLL | None = None
+_host: ctypes.CDLL | None = None
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or the CUDA runtime reported a launch error."""
+
+
+_HOST_ERR = {
+    -1: "bad shape", -2: "bad alignment", -3: "CUDA driver entry point unavailable",
+    -4: "tensor-map encode failed", -5: "size beyond the supported maximum", -6: "unsupported configuration",
+}
+
+
+def kernels() -> ctypes.CDLL:
+    global _kernels
+    if _kernels is None:
+        with _lock:
+            if _kernels is None:
+                from . import build
+                path = build.build_kernels()
+                _kernels = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+    return _kernels
+
+
+def host() -> ctypes.CDLL:
+    global _host
+    if _host is None:
+        with _lock:
+            if _host is None:
+                from . import build
+                path = build.build_host()
+                if path is None:
+                    raise KernelError("native host library has no sources")
+                _host = ctypes.CDLL(str(path))
+    return _host
+
+
+def check(rc: int, name: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{name}: {_HOST_ERR.get(rc, 'host error')} ({rc})")
+    raise KernelError(f"{name}: CUDA error {rc}")
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# ------------------------------------------------------------------------------------------
+# Device status word: int32[4] = (code, kernel id, detail0, detail1) per device.
+# ------------------------------------------------------------------------------------------
+_status: dict[int, torch.Tensor] = {}
+
+STATUS_CODES = {0: "ok", 1: "timeout", 2: "contract", 3: "bounds", 4: "non-finite", 5: "capacity"}
+
+
+class DeviceStatusError(RuntimeError):
+    def __init__(self, code: int, kernel: int, d0: int, d1: int):
+        super().__init__(f"device status: {STATUS_CODES.get(code, code)} from kernel id {kernel} "
+                         f"(detail {d0}, {d1})")
+        self.code, self.kernel, self.detail = code, kernel, (d0, d1)
+
+
+def status_tensor(device: torch.device | int | None = None) -> torch.Tensor:
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev is None:
+        dev = torch.cuda.current_device()
+    t = _status.get(dev)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+        _status[dev] = t
+    return t
+
+
+def read_status(device=None, clear: bool = True) -> tuple[int, int, int, int]:
+    """Synchronising read of the status word (call at an existing sync point)."""
+    t = status_tensor(device)
+    vals = tuple(int(v) for v in t.cpu().tolist())
+    if clear and vals[0] != 0:
+        t.zero_()
+    return vals  # type: ignore[return-value]
+
+
+def check_status(device=None) -> None:
+    code, kid, d0, d1 = read_status(device)
+    if code != 0:
+        raise DeviceStatusError(code, kid, d0, d1)
