@@ -1,0 +1,210 @@
+"""Numerics of every CUDA operator against the plain PyTorch FP32 oracle of the same op."""
+import math
+
+import pytest
+import torch
+
+from flyingfish_b200 import ops
+from flyingfish_b200.ops import ref
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+def _rand(shape, seed, scale=1.0, device="cuda"):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(BF16).to(device)
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{bad} / {a.numel()} mismatches, max err {err.max().item():.4g}"
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 64), (16, 384, 128), (64, 4096, 4096), (128, 1024, 512),
+                                   (7, 6144, 4096), (33, 128256 // 8, 1024)])
+def test_gemm_skinny(m, n, k):
+    x, w = _rand((m, k), 1), _rand((n, k), 2, 0.05)
+    y = ops.linear(x, w)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(y, ref.linear(x.cpu(), w.cpu()))
+
+
+@pytest.mark.parametrize("m,n,k", [(129, 256, 64), (256, 512, 256), (1000, 768, 320), (2048, 4096, 4096),
+                                   (300, 1000, 136)])
+def test_gemm_large(m, n, k):
+    x, w = _rand((m, k), 3), _rand((n, k), 4, 0.05)
+    y = ops.linear(x, w)
+    torch.cuda.synchronize()
+    ops.check_status()
+    _close(y, ref.linear(x.cpu(), w.cpu()))
+
+
+def test_gemm_fp32_out():
+    x, w = _rand((200, 256), 5), _rand((512, 256), 6, 0.05)
+    y = ops.linear(x, w, out_dtype=torch.float32)
+    ops.check_status()
+    _close(y, x.float().cpu() @ w.float().cpu().t(), 1e-3, 1e-3)
+
+
+def test_gemm_deterministic_and_repeatable():
+    x, w = _rand((48, 4096), 7), _rand((4096, 4096), 8, 0.05)
+    a = ops.linear(x, w).clone()
+    b = ops.linear(x, w).clone()
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("m", [8, 300])
+def test_gemm_swiglu(m):
+    f, h = 512, 256
+    x = _rand((m, h), 9)
+    wg, wu = _rand((f, h), 10, 0.05), _rand((f, h), 11, 0.05)
+    wi = ref.interleave_gate_up(wg, wu)
+    y = ops.linear_swiglu(x, wi)
+    ops.check_status()
+    expect = ref.silu_mul(torch.cat([ref.linear(x.cpu(), wg.cpu()), ref.linear(x.cpu(), wu.cpu())], dim=1))
+    _close(y, expect)
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 4096), (64, 4096), (5, 7168), (3, 256), (2, 8192)])
+def test_norms(rows, hidden):
+    x, res, w = _rand((rows, hidden), 12), _rand((rows, hidden), 13), _rand((hidden,), 14)
+    n = ops.rmsnorm(x, w, 1e-5)
+    _close(n, ref.rmsnorm(x.cpu(), w.cpu(), 1e-5), 1e-2, 1e-2)
+    res2 = res.clone()
+    n2 = ops.add_rmsnorm(x, res2, w, 1e-5)
+    er, en = ref.add_rmsnorm(x.cpu(), res.cpu(), w.cpu(), 1e-5)
+    assert torch.equal(res2.cpu(), er), "residual must be bit-exact (one BF16 rounding of the sum)"
+    _close(n2, en, 1e-2, 1e-2)
+    ops.check_status()
+
+
+def test_embed_rmsnorm_and_bad_id_status():
+    vocab, hidden = 1000, 512
+    table, w = _rand((vocab, hidden), 15), _rand((hidden,), 16)
+    ids = torch.tensor([0, 5, 999, 17], dtype=torch.int32, device="cuda")
+    x, n = ops.embed_rmsnorm(ids, table, w, 1e-6)
+    ex, en = ref.embed_rmsnorm(ids.cpu(), table.cpu(), w.cpu(), 1e-6)
+    assert torch.equal(x.cpu(), ex)
+    _close(n, en, 1e-2, 1e-2)
+    ops.check_status()
+    # a token id outside the table is reported through the status word, not by a fault
+    bad = torch.tensor([3, 1000], dtype=torch.int32, device="cuda")
+    ops.embed_rmsnorm(bad, table, w, 1e-6)
+    code, kid, d0, d1 = ops.read_status()
+    assert code == 3 and d0 == 1 and d1 == 1000
+    assert ops.read_status()[0] == 0
+
+
+def test_rope_kv_paged():
+    rows, hq, hkv, d, bs, nb = 37, 4, 2, 128, 64, 6
+    qkv = _rand((rows, (hq + 2 * hkv) * d), 17)
+    pos = torch.arange(100, 100 + rows, dtype=torch.int32, device="cuda")
+    slots = (torch.arange(rows, dtype=torch.int32) + 70).to("cuda")
+    slots[3] = -1
+    kc = torch.zeros(nb, hkv, bs, d, dtype=BF16, device="cuda"); vc = torch.zeros_like(kc)
+    q2, kc2, vc2 = qkv.cpu().clone(), kc.cpu().clone(), vc.cpu().clone()
+    ops.rope_kv_paged(qkv, pos, slots, kc, vc, hq, hkv, d, 5e5)
+    ref.rope_kv_paged(q2, pos.cpu(), slots.cpu(), kc2, vc2, hq, hkv, d, 5e5)
+    ops.check_status()
+    # BF16 arithmetic contract: allow one ULP from fast sin/cos differences
+    _close(qkv[:, : (hq + hkv) * d], q2[:, : (hq + hkv) * d], 1e-2, 1e-2)
+    _close(kc, kc2, 1e-2, 1e-2)
+    assert torch.equal(vc.cpu(), vc2)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_silu_mul(mode):
+    gu = _rand((9, 2 * 1024), 18, 2.0)
+    _close(ops.silu_mul(gu, mode=mode), ref.silu_mul(gu.cpu(), mode=mode), 1e-2, 1e-3)
+
+
+def test_argmax_ties_lower_id():
+    lg = _rand((5, 5000), 19)
+    lg[0, 10] = 100.0; lg[0, 4000] = 100.0
+    lg[1, :] = 0.0
+    ids = ops.argmax_rows(lg)
+    assert ids.cpu().tolist() == ref.argmax_rows(lg.cpu()).tolist()
+    assert ids[0].item() == 10 and ids[1].item() == 0
+    ops.check_status()
+
+
+def _fill_cache(nb, hkv, d, seed):
+    kc = _rand((nb, hkv, 64, d), seed)
+    vc = _rand((nb, hkv, 64, d), seed + 1)
+    return kc, vc
+
+
+@pytest.mark.parametrize("batch,hq,hkv,ctxs", [(1, 4, 1, [1]), (3, 8, 2, [5, 64, 200]), (2, 32, 8, [1024, 777]),
+                                                (4, 8, 1, [130, 64, 63, 65])])
+def test_attn_decode(batch, hq, hkv, ctxs):
+    d = 128
+    max_blocks = 20
+    nb = batch * max_blocks
+    kc, vc = _fill_cache(nb, hkv, d, 20)
+    perm = torch.randperm(nb, generator=torch.Generator().manual_seed(3)).to(torch.int32)
+    bt = perm.view(batch, max_blocks).contiguous().cuda()
+    ctx = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+    q = _rand((batch, (hq + 2 * hkv) * d), 22)
+    out = ops.attn_decode(q, kc, vc, bt, ctx, hq, hkv, d, 1 / math.sqrt(d), max_ctx=max_blocks * 64)
+    ops.check_status()
+    expect = ref.attention_paged(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), torch.arange(batch, dtype=torch.int32),
+                                 torch.ones(batch, dtype=torch.int32), ctx.cpu(), hq, hkv, d, 1 / math.sqrt(d))
+    _close(out, expect, 2e-2, 2e-2)
+
+
+def test_attn_decode_multirow_causal_and_tree():
+    d, hq, hkv, batch, nq = 128, 4, 1, 2, 4
+    max_blocks = 4
+    kc, vc = _fill_cache(batch * max_blocks, hkv, d, 30)
+    bt = torch.arange(batch * max_blocks, dtype=torch.int32).view(batch, max_blocks).cuda()
+    ctx = torch.tensor([70, 133], dtype=torch.int32, device="cuda")
+    q = _rand((batch * nq, hq * d), 32)
+    qs = torch.arange(batch, dtype=torch.int32) * nq
+    ql = torch.full((batch,), nq, dtype=torch.int32)
+    out = ops.attn_decode(q, kc, vc, bt, ctx, hq, hkv, d, 0.088, nq=nq)
+    expect = ref.attention_paged(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), qs, ql, ctx.cpu(), hq, hkv, d, 0.088)
+    _close(out, expect, 2e-2, 2e-2)
+    # tree: row 0 root, rows 1 and 2 children of 0, row 3 child of 1
+    masks = torch.tensor([[0b0001, 0b0011, 0b0101, 0b1011]] * batch, dtype=torch.int64)
+    out = ops.attn_decode(q, kc, vc, bt, ctx, hq, hkv, d, 0.088, nq=nq, tree_mask=masks.cuda())
+    expect = ref.attention_paged(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), qs, ql, ctx.cpu(), hq, hkv, d, 0.088,
+                                 tree_mask=masks)
+    _close(out, expect, 2e-2, 2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("qlens,pasts", [([64], [0]), ([100, 7, 129], [0, 64, 30]), ([300], [200])])
+def test_attn_prefill(qlens, pasts):
+    d, hq, hkv = 128, 4, 2
+    batch = len(qlens)
+    max_blocks = 10
+    kc, vc = _fill_cache(batch * max_blocks, hkv, d, 40)
+    bt = torch.arange(batch * max_blocks, dtype=torch.int32).view(batch, max_blocks).cuda()
+    ql = torch.tensor(qlens, dtype=torch.int32)
+    qs = torch.cumsum(ql, 0).to(torch.int32) - ql
+    ctx = ql + torch.tensor(pasts, dtype=torch.int32)
+    rows = int(ql.sum())
+    q = _rand((rows, (hq + 2 * hkv) * d), 42)
+    out = ops.attn_prefill(q, kc, vc, bt, qs.cuda(), ql.cuda(), ctx.cuda(), max(qlens), hq, hkv, d, 0.088)
+    ops.check_status()
+    expect = ref.attention_paged(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), qs, ql, ctx, hq, hkv, d, 0.088)
+    _close(out, expect, 2e-2, 2e-2)
+
+
+def test_sampler_matches_host_reference():
+    torch.manual_seed(0)
+    lg = (torch.randn(4, 3000) * 3).cuda()
+    for (t, k, p) in [(0.7, 50, 0.9), (1.0, 0, 0.5), (1.3, 5, 1.0)]:
+        got = ops.sample_rows(lg, t, k, p, seed=1234, step=7)
+        probs = [ref.sampling_probs(lg[r].cpu(), t, k, p) for r in range(4)]
+        for r in range(4):
+            assert probs[r][int(got[r])] > 0, "sampled id must lie in the kept set"
+    # determinism
+    a = ops.sample_rows(lg, 0.8, 40, 0.95, seed=5, step=1)
+    b = ops.sample_rows(lg, 0.8, 40, 0.95, seed=5, step=1)
+    assert torch.equal(a, b)
