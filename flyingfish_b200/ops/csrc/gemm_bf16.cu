@@ -434,3 +434,60 @@ FF_EXPORT int ff_gemm_skinny(const void* X, const void* W, void* Y, int M, int N
                                     scratch, counters, status);
   return launch_result();
 }
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of the decode-shape GEMM (declared in ff_noalloc.h).
+//
+// Some callers cannot obtain device memory at the point where they need this GEMM: code that
+// runs inside a memory-budgeted plugin or a real-time serving loop whose allocator is frozen
+// after start-up, or a host that simply has no allocator handle to give us (a C caller that
+// only owns its input and output buffers). For them the split-K partial sums and the per-tile
+// arrival counters live in a fixed array inside this library instead of caller scratch.
+//
+//  * Limit: splits * M * N * 4 bytes must fit in FF_NOALLOC_SCRATCH_BYTES (8 MiB) and
+//    ceil(N/128) in FF_NOALLOC_MAX_TILES (2048); larger problems are refused with
+//    FF_HOST_TOO_LARGE. Every GPU that loads this library holds the 8 MiB until exit.
+//  * The first call on a device resolves the device addresses of the arrays
+//    (cudaGetSymbolAddress, with that device current) and caches them; make that first call
+//    before starting any stream capture.
+//  * All calls share the one array: two calls that may overlap on the GPU (different streams,
+//    no ordering between them) race on it. Calls on one stream are safe. The counters are
+//    cleared by every call before the kernel runs, so a call does not depend on how the
+//    previous one ended.
+//  * No cudaMalloc / cudaFree / allocating library routine is called here.
+// ---------------------------------------------------------------------------------------
+#include "ff_noalloc.h"
+
+namespace ff {
+static __device__ __align__(256) float g_noalloc_scratch[FF_NOALLOC_SCRATCH_BYTES / 4];
+static __device__ __align__(256) int g_noalloc_counters[FF_NOALLOC_MAX_TILES];
+
+struct NoAllocPtrs { float* scratch; int* counters; bool ready; };
+static NoAllocPtrs g_noalloc_ptrs[64] = {};
+}  // namespace ff
+
+FF_EXPORT int ff_gemm_skinny_noalloc(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
+                                     int ldy, int* status, cudaStream_t stream) {
+  if (M <= 0 || M > 256 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
+  long long scratch_bytes = 0, counter_bytes = 0;
+  const int splits = ff_gemm_skinny_plan(M, N, K, &scratch_bytes, &counter_bytes);
+  if (scratch_bytes > (long long)FF_NOALLOC_SCRATCH_BYTES || counter_bytes > (long long)FF_NOALLOC_MAX_TILES * 4)
+    return FF_HOST_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return FF_HOST_UNSUPPORTED;
+  NoAllocPtrs& p = g_noalloc_ptrs[dev];
+  if (!p.ready) {
+    // In host code the array names are host-side stand-ins; the kernel needs the device address.
+    void* ps = nullptr; void* pc = nullptr;
+    e = cudaGetSymbolAddress(&ps, g_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaGetSymbolAddress(&pc, g_noalloc_counters);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    p.scratch = static_cast<float*>(ps); p.counters = static_cast<int*>(pc); p.ready = true;
+  }
+  e = cudaMemsetAsync(p.counters, 0, (size_t)counter_bytes, stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return ff_gemm_skinny(X, W, Y, M, N, K, ldx, ldw, ldy, splits, p.scratch, p.counters, status, stream);
+}
