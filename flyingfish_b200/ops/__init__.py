@@ -162,13 +162,9 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tenso
     return out
 
 
-def silu_mul_interleaved(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+def silu_mul_interleaved(gu: torch.Tensor, out: torch.Tensor | None = None, mode: int = 0) -> torch.Tensor:
     """SwiGLU on the per-128 interleaved gate/up layout produced by the fused weight."""
-    m, n = gu.shape
-    g = gu.view(m, n // 256, 2, 128)
-    # strided views: gate = g[:, :, 0], up = g[:, :, 1]; materialise as [gate | up] then reuse silu_mul
-    packed = torch.cat([g[:, :, 0].reshape(m, n // 2), g[:, :, 1].reshape(m, n // 2)], dim=1)
-    return silu_mul(packed, out=out)
+    return silu_mul(gu, mode=mode, out=out, interleaved=True)
 
 
 # ------------------------------------------------------------------------------------------
@@ -278,14 +274,19 @@ def rope_kv_paged(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tenso
     _count()
 
 
-def silu_mul(gu: torch.Tensor, mode: int = 0, limit: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
+def silu_mul(gu: torch.Tensor, mode: int = 0, limit: float = 0.0, out: torch.Tensor | None = None,
+             interleaved: bool = False) -> torch.Tensor:
     if not _is_cuda(gu):
+        if interleaved:
+            m, n = gu.shape
+            g = gu.view(m, n // 256, 2, 128)
+            gu = torch.cat([g[:, :, 0].reshape(m, n // 2), g[:, :, 1].reshape(m, n // 2)], dim=1)
         return ref.silu_mul(gu, mode, limit)
     rows, ld = _rows2d(gu)
     f = gu.shape[1] // 2
     if out is None:
         out = torch.empty(rows, f, dtype=BF16, device=gu.device)
-    rc = kernels().ff_silu_mul(ptr(gu), ptr(out), rows, f, ld, out.stride(0), mode, c_float(limit), stream_ptr())
+    rc = kernels().ff_silu_mul(ptr(gu), ptr(out), rows, f, ld, out.stride(0), mode, c_float(limit), int(interleaved), stream_ptr())
     check(rc, "ff_silu_mul")
     _count()
     return out

@@ -379,7 +379,9 @@ FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ct
   const int pages = (max_ctx + PAGE - 1) / PAGE;
   const int ctas = batch * hkv;
   int nsplit = 1;
-  const int target = 148 * 3;              // three 64-KiB CTAs fit on one SM
+  // three 64-KiB CTAs fit on one SM; aim for at least four full waves so the ragged last wave
+  // costs little
+  const int target = 148 * 3 * 4;
   if (ctas < target) nsplit = (target + ctas - 1) / ctas;
   if (nsplit > pages) nsplit = pages;
   if (nsplit < 1) nsplit = 1;

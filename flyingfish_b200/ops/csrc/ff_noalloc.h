@@ -11,8 +11,9 @@
 // Rules for the caller:
 //   * X, W, Y are device pointers owned by the caller; ldx/ldw/ldy are row pitches in elements
 //     (multiples of 8); `status` may be null or point to int32[4] in device memory.
-//   * splits*M*N*4 bytes must fit in FF_NOALLOC_SCRATCH_BYTES and ceil(N/128) in
-//     FF_NOALLOC_MAX_TILES; otherwise the call returns -5 and launches nothing.
+//   * The partial-sum slots (2 * grid * M * 128 * 4 bytes, grid = ff_gemm_skinny_plan(M, N, K) <= 148)
+//     must fit in FF_NOALLOC_SCRATCH_BYTES and ceil(N/128) in FF_NOALLOC_MAX_TILES; otherwise the
+//     call returns -5 and launches nothing.
 //   * The first call on each device looks up the array's device address; issue it before any
 //     stream capture begins on that device.
 //   * All calls share the array, so calls that can overlap on the GPU race; order them on one

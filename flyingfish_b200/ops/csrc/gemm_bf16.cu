@@ -16,6 +16,7 @@
 // This replaces the reference's cuBLAS/cuBLASLt calls (src/backend/cuda/blas.rs:852-1080)
 // and its mma.sync skinny kernel (kernels/gemm_skinny.cu).
 #include "ptx.cuh"
+#include "comm.cuh"
 #include "host_util.h"
 
 namespace ff {
@@ -228,137 +229,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
-// ---------------------------------------------------------------------------------------
-// Decode-shape kernel: swap-AB + split-K.
-//   D[n (128 TMEM lanes), t (ntok columns)] = W[n, k-range] · X[t, k-range]ᵀ
-// grid = (ceil(N/128), splits). scratch: fp32 [splits][M][N]; counters: int32 [ceil(N/128)],
-// zero before the first launch, left zero by every launch.
-// ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(192, 1)
-gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                   __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldy, int ntok, int splits, int STAGES,
-                   float* __restrict__ scratch, int* __restrict__ counters, int* status) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ PipeBars bars;
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int A_BYTES = BM * BK * 2;
-  const int b_bytes = ntok * BK * 2;
-  const int stage_bytes = A_BYTES + b_bytes;
-  uint32_t tmem_cols = 32; while ((int)tmem_cols < ntok) tmem_cols <<= 1;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tn = blockIdx.x, split = blockIdx.y;
-  const int kblocks_total = (K + BK - 1) / BK;
-  const int per = (kblocks_total + splits - 1) / splits;
-  const int kb0 = split * per;
-  const int kb1 = min(kblocks_total, kb0 + per);
-  const int nkb = max(0, kb1 - kb0);
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.empty[i], 1); }
-    mbar_init(&bars.tmem_full[0], 1);
-    bars.abort_flag = 0; bars.is_last = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) { tmem_alloc(&bars.tmem_base, tmem_cols); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = bars.tmem_base;
-  volatile int* abort_flag = &bars.abort_flag;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX);
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES; const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag, status, KID_GEMM_SKINNY, 1)) break;
-        mbar_expect_tx(&bars.full[s], stage_bytes);
-        uint8_t* sa = smem + s * stage_bytes;
-        tma_load_2d(sa, &tmW, &bars.full[s], (kb0 + i) * BK, tn * BM);
-        tma_load_2d(sa + A_BYTES, &tmX, &bars.full[s], (kb0 + i) * BK, 0);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc(1, 1, 0, 0, BM, ntok);
-      bool ok = true;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES; const uint32_t ph = (i / STAGES) & 1;
-        if (!mbar_wait(&bars.full[s], ph, abort_flag, status, KID_GEMM_SKINNY, 3)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sa = smem_u32(smem + s * stage_bytes);
-        const uint64_t da = umma_desc_sw128(sa, 16, 1024);
-        const uint64_t db = umma_desc_sw128(sa + A_BYTES, 16, 1024);
-#pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
-        umma_commit(&bars.empty[s]);
-      }
-      if (ok) umma_commit(&bars.tmem_full[0]);
-    }
-  } else {
-    const int q = warp & 3;
-    const int n = tn * BM + q * 32 + lane;
-    bool ok = true;
-    if (nkb > 0) ok = mbar_wait(&bars.tmem_full[0], 0, abort_flag, status, KID_GEMM_SKINNY, 4);
-    tc_fence_after();
-    const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
-    if (ok) {
-      if (splits == 1) {
-        for (int c = 0; c < ntok; c += 16) {
-          uint32_t r[16];
-          tmem_ld_x16(taddr + c, r);
-          tmem_ld_wait();
-          if (n < N) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c + j < M) Y[(size_t)(c + j) * ldy + n] = __float2bfloat16(__uint_as_float(r[j]));
-          }
-        }
-      } else {
-        float* part = scratch + (size_t)split * M * N;
-        for (int c = 0; c < ntok; c += 16) {
-          uint32_t r[16];
-          if (nkb > 0) { tmem_ld_x16(taddr + c, r); tmem_ld_wait(); }
-          else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = 0u;
-          }
-          if (n < N) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c + j < M) part[(size_t)(c + j) * N + n] = __uint_as_float(r[j]);
-          }
-        }
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const int prev = atomicAdd(&counters[tn], 1);
-          bars.is_last = (prev == splits - 1);
-          if (prev == splits - 1) counters[tn] = 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (bars.is_last) {
-          __threadfence();
-          if (n < N) {
-            for (int t = 0; t < M; ++t) {
-              float acc = 0.f;
-              for (int s = 0; s < splits; ++s) acc += __ldcg(scratch + ((size_t)s * M + t) * N + n);
-              Y[(size_t)t * ldy + n] = __float2bfloat16(acc);
-            }
-          }
-        }
-      }
-    }
-    tc_fence_before();
-  }
-
-  __syncthreads();
-  if (bars.abort_flag) {
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
-  }
-  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, tmem_cols); }
-}
 
 }  // namespace ff
 
@@ -391,103 +261,3 @@ FF_EXPORT int ff_gemm_bf16(const void* X, const void* W, void* Y, int M, int N, 
   return launch_result();
 }
 
-// Scratch requirement of the decode-shape kernel for a given problem:
-// returns the number of splits it will use; *scratch_bytes / *counter_bytes are what the
-// caller must provide (scratch may be null when the answer is 1 split).
-FF_EXPORT int ff_gemm_skinny_plan(int M, int N, int K, long long* scratch_bytes, long long* counter_bytes) {
-  const int tiles_n = (N + BM - 1) / BM;
-  const int kblocks = (K + BK - 1) / BK;
-  int splits = 1;
-  const int sms = 148;
-  if (tiles_n < sms) {
-    splits = (sms + tiles_n - 1) / tiles_n;
-    // keep at least 4 k-blocks (one pipeline fill) per split
-    const int max_splits = kblocks / 4 > 0 ? kblocks / 4 : 1;
-    if (splits > max_splits) splits = max_splits;
-    if (splits > 16) splits = 16;
-  }
-  if (scratch_bytes) *scratch_bytes = splits > 1 ? (long long)splits * M * N * 4 : 0;
-  if (counter_bytes) *counter_bytes = (long long)tiles_n * 4;
-  return splits;
-}
-
-FF_EXPORT int ff_gemm_skinny(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
-                             int splits, float* scratch, int* counters, int* status, cudaStream_t stream) {
-  if (M <= 0 || M > 256 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
-  if ((K % 8) || (ldx % 8) || (ldw % 8)) return FF_HOST_BAD_ALIGN;
-  if (splits < 1 || (splits > 1 && (scratch == nullptr || counters == nullptr))) return FF_HOST_BAD_SHAPE;
-  const int ntok = (M + 15) / 16 * 16;
-  CUtensorMap tmW, tmX;
-  int r = make_tmap_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, BK, BM);
-  if (r) return r;
-  r = make_tmap_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, (uint64_t)ldx * 2, BK, ntok);
-  if (r) return r;
-  const int stage_bytes = BM * BK * 2 + ntok * BK * 2;
-  int stages = (200 * 1024) / stage_bytes;
-  if (stages > 8) stages = 8;
-  const int smem = stages * stage_bytes + 1024;
-  auto kern = gemm_skinny_kernel;
-  static bool attr_done = false;
-  if (!attr_done) { r = opt_in_smem(kern, 200 * 1024 + 1024); if (r) return r; attr_done = true; }
-  dim3 grid((N + BM - 1) / BM, splits);
-  kern<<<grid, 192, smem, stream>>>(tmW, tmX, reinterpret_cast<__nv_bfloat16*>(Y), M, N, K, ldy, ntok, splits, stages,
-                                    scratch, counters, status);
-  return launch_result();
-}
-
-// ---------------------------------------------------------------------------------------
-// Allocation-free variant of the decode-shape GEMM (declared in ff_noalloc.h).
-//
-// Some callers cannot obtain device memory at the point where they need this GEMM: code that
-// runs inside a memory-budgeted plugin or a real-time serving loop whose allocator is frozen
-// after start-up, or a host that simply has no allocator handle to give us (a C caller that
-// only owns its input and output buffers). For them the split-K partial sums and the per-tile
-// arrival counters live in a fixed array inside this library instead of caller scratch.
-//
-//  * Limit: splits * M * N * 4 bytes must fit in FF_NOALLOC_SCRATCH_BYTES (8 MiB) and
-//    ceil(N/128) in FF_NOALLOC_MAX_TILES (2048); larger problems are refused with
-//    FF_HOST_TOO_LARGE. Every GPU that loads this library holds the 8 MiB until exit.
-//  * The first call on a device resolves the device addresses of the arrays
-//    (cudaGetSymbolAddress, with that device current) and caches them; make that first call
-//    before starting any stream capture.
-//  * All calls share the one array: two calls that may overlap on the GPU (different streams,
-//    no ordering between them) race on it. Calls on one stream are safe. The counters are
-//    cleared by every call before the kernel runs, so a call does not depend on how the
-//    previous one ended.
-//  * No cudaMalloc / cudaFree / allocating library routine is called here.
-// ---------------------------------------------------------------------------------------
-#include "ff_noalloc.h"
-
-namespace ff {
-static __device__ __align__(256) float g_noalloc_scratch[FF_NOALLOC_SCRATCH_BYTES / 4];
-static __device__ __align__(256) int g_noalloc_counters[FF_NOALLOC_MAX_TILES];
-
-struct NoAllocPtrs { float* scratch; int* counters; bool ready; };
-static NoAllocPtrs g_noalloc_ptrs[64] = {};
-}  // namespace ff
-
-FF_EXPORT int ff_gemm_skinny_noalloc(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
-                                     int ldy, int* status, cudaStream_t stream) {
-  if (M <= 0 || M > 256 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
-  long long scratch_bytes = 0, counter_bytes = 0;
-  const int splits = ff_gemm_skinny_plan(M, N, K, &scratch_bytes, &counter_bytes);
-  if (scratch_bytes > (long long)FF_NOALLOC_SCRATCH_BYTES || counter_bytes > (long long)FF_NOALLOC_MAX_TILES * 4)
-    return FF_HOST_TOO_LARGE;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 0 || dev >= 64) return FF_HOST_UNSUPPORTED;
-  NoAllocPtrs& p = g_noalloc_ptrs[dev];
-  if (!p.ready) {
-    // In host code the array names are host-side stand-ins; the kernel needs the device address.
-    void* ps = nullptr; void* pc = nullptr;
-    e = cudaGetSymbolAddress(&ps, g_noalloc_scratch);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    e = cudaGetSymbolAddress(&pc, g_noalloc_counters);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    p.scratch = static_cast<float*>(ps); p.counters = static_cast<int*>(pc); p.ready = true;
-  }
-  e = cudaMemsetAsync(p.counters, 0, (size_t)counter_bytes, stream);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  return ff_gemm_skinny(X, W, Y, M, N, K, ldx, ldw, ldy, splits, p.scratch, p.counters, status, stream);
-}

@@ -90,14 +90,18 @@ __device__ __forceinline__ float act_combine(float g, float u, int mode, float l
   return (g / (1.f + __expf(-g))) * u;
 }
 
+// interleaved != 0: gate/up alternate per 128 columns ([g0..g127 | u0..u127 | g128.. ]), the layout
+// produced by a weight fused for the GEMM's SwiGLU epilogue; otherwise [gate | up] halves.
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows,
-                                int f, int ldgu, int ldo, int mode, float limit) {
+                                int f, int ldgu, int ldo, int mode, float limit, int interleaved) {
   const int vec_per_row = f >> 3;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)rows * vec_per_row) return;
   const int row = (int)(gid / vec_per_row), c = (int)(gid % vec_per_row);
-  const uint4 g = reinterpret_cast<const uint4*>(gu + (size_t)row * ldgu)[c];
-  const uint4 u = reinterpret_cast<const uint4*>(gu + (size_t)row * ldgu + f)[c];
+  const int gc = interleaved ? ((c >> 4) * 32 + (c & 15)) : c;          // 16 vectors per 128 columns
+  const int uc = interleaved ? gc + 16 : c + vec_per_row;
+  const uint4 g = reinterpret_cast<const uint4*>(gu + (size_t)row * ldgu)[gc];
+  const uint4 u = reinterpret_cast<const uint4*>(gu + (size_t)row * ldgu)[uc];
   const uint32_t* gp = reinterpret_cast<const uint32_t*>(&g);
   const uint32_t* up = reinterpret_cast<const uint32_t*>(&u);
   uint4 o; uint32_t* op = reinterpret_cast<uint32_t*>(&o);
@@ -319,11 +323,12 @@ FF_EXPORT int ff_rope_kv_paged(void* qkv, const int* positions, const int* slots
 }
 
 FF_EXPORT int ff_silu_mul(const void* gu, void* out, int rows, int f, int ldgu, int ldo, int mode, float limit,
-                          cudaStream_t s) {
+                          int interleaved, cudaStream_t s) {
   if (rows <= 0 || f <= 0 || f % 8 || ldgu % 8 || ldo % 8) return FF_HOST_BAD_SHAPE;
+  if (interleaved && f % 128) return FF_HOST_BAD_SHAPE;
   const long long total = (long long)rows * (f / 8);
   silu_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows,
-                                                                   f, ldgu, ldo, mode, limit);
+                                                                   f, ldgu, ldo, mode, limit, interleaved);
   return launch_result();
 }
 

@@ -1,0 +1,195 @@
+"""Tensor-parallel communicator.
+
+The reference has no distributed runtime at all (its only multi-GPU feature bounces one layer's
+activations through pinned host memory, src/backend/cuda/engine_moe.rs:1643-1830, and forbids
+direct peer access, src/backend/cuda/mod.rs:448-484). On an NVSwitch box every GPU can store
+into every peer at full NVLink bandwidth, so this build does the opposite:
+
+* plumbing (rendezvous, barriers, large collectives, baseline path): ``torch.distributed`` over
+  NCCL (``gloo`` on CPU for the host-side tests);
+* hot path: one arena of *symmetric memory* per rank, mapped into every peer, and hand-written
+  kernels that push tiles / vectors into peers' arenas with plain stores and poll local flags
+  (``csrc/comm.cuh``). ``row_linear`` runs the row-parallel projection and its all-reduce as ONE
+  kernel (``ff_gemm_ar``) at decode sizes.
+
+A start-up self-test writes a rank-specific pattern into every peer's arena and verifies what
+arrived (the reference verifies its transport the same way, src/backend/cuda/mod.rs:487-664).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_longlong, c_ulonglong
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import lib as oplib
+from ..utils.log import log_json
+
+SLOT_BYTES = 4 << 20          # one source-rank slot: 256 rows x 8192 columns of BF16
+
+
+class TransportError(RuntimeError):
+    pass
+
+
+class SymmArena:
+    """Symmetric per-rank buffer with peer mappings (``torch.distributed._symmetric_memory``)."""
+
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, slot_bytes: int = SLOT_BYTES):
+        import torch.distributed._symmetric_memory as symm
+        self.group, self.device = group, device
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        lib = oplib.kernels()
+        lib.ff_arena_data_offset.restype = c_longlong
+        self.data_off = int(lib.ff_arena_data_offset())
+        self.slot_bytes = slot_bytes
+        self.half_bytes = slot_bytes * self.world
+        total = self.data_off + 2 * self.half_bytes
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buf, group)
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.ptrs = (c_ulonglong * 8)(*(ptrs + [0] * (8 - len(ptrs))))
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+
+    def args(self) -> tuple:
+        return (self.ptrs, self.rank, self.world, c_longlong(self.half_bytes), c_longlong(self.slot_bytes))
+
+    def self_test(self, words: int = 1 << 16) -> None:
+        """Every rank writes a pattern into its slot on every peer; every rank verifies all slots,
+        then verifies that a planted single-word flip IS detected."""
+        lib = oplib.kernels()
+        s = oplib.stream_ptr()
+        bad = torch.zeros(1, dtype=torch.int32, device=self.device)
+        oplib.check(lib.ff_transport_fill(*self.args(), words, 0x5EED, s), "ff_transport_fill")
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        oplib.check(lib.ff_transport_verify(*self.args(), words, 0x5EED, oplib.ptr(bad), s), "ff_transport_verify")
+        n_bad = int(bad.item())
+        if n_bad:
+            raise TransportError(f"rank {self.rank}: {n_bad} corrupted words in the peer transport self-test")
+        # negative control: flip one word locally, the verifier must see exactly one mismatch
+        off = self.data_off + ((self.rank + 1) % self.world) * self.slot_bytes + 4 * 123
+        self.buf[off] ^= 0x40
+        bad.zero_()
+        oplib.check(lib.ff_transport_verify(*self.args(), words, 0x5EED, oplib.ptr(bad), s), "ff_transport_verify")
+        if int(bad.item()) != 1:
+            raise TransportError("transport self-test did not detect a planted corruption")
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        # leave the data area clean (flags/epoch untouched: they were not used)
+        self.buf[self.data_off:].zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+
+class TPComm:
+    """Tensor-parallel group: fused peer-memory kernels on CUDA, plain collectives on CPU."""
+
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, arena: SymmArena | None):
+        self.group, self.device, self.arena = group, device, arena
+        self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
+        self.fused = arena is not None
+        self.stats = {"gemm_ar": 0, "oneshot_ar": 0, "nccl_ar": 0}
+
+    @classmethod
+    def create(cls, group: dist.ProcessGroup, device: torch.device | str, fused: bool = True,
+               self_test: bool = True) -> "TPComm":
+        device = torch.device(device)
+        arena = None
+        if device.type == "cuda" and fused and dist.get_world_size(group) > 1:
+            arena = SymmArena(group, device)
+            if self_test:
+                arena.self_test()
+            log_json("cuda_peer_topology", verbose_only=True, rank=arena.rank, world=arena.world,
+                     transport="symmetric_memory_p2p", multicast=bool(arena.multicast_ptr))
+        return cls(group, device, arena)
+
+    # -- collectives --------------------------------------------------------------------------
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.size == 1:
+            return x
+        if self.fused and x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0 \
+                and x.numel() * 2 <= self.arena.slot_bytes:
+            out = torch.empty_like(x)
+            rc = oplib.kernels().ff_allreduce_oneshot(*self.arena.args(), oplib.ptr(x), oplib.ptr(out),
+                                                      c_longlong(x.numel()), oplib.ptr(oplib.status_tensor(x.device)),
+                                                      oplib.stream_ptr())
+            oplib.check(rc, "ff_allreduce_oneshot")
+            self.stats["oneshot_ar"] += 1
+            ops._count()
+            return out
+        if x.dtype in (torch.bfloat16, torch.float16) and not x.is_cuda:
+            y = x.to(torch.float32)                      # gloo has no 16-bit reductions on every build
+            dist.all_reduce(y, group=self.group)
+            return y.to(x.dtype)
+        dist.all_reduce(x, group=self.group)
+        self.stats["nccl_ar"] += 1
+        return x
+
+    def row_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Row-parallel projection: ``sum_r x_r @ w_r.T``. One fused kernel at decode sizes."""
+        if self.size == 1:
+            return ops.linear(x, w)
+        m, n = x.shape[0], w.shape[0]
+        if self.fused and x.is_cuda and m <= ops.SKINNY_MAX_M and n % 8 == 0 and m * n * 2 <= self.arena.slot_bytes:
+            lib = oplib.kernels()
+            k = x.shape[1]
+            sb, cb = c_longlong(0), c_longlong(0)
+            grid = lib.ff_gemm_skinny_plan(m, n, k, ctypes.byref(sb), ctypes.byref(cb))
+            ws = ops.workspace(x.device)
+            scratch = ws.ensure("gemm_scratch", sb.value // 4) if grid > 1 else None
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+            rc = lib.ff_gemm_ar(*self.arena.args(), oplib.ptr(x), oplib.ptr(w), oplib.ptr(out), m, n, k, x.stride(0),
+                                w.stride(0), n, grid, oplib.ptr(scratch), oplib.ptr(ws.gemm_counters),
+                                oplib.ptr(oplib.status_tensor(x.device)), oplib.stream_ptr())
+            oplib.check(rc, "ff_gemm_ar")
+            self.stats["gemm_ar"] += 1
+            ops._count()
+            return out
+        return self.all_reduce(ops.linear(x, w))
+
+    def all_gather_cat(self, x: torch.Tensor) -> torch.Tensor:
+        """Concatenate equally-shaped shards along the last dim."""
+        if self.size == 1:
+            return x
+        parts = [torch.empty_like(x) for _ in range(self.size)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def argmax_merge(self, vals: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """Merge vocabulary-parallel greedy candidates: (row max, global id) per rank -> global
+        argmax with ties to the lower id."""
+        rows = vals.numel()
+        if self.fused and vals.is_cuda and rows * 8 <= self.arena.slot_bytes:
+            pad = (rows + 3) // 4 * 4
+            packed = torch.zeros(2 * pad, dtype=torch.int32, device=vals.device)
+            packed[:rows] = vals.view(torch.int32)
+            packed[pad: pad + rows] = ids
+            gathered = torch.empty(self.size, 2 * pad, dtype=torch.int32, device=vals.device)
+            lib = oplib.kernels()
+            rc = lib.ff_allgather_push(*self.arena.args(), oplib.ptr(packed), oplib.ptr(gathered), packed.numel() * 4,
+                                       oplib.ptr(oplib.status_tensor(vals.device)), oplib.stream_ptr())
+            oplib.check(rc, "ff_allgather_push")
+            all_vals = gathered[:, :rows].contiguous().view(torch.float32)
+            all_ids = gathered[:, pad: pad + rows].contiguous()
+            out = torch.empty(rows, dtype=torch.int32, device=vals.device)
+            oplib.check(lib.ff_argmax_merge(oplib.ptr(all_vals), oplib.ptr(all_ids), oplib.ptr(out), self.size, rows,
+                                            oplib.stream_ptr()), "ff_argmax_merge")
+            ops._count(2)
+            return out
+        vs = [torch.empty_like(vals) for _ in range(self.size)]
+        is_ = [torch.empty_like(ids) for _ in range(self.size)]
+        dist.all_gather(vs, vals, group=self.group)
+        dist.all_gather(is_, ids, group=self.group)
+        v, i = torch.stack(vs), torch.stack(is_)
+        best = v.max(0).values
+        cand = torch.where(v == best[None], i, torch.full_like(i, 2 ** 31 - 1))
+        return cand.min(0).values.to(torch.int32)
+
+    def barrier(self) -> None:
+        dist.barrier(self.group)

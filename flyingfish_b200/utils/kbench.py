@@ -1,0 +1,148 @@
+"""Single-kernel timing harness (``python -m flyingfish_b200.utils.kbench <op> ...``).
+
+Times one operator with CUDA events on the launching stream: warm-up iterations, then timed
+iterations with an L2 flush (a write larger than L2) before each one unless the operands are
+themselves larger than L2. Prints one JSON line per case with the achieved bandwidth / FLOP rate
+and the fraction of the measured peaks of the box (``MEASURED_PEAKS.json`` at the repository root
+when present, otherwise the stated fallback). The same harness feeds the calibration step and is
+the command behind the ncu summaries under ``profiles/``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+from pathlib import Path
+
+import torch
+
+from .. import ops
+
+ROOT = Path(__file__).resolve().parents[2]
+L2_BYTES = 126 << 20
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class Flusher:
+    def __init__(self, device):
+        self.buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+
+    def __call__(self):
+        self.buf.zero_()
+
+
+def time_op(fn, iters: int, warmup: int, flush: Flusher | None) -> dict:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)      # us
+    times.sort()
+    return {"us_median": times[len(times) // 2], "us_min": times[0], "us_p90": times[int(len(times) * 0.9)]}
+
+
+def bench_gemm(args) -> dict:
+    dev = torch.device("cuda")
+    m, n, k = args.m, args.n, args.k
+    x = (torch.randn(m, k, device=dev) * 1.0).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=dev) * 0.05).to(torch.bfloat16)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    if args.torch:
+        fn = lambda: torch.matmul(x, w.t(), out=out)
+    else:
+        fn = lambda: ops.linear(x, w, out=out)
+    byts = (m * k + n * k + m * n) * 2
+    r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
+    pk = peaks()
+    t = r["us_median"] * 1e-6
+    r.update(op="gemm_torch" if args.torch else "gemm", m=m, n=n, k=k, gbs=byts / t / 1e9,
+             tflops=2.0 * m * n * k / t / 1e12)
+    r["frac_hbm"] = r["gbs"] / pk["hbm_gbs"]
+    r["frac_tensor"] = r["tflops"] / pk["bf16_tflops"]
+    r["peaks"] = pk["source"]
+    return r
+
+
+def bench_attn_decode(args) -> dict:
+    dev = torch.device("cuda")
+    b, ctx, hq, hkv, d = args.batch, args.ctx, args.hq, args.hkv, 128
+    blocks_per = (ctx + 63) // 64
+    nb = b * blocks_per
+    kc = torch.randn(nb, hkv, 64, d, device=dev).to(torch.bfloat16)
+    vc = torch.randn(nb, hkv, 64, d, device=dev).to(torch.bfloat16)
+    bt = torch.arange(nb, dtype=torch.int32, device=dev).view(b, blocks_per)
+    cl = torch.full((b,), ctx, dtype=torch.int32, device=dev)
+    q = torch.randn(b, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16)
+    fn = lambda: ops.attn_decode(q, kc, vc, bt, cl, hq, hkv, d, 1 / math.sqrt(d), max_ctx=ctx)
+    byts = 2 * b * ctx * hkv * d * 2
+    r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
+    pk = peaks()
+    r.update(op="attn_decode", batch=b, ctx=ctx, hq=hq, hkv=hkv, gbs=byts / (r["us_median"] * 1e-6) / 1e9)
+    r["frac_hbm"] = r["gbs"] / pk["hbm_gbs"]
+    r["peaks"] = pk["source"]
+    return r
+
+
+def bench_attn_prefill(args) -> dict:
+    dev = torch.device("cuda")
+    b, ctx, hq, hkv, d = args.batch, args.ctx, args.hq, args.hkv, 128
+    blocks_per = (ctx + 63) // 64
+    nb = b * blocks_per
+    kc = torch.randn(nb, hkv, 64, d, device=dev).to(torch.bfloat16)
+    vc = torch.randn(nb, hkv, 64, d, device=dev).to(torch.bfloat16)
+    bt = torch.arange(nb, dtype=torch.int32, device=dev).view(b, blocks_per)
+    ql = torch.full((b,), ctx, dtype=torch.int32, device=dev)
+    qs = (torch.arange(b, dtype=torch.int32, device=dev) * ctx)
+    q = torch.randn(b * ctx, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16)
+    fn = lambda: ops.attn_prefill(q, kc, vc, bt, qs, ql, ql, ctx, hq, hkv, d, 1 / math.sqrt(d))
+    flops = 4.0 * b * hq * d * ctx * (ctx + 1) / 2
+    r = time_op(fn, args.iters, args.warmup, None)
+    pk = peaks()
+    r.update(op="attn_prefill", batch=b, ctx=ctx, hq=hq, hkv=hkv, tflops=flops / (r["us_median"] * 1e-6) / 1e12)
+    r["frac_tensor"] = r["tflops"] / pk["bf16_tflops"]
+    r["peaks"] = pk["source"]
+    return r
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(prog="kbench")
+    sub = ap.add_subparsers(dest="op", required=True)
+    for name in ("gemm", "attn_decode", "attn_prefill"):
+        p = sub.add_parser(name)
+        p.add_argument("--iters", type=int, default=20)
+        p.add_argument("--warmup", type=int, default=3)
+        p.add_argument("--no-flush", action="store_true")
+        if name == "gemm":
+            p.add_argument("--m", type=int, default=64)
+            p.add_argument("--n", type=int, default=4096)
+            p.add_argument("--k", type=int, default=4096)
+            p.add_argument("--torch", action="store_true", help="time torch.matmul (cuBLAS) instead, as the baseline")
+        else:
+            p.add_argument("--batch", type=int, default=64)
+            p.add_argument("--ctx", type=int, default=1024)
+            p.add_argument("--hq", type=int, default=32)
+            p.add_argument("--hkv", type=int, default=8)
+    args = ap.parse_args(argv)
+    fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill}[args.op]
+    print(json.dumps(fn(args)))
+    ops.check_status()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

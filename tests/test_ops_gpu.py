@@ -208,3 +208,26 @@ def test_sampler_matches_host_reference():
     a = ops.sample_rows(lg, 0.8, 40, 0.95, seed=5, step=1)
     b = ops.sample_rows(lg, 0.8, 40, 0.95, seed=5, step=1)
     assert torch.equal(a, b)
+
+
+def test_silu_mul_interleaved_layout():
+    f, m = 512, 5
+    g, u = _rand((m, f), 50, 2.0), _rand((m, f), 51, 2.0)
+    inter = torch.cat([g.view(m, f // 128, 1, 128), u.view(m, f // 128, 1, 128)], dim=2).reshape(m, 2 * f).contiguous()
+    got = ops.silu_mul(inter, interleaved=True)
+    _close(got, ref.silu_mul(torch.cat([g, u], dim=1).cpu()), 1e-2, 1e-3)
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 28672, 4096), (64, 4096, 14336), (3, 128256, 4096), (128, 6144, 4096),
+                                   (16, 130, 64), (1, 128, 128)])
+def test_gemm_skinny_streamk_shapes(m, n, k):
+    """Shapes whose work units split unevenly over the persistent CTAs (partial tiles at both ends)."""
+    x, w = _rand((m, k), 52), _rand((n, k), 53, 0.03)
+    y = ops.linear(x, w)
+    y2 = ops.linear(x, w)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(y, y2), "stream-K fix-up must be deterministic"
+    # reference on the GPU in FP32 (the CPU matmul of the big shapes is slow)
+    expect = (x.float() @ w.float().t())
+    _close(y, expect)

@@ -1,0 +1,80 @@
+"""Worker for the tensor-parallel tests (launched with torch.distributed.run)."""
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--device", default="cpu")
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--mode", default="model")
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if args.device == "cuda":
+        torch.cuda.set_device(local)
+        device = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=device)
+    else:
+        device = torch.device("cpu")
+        dist.init_process_group("gloo")
+    from flyingfish_b200.parallel.comm import TPComm
+    from flyingfish_b200.api import Model
+    from flyingfish_b200.config import Settings
+    from flyingfish_b200 import ops
+    comm = TPComm.create(dist.group.WORLD, device)
+    result = {}
+    if args.mode == "model":
+        m = Model.load("tiny-llama", Settings(capacity=256, max_batch=4, graph=(args.device == "cuda")), device=device,
+                       seed=0, comm=comm)
+        g = torch.Generator().manual_seed(7)
+        prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (40, 9)]
+        result["tokens"] = m.generate_batch(prompts, 10)
+        result["stats"] = comm.stats
+    elif args.mode == "kernels":
+        g = torch.Generator().manual_seed(11)
+        ok = True
+        errs = []
+        for (m_, n_, k_) in [(1, 512, 256), (64, 4096, 2048), (17, 1024, 4096), (128, 256, 512)]:
+            xs = [(torch.randn(m_, k_, generator=g)).to(torch.bfloat16) for _ in range(world)]
+            ws = [(torch.randn(n_, k_, generator=g) * 0.05).to(torch.bfloat16) for _ in range(world)]
+            parts = [(xs[r].float() @ ws[r].float().t()).to(torch.bfloat16).float() for r in range(world)]
+            expect = sum(parts)
+            for rep in range(3):      # repeated launches exercise the epoch / parity protocol
+                y = comm.row_linear(xs[rank].to(device), ws[rank].to(device))
+                err = (y.float().cpu() - expect).abs().max().item()
+                errs.append(err)
+                ok = ok and err <= 0.05 + 0.02 * expect.abs().max().item()
+            v = torch.randn(m_ * n_, generator=g).to(torch.bfloat16)
+            vs = [(v.float() * (r + 1)).to(torch.bfloat16) for r in range(world)]
+            yr = comm.all_reduce(vs[rank].to(device).clone())
+            exp = sum(t.float() for t in vs)
+            err = (yr.float().cpu() - exp).abs().max().item()
+            errs.append(err)
+            ok = ok and err <= 0.05 + 0.02 * exp.abs().max().item()
+        # bitwise identical on every rank
+        y = comm.row_linear(xs[rank].to(device), ws[rank].to(device))
+        gathered = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(gathered, y)
+        same = all(torch.equal(gathered[0], t) for t in gathered)
+        if device.type == "cuda":
+            torch.cuda.synchronize()
+            ops.check_status(device)
+        result.update(ok=ok, errs=errs, same=same, stats=comm.stats)
+    if rank == 0:
+        Path(args.out).write_text(json.dumps(result))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
