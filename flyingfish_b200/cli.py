@@ -1,0 +1,362 @@
+"""``ff`` command line (``python -m flyingfish_b200.cli`` / the ``ff`` console script).
+
+Same shape as the reference's CLI (src/main.rs:19-60, 177-516): global options come BEFORE the
+subcommand (``ff --model M generate --prompt ...``), ``--model`` falls back to
+``FLYINGFISH_MODEL``, results are one JSON object on stdout, decisions are JSON lines on stderr.
+Subcommands: calibrate, generate, serve, bench, profile, inspect, tokenize, embed, verify,
+compare-prefill, compare-log, plus the speculative-decoding tools (verify-spec, bench-spec,
+profile-spec). ``--model`` accepts a checkpoint directory or one of the named random-init shapes
+(``ff inspect --shapes`` lists them).
+
+Writes never go inside a model directory or under a path component named ``models`` and never
+overwrite an existing file (src/main.rs:518-545).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+from pathlib import Path
+
+from .config import NAMED_SHAPES, Settings
+
+
+def _global_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="ff", description="flyingfish_b200 inference engine")
+    p.add_argument("--model", default=os.environ.get("FLYINGFISH_MODEL"))
+    p.add_argument("--draft-model", default=os.environ.get("FLYINGFISH_DRAFT_MODEL"))
+    p.add_argument("--device", type=int, default=0)
+    p.add_argument("--verbose", action="store_true")
+    p.add_argument("--capacity", type=int, default=4096)
+    p.add_argument("--chunk", type=int, default=None)
+    p.add_argument("--device-budget-gib", type=float, default=None)
+    p.add_argument("--tree-builder", choices=["waves", "serial"], default="waves")
+    p.add_argument("--spec-budget", choices=["chain", "tree16", "tree32", "tree64"], default="chain")
+    p.add_argument("--spec-graph", type=lambda s: s.lower() != "false", default=True)
+    p.add_argument("--prefix-cache", type=lambda s: s.lower() == "true", default=False)
+    p.add_argument("--kv-format", choices=["bf16", "affine8"], default="bf16")
+    p.add_argument("--runtime-dir", default=os.environ.get("FLYINGFISH_RUNTIME_DIR"))
+    p.add_argument("--dram-gb-s", type=float, default=6550.0)
+    p.add_argument("--gemm-tflops", type=float, default=1385.0)
+    p.add_argument("--max-batch", type=int, default=64)
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--cpu", action="store_true", help="run on the host (tiny shapes / debugging)")
+    p.add_argument("--seed", type=int, default=0)
+    sub = p.add_subparsers(dest="command", required=True)
+
+    g = sub.add_parser("generate")
+    src = g.add_mutually_exclusive_group(required=True)
+    src.add_argument("--prompt")
+    src.add_argument("--tokens")
+    src.add_argument("--tokens-file")
+    g.add_argument("--max-new-tokens", type=int, default=32)
+    g.add_argument("--graph", action="store_true")
+    g.add_argument("--mtp", type=int, default=None, choices=range(0, 5))
+    g.add_argument("--dump")
+    g.add_argument("--trace-layer", type=int, default=None)
+    g.add_argument("--ignore-eos", action="store_true")
+
+    s = sub.add_parser("serve")
+    s.add_argument("--port", type=int, default=8080)
+    s.add_argument("--mtp", type=int, default=None, choices=range(0, 5))
+    s.add_argument("--allow-sampling", action="store_true")
+
+    b = sub.add_parser("bench")
+    b.add_argument("--steps", type=int, default=256)
+    b.add_argument("--warmup", type=int, default=32)
+    b.add_argument("--runs", type=int, default=3)
+    b.add_argument("--graph", action="store_true")
+    b.add_argument("--batch", type=int, default=1)
+    b.add_argument("--prompt-tokens", type=int, default=128)
+
+    pr = sub.add_parser("profile")
+    pr.add_argument("--phase", choices=["decode", "prefill"], default="decode")
+    pr.add_argument("--prompt-tokens", type=int, default=128)
+
+    i = sub.add_parser("inspect")
+    i.add_argument("--shapes", action="store_true")
+
+    t = sub.add_parser("tokenize")
+    t.add_argument("--prompt", required=True)
+
+    c = sub.add_parser("calibrate")
+    c.add_argument("--force", action="store_true")
+
+    e = sub.add_parser("embed")
+    e.add_argument("--prompt", required=True)
+
+    v = sub.add_parser("verify")
+    v.add_argument("--trace", required=True)
+    v.add_argument("--reference", required=True)
+    v.add_argument("--limits")
+    cp = sub.add_parser("compare-prefill")
+    cp.add_argument("--trace", required=True)
+    cp.add_argument("--reference", required=True)
+    cl = sub.add_parser("compare-log")
+    cl.add_argument("--a", required=True)
+    cl.add_argument("--b", required=True)
+
+    for name in ("verify-spec", "bench-spec", "profile-spec"):
+        sp = sub.add_parser(name)
+        sp.add_argument("--prompt-tokens", type=int, default=64)
+        sp.add_argument("--max-new-tokens", type=int, default=64)
+        sp.add_argument("--mtp", type=int, default=2)
+        sp.add_argument("--strict", action="store_true")
+    return p
+
+
+def parse_tokens_arg(args) -> list[int] | None:
+    """``--tokens a,b,c`` or ``--tokens-file`` holding an array, ``{"input_ids": [...]}`` or a nested
+    first row (src/main.rs:73-97)."""
+    if getattr(args, "tokens", None):
+        return [int(x) for x in args.tokens.split(",") if x.strip()]
+    if getattr(args, "tokens_file", None):
+        data = json.loads(Path(args.tokens_file).read_text())
+        if isinstance(data, dict):
+            data = data["input_ids"]
+        if data and isinstance(data[0], list):
+            data = data[0]
+        return [int(x) for x in data]
+    return None
+
+
+def check_output_path(path: str | Path, model: str | None) -> Path:
+    p = Path(path).resolve()
+    if p.exists():
+        raise SystemExit(f"refusing to overwrite {p}")
+    if any(part == "models" for part in p.parts):
+        raise SystemExit(f"refusing to write under a 'models' directory: {p}")
+    if model and Path(model).is_dir():
+        m = Path(model).resolve()
+        if m == p or m in p.parents:
+            raise SystemExit(f"refusing to write inside the model directory: {p}")
+    return p
+
+
+def settings_from(args) -> Settings:
+    return Settings(device=args.device, capacity=args.capacity, chunk=args.chunk,
+                    device_budget_gib=args.device_budget_gib, draft_model=args.draft_model,
+                    tree_builder=args.tree_builder,
+                    spec_budget=args.spec_budget if args.draft_model else "chain",
+                    spec_graph=args.spec_graph, prefix_cache=args.prefix_cache, kv_format=args.kv_format,
+                    runtime_dir=args.runtime_dir, dram_gb_s=args.dram_gb_s, gemm_tflops=args.gemm_tflops,
+                    verbose=args.verbose, max_batch=args.max_batch, tp=args.tp)
+
+
+def resolve_mtp_depth(requested: int | None, has_mtp: bool, arch: str) -> int:
+    """Default depth 4 when the checkpoint ships MTP tensors and the architecture binds them,
+    0 for DeepSeek-style checkpoints unless asked for (src/main.rs:771-809)."""
+    if requested is not None:
+        if requested > 0 and not has_mtp:
+            raise SystemExit("--mtp given but the checkpoint has no MTP component")
+        return requested
+    if not has_mtp:
+        return 0
+    return 0 if arch == "deepseek_v3" else 4
+
+
+def _load(args):
+    import torch
+    from .api import Model
+    from .utils.log import with_verbose
+    if not args.model:
+        raise SystemExit("--model (or FLYINGFISH_MODEL) is required before the subcommand")
+    st = settings_from(args)
+    device = "cpu" if args.cpu or not torch.cuda.is_available() else f"cuda:{args.device}"
+    with with_verbose(args.verbose):
+        return Model.load(args.model, st, device=device, seed=args.seed)
+
+
+def cmd_generate(args) -> dict:
+    from .api import generate_plain
+    from .loaders.tokenizer import ByteTokenizer
+    if args.dump and args.graph:
+        raise SystemExit("--dump is incompatible with --graph")
+    if args.dump:
+        check_output_path(args.dump, args.model)
+    model = _load(args)
+    tk = model.tokenizer or ByteTokenizer(model.spec.vocab)
+    ids = parse_tokens_arg(args)
+    if ids is None:
+        ids = tk.encode(args.prompt)
+    if len(ids) + args.max_new_tokens > args.capacity:
+        raise SystemExit(f"prompt ({len(ids)}) + max-new-tokens ({args.max_new_tokens}) exceeds --capacity {args.capacity}")
+    trace = None
+    if args.dump:
+        from .utils.trace import Trace
+        trace = Trace(device=str(model.engine.device), only_layer=args.trace_layer)
+        model.engine.model.trace = trace
+    depth = resolve_mtp_depth(args.mtp, model.spec.mtp_layers > 0, model.spec.arch)
+    mode = "plain"
+    extra = {}
+    if depth > 0:
+        from .spec.mtp import generate_mtp
+        out = generate_mtp(model, ids, args.max_new_tokens, depth=depth, ignore_eos=args.ignore_eos)
+        mode = "mtp"
+        extra = {"mtp_depth": depth, "mtp_verify": out.extra.get("verify", "batched"),
+                 "accepted_per_round": out.extra.get("accepted_per_round")}
+    else:
+        out = generate_plain(model, ids, args.max_new_tokens, ignore_eos=args.ignore_eos, graph=args.graph)
+    if trace is not None:
+        trace.save(args.dump)
+    return {"input_ids": ids, "generated_ids": out.ids, "text": tk.decode(out.ids), "load_ms": model.load_ms,
+            "prefill_ms": out.prefill_ms, "capture_ms": out.capture_ms, "decode_ms": out.decode_ms,
+            "decode_steps": out.decode_steps, "decode_tok_s": out.decode_tok_s, "graph": bool(args.graph),
+            "dump": args.dump, "trace_layer": args.trace_layer, "mode": mode, **extra}
+
+
+def cmd_bench(args) -> dict:
+    """Decode benchmark with the reference's protocol (src/bench.rs:47-51, 89-93, 137-226): at least
+    200 timed steps per run after the warm-up, CUDA-event timing per step, median / p10 / p90,
+    roofline % = (decode weight bytes + KV bytes read) / time against ``--dram-gb-s``; prefill
+    tokens/s against the FLOP model and ``--gemm-tflops``."""
+    import torch
+    if args.steps < 200:
+        raise SystemExit("bench needs --steps >= 200")
+    model = _load(args)
+    eng, spec = model.engine, model.spec
+    eng.use_graph = args.graph and eng.device.type == "cuda"
+    g = torch.Generator().manual_seed(1)
+    need = args.prompt_tokens + args.warmup + args.steps + 2
+    if need > args.capacity:
+        raise SystemExit(f"bench needs --capacity >= {need}")
+    runs = []
+    prefill_tok_s = []
+    cuda = eng.device.type == "cuda"
+    for _ in range(args.runs):
+        eng.reset()
+        prompts = [torch.randint(0, spec.vocab, (args.prompt_tokens,), generator=g).tolist() for _ in range(args.batch)]
+        seqs = [eng.add_sequence(p) for p in prompts]
+        t0 = time.perf_counter()
+        eng.prefill(seqs)
+        if cuda:
+            torch.cuda.synchronize()
+        prefill_tok_s.append(args.batch * args.prompt_tokens / (time.perf_counter() - t0))
+        for _ in range(args.warmup):
+            eng.decode(seqs)
+        ms = []
+        for _ in range(args.steps):
+            if cuda:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); eng.decode(seqs); e1.record(); torch.cuda.synchronize()
+                ms.append(e0.elapsed_time(e1))
+            else:
+                t = time.perf_counter(); eng.decode(seqs); ms.append((time.perf_counter() - t) * 1e3)
+        ms.sort()
+        runs.append({"median_ms": statistics.median(ms), "p10_ms": ms[len(ms) // 10], "p90_ms": ms[len(ms) * 9 // 10]})
+        for s in seqs:
+            eng.free_sequence(s.seq_id)
+    med = statistics.median(r["median_ms"] for r in runs)
+    ctx = args.prompt_tokens + args.warmup + args.steps // 2
+    kv_bytes = args.batch * ctx * spec.layers * 2 * spec.kv_heads * spec.head_dim * 2
+    moved = spec.decode_weight_bytes() + kv_bytes
+    t_, L, h, f = args.prompt_tokens, spec.layers, spec.hidden, spec.ffn
+    flops = 2 * t_ * L * (h * spec.qkv_dim + h * h + 3 * h * f) + 2 * h * spec.vocab + 2 * h * t_ * (t_ + 1) * L
+    ptok = statistics.median(prefill_tok_s)
+    return {"model": model.name, "batch": args.batch, "steps": args.steps, "warmup": args.warmup, "runs": runs,
+            "median_ms": med, "decode_tok_s": args.batch * 1000.0 / med, "graph": eng.use_graph,
+            "decode_bytes": moved, "roofline_pct": 100.0 * (moved / (med / 1e3) / 1e9) / args.dram_gb_s,
+            "prefill_tok_s": ptok,
+            "prefill_roofline_pct": 100.0 * (flops * args.batch * ptok / (args.batch * t_) / 1e12) / args.gemm_tflops}
+
+
+def cmd_profile(args) -> dict:
+    """One decode step or one prefill bracketed by cudaProfilerStart/Stop and an NVTX range
+    (src/bench.rs:229-267, src/backend/cuda/profile.rs:5-45)."""
+    import torch
+    model = _load(args)
+    eng = model.engine
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, model.spec.vocab, (args.prompt_tokens,), generator=g).tolist()
+    cuda = eng.device.type == "cuda"
+    if args.phase == "decode":
+        model.prefill(ids)
+        model.decode()
+    if cuda:
+        torch.cuda.synchronize(); torch.cuda.profiler.start(); torch.cuda.nvtx.range_push(f"ff.{args.phase}")
+    t0 = time.perf_counter()
+    if args.phase == "decode":
+        model.decode()
+    else:
+        model.prefill(ids)
+    if cuda:
+        torch.cuda.synchronize(); torch.cuda.nvtx.range_pop(); torch.cuda.profiler.stop()
+    return {"phase": args.phase, "ms": (time.perf_counter() - t0) * 1e3}
+
+
+def cmd_inspect(args) -> dict:
+    if args.shapes:
+        return {"shapes": {k: f().to_json() for k, f in NAMED_SHAPES.items()}}
+    from .config import named_shape, read_model_spec
+    p = Path(args.model or "")
+    if p.is_dir():
+        from .loaders.checkpoint import inspect_checkpoint
+        spec = read_model_spec(p)
+        return {"spec": spec.to_json(), **inspect_checkpoint(p)}
+    return {"spec": named_shape(args.model).to_json()}
+
+
+def cmd_tokenize(args) -> dict:
+    from .loaders.tokenizer import ByteTokenizer, load_tokenizer
+    tk = (load_tokenizer(args.model) if args.model and Path(args.model).is_dir() else None) or ByteTokenizer()
+    ids = tk.encode(args.prompt)
+    return {"ids": ids, "count": len(ids)}
+
+
+def cmd_calibrate(args) -> dict:
+    from .planner.calibrate import calibrate
+    return calibrate(args.model, settings_from(args), force=args.force, cpu=args.cpu)
+
+
+def cmd_embed(args) -> dict:
+    from .loaders.tokenizer import ByteTokenizer
+    model = _load(args)
+    tk = model.tokenizer or ByteTokenizer(model.spec.vocab)
+    from .models.embedding import embed_text
+    vec = embed_text(model, tk.encode(args.prompt))
+    return {"dim": len(vec), "embedding": vec}
+
+
+def cmd_serve(args) -> None:
+    from .loaders.tokenizer import read_chat_template
+    from .serve.http import run
+    model = _load(args)
+    tmpl = read_chat_template(args.model) if Path(args.model).is_dir() else None
+    run(model, port=args.port, allow_sampling=args.allow_sampling, chat_template=tmpl)
+
+
+def cmd_verify(args) -> dict:
+    from .utils.verify import compare_traces
+    return compare_traces(args.trace, args.reference, getattr(args, "limits", None))
+
+
+def cmd_compare_log(args) -> dict:
+    from .utils.verify import compare_logs
+    return compare_logs(args.a, args.b)
+
+
+def cmd_spec(args) -> dict:
+    from .spec.drivers import run_spec_tool
+    model = _load(args)
+    return run_spec_tool(args.command, model, args.prompt_tokens, args.max_new_tokens, args.mtp, args.strict)
+
+
+def main(argv: list[str] | None = None) -> int:
+    args = _global_parser().parse_args(argv)
+    handlers = {"generate": cmd_generate, "bench": cmd_bench, "profile": cmd_profile, "inspect": cmd_inspect,
+                "tokenize": cmd_tokenize, "calibrate": cmd_calibrate, "embed": cmd_embed, "verify": cmd_verify,
+                "compare-prefill": cmd_verify, "compare-log": cmd_compare_log, "verify-spec": cmd_spec,
+                "bench-spec": cmd_spec, "profile-spec": cmd_spec}
+    if args.command == "serve":
+        cmd_serve(args)
+        return 0
+    out = handlers[args.command](args)
+    print(json.dumps(out, default=str))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -143,29 +143,24 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       ++seg_it;
       if (!mbar_wait(&bars.tmem_full[acc], aph, abort_flag, status, KID_GEMM_SKINNY, 4)) { ok = false; break; }
       tc_fence_after();
-      const int n = sg.tile * SBM + nl;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * ntok;
       const bool whole = sg.kb0 == 0 && sg.kb1 == kblocks;
       bool final_here = whole;
+      const int c16 = e & 15, r0 = e >> 4;          // cooperative layout: 16 threads per 256-byte tile row
       if (whole) {
+        // TMEM -> BF16 staging tile sT[t][128]
         for (int c = 0; c < ntok; c += 16) {
           uint32_t r[16];
           tmem_ld_x16(taddr + c, r);
           tmem_ld_wait();
-          if (FUSE_AR) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) if (c + j < M) sT[(c + j) * SBM + nl] = __float2bfloat16(__uint_as_float(r[j]));
-          } else if (n < N) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c + j < M) Y[(size_t)(c + j) * ldy + n] = __float2bfloat16(__uint_as_float(r[j]));
-          }
+          for (int j = 0; j < 16; ++j) if (c + j < M) sT[(c + j) * SBM + nl] = __float2bfloat16(__uint_as_float(r[j]));
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.tmem_empty[acc]);
       } else {
-        // partial tile: slot 2*cta + (1 if this segment starts the tile)
+        // partial tile: FP32 slot 2*cta + (1 if this segment starts the tile), layout [t][128]
         float* part = scratch + ((size_t)(2 * blockIdx.x + (sg.kb0 == 0 ? 1 : 0)) * M) * SBM;
         for (int c = 0; c < ntok; c += 16) {
           uint32_t r[16];
@@ -191,19 +186,60 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         final_here = bars.flag_a != 0;
         if (final_here) {
           __threadfence();
-          for (int t = 0; t < M; ++t) {
-            float sum = 0.f;
-            for (int c = c_first; c <= c_last; ++c)
-              sum += __ldcg(scratch + ((size_t)(2 * c + (c == c_first ? 1 : 0)) * M + t) * SBM + nl);
-            if (FUSE_AR) sT[t * SBM + nl] = __float2bfloat16(sum);
-            else if (n < N) Y[(size_t)t * ldy + n] = __float2bfloat16(sum);
+          // vectorised fix-up: each thread owns 8 columns of rows r0, r0+8, ...; four rows at a
+          // time keep eight independent 16-byte loads in flight per partial
+          for (int t0 = r0; t0 < M; t0 += 32) {
+            float a[4][8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) a[i][j] = 0.f;
+            for (int c = c_first; c <= c_last; ++c) {
+              const float* src = scratch + ((size_t)(2 * c + (c == c_first ? 1 : 0)) * M) * SBM + c16 * 8;
+              float4 v[4][2];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int t = t0 + 8 * i;
+                if (t < M) {
+                  v[i][0] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM));
+                  v[i][1] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM + 4));
+                } else { v[i][0] = make_float4(0, 0, 0, 0); v[i][1] = v[i][0]; }
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                a[i][0] += v[i][0].x; a[i][1] += v[i][0].y; a[i][2] += v[i][0].z; a[i][3] += v[i][0].w;
+                a[i][4] += v[i][1].x; a[i][5] += v[i][1].y; a[i][6] += v[i][1].z; a[i][7] += v[i][1].w;
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int t = t0 + 8 * i;
+              if (t < M) {
+                uint4 o;
+                o.x = pack_bf16x2(a[i][0], a[i][1]); o.y = pack_bf16x2(a[i][2], a[i][3]);
+                o.z = pack_bf16x2(a[i][4], a[i][5]); o.w = pack_bf16x2(a[i][6], a[i][7]);
+                *reinterpret_cast<uint4*>(sT + t * SBM + c16 * 8) = o;
+              }
+            }
           }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // flag_a is reused by the next segment
       }
+      if (!FUSE_AR && final_here) {
+        // staging tile -> Y, 256 contiguous bytes per row
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int col = sg.tile * SBM + c16 * 8;
+        const bool vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+        if (col + 8 <= N && vec_ok) {
+          for (int t = r0; t < M; t += 8)
+            *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8);
+        } else if (col < N) {
+          for (int t = r0; t < M; t += 8)
+            for (int j = 0; j < 8 && col + j < N; ++j) Y[(size_t)t * ldy + col + j] = sT[t * SBM + c16 * 8 + j];
+        }
+      }
+      if (!FUSE_AR) asm volatile("bar.sync 1, 128;" ::: "memory");   // sT and flag_a are reused by the next segment
       if (FUSE_AR && final_here) {
         const int parity = ar_epoch & 1;
-        const int c16 = e & 15, r0 = e >> 4;          // 16 threads per 256-byte tile row
         const int col = sg.tile * SBM + c16 * 8;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (col < N) {
@@ -300,7 +336,7 @@ static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int 
   r = make_tmap_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, (uint64_t)ldx * 2, SBK, ntok);
   if (r) return r;
   const int stage_bytes = SBM * SBK * 2 + ntok * SBK * 2;
-  const int staging = arena ? ((M * SBM * 2 + 1023) / 1024) * 1024 : 0;
+  const int staging = ((M * SBM * 2 + 1023) / 1024) * 1024;
   int stages = (200 * 1024 - staging) / stage_bytes;
   if (stages > SK_MAX_STAGES) stages = SK_MAX_STAGES;
   if (stages < 2) return FF_HOST_TOO_LARGE;
