@@ -1,29 +1,124 @@
-"""CUDA side of the MoE operators (see :mod:`flyingfish_b200.ops.moe_ops`)."""
+"""CUDA side of the MoE operators (see :mod:`flyingfish_b200.ops.moe_ops`): router top-k kernel,
+device-side dispatch (count / scan / permute), grouped tcgen05 GEMMs with SwiGLU in the gate/up
+epilogue, deterministic combine -- ``csrc/moe.cu``."""
 from __future__ import annotations
+
+from ctypes import c_float
 
 import torch
 
-from . import ref
-from . import linear, silu_mul
+from . import _count, _require, linear, workspace
+from .lib import check, kernels, ptr, status_tensor, stream_ptr
+
+SCORE_MODES = {"softmax": 0, "sigmoid": 1, "noaux": 2}
 
 
 def route(x, w_router, top_k, score, bias, n_groups, topk_groups, routed_scaling, renormalize):
-    return ref.moe_route(x, w_router, top_k, score, bias, n_groups, topk_groups, routed_scaling, renormalize)
+    rows = x.shape[0]
+    e = w_router.shape[0]
+    logits = linear(x, w_router)                       # FP32 accumulate, rounded to BF16
+    out_w = torch.empty(rows, top_k, dtype=torch.float32, device=x.device)
+    out_ids = torch.empty(rows, top_k, dtype=torch.int32, device=x.device)
+    rc = kernels().ff_moe_topk(ptr(logits), ptr(bias), ptr(out_w), ptr(out_ids), rows, e, top_k, SCORE_MODES[score],
+                               n_groups, topk_groups, c_float(routed_scaling), int(renormalize), logits.stride(0),
+                               ptr(status_tensor(x.device)), stream_ptr())
+    check(rc, "ff_moe_topk")
+    _count()
+    return out_w, out_ids
 
 
-def experts_forward(x, weights, ids, w_gate_up, w_down, mode):
-    rows, h = x.shape
-    n_exp = w_gate_up.shape[0]
-    contrib = torch.zeros(rows, ids.shape[1], h, dtype=torch.float32, device=x.device)
-    for e in range(n_exp):
-        r, c = torch.nonzero(ids == e, as_tuple=True)
-        if r.numel() == 0:
-            continue
-        y = linear(silu_mul(linear(x[r].contiguous(), w_gate_up[e]), mode), w_down[e]).to(torch.float32)
-        contrib[r, c] = y * weights[r, c, None]
-    order = torch.argsort(ids.long(), dim=-1, stable=True)
-    ordered = torch.gather(contrib, 1, order[:, :, None].expand_as(contrib))
-    acc = torch.zeros(rows, h, dtype=torch.float32, device=x.device)
-    for j in range(ids.shape[1]):
-        acc = acc + ordered[:, j]
-    return acc.to(x.dtype)
+def interleave64(w_gate_up: torch.Tensor) -> torch.Tensor:
+    """[E, 2f, h] with rows [gate | up] -> rows interleaved per 64 (64 gate rows, the matching 64
+    up rows, ...) so a 128-row weight tile carries both halves of 64 outputs."""
+    e, two_f, h = w_gate_up.shape
+    f = two_f // 2
+    _require(f % 64 == 0, "expert FFN width must be a multiple of 64")
+    g = w_gate_up[:, :f].reshape(e, f // 64, 1, 64, h)
+    u = w_gate_up[:, f:].reshape(e, f // 64, 1, 64, h)
+    return torch.cat([g, u], dim=2).reshape(e, two_f, h).contiguous()
+
+
+_i64_cache: dict[int, torch.Tensor] = {}
+
+
+def _gu_interleaved(w_gate_up: torch.Tensor) -> torch.Tensor:
+    key = w_gate_up.data_ptr()
+    t = _i64_cache.get(key)
+    if t is None or t.shape != w_gate_up.shape:
+        t = interleave64(w_gate_up)
+        _i64_cache[key] = t
+    return t
+
+
+class _MoeWorkspace:
+    def __init__(self):
+        self.sorted: torch.Tensor | None = None
+
+
+_moe_ws: dict[int, _MoeWorkspace] = {}
+
+
+def _sorted_buffer(device, capacity: int, hidden: int) -> torch.Tensor:
+    ws = _moe_ws.setdefault(device.index or 0, _MoeWorkspace())
+    need = capacity * hidden
+    if ws.sorted is None or ws.sorted.numel() < need:
+        _require(not torch.cuda.is_current_stream_capturing(), "MoE workspace too small during graph capture")
+        ws.sorted = torch.zeros(int(need * 1.2) + 16 * hidden, dtype=torch.bfloat16, device=device)
+    return ws.sorted[:need].view(capacity, hidden)
+
+
+def dispatch_local(x, ids, n_experts_total: int, e_lo: int, e_hi: int):
+    """Device-side count / scan / permute for the experts [e_lo, e_hi) owned locally.
+    Returns (sorted rows, pos, seg_off, counts, capacity)."""
+    rows, hidden = x.shape
+    top_k = ids.shape[1]
+    el = e_hi - e_lo
+    capacity = ((rows * top_k + 16 * el + 15) // 16) * 16
+    dev = x.device
+    meta = torch.empty(3 * el + 1, dtype=torch.int32, device=dev)
+    counts, seg_off, cursors = meta[:el], meta[el: 2 * el + 1], meta[2 * el + 1:]
+    pos = torch.empty(rows * top_k, dtype=torch.int32, device=dev)
+    sorted_x = _sorted_buffer(dev, capacity, hidden)
+    rc = kernels().ff_moe_dispatch_local(ptr(x), ptr(ids), rows, top_k, hidden, x.stride(0), n_experts_total, e_lo, e_hi,
+                                         ptr(counts), ptr(seg_off), ptr(cursors), ptr(sorted_x), ptr(pos), capacity,
+                                         ptr(status_tensor(dev)), stream_ptr())
+    check(rc, "ff_moe_dispatch_local")
+    _count(3)
+    return sorted_x, pos, seg_off, counts, capacity
+
+
+def grouped_gemm(xs, w, seg_off, counts, capacity: int, epi: int) -> torch.Tensor:
+    el, nw, k = w.shape
+    n_out = nw // 2 if epi == 1 else nw
+    y = torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs.device)
+    rc = kernels().ff_moe_grouped_gemm(ptr(xs), ptr(w), ptr(y), ptr(seg_off), ptr(counts), el, nw, k, capacity, n_out,
+                                       epi, ptr(status_tensor(xs.device)), stream_ptr())
+    check(rc, "ff_moe_grouped_gemm")
+    _count()
+    return y
+
+
+def combine(y, pos, ids, weights, rows: int, hidden: int, out: torch.Tensor | None = None,
+            accumulate: bool = False) -> torch.Tensor:
+    top_k = ids.shape[1]
+    if out is None:
+        out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=y.device)
+    rc = kernels().ff_moe_combine(ptr(y), ptr(pos), ptr(ids), ptr(weights), ptr(out), rows, hidden, top_k, y.stride(0),
+                                  int(accumulate), stream_ptr())
+    check(rc, "ff_moe_combine")
+    _count()
+    return out
+
+
+def experts_forward(x, weights, ids, w_gate_up, w_down, mode, e_lo: int = 0, n_experts_total: int | None = None):
+    """Routed experts on one device: dispatch -> gate/up grouped GEMM (+SwiGLU) -> down grouped
+    GEMM -> combine. ``w_gate_up`` is [E_local, 2f, h] in [gate | up] row order."""
+    _require(mode == 0, "grouped GEMM epilogue implements SwiGLU rounding mode 0")
+    rows, hidden = x.shape
+    el = w_gate_up.shape[0]
+    total = n_experts_total if n_experts_total is not None else el
+    wgu = _gu_interleaved(w_gate_up)
+    xs, pos, seg_off, counts, cap = dispatch_local(x.contiguous(), ids.contiguous(), total, e_lo, e_lo + el)
+    h = grouped_gemm(xs, wgu, seg_off, counts, cap, epi=1)
+    y = grouped_gemm(h, w_down, seg_off, counts, cap, epi=0)
+    return combine(y, pos, ids, weights.contiguous(), rows, hidden)
