@@ -31,8 +31,10 @@ def _r(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 # linear
 # ------------------------------------------------------------------------------------------
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """``y = x @ w.T`` with FP32 accumulation, one rounding to the output dtype."""
-    y = x.to(F32) @ w.to(F32).t()
+    """``y = x @ w.T``, one rounding to the output dtype. The products are accumulated in FP64 so
+    the oracle does not depend on how a BLAS blocks the sum for a given batch size (results are
+    batch-invariant, as the device kernels' are)."""
+    y = x.to(torch.float64) @ w.to(torch.float64).t()
     return y.to(out_dtype or x.dtype)
 
 
@@ -40,7 +42,7 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, mode: int = 0) -
     """Fused gate/up projection + SwiGLU for a weight whose rows are interleaved per 128:
     rows [256*t, 256*t+128) are gate rows for outputs [128*t, 128*t+128), the next 128 the
     matching up rows."""
-    y = x.to(F32) @ w_interleaved.to(F32).t()
+    y = (x.to(torch.float64) @ w_interleaved.to(torch.float64).t()).to(F32)
     n = y.shape[-1]
     y = y.view(*y.shape[:-1], n // 256, 2, 128)
     gate, up = y[..., 0, :], y[..., 1, :]
@@ -318,7 +320,7 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top_k: int, score: str = 
       unbiased scores renormalised and multiplied by ``routed_scaling``.
     Returns (weights FP32 [rows, k], ids int32 [rows, k]) with ids in selection order."""
     dt = logits_dtype or x.dtype
-    logits = _r(x.to(F32) @ w_router.to(F32).t(), dt)
+    logits = _r((x.to(torch.float64) @ w_router.to(torch.float64).t()).to(F32), dt)
     if score == "softmax":
         s = torch.softmax(logits, dim=-1)
         w, ids = topk_lower_tie(s, top_k)

@@ -1,0 +1,153 @@
+"""Expert-parallel communicator: every rank owns ``E / world`` experts and its own token rows
+(attention is data-parallel), token rows travel to the experts' owners and results come back.
+
+CUDA path (``csrc/moe_ep.cu``): rows are scattered straight into the owners' expert input buffers
+with peer stores issued by the dispatch kernel, the owners run the grouped tcgen05 GEMMs on what
+arrived, and the combine kernel reads the expert outputs directly out of the owners' memory --
+no NCCL all-to-all on the hot path, no host involvement. CPU path (gloo): the same semantics
+written with collectives, used by the host-side tests and as the library-call baseline.
+
+The reference's closest feature is its 2-GPU "peer compute" expert residency, which moves one
+layer's packet through pinned host memory (src/backend/cuda/engine_moe.rs:1643-1830).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_ulonglong
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..ops import lib as oplib
+from ..ops import moe_ops, ref
+
+
+class EpArenaHost(ctypes.Structure):
+    _fields_ = [("ptrs", c_ulonglong * 8), ("rank", c_int), ("world", c_int), ("E", c_int), ("E_local", c_int),
+                ("hidden", c_int), ("capacity", c_int), ("off_flags", c_longlong), ("off_counts", c_longlong),
+                ("off_x", c_longlong), ("off_y", c_longlong)]
+
+
+class EPComm:
+    def __init__(self, group: dist.ProcessGroup, device: torch.device | str, num_experts: int, hidden: int,
+                 max_rows: int = 0, top_k: int = 1, inter: int = 0):
+        self.group = group
+        self.device = torch.device(device)
+        self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
+        assert num_experts % self.size == 0, "experts must divide evenly over the expert-parallel ranks"
+        self.E, self.El, self.hidden = num_experts, num_experts // self.size, hidden
+        self.stats = {"fused_calls": 0, "baseline_calls": 0}
+        self.arena = None
+        if self.device.type == "cuda" and self.size > 1:
+            self._setup_arena(max_rows, top_k)
+
+    # -- symmetric buffers -----------------------------------------------------------------------
+    def _setup_arena(self, max_rows: int, top_k: int) -> None:
+        import torch.distributed._symmetric_memory as symm
+        lib = oplib.kernels()
+        lib.ff_ep_arena_layout.restype = c_longlong
+        # worst case every rank sends all its assignments to one owner; 2x the balanced share is
+        # the default budget, overflow is reported through the status word
+        cap = max(256, 2 * max_rows * top_k + 16 * self.El)
+        cap = (cap + 15) // 16 * 16
+        offs = [c_longlong(0) for _ in range(4)]
+        total = lib.ff_ep_arena_layout(self.size, self.E, self.hidden, cap, *[ctypes.byref(o) for o in offs])
+        self.buf = symm.empty(int(total), dtype=torch.uint8, device=self.device)
+        self.handle = symm.rendezvous(self.buf, self.group)
+        self.buf.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        h = EpArenaHost()
+        for i in range(8):
+            h.ptrs[i] = ptrs[i] if i < len(ptrs) else 0
+        h.rank, h.world, h.E, h.E_local, h.hidden, h.capacity = self.rank, self.size, self.E, self.El, self.hidden, cap
+        h.off_flags, h.off_counts, h.off_x, h.off_y = (o.value for o in offs)
+        self.arena = h
+        self.capacity = cap
+        self.recv_x = self.buf[h.off_x: h.off_x + cap * self.hidden * 2].view(torch.bfloat16).view(cap, self.hidden)
+        self.out_y = self.buf[h.off_y: h.off_y + cap * self.hidden * 2].view(torch.bfloat16).view(cap, self.hidden)
+        self.scratch = torch.zeros(2 * self.E + 2 * self.El + 1, dtype=torch.int32, device=self.device)
+
+    # -- one MoE layer ---------------------------------------------------------------------------
+    def dispatch_ffn_combine(self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor, lw, mode: int
+                             ) -> torch.Tensor:
+        """Routed-expert output for the local rows ``x`` (shared expert not included)."""
+        if self.arena is not None and x.is_cuda:
+            return self._fused(x, weights, ids, lw, mode)
+        return self._baseline(x, weights, ids, lw, mode)
+
+    def _fused(self, x, weights, ids, lw, mode):
+        from ..ops import moe_cuda
+        lib = oplib.kernels()
+        rows, top_k = ids.shape
+        E, El = self.E, self.El
+        counts_s, cursors = self.scratch[:E], self.scratch[E: 2 * E]
+        seg_off, counts = self.scratch[2 * E: 2 * E + El + 1], self.scratch[2 * E + El + 1:]
+        pos = torch.empty(rows * top_k, dtype=torch.int32, device=x.device)
+        st = oplib.status_tensor(x.device)
+        x = x.contiguous(); ids = ids.contiguous(); weights = weights.contiguous()
+        rc = lib.ff_ep_dispatch(ctypes.byref(self.arena), oplib.ptr(x), oplib.ptr(ids), rows, top_k, x.stride(0),
+                                oplib.ptr(counts_s), oplib.ptr(cursors), oplib.ptr(pos), oplib.ptr(seg_off),
+                                oplib.ptr(counts), oplib.ptr(st), oplib.stream_ptr())
+        oplib.check(rc, "ff_ep_dispatch")
+        ops._count(3)
+        wgu = moe_cuda._gu_interleaved(lw.experts_gu)
+        h = moe_cuda.grouped_gemm(self.recv_x, wgu, seg_off, counts, self.capacity, epi=1)
+        # the down projection writes into the symmetric output buffer the peers read from
+        f = h.shape[1]
+        rc = lib.ff_moe_grouped_gemm(oplib.ptr(h), oplib.ptr(lw.experts_down), oplib.ptr(self.out_y), oplib.ptr(seg_off),
+                                     oplib.ptr(counts), El, self.hidden, f, self.capacity, self.hidden, 0,
+                                     oplib.ptr(st), oplib.stream_ptr())
+        oplib.check(rc, "ff_moe_grouped_gemm(down)")
+        out = torch.empty(rows, self.hidden, dtype=torch.bfloat16, device=x.device)
+        rc = lib.ff_ep_combine(ctypes.byref(self.arena), oplib.ptr(pos), oplib.ptr(ids), oplib.ptr(weights),
+                               oplib.ptr(out), rows, top_k, oplib.ptr(st), oplib.stream_ptr())
+        oplib.check(rc, "ff_ep_combine")
+        ops._count(2)
+        self.stats["fused_calls"] += 1
+        return out
+
+    def _baseline(self, x, weights, ids, lw, mode):
+        """Collective formulation (gloo / NCCL): gather rows, every rank computes the contributions of
+        its experts, contributions are summed across ranks (exactly one rank is non-zero per
+        entry), each rank reduces its own rows in ascending expert id."""
+        rows, k = ids.shape
+        n_rows = torch.tensor([rows], dtype=torch.int64, device=x.device)
+        all_n = [torch.zeros_like(n_rows) for _ in range(self.size)]
+        dist.all_gather(all_n, n_rows, group=self.group)
+        counts = [int(t.item()) for t in all_n]
+        mx = max(counts)
+
+        def gather(t, pad_val=0):
+            pad = torch.full((mx,) + t.shape[1:], pad_val, dtype=t.dtype, device=t.device)
+            pad[: t.shape[0]] = t
+            out = [torch.empty_like(pad) for _ in range(self.size)]
+            dist.all_gather(out, pad, group=self.group)
+            return torch.cat([o[:c] for o, c in zip(out, counts)], 0)
+
+        xf = x.to(torch.float32) if x.dtype == torch.bfloat16 and not x.is_cuda else x
+        ax = gather(xf).to(x.dtype)
+        aid = gather(ids)
+        aw = gather(weights)
+        total = ax.shape[0]
+        e0 = self.rank * self.El
+        contrib = torch.zeros(total, k, self.hidden, dtype=torch.float32, device=x.device)
+        for le in range(self.El):
+            r, c = torch.nonzero(aid == e0 + le, as_tuple=True)
+            if r.numel() == 0:
+                continue
+            y = ref.expert_ffn(ax[r], lw.experts_gu[le], lw.experts_down[le], mode) if not x.is_cuda else \
+                ops.linear(ops.silu_mul(ops.linear(ax[r].contiguous(), lw.experts_gu[le]), mode), lw.experts_down[le])
+            contrib[r, c] = y.to(torch.float32) * aw[r, c, None]
+        dist.all_reduce(contrib, group=self.group)
+        start = sum(counts[: self.rank])
+        mine = contrib[start: start + rows]
+        order = torch.argsort(ids.long(), dim=-1, stable=True)
+        ordered = torch.gather(mine, 1, order[:, :, None].expand_as(mine))
+        acc = torch.zeros(rows, self.hidden, dtype=torch.float32, device=x.device)
+        for j in range(k):
+            acc = acc + ordered[:, j]
+        self.stats["baseline_calls"] += 1
+        return acc.to(x.dtype)

@@ -57,3 +57,28 @@ def test_tp2_model_gpu(tmp_path):
     single = _single("cuda")
     assert res["tokens"][0][:3] == single[0][:3]
     assert res["stats"]["gemm_ar"] > 0
+
+
+def _single_moe(device, prompts):
+    from flyingfish_b200.api import Model
+    from flyingfish_b200.config import Settings
+    m = Model.load("qwen3-moe-tiny", Settings(capacity=256, max_batch=4, graph=False), device=device, seed=0)
+    return m.generate_batch(prompts, 8)
+
+
+def test_ep2_gloo_matches_single_rank(tmp_path):
+    """Expert parallelism with data-parallel attention: every rank serves different sequences and
+    must produce exactly what a single rank holding all experts produces for them."""
+    res = _launch(2, "cpu", "ep", tmp_path, 29514)
+    for r in res["per_rank"]:
+        assert r["tokens"] == _single_moe("cpu", r["prompts"])
+
+
+@pytest.mark.gpu
+def test_ep2_fused_dispatch_combine_gpu(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _launch(2, "cuda", "ep", tmp_path, 29515)
+    assert res["stats"]["fused_calls"] > 0
+    for r in res["per_rank"]:
+        assert r["tokens"] == _single_moe("cuda", r["prompts"])

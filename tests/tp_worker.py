@@ -70,6 +70,21 @@ def main():
             torch.cuda.synchronize()
             ops.check_status(device)
         result.update(ok=ok, errs=errs, same=same, stats=comm.stats)
+    elif args.mode == "ep":
+        from flyingfish_b200.parallel.ep import EPComm
+        from flyingfish_b200.config import named_shape
+        spec = named_shape("qwen3-moe-tiny")
+        ep = EPComm(dist.group.WORLD, device, spec.moe.num_experts, spec.hidden, max_rows=128, top_k=spec.moe.top_k)
+        m = Model.load("qwen3-moe-tiny", Settings(capacity=256, max_batch=4, graph=False), device=device, seed=0, ep=ep)
+        g = torch.Generator().manual_seed(100 + rank)       # every rank serves its own sequences
+        prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (33, 12)]
+        toks = m.generate_batch(prompts, 8)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, {"prompts": prompts, "tokens": toks})
+        if device.type == "cuda":
+            torch.cuda.synchronize()
+            ops.check_status(device)
+        result.update(per_rank=gathered, stats=ep.stats)
     if rank == 0:
         Path(args.out).write_text(json.dumps(result))
     dist.barrier()
