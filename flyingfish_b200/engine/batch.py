@@ -30,7 +30,8 @@ class BatchLayout:
         self.q_start = o; o += self.max_batch
         self.q_lens = o; o += self.max_batch
         self.ctx_lens = o; o += self.max_batch
-        self.logit_rows = o; o += self.max_batch * 8      # up to 8 logit rows per sequence (verify)
+        self.n_logit = max(self.max_batch * 8, self.max_rows)   # verify rows / all-row logits
+        self.logit_rows = o; o += self.n_logit
         self.block_table = o; o += self.max_batch * self.max_blocks
         self.tree_mask = o; o += 2 * self.max_rows        # int64 per row, stored as two int32
         self.total = o
@@ -92,7 +93,7 @@ class ForwardBatch:
         h = self.host
         rows, batch = len(ids), len(q_lens)
         assert rows <= L.max_rows and batch <= L.max_batch, "batch exceeds the layout capacity"
-        assert len(logit_rows) <= L.max_batch * 8
+        assert len(logit_rows) <= L.n_logit
         self.rows, self.batch, self.nq, self.is_decode = rows, batch, nq, is_decode
         h[L.ids: L.ids + rows] = torch.as_tensor(ids, dtype=torch.int32)
         h[L.positions: L.positions + rows] = torch.as_tensor(positions, dtype=torch.int32)

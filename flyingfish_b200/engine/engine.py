@@ -270,6 +270,62 @@ class Engine:
             self.poisoned = True
             raise
 
+    # -- speculative verification --------------------------------------------------------------
+    def verify(self, seqs: list[Sequence], drafts: list[list[int]], return_hidden: bool = False):
+        """Feed every sequence's pending token plus its draft tokens (same count k for all) through
+        the target in ONE forward of k+1 rows per sequence and return the target's greedy token
+        after each row: ``[[t_0 .. t_k]]`` per sequence. Nothing is committed; call
+        :meth:`commit_verified` with the number of accepted drafts. Rows of rejected drafts leave
+        stale K/V behind the committed length, which later steps simply overwrite (the paged
+        cache needs no copy-back, unlike the reference's gather/scatter of tree rows,
+        kernels/tree/meta.cu)."""
+        self._check()
+        if self.fail_next_step:
+            self.fail_next_step = False
+            self.poisoned = True
+            raise RuntimeError("injected step failure")
+        try:
+            k = len(drafts[0])
+            assert all(len(d) == k for d in drafts), "all sequences must carry the same number of drafts"
+            nq = k + 1
+            fb = self.prefill_batch
+            ids, positions, slots, q_lens, ctx_lens, block_rows = [], [], [], [], [], []
+            for s, d in zip(seqs, drafts):
+                kvs = self.kv.seqs[s.seq_id]
+                if kvs.length + nq > self.settings.capacity:
+                    raise OutOfBlocks(f"sequence {s.seq_id}: no KV headroom for {nq} verification rows")
+                sl = self.kv.reserve(s.seq_id, nq)
+                ids += [s.pending] + list(d)
+                positions += list(range(kvs.length, kvs.length + nq))
+                slots += sl
+                q_lens.append(nq)
+                ctx_lens.append(kvs.length + nq)
+                block_rows.append(list(kvs.blocks))
+            rows = len(ids)
+            fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
+                    logit_rows=list(range(rows)), is_decode=False)
+            fb.upload()
+            n = self.model.hidden_states(fb, self.kv)
+            out = self.model.greedy(self.model.logits(n, fb))
+            toks = [int(t) for t in out.cpu().tolist()]
+            self._after_sync()
+            self.stats["verify_rows"] = self.stats.get("verify_rows", 0) + rows
+            res = [toks[i * nq: (i + 1) * nq] for i in range(len(seqs))]
+            if return_hidden:
+                hid = self.model.last_residual
+                return res, [hid[i * nq: (i + 1) * nq] for i in range(len(seqs))]
+            return res
+        except Exception:
+            self.poisoned = True
+            raise
+
+    def commit_verified(self, seq: Sequence, emitted: list[int], n_draft_accepted: int) -> None:
+        """Commit the pending token and the accepted drafts (their K/V rows are already in place),
+        publish ``emitted`` and make its last token the new pending one."""
+        self.kv.commit(seq.seq_id, n_draft_accepted + 1)
+        seq.output.extend(emitted)
+        seq.pending = emitted[-1]
+
     def _after_sync(self) -> None:
         """Runs right after a device-to-host read (an existing sync point): surface device status."""
         if self.device.type == "cuda":

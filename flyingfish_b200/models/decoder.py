@@ -53,6 +53,7 @@ class DecoderModel:
         self.trace = trace           # optional flyingfish_b200.utils.trace.Trace
         self.capture_taps: dict[int, int] = {}    # layer index -> tap slot for draft-model hidden taps
         self.capture_slab: torch.Tensor | None = None
+        self.normed_sink: list | None = None      # when a list: every forward appends its final-normed rows
 
     # -- pieces ----------------------------------------------------------------------------
     def _attention(self, i: int, n: torch.Tensor, b: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
@@ -91,10 +92,17 @@ class DecoderModel:
         return self.comm.row_linear(hmid, lw.wdown)
 
     # -- forward ---------------------------------------------------------------------------
-    def hidden_states(self, b: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
-        """Runs all layers; returns the final-normed activations [rows, hidden]."""
+    def hidden_states(self, b: ForwardBatch, kv: PagedKVCache, inputs_embeds: torch.Tensor | None = None
+                      ) -> torch.Tensor:
+        """Runs all layers; returns the final-normed activations [rows, hidden]. ``inputs_embeds``
+        replaces the embedding lookup (multi-token-prediction heads feed a projected mix of the
+        next token's embedding and the previous hidden state)."""
         w, s = self.w, self.spec
-        x, n = ops.embed_rmsnorm(b.ids, w.embed, w.layers[0].input_ln, s.rms_eps)
+        if inputs_embeds is None:
+            x, n = ops.embed_rmsnorm(b.ids, w.embed, w.layers[0].input_ln, s.rms_eps)
+        else:
+            x = inputs_embeds.clone()
+            n = ops.rmsnorm(x, w.layers[0].input_ln, s.rms_eps)
         if self.trace is not None:
             self.trace.record("embed", x)
         for i in range(s.layers):
@@ -110,6 +118,8 @@ class DecoderModel:
             if self.trace is not None:
                 self.trace.record(f"layer.{i}", x)
         self.last_residual = x
+        if self.normed_sink is not None:
+            self.normed_sink.append(n)
         return n
 
     def logits(self, n: torch.Tensor, b: ForwardBatch) -> torch.Tensor:
