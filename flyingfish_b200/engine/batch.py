@@ -116,7 +116,8 @@ class ForwardBatch:
         self.max_ctx = int(max(ctx_lens)) if batch else 0
         self.use_tree_mask = tree_mask is not None
         if tree_mask is not None:
-            tm = torch.as_tensor(tree_mask, dtype=torch.int64)
+            # bit 63 may be set: store the two's complement value
+            tm = torch.as_tensor([m - (1 << 64) if m >= (1 << 63) else m for m in tree_mask], dtype=torch.int64)
             h[L.tree_mask: L.tree_mask + 2 * rows].view(torch.int64)[:] = tm
 
     def h2d_bytes(self) -> int:

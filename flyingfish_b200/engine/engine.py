@@ -319,6 +319,61 @@ class Engine:
             self.poisoned = True
             raise
 
+    def forward_rows(self, seq: Sequence, tokens: list[int], return_logits: bool = True) -> torch.Tensor:
+        """Uncommitted forward of ``tokens`` placed after the sequence's committed prefix (causal);
+        returns the logits (or greedy ids) of every row. The K/V rows written stay behind the
+        committed length and are overwritten by whatever runs next."""
+        self._check()
+        kvs = self.kv.seqs[seq.seq_id]
+        n = len(tokens)
+        sl = self.kv.reserve(seq.seq_id, n)
+        fb = self.prefill_batch
+        fb.fill(ids=tokens, positions=list(range(kvs.length, kvs.length + n)), slots=sl, q_lens=[n],
+                ctx_lens=[kvs.length + n], block_rows=[list(kvs.blocks)], logit_rows=list(range(n)), is_decode=False)
+        fb.upload()
+        return self.model.forward(fb, self.kv, return_logits=return_logits)
+
+    def verify_tree(self, seq: Sequence, tokens: list[int], depths: list[int], masks: list[int]) -> list[int]:
+        """Verify a draft tree in one forward: row i holds ``tokens[i]`` at sequence position
+        ``committed + depths[i]`` and cache slot ``committed + i``; ``masks[i]`` (bit j = row j is an
+        ancestor-or-self) restricts what it sees among the tree rows. Returns the target's greedy
+        token after every row."""
+        self._check()
+        try:
+            kvs = self.kv.seqs[seq.seq_id]
+            n = len(tokens)
+            assert n <= 64 and tokens[0] == seq.pending
+            if kvs.length + n > self.settings.capacity:
+                raise OutOfBlocks("no KV headroom for the verification tree")
+            sl = self.kv.reserve(seq.seq_id, n)
+            fb = self._decode_batch(1) if n == 1 else self.prefill_batch
+            fb = self.prefill_batch
+            fb.fill(ids=tokens, positions=[kvs.length + d for d in depths], slots=sl, q_lens=[n],
+                    ctx_lens=[kvs.length + n], block_rows=[list(kvs.blocks)], logit_rows=list(range(n)),
+                    is_decode=True, nq=n, tree_mask=masks)
+            fb.max_ctx = self.settings.capacity
+            fb.upload()
+            out = self.model.forward(fb, self.kv)
+            toks = [int(t) for t in out.cpu().tolist()]
+            self._after_sync()
+            return toks
+        except Exception:
+            self.poisoned = True
+            raise
+
+    def commit_tree_path(self, seq: Sequence, path_rows: list[int], emitted: list[int]) -> None:
+        """Compact the K/V of the accepted tree path onto consecutive positions and commit it."""
+        kvs = self.kv.seqs[seq.seq_id]
+        base = kvs.length
+        src = [base + r for r in path_rows]
+        dst = [base + j for j in range(len(path_rows))]
+        moves = [(s_, d_) for s_, d_ in zip(src, dst) if s_ != d_]
+        if moves:
+            self.kv.move_rows(seq.seq_id, [m[0] for m in moves], [m[1] for m in moves])
+        self.kv.commit(seq.seq_id, len(path_rows))
+        seq.output.extend(emitted)
+        seq.pending = emitted[-1]
+
     def commit_verified(self, seq: Sequence, emitted: list[int], n_draft_accepted: int) -> None:
         """Commit the pending token and the accepted drafts (their K/V rows are already in place),
         publish ``emitted`` and make its last token the new pending one."""

@@ -146,3 +146,24 @@ class PagedKVCache:
         blocks = self.seqs[seq_id].blocks
         assert len(blocks) <= width, "block table too narrow for the sequence"
         return blocks + [0] * (width - len(blocks))
+
+    def move_rows(self, seq_id: int, src_positions: list[int], dst_positions: list[int]) -> None:
+        """Copy the K/V rows at ``src_positions`` of a sequence to ``dst_positions`` in every layer
+        (gather first, then scatter, so overlapping sets are safe). Used to compact the accepted
+        path of a verification tree onto consecutive positions (the reference's
+        ``tree_kv_gather`` / ``tree_kv_scatter``, kernels/tree/meta.cu)."""
+        if not src_positions:
+            return
+        s = self.seqs[seq_id]
+        bs = self.block_size
+        dev = self.device
+        sb = torch.tensor([s.blocks[p // bs] for p in src_positions], device=dev)
+        so = torch.tensor([p % bs for p in src_positions], device=dev)
+        db = torch.tensor([s.blocks[p // bs] for p in dst_positions], device=dev)
+        do = torch.tensor([p % bs for p in dst_positions], device=dev)
+        for layer in range(self.layers):
+            for cache in (self.k[layer], self.v[layer]):
+                if cache is None:
+                    continue
+                rows = cache[sb, :, so, :].clone()
+                cache[db, :, do, :] = rows

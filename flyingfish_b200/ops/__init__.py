@@ -315,8 +315,8 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, blo
     if not _is_cuda(q):
         q_start = torch.arange(batch, dtype=torch.int32) * nq
         q_lens = torch.full((batch,), nq, dtype=torch.int32)
-        return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale,
-                                   tree_mask)
+        tm = None if tree_mask is None else tree_mask.view(batch, nq)
+        return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale, tm)
     rows, ldq = _rows2d(q)
     _require(rows == batch * nq, "attn_decode: q rows must equal batch * nq")
     _require(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attn_decode: block table int32")

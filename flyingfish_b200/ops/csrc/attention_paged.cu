@@ -182,21 +182,23 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
                    int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // blockIdx.y = row tile * hkv + kv head: nq * G packed rows are processed 16 at a time
+  const int split = blockIdx.x, kvh = blockIdx.y % hkv, rt = blockIdx.y / hkv, b = blockIdx.z;
   const int G = hq / hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int ctx = ctx_lens[b];
   const int pages = (ctx + PAGE - 1) / PAGE;
   const int per = (pages + nsplit - 1) / nsplit;
   const int p0 = split * per, p1 = min(pages, p0 + per);
-  const int rows_used = nq * G;
+  const int rows_total = nq * G;
+  const int rows_used = min(16, rows_total - rt * 16);
 
-  // rows g and g+8 of the packed tile: row r -> (query r / G, head kvh*G + r % G)
+  // rows g and g+8 of the packed tile: packed row r -> (query r / G, head kvh*G + r % G)
   const __nv_bfloat16* qp[2]; int lim[2]; unsigned long long mk[2];
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
-    const int r = g + e * 8;
-    if (r < rows_used) {
+    const int r = rt * 16 + g + e * 8;
+    if (r < rows_total) {
       const int qi = r / G, hh = kvh * G + r % G;
       qp[e] = q + (size_t)(b * nq + qi) * ldq + (size_t)hh * HD;
       lim[e] = ctx - nq + qi;
@@ -250,6 +252,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   __syncthreads();
   const int d = threadIdx.x;   // 128 threads = 128 dims
   for (int r = 0; r < rows_used; ++r) {
+    const int rg = rt * 16 + r;
     float M = NEG_BIG;
 #pragma unroll
     for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) * 2]);
@@ -260,7 +263,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       L += sml[(w * 16 + r) * 2 + 1] * sc;
       acc += so[(w * 16 + r) * HD + d] * sc;
     }
-    const int qi = r / G, hh = kvh * G + r % G;
+    const int qi = rg / G, hh = kvh * G + rg % G;
     if (nsplit == 1) {
       out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
     } else {
@@ -377,7 +380,7 @@ constexpr int ATTN_SMEM = 4 * PAGE * HD * 2;   // 64 KiB: two stages of K and V 
 FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ctx, long long* part_o_bytes,
                                   long long* part_ml_bytes) {
   const int pages = (max_ctx + PAGE - 1) / PAGE;
-  const int ctas = batch * hkv;
+  const int ctas = batch * hkv * ((nq * (hq / hkv) + 15) / 16);
   int nsplit = 1;
   // three 64-KiB CTAs fit on one SM; aim for at least four full waves so the ragged last wave
   // costs little
@@ -396,13 +399,14 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
                              float* part_ml, int batch, int hq, int hkv, int head_dim, int nq, int ldq, int max_blocks,
                              int num_blocks, int nsplit, float scale, int* status, cudaStream_t s) {
   if (head_dim != HD || batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv) return FF_HOST_BAD_SHAPE;
-  if (nq < 1 || nq * (hq / hkv) > 16 || nq > 64) return FF_HOST_BAD_SHAPE;
+  if (nq < 1 || nq > 64) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || nsplit < 1) return FF_HOST_BAD_ALIGN;
   if (nsplit > 1 && (!part_o || !part_ml)) return FF_HOST_BAD_SHAPE;
   static bool attr = false;
   if (!attr) { if (int r = opt_in_smem(attn_decode_kernel, ATTN_SMEM)) return r; attr = true; }
   const float scale_log2 = scale * 1.4426950408889634f;
-  dim3 grid(nsplit, hkv, batch);
+  const int row_tiles = (nq * (hq / hkv) + 15) / 16;
+  dim3 grid(nsplit, hkv * row_tiles, batch);
   attn_decode_kernel<<<grid, 128, ATTN_SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache,
       (const __nv_bfloat16*)vcache, block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
       ldq, max_blocks, num_blocks, nsplit, scale_log2, status);

@@ -84,3 +84,25 @@ def test_poisoning_after_injected_failure():
     m.reset()
     m.prefill(_prompt(2048, 10, 4))
     m.decode()
+
+
+def test_speculation_on_gpu_equals_greedy():
+    """Chain (draft model), MTP and tree speculation through the CUDA kernels (multi-row verify
+    via the prefill kernel, tree verify via the masked decode kernel) reproduce plain greedy."""
+    from flyingfish_b200.spec.chain import ChainSpeculator
+    from flyingfish_b200.spec.mtp import MtpSpeculator
+    from flyingfish_b200.spec.tree_spec import TreeSpeculator
+    ids = _prompt(2048, 35, 9)
+    t = _load("cuda", graph=False)
+    d = _load("cuda", graph=False)
+    plain = generate_plain(t, ids, 16, ignore_eos=True, graph=False).ids
+    t.reset()
+    spec = ChainSpeculator(t, d, k=4)
+    assert spec.generate(ids, 16).ids == plain
+    assert spec.stats.acceptance_rate == 1.0
+    t.reset(); d.reset()
+    assert MtpSpeculator(t, depth=2, seed=3).generate(ids, 16).ids == plain
+    t.reset()
+    tree = TreeSpeculator(t, d, "tree32", "waves")
+    assert tree.generate(ids, 16).ids == plain
+    assert tree.stats.accepted > 0

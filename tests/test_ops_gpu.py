@@ -231,3 +231,29 @@ def test_gemm_skinny_streamk_shapes(m, n, k):
     # reference on the GPU in FP32 (the CPU matmul of the big shapes is slow)
     expect = (x.float() @ w.float().t())
     _close(y, expect)
+
+
+def test_attn_decode_many_rows_tree():
+    """40 query rows x 4 heads per kv head = 10 packed row tiles, random ancestor masks."""
+    d, hq, hkv, batch, nq = 128, 8, 2, 2, 40
+    max_blocks = 6
+    kc, vc = _fill_cache(batch * max_blocks, hkv, d, 60)
+    bt = torch.arange(batch * max_blocks, dtype=torch.int32).view(batch, max_blocks).cuda()
+    ctx = torch.tensor([100, 290], dtype=torch.int32, device="cuda")
+    q = _rand((batch * nq, hq * d), 62)
+    g = torch.Generator().manual_seed(5)
+    masks = []
+    for b in range(batch):
+        row = []
+        for r in range(nq):
+            m = int(torch.randint(0, 2 ** 31, (1,), generator=g)) & ((1 << r) - 1)
+            row.append(m | (1 << r))
+        masks.append(row)
+    masks = torch.tensor(masks, dtype=torch.int64)
+    out = ops.attn_decode(q, kc, vc, bt, ctx, hq, hkv, d, 0.088, nq=nq, tree_mask=masks.cuda())
+    ops.check_status()
+    qs = torch.arange(batch, dtype=torch.int32) * nq
+    ql = torch.full((batch,), nq, dtype=torch.int32)
+    expect = ref.attention_paged(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), qs, ql, ctx.cpu(), hq, hkv, d, 0.088,
+                                 tree_mask=masks)
+    _close(out, expect, 2e-2, 2e-2)

@@ -112,3 +112,46 @@ def test_mtp_fault_is_transactional():
     spec.fault = Fault.NONE
     t.reset()
     assert spec.generate(ids, 9).ids == plain
+
+
+def test_tree_builder_budget_masks_and_order():
+    from flyingfish_b200.spec.tree import VerifyCostSchedule, build_tree
+    import math
+
+    def children(paths):
+        outs = []
+        for p in paths:
+            base = sum(p) % 7
+            outs.append([(100 + base + i, math.log(w)) for i, w in enumerate([0.5, 0.3, 0.15, 0.05])])
+        return outs
+
+    for builder in ("waves", "serial"):
+        t = build_tree(1, children, 16, builder)
+        assert len(t) == 16 and t.parents[0] == -1
+        t.check()
+        for r in range(1, len(t)):
+            assert t.masks[r] & (1 << t.parents[r]) and t.masks[r] & 1        # parent and root visible
+            assert bin(t.masks[r]).count("1") == t.depth[r] + 1
+        assert t.positions(50)[0] == 50 and max(t.positions(50)) <= 50 + 7
+    s = build_tree(1, children, 8, "serial")
+    assert all(s.logp[i] >= s.logp[i + 1] - 1e-9 for i in range(1, len(s) - 1)), "serial builder is best-first"
+    assert len(build_tree(1, children, 1)) == 1
+    sched = VerifyCostSchedule(tau=0.8, miss_cost_ms=0.5, step_ms=1.0, expected_new_experts_per_row=1.0)
+    assert sched.select_rows([0.99, 0.98, 0.97, 0.2, 0.9]) <= 5
+    assert sched.select_rows([0.1]) == 2
+    assert VerifyCostSchedule().select_rows([0.95] * 10) == 8
+
+
+@pytest.mark.parametrize("seed_draft,builder", [(0, "waves"), (0, "serial"), (5, "waves")])
+def test_tree_speculation_equals_greedy(seed_draft, builder):
+    from flyingfish_b200.spec.tree_spec import TreeSpeculator
+    t, d = _models(seed_draft=seed_draft)
+    g = torch.Generator().manual_seed(6)
+    ids = torch.randint(0, 2048, (13,), generator=g).tolist()
+    plain = generate_plain(t, ids, 12, ignore_eos=True, graph=False).ids
+    t.reset()
+    spec = TreeSpeculator(t, d, "tree16", builder)
+    out = spec.generate(ids, 12)
+    assert out.ids == plain
+    if seed_draft == 0:
+        assert spec.stats.accepted > 0, "an identical draft model must get tokens accepted"
