@@ -109,8 +109,11 @@ class SafetensorsFile:
         buf = memoryview(self._mm)[self.data_start + info.begin: self.data_start + info.end]
         if info.nbytes == 0:
             return torch.empty(info.shape, dtype=dt)
-        t = torch.frombuffer(buf, dtype=torch.uint8).view(dt) if dt != torch.bool else \
-            torch.frombuffer(buf, dtype=torch.uint8).to(torch.bool)
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)      # read-only mapping: views are never written
+            raw = torch.frombuffer(buf, dtype=torch.uint8)
+        t = raw.view(dt) if dt != torch.bool else raw.to(torch.bool)
         return t.view(info.shape)
 
     def byte_range(self, name: str) -> tuple[int, int]:
@@ -119,8 +122,12 @@ class SafetensorsFile:
         return self.data_start + info.begin, self.data_start + info.end
 
     def close(self) -> None:
+        """Release the mapping. Tensor views handed out earlier keep it alive until they are
+        garbage-collected, in which case only the file descriptor is closed here."""
         try:
             self._mm.close()
+        except BufferError:
+            pass
         finally:
             self._f.close()
 
