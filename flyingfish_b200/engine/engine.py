@@ -239,10 +239,13 @@ class Engine:
         try:
             n = len(seqs)
             bucket = bucket_for(n)
+            provider = getattr(self.model, "expert_provider", None)
+            if provider is not None:
+                provider.begin_token()
             for s in seqs:
                 if self.kv.seqs[s.seq_id].length + 1 > self.settings.capacity:
                     raise OutOfBlocks(f"sequence {s.seq_id} reached the KV capacity {self.settings.capacity}")
-            if self.use_graph:
+            if self.use_graph and provider is None:
                 g = self.capture(bucket)
                 fb = g.batch
                 self._fill_decode(fb, seqs, bucket)
@@ -256,6 +259,8 @@ class Engine:
                 fb.upload()
                 out = self.model.forward(fb, self.kv)
             toks = [int(t) for t in out[:n].cpu().tolist()]
+            if provider is not None:
+                provider.finish_token()
             self.stats["h2d_bytes"] += fb.h2d_bytes()
             self.stats["d2h_bytes"] += 4 * bucket
             self._after_sync()

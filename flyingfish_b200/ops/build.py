@@ -32,7 +32,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=x86-64-v3", "-pthread", "-fvisibility=hidden"]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-pthread", "-fvisibility=hidden"]
 
 
 def _nvcc() -> str:

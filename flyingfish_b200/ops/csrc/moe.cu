@@ -117,6 +117,7 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int n_assign, int 
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_assign) return;
   const int e = ids[i];
+  if (e == -1) return;                       // assignment served elsewhere (another tier / rank)
   if (e < 0 || e >= E) { set_status(status, KID_MOE_DISPATCH, FF_ERR_BOUNDS, i, e); return; }
   if (e >= e_lo && e < e_hi) atomicAdd(&counts[e - e_lo], 1);
 }
