@@ -155,3 +155,39 @@ def test_tiered_provider_matches_all_resident(mode):
     assert agree >= 10, (out, plain)                     # FP32 SIMD vs FP64 oracle may flip a late token
     assert prov.stats["cpu_rows"] > 0 and prov.stats["gpu_rows"] > 0
     assert prov.res.stats["tokens"] == 11 and prov.res.hit_rate() > 0.3
+
+
+def test_catalogue_disk_tier_and_span_plan(tmp_path):
+    from flyingfish_b200.config import spec_from_hf_config
+    from flyingfish_b200.experts.catalogue import ExpertCatalogue, slot_layout
+    from flyingfish_b200.experts.disk import DiskExperts
+    from flyingfish_b200.experts.span import ExpertClass, plan_layer
+    from flyingfish_b200.loaders.checkpoint import manifest, save_decoder_checkpoint
+    from flyingfish_b200.loaders.safetensors_io import MappedCheckpoint
+    cfg = {"architectures": ["Qwen3MoeForCausalLM"], "hidden_size": 128, "num_attention_heads": 2, "num_key_value_heads": 1,
+           "head_dim": 64, "intermediate_size": 256, "moe_intermediate_size": 64, "num_experts": 4, "num_experts_per_tok": 2,
+           "num_hidden_layers": 2, "vocab_size": 256, "torch_dtype": "bfloat16", "hidden_act": "silu"}
+    spec = spec_from_hf_config(cfg, "moe")
+    g = torch.Generator().manual_seed(0)
+    tensors = {n: (torch.randn(s, generator=g) * 0.05).to(torch.bfloat16) for n, (s, c) in manifest(spec).items()}
+    d = tmp_path / "ck"
+    save_decoder_checkpoint(d, spec, tensors, cfg, shards=2)
+    ck = MappedCheckpoint(d)
+    cat = ExpertCatalogue.from_checkpoint(ck, spec)
+    lay = slot_layout(spec)
+    assert cat.slot_bytes() == lay.total == 3 * 64 * 128 * 2 and len(cat.files()) == 2
+    disk = DiskExperts(cat, {(1, 3), (0, 2)}, ring_slots=2, threads=2)
+    assert disk.on_disk(1, 3) and not disk.on_disk(1, 0)
+    disk.prefetch(0, [2])
+    for (l, e) in ((1, 3), (0, 2), (1, 3)):
+        gu, down = disk.fetch(l, e)
+        p = f"model.layers.{l}.mlp.experts.{e}."
+        assert torch.equal(gu[:64], tensors[p + "gate_proj.weight"]) and torch.equal(gu[64:], tensors[p + "up_proj.weight"])
+        assert torch.equal(down, tensors[p + "down_proj.weight"])
+    assert disk.stats["hits"] >= 1 and disk.stats["prefetched"] == 1
+    disk.close(); ck.close()
+    plan = plan_layer({0: 500, 1: 1, 2: 40, 3: 0}, resident={0}, slot_bytes=50_000_000, staging_slots=1,
+                      rates=TransferRates(h2d_bytes_s=50e9), cpu=CpuService(per_expert_s=2e-4, workers=4))
+    assert plan.classes[0] == ExpertClass.RESIDENT and plan.classes[2] == ExpertClass.STAGED
+    assert plan.classes[1] == ExpertClass.CPU and 3 not in plan.classes
+    assert [c.experts for c in plan.cohorts] == [[2]] and plan.cpu_rows == 1
