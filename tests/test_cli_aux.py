@@ -1,0 +1,159 @@
+"""CLI parsing and JSON output, output-path guard, trace / verify tools, prefix cache, the
+calibration closure and cache -- all on CPU with the tiny decoder."""
+import json
+
+import pytest
+import torch
+
+from flyingfish_b200 import cli
+from flyingfish_b200.api import Model, generate_plain
+from flyingfish_b200.config import Settings
+from flyingfish_b200.planner.calibrate import (Closure, ClosureError, ClosureState, calibrate, check_runtime_dir,
+                                               host_memory_limit)
+
+
+def _run(argv, capsys):
+    assert cli.main(argv) == 0
+    return json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+
+
+def test_generate_json_fields(capsys):
+    out = _run(["--model", "tiny-llama", "--cpu", "--capacity", "128", "generate", "--tokens", "1,2,3,4", "--max-new-tokens", "5",
+                "--ignore-eos"], capsys)
+    for k in ("input_ids", "generated_ids", "text", "load_ms", "prefill_ms", "capture_ms", "decode_ms", "decode_steps",
+              "decode_tok_s", "graph", "dump", "trace_layer", "mode"):
+        assert k in out
+    assert out["input_ids"] == [1, 2, 3, 4] and len(out["generated_ids"]) == 5 and out["mode"] == "plain"
+    assert out["decode_steps"] == 4      # the first id comes from prefill
+
+
+def test_global_options_come_first_and_model_is_required(capsys, monkeypatch):
+    monkeypatch.delenv("FLYINGFISH_MODEL", raising=False)
+    with pytest.raises(SystemExit):
+        cli.main(["generate", "--tokens", "1"])
+    with pytest.raises(SystemExit):
+        cli.main(["--model", "tiny-llama", "--cpu", "generate", "--tokens", "1", "--prompt", "x"])
+    with pytest.raises(SystemExit):
+        cli.main(["--model", "tiny-llama", "--cpu", "--capacity", "8", "generate", "--tokens", "1,2,3", "--max-new-tokens", "9"])
+    monkeypatch.setenv("FLYINGFISH_MODEL", "tiny-llama")
+    out = _run(["--cpu", "--capacity", "64", "generate", "--prompt", "hi", "--max-new-tokens", "2", "--ignore-eos"], capsys)
+    assert out["input_ids"] == [104, 105]
+
+
+def test_tokens_file_forms(tmp_path):
+    class A: pass
+    for content, want in (([1, 2], [1, 2]), ({"input_ids": [3, 4]}, [3, 4]), ([[5, 6], [7]], [5, 6])):
+        p = tmp_path / f"t{len(str(content))}.json"
+        p.write_text(json.dumps(content))
+        a = A(); a.tokens = None; a.tokens_file = str(p)
+        assert cli.parse_tokens_arg(a) == want
+
+
+def test_output_path_guard(tmp_path):
+    (tmp_path / "exists.bin").write_text("x")
+    with pytest.raises(SystemExit):
+        cli.check_output_path(tmp_path / "exists.bin", None)
+    (tmp_path / "models").mkdir()
+    with pytest.raises(SystemExit):
+        cli.check_output_path(tmp_path / "models" / "new.bin", None)
+    md = tmp_path / "ckpt"; md.mkdir()
+    with pytest.raises(SystemExit):
+        cli.check_output_path(md / "trace.safetensors", str(md))
+    assert cli.check_output_path(tmp_path / "fine.bin", str(md)).name == "fine.bin"
+
+
+def test_mtp_depth_resolution():
+    assert cli.resolve_mtp_depth(None, False, "llama") == 0
+    assert cli.resolve_mtp_depth(None, True, "llama") == 4
+    assert cli.resolve_mtp_depth(None, True, "deepseek_v3") == 0
+    assert cli.resolve_mtp_depth(2, True, "deepseek_v3") == 2
+    with pytest.raises(SystemExit):
+        cli.resolve_mtp_depth(2, False, "llama")
+
+
+def test_inspect_tokenize_and_bench_floor(capsys):
+    out = _run(["inspect", "--shapes"], capsys)
+    assert "llama3-8b-shape" in out["shapes"] and out["shapes"]["deepseek-v3-shape"]["mla"]["kv_lora_rank"] == 512
+    out = _run(["tokenize", "--prompt", "abc"], capsys)
+    assert out == {"ids": [97, 98, 99], "count": 3}
+    with pytest.raises(SystemExit):
+        cli.main(["--model", "tiny-llama", "--cpu", "bench", "--steps", "10"])
+
+
+def test_dump_and_verify_roundtrip(tmp_path, capsys):
+    a, b = tmp_path / "a.safetensors", tmp_path / "b.safetensors"
+    base = ["--model", "tiny-llama", "--cpu", "--capacity", "64", "generate", "--tokens", "5,6,7", "--max-new-tokens", "2", "--ignore-eos"]
+    _run(base + ["--dump", str(a)], capsys)
+    _run(base + ["--dump", str(b), "--trace-layer", "1"], capsys)
+    with pytest.raises(SystemExit):
+        cli.main(base + ["--dump", str(tmp_path / "c.st"), "--graph"])
+    from flyingfish_b200.utils.verify import compare_traces, tensor_metrics
+    rep = compare_traces(a, a)
+    assert rep["ok"] and all(m["max_abs"] == 0 for m in rep["tensors"].values())
+    assert any(k.endswith("logits") and "top_two_margin" in m for k, m in rep["tensors"].items())
+    rep = compare_traces(b, a)
+    assert not rep["ok"] and any("missing_in" in m for m in rep["tensors"].values())
+    m = tensor_metrics(torch.tensor([1.0, 2.0]), torch.tensor([1.0, 2.0078125]))
+    assert m["bf16_bit_mismatches"] == 0 or m["half_ulp_ratio"] >= 1.0
+    lim = tmp_path / "lim.json"; lim.write_text(json.dumps({"*": 1e-9}))
+    assert compare_traces(a, a, lim)["ok"]
+
+
+def test_compare_logs(tmp_path):
+    from flyingfish_b200.utils.verify import compare_logs
+    (tmp_path / "a.log").write_text('{"generated_ids": [1, 2]}\n')
+    (tmp_path / "b.log").write_text('noise\n{"generated_ids": [1, 3]}\n')
+    assert not compare_logs(tmp_path / "a.log", tmp_path / "b.log")["ok"]
+    assert compare_logs(tmp_path / "a.log", tmp_path / "a.log")["ok"]
+
+
+def test_prefix_cache_roundtrip(tmp_path):
+    from flyingfish_b200.utils.prefix_cache import PrefixError, restore_prefix, save_prefix
+    m = Model.load("tiny-llama", Settings(capacity=256, max_batch=2, graph=False), device="cpu", seed=0)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 2048, (70,), generator=g).tolist()
+    want = generate_plain(m, ids, 6, ignore_eos=True, graph=False).ids
+    m.reset()
+    seq = m.engine.add_sequence(ids[:66])
+    m.engine.prefill([seq])
+    pkg = save_prefix(m, seq, tmp_path / "pfx")
+    m.reset()
+    seq2 = restore_prefix(m, pkg)
+    assert m.engine.kv.seqs[seq2.seq_id].length == 66
+    seq2.prompt = ids                      # continue with the rest of the prompt
+    first = m.engine.prefill([seq2])[0]
+    got = [first] + [m.engine.decode([seq2])[0] for _ in range(5)]
+    assert got == want
+    with pytest.raises(PrefixError):
+        save_prefix(m, seq2, pkg)          # no overwrite
+    other = Model.load("tiny-llama", Settings(capacity=256, max_batch=2, graph=False, kv_format="affine8"), device="cpu")
+    with pytest.raises(PrefixError, match="different"):
+        restore_prefix(other, pkg)
+    man = json.loads((pkg / "manifest.json").read_text()); man["tokens"][0] ^= 1
+    (pkg / "manifest.json").write_text(json.dumps(man))
+    m.reset()
+    with pytest.raises(PrefixError, match="corrupt"):
+        restore_prefix(m, pkg)
+
+
+def test_closure_state_machine_and_calibration_cache(tmp_path):
+    c = Closure()
+    c.measure("x"); c.declare_shape((1, 2, 3))
+    with pytest.raises(ClosureError):
+        c.capture()
+    c.freeze()
+    with pytest.raises(ClosureError):
+        c.measure("late")
+    c.capture(); c.declare_shape((4, 5, 6)); c.ready()
+    assert c.state is ClosureState.READY and c.captures == 1
+    with pytest.raises(ClosureError):
+        c.declare_shape((7, 8, 9))
+    c.declare_shape((1, 2, 3))
+    with pytest.raises(ClosureError):
+        check_runtime_dir(tmp_path / "models" / "rt")
+    assert host_memory_limit() > 0
+    st = Settings(runtime_dir=str(tmp_path / "rt"))
+    d1 = calibrate("qwen3-moe-tiny", st, cpu=True)
+    assert not d1["cached"] and d1["disk_bytes_s"] > 0 and "cpu_service" in d1
+    assert calibrate("qwen3-moe-tiny", st, cpu=True)["cached"]
+    assert not calibrate("qwen3-moe-tiny", st, force=True, cpu=True)["cached"]
