@@ -69,7 +69,13 @@ class Model:
             name = path.name
         else:
             spec = read_model_spec(path) if path.is_dir() else named_shape(model)
-            weights = random_decoder_weights(spec, seed, device, tp, epi)
+            if spec.mla is not None:
+                from .models.deepseek import build_deepseek_weights
+                from .models.weights import DTYPES, synthetic_source
+                weights = build_deepseek_weights(spec, synthetic_source(spec, seed, device, DTYPES[spec.dtype]),
+                                                 device, tp, epi)
+            else:
+                weights = random_decoder_weights(spec, seed, device, tp, epi)
             name = spec.name
         if spec.mla is not None:
             from .models.deepseek import DeepseekModel

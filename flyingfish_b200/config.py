@@ -139,6 +139,17 @@ def deepseek_v3_tiny() -> ModelSpec:
                     n_groups=4, topk_groups=2, routed_scaling=2.5, first_dense_layers=1, dense_ffn=512))
 
 
+def deepseek_v3_mini() -> ModelSpec:
+    """DeepSeek-V3 attention geometry (kv_lora 512, rope 64, nope 128, v 128) with a handful of
+    heads and layers: the smallest shape the MLA CUDA kernel serves."""
+    return ModelSpec(
+        name="deepseek-v3-mini", arch="deepseek_v3", layers=2, hidden=512, heads=4, kv_heads=4, head_dim=128,
+        ffn=1024, vocab=2048, rope_theta=1e4, rms_eps=1e-6,
+        mla=MlaSpec(q_lora_rank=256, kv_lora_rank=512, qk_nope_dim=128, qk_rope_dim=64, v_head_dim=128),
+        moe=MoeSpec(num_experts=16, top_k=4, expert_ffn=256, score="noaux", n_shared=1, shared_ffn=256,
+                    n_groups=4, topk_groups=2, routed_scaling=2.5, first_dense_layers=1, dense_ffn=1024))
+
+
 def qwen3_moe_235b() -> ModelSpec:
     return ModelSpec(
         name="qwen3-moe-235b-shape", arch="qwen3_moe", layers=94, hidden=4096, heads=64, kv_heads=4, head_dim=128,
@@ -155,7 +166,7 @@ def qwen3_moe_tiny() -> ModelSpec:
 
 NAMED_SHAPES = {
     "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
-    "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny,
+    "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }
 

@@ -67,7 +67,11 @@ class Engine:
         tp = model.w.tp.size
         hkv = max(1, spec.kv_heads // tp)
         dtype = model.w.embed.dtype
-        self.kv = PagedKVCache(spec.layers, hkv, spec.head_dim, num_blocks, settings.kv_block, dtype, self.device)
+        if spec.mla is not None:       # one latent row per token: [kv_lora | rope key], no separate V
+            self.kv = PagedKVCache(spec.layers, 1, spec.mla.kv_lora_rank + spec.mla.qk_rope_dim, num_blocks,
+                                   settings.kv_block, dtype, self.device, v_head_dim=0)
+        else:
+            self.kv = PagedKVCache(spec.layers, hkv, spec.head_dim, num_blocks, settings.kv_block, dtype, self.device)
         self.max_blocks = (settings.capacity + settings.kv_block - 1) // settings.kv_block
         self.max_batch = max(settings.max_batch, 1)
         self.max_prefill_rows = max_prefill_rows

@@ -408,3 +408,21 @@ def sample_rows(logits: torch.Tensor, temperature: float, top_k: int, top_p: flo
     check(rc, "ff_sample_rows")
     _count()
     return out
+
+
+def rope_inplace(x: torch.Tensor, positions: torch.Tensor, heads: int, dim: int, theta: float,
+                 inv_freq: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate-half RoPE on a standalone [rows, heads*dim] tensor (no cache write); same numerics
+    contract as :func:`rope_kv_paged`."""
+    if not _is_cuda(x):
+        rows = x.shape[0]
+        y = ref.rope_rotate_half(x[:, : heads * dim].reshape(rows, heads, dim), positions, theta, None, inv_freq)
+        x[:, : heads * dim] = y.reshape(rows, -1)
+        return x
+    rows, ld = _rows2d(x)
+    _require(dim % 16 == 0 and positions.dtype == torch.int32, "rope_inplace: dim % 16 == 0, int32 positions")
+    rc = kernels().ff_rope_kv_paged(ptr(x), ptr(positions), None, None, None, ptr(inv_freq), rows, heads, 0, dim, dim, 64, 0,
+                                    c_float(theta), ld, ptr(status_tensor(x.device)), stream_ptr())
+    check(rc, "ff_rope_kv_paged(rope only)")
+    _count()
+    return x
