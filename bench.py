@@ -130,7 +130,9 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=device)
         if args.parallelism == "tp":
             from flyingfish_b200.parallel.comm import TPComm
-            comm = TPComm.create(dist.group.WORLD, device)
+            from flyingfish_b200.config import named_shape as _ns
+            _h = _ns(args.model).hidden
+            comm = TPComm.create(dist.group.WORLD, device, slot_bytes=(8192 // world) * _h * 2)
 
     global_batch = args.batch if (args.parallelism == "tp" or world == 1) else args.batch * world
     local_batch = args.batch

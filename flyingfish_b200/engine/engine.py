@@ -165,6 +165,12 @@ class Engine:
             block_rows.append(list(kvs.blocks))
             logit_rows.append(row + take - 1)
             row += take
+        mult = getattr(self.model.comm, "size", 1) * 128 if getattr(self.model.comm, "fused", False) else 1
+        if mult > 1 and row >= mult and (row + mult - 1) // mult * mult <= fb.layout.max_rows:
+            # sequence-parallel prefill shards rows over the ranks in 128-row blocks: pad with rows
+            # that belong to no sequence (no KV write, no logits)
+            pad = (row + mult - 1) // mult * mult - row
+            ids += [0] * pad; positions += [0] * pad; slots += [-1] * pad
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
                 logit_rows=logit_rows, is_decode=False)
         fb.upload()

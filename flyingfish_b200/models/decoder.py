@@ -98,6 +98,8 @@ class DecoderModel:
         replaces the embedding lookup (multi-token-prediction heads feed a projected mix of the
         next token's embedding and the previous hidden state)."""
         w, s = self.w, self.spec
+        if inputs_embeds is None and self._sequence_parallel(b):
+            return self._hidden_states_sp(b, kv)
         if inputs_embeds is None:
             x, n = ops.embed_rmsnorm(b.ids, w.embed, w.layers[0].input_ln, s.rms_eps)
         else:
@@ -121,6 +123,42 @@ class DecoderModel:
         if self.normed_sink is not None:
             self.normed_sink.append(n)
         return n
+
+    # -- sequence-parallel prefill (tensor parallel, fused AG->GEMM / GEMM->RS) -------------------
+    def _sequence_parallel(self, b: ForwardBatch) -> bool:
+        c = self.comm
+        if getattr(c, "size", 1) < 2 or b.is_decode or not getattr(c, "fused", False) or self.trace is not None:
+            return False
+        if any(lw.router is not None or not lw.wgu_interleaved for lw in self.w.layers) or self.spec.qk_norm:
+            return False
+        f_local = self.w.layers[0].wdown.shape[1]
+        return c.sp_ok(b.rows, self.spec.hidden, self.spec.hidden) and (2 * f_local) % 256 == 0
+
+    def _hidden_states_sp(self, b: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
+        """Activations between the projections are row-sharded over the ranks (each owns
+        ``rows / world`` rows of the residual stream); QKV and gate/up run as all-gather -> GEMM,
+        O and down as GEMM -> reduce-scatter, each one fused kernel."""
+        w, s, c = self.w, self.spec, self.comm
+        rpr = b.rows // c.size
+        r0 = c.rank * rpr
+        x, n = ops.embed_rmsnorm(b.ids[r0: r0 + rpr].contiguous(), w.embed, w.layers[0].input_ln, s.rms_eps)
+        for i in range(s.layers):
+            lw = w.layers[i]
+            qkv = c.ag_linear(n, lw.wqkv)
+            ops.rope_kv_paged(qkv, b.positions, b.slots, kv.k[i], kv.v[i], self.hq, self.hkv, self.d, s.rope_theta)
+            a = torch.zeros(b.rows, self.hq * self.d, dtype=qkv.dtype, device=qkv.device)    # padding rows stay finite
+            ops.attn_prefill(qkv, kv.k[i], kv.v[i], b.block_table, b.q_start, b.q_lens, b.ctx_lens, b.max_q_len,
+                             self.hq, self.hkv, self.d, self.scale, out=a)
+            o = c.rs_linear(a, lw.wo)
+            n = ops.add_rmsnorm(o, x, lw.post_ln, s.rms_eps)
+            hmid = c.ag_linear(n, lw.wgu, swiglu=True)
+            dn = c.rs_linear(hmid, lw.wdown)
+            next_w = w.layers[i + 1].input_ln if i + 1 < s.layers else w.final_norm
+            n = ops.add_rmsnorm(dn, x, next_w, s.rms_eps)
+        full = c.all_gather_rows(n)
+        if self.normed_sink is not None:
+            self.normed_sink.append(full)
+        return full
 
     def logits(self, n: torch.Tensor, b: ForwardBatch) -> torch.Tensor:
         """lm_head on the rows named by ``b.logit_rows`` -> [n_rows, local vocab]."""

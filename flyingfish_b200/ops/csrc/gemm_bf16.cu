@@ -51,10 +51,37 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 
 // epi: 0 = store bf16; 1 = SwiGLU (columns [0,BN/2) of a tile are gate, [BN/2,BN) are up; output
 // has N/2 columns); 2 = store fp32.
-template <int BN, int STAGES>
+// COMM (tensor-parallel prefill, rows split evenly over the ranks in 128-row blocks):
+//   1 = all-gather -> GEMM : A is row-sharded. The epilogue warps first push this rank's shard into
+//       every peer's arena (peer stores, one flag per 128-row block), the TMA producer waits for
+//       the block's flag before loading it from the LOCAL arena copy; own rows are scheduled first
+//       so the transfer of the other shards overlaps the math.
+//   2 = GEMM -> reduce-scatter : every finished tile is stored straight into the arena slot of the
+//       rank that owns those rows (peer stores from the epilogue); when all column tiles of a row
+//       block are out, its flag goes to the owner. After its tiles a CTA reduces owned row blocks:
+//       waits for the block's flags from all ranks and sums the slots in rank order.
+struct CommArgs {
+  PeerArena ar;
+  int rows_per_rank;                  // multiple of 128; M == rows_per_rank * world
+  int* tile_counters;                 // COMM 2: int32 per row tile, zero before the first launch
+  __nv_bfloat16* rs_out;              // COMM 2: [rows_per_rank, N]
+  const __nv_bfloat16* x_shard;       // COMM 1: [rows_per_rank, K]
+  int ldx;
+};
+
+template <int COMM>
+__device__ __forceinline__ int comm_tm(int tm, int tiles_per_rank, int rank, int world) {
+  if (COMM != 1) return tm;
+  // logical order: own rows first, then the ranks after me
+  const int j = tm / tiles_per_rank, r = tm - j * tiles_per_rank;
+  return ((rank + j) % world) * tiles_per_rank + r;
+}
+
+template <int BN, int STAGES, int COMM>
 __global__ void __launch_bounds__(192, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 void* __restrict__ Cout, int M, int N, int K, int ldc, int epi, int* status) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA1,
+                 const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout, int M, int N, int K, int ldc, int epi,
+                 int* status, CommArgs ca) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -66,11 +93,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int kblocks = (K + BK - 1) / BK;
+  const int tiles_per_rank = COMM ? ca.rows_per_rank / BM : 1;
+  int epoch = 0;
+  if (COMM) epoch = ld_volatile(arena_epoch(ca.ar)) + 1;
+  const int parity = epoch & 1;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&bars.tmem_full[i], 1); mbar_init(&bars.tmem_empty[i], 4); }
-    bars.abort_flag = 0;
+    bars.abort_flag = 0; bars.is_last = 0;
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(&bars.tmem_base, TMEM_COLS); tmem_relinquish(); }
@@ -87,12 +118,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+        tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world);
+        const int src = tm / tiles_per_rank, rb = tm - src * tiles_per_rank;
+        if (COMM == 1) {
+          // the rows of this tile must have arrived in the local arena copy
+          if (!wait_flag(arena_flag(ca.ar, ca.ar.rank, src, rb), epoch, status, KID_AG_GEMM, src)) {
+            bars.abort_flag = 1; ok = false; break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");     // peer-written data -> visible to the TMA engine
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES; const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag, status, KID_GEMM_BF16, 1)) { ok = false; break; }
           mbar_expect_tx(&bars.full[s], STAGE_BYTES);
           uint8_t* sa = smem + s * STAGE_BYTES;
-          tma_load_2d(sa, &tmA, &bars.full[s], kb * BK, tm * BM);
+          if (COMM == 1) tma_load_3d(sa, parity ? &tmA1 : &tmA, &bars.full[s], kb * BK, rb * BM, src);
+          else tma_load_2d(sa, &tmA, &bars.full[s], kb * BK, tm * BM);
           tma_load_2d(sa + A_BYTES, &tmB, &bars.full[s], kb * BK, tn * BN);
         }
       }
@@ -127,10 +168,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // epilogue warps 2..5 ; TMEM lane quarter = warp % 4
     const int q = warp & 3;
+    const int e = (warp - 2) * 32 + lane;
     uint32_t tile_it = 0;
     bool ok = true;
+    if (COMM == 1) {
+      // push my activation shard, 128-row block by block, to every rank (myself included)
+      const int kvec = K >> 3;
+      for (int rb = blockIdx.x; rb < tiles_per_rank; rb += gridDim.x) {
+        for (int pi = 0; pi < ca.ar.world; ++pi) {
+          const int p = (ca.ar.rank + pi) % ca.ar.world;
+          uint4* dst = reinterpret_cast<uint4*>(arena_slot(ca.ar, p, parity, ca.ar.rank)) + (size_t)rb * BM * kvec;
+          for (int idx = e; idx < BM * kvec; idx += 128) {
+            const int r = idx / kvec, c = idx - r * kvec;
+            dst[idx] = reinterpret_cast<const uint4*>(ca.x_shard + (size_t)(rb * BM + r) * ca.ldx)[c];
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (e == 0) {
+          __threadfence_system();
+          for (int p = 0; p < ca.ar.world; ++p) st_release_sys(arena_flag(ca.ar, p, ca.ar.rank, rb), epoch);
+        }
+      }
+    }
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
       int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
+      tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world);
       const int acc = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
       if (!mbar_wait(&bars.tmem_full[acc], aph, abort_flag, status, KID_GEMM_BF16, 4)) { ok = false; break; }
       tc_fence_after();
@@ -191,6 +253,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       } else {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + (size_t)row * ldc + (size_t)tn * BN;
+        if (COMM == 2) {
+          // the rows of this tile belong to rank `owner`: store into its arena slot for source = me
+          const int owner = tm / tiles_per_rank;
+          crow = reinterpret_cast<__nv_bfloat16*>(arena_slot(ca.ar, owner, parity, ca.ar.rank)) +
+                 (size_t)(row - owner * ca.rows_per_rank) * N + (size_t)tn * BN;
+        }
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -216,6 +284,58 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.tmem_empty[acc]);
+      if (COMM == 2) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (e == 0) {
+          __threadfence_system();
+          const int prev = atomicAdd(&ca.tile_counters[tm], 1);
+          if (prev == tiles_n - 1) {                      // last column tile of this row block on this rank
+            ca.tile_counters[tm] = 0;
+            __threadfence_system();
+            const int owner = tm / tiles_per_rank;
+            st_release_sys(arena_flag(ca.ar, owner, ca.ar.rank, tm - owner * tiles_per_rank), epoch);
+          }
+        }
+      }
+    }
+    if (COMM == 2 && ok) {
+      // reduce the row blocks this rank owns: slots of all source ranks, in rank order
+      const int nvec = N >> 3;
+      for (int i = blockIdx.x; i < tiles_per_rank; i += gridDim.x) {
+        if (e == 0) bars.is_last = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (e < ca.ar.world)
+          if (!wait_flag(arena_flag(ca.ar, ca.ar.rank, e, i), epoch, status, KID_GEMM_RS, e)) bars.is_last = 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (bars.is_last) {
+          for (int idx = e; idx < BM * nvec; idx += 128) {
+            const size_t off = (size_t)i * BM * nvec + idx;
+            float a8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a8[j] = 0.f;
+            for (int r = 0; r < ca.ar.world; ++r) {
+              const uint4 d = reinterpret_cast<const uint4*>(arena_slot(ca.ar, ca.ar.rank, parity, r))[off];
+              const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[2 * j] += f.x; a8[2 * j + 1] += f.y; }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(a8[0], a8[1]); o.y = pack_bf16x2(a8[2], a8[3]);
+            o.z = pack_bf16x2(a8[4], a8[5]); o.w = pack_bf16x2(a8[6], a8[7]);
+            reinterpret_cast<uint4*>(ca.rs_out)[off] = o;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
+    if (COMM && e == 0) {
+      __threadfence();
+      const int prev = atomicAdd(arena_done(ca.ar), 1);
+      if (prev == (int)gridDim.x - 1) {
+        *arena_done(ca.ar) = 0;
+        __threadfence();
+        *reinterpret_cast<volatile int*>(arena_epoch(ca.ar)) = epoch;
+      }
     }
   }
 
@@ -252,12 +372,87 @@ FF_EXPORT int ff_gemm_bf16(const void* X, const void* W, void* Y, int M, int N, 
   r = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, BK, BN);
   if (r) return r;
   const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
-  auto kern = gemm_bf16_kernel<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, 0>;
   static bool attr_done = false;
   if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 192, smem, stream>>>(tmA, tmB, Y, M, N, K, ldy, epi, status);
+  CommArgs none = {};
+  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmB, Y, M, N, K, ldy, epi, status, none);
+  return launch_result();
+}
+
+static int fill_comm(CommArgs& ca, const unsigned long long* ptrs, int rank, int world, long long half_bytes,
+                     long long slot_bytes, int M, long long need_slot_bytes) {
+  if (world < 2 || world > MAX_RANKS || rank < 0 || rank >= world) return FF_HOST_BAD_SHAPE;
+  if (M % (world * BM)) return FF_HOST_BAD_SHAPE;
+  if (need_slot_bytes > slot_bytes || half_bytes < slot_bytes * world) return FF_HOST_TOO_LARGE;
+  if (M / world / BM > MAX_FLAGS) return FF_HOST_TOO_LARGE;
+  for (int i = 0; i < MAX_RANKS; ++i) ca.ar.base[i] = i < world ? reinterpret_cast<uint8_t*>(ptrs[i]) : nullptr;
+  ca.ar.rank = rank; ca.ar.world = world; ca.ar.half_bytes = half_bytes; ca.ar.slot_bytes = slot_bytes;
+  ca.rows_per_rank = M / world;
+  return 0;
+}
+
+// Column-parallel projection fused with the all-gather of its row-sharded input:
+// Y[M, N] = gather(X_shards)[M, K] · W[N, K]ᵀ, X_shard = this rank's rows [M/world, K].
+FF_EXPORT int ff_ag_gemm(const unsigned long long* ptrs, int rank, int world, long long half_bytes, long long slot_bytes,
+                         const void* x_shard, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
+                         int epi, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return FF_HOST_BAD_SHAPE;
+  if (epi == 1 && (N % 256)) return FF_HOST_BAD_SHAPE;
+  if (epi == 2) return FF_HOST_UNSUPPORTED;
+  const int out_cols = (epi == 1) ? N / 2 : N;
+  if ((ldy % 8) || ldy < out_cols || (reinterpret_cast<uintptr_t>(Y) & 15)) return FF_HOST_BAD_ALIGN;
+  CommArgs ca = {};
+  int r = fill_comm(ca, ptrs, rank, world, half_bytes, slot_bytes, M, (long long)(M / world) * K * 2);
+  if (r) return r;
+  ca.x_shard = reinterpret_cast<const __nv_bfloat16*>(x_shard); ca.ldx = ldx;
+  constexpr int BN = 256, STAGES = 4;
+  CUtensorMap tmA0, tmA1, tmB;
+  uint8_t* data = reinterpret_cast<uint8_t*>(ptrs[rank]) + DATA_OFF;
+  r = make_tmap_3d(&tmA0, data, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, ca.rows_per_rank, world, (uint64_t)K * 2,
+                   (uint64_t)slot_bytes, BK, BM, 1);
+  if (r) return r;
+  r = make_tmap_3d(&tmA1, data + half_bytes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, ca.rows_per_rank, world,
+                   (uint64_t)K * 2, (uint64_t)slot_bytes, BK, BM, 1);
+  if (r) return r;
+  r = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, BK, BN);
+  if (r) return r;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+  auto kern = gemm_bf16_kernel<BN, STAGES, 1>;
+  static bool attr_done = false;
+  if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, 192, smem, stream>>>(tmA0, tmA1, tmB, Y, M, N, K, ldy, epi, status, ca);
+  return launch_result();
+}
+
+// Row-parallel projection fused with the reduce-scatter of its output:
+// out[M/world, N] = rows owned by this rank of sum_r X_r[M, K_r] · W_r[N, K_r]ᵀ.
+FF_EXPORT int ff_gemm_rs(const unsigned long long* ptrs, int rank, int world, long long half_bytes, long long slot_bytes,
+                         const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldw,
+                         int* tile_counters, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (N % 8)) return FF_HOST_BAD_SHAPE;
+  if (!tile_counters || (reinterpret_cast<uintptr_t>(out) & 15)) return FF_HOST_BAD_ALIGN;
+  CommArgs ca = {};
+  int r = fill_comm(ca, ptrs, rank, world, half_bytes, slot_bytes, M, (long long)(M / world) * N * 2);
+  if (r) return r;
+  ca.tile_counters = tile_counters; ca.rs_out = reinterpret_cast<__nv_bfloat16*>(out);
+  constexpr int BN = 256, STAGES = 4;
+  CUtensorMap tmA, tmB;
+  r = make_tmap_2d(&tmA, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, (uint64_t)ldx * 2, BK, BM);
+  if (r) return r;
+  r = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, BK, BN);
+  if (r) return r;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+  auto kern = gemm_bf16_kernel<BN, STAGES, 2>;
+  static bool attr_done = false;
+  if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmB, nullptr, M, N, K, N, 0, status, ca);
   return launch_result();
 }
 

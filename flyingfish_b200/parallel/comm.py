@@ -94,15 +94,18 @@ class TPComm:
         self.group, self.device, self.arena = group, device, arena
         self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
         self.fused = arena is not None
-        self.stats = {"gemm_ar": 0, "oneshot_ar": 0, "nccl_ar": 0}
+        self.stats = {"gemm_ar": 0, "oneshot_ar": 0, "nccl_ar": 0, "ag_gemm": 0, "gemm_rs": 0}
+        self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=device) if arena is not None else None
 
     @classmethod
     def create(cls, group: dist.ProcessGroup, device: torch.device | str, fused: bool = True,
-               self_test: bool = True) -> "TPComm":
+               self_test: bool = True, slot_bytes: int = SLOT_BYTES) -> "TPComm":
+        """``slot_bytes``: bytes one rank may deposit in a peer per collective; sequence-parallel
+        prefill needs ``rows_per_rank * hidden * 2``."""
         device = torch.device(device)
         arena = None
         if device.type == "cuda" and fused and dist.get_world_size(group) > 1:
-            arena = SymmArena(group, device)
+            arena = SymmArena(group, device, max(SLOT_BYTES, (slot_bytes + 255) // 256 * 256))
             if self_test:
                 arena.self_test()
             log_json("cuda_peer_topology", verbose_only=True, rank=arena.rank, world=arena.world,
@@ -152,6 +155,48 @@ class TPComm:
             ops._count()
             return out
         return self.all_reduce(ops.linear(x, w))
+
+    # -- sequence-parallel prefill: fused all-gather -> GEMM and GEMM -> reduce-scatter ---------
+    def sp_ok(self, rows: int, k: int, n: int) -> bool:
+        """Can ``rows`` (total) be processed with the fused sequence-parallel kernels?"""
+        if not self.fused or rows % (self.size * 128):
+            return False
+        rpr = rows // self.size
+        return rpr * max(k, n) * 2 <= self.arena.slot_bytes
+
+    def ag_linear(self, x_shard: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+        """Column-parallel projection of row-sharded activations: returns ``[rows_total, N_local]``
+        (``N_local / 2`` with the fused SwiGLU epilogue) -- one kernel (``ff_ag_gemm``)."""
+        rpr, k = x_shard.shape
+        n = w.shape[0]
+        m = rpr * self.size
+        out = torch.empty(m, n // 2 if swiglu else n, dtype=torch.bfloat16, device=x_shard.device)
+        rc = oplib.kernels().ff_ag_gemm(*self.arena.args(), oplib.ptr(x_shard), oplib.ptr(w), oplib.ptr(out), m, n, k,
+                                        x_shard.stride(0), w.stride(0), out.stride(0), 1 if swiglu else 0,
+                                        oplib.ptr(oplib.status_tensor(x_shard.device)), oplib.stream_ptr())
+        oplib.check(rc, "ff_ag_gemm")
+        self.stats["ag_gemm"] += 1
+        ops._count()
+        return out
+
+    def rs_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """Row-parallel projection with the reduce-scatter fused in: returns this rank's
+        ``[rows_total / world, N]`` rows of the summed output -- one kernel (``ff_gemm_rs``)."""
+        m, k = x.shape
+        n = w.shape[0]
+        out = torch.empty(m // self.size, n, dtype=torch.bfloat16, device=x.device)
+        rc = oplib.kernels().ff_gemm_rs(*self.arena.args(), oplib.ptr(x), oplib.ptr(w), oplib.ptr(out), m, n, k,
+                                        x.stride(0), w.stride(0), oplib.ptr(self.tile_counters),
+                                        oplib.ptr(oplib.status_tensor(x.device)), oplib.stream_ptr())
+        oplib.check(rc, "ff_gemm_rs")
+        self.stats["gemm_rs"] += 1
+        ops._count()
+        return out
+
+    def all_gather_rows(self, x_shard: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(x_shard.shape[0] * self.size, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        dist.all_gather_into_tensor(out, x_shard.contiguous(), group=self.group)
+        return out
 
     def all_gather_cat(self, x: torch.Tensor) -> torch.Tensor:
         """Concatenate equally-shaped shards along the last dim."""

@@ -82,3 +82,19 @@ def test_ep2_fused_dispatch_combine_gpu(tmp_path):
     assert res["stats"]["fused_calls"] > 0
     for r in res["per_rank"]:
         assert r["tokens"] == _single_moe("cuda", r["prompts"])
+
+
+@pytest.mark.gpu
+def test_tp2_sequence_parallel_fused_prefill(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _launch(2, "cuda", "sp", tmp_path, 29516)
+    assert res["ok"], res["errs"]
+    assert res["stats"]["ag_gemm"] > 18 and res["stats"]["gemm_rs"] > 18, "the model's prefill must take the fused path"
+    from flyingfish_b200.api import Model
+    from flyingfish_b200.config import Settings
+    m = Model.load("tiny-llama", Settings(capacity=1024, max_batch=4, graph=False), device="cuda", seed=0)
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (300, 150)]
+    single = m.generate_batch(prompts, 6)
+    assert res["tokens"][0][:2] == single[0][:2] and res["tokens"][1][:2] == single[1][:2]

@@ -31,7 +31,7 @@ def main():
     from flyingfish_b200.api import Model
     from flyingfish_b200.config import Settings
     from flyingfish_b200 import ops
-    comm = TPComm.create(dist.group.WORLD, device)
+    comm = TPComm.create(dist.group.WORLD, device, slot_bytes=8 << 20)
     result = {}
     if args.mode == "model":
         m = Model.load("tiny-llama", Settings(capacity=256, max_batch=4, graph=(args.device == "cuda")), device=device,
@@ -70,6 +70,38 @@ def main():
             torch.cuda.synchronize()
             ops.check_status(device)
         result.update(ok=ok, errs=errs, same=same, stats=comm.stats)
+    elif args.mode == "sp":
+        # fused all-gather -> GEMM and GEMM -> reduce-scatter against an FP32 reference, repeated
+        # launches, then a sequence-parallel prefill of the tiny decoder
+        g = torch.Generator().manual_seed(21)
+        ok, errs = True, []
+        for (m_, n_, k_) in [(256 * world, 512, 256), (128 * world, 768, 1024), (512 * world, 256, 2048)]:
+            x = torch.randn(m_, k_, generator=g).to(torch.bfloat16)
+            wt = (torch.randn(n_, k_, generator=g) * 0.05).to(torch.bfloat16)
+            rpr = m_ // world
+            want = (x.float() @ wt.float().t())
+            for rep in range(3):
+                y = comm.ag_linear(x[rank * rpr: (rank + 1) * rpr].to(device).contiguous(), wt.to(device))
+                err = (y.float().cpu() - want).abs().max().item()
+                errs.append(err); ok = ok and err <= 0.05 + 0.02 * want.abs().max().item()
+            # row-parallel: K split over ranks
+            kk = k_ // world
+            xs = x[:, rank * kk: (rank + 1) * kk].to(device).contiguous()
+            ws_ = wt[:, rank * kk: (rank + 1) * kk].to(device).contiguous()
+            parts = [(x[:, r * kk: (r + 1) * kk].float() @ wt[:, r * kk: (r + 1) * kk].float().t()).to(torch.bfloat16).float()
+                     for r in range(world)]
+            want_rs = sum(parts)[rank * rpr: (rank + 1) * rpr]
+            for rep in range(3):
+                y = comm.rs_linear(xs, ws_)
+                err = (y.float().cpu() - want_rs).abs().max().item()
+                errs.append(err); ok = ok and err <= 0.05 + 0.02 * want_rs.abs().max().item()
+        m = Model.load("tiny-llama", Settings(capacity=1024, max_batch=4, graph=True), device=device, seed=0, comm=comm)
+        gg = torch.Generator().manual_seed(8)
+        prompts = [torch.randint(0, 2048, (n,), generator=gg).tolist() for n in (300, 150)]
+        toks = m.generate_batch(prompts, 6)
+        torch.cuda.synchronize()
+        ops.check_status(device)
+        result.update(ok=ok, errs=errs, tokens=toks, stats=comm.stats)
     elif args.mode == "ep":
         from flyingfish_b200.parallel.ep import EPComm
         from flyingfish_b200.config import named_shape
