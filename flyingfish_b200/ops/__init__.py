@@ -125,7 +125,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
         scratch_b, counter_b = c_longlong(0), c_longlong(0)
         splits = lib.ff_gemm_skinny_plan(m, n, k, ctypes.byref(scratch_b), ctypes.byref(counter_b))
         ws = workspace(x.device)
-        scratch = ws.ensure("gemm_scratch", scratch_b.value // 4) if splits > 1 else None
+        scratch = ws.ensure("gemm_scratch", scratch_b.value // 4) if scratch_b.value > 0 else None
         _require(counter_b.value // 4 <= ws.gemm_counters.numel(), "linear: too many column tiles for counters")
         rc = lib.ff_gemm_skinny(ptr(x), ptr(w), ptr(out), m, n, k, ldx, ldw, out.stride(0), splits, ptr(scratch),
                                 ptr(ws.gemm_counters), ptr(st), stream_ptr())

@@ -181,6 +181,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
                    int* status) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem[];
   // blockIdx.y = row tile * hkv + kv head: nq * G packed rows are processed 16 at a time
   const int split = blockIdx.x, kvh = blockIdx.y % hkv, rt = blockIdx.y / hkv, b = blockIdx.z;
@@ -278,6 +280,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 __global__ void __launch_bounds__(128)
 attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
                   int rows_per_seq, int nsplit) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x, b = row / rows_per_seq, r = row % rows_per_seq, d = threadIdx.x;
   float M = NEG_BIG;
   for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(((size_t)b * nsplit + s) * rows_per_seq + r) * 2]);
@@ -407,12 +411,12 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
   const float scale_log2 = scale * 1.4426950408889634f;
   const int row_tiles = (nq * (hq / hkv) + 15) / 16;
   dim3 grid(nsplit, hkv * row_tiles, batch);
-  attn_decode_kernel<<<grid, 128, ATTN_SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache,
+  if (int lr_ = launch_pdl(attn_decode_kernel, dim3(grid), dim3(128), ATTN_SMEM, s, 0, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache,
       (const __nv_bfloat16*)vcache, block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
-      ldq, max_blocks, num_blocks, nsplit, scale_log2, status);
+      ldq, max_blocks, num_blocks, nsplit, scale_log2, status)) return lr_;
   if (int r = launch_result()) return r;
   if (nsplit > 1) {
-    attn_merge_kernel<<<batch * nq * hq, 128, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, nq * hq, nsplit);
+    if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * nq * hq), dim3(128), 0, s, 0, part_o, part_ml, (__nv_bfloat16*)out, nq * hq, nsplit)) return lr_;
     return launch_result();
   }
   return 0;

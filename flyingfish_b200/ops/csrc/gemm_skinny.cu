@@ -3,6 +3,8 @@
 //
 //   * Swap-AB: a 128-row weight tile is the UMMA "A" operand, the tokens are the UMMA N dimension
 //     (padded to 16), so D[n (128 TMEM lanes), t (columns)] and small batches waste no tile rows.
+//   * Few column tiles (tiles x 2 <= SMs): cluster split-K, the partials meet in distributed shared
+//     memory (see the kernel). Otherwise:
 //   * Persistent stream-K: the (column tile, k-block) work units are split evenly over one CTA per
 //     SM, so no wave quantisation for any N. A CTA's share may start or end inside a tile; such
 //     partial tiles go to FP32 scratch and the CTA that completes a tile (atomic arrival count)
@@ -54,16 +56,89 @@ __device__ __forceinline__ bool next_segment(long long& u, long long u1, int kbl
   return true;
 }
 
+// Final output of one tile (or of this CTA's rows of it): the BF16 values sit in the staging tile
+// sT[t][128]; rows handled are t = row0 + 8*row_step*i + row_step*(e/16). Either stores them to Y
+// or (FUSE_AR) pushes them to every peer, waits for the peers' rows and writes the rank-ordered sum.
+// Called by all 128 epilogue threads.
+template <bool FUSE_AR>
+__device__ __forceinline__ void emit_tile(const __nv_bfloat16* sT, __nv_bfloat16* __restrict__ Y, int M, int N, int ldy,
+                                          int tile, int flag_idx, int row0, int row_step, int e, SkinnyBars& bars,
+                                          const PeerArena& ar, int ar_epoch, int* status) {
+  const int c16 = e & 15, r0 = e >> 4;          // 16 threads per 256-byte tile row
+  const int col = tile * SBM + c16 * 8;
+  const int t_first = row0 + row_step * r0, t_inc = 8 * row_step;
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (!FUSE_AR) {
+    const bool vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
+    if (col + 8 <= N && vec_ok) {
+      for (int t = t_first; t < M; t += t_inc)
+        *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8);
+    } else if (col < N) {
+      for (int t = t_first; t < M; t += t_inc)
+        for (int j = 0; j < 8 && col + j < N; ++j) Y[(size_t)t * ldy + col + j] = sT[t * SBM + c16 * 8 + j];
+    }
+  } else {
+    const int parity = ar_epoch & 1;
+    if (col < N) {
+      for (int pi = 1; pi < ar.world; ++pi) {
+        const int p = (ar.rank + pi) % ar.world;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, p, parity, ar.rank));
+        for (int t = t_first; t < M; t += t_inc)
+          *reinterpret_cast<uint4*>(dst + (size_t)t * N + col) = *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8);
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (e == 0) {
+      __threadfence_system();
+      for (int pi = 1; pi < ar.world; ++pi)
+        st_release_sys(arena_flag(ar, (ar.rank + pi) % ar.world, ar.rank, flag_idx), ar_epoch);
+      bars.flag_b = 1;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (e < ar.world && e != ar.rank)
+      if (!wait_flag(arena_flag(ar, ar.rank, e, flag_idx), ar_epoch, status, KID_GEMM_AR, e)) bars.flag_b = 0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (bars.flag_b && col < N) {
+      for (int t = t_first; t < M; t += t_inc) {
+        float a8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a8[j] = 0.f;
+        for (int r = 0; r < ar.world; ++r) {
+          const uint4 d = (r == ar.rank)
+              ? *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8)
+              : *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const __nv_bfloat16*>(arena_slot(ar, ar.rank, parity, r)) + (size_t)t * N + col);
+          const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[2 * j] += f.x; a8[2 * j + 1] += f.y; }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(a8[0], a8[1]); o.y = pack_bf16x2(a8[2], a8[3]);
+        o.z = pack_bf16x2(a8[4], a8[5]); o.w = pack_bf16x2(a8[6], a8[7]);
+        *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = o;
+      }
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");   // sT, flag_a and flag_b are reused by the next segment
+}
+
+// cl_size == 1: persistent stream-K over gridDim.x CTAs.
+// cl_size  > 1: cluster split-K. Cluster c owns column tile c; its CTA r multiplies k-blocks
+//   [kblocks*r/S, kblocks*(r+1)/S), leaves the FP32 partial in its own shared memory, and after a
+//   cluster barrier CTA r sums token rows t = r (mod S) over the S partials through distributed shared
+//   memory in CTA order (bitwise deterministic) -- no trip through global scratch, no serial fix-up.
 template <bool FUSE_AR>
 __global__ void __launch_bounds__(192, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldy, int ntok, int stages, int stage_smem_off,
-                   float* __restrict__ scratch, int* __restrict__ counters, int* status, PeerArena ar) {
+                   int cl_size, float* __restrict__ scratch, int* __restrict__ counters, int* status, PeerArena ar) {
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   __shared__ SkinnyBars bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __nv_bfloat16* sT = reinterpret_cast<__nv_bfloat16*>(smem);       // AR staging tile [t][128] (FUSE_AR only)
+  __nv_bfloat16* sT = reinterpret_cast<__nv_bfloat16*>(smem);       // BF16 staging tile [t][128]
   uint8_t* pipe = smem + stage_smem_off;
+  float* sP = reinterpret_cast<float*>(pipe);                       // cluster mode: FP32 partial [t][128], after the main loop
   constexpr int A_BYTES = SBM * SBK * 2;
   const int b_bytes = ntok * SBK * 2;
   const int stage_bytes = A_BYTES + b_bytes;
@@ -73,7 +148,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int kblocks = (K + SBK - 1) / SBK;
   const long long total = (long long)tiles_n * kblocks;
   const int G = gridDim.x;
-  const long long u0 = total * blockIdx.x / G, u1 = total * (blockIdx.x + 1) / G;
+  const bool clustered = cl_size > 1;
+  const int crank = clustered ? (int)cluster_ctarank() : 0;
+  long long u0, u1;
+  if (clustered) {
+    const long long base = (long long)(blockIdx.x / cl_size) * kblocks;
+    u0 = base + (long long)kblocks * crank / cl_size; u1 = base + (long long)kblocks * (crank + 1) / cl_size;
+  } else {
+    u0 = total * blockIdx.x / G; u1 = total * (blockIdx.x + 1) / G;
+  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < stages; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.empty[i], 1); }
@@ -81,6 +164,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     bars.abort_flag = 0; bars.flag_a = 0; bars.flag_b = 0;
     mbar_fence_init();
   }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX); }
   if (warp == 1) { tmem_alloc(&bars.tmem_base, tmem_cols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -90,17 +174,31 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX);
+      const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+      // Weights are written by no kernel, so the first `stages` weight tiles are requested before
+      // the wait on the preceding kernel; the activations follow once that kernel is complete.
+      const uint32_t pre = (uint32_t)min((long long)stages, u1 - u0);
+      {
+        uint32_t it = 0; long long u = u0; Segment sg;
+        while (it < pre && next_segment(u, u1, kblocks, sg))
+          for (int kb = sg.kb0; kb < sg.kb1 && it < pre; ++kb, ++it) {
+            mbar_expect_tx(&bars.full[it], stage_bytes);
+            tma_load_2d_hint(pipe + it * stage_bytes, &tmW, &bars.full[it], kb * SBK, sg.tile * SBM, pol_w);
+          }
+      }
+      pdl_wait();
       uint32_t it = 0; bool ok = true;
       long long u = u0; Segment sg;
       while (ok && next_segment(u, u1, kblocks, sg)) {
         for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % stages; const uint32_t ph = (it / stages) & 1;
-          if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag, status, KID_GEMM_SKINNY, 1)) { ok = false; break; }
-          mbar_expect_tx(&bars.full[s], stage_bytes);
           uint8_t* sa = pipe + s * stage_bytes;
-          tma_load_2d(sa, &tmW, &bars.full[s], kb * SBK, sg.tile * SBM);
-          tma_load_2d(sa + A_BYTES, &tmX, &bars.full[s], kb * SBK, 0);
+          if (it >= pre) {
+            if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag, status, KID_GEMM_SKINNY, 1)) { ok = false; break; }
+            mbar_expect_tx(&bars.full[s], stage_bytes);
+            tma_load_2d_hint(sa, &tmW, &bars.full[s], kb * SBK, sg.tile * SBM, pol_w);
+          }
+          tma_load_2d_hint(sa + A_BYTES, &tmX, &bars.full[s], kb * SBK, 0, pol_x);
         }
       }
     }
@@ -134,6 +232,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int q = warp & 3;
     const int nl = q * 32 + lane;                 // row inside the weight tile
     const int e = (warp - 2) * 32 + lane;         // 0..127, cooperative index
+    pdl_wait();                                   // scratch, counters, the arena and Y belong to earlier kernels until here
     int ar_epoch = 0;
     if (FUSE_AR) ar_epoch = ld_volatile(arena_epoch(ar)) + 1;
     uint32_t seg_it = 0; bool ok = true;
@@ -144,6 +243,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (!mbar_wait(&bars.tmem_full[acc], aph, abort_flag, status, KID_GEMM_SKINNY, 4)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * ntok;
+      if (clustered) {
+        // the pipeline is drained (single segment): its shared memory now holds the FP32 partial
+        for (int c = 0; c < ntok; c += 16) {
+          uint32_t r[16];
+          tmem_ld_x16(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (c + j < M) sP[(c + j) * SBM + nl] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        break;
+      }
       const bool whole = sg.kb0 == 0 && sg.kb1 == kblocks;
       bool final_here = whole;
       const int c16 = e & 15, r0 = e >> 4;          // cooperative layout: 16 threads per 256-byte tile row
@@ -186,30 +297,37 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         final_here = bars.flag_a != 0;
         if (final_here) {
           __threadfence();
-          // vectorised fix-up: each thread owns 8 columns of rows r0, r0+8, ...; four rows at a
-          // time keep eight independent 16-byte loads in flight per partial
+          // vectorised fix-up: each thread owns 8 columns of rows r0, r0+8, ...; four rows of two
+          // partials at a time keep sixteen independent 16-byte loads in flight; the adds stay in
+          // ascending CTA order
           for (int t0 = r0; t0 < M; t0 += 32) {
             float a[4][8];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
               for (int j = 0; j < 8; ++j) a[i][j] = 0.f;
-            for (int c = c_first; c <= c_last; ++c) {
-              const float* src = scratch + ((size_t)(2 * c + (c == c_first ? 1 : 0)) * M) * SBM + c16 * 8;
-              float4 v[4][2];
+            for (int c = c_first; c <= c_last; c += 2) {
+              float4 v[2][4][2];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int t = t0 + 8 * i;
-                if (t < M) {
-                  v[i][0] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM));
-                  v[i][1] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM + 4));
-                } else { v[i][0] = make_float4(0, 0, 0, 0); v[i][1] = v[i][0]; }
+              for (int h = 0; h < 2; ++h) {
+                const int cc = c + h;
+                const float* src = scratch + ((size_t)(2 * cc + (cc == c_first ? 1 : 0)) * M) * SBM + c16 * 8;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int t = t0 + 8 * i;
+                  if (t < M && cc <= c_last) {
+                    v[h][i][0] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM));
+                    v[h][i][1] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM + 4));
+                  } else { v[h][i][0] = make_float4(0, 0, 0, 0); v[h][i][1] = v[h][i][0]; }
+                }
               }
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                a[i][0] += v[i][0].x; a[i][1] += v[i][0].y; a[i][2] += v[i][0].z; a[i][3] += v[i][0].w;
-                a[i][4] += v[i][1].x; a[i][5] += v[i][1].y; a[i][6] += v[i][1].z; a[i][7] += v[i][1].w;
-              }
+              for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  a[i][0] += v[h][i][0].x; a[i][1] += v[h][i][0].y; a[i][2] += v[h][i][0].z; a[i][3] += v[h][i][0].w;
+                  a[i][4] += v[h][i][1].x; a[i][5] += v[h][i][1].y; a[i][6] += v[h][i][1].z; a[i][7] += v[h][i][1].w;
+                }
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -224,65 +342,32 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
         }
       }
-      if (!FUSE_AR && final_here) {
-        // staging tile -> Y, 256 contiguous bytes per row
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int col = sg.tile * SBM + c16 * 8;
-        const bool vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
-        if (col + 8 <= N && vec_ok) {
-          for (int t = r0; t < M; t += 8)
-            *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8);
-        } else if (col < N) {
-          for (int t = r0; t < M; t += 8)
-            for (int j = 0; j < 8 && col + j < N; ++j) Y[(size_t)t * ldy + col + j] = sT[t * SBM + c16 * 8 + j];
+      if (final_here) emit_tile<FUSE_AR>(sT, Y, M, N, ldy, sg.tile, sg.tile, 0, 1, e, bars, ar, ar_epoch, status);
+      else asm volatile("bar.sync 1, 128;" ::: "memory");   // flag_a is reused by the next segment
+    }
+    if (clustered) {
+      // ---- cluster split-K reduction through distributed shared memory --------------------------
+      __syncwarp();
+      cluster_sync_all();                                      // (1) every CTA's partial is in its sP
+      if (ok) {
+        const int c4 = e & 31, rr = e >> 5;                    // 32 threads per FP32 row, four rows at a time
+        const uint32_t sp_base = smem_u32(sP);
+        for (int t = crank + cl_size * rr; t < M; t += 4 * cl_size) {
+          const uint32_t off = sp_base + (uint32_t)(t * SBM + c4 * 4) * 4u;
+          float4 v[8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s) if (s < cl_size) v[s] = ld_dsmem_f4(dsmem_addr(off, s));
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int s = 0; s < 8; ++s) if (s < cl_size) { a.x += v[s].x; a.y += v[s].y; a.z += v[s].z; a.w += v[s].w; }
+          uint2 o; o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
+          *reinterpret_cast<uint2*>(sT + t * SBM + c4 * 4) = o;
         }
       }
-      if (!FUSE_AR) asm volatile("bar.sync 1, 128;" ::: "memory");   // sT and flag_a are reused by the next segment
-      if (FUSE_AR && final_here) {
-        const int parity = ar_epoch & 1;
-        const int col = sg.tile * SBM + c16 * 8;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (col < N) {
-          for (int pi = 1; pi < ar.world; ++pi) {
-            const int p = (ar.rank + pi) % ar.world;
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, p, parity, ar.rank));
-            for (int t = r0; t < M; t += 8)
-              *reinterpret_cast<uint4*>(dst + (size_t)t * N + col) = *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8);
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (e == 0) {
-          __threadfence_system();
-          for (int pi = 1; pi < ar.world; ++pi)
-            st_release_sys(arena_flag(ar, (ar.rank + pi) % ar.world, ar.rank, sg.tile), ar_epoch);
-          bars.flag_b = 1;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (e < ar.world && e != ar.rank)
-          if (!wait_flag(arena_flag(ar, ar.rank, e, sg.tile), ar_epoch, status, KID_GEMM_AR, e)) bars.flag_b = 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (bars.flag_b && col < N) {
-          for (int t = r0; t < M; t += 8) {
-            float a8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) a8[j] = 0.f;
-            for (int r = 0; r < ar.world; ++r) {
-              const uint4 d = (r == ar.rank)
-                  ? *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8)
-                  : *reinterpret_cast<const uint4*>(
-                        reinterpret_cast<const __nv_bfloat16*>(arena_slot(ar, ar.rank, parity, r)) + (size_t)t * N + col);
-              const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[2 * j] += f.x; a8[2 * j + 1] += f.y; }
-            }
-            uint4 o;
-            o.x = pack_bf16x2(a8[0], a8[1]); o.y = pack_bf16x2(a8[2], a8[3]);
-            o.z = pack_bf16x2(a8[4], a8[5]); o.w = pack_bf16x2(a8[6], a8[7]);
-            *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = o;
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // sT and flag_b are reused
-      }
+      __syncwarp();
+      cluster_sync_all();                                      // (2) nobody reads this CTA's sP any more
+      if (ok) emit_tile<FUSE_AR>(sT, Y, M, N, ldy, sg.tile, sg.tile * cl_size + crank, crank, cl_size, e, bars, ar,
+                                 ar_epoch, status);
     }
     if (FUSE_AR && e == 0) {
       __threadfence();
@@ -293,6 +378,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         *reinterpret_cast<volatile int*>(arena_epoch(ar)) = ar_epoch;
       }
     }
+  }
+  if (clustered && warp < 2) {           // the producer and MMA warps take part in both cluster barriers
+    __syncwarp();
+    cluster_sync_all();
+    cluster_sync_all();
   }
 
   __syncthreads();
@@ -306,19 +396,70 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 }  // namespace ff
 using namespace ff;
 
-// Plan for a problem: returns the grid size (one persistent CTA per SM, fewer for tiny problems);
-// *scratch_bytes = FP32 partial slots (two per CTA), *counter_bytes = one int32 per column tile
-// (zero before the first launch; every launch leaves them zero).
+// Largest number of co-resident clusters of `s` CTAs of this kernel (0 when such a cluster cannot be
+// launched); queried once per cluster size.
+static int skinny_max_clusters(int s) {
+  static int cached[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+  if (s < 2 || s > 8) return 0;
+  if (cached[s] >= 0) return cached[s];
+  auto kern = gemm_skinny_kernel<false>;
+  if (opt_in_smem(kern, 201 * 1024)) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(s * 64); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = 201 * 1024;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = s; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  cached[s] = n;
+  return n;
+}
+
+// Cluster size for a problem (1 = persistent stream-K). Cluster split-K is used when every column
+// tile can have its own co-resident cluster: few tiles, so the K range is what has to be spread
+// over the SMs.
+static int skinny_cluster_size(int M, int N, int K) {
+  const int tiles_n = (N + SBM - 1) / SBM;
+  const int kblocks = (K + SBK - 1) / SBK;
+  if (M > 128 || tiles_n > 74) return 1;
+  int s = 148 / tiles_n;
+  if (s > 8) s = 8;
+  for (; s >= 2; --s)
+    if (kblocks / s >= 2 && skinny_max_clusters(s) >= tiles_n) return s;
+  return 1;
+}
+
+// Plan for a problem: returns the grid size (cluster split-K: tiles x cluster size; otherwise one
+// persistent CTA per SM, fewer for tiny problems);
+// *scratch_bytes = FP32 partial slots (two per CTA; none in cluster mode), *counter_bytes = one int32
+// per column tile (zero before the first launch; every launch leaves them zero).
 FF_EXPORT int ff_gemm_skinny_plan(int M, int N, int K, long long* scratch_bytes, long long* counter_bytes) {
   const int tiles_n = (N + SBM - 1) / SBM;
   const int kblocks = (K + SBK - 1) / SBK;
+  if (counter_bytes) *counter_bytes = (long long)tiles_n * 4;
+  const int cl = skinny_cluster_size(M, N, K);
+  if (cl > 1) {
+    if (scratch_bytes) *scratch_bytes = 0;
+    return tiles_n * cl;
+  }
   const long long total = (long long)tiles_n * kblocks;
   long long g = total / 2;                 // at least two k-blocks of work per CTA
   if (g > 148) g = 148;
   if (g < 1) g = 1;
   if (scratch_bytes) *scratch_bytes = g > 1 ? 2 * g * (long long)M * SBM * 4 : 0;
-  if (counter_bytes) *counter_bytes = (long long)tiles_n * 4;
   return (int)g;
+}
+
+template <bool FUSE_AR>
+static int skinny_launch_kernel(int grid, int cl, int smem, cudaStream_t stream, const CUtensorMap& tmW,
+                                const CUtensorMap& tmX, __nv_bfloat16* Y, int M, int N, int K, int ldy, int ntok,
+                                int stages, int staging, float* scratch, int* counters, int* status, const PeerArena& ar) {
+  auto kern = gemm_skinny_kernel<FUSE_AR>;
+  static bool attr_done = false;
+  if (!attr_done) { int r = opt_in_smem(kern, 201 * 1024); if (r) return r; attr_done = true; }
+  return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmW, tmX, Y, M, N, K, ldy, ntok, stages, staging, cl,
+                    scratch, counters, status, ar);
 }
 
 static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
@@ -326,9 +467,16 @@ static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int 
                               const PeerArena* arena) {
   if (M <= 0 || M > 256 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
   if ((K % 8) || (ldx % 8) || (ldw % 8)) return FF_HOST_BAD_ALIGN;
-  if (grid < 1 || grid > 1024 || (grid > 1 && (scratch == nullptr || counters == nullptr))) return FF_HOST_BAD_SHAPE;
-  const long long total = (long long)((N + SBM - 1) / SBM) * ((K + SBK - 1) / SBK);
-  if (grid > total) return FF_HOST_BAD_SHAPE;
+  const int tiles_n = (N + SBM - 1) / SBM;
+  const long long total = (long long)tiles_n * ((K + SBK - 1) / SBK);
+  const int cl = skinny_cluster_size(M, N, K);
+  if (cl > 1) {
+    if (grid != tiles_n * cl) return FF_HOST_BAD_SHAPE;
+    if (arena != nullptr && tiles_n * cl > MAX_FLAGS) return FF_HOST_TOO_LARGE;
+  } else {
+    if (grid < 1 || grid > 1024 || (grid > 1 && (scratch == nullptr || counters == nullptr))) return FF_HOST_BAD_SHAPE;
+    if (grid > total) return FF_HOST_BAD_SHAPE;
+  }
   const int ntok = (M + 15) / 16 * 16;
   CUtensorMap tmW, tmX;
   int r = make_tmap_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, SBK, SBM);
@@ -340,22 +488,15 @@ static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int 
   int stages = (200 * 1024 - staging) / stage_bytes;
   if (stages > SK_MAX_STAGES) stages = SK_MAX_STAGES;
   if (stages < 2) return FF_HOST_TOO_LARGE;
+  if (cl > 1 && (long long)M * SBM * 4 > (long long)stages * stage_bytes) return FF_HOST_TOO_LARGE;
   const int smem = staging + stages * stage_bytes + 1024;
   PeerArena none = {};
-  if (arena == nullptr) {
-    auto kern = gemm_skinny_kernel<false>;
-    static bool attr_done = false;
-    if (!attr_done) { r = opt_in_smem(kern, 201 * 1024); if (r) return r; attr_done = true; }
-    kern<<<grid, 192, smem, stream>>>(tmW, tmX, reinterpret_cast<__nv_bfloat16*>(Y), M, N, K, ldy, ntok, stages, staging,
-                                      scratch, counters, status, none);
-  } else {
-    auto kern = gemm_skinny_kernel<true>;
-    static bool attr_done = false;
-    if (!attr_done) { r = opt_in_smem(kern, 201 * 1024); if (r) return r; attr_done = true; }
-    kern<<<grid, 192, smem, stream>>>(tmW, tmX, reinterpret_cast<__nv_bfloat16*>(Y), M, N, K, ldy, ntok, stages, staging,
-                                      scratch, counters, status, *arena);
-  }
-  return launch_result();
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
+  if (arena == nullptr)
+    return skinny_launch_kernel<false>(grid, cl, smem, stream, tmW, tmX, y, M, N, K, ldy, ntok, stages, staging, scratch,
+                                       counters, status, none);
+  return skinny_launch_kernel<true>(grid, cl, smem, stream, tmW, tmX, y, M, N, K, ldy, ntok, stages, staging, scratch,
+                                    counters, status, *arena);
 }
 
 // `grid` is the value returned by ff_gemm_skinny_plan for the same problem.

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace ff {
 
@@ -87,6 +88,40 @@ inline int sm_count() {
 inline int launch_result() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? FF_HOST_OK : static_cast<int>(e);
+}
+
+// Programmatic dependent launch. A kernel started through launch_pdl may begin while the previous
+// kernel of the stream is still running (its prologue, and loads of data that no kernel writes,
+// overlap that kernel's tail); every such kernel executes griddepcontrol.wait before it touches
+// memory a predecessor produces, and griddepcontrol.launch_dependents early so that its own
+// successor may do the same. FLYINGFISH_PDL=0 turns the attribute off (plain stream order).
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("FLYINGFISH_PDL"); v = (e != nullptr && e[0] == '0') ? 0 : 1; }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute at[2];
+  unsigned n = 0;
+  if (pdl_enabled()) {
+    at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster > 1) {
+    at[n].id = cudaLaunchAttributeClusterDimension;
+    at[n].val.clusterDim.x = (unsigned)cluster; at[n].val.clusterDim.y = 1; at[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = at; cfg.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
+  return FF_HOST_OK;
 }
 
 template <typename K>

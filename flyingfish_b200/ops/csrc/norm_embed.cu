@@ -35,6 +35,8 @@ norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ res
             const __nv_bfloat16* __restrict__ table, const __nv_bfloat16* __restrict__ w,
             __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ capture, int capture_stride, int hidden,
             int vocab, float eps, int unit_offset, int ldx, int* status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;
@@ -96,6 +98,8 @@ norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ res
 
 // plain residual add: res = bf16(res + x)
 __global__ void residual_add_kernel(__nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ x, size_t nvec) {
+  pdl_trigger();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nvec) return;
   uint4 a = reinterpret_cast<const uint4*>(x)[i], r = reinterpret_cast<uint4*>(res)[i];
@@ -108,6 +112,8 @@ __global__ void residual_add_kernel(__nv_bfloat16* __restrict__ res, const __nv_
 // plain embedding gather (no norm): out[r] = table[ids[r]] * scale
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                              __nv_bfloat16* __restrict__ out, int hidden, int vocab, float scale, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   if (id < 0 || id >= vocab) { set_status(status, KID_EMBED, FF_ERR_BOUNDS, row, id); id = 0; }
@@ -136,8 +142,8 @@ FF_EXPORT int ff_rmsnorm(const void* x, const void* w, void* out, int rows, int 
   if (int r = check_hidden(hidden)) return r;
   if (rows <= 0) return FF_HOST_BAD_SHAPE;
   if (ldx % 8) return FF_HOST_BAD_ALIGN;
-  norm_kernel<0><<<rows, NORM_THREADS, 0, s>>>((const __nv_bfloat16*)x, nullptr, nullptr, nullptr,
-      (const __nv_bfloat16*)w, (__nv_bfloat16*)out, nullptr, 0, hidden, 0, eps, unit_offset, ldx, status);
+  if (int lr_ = launch_pdl(norm_kernel<0>, dim3(rows), dim3(NORM_THREADS), 0, s, 0, (const __nv_bfloat16*)x, nullptr, nullptr, nullptr,
+      (const __nv_bfloat16*)w, (__nv_bfloat16*)out, nullptr, 0, hidden, 0, eps, unit_offset, ldx, status)) return lr_;
   return launch_result();
 }
 
@@ -145,8 +151,8 @@ FF_EXPORT int ff_embed_rmsnorm(const int* ids, const void* table, const void* w,
                                int hidden, int vocab, float eps, int unit_offset, int* status, cudaStream_t s) {
   if (int r = check_hidden(hidden)) return r;
   if (rows <= 0) return FF_HOST_BAD_SHAPE;
-  norm_kernel<1><<<rows, NORM_THREADS, 0, s>>>(nullptr, (__nv_bfloat16*)res, ids, (const __nv_bfloat16*)table,
-      (const __nv_bfloat16*)w, (__nv_bfloat16*)out, nullptr, 0, hidden, vocab, eps, unit_offset, hidden, status);
+  if (int lr_ = launch_pdl(norm_kernel<1>, dim3(rows), dim3(NORM_THREADS), 0, s, 0, nullptr, (__nv_bfloat16*)res, ids, (const __nv_bfloat16*)table,
+      (const __nv_bfloat16*)w, (__nv_bfloat16*)out, nullptr, 0, hidden, vocab, eps, unit_offset, hidden, status)) return lr_;
   return launch_result();
 }
 
@@ -157,22 +163,22 @@ FF_EXPORT int ff_add_rmsnorm(const void* x, void* res, const void* w, void* out,
   if (int r = check_hidden(hidden)) return r;
   if (rows <= 0) return FF_HOST_BAD_SHAPE;
   if (ldx % 8 || capture_stride % 8) return FF_HOST_BAD_ALIGN;
-  norm_kernel<2><<<rows, NORM_THREADS, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)res, nullptr, nullptr,
+  if (int lr_ = launch_pdl(norm_kernel<2>, dim3(rows), dim3(NORM_THREADS), 0, s, 0, (const __nv_bfloat16*)x, (__nv_bfloat16*)res, nullptr, nullptr,
       (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (__nv_bfloat16*)capture, capture_stride, hidden, 0, eps,
-      unit_offset, ldx, status);
+      unit_offset, ldx, status)) return lr_;
   return launch_result();
 }
 
 FF_EXPORT int ff_residual_add(void* res, const void* x, long long n, cudaStream_t s) {
   if (n <= 0 || (n % 8)) return FF_HOST_BAD_SHAPE;
   const size_t nvec = (size_t)n / 8;
-  residual_add_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)res, (const __nv_bfloat16*)x, nvec);
+  if (int lr_ = launch_pdl(residual_add_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)res, (const __nv_bfloat16*)x, nvec)) return lr_;
   return launch_result();
 }
 
 FF_EXPORT int ff_embed(const int* ids, const void* table, void* out, int rows, int hidden, int vocab, float scale,
                        int* status, cudaStream_t s) {
   if (rows <= 0 || hidden <= 0 || (hidden % 8)) return FF_HOST_BAD_SHAPE;
-  embed_kernel<<<rows, 256, 0, s>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, hidden, vocab, scale, status);
+  if (int lr_ = launch_pdl(embed_kernel, dim3(rows), dim3(256), 0, s, 0, ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, hidden, vocab, scale, status)) return lr_;
   return launch_result();
 }

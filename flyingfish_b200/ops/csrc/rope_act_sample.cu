@@ -21,6 +21,8 @@ __global__ void rope_kv_paged_kernel(__nv_bfloat16* __restrict__ qkv, const int*
                                      __nv_bfloat16* __restrict__ vcache, const float* __restrict__ inv_freq_tab,
                                      int rows, int hq, int hkv, int dim, int rot_dim, int block_size, int num_blocks,
                                      float theta, int ldqkv, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int vec_per_head = dim >> 4;                 // pairs of uint4
   const int heads = hq + 2 * hkv;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -94,6 +96,8 @@ __device__ __forceinline__ float act_combine(float g, float u, int mode, float l
 // produced by a weight fused for the GEMM's SwiGLU epilogue; otherwise [gate | up] halves.
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows,
                                 int f, int ldgu, int ldo, int mode, float limit, int interleaved) {
+  pdl_trigger();
+  pdl_wait();
   const int vec_per_row = f >> 3;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)rows * vec_per_row) return;
@@ -115,6 +119,8 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 
 // logits softcap: x = cap * tanh(x / cap) (Gemma), in place
 __global__ void softcap_kernel(__nv_bfloat16* __restrict__ x, long long n, float cap) {
+  pdl_trigger();
+  pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) x[i] = __float2bfloat16(cap * tanhf(__bfloat162float(x[i]) / cap));
 }
@@ -130,6 +136,8 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out_ids, float* __restrict__ out_vals, int vocab,
                    int ld, int id_offset, const int* __restrict__ valid_rows, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   if (valid_rows && row >= *valid_rows) return;
   __shared__ float sv[32];
@@ -171,6 +179,8 @@ argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out_ids, floa
 // merge vocab-parallel candidates: vals/ids [ranks][rows] -> ids[rows]; ties -> lower id
 __global__ void argmax_merge_kernel(const float* __restrict__ vals, const int* __restrict__ ids, int* __restrict__ out,
                                     int ranks, int rows) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float best = -INFINITY; int bi = 0x7fffffff;
@@ -316,9 +326,9 @@ FF_EXPORT int ff_rope_kv_paged(void* qkv, const int* positions, const int* slots
                                int num_blocks, float theta, int ldqkv, int* status, cudaStream_t s) {
   if (rows <= 0 || dim % 16 || rot_dim > dim || rot_dim % 2 || ldqkv % 8) return FF_HOST_BAD_SHAPE;
   const long long total = (long long)rows * (hq + 2 * hkv) * (dim / 16);
-  rope_kv_paged_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)qkv, positions, slots,
+  if (int lr_ = launch_pdl(rope_kv_paged_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)qkv, positions, slots,
       (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, inv_freq, rows, hq, hkv, dim, rot_dim, block_size, num_blocks,
-      theta, ldqkv, status);
+      theta, ldqkv, status)) return lr_;
   return launch_result();
 }
 
@@ -327,14 +337,14 @@ FF_EXPORT int ff_silu_mul(const void* gu, void* out, int rows, int f, int ldgu, 
   if (rows <= 0 || f <= 0 || f % 8 || ldgu % 8 || ldo % 8) return FF_HOST_BAD_SHAPE;
   if (interleaved && f % 128) return FF_HOST_BAD_SHAPE;
   const long long total = (long long)rows * (f / 8);
-  silu_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows,
-                                                                   f, ldgu, ldo, mode, limit, interleaved);
+  if (int lr_ = launch_pdl(silu_mul_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows,
+                                                                   f, ldgu, ldo, mode, limit, interleaved)) return lr_;
   return launch_result();
 }
 
 FF_EXPORT int ff_softcap(void* x, long long n, float cap, cudaStream_t s) {
   if (n <= 0) return FF_HOST_BAD_SHAPE;
-  softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)x, n, cap);
+  if (int lr_ = launch_pdl(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)x, n, cap)) return lr_;
   return launch_result();
 }
 
@@ -342,18 +352,21 @@ FF_EXPORT int ff_softcap(void* x, long long n, float cap, cudaStream_t s) {
 FF_EXPORT int ff_argmax_rows(const void* logits, int* out_ids, float* out_vals, int rows, int vocab, int ld, int dtype,
                              int id_offset, const int* valid_rows, int* status, cudaStream_t s) {
   if (rows <= 0 || vocab <= 0) return FF_HOST_BAD_SHAPE;
-  if (dtype == 0)
-    argmax_rows_kernel<__nv_bfloat16><<<rows, 1024, 0, s>>>((const __nv_bfloat16*)logits, out_ids, out_vals, vocab, ld,
-                                                            id_offset, valid_rows, status);
-  else
-    argmax_rows_kernel<float><<<rows, 1024, 0, s>>>((const float*)logits, out_ids, out_vals, vocab, ld, id_offset,
-                                                    valid_rows, status);
+  int lr;
+  if (dtype == 0) {
+    lr = launch_pdl(argmax_rows_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), 0, s, 0, (const __nv_bfloat16*)logits, out_ids,
+                    out_vals, vocab, ld, id_offset, valid_rows, status);
+  } else {
+    lr = launch_pdl(argmax_rows_kernel<float>, dim3(rows), dim3(1024), 0, s, 0, (const float*)logits, out_ids, out_vals, vocab,
+                    ld, id_offset, valid_rows, status);
+  }
+  if (lr) return lr;
   return launch_result();
 }
 
 FF_EXPORT int ff_argmax_merge(const float* vals, const int* ids, int* out, int ranks, int rows, cudaStream_t s) {
   if (ranks <= 0 || rows <= 0) return FF_HOST_BAD_SHAPE;
-  argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, s>>>(vals, ids, out, ranks, rows);
+  if (int lr_ = launch_pdl(argmax_merge_kernel, dim3((rows + 127) / 128), dim3(128), 0, s, 0, vals, ids, out, ranks, rows)) return lr_;
   return launch_result();
 }
 

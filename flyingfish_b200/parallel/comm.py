@@ -145,7 +145,7 @@ class TPComm:
             sb, cb = c_longlong(0), c_longlong(0)
             grid = lib.ff_gemm_skinny_plan(m, n, k, ctypes.byref(sb), ctypes.byref(cb))
             ws = ops.workspace(x.device)
-            scratch = ws.ensure("gemm_scratch", sb.value // 4) if grid > 1 else None
+            scratch = ws.ensure("gemm_scratch", sb.value // 4) if sb.value > 0 else None
             out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
             rc = lib.ff_gemm_ar(*self.arena.args(), oplib.ptr(x), oplib.ptr(w), oplib.ptr(out), m, n, k, x.stride(0),
                                 w.stride(0), n, grid, oplib.ptr(scratch), oplib.ptr(ws.gemm_counters),
