@@ -61,19 +61,24 @@ def _up_to_date(lib: Path, stamp: str) -> bool:
     return lib.exists() and s.exists() and s.read_text().strip() == stamp
 
 
-def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile all ``csrc/*.cu`` into ``_ff_kernels.so`` (no-op when up to date)."""
-    lib = HERE / "_ff_kernels.so"
+def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False, timeline: bool = False) -> Path:
+    """Compile all ``csrc/*.cu`` into ``_ff_kernels.so`` (no-op when up to date).
+
+    ``timeline=True`` builds the tracing variant ``_ff_kernels_tl.so`` (``-DFF_TIMELINE``): kernels
+    record (time, SM, phase) stamps into the enlarged status buffer, see ``utils/timeline.py``."""
+    lib = HERE / ("_ff_kernels_tl.so" if timeline else "_ff_kernels.so")
     srcs = kernel_sources()
     deps = srcs + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    stamp = _hash(deps, " ".join(NVCC_FLAGS))
+    base_flags = list(NVCC_FLAGS) + (["-DFF_TIMELINE"] if timeline else [])
+    stamp = _hash(deps, " ".join(base_flags))
     if not force and _up_to_date(lib, stamp):
         return lib
-    BUILD.mkdir(exist_ok=True)
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
+    build_dir = BUILD / "tl" if timeline else BUILD
+    build_dir.mkdir(parents=True, exist_ok=True)
+    flags = base_flags + (["-Xptxas", "-v"] if ptxas_info else [])
 
     def compile_one(src: Path) -> Path:
-        obj = BUILD / (src.stem + ".o")
+        obj = build_dir / (src.stem + ".o")
         ostamp = obj.with_suffix(".stamp")
         key = _hash([src] + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")), " ".join(flags))
         if not force and obj.exists() and ostamp.exists() and ostamp.read_text() == key:

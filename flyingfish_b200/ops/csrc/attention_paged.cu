@@ -182,7 +182,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
                    int* status) {
   pdl_trigger();
+  if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 0);
   pdl_wait();
+  if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 1);
   extern __shared__ __align__(1024) uint8_t smem[];
   // blockIdx.y = row tile * hkv + kv head: nq * G packed rows are processed 16 at a time
   const int split = blockIdx.x, kvh = blockIdx.y % hkv, rt = blockIdx.y / hkv, b = blockIdx.z;

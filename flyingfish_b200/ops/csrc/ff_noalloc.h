@@ -2,7 +2,7 @@
 // engine, whose host runtime always owns an allocator.
 //
 // ff_gemm_skinny_noalloc computes Y[M,N] = X[M,K] * W[N,K]^T (BF16 in, FP32 accumulate, BF16 out)
-// for decode-sized M (1..256) exactly like ff_gemm_skinny, but takes no scratch from the caller:
+// for decode-sized M (1..128) exactly like ff_gemm_skinny, but takes no scratch from the caller:
 // the split-K partial sums and tile counters live in a fixed array inside the library. It is
 // meant for callers that cannot allocate device memory when they need the product -- a host
 // whose allocator is frozen after start-up, a plugin with a fixed memory budget, or a C caller
@@ -11,9 +11,10 @@
 // Rules for the caller:
 //   * X, W, Y are device pointers owned by the caller; ldx/ldw/ldy are row pitches in elements
 //     (multiples of 8); `status` may be null or point to int32[4] in device memory.
-//   * The partial-sum slots (2 * grid * M * 128 * 4 bytes, grid = ff_gemm_skinny_plan(M, N, K) <= 148)
-//     must fit in FF_NOALLOC_SCRATCH_BYTES and ceil(N/128) in FF_NOALLOC_MAX_TILES; otherwise the
-//     call returns -5 and launches nothing.
+//   * The partial-sum slots (the scratch size ff_gemm_skinny_plan(M, N, K) reports: 2 * grid * M * 256 * 4
+//     bytes for problems it runs as stream-K, none for cluster split-K) must fit in
+//     FF_NOALLOC_SCRATCH_BYTES and the weight tiles in FF_NOALLOC_MAX_TILES; otherwise, and for
+//     M > 128, the call returns -5 and launches nothing.
 //   * The first call on each device looks up the array's device address; issue it before any
 //     stream capture begins on that device.
 //   * All calls share the array, so calls that can overlap on the GPU race; order them on one

@@ -1,20 +1,28 @@
-// Decode-shape BF16 linear (M <= 256 tokens):  Y[M,N] = X[M,K] · W[N,K]ᵀ, bound by the weight
+// Decode-shape BF16 linear (M <= 128 tokens):  Y[M,N] = X[M,K] · W[N,K]ᵀ, bound by the weight
 // stream from HBM, so the job of the kernel is to keep every SM pulling weights at full rate.
 //
-//   * Swap-AB: a 128-row weight tile is the UMMA "A" operand, the tokens are the UMMA N dimension
-//     (padded to 16), so D[n (128 TMEM lanes), t (columns)] and small batches waste no tile rows.
-//   * Few column tiles (tiles x 2 <= SMs): cluster split-K, the partials meet in distributed shared
-//     memory (see the kernel). Otherwise:
-//   * Persistent stream-K: the (column tile, k-block) work units are split evenly over one CTA per
-//     SM, so no wave quantisation for any N. A CTA's share may start or end inside a tile; such
-//     partial tiles go to FP32 scratch and the CTA that completes a tile (atomic arrival count)
-//     adds the partials in ascending CTA order -> bitwise deterministic.
-//   * Same warp-specialised pipeline as the large-M kernel (TMA producer, one MMA-issuing
-//     thread, two TMEM accumulators, four epilogue warps).
-//   * FUSE_AR: the tile's final sums are not stored but pushed as BF16 into every
-//     tensor-parallel peer's arena slot (plain peer stores over NVLink), flagged, and the
-//     rank-ordered sum of all ranks' tiles is written: the row-parallel projection and its
-//     all-reduce are one kernel (no NCCL call, no second launch).
+//   * The tokens are the UMMA M dimension (128 TMEM lanes, only ceil16(M) rows are loaded, the rest of
+//     the accumulator is never read) and up to 256 weight rows are the UMMA N dimension. A
+//     tcgen05.mma costs about the same whatever its N, so the weight bytes one instruction consumes
+//     decide how fast an SM can stream: with the weights as the wide B operand (256 rows x 32 bytes per
+//     instruction) the tensor pipe is no longer the limit; with the weights as the 128-row A operand
+//     (swap-AB) it capped an SM near 40 GB/s, below its share of HBM.
+//   * Few weight tiles: cluster split-K. One cluster per tile of `tile_rows` weight rows, CTA s of
+//     the cluster multiplies its share of K and pushes the FP32 partial of token rows t = r (mod S)
+//     into slot s of CTA r's shared memory (distributed-shared-memory stores); after one cluster
+//     barrier every CTA sums its rows over the S slots in CTA order (bitwise deterministic) from its
+//     own shared memory: no global scratch, no serial fix-up, no remote loads. tile_rows (a multiple of 16, at most 256) is chosen so that tiles x S fills the SMs.
+//   * Many tiles: persistent stream-K. The (tile, k-block) units are split evenly over one CTA per SM;
+//     partial tiles go to FP32 scratch and the CTA that completes a tile (arrival counter) adds the
+//     partials in ascending CTA order -> bitwise deterministic.
+//   * Warp-specialised pipeline (TMA producer, one MMA-issuing thread, two TMEM accumulators, four
+//     epilogue warps). Launched with programmatic dependent launch: barriers, TMEM and the first
+//     weight tiles are set up while the preceding kernel still runs; activations are read after
+//     griddepcontrol.wait.
+//   * FUSE_AR: the final sums are not stored but written as BF16 into every tensor-parallel rank's
+//     arena slot (plain peer stores over NVLink, own slot included), flagged, and the rank-ordered
+//     sum of all ranks' values is written: the row-parallel projection and its all-reduce are one
+//     kernel (no NCCL call, no second launch).
 // Replaces the reference's skinny GEMM (kernels/gemm_skinny.cu: rows <= 16, 4 warps split K,
 // mma.sync) and its cuBLAS calls for small row counts (src/backend/cuda/blas.rs:852-1080).
 #include "ptx.cuh"
@@ -23,9 +31,11 @@
 
 namespace ff {
 
-constexpr int SBM = 128;          // weight rows per tile (UMMA M)
+constexpr int STOK = 128;         // token lanes of the accumulator (UMMA M)
+constexpr int SBN = 256;          // most weight rows per tile (UMMA N)
 constexpr int SBK = 64;           // k-block: 64 bf16 = one 128-byte swizzle row
 constexpr int SK_MAX_STAGES = 8;
+constexpr int SP_PAD = 4;         // FP32 partial rows in shared memory are padded by 4 floats
 
 struct alignas(8) SkinnyBars {
   uint64_t full[SK_MAX_STAGES];
@@ -56,95 +66,99 @@ __device__ __forceinline__ bool next_segment(long long& u, long long u1, int kbl
   return true;
 }
 
-// Final output of one tile (or of this CTA's rows of it): the BF16 values sit in the staging tile
-// sT[t][128]; rows handled are t = row0 + 8*row_step*i + row_step*(e/16). Either stores them to Y
-// or (FUSE_AR) pushes them to every peer, waits for the peers' rows and writes the rank-ordered sum.
-// Called by all 128 epilogue threads.
+// Where the final values of a tile go: Y, or (FUSE_AR) the arena slot of this rank on every rank.
 template <bool FUSE_AR>
-__device__ __forceinline__ void emit_tile(const __nv_bfloat16* sT, __nv_bfloat16* __restrict__ Y, int M, int N, int ldy,
-                                          int tile, int flag_idx, int row0, int row_step, int e, SkinnyBars& bars,
-                                          const PeerArena& ar, int ar_epoch, int* status) {
-  const int c16 = e & 15, r0 = e >> 4;          // 16 threads per 256-byte tile row
-  const int col = tile * SBM + c16 * 8;
-  const int t_first = row0 + row_step * r0, t_inc = 8 * row_step;
-  asm volatile("bar.sync 1, 128;" ::: "memory");
-  if (!FUSE_AR) {
-    const bool vec_ok = (ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0);
-    if (col + 8 <= N && vec_ok) {
-      for (int t = t_first; t < M; t += t_inc)
-        *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8);
-    } else if (col < N) {
-      for (int t = t_first; t < M; t += t_inc)
-        for (int j = 0; j < 8 && col + j < N; ++j) Y[(size_t)t * ldy + col + j] = sT[t * SBM + c16 * 8 + j];
-    }
-  } else {
-    const int parity = ar_epoch & 1;
-    if (col < N) {
-      for (int pi = 1; pi < ar.world; ++pi) {
+struct TileSink {
+  __nv_bfloat16* Y; int N, ldy; bool vec8;      // vec8: 16-byte stores of eight values are aligned
+  PeerArena ar; int parity;
+
+  // eight consecutive columns col..col+7 of token row t (col is a multiple of 8)
+  __device__ __forceinline__ void put8(int t, int col, const float* a) const {
+    if (col >= N) return;
+    uint4 o;
+    o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]);
+    o.z = pack_bf16x2(a[4], a[5]); o.w = pack_bf16x2(a[6], a[7]);
+    if (!FUSE_AR) {
+      __nv_bfloat16* dst = Y + (size_t)t * ldy + col;
+      if (vec8 && col + 8 <= N) { *reinterpret_cast<uint4*>(dst) = o; return; }
+      const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(&o);
+      for (int j = 0; j < 8 && col + j < N; ++j) dst[j] = ob[j];
+    } else {
+      // N % 8 == 0 and 16-byte aligned slots are checked by the host
+      for (int pi = 0; pi < ar.world; ++pi) {
         const int p = (ar.rank + pi) % ar.world;
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, p, parity, ar.rank));
-        for (int t = t_first; t < M; t += t_inc)
-          *reinterpret_cast<uint4*>(dst + (size_t)t * N + col) = *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8);
-      }
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (e == 0) {
-      __threadfence_system();
-      for (int pi = 1; pi < ar.world; ++pi)
-        st_release_sys(arena_flag(ar, (ar.rank + pi) % ar.world, ar.rank, flag_idx), ar_epoch);
-      bars.flag_b = 1;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (e < ar.world && e != ar.rank)
-      if (!wait_flag(arena_flag(ar, ar.rank, e, flag_idx), ar_epoch, status, KID_GEMM_AR, e)) bars.flag_b = 0;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (bars.flag_b && col < N) {
-      for (int t = t_first; t < M; t += t_inc) {
-        float a8[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) a8[j] = 0.f;
-        for (int r = 0; r < ar.world; ++r) {
-          const uint4 d = (r == ar.rank)
-              ? *reinterpret_cast<const uint4*>(sT + t * SBM + c16 * 8)
-              : *reinterpret_cast<const uint4*>(
-                    reinterpret_cast<const __nv_bfloat16*>(arena_slot(ar, ar.rank, parity, r)) + (size_t)t * N + col);
-          const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[2 * j] += f.x; a8[2 * j + 1] += f.y; }
-        }
-        uint4 o;
-        o.x = pack_bf16x2(a8[0], a8[1]); o.y = pack_bf16x2(a8[2], a8[3]);
-        o.z = pack_bf16x2(a8[4], a8[5]); o.w = pack_bf16x2(a8[6], a8[7]);
-        *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = o;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, p, parity, ar.rank)) + (size_t)t * N + col;
+        *reinterpret_cast<uint4*>(dst) = o;
       }
     }
   }
-  asm volatile("bar.sync 1, 128;" ::: "memory");   // sT, flag_a and flag_b are reused by the next segment
+};
+
+// FUSE_AR: after this CTA's values of (tile, rows row0 + i*row_step) are in every rank's slot, flag the
+// peers, wait for theirs, and write the rank-ordered sum. Called by all 128 epilogue threads.
+__device__ __forceinline__ void allreduce_tile(const TileSink<true>& sink, int M, int tile, int tile_rows, int flag_idx,
+                                               int row0, int row_step, int e, SkinnyBars& bars, int ar_epoch, int* status) {
+  const PeerArena& ar = sink.ar;
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (e == 0) {
+    __threadfence_system();
+    for (int pi = 1; pi < ar.world; ++pi)
+      st_release_sys(arena_flag(ar, (ar.rank + pi) % ar.world, ar.rank, flag_idx), ar_epoch);
+    bars.flag_b = 1;
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (e < ar.world && e != ar.rank)
+    if (!wait_flag(arena_flag(ar, ar.rank, e, flag_idx), ar_epoch, status, KID_GEMM_AR, e)) bars.flag_b = 0;
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (bars.flag_b) {
+    const int vec_per_row = tile_rows / 8;                       // 16-byte vectors of eight values
+    const int rows = (M - row0 + row_step - 1) / row_step;
+    for (int i = e; i < rows * vec_per_row; i += 128) {
+      const int t = row0 + (i / vec_per_row) * row_step;
+      const int col = tile * tile_rows + (i % vec_per_row) * 8;
+      if (col >= sink.N) continue;
+      float a8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a8[j] = 0.f;
+      for (int r = 0; r < ar.world; ++r) {
+        const uint4 d = *reinterpret_cast<const uint4*>(
+            reinterpret_cast<const __nv_bfloat16*>(arena_slot(ar, ar.rank, sink.parity, r)) + (size_t)t * sink.N + col);
+        const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[2 * j] += f.x; a8[2 * j + 1] += f.y; }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(a8[0], a8[1]); o.y = pack_bf16x2(a8[2], a8[3]);
+      o.z = pack_bf16x2(a8[4], a8[5]); o.w = pack_bf16x2(a8[6], a8[7]);
+      *reinterpret_cast<uint4*>(sink.Y + (size_t)t * sink.ldy + col) = o;
+    }
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");   // flag_b is reused by the next tile
 }
 
-// cl_size == 1: persistent stream-K over gridDim.x CTAs.
-// cl_size  > 1: cluster split-K. Cluster c owns column tile c; its CTA r multiplies k-blocks
-//   [kblocks*r/S, kblocks*(r+1)/S), leaves the FP32 partial in its own shared memory, and after a
-//   cluster barrier CTA r sums token rows t = r (mod S) over the S partials through distributed shared
-//   memory in CTA order (bitwise deterministic) -- no trip through global scratch, no serial fix-up.
+// cl_size == 1: persistent stream-K over gridDim.x CTAs.  cl_size > 1: cluster split-K, cluster c
+// owns weight tile c, CTA r of it the k-blocks [kblocks*r/S, kblocks*(r+1)/S).
 template <bool FUSE_AR>
 __global__ void __launch_bounds__(192, 1)
-gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                   __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldy, int ntok, int stages, int stage_smem_off,
-                   int cl_size, float* __restrict__ scratch, int* __restrict__ counters, int* status, PeerArena ar) {
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                   __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldy, int ntok, int tile_rows, int stages,
+                   int cl_size, int pipe_off, float* __restrict__ scratch, int* __restrict__ counters, int* status,
+                   PeerArena ar) {
   pdl_trigger();
+  if (cl_size > 1) cluster_arrive_relaxed();         // phase A: "this CTA runs" (waited on before the first remote store)
+  if (threadIdx.x == 0) FF_TL(status, KID_GEMM_SKINNY, 0);
   extern __shared__ uint8_t smem_raw[];
   __shared__ SkinnyBars bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __nv_bfloat16* sT = reinterpret_cast<__nv_bfloat16*>(smem);       // BF16 staging tile [t][128]
-  uint8_t* pipe = smem + stage_smem_off;
-  float* sP = reinterpret_cast<float*>(pipe);                       // cluster mode: FP32 partial [t][128], after the main loop
-  constexpr int A_BYTES = SBM * SBK * 2;
-  const int b_bytes = ntok * SBK * 2;
-  const int stage_bytes = A_BYTES + b_bytes;
-  uint32_t tmem_cols = 32; while ((int)tmem_cols < 2 * ntok) tmem_cols <<= 1;
+  // cluster mode: receive buffer [source CTA][owned row][tile_rows + SP_PAD] FP32 for the partials of this CTA's rows
+  float* recv = reinterpret_cast<float*>(smem);
+  uint8_t* pipe = smem + pipe_off;
+  constexpr int A_BYTES = STOK * SBK * 2;            // activation tile region (ntok rows of it are loaded)
+  const int stage_bytes = A_BYTES + tile_rows * SBK * 2;
+  const int tx_bytes = (ntok + tile_rows) * SBK * 2;
+  uint32_t tmem_cols = 32; while ((int)tmem_cols < 2 * tile_rows) tmem_cols <<= 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_n = (N + SBM - 1) / SBM;
+  const int tiles_n = (N + tile_rows - 1) / tile_rows;
   const int kblocks = (K + SBK - 1) / SBK;
   const long long total = (long long)tiles_n * kblocks;
   const int G = gridDim.x;
@@ -158,35 +172,39 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     u0 = total * blockIdx.x / G; u1 = total * (blockIdx.x + 1) / G;
   }
 
+  // Thread 0 is the TMA producer. It initialises the barriers and at once requests the first `stages`
+  // weight tiles (weights are written by no kernel, so this needs no wait on the preceding kernel),
+  // while warp 1 allocates TMEM; the other roles meet it at the block barrier.
+  const uint32_t pre = (uint32_t)min((long long)stages, u1 - u0);
+  uint64_t pol_w = 0;
   if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX);
     for (int i = 0; i < stages; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&bars.tmem_full[i], 1); mbar_init(&bars.tmem_empty[i], 4); }
     bars.abort_flag = 0; bars.flag_a = 0; bars.flag_b = 0;
     mbar_fence_init();
+    pol_w = l2_policy_evict_first();
+    uint32_t it = 0; long long u = u0; Segment sg;
+    while (it < pre && next_segment(u, u1, kblocks, sg))
+      for (int kb = sg.kb0; kb < sg.kb1 && it < pre; ++kb, ++it) {
+        mbar_expect_tx(&bars.full[it], tx_bytes);
+        tma_load_2d_hint(pipe + it * stage_bytes + A_BYTES, &tmW, &bars.full[it], kb * SBK, sg.tile * tile_rows, pol_w);
+      }
+    FF_TL(status, KID_GEMM_SKINNY, 2);
   }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX); }
   if (warp == 1) { tmem_alloc(&bars.tmem_base, tmem_cols); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars.tmem_base;
   volatile int* abort_flag = &bars.abort_flag;
+  if (threadIdx.x == 0) FF_TL(status, KID_GEMM_SKINNY, 1);
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
-      // Weights are written by no kernel, so the first `stages` weight tiles are requested before
-      // the wait on the preceding kernel; the activations follow once that kernel is complete.
-      const uint32_t pre = (uint32_t)min((long long)stages, u1 - u0);
-      {
-        uint32_t it = 0; long long u = u0; Segment sg;
-        while (it < pre && next_segment(u, u1, kblocks, sg))
-          for (int kb = sg.kb0; kb < sg.kb1 && it < pre; ++kb, ++it) {
-            mbar_expect_tx(&bars.full[it], stage_bytes);
-            tma_load_2d_hint(pipe + it * stage_bytes, &tmW, &bars.full[it], kb * SBK, sg.tile * SBM, pol_w);
-          }
-      }
+      const uint64_t pol_x = l2_policy_evict_last();
       pdl_wait();
+      FF_TL(status, KID_GEMM_SKINNY, 3);
       uint32_t it = 0; bool ok = true;
       long long u = u0; Segment sg;
       while (ok && next_segment(u, u1, kblocks, sg)) {
@@ -195,27 +213,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           uint8_t* sa = pipe + s * stage_bytes;
           if (it >= pre) {
             if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag, status, KID_GEMM_SKINNY, 1)) { ok = false; break; }
-            mbar_expect_tx(&bars.full[s], stage_bytes);
-            tma_load_2d_hint(sa, &tmW, &bars.full[s], kb * SBK, sg.tile * SBM, pol_w);
+            mbar_expect_tx(&bars.full[s], tx_bytes);
+            tma_load_2d_hint(sa + A_BYTES, &tmW, &bars.full[s], kb * SBK, sg.tile * tile_rows, pol_w);
           }
-          tma_load_2d_hint(sa + A_BYTES, &tmX, &bars.full[s], kb * SBK, 0, pol_x);
+          tma_load_2d_hint(sa, &tmX, &bars.full[s], kb * SBK, 0, pol_x);
         }
       }
+      FF_TL(status, KID_GEMM_SKINNY, 4);
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(1, 1, 0, 0, SBM, ntok);
+      const uint32_t idesc = umma_idesc(1, 1, 0, 0, STOK, tile_rows);
       uint32_t it = 0, seg_it = 0; bool ok = true;
       long long u = u0; Segment sg;
       while (ok && next_segment(u, u1, kblocks, sg)) {
         const int acc = seg_it & 1; const uint32_t aph = (seg_it >> 1) & 1;
         if (!mbar_wait(&bars.tmem_empty[acc], aph ^ 1, abort_flag, status, KID_GEMM_SKINNY, 2)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * ntok;
+        const uint32_t d_tmem = tmem_base + acc * tile_rows;
         for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
           const int s = it % stages; const uint32_t ph = (it / stages) & 1;
           if (!mbar_wait(&bars.full[s], ph, abort_flag, status, KID_GEMM_SKINNY, 3)) { ok = false; break; }
           tc_fence_after();
+          if (it == 0) FF_TL(status, KID_GEMM_SKINNY, 5);
           const uint32_t sa = smem_u32(pipe + s * stage_bytes);
           const uint64_t da = umma_desc_sw128(sa, 16, 1024);
           const uint64_t db = umma_desc_sw128(sa + A_BYTES, 16, 1024);
@@ -226,149 +246,197 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (ok) umma_commit(&bars.tmem_full[acc]);
         ++seg_it;
       }
+      FF_TL(status, KID_GEMM_SKINNY, 6);
     }
   } else {
-    // ---- epilogue warps 2..5 ; TMEM lane quarter = warp % 4 -----------------------------------
+    // ---- epilogue warps 2..5 ; TMEM lane quarter = warp % 4 ; lane = token ----------------------
     const int q = warp & 3;
-    const int nl = q * 32 + lane;                 // row inside the weight tile
+    const int t_own = q * 32 + lane;              // token row held by this thread's TMEM lane
+    const bool row_live = q * 32 < M;             // warp-uniform: this quarter holds real tokens
     const int e = (warp - 2) * 32 + lane;         // 0..127, cooperative index
+    const int vpr = tile_rows / 8;                // 8-value vectors per tile row
     pdl_wait();                                   // scratch, counters, the arena and Y belong to earlier kernels until here
+    if (e == 0) FF_TL(status, KID_GEMM_SKINNY, 7);
     int ar_epoch = 0;
     if (FUSE_AR) ar_epoch = ld_volatile(arena_epoch(ar)) + 1;
+    TileSink<FUSE_AR> sink;
+    sink.Y = Y; sink.N = N; sink.ldy = ldy; sink.ar = ar; sink.parity = ar_epoch & 1;
+    sink.vec8 = FUSE_AR || ((ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(Y) & 15) == 0));
     uint32_t seg_it = 0; bool ok = true;
     long long u = u0; Segment sg;
+    sg.tile = 0; sg.kb0 = 0; sg.kb1 = 0;
     while (ok && next_segment(u, u1, kblocks, sg)) {
       const int acc = seg_it & 1; const uint32_t aph = (seg_it >> 1) & 1;
       ++seg_it;
       if (!mbar_wait(&bars.tmem_full[acc], aph, abort_flag, status, KID_GEMM_SKINNY, 4)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * ntok;
+      if (e == 0) FF_TL(status, KID_GEMM_SKINNY, 8);
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * tile_rows;
+      const int col0 = sg.tile * tile_rows;
       if (clustered) {
-        // the pipeline is drained (single segment): its shared memory now holds the FP32 partial
-        for (int c = 0; c < ntok; c += 16) {
-          uint32_t r[16];
-          tmem_ld_x16(taddr + c, r);
-          tmem_ld_wait();
+        // push this CTA's partial of token row t into slot `crank` of the row's owner, CTA t % S
+        cluster_wait();                                          // phase A: every CTA of the cluster runs
+        if (row_live) {
+          const int rows_per = (M + cl_size - 1) / cl_size;
+          const int owner = t_own % cl_size, ti = t_own / cl_size;
+          const uint32_t dst = dsmem_addr(
+              smem_u32(recv) + (uint32_t)((crank * rows_per + ti) * (tile_rows + SP_PAD)) * 4u, owner);
+          for (int c = 0; c < tile_rows; c += 16) {
+            uint32_t r[16];
+            tmem_ld_x16(taddr + c, r);
+            tmem_ld_wait();
+            if (t_own < M) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) if (c + j < M) sP[(c + j) * SBM + nl] = __uint_as_float(r[j]);
+              for (int j = 0; j < 4; ++j)
+                st_dsmem_f4(dst + (uint32_t)(c + 4 * j) * 4u,
+                            make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                        __uint_as_float(r[4 * j + 3])));
+            }
+          }
         }
         tc_fence_before();
         break;
       }
       const bool whole = sg.kb0 == 0 && sg.kb1 == kblocks;
-      bool final_here = whole;
-      const int c16 = e & 15, r0 = e >> 4;          // cooperative layout: 16 threads per 256-byte tile row
       if (whole) {
-        // TMEM -> BF16 staging tile sT[t][128]
-        for (int c = 0; c < ntok; c += 16) {
-          uint32_t r[16];
-          tmem_ld_x16(taddr + c, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) if (c + j < M) sT[(c + j) * SBM + nl] = __float2bfloat16(__uint_as_float(r[j]));
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars.tmem_empty[acc]);
-      } else {
-        // partial tile: FP32 slot 2*cta + (1 if this segment starts the tile), layout [t][128]
-        float* part = scratch + ((size_t)(2 * blockIdx.x + (sg.kb0 == 0 ? 1 : 0)) * M) * SBM;
-        for (int c = 0; c < ntok; c += 16) {
-          uint32_t r[16];
-          tmem_ld_x16(taddr + c, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) if (c + j < M) part[(size_t)(c + j) * SBM + nl] = __uint_as_float(r[j]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars.tmem_empty[acc]);
-        const int c_first = unit_owner((long long)sg.tile * kblocks, total, G);
-        const int c_last = unit_owner((long long)(sg.tile + 1) * kblocks - 1, total, G);
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (e == 0) {
-          const int prev = atomicAdd(&counters[sg.tile], 1);
-          const int last = (prev == c_last - c_first);
-          if (last) counters[sg.tile] = 0;
-          bars.flag_a = last;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        final_here = bars.flag_a != 0;
-        if (final_here) {
-          __threadfence();
-          // vectorised fix-up: each thread owns 8 columns of rows r0, r0+8, ...; four rows of two
-          // partials at a time keep sixteen independent 16-byte loads in flight; the adds stay in
-          // ascending CTA order
-          for (int t0 = r0; t0 < M; t0 += 32) {
-            float a[4][8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) a[i][j] = 0.f;
-            for (int c = c_first; c <= c_last; c += 2) {
-              float4 v[2][4][2];
+        // TMEM -> registers -> output
+        if (row_live) {
+          for (int c = 0; c < tile_rows; c += 16) {
+            uint32_t r[16];
+            tmem_ld_x16(taddr + c, r);
+            tmem_ld_wait();
+            if (t_own < M) {
+              float a8[8];
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
-                const int cc = c + h;
-                const float* src = scratch + ((size_t)(2 * cc + (cc == c_first ? 1 : 0)) * M) * SBM + c16 * 8;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int t = t0 + 8 * i;
-                  if (t < M && cc <= c_last) {
-                    v[h][i][0] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM));
-                    v[h][i][1] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)t * SBM + 4));
-                  } else { v[h][i][0] = make_float4(0, 0, 0, 0); v[h][i][1] = v[h][i][0]; }
-                }
-              }
-#pragma unroll
-              for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  a[i][0] += v[h][i][0].x; a[i][1] += v[h][i][0].y; a[i][2] += v[h][i][0].z; a[i][3] += v[h][i][0].w;
-                  a[i][4] += v[h][i][1].x; a[i][5] += v[h][i][1].y; a[i][6] += v[h][i][1].z; a[i][7] += v[h][i][1].w;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int t = t0 + 8 * i;
-              if (t < M) {
-                uint4 o;
-                o.x = pack_bf16x2(a[i][0], a[i][1]); o.y = pack_bf16x2(a[i][2], a[i][3]);
-                o.z = pack_bf16x2(a[i][4], a[i][5]); o.w = pack_bf16x2(a[i][6], a[i][7]);
-                *reinterpret_cast<uint4*>(sT + t * SBM + c16 * 8) = o;
+                for (int j = 0; j < 8; ++j) a8[j] = __uint_as_float(r[8 * h + j]);
+                sink.put8(t_own, col0 + c + 8 * h, a8);
               }
             }
           }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.tmem_empty[acc]);
+        if constexpr (FUSE_AR) allreduce_tile(sink, M, sg.tile, tile_rows, sg.tile, 0, 1, e, bars, ar_epoch, status);
+        continue;
       }
-      if (final_here) emit_tile<FUSE_AR>(sT, Y, M, N, ldy, sg.tile, sg.tile, 0, 1, e, bars, ar, ar_epoch, status);
-      else asm volatile("bar.sync 1, 128;" ::: "memory");   // flag_a is reused by the next segment
-    }
-    if (clustered) {
-      // ---- cluster split-K reduction through distributed shared memory --------------------------
-      __syncwarp();
-      cluster_sync_all();                                      // (1) every CTA's partial is in its sP
-      if (ok) {
-        const int c4 = e & 31, rr = e >> 5;                    // 32 threads per FP32 row, four rows at a time
-        const uint32_t sp_base = smem_u32(sP);
-        for (int t = crank + cl_size * rr; t < M; t += 4 * cl_size) {
-          const uint32_t off = sp_base + (uint32_t)(t * SBM + c4 * 4) * 4u;
-          float4 v[8];
+      // partial tile: FP32 slot 2*cta + (1 if this segment starts the tile), layout [t][tile_rows]
+      const size_t slot_elems = (size_t)M * tile_rows;
+      float* part = scratch + (size_t)(2 * blockIdx.x + (sg.kb0 == 0 ? 1 : 0)) * slot_elems;
+      if (row_live) {
+        for (int c = 0; c < tile_rows; c += 16) {
+          uint32_t r[16];
+          tmem_ld_x16(taddr + c, r);
+          tmem_ld_wait();
+          if (t_own < M) {
+            float4* dst = reinterpret_cast<float4*>(part + (size_t)t_own * tile_rows + c);
 #pragma unroll
-          for (int s = 0; s < 8; ++s) if (s < cl_size) v[s] = ld_dsmem_f4(dsmem_addr(off, s));
-          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int s = 0; s < 8; ++s) if (s < cl_size) { a.x += v[s].x; a.y += v[s].y; a.z += v[s].z; a.w += v[s].w; }
-          uint2 o; o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
-          *reinterpret_cast<uint2*>(sT + t * SBM + c4 * 4) = o;
+            for (int j = 0; j < 4; ++j)
+              dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                   __uint_as_float(r[4 * j + 3]));
+          }
         }
       }
+      tc_fence_before();
       __syncwarp();
-      cluster_sync_all();                                      // (2) nobody reads this CTA's sP any more
-      if (ok) emit_tile<FUSE_AR>(sT, Y, M, N, ldy, sg.tile, sg.tile * cl_size + crank, crank, cl_size, e, bars, ar,
-                                 ar_epoch, status);
+      if (lane == 0) mbar_arrive(&bars.tmem_empty[acc]);
+      const int c_first = unit_owner((long long)sg.tile * kblocks, total, G);
+      const int c_last = unit_owner((long long)(sg.tile + 1) * kblocks - 1, total, G);
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (e == 0) {
+        const int prev = atomicAdd(&counters[sg.tile], 1);
+        const int last = (prev == c_last - c_first);
+        if (last) counters[sg.tile] = 0;
+        bars.flag_a = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const bool final_here = bars.flag_a != 0;
+      if (final_here) {
+        __threadfence();
+        // fix-up: 8-value vectors of the tile are dealt round-robin to the 128 threads; four vectors of two
+        // partials (sixteen independent 16-byte loads) are in flight at a time; the adds stay in ascending
+        // CTA order
+        const int nvec = M * vpr;
+        for (int i0 = e; i0 < nvec; i0 += 512) {
+          float a8[4][8];
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a8[g][j] = 0.f;
+          for (int c = c_first; c <= c_last; c += 2) {
+            float4 v[4][2][2];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int i = i0 + 128 * g;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int cc = c + h;
+                if (i < nvec && cc <= c_last) {
+                  const float* src = scratch + (size_t)(2 * cc + (cc == c_first ? 1 : 0)) * slot_elems + (size_t)i * 8;
+                  v[g][h][0] = __ldcg(reinterpret_cast<const float4*>(src));
+                  v[g][h][1] = __ldcg(reinterpret_cast<const float4*>(src + 4));
+                } else { v[g][h][0] = make_float4(0, 0, 0, 0); v[g][h][1] = v[g][h][0]; }
+              }
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                a8[g][0] += v[g][h][0].x; a8[g][1] += v[g][h][0].y; a8[g][2] += v[g][h][0].z; a8[g][3] += v[g][h][0].w;
+                a8[g][4] += v[g][h][1].x; a8[g][5] += v[g][h][1].y; a8[g][6] += v[g][h][1].z; a8[g][7] += v[g][h][1].w;
+              }
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int i = i0 + 128 * g;
+            if (i < nvec) { const int t = i / vpr, c8 = i - t * vpr; sink.put8(t, col0 + c8 * 8, a8[g]); }
+          }
+        }
+        if constexpr (FUSE_AR) allreduce_tile(sink, M, sg.tile, tile_rows, sg.tile, 0, 1, e, bars, ar_epoch, status);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // flag_a is reused by the next segment
     }
+    if (clustered) {
+      // ---- cluster split-K reduction: every partial of this CTA's rows is in its receive buffer after
+      // the barrier; nothing touches another CTA's shared memory afterwards, so CTAs leave independently
+      if (!ok) cluster_wait();                                 // phase A was not consumed on the error path
+      __syncwarp();
+      cluster_sync_all();                                      // phase B
+      if (e == 0) FF_TL(status, KID_GEMM_SKINNY, 9);
+      if (ok) {
+        const int rows_per = (M + cl_size - 1) / cl_size;
+        const int rows = (M - crank + cl_size - 1) / cl_size;  // token rows t = crank (mod cl_size)
+        const int col0 = sg.tile * tile_rows;
+        const int ldp = tile_rows + SP_PAD;
+        for (int i = e; i < rows * vpr; i += 128) {
+          const int ti = i / vpr, c8 = i - ti * vpr;
+          const float* src = recv + (size_t)ti * ldp + c8 * 8;
+          float4 v[8][2];
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s < cl_size) {
+              const float4* p4 = reinterpret_cast<const float4*>(src + (size_t)s * rows_per * ldp);
+              v[s][0] = p4[0]; v[s][1] = p4[1];
+            }
+          float a8[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a8[j] = 0.f;
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s < cl_size) {
+              a8[0] += v[s][0].x; a8[1] += v[s][0].y; a8[2] += v[s][0].z; a8[3] += v[s][0].w;
+              a8[4] += v[s][1].x; a8[5] += v[s][1].y; a8[6] += v[s][1].z; a8[7] += v[s][1].w;
+            }
+          sink.put8(crank + ti * cl_size, col0 + c8 * 8, a8);
+        }
+      }
+      if constexpr (FUSE_AR)
+        if (ok) allreduce_tile(sink, M, sg.tile, tile_rows, sg.tile * cl_size + crank, crank, cl_size, e, bars, ar_epoch, status);
+    }
+    if (e == 0) FF_TL(status, KID_GEMM_SKINNY, 10);
     if (FUSE_AR && e == 0) {
       __threadfence();
       const int prev = atomicAdd(arena_done(ar), 1);
@@ -379,13 +447,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   }
-  if (clustered && warp < 2) {           // the producer and MMA warps take part in both cluster barriers
+  if (clustered && warp < 2) {           // the producer and MMA warps take part in both cluster barrier phases
     __syncwarp();
-    cluster_sync_all();
+    cluster_wait();
     cluster_sync_all();
   }
 
   __syncthreads();
+  if (threadIdx.x == 0) FF_TL(status, KID_GEMM_SKINNY, 11);
   if (bars.abort_flag) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
@@ -396,6 +465,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 }  // namespace ff
 using namespace ff;
 
+constexpr int SK_SMEM_LIMIT = 200 * 1024;       // pipeline bytes a CTA may use (one CTA per SM)
+
 // Largest number of co-resident clusters of `s` CTAs of this kernel (0 when such a cluster cannot be
 // launched); queried once per cluster size.
 static int skinny_max_clusters(int s) {
@@ -403,9 +474,9 @@ static int skinny_max_clusters(int s) {
   if (s < 2 || s > 8) return 0;
   if (cached[s] >= 0) return cached[s];
   auto kern = gemm_skinny_kernel<false>;
-  if (opt_in_smem(kern, 201 * 1024)) return 0;
+  if (opt_in_smem(kern, SK_SMEM_LIMIT + 1024)) return 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(s * 64); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = 201 * 1024;
+  cfg.gridDim = dim3(s * 64); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = SK_SMEM_LIMIT + 1024;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = s; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
@@ -416,87 +487,130 @@ static int skinny_max_clusters(int s) {
   return n;
 }
 
-// Cluster size for a problem (1 = persistent stream-K). Cluster split-K is used when every column
-// tile can have its own co-resident cluster: few tiles, so the K range is what has to be spread
-// over the SMs.
-static int skinny_cluster_size(int M, int N, int K) {
-  const int tiles_n = (N + SBM - 1) / SBM;
-  const int kblocks = (K + SBK - 1) / SBK;
-  if (M > 128 || tiles_n > 74) return 1;
-  int s = 148 / tiles_n;
-  if (s > 8) s = 8;
-  for (; s >= 2; --s)
-    if (kblocks / s >= 2 && skinny_max_clusters(s) >= tiles_n) return s;
-  return 1;
+// Decomposition of a problem. cluster == 1: persistent stream-K over tiles of tile_rows weight rows.
+// cluster > 1: cluster split-K, one cluster per tile, `tiles` clusters.
+struct SkinnyConfig { int cluster, tile_rows, tiles, stages, pipe_off; };
+
+static int skinny_stages(int tile_rows, int reserved = 0) {
+  int st = (SK_SMEM_LIMIT - reserved) / (STOK * SBK * 2 + tile_rows * SBK * 2);
+  if (st > SK_MAX_STAGES) st = SK_MAX_STAGES;
+  if (const char* ev = getenv("FF_SKINNY_STAGES")) { const int v = atoi(ev); if (v >= 2 && v < st) st = v; }
+  return st;
 }
+
+static SkinnyConfig skinny_config(int M, int N, int K) {
+  const int kblocks = (K + SBK - 1) / SBK;
+  static int env_s = -1, env_r = -1;
+  if (env_s < 0) {
+    const char* a = getenv("FF_SKINNY_S"); const char* b = getenv("FF_SKINNY_R");
+    env_s = a ? atoi(a) : 0; env_r = b ? atoi(b) : 0;
+  }
+  // stream-K: widest tile that N fills
+  int rows1 = 128;                               // measured: 128-row tiles beat 256 (the fix-up moves half the bytes)
+  if (N < rows1) rows1 = (N + 15) / 16 * 16;
+  if (env_r > 0 && env_s == 1) rows1 = env_r;
+  SkinnyConfig best = {1, rows1, (N + rows1 - 1) / rows1, skinny_stages(rows1), 0};
+  if (env_s == 1) return best;
+  // Time model (microseconds). A CTA takes in at most ~60 GB/s (weights plus the activation tile it
+  // re-reads from L2 for every k-block), a pipeline of `st` stages cannot turn a k-block around faster
+  // than the ~1.5 us load latency / st, and all CTAs together cannot beat HBM (~5.9 TB/s on reads).
+  const int ntok = (M + 15) / 16 * 16;
+  auto model = [&](int rows, int kb_per_cta, int st, double ctas) {
+    const double per_kb = (rows + ntok) * 128.0 / 60e3;
+    const double lat_kb = 1.5 / st;
+    const double t_cta = kb_per_cta * (per_kb > lat_kb ? per_kb : lat_kb);
+    const double t_hbm = (double)N * K * 2.0 / 5.9e6;
+    (void)ctas;
+    return t_cta > t_hbm ? t_cta : t_hbm;
+  };
+  const long long units = (long long)best.tiles * kblocks;
+  const int g1 = (int)(units / 2 > 148 ? 148 : (units / 2 < 1 ? 1 : units / 2));
+  // stream-K pays a trip through global scratch for the partial tiles: about 4 us on top
+  double best_cost = model(rows1, (int)((units + g1 - 1) / g1), best.stages, g1) + (g1 > best.tiles ? 4.0 : 0.0);
+  for (int s = 2; s <= 8; ++s) {
+    if (env_s > 0 && s != env_s) continue;
+    if (kblocks / s < 2) continue;
+    // one cluster slot is left free: a launch that needs every slot can find one taken when it starts
+    // while the preceding kernel drains (programmatic dependent launch), and then runs in two waves
+    const int maxc = skinny_max_clusters(s) - (s > 2 ? 1 : 0);
+    if (maxc <= 0) continue;
+    for (int rows = 64; rows <= SBN; rows += 16) {
+      if (env_r > 0 && rows != env_r) continue;
+      const int tiles = (N + rows - 1) / rows;
+      if (tiles > maxc) continue;
+      // receive buffer: S slots x ceil(M/S) rows of (rows + pad) floats, in front of the pipeline
+      const int recv = (s * ((M + s - 1) / s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
+      const int st = skinny_stages(rows, recv);
+      if (st < 3) continue;
+      const double c = model(rows, (kblocks + s - 1) / s, st, (double)tiles * s);
+      if (c < best_cost - 1e-9 || (env_s > 0 && best.cluster == 1)) { best_cost = c; best = {s, rows, tiles, st, recv}; }
+    }
+  }
+  return best;
+}
+
+// Number of co-resident clusters of `s` CTAs of the decode GEMM on the current device (0: not launchable).
+FF_EXPORT int ff_gemm_skinny_max_clusters(int s) { return skinny_max_clusters(s); }
 
 // Plan for a problem: returns the grid size (cluster split-K: tiles x cluster size; otherwise one
 // persistent CTA per SM, fewer for tiny problems);
 // *scratch_bytes = FP32 partial slots (two per CTA; none in cluster mode), *counter_bytes = one int32
-// per column tile (zero before the first launch; every launch leaves them zero).
+// per weight tile (zero before the first launch; every launch leaves them zero).
 FF_EXPORT int ff_gemm_skinny_plan(int M, int N, int K, long long* scratch_bytes, long long* counter_bytes) {
-  const int tiles_n = (N + SBM - 1) / SBM;
   const int kblocks = (K + SBK - 1) / SBK;
-  if (counter_bytes) *counter_bytes = (long long)tiles_n * 4;
-  const int cl = skinny_cluster_size(M, N, K);
-  if (cl > 1) {
+  const SkinnyConfig cfg = skinny_config(M, N, K);
+  if (counter_bytes) *counter_bytes = (long long)cfg.tiles * 4;
+  if (cfg.cluster > 1) {
     if (scratch_bytes) *scratch_bytes = 0;
-    return tiles_n * cl;
+    return cfg.tiles * cfg.cluster;
   }
-  const long long total = (long long)tiles_n * kblocks;
+  const long long total = (long long)cfg.tiles * kblocks;
   long long g = total / 2;                 // at least two k-blocks of work per CTA
   if (g > 148) g = 148;
   if (g < 1) g = 1;
-  if (scratch_bytes) *scratch_bytes = g > 1 ? 2 * g * (long long)M * SBM * 4 : 0;
+  if (scratch_bytes) *scratch_bytes = g > 1 ? 2 * g * (long long)M * cfg.tile_rows * 4 : 0;
   return (int)g;
-}
-
-template <bool FUSE_AR>
-static int skinny_launch_kernel(int grid, int cl, int smem, cudaStream_t stream, const CUtensorMap& tmW,
-                                const CUtensorMap& tmX, __nv_bfloat16* Y, int M, int N, int K, int ldy, int ntok,
-                                int stages, int staging, float* scratch, int* counters, int* status, const PeerArena& ar) {
-  auto kern = gemm_skinny_kernel<FUSE_AR>;
-  static bool attr_done = false;
-  if (!attr_done) { int r = opt_in_smem(kern, 201 * 1024); if (r) return r; attr_done = true; }
-  return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmW, tmX, Y, M, N, K, ldy, ntok, stages, staging, cl,
-                    scratch, counters, status, ar);
 }
 
 static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
                               int grid, float* scratch, int* counters, int* status, cudaStream_t stream,
                               const PeerArena* arena) {
-  if (M <= 0 || M > 256 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
+  if (M <= 0 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
+  if (M > STOK) return FF_HOST_TOO_LARGE;
   if ((K % 8) || (ldx % 8) || (ldw % 8)) return FF_HOST_BAD_ALIGN;
-  const int tiles_n = (N + SBM - 1) / SBM;
-  const long long total = (long long)tiles_n * ((K + SBK - 1) / SBK);
-  const int cl = skinny_cluster_size(M, N, K);
+  const SkinnyConfig cfg = skinny_config(M, N, K);
+  const int cl = cfg.cluster;
+  const long long total = (long long)cfg.tiles * ((K + SBK - 1) / SBK);
   if (cl > 1) {
-    if (grid != tiles_n * cl) return FF_HOST_BAD_SHAPE;
-    if (arena != nullptr && tiles_n * cl > MAX_FLAGS) return FF_HOST_TOO_LARGE;
+    if (grid != cfg.tiles * cl) return FF_HOST_BAD_SHAPE;
+    if (arena != nullptr && cfg.tiles * cl > MAX_FLAGS) return FF_HOST_TOO_LARGE;
   } else {
     if (grid < 1 || grid > 1024 || (grid > 1 && (scratch == nullptr || counters == nullptr))) return FF_HOST_BAD_SHAPE;
     if (grid > total) return FF_HOST_BAD_SHAPE;
+    if (arena != nullptr && cfg.tiles > MAX_FLAGS) return FF_HOST_TOO_LARGE;
   }
   const int ntok = (M + 15) / 16 * 16;
-  CUtensorMap tmW, tmX;
-  int r = make_tmap_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, SBK, SBM);
+  CUtensorMap tmX, tmW;
+  int r = make_tmap_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, (uint64_t)ldx * 2, SBK, ntok);
   if (r) return r;
-  r = make_tmap_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, (uint64_t)ldx * 2, SBK, ntok);
+  r = make_tmap_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, SBK, cfg.tile_rows);
   if (r) return r;
-  const int stage_bytes = SBM * SBK * 2 + ntok * SBK * 2;
-  const int staging = ((M * SBM * 2 + 1023) / 1024) * 1024;
-  int stages = (200 * 1024 - staging) / stage_bytes;
-  if (stages > SK_MAX_STAGES) stages = SK_MAX_STAGES;
-  if (stages < 2) return FF_HOST_TOO_LARGE;
-  if (cl > 1 && (long long)M * SBM * 4 > (long long)stages * stage_bytes) return FF_HOST_TOO_LARGE;
-  const int smem = staging + stages * stage_bytes + 1024;
-  PeerArena none = {};
+  if (cfg.stages < 2) return FF_HOST_TOO_LARGE;
+  const int smem = cfg.pipe_off + cfg.stages * (STOK * SBK * 2 + cfg.tile_rows * SBK * 2) + 1024;
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
-  if (arena == nullptr)
-    return skinny_launch_kernel<false>(grid, cl, smem, stream, tmW, tmX, y, M, N, K, ldy, ntok, stages, staging, scratch,
-                                       counters, status, none);
-  return skinny_launch_kernel<true>(grid, cl, smem, stream, tmW, tmX, y, M, N, K, ldy, ntok, stages, staging, scratch,
-                                    counters, status, *arena);
+  if (arena == nullptr) {
+    auto kern = gemm_skinny_kernel<false>;
+    static bool attr_done = false;
+    if (!attr_done) { r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r; attr_done = true; }
+    PeerArena none = {};
+    return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
+                      cfg.stages, cl, cfg.pipe_off, scratch, counters, status, none);
+  }
+  auto kern = gemm_skinny_kernel<true>;
+  static bool attr_done_ar = false;
+  if (!attr_done_ar) { r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r; attr_done_ar = true; }
+  return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
+                    cfg.stages, cl, cfg.pipe_off, scratch, counters, status, *arena);
 }
 
 // `grid` is the value returned by ff_gemm_skinny_plan for the same problem.
@@ -505,15 +619,14 @@ FF_EXPORT int ff_gemm_skinny(const void* X, const void* W, void* Y, int M, int N
   return gemm_skinny_launch(X, W, Y, M, N, K, ldx, ldw, ldy, grid, scratch, counters, status, stream, nullptr);
 }
 
-// Row-parallel projection fused with the tensor-parallel all-reduce (decode shapes, M <= 256):
+// Row-parallel projection fused with the tensor-parallel all-reduce (decode shapes, M <= 128):
 // Y = sum over ranks of X_r · W_rᵀ, identical bits on every rank. ptrs: arena base of every rank.
 FF_EXPORT int ff_gemm_ar(const unsigned long long* ptrs, int rank, int world, long long half_bytes,
                          long long slot_bytes, const void* X, const void* W, void* Y, int M, int N, int K, int ldx,
                          int ldw, int ldy, int grid, float* scratch, int* counters, int* status, cudaStream_t stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return FF_HOST_BAD_SHAPE;
   if (N % 8 || (long long)M * N * 2 > slot_bytes || half_bytes < slot_bytes * world) return FF_HOST_TOO_LARGE;
-  if ((N + SBM - 1) / SBM > MAX_FLAGS) return FF_HOST_TOO_LARGE;
-  if ((reinterpret_cast<uintptr_t>(Y) & 15) || (ldy % 8)) return FF_HOST_BAD_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(Y) & 15) || (ldy % 8) || (slot_bytes % 16)) return FF_HOST_BAD_ALIGN;
   PeerArena a;
   for (int i = 0; i < MAX_RANKS; ++i) a.base[i] = i < world ? reinterpret_cast<uint8_t*>(ptrs[i]) : nullptr;
   a.rank = rank; a.world = world; a.half_bytes = half_bytes; a.slot_bytes = slot_bytes;
@@ -529,9 +642,10 @@ FF_EXPORT int ff_gemm_ar(const unsigned long long* ptrs, int rank, int world, lo
 // only owns its input and output buffers). For them the split-K partial sums and the per-tile
 // arrival counters live in a fixed array inside this library instead of caller scratch.
 //
-//  * Limit: the partial-sum slots (2 * grid * M * 128 * 4 bytes, grid <= 148 persistent CTAs) must
-//    fit in FF_NOALLOC_SCRATCH_BYTES (8 MiB) and ceil(N/128) in FF_NOALLOC_MAX_TILES (2048); larger
-//    problems are refused with FF_HOST_TOO_LARGE (in practice M <= 55 tokens for wide layers).
+//  * Limit: the partial-sum slots (2 * grid * M * 256 * 4 bytes, grid <= 148 persistent CTAs; none when
+//    the problem runs as cluster split-K) must fit in FF_NOALLOC_SCRATCH_BYTES (8 MiB) and the weight
+//    tiles in FF_NOALLOC_MAX_TILES (2048); larger problems are refused with FF_HOST_TOO_LARGE (in
+//    practice M <= 27 tokens for wide layers), and so is M > 128.
 //    Every GPU that loads this library holds the 8 MiB until exit.
 //  * The first call on a device resolves the device addresses of the arrays
 //    (cudaGetSymbolAddress, with that device current) and caches them; make that first call
@@ -554,7 +668,8 @@ static NoAllocPtrs g_noalloc_ptrs[64] = {};
 
 FF_EXPORT int ff_gemm_skinny_noalloc(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
                                      int ldy, int* status, cudaStream_t stream) {
-  if (M <= 0 || M > 256 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
+  if (M <= 0 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
+  if (M > STOK) return FF_HOST_TOO_LARGE;
   long long scratch_bytes = 0, counter_bytes = 0;
   const int grid = ff_gemm_skinny_plan(M, N, K, &scratch_bytes, &counter_bytes);
   if (scratch_bytes > (long long)FF_NOALLOC_SCRATCH_BYTES || counter_bytes > (long long)FF_NOALLOC_MAX_TILES * 4)

@@ -36,7 +36,9 @@ norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ res
             __nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ capture, int capture_stride, int hidden,
             int vocab, float eps, int unit_offset, int ldx, int* status) {
   pdl_trigger();
+  if (threadIdx.x == 0) FF_TL(status, KID_NORM, 0);
   pdl_wait();
+  if (threadIdx.x == 0) FF_TL(status, KID_NORM, 1);
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;

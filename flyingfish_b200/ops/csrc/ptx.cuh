@@ -53,6 +53,33 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
 }
 
+// ---------------------------------------------------------------------------------------
+// Device timeline (compiled in only with -DFF_TIMELINE; the tracing build of the library).
+// The status buffer is then larger: int32 word 8 counts records, 16-byte records start at word 16:
+// {globaltimer lo, hi, kernel id << 16 | phase, SM id << 20 | linear block index}. One thread per CTA
+// calls FF_TL at the points of interest; the host reads the buffer after a synchronise.
+// ---------------------------------------------------------------------------------------
+#ifdef FF_TIMELINE
+#ifndef FF_TL_CAP
+#define FF_TL_CAP (1 << 18)
+#endif
+__device__ __forceinline__ void timeline_record(int* status, int kid, int phase) {
+  if (status == nullptr) return;
+  const int i = atomicAdd(status + 8, 1);
+  if (i >= FF_TL_CAP) return;
+  const uint64_t t = globaltimer_ns();
+  uint32_t sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+  int4 rec;
+  rec.x = (int)(uint32_t)t; rec.y = (int)(uint32_t)(t >> 32);
+  const uint32_t lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  rec.z = (kid << 16) | (phase & 0xffff); rec.w = (int)((sm << 20) | (lin & 0xfffffu));
+  reinterpret_cast<int4*>(status + 16)[i] = rec;
+}
+#define FF_TL(status, kid, phase) timeline_record(status, kid, phase)
+#else
+#define FF_TL(status, kid, phase) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -150,6 +177,9 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 __device__ __forceinline__ void cluster_sync_all() {     // every thread of every CTA, warps converged
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// split form: arrive early (e.g. at kernel entry), wait where the peers' progress is needed
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t cta_rank) {
   uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(cta_rank)); return r;
 }
@@ -157,6 +187,10 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
+}
+
+__device__ __forceinline__ void st_dsmem_f4(uint32_t addr, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
 // ---- programmatic dependent launch ---------------------------------------------------------------

@@ -22,7 +22,9 @@ __global__ void rope_kv_paged_kernel(__nv_bfloat16* __restrict__ qkv, const int*
                                      int rows, int hq, int hkv, int dim, int rot_dim, int block_size, int num_blocks,
                                      float theta, int ldqkv, int* status) {
   pdl_trigger();
+  if (threadIdx.x == 0) FF_TL(status, KID_ROPE_KV, 0);
   pdl_wait();
+  if (threadIdx.x == 0) FF_TL(status, KID_ROPE_KV, 1);
   const int vec_per_head = dim >> 4;                 // pairs of uint4
   const int heads = hq + 2 * hkv;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -137,7 +139,9 @@ __global__ void __launch_bounds__(1024)
 argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out_ids, float* __restrict__ out_vals, int vocab,
                    int ld, int id_offset, const int* __restrict__ valid_rows, int* status) {
   pdl_trigger();
+  if (threadIdx.x == 0) FF_TL(status, KID_SAMPLE, 0);
   pdl_wait();
+  if (threadIdx.x == 0) FF_TL(status, KID_SAMPLE, 1);
   const int row = blockIdx.x;
   if (valid_rows && row >= *valid_rows) return;
   __shared__ float sv[32];

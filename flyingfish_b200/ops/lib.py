@@ -9,12 +9,17 @@ fallback for the CUDA path.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
 import torch
 
 _HERE = Path(__file__).resolve().parent
+# FLYINGFISH_TIMELINE=1 loads the tracing build of the kernels and enlarges the status buffer
+# (word 8 = record count, 16-byte records from word 16 on; see utils/timeline.py).
+TIMELINE = os.environ.get("FLYINGFISH_TIMELINE", "0") == "1"
+TIMELINE_CAP = 1 << 18
 _lock = threading.Lock()
 _kernels: ctypes.CDLL | None = None
 _host: ctypes.CDLL | None = None
@@ -36,7 +41,7 @@ def kernels() -> ctypes.CDLL:
         with _lock:
             if _kernels is None:
                 from . import build
-                path = build.build_kernels()
+                path = build.build_kernels(timeline=TIMELINE)
                 _kernels = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
     return _kernels
 
@@ -91,7 +96,7 @@ def status_tensor(device: torch.device | int | None = None) -> torch.Tensor:
         dev = torch.cuda.current_device()
     t = _status.get(dev)
     if t is None:
-        t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+        t = torch.zeros(16 + 4 * TIMELINE_CAP if TIMELINE else 4, dtype=torch.int32, device=f"cuda:{dev}")
         _status[dev] = t
     return t
 
@@ -99,9 +104,9 @@ def status_tensor(device: torch.device | int | None = None) -> torch.Tensor:
 def read_status(device=None, clear: bool = True) -> tuple[int, int, int, int]:
     """Synchronising read of the status word (call at an existing sync point)."""
     t = status_tensor(device)
-    vals = tuple(int(v) for v in t.cpu().tolist())
+    vals = tuple(int(v) for v in t[:4].cpu().tolist())
     if clear and vals[0] != 0:
-        t.zero_()
+        t[:4].zero_()
     return vals  # type: ignore[return-value]
 
 

@@ -36,7 +36,10 @@ class Flusher:
         self.buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
 
     def __call__(self):
-        self.buf.zero_()
+        # several passes: the GPU must still be busy flushing when the timed launch is enqueued,
+        # otherwise the host's launch latency lands between the two events
+        for _ in range(4):
+            self.buf.zero_()
 
 
 def time_op(fn, iters: int, warmup: int, flush: Flusher | None) -> dict:
@@ -54,7 +57,9 @@ def time_op(fn, iters: int, warmup: int, flush: Flusher | None) -> dict:
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) * 1e3)      # us
     times.sort()
-    return {"us_median": times[len(times) // 2], "us_min": times[0], "us_p90": times[int(len(times) * 0.9)]}
+    # event timestamps tick in steps of about 2 us on some boxes: the mean over many iterations resolves finer
+    return {"us_median": times[len(times) // 2], "us_min": times[0], "us_p90": times[int(len(times) * 0.9)],
+            "us_mean": sum(times) / len(times)}
 
 
 def bench_gemm(args) -> dict:
