@@ -54,14 +54,18 @@ class DecoderModel:
         self.capture_taps: dict[int, int] = {}    # layer index -> tap slot for draft-model hidden taps
         self.capture_slab: torch.Tensor | None = None
         self.normed_sink: list | None = None      # when a list: every forward appends its final-normed rows
+        self._rope_cs: torch.Tensor | None = None  # per-forward cos/sin table of the fused QKV kernels
 
     # -- pieces ----------------------------------------------------------------------------
     def _attention(self, i: int, n: torch.Tensor, b: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
         lw, s = self.w.layers[i], self.spec
-        qkv = ops.linear(n, lw.wqkv)
         if s.qk_norm:
+            qkv = ops.linear(n, lw.wqkv)
             self._qk_norm(qkv, lw)
-        ops.rope_kv_paged(qkv, b.positions, b.slots, kv.k[i], kv.v[i], self.hq, self.hkv, self.d, s.rope_theta)
+            ops.rope_kv_paged(qkv, b.positions, b.slots, kv.k[i], kv.v[i], self.hq, self.hkv, self.d, s.rope_theta)
+        else:
+            qkv = ops.linear_rope_kv(n, lw.wqkv, b.positions, b.slots, kv.k[i], kv.v[i], self.hq, self.hkv, self.d,
+                                     s.rope_theta, cos_sin=self._rope_cs)
         if b.is_decode:
             a = ops.attn_decode(qkv, kv.k[i], kv.v[i], b.block_table, b.ctx_lens, self.hq, self.hkv, self.d,
                                 self.scale, nq=b.nq, tree_mask=b.tree_mask, max_ctx=b.max_ctx)
@@ -98,8 +102,12 @@ class DecoderModel:
         replaces the embedding lookup (multi-token-prediction heads feed a projected mix of the
         next token's embedding and the previous hidden state)."""
         w, s = self.w, self.spec
+        self._rope_cs = None
         if inputs_embeds is None and self._sequence_parallel(b):
             return self._hidden_states_sp(b, kv)
+        if b.positions.is_cuda and b.positions.shape[0] <= ops.SKINNY_MAX_M and self.d == 128 and not s.qk_norm:
+            # one cos/sin table per step for the fused QKV + rotary + KV-write kernels of all layers
+            self._rope_cs = ops.rope_table(b.positions, self.d, s.rope_theta)
         if inputs_embeds is None:
             x, n = ops.embed_rmsnorm(b.ids, w.embed, w.layers[0].input_ln, s.rms_eps)
         else:

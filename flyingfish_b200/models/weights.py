@@ -7,7 +7,7 @@ generator feed the same code. Fusions done here, once, at load time:
 
 * ``wqkv``  = [q | k | v] rows (the reference's fused QKV catalog, src/backend/cuda/weights.rs),
   sharded by heads for tensor parallelism;
-* ``wgu``   = gate/up rows interleaved per 128 so the GEMM epilogue can apply SwiGLU;
+* ``wgu``   = gate/up rows interleaved per 64 so the GEMM epilogues can apply SwiGLU;
 * row-parallel ``wo`` / ``wdown`` shards split the input dimension;
 * ``lm_head`` is vocabulary-parallel.
 
@@ -69,7 +69,7 @@ class LayerWeights:
     wo: torch.Tensor = None              # [hidden, hq/tp * d]
     q_norm: torch.Tensor | None = None
     k_norm: torch.Tensor | None = None
-    wgu: torch.Tensor | None = None      # dense FFN, gate/up interleaved per 128 (or [gate|up] if not divisible)
+    wgu: torch.Tensor | None = None      # dense FFN, gate/up interleaved per 64 (or [gate|up] if not divisible)
     wgu_interleaved: bool = True
     wdown: torch.Tensor | None = None
     # MoE

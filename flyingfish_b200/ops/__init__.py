@@ -13,6 +13,7 @@ through the status word (:func:`flyingfish_b200.ops.lib.check_status`).
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
@@ -96,6 +97,9 @@ def workspace(device: torch.device) -> _Workspace:
 # linear
 # ------------------------------------------------------------------------------------------
 SKINNY_MAX_M = 128
+# decode-shape epilogue fusions (FLYINGFISH_FUSE_SWIGLU=0 / FLYINGFISH_FUSE_ROPE=0 fall back to separate kernels)
+FUSE_SWIGLU = os.environ.get("FLYINGFISH_FUSE_SWIGLU", "1") != "0"
+FUSE_ROPE = os.environ.get("FLYINGFISH_FUSE_ROPE", "1") != "0"
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
@@ -142,19 +146,31 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
 def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor | None = None,
                   mode: int = 0) -> torch.Tensor:
     """Gate/up projection with the SwiGLU activation fused into the GEMM epilogue. The weight is
-    the per-128 interleaved ``[2f, h]`` matrix built by :func:`ref.interleave_gate_up`."""
+    the per-64 interleaved ``[2f, h]`` matrix built by :func:`ref.interleave_gate_up`."""
     if not _is_cuda(x):
         return ref.linear_swiglu(x, w_interleaved, mode)
     m, ldx = _rows2d(x)
     n, ldw = _rows2d(w_interleaved)
     k = x.shape[1]
     _require(n % 256 == 0 and mode == 0, "linear_swiglu: N must be a multiple of 256 and mode 0")
-    if m <= SKINNY_MAX_M:
-        # decode shapes: two small kernels beat a 128-row tile that is mostly padding
-        gu = linear(x, w_interleaved)
-        return silu_mul_interleaved(gu, out)
     if out is None:
         out = torch.empty(m, n // 2, dtype=BF16, device=x.device)
+    if m <= SKINNY_MAX_M and not FUSE_SWIGLU:
+        return silu_mul_interleaved(linear(x, w_interleaved), out)
+    if m <= SKINNY_MAX_M:
+        # decode shapes: the weight-streaming kernel applies SwiGLU row-wise in its epilogue
+        lib = kernels()
+        scratch_b, counter_b = c_longlong(0), c_longlong(0)
+        grid = lib.ff_gemm_skinny_plan_epi(m, n, k, 1, ctypes.byref(scratch_b), ctypes.byref(counter_b))
+        check(min(grid, 0), "ff_gemm_skinny_plan_epi")
+        ws = workspace(x.device)
+        scratch = ws.ensure("gemm_scratch", scratch_b.value // 4) if scratch_b.value > 0 else None
+        _require(counter_b.value // 4 <= ws.gemm_counters.numel(), "linear_swiglu: too many column tiles for counters")
+        rc = lib.ff_gemm_skinny_swiglu(ptr(x), ptr(w_interleaved), ptr(out), m, n, k, ldx, ldw, out.stride(0), grid,
+                                       ptr(scratch), ptr(ws.gemm_counters), ptr(status_tensor(x.device)), stream_ptr())
+        check(rc, "ff_gemm_skinny_swiglu")
+        _count()
+        return out
     rc = kernels().ff_gemm_bf16(ptr(x), ptr(w_interleaved), ptr(out), m, n, k, ldx, ldw, out.stride(0), 1,
                                 ptr(status_tensor(x.device)), stream_ptr())
     check(rc, "ff_gemm_bf16(swiglu)")
@@ -163,7 +179,7 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tenso
 
 
 def silu_mul_interleaved(gu: torch.Tensor, out: torch.Tensor | None = None, mode: int = 0) -> torch.Tensor:
-    """SwiGLU on the per-128 interleaved gate/up layout produced by the fused weight."""
+    """SwiGLU on the per-64 interleaved gate/up layout produced by the fused weight."""
     return silu_mul(gu, mode=mode, out=out, interleaved=True)
 
 
@@ -274,12 +290,71 @@ def rope_kv_paged(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tenso
     _count()
 
 
+def rope_table(positions: torch.Tensor, rot_dim: int, theta: float, inv_freq: torch.Tensor | None = None) -> torch.Tensor:
+    """``[rows, rot_dim/2, 2]`` FP32 (cos, sin) of ``position * inv_freq``, rounded to BF16 as the rotation
+    kernels round them. Computed once per step and shared by every layer's fused QKV epilogue."""
+    rows = positions.shape[0]
+    out = torch.empty(rows, rot_dim // 2, 2, dtype=torch.float32, device=positions.device)
+    if not _is_cuda(positions):
+        i = torch.arange(rot_dim // 2, dtype=torch.float32)
+        inv = inv_freq.float() if inv_freq is not None else 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), 2 * i / rot_dim)
+        ang = positions.float()[:, None] * inv[None, :]
+        out[..., 0] = torch.cos(ang).to(BF16).float()
+        out[..., 1] = torch.sin(ang).to(BF16).float()
+        return out
+    rc = kernels().ff_rope_table(ptr(positions), ptr(inv_freq), ptr(out), rows, rot_dim, c_float(theta), stream_ptr())
+    check(rc, "ff_rope_table")
+    _count()
+    return out
+
+
+def linear_rope_kv(x: torch.Tensor, wqkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                   kcache: torch.Tensor, vcache: torch.Tensor, hq: int, hkv: int, dim: int, theta: float,
+                   rot_dim: int | None = None, inv_freq: torch.Tensor | None = None,
+                   cos_sin: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused QKV projection + rotary embedding + paged KV write: ``qkv = x @ wqkv.T`` with Q and K
+    rotated and K/V stored at ``slots``. Decode shapes with 128-dim heads run as one kernel (the
+    rotation and the cache write are the GEMM's epilogue; ``cos_sin`` from :func:`rope_table` is
+    reused across layers); everything else as GEMM + rope kernel."""
+    m = x.shape[0]
+    n = wqkv.shape[0]
+    fused = (FUSE_ROPE and _is_cuda(x) and m <= SKINNY_MAX_M and dim == 128 and n == (hq + 2 * hkv) * 128 and x.dtype == BF16
+             and kcache.dim() == 4 and kcache.is_contiguous() and vcache.is_contiguous())
+    if not fused:
+        qkv = linear(x, wqkv)
+        rope_kv_paged(qkv, positions, slots, kcache, vcache, hq, hkv, dim, theta, rot_dim, inv_freq)
+        return qkv
+    _require(positions.dtype == torch.int32 and slots.dtype == torch.int32, "linear_rope_kv: int32 metadata")
+    nb, ch, bs, cd = kcache.shape
+    _require(ch == hkv and cd == dim, "linear_rope_kv: cache geometry differs from the heads")
+    _, ldx = _rows2d(x)
+    _, ldw = _rows2d(wqkv)
+    k = x.shape[1]
+    out = torch.empty(m, n, dtype=BF16, device=x.device)
+    lib = kernels()
+    scratch_b, counter_b = c_longlong(0), c_longlong(0)
+    grid = lib.ff_gemm_skinny_plan_epi(m, n, k, 2, ctypes.byref(scratch_b), ctypes.byref(counter_b))
+    check(min(grid, 0), "ff_gemm_skinny_plan_epi")
+    ws = workspace(x.device)
+    scratch = ws.ensure("gemm_scratch", scratch_b.value // 4) if scratch_b.value > 0 else None
+    _require(counter_b.value // 4 <= ws.gemm_counters.numel(), "linear_rope_kv: too many column tiles for counters")
+    if cos_sin is None:
+        cos_sin = rope_table(positions, rot_dim or dim, theta, inv_freq)
+    _require(cos_sin.shape == (m, (rot_dim or dim) // 2, 2) and cos_sin.is_contiguous(), "linear_rope_kv: cos/sin table shape")
+    rc = lib.ff_gemm_skinny_rope_kv(ptr(x), ptr(wqkv), ptr(out), m, n, k, ldx, ldw, n, grid, ptr(scratch),
+                                    ptr(ws.gemm_counters), ptr(cos_sin), ptr(slots), ptr(kcache), ptr(vcache),
+                                    hq, hkv, rot_dim or dim, bs, nb, ptr(status_tensor(x.device)), stream_ptr())
+    check(rc, "ff_gemm_skinny_rope_kv")
+    _count()
+    return out
+
+
 def silu_mul(gu: torch.Tensor, mode: int = 0, limit: float = 0.0, out: torch.Tensor | None = None,
              interleaved: bool = False) -> torch.Tensor:
     if not _is_cuda(gu):
         if interleaved:
             m, n = gu.shape
-            g = gu.view(m, n // 256, 2, 128)
+            g = gu.view(m, n // 128, 2, 64)
             gu = torch.cat([g[:, :, 0].reshape(m, n // 2), g[:, :, 1].reshape(m, n // 2)], dim=1)
         return ref.silu_mul(gu, mode, limit)
     rows, ld = _rows2d(gu)

@@ -49,7 +49,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
-// epi: 0 = store bf16; 1 = SwiGLU (columns [0,BN/2) of a tile are gate, [BN/2,BN) are up; output
+// epi: 0 = store bf16; 1 = SwiGLU (every 128 columns of a tile are 64 gate then the matching 64 up columns; output
 // has N/2 columns); 2 = store fp32.
 // COMM (tensor-parallel prefill, rows split evenly over the ranks in 128-row blocks):
 //   1 = all-gather -> GEMM : A is row-sharded. The epilogue warps first push this rank's shard into
@@ -205,8 +205,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < HALF; c += 16) {
           uint32_t g[16], u[16];
-          tmem_ld_x16(taddr + c, g);
-          tmem_ld_x16(taddr + HALF + c, u);
+          const int gc = (c >> 6) * 128 + (c & 63);      // 64 gate columns, then the matching 64 up columns
+          tmem_ld_x16(taddr + gc, g);
+          tmem_ld_x16(taddr + gc + 64, u);
           tmem_ld_wait();
           if (row < M) {
             uint32_t o[8];

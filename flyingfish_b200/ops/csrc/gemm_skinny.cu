@@ -94,6 +94,79 @@ struct TileSink {
   }
 };
 
+// Row-wise epilogues over a 128-row weight tile whose first 64 columns pair with its last 64:
+//   mode 1  SwiGLU: columns [0,64) are gate, [64,128) the matching up values (weight interleaved per
+//           64 rows); output column tile*64 + j = silu(gate_j) * up_j, N/2 output columns.
+//   mode 2  rotary embedding + KV-cache write for a fused QKV projection with 128-dim heads: the tile
+//           is one head; Q and K heads are rotated (pairs j, j + 64), Q/K/V go to Y and K/V also to
+//           their slot of the paged cache.
+// Both round the accumulators to BF16 first and then do exactly what the stand-alone kernels
+// (silu_mul, rope_kv_paged) do, so fused and unfused paths give the same bits.
+struct SkinnyEpi {
+  int mode;
+  const float2* cos_sin;       // [rows, rot_dim/2] (cos, sin) of position * inv_freq, rounded to BF16 (ff_rope_table)
+  const int* slots;
+  __nv_bfloat16* kcache; __nv_bfloat16* vcache;
+  int hq, hkv, rot_dim, block_size, num_blocks;
+};
+
+__device__ __forceinline__ float bf16r_sk(float x) { return __bfloat162float(__float2bfloat16(x)); }
+__device__ __forceinline__ float silu_sk(float x) { return x / (1.0f + __expf(-x)); }
+
+// lo/hi: eight values each of token row t, tile columns [j8*8, j8*8+8) and [64 + j8*8, ...)
+__device__ __forceinline__ void emit_pair(const SkinnyEpi& ep, __nv_bfloat16* __restrict__ Y, int N, int ldy, int t, int tile,
+                                          int j8, const float* lo, const float* hi, int* status) {
+  if (ep.mode == 1) {
+    const int col = tile * 64 + j8 * 8;
+    if (col >= N / 2) return;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a0 = bf16r_sk(silu_sk(bf16r_sk(lo[2 * j]))), a1 = bf16r_sk(silu_sk(bf16r_sk(lo[2 * j + 1])));
+      o[j] = pack_bf16x2(a0 * bf16r_sk(hi[2 * j]), a1 * bf16r_sk(hi[2 * j + 1]));
+    }
+    *reinterpret_cast<uint4*>(Y + (size_t)t * ldy + col) = make_uint4(o[0], o[1], o[2], o[3]);
+    return;
+  }
+  // mode 2
+  const int head = tile;
+  if (head >= ep.hq + 2 * ep.hkv) return;
+  float a[8], b[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { a[j] = bf16r_sk(lo[j]); b[j] = bf16r_sk(hi[j]); }
+  const bool is_v = head >= ep.hq + ep.hkv;
+  if (!is_v) {
+    const int rhalf = ep.rot_dim >> 1;
+    const float2* tab = ep.cos_sin + (size_t)t * rhalf;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = j8 * 8 + j;
+      if (i < rhalf) {
+        const float2 c_s = tab[i];
+        const float cs = c_s.x, sn = c_s.y;
+        const float x1 = a[j], x2 = b[j];
+        a[j] = bf16r_sk(bf16r_sk(x1 * cs) - bf16r_sk(x2 * sn));
+        b[j] = bf16r_sk(bf16r_sk(x2 * cs) + bf16r_sk(x1 * sn));
+      }
+    }
+  }
+  const uint4 vlo = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+  const uint4 vhi = make_uint4(pack_bf16x2(b[0], b[1]), pack_bf16x2(b[2], b[3]), pack_bf16x2(b[4], b[5]), pack_bf16x2(b[6], b[7]));
+  __nv_bfloat16* y = Y + (size_t)t * ldy + (size_t)head * 128 + j8 * 8;
+  *reinterpret_cast<uint4*>(y) = vlo;
+  *reinterpret_cast<uint4*>(y + 64) = vhi;
+  if (head >= ep.hq) {
+    const int slot = ep.slots[t];
+    if (slot < 0) return;                               // padding row: nothing cached
+    const int blk = slot / ep.block_size, off = slot - blk * ep.block_size;
+    if (blk >= ep.num_blocks) { set_status(status, KID_ROPE_KV, FF_ERR_BOUNDS, t, slot); return; }
+    const int kvh = is_v ? head - ep.hq - ep.hkv : head - ep.hq;
+    __nv_bfloat16* dst = (is_v ? ep.vcache : ep.kcache) + (((size_t)blk * ep.hkv + kvh) * ep.block_size + off) * 128 + j8 * 8;
+    *reinterpret_cast<uint4*>(dst) = vlo;
+    *reinterpret_cast<uint4*>(dst + 64) = vhi;
+  }
+}
+
 // FUSE_AR: after this CTA's values of (tile, rows row0 + i*row_step) are in every rank's slot, flag the
 // peers, wait for theirs, and write the rank-ordered sum. Called by all 128 epilogue threads.
 __device__ __forceinline__ void allreduce_tile(const TileSink<true>& sink, int M, int tile, int tile_rows, int flag_idx,
@@ -143,7 +216,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldy, int ntok, int tile_rows, int stages,
                    int cl_size, int pipe_off, float* __restrict__ scratch, int* __restrict__ counters, int* status,
-                   PeerArena ar) {
+                   PeerArena ar, SkinnyEpi ep) {
   pdl_trigger();
   if (cl_size > 1) cluster_arrive_relaxed();         // phase A: "this CTA runs" (waited on before the first remote store)
   if (threadIdx.x == 0) FF_TL(status, KID_GEMM_SKINNY, 0);
@@ -300,7 +373,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const bool whole = sg.kb0 == 0 && sg.kb1 == kblocks;
       if (whole) {
         // TMEM -> registers -> output
-        if (row_live) {
+        if (row_live && ep.mode != 0) {
+          for (int c = 0; c < 64; c += 16) {
+            uint32_t g[16], u[16];
+            tmem_ld_x16(taddr + c, g);
+            tmem_ld_x16(taddr + 64 + c, u);
+            tmem_ld_wait();
+            if (t_own < M) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+                emit_pair(ep, Y, N, ldy, t_own, sg.tile, (c >> 3) + h, reinterpret_cast<const float*>(g) + 8 * h,
+                          reinterpret_cast<const float*>(u) + 8 * h, status);
+            }
+          }
+        } else if (row_live) {
           for (int c = 0; c < tile_rows; c += 16) {
             uint32_t r[16];
             tmem_ld_x16(taddr + c, r);
@@ -359,8 +445,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         // fix-up: 8-value vectors of the tile are dealt round-robin to the 128 threads; four vectors of two
         // partials (sixteen independent 16-byte loads) are in flight at a time; the adds stay in ascending
         // CTA order
+        // with a row-wise epilogue a thread takes the two paired vectors (j8, j8 + 8) of a row together
+        const bool paired = ep.mode != 0;
         const int nvec = M * vpr;
-        for (int i0 = e; i0 < nvec; i0 += 512) {
+        const int i_end = paired ? M * 8 : nvec;
+        for (int i0 = e; i0 < i_end; i0 += (paired ? 256 : 512)) {
           float a8[4][8];
 #pragma unroll
           for (int g = 0; g < 4; ++g)
@@ -370,7 +459,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             float4 v[4][2][2];
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
-              const int i = i0 + 128 * g;
+              int i = i0 + 128 * g;
+              if (paired) { const int pr = i0 + 128 * (g >> 1); i = pr < i_end ? (pr >> 3) * 16 + (pr & 7) + 8 * (g & 1) : nvec; }
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
                 const int cc = c + h;
@@ -389,10 +479,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                 a8[g][4] += v[g][h][1].x; a8[g][5] += v[g][h][1].y; a8[g][6] += v[g][h][1].z; a8[g][7] += v[g][h][1].w;
               }
           }
+          if (paired) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int i = i0 + 128 * g;
-            if (i < nvec) { const int t = i / vpr, c8 = i - t * vpr; sink.put8(t, col0 + c8 * 8, a8[g]); }
+            for (int g = 0; g < 4; g += 2) {
+              const int pr = i0 + 128 * (g >> 1);
+              if (pr < i_end) emit_pair(ep, Y, N, ldy, pr >> 3, sg.tile, pr & 7, a8[g], a8[g + 1], status);
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int i = i0 + 128 * g;
+              if (i < nvec) { const int t = i / vpr, c8 = i - t * vpr; sink.put8(t, col0 + c8 * 8, a8[g]); }
+            }
           }
         }
         if constexpr (FUSE_AR) allreduce_tile(sink, M, sg.tile, tile_rows, sg.tile, 0, 1, e, bars, ar_epoch, status);
@@ -411,6 +509,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const int rows = (M - crank + cl_size - 1) / cl_size;  // token rows t = crank (mod cl_size)
         const int col0 = sg.tile * tile_rows;
         const int ldp = tile_rows + SP_PAD;
+        if (ep.mode != 0) {
+          for (int i = e; i < rows * 8; i += 128) {
+            const int ti = i >> 3, j8 = i & 7;
+            float lo[8], hi[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { lo[j] = 0.f; hi[j] = 0.f; }
+            for (int s = 0; s < cl_size; ++s) {
+              const float4* p4 = reinterpret_cast<const float4*>(recv + ((size_t)s * rows_per + ti) * ldp + j8 * 8);
+              const float4 l0 = p4[0], l1 = p4[1], h0 = p4[16], h1 = p4[17];
+              lo[0] += l0.x; lo[1] += l0.y; lo[2] += l0.z; lo[3] += l0.w; lo[4] += l1.x; lo[5] += l1.y; lo[6] += l1.z; lo[7] += l1.w;
+              hi[0] += h0.x; hi[1] += h0.y; hi[2] += h0.z; hi[3] += h0.w; hi[4] += h1.x; hi[5] += h1.y; hi[6] += h1.z; hi[7] += h1.w;
+            }
+            emit_pair(ep, Y, N, ldy, crank + ti * cl_size, sg.tile, j8, lo, hi, status);
+          }
+        } else
         for (int i = e; i < rows * vpr; i += 128) {
           const int ti = i / vpr, c8 = i - ti * vpr;
           const float* src = recv + (size_t)ti * ldp + c8 * 8;
@@ -498,7 +611,8 @@ static int skinny_stages(int tile_rows, int reserved = 0) {
   return st;
 }
 
-static SkinnyConfig skinny_config(int M, int N, int K) {
+// epi != 0 (row-wise epilogue): tiles are exactly 128 rows.
+static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
   const int kblocks = (K + SBK - 1) / SBK;
   static int env_s = -1, env_r = -1;
   if (env_s < 0) {
@@ -508,13 +622,17 @@ static SkinnyConfig skinny_config(int M, int N, int K) {
   // stream-K: widest tile that N fills
   int rows1 = 128;                               // measured: 128-row tiles beat 256 (the fix-up moves half the bytes)
   if (N < rows1) rows1 = (N + 15) / 16 * 16;
-  if (env_r > 0 && env_s == 1) rows1 = env_r;
+  if (env_r > 0 && env_s == 1 && epi == 0) rows1 = env_r;
   SkinnyConfig best = {1, rows1, (N + rows1 - 1) / rows1, skinny_stages(rows1), 0};
   if (env_s == 1) return best;
   // Time model (microseconds). A CTA takes in at most ~60 GB/s (weights plus the activation tile it
   // re-reads from L2 for every k-block), a pipeline of `st` stages cannot turn a k-block around faster
   // than the ~1.5 us load latency / st, and all CTAs together cannot beat HBM (~5.9 TB/s on reads).
-  const int ntok = (M + 15) / 16 * 16;
+  // The choice must not depend on M: the K split fixes the order of the FP32 additions, and a
+  // row's bits may not change with the batch it is computed in. So the model assumes 64 tokens and
+  // the receive buffer is sized for 128.
+  const int ntok = 64;
+  (void)M;
   auto model = [&](int rows, int kb_per_cta, int st, double ctas) {
     const double per_kb = (rows + ntok) * 128.0 / 60e3;
     const double lat_kb = 1.5 / st;
@@ -535,18 +653,37 @@ static SkinnyConfig skinny_config(int M, int N, int K) {
     const int maxc = skinny_max_clusters(s) - (s > 2 ? 1 : 0);
     if (maxc <= 0) continue;
     for (int rows = 64; rows <= SBN; rows += 16) {
-      if (env_r > 0 && rows != env_r) continue;
+      if (epi != 0 && rows != 128) continue;
+      if (epi == 0 && env_r > 0 && rows != env_r) continue;
       const int tiles = (N + rows - 1) / rows;
       if (tiles > maxc) continue;
       // receive buffer: S slots x ceil(M/S) rows of (rows + pad) floats, in front of the pipeline
-      const int recv = (s * ((M + s - 1) / s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
+      const int recv = (s * ((STOK + s - 1) / s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
       const int st = skinny_stages(rows, recv);
       if (st < 3) continue;
       const double c = model(rows, (kblocks + s - 1) / s, st, (double)tiles * s);
       if (c < best_cost - 1e-9 || (env_s > 0 && best.cluster == 1)) { best_cost = c; best = {s, rows, tiles, st, recv}; }
     }
   }
+  if (best.cluster > 1) {
+    // the split (cluster, tile_rows) is fixed above for every M; the receive buffer and with it the pipeline depth
+    // follow the actual M
+    const int s = best.cluster;
+    best.pipe_off = (s * ((M + s - 1) / s) * (best.tile_rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
+    best.stages = skinny_stages(best.tile_rows, best.pipe_off);
+  }
   return best;
+}
+
+// Decomposition chosen for a problem: out = {cluster size, tile rows, tiles, pipeline stages, grid}.
+FF_EXPORT int ff_gemm_skinny_config(int M, int N, int K, int epi, int* out) {
+  if (M <= 0 || M > STOK || N <= 0 || K <= 0 || out == nullptr) return FF_HOST_BAD_SHAPE;
+  const SkinnyConfig c = skinny_config(M, N, K, epi);
+  long long sb = 0, cb = 0;
+  out[0] = c.cluster; out[1] = c.tile_rows; out[2] = c.tiles; out[3] = c.stages;
+  out[4] = (c.cluster > 1) ? c.tiles * c.cluster : 0;
+  (void)sb; (void)cb;
+  return 0;
 }
 
 // Number of co-resident clusters of `s` CTAs of the decode GEMM on the current device (0: not launchable).
@@ -556,9 +693,9 @@ FF_EXPORT int ff_gemm_skinny_max_clusters(int s) { return skinny_max_clusters(s)
 // persistent CTA per SM, fewer for tiny problems);
 // *scratch_bytes = FP32 partial slots (two per CTA; none in cluster mode), *counter_bytes = one int32
 // per weight tile (zero before the first launch; every launch leaves them zero).
-FF_EXPORT int ff_gemm_skinny_plan(int M, int N, int K, long long* scratch_bytes, long long* counter_bytes) {
+static int skinny_plan(int M, int N, int K, int epi, long long* scratch_bytes, long long* counter_bytes) {
   const int kblocks = (K + SBK - 1) / SBK;
-  const SkinnyConfig cfg = skinny_config(M, N, K);
+  const SkinnyConfig cfg = skinny_config(M, N, K, epi);
   if (counter_bytes) *counter_bytes = (long long)cfg.tiles * 4;
   if (cfg.cluster > 1) {
     if (scratch_bytes) *scratch_bytes = 0;
@@ -572,13 +709,28 @@ FF_EXPORT int ff_gemm_skinny_plan(int M, int N, int K, long long* scratch_bytes,
   return (int)g;
 }
 
+FF_EXPORT int ff_gemm_skinny_plan(int M, int N, int K, long long* scratch_bytes, long long* counter_bytes) {
+  return skinny_plan(M, N, K, 0, scratch_bytes, counter_bytes);
+}
+
+// Plan for the variants with a row-wise epilogue (epi 1 SwiGLU, 2 rotary + KV write): N % 128 == 0.
+FF_EXPORT int ff_gemm_skinny_plan_epi(int M, int N, int K, int epi, long long* scratch_bytes, long long* counter_bytes) {
+  if (N % 128) return FF_HOST_BAD_SHAPE;
+  return skinny_plan(M, N, K, epi, scratch_bytes, counter_bytes);
+}
+
 static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
                               int grid, float* scratch, int* counters, int* status, cudaStream_t stream,
-                              const PeerArena* arena) {
+                              const PeerArena* arena, const SkinnyEpi* epi = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return FF_HOST_BAD_SHAPE;
+  SkinnyEpi ep = {};
+  if (epi != nullptr) {
+    ep = *epi;
+    if (arena != nullptr || (N % 128) || (ldy % 8) || (reinterpret_cast<uintptr_t>(Y) & 15)) return FF_HOST_BAD_SHAPE;
+  }
   if (M > STOK) return FF_HOST_TOO_LARGE;
   if ((K % 8) || (ldx % 8) || (ldw % 8)) return FF_HOST_BAD_ALIGN;
-  const SkinnyConfig cfg = skinny_config(M, N, K);
+  const SkinnyConfig cfg = skinny_config(M, N, K, ep.mode);
   const int cl = cfg.cluster;
   const long long total = (long long)cfg.tiles * ((K + SBK - 1) / SBK);
   if (cl > 1) {
@@ -604,19 +756,45 @@ static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int 
     if (!attr_done) { r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r; attr_done = true; }
     PeerArena none = {};
     return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
-                      cfg.stages, cl, cfg.pipe_off, scratch, counters, status, none);
+                      cfg.stages, cl, cfg.pipe_off, scratch, counters, status, none, ep);
   }
   auto kern = gemm_skinny_kernel<true>;
   static bool attr_done_ar = false;
   if (!attr_done_ar) { r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r; attr_done_ar = true; }
   return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
-                    cfg.stages, cl, cfg.pipe_off, scratch, counters, status, *arena);
+                    cfg.stages, cl, cfg.pipe_off, scratch, counters, status, *arena, ep);
 }
 
 // `grid` is the value returned by ff_gemm_skinny_plan for the same problem.
 FF_EXPORT int ff_gemm_skinny(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
                              int grid, float* scratch, int* counters, int* status, cudaStream_t stream) {
   return gemm_skinny_launch(X, W, Y, M, N, K, ldx, ldw, ldy, grid, scratch, counters, status, stream, nullptr);
+}
+
+// Gate/up projection with the SwiGLU applied in the epilogue: W is [N, K] with gate/up rows interleaved per
+// 64, Y is [M, N/2]. `grid` from ff_gemm_skinny_plan_epi(M, N, K, 1).
+FF_EXPORT int ff_gemm_skinny_swiglu(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
+                                    int grid, float* scratch, int* counters, int* status, cudaStream_t stream) {
+  SkinnyEpi ep = {};
+  ep.mode = 1;
+  return gemm_skinny_launch(X, W, Y, M, N, K, ldx, ldw, ldy, grid, scratch, counters, status, stream, nullptr, &ep);
+}
+
+// Fused QKV projection with rotary embedding and paged KV-cache write in the epilogue (128-dim heads;
+// N = (hq + 2*hkv) * 128). Y receives the rotated Q/K and V rows; K and V also go to `slots` of the cache
+// (layout [blocks, hkv, block_size, 128]; negative slots are skipped). cos_sin: [M, rot_dim/2] float pairs from
+// ff_rope_table. `grid` from
+// ff_gemm_skinny_plan_epi(M, N, K, 2).
+FF_EXPORT int ff_gemm_skinny_rope_kv(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
+                                     int grid, float* scratch, int* counters, const float* cos_sin, const int* slots,
+                                     void* kcache, void* vcache, int hq, int hkv, int rot_dim, int block_size,
+                                     int num_blocks, int* status, cudaStream_t stream) {
+  if (hq <= 0 || hkv <= 0 || N != (hq + 2 * hkv) * 128 || rot_dim > 128 || rot_dim % 2) return FF_HOST_BAD_SHAPE;
+  SkinnyEpi ep = {};
+  ep.mode = 2; ep.cos_sin = reinterpret_cast<const float2*>(cos_sin); ep.slots = slots;
+  ep.kcache = static_cast<__nv_bfloat16*>(kcache); ep.vcache = static_cast<__nv_bfloat16*>(vcache);
+  ep.hq = hq; ep.hkv = hkv; ep.rot_dim = rot_dim; ep.block_size = block_size; ep.num_blocks = num_blocks;
+  return gemm_skinny_launch(X, W, Y, M, N, K, ldx, ldw, ldy, grid, scratch, counters, status, stream, nullptr, &ep);
 }
 
 // Row-parallel projection fused with the tensor-parallel all-reduce (decode shapes, M <= 128):

@@ -94,7 +94,22 @@ __device__ __forceinline__ float act_combine(float g, float u, int mode, float l
   return (g / (1.f + __expf(-g))) * u;
 }
 
-// interleaved != 0: gate/up alternate per 128 columns ([g0..g127 | u0..u127 | g128.. ]), the layout
+// (cos, sin) of position * inv_freq for every row and rotary pair, rounded to BF16 like the rotation
+// kernels round them: computed once per step, read by every layer's fused QKV epilogue.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq_tab,
+                                  float2* __restrict__ out, int rows, int rhalf, int rot_dim, float theta) {
+  pdl_trigger();
+  pdl_wait();
+  const int gid = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= rows * rhalf) return;
+  const int row = gid / rhalf, i = gid - row * rhalf;
+  const float inv = inv_freq_tab ? inv_freq_tab[i] : 1.0f / powf(theta, (float)(2 * i) / (float)rot_dim);
+  float sn, cs;
+  sincosf((float)positions[row] * inv, &sn, &cs);
+  out[gid] = make_float2(bf16r(cs), bf16r(sn));
+}
+
+// interleaved != 0: gate/up alternate per 64 columns ([g0..g63 | u0..u63 | g64.. ]), the layout
 // produced by a weight fused for the GEMM's SwiGLU epilogue; otherwise [gate | up] halves.
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows,
                                 int f, int ldgu, int ldo, int mode, float limit, int interleaved) {
@@ -104,8 +119,8 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)rows * vec_per_row) return;
   const int row = (int)(gid / vec_per_row), c = (int)(gid % vec_per_row);
-  const int gc = interleaved ? ((c >> 4) * 32 + (c & 15)) : c;          // 16 vectors per 128 columns
-  const int uc = interleaved ? gc + 16 : c + vec_per_row;
+  const int gc = interleaved ? ((c >> 3) * 16 + (c & 7)) : c;           // 8 vectors per 64 columns
+  const int uc = interleaved ? gc + 8 : c + vec_per_row;
   const uint4 g = reinterpret_cast<const uint4*>(gu + (size_t)row * ldgu)[gc];
   const uint4 u = reinterpret_cast<const uint4*>(gu + (size_t)row * ldgu)[uc];
   const uint32_t* gp = reinterpret_cast<const uint32_t*>(&g);
@@ -336,10 +351,20 @@ FF_EXPORT int ff_rope_kv_paged(void* qkv, const int* positions, const int* slots
   return launch_result();
 }
 
+// out: float2 [rows, rot_dim/2]
+FF_EXPORT int ff_rope_table(const int* positions, const float* inv_freq, float* out, int rows, int rot_dim, float theta,
+                            cudaStream_t s) {
+  if (rows <= 0 || rot_dim <= 0 || rot_dim % 2) return FF_HOST_BAD_SHAPE;
+  const int rhalf = rot_dim / 2, total = rows * rhalf;
+  if (int lr_ = launch_pdl(rope_table_kernel, dim3((total + 127) / 128), dim3(128), 0, s, 0, positions, inv_freq,
+                           reinterpret_cast<float2*>(out), rows, rhalf, rot_dim, theta)) return lr_;
+  return launch_result();
+}
+
 FF_EXPORT int ff_silu_mul(const void* gu, void* out, int rows, int f, int ldgu, int ldo, int mode, float limit,
                           int interleaved, cudaStream_t s) {
   if (rows <= 0 || f <= 0 || f % 8 || ldgu % 8 || ldo % 8) return FF_HOST_BAD_SHAPE;
-  if (interleaved && f % 128) return FF_HOST_BAD_SHAPE;
+  if (interleaved && f % 64) return FF_HOST_BAD_SHAPE;
   const long long total = (long long)rows * (f / 8);
   if (int lr_ = launch_pdl(silu_mul_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows,
                                                                    f, ldgu, ldo, mode, limit, interleaved)) return lr_;

@@ -39,23 +39,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 
 
 def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, mode: int = 0) -> torch.Tensor:
-    """Fused gate/up projection + SwiGLU for a weight whose rows are interleaved per 128:
-    rows [256*t, 256*t+128) are gate rows for outputs [128*t, 128*t+128), the next 128 the
-    matching up rows."""
+    """Fused gate/up projection + SwiGLU for a weight whose rows are interleaved per 64:
+    rows [128*t, 128*t+64) are gate rows for outputs [64*t, 64*t+64), the next 64 the
+    matching up rows (one 128-row weight tile of the decode GEMM holds both)."""
     y = (x.to(torch.float64) @ w_interleaved.to(torch.float64).t()).to(F32)
     n = y.shape[-1]
-    y = y.view(*y.shape[:-1], n // 256, 2, 128)
+    y = y.view(*y.shape[:-1], n // 128, 2, 64)
     gate, up = y[..., 0, :], y[..., 1, :]
     gu = torch.cat([gate.reshape(*y.shape[:-3], -1), up.reshape(*y.shape[:-3], -1)], dim=-1).to(x.dtype)
     return silu_mul(gu, mode=mode)
 
 
 def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
-    """Build the per-128 interleaved [2f, h] weight used by the fused SwiGLU GEMM epilogue."""
+    """Build the per-64 interleaved [2f, h] weight used by the fused SwiGLU GEMM epilogues."""
     f, h = w_gate.shape
-    assert f % 128 == 0
-    g = w_gate.view(f // 128, 1, 128, h)
-    u = w_up.view(f // 128, 1, 128, h)
+    assert f % 64 == 0
+    g = w_gate.view(f // 64, 1, 64, h)
+    u = w_up.view(f // 64, 1, 64, h)
     return torch.cat([g, u], dim=1).reshape(2 * f, h).contiguous()
 
 

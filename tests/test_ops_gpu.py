@@ -70,6 +70,39 @@ def test_gemm_swiglu(m):
     _close(y, expect)
 
 
+@pytest.mark.parametrize("m,f,h", [(64, 14336, 1024), (7, 1024, 4096), (128, 2048, 512)])
+def test_decode_gemm_swiglu_epilogue_matches_unfused(m, f, h):
+    """The decode GEMM's SwiGLU epilogue (stream-K and cluster split-K decompositions) against GEMM
+    followed by the stand-alone activation kernel. The two GEMMs may split K differently (the fused
+    one uses 128-row tiles), so sums can differ in the last FP32 bit before rounding."""
+    x = _rand((m, h), 31)
+    wi = ref.interleave_gate_up(_rand((f, h), 32, 0.05), _rand((f, h), 33, 0.05))
+    fused = ops.linear_swiglu(x, wi)
+    unfused = ops.silu_mul_interleaved(ops.linear(x, wi))
+    ops.check_status()
+    _close(fused, unfused, 2e-2, 2e-2)
+    assert torch.equal(fused, ops.linear_swiglu(x, wi))
+
+
+@pytest.mark.parametrize("m,hq,hkv,h", [(64, 32, 8, 1024), (5, 4, 2, 4096), (128, 16, 16, 512)])
+def test_decode_gemm_rope_kv_epilogue_matches_unfused(m, hq, hkv, h):
+    d, bs, nb = 128, 64, 8
+    x = _rand((m, h), 34)
+    w = _rand(((hq + 2 * hkv) * d, h), 35, 0.05)
+    pos = torch.arange(50, 50 + m, dtype=torch.int32, device="cuda")
+    slots = (torch.arange(m, dtype=torch.int32) + 9).to("cuda")
+    slots[min(3, m - 1)] = -1
+    kc = torch.zeros(nb, hkv, bs, d, dtype=BF16, device="cuda"); vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    fused = ops.linear_rope_kv(x, w, pos, slots, kc, vc, hq, hkv, d, 5e5)
+    qkv = ops.linear(x, w)
+    ops.rope_kv_paged(qkv, pos, slots, kc2, vc2, hq, hkv, d, 5e5)
+    ops.check_status()
+    _close(fused, qkv, 2e-2, 2e-2)
+    _close(kc, kc2, 2e-2, 2e-2)
+    _close(vc, vc2, 2e-2, 2e-2)
+
+
 @pytest.mark.parametrize("rows,hidden", [(1, 4096), (64, 4096), (5, 7168), (3, 256), (2, 8192)])
 def test_norms(rows, hidden):
     x, res, w = _rand((rows, hidden), 12), _rand((rows, hidden), 13), _rand((hidden,), 14)
@@ -213,7 +246,7 @@ def test_sampler_matches_host_reference():
 def test_silu_mul_interleaved_layout():
     f, m = 512, 5
     g, u = _rand((m, f), 50, 2.0), _rand((m, f), 51, 2.0)
-    inter = torch.cat([g.view(m, f // 128, 1, 128), u.view(m, f // 128, 1, 128)], dim=2).reshape(m, 2 * f).contiguous()
+    inter = torch.cat([g.view(m, f // 64, 1, 64), u.view(m, f // 64, 1, 64)], dim=2).reshape(m, 2 * f).contiguous()
     got = ops.silu_mul(inter, interleaved=True)
     _close(got, ref.silu_mul(torch.cat([g, u], dim=1).cpu()), 1e-2, 1e-3)
 
