@@ -21,6 +21,12 @@ namespace ff {
 
 constexpr int HD = 128;             // head dim
 constexpr int PAGE = 64;            // tokens per cache block
+#ifndef DEC_WARPS
+#define DEC_WARPS 4                 // decode attention: warps per CTA (keys per warp = 64 / DEC_WARPS)
+#endif
+#ifndef DEC_STAGES
+#define DEC_STAGES 2                // decode attention: pages in flight per CTA + 1
+#endif
 constexpr float NEG_BIG = -3.0e38f;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
@@ -44,8 +50,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// byte offset of 16-byte chunk `c` of row `r` in a [rows][128] bf16 tile with XOR swizzle
-__device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)((r * 16 + (c ^ (r & 7))) * 16); }
+// A 64-row page tile [64][128] bf16 sits in shared memory as two halves of 64 dims, each [64 rows][128 bytes]
+// with the 16-byte chunk index XORed by row % 8: exactly what a TMA load of a {64 dims, 64 rows} box
+// with 128-byte swizzle writes, so the same tile can come from cp.async or from TMA.
+// Byte offset of 16-byte chunk `c` (0..15) of row `r`:
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  return (uint32_t)((c >> 3) * (PAGE * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
 
 // copy one page slice [nrows][128] bf16 from global to a swizzled smem tile, all `nthreads` threads
 __device__ __forceinline__ void load_tile_async(uint8_t* stile, const __nv_bfloat16* gsrc, int nrows, int tid,
@@ -76,14 +87,15 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[8][4], RowState& 
 #pragma unroll
   for (int i = 0; i < NT8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
   // S = Q K^T
+  // chunk = 2*kk + h with h = (lane >> 3) & 1: (chunk & 7) ^ (key & 7) = (2*(kk & 3)) ^ (h ^ (lane & 7))
+  const uint32_t kbase = sK + (uint32_t)(key_off + ((lane >> 4) << 3) + (lane & 7)) * 128u;
+  const uint32_t khx = ((lane >> 3) & 1) ^ (lane & 7);
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
 #pragma unroll
     for (int np = 0; np < NT8 / 2; ++np) {
-      const int key = key_off + np * 16 + ((lane >> 4) << 3) + (lane & 7);
-      const int chunk = kk * 2 + ((lane >> 3) & 1);
       uint32_t b0, b1, b2, b3;
-      ldmatrix_x4(sK + tile_off(key, chunk), b0, b1, b2, b3);
+      ldmatrix_x4(kbase + (uint32_t)(np * 16 * 128 + (kk >> 2) * (PAGE * 128)) + (((uint32_t)(2 * (kk & 3)) ^ khx) << 4), b0, b1, b2, b3);
       mma_bf16(s[2 * np], qf[kk], b0, b1);
       mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
     }
@@ -124,8 +136,11 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[8][4], RowState& 
   }
   st.l[0] = st.l[0] * a0 + rs0;   // per-thread partial row sums; quad-reduced at the end
   st.l[1] = st.l[1] * a1 + rs1;
+  // the running maxima settle after the first tiles: skip the 64 multiplications by exactly 1
+  if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) { st.o[i][0] *= a0; st.o[i][1] *= a0; st.o[i][2] *= a1; st.o[i][3] *= a1; }
+    for (int i = 0; i < 16; ++i) { st.o[i][0] *= a0; st.o[i][1] *= a0; st.o[i][2] *= a1; st.o[i][3] *= a1; }
+  }
   // O += P V
 #pragma unroll
   for (int ks = 0; ks < NT8 / 2; ++ks) {
@@ -134,12 +149,12 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[8][4], RowState& 
     pa[1] = pack_bf16x2(s[2 * ks][2], s[2 * ks][3]);
     pa[2] = pack_bf16x2(s[2 * ks + 1][0], s[2 * ks + 1][1]);
     pa[3] = pack_bf16x2(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+    const uint32_t vbase = sV + (uint32_t)(key_off + ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7)) * 128u;
+    const uint32_t vhx = (lane >> 4) ^ (lane & 7);
 #pragma unroll
     for (int dp = 0; dp < 8; ++dp) {
-      const int key = key_off + ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
-      const int chunk = dp * 2 + (lane >> 4);
       uint32_t b0, b1, b2, b3;
-      ldmatrix_x4_trans(sV + tile_off(key, chunk), b0, b1, b2, b3);
+      ldmatrix_x4_trans(vbase + (uint32_t)((dp >> 2) * (PAGE * 128)) + (((uint32_t)(2 * (dp & 3)) ^ vhx) << 4), b0, b1, b2, b3);
       mma_bf16(st.o[2 * dp], pa, b0, b1);
       mma_bf16(st.o[2 * dp + 1], pa, b2, b3);
     }
@@ -172,11 +187,14 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[8][4], const __nv_bf
 //   part_o     : fp32 [B][nsplit][nq*hq][128], part_ml : fp32 [B][nsplit][nq*hq][2]
 //   ctx_lens   : keys visible to the LAST query row of the sequence (includes the nq new tokens)
 //   tree_mask  : optional u64 [B][nq]; bit i of row r = key (ctx-nq+i) visible to row r
-// grid (nsplit, hkv, B), 128 threads, each warp owns 16 keys of every 64-key page.
+// grid (nsplit, hkv * row tiles, B), NW warps, each warp owns 64/NW keys of every 64-key page.
+// Measured on B200 (batch 64, context 1100, 32/8 heads): four 16-key warps 75.6 us, two 32-key warps
+// 80.3 us -- the wider warps issue fewer instructions per key but leave too few warps per SM.
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
-attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
-                   const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
+template <int NW>
+__global__ void __launch_bounds__(32 * NW)
+attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __nv_bfloat16* __restrict__ q, const int* __restrict__ block_table,
                    const int* __restrict__ ctx_lens, const unsigned long long* __restrict__ tree_mask,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
@@ -185,7 +203,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 0);
   pdl_wait();
   if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 1);
-  extern __shared__ __align__(1024) uint8_t smem[];
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled TMA destinations need 1024-byte alignment
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // blockIdx.y = row tile * hkv + kv head: nq * G packed rows are processed 16 at a time
   const int split = blockIdx.x, kvh = blockIdx.y % hkv, rt = blockIdx.y / hkv, b = blockIdx.z;
   const int G = hq / hkv;
@@ -213,25 +233,48 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   load_q_frags(qf, qp[0], qp[1]);
   RowState st; init_state(st);
 
-  uint8_t* sKbuf[2] = {smem, smem + 2 * PAGE * HD * 2};
-  uint8_t* sVbuf[2] = {smem + PAGE * HD * 2, smem + 3 * PAGE * HD * 2};
+  // DEC_STAGES stages of (K page, V page); thread 0 keeps DEC_STAGES-1 pages requested by TMA (four 8-KiB
+  // boxes each: K and V, low and high 64 dims) ahead of the page all warps work on
+  constexpr int STAGE_BYTES = 2 * PAGE * HD * 2;     // K page + V page
+  __shared__ uint64_t full_bar[DEC_STAGES];
+  __shared__ int abort_flag;
   bool bad = false;
+  // the block ids of this CTA's pages, fetched once by all threads: the page loop then issues its
+  // TMA loads without a dependent global load in front of each
+  __shared__ int sblk[128];
+  for (int i = threadIdx.x; i < 128 && p0 + i < p1; i += 32 * NW) sblk[i] = block_table[(size_t)b * max_blocks + p0 + i];
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < DEC_STAGES; ++i) mbar_init(&full_bar[i], 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
   auto issue = [&](int page_idx, int buf) {
-    int blk = block_table[(size_t)b * max_blocks + page_idx];
+    int blk = (page_idx - p0 < 128) ? sblk[page_idx - p0] : block_table[(size_t)b * max_blocks + page_idx];
     if (blk < 0 || blk >= num_blocks) { bad = true; blk = 0; }
-    const size_t base = ((size_t)blk * hkv + kvh) * PAGE * HD;
-    load_tile_async(sKbuf[buf], kcache + base, PAGE, threadIdx.x, 128);
-    load_tile_async(sVbuf[buf], vcache + base, PAGE, threadIdx.x, 128);
-    cp_async_commit();
+    const int row = (blk * hkv + kvh) * PAGE;
+    uint8_t* sk = smem + buf * STAGE_BYTES;
+    uint8_t* sv = sk + PAGE * HD * 2;
+    mbar_expect_tx(&full_bar[buf], STAGE_BYTES);
+    tma_load_2d(sk, &tmK, &full_bar[buf], 0, row);
+    tma_load_2d(sk + PAGE * 128, &tmK, &full_bar[buf], 64, row);
+    tma_load_2d(sv, &tmV, &full_bar[buf], 0, row);
+    tma_load_2d(sv + PAGE * 128, &tmV, &full_bar[buf], 64, row);
   };
-  if (p0 < p1) issue(p0, 0);
+  if (threadIdx.x == 0)
+    for (int i = 0; i < DEC_STAGES - 1 && p0 + i < p1; ++i) issue(p0 + i, i);
+  bool ok = true;
   for (int p = p0; p < p1; ++p) {
-    const int buf = (p - p0) & 1;
-    if (p + 1 < p1) { issue(p + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-    __syncthreads();
-    const int key0 = p * PAGE + warp * 16;
-    if (key0 < ctx)
-      warp_tile<2>(qf, st, smem_u32(sKbuf[buf]), smem_u32(sVbuf[buf]), warp * 16, key0, lim[0], lim[1],
+    const int it = p - p0, buf = it % DEC_STAGES;
+    const uint32_t ph = (it / DEC_STAGES) & 1;
+    // the stage refilled here was last read in iteration p-1, which every warp has left (barrier below)
+    if (threadIdx.x == 0 && p + DEC_STAGES - 1 < p1) issue(p + DEC_STAGES - 1, (it + DEC_STAGES - 1) % DEC_STAGES);
+    if (ok && !mbar_wait(&full_bar[buf], ph, &abort_flag, status, KID_ATTN_DECODE, 1)) ok = false;
+    constexpr int KPW = PAGE / NW;                     // keys per warp
+    const int key0 = p * PAGE + warp * KPW;
+    const uint32_t sk = smem_u32(smem + buf * STAGE_BYTES);
+    if (ok && key0 < ctx)
+      warp_tile<KPW / 8>(qf, st, sk, sk + PAGE * HD * 2, warp * KPW, key0, lim[0], lim[1],
                    tree_mask != nullptr, ctx - nq, mk[0], mk[1], scale_log2);
     __syncthreads();
   }
@@ -241,8 +284,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   float l0 = st.l[0], l1 = st.l[1];
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  float* so = reinterpret_cast<float*>(smem);              // [4 warps][16 rows][128]
-  float* sml = so + 4 * 16 * HD;                           // [4][16][2]
+  float* so = reinterpret_cast<float*>(smem);              // [NW warps][16 rows][128]
+  float* sml = so + NW * 16 * HD;                          // [NW][16][2]
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int d = i * 8 + 2 * t;
@@ -254,26 +297,26 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     sml[(warp * 16 + g + 8) * 2] = st.m[1]; sml[(warp * 16 + g + 8) * 2 + 1] = l1;
   }
   __syncthreads();
-  const int d = threadIdx.x;   // 128 threads = 128 dims
   for (int r = 0; r < rows_used; ++r) {
     const int rg = rt * 16 + r;
     float M = NEG_BIG;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, sml[(w * 16 + r) * 2]);
-    float L = 0.f, acc = 0.f;
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, sml[(w * 16 + r) * 2]);
+    float L = 0.f, sc[NW];
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float sc = exp2f(sml[(w * 16 + r) * 2] - M);
-      L += sml[(w * 16 + r) * 2 + 1] * sc;
-      acc += so[(w * 16 + r) * HD + d] * sc;
-    }
+    for (int w = 0; w < NW; ++w) { sc[w] = exp2f(sml[(w * 16 + r) * 2] - M); L += sml[(w * 16 + r) * 2 + 1] * sc[w]; }
     const int qi = rg / G, hh = kvh * G + rg % G;
-    if (nsplit == 1) {
-      out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
-    } else {
-      const size_t pr = ((size_t)b * nsplit + split) * (nq * hq) + (size_t)qi * hq + hh;
-      part_o[pr * HD + d] = acc;
-      if (d == 0) { part_ml[pr * 2] = M; part_ml[pr * 2 + 1] = L; }
+    for (int d = threadIdx.x; d < HD; d += 32 * NW) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) acc += so[(w * 16 + r) * HD + d] * sc[w];
+      if (nsplit == 1) {
+        out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+      } else {
+        const size_t pr = ((size_t)b * nsplit + split) * (nq * hq) + (size_t)qi * hq + hh;
+        part_o[pr * HD + d] = acc;
+        if (d == 0) { part_ml[pr * 2] = M; part_ml[pr * 2 + 1] = L; }
+      }
     }
   }
 }
@@ -380,7 +423,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 }  // namespace ff
 using namespace ff;
 
-constexpr int ATTN_SMEM = 4 * PAGE * HD * 2;   // 64 KiB: two stages of K and V pages
+constexpr int ATTN_SMEM = 4 * PAGE * HD * 2;   // 64 KiB: two stages of K and V pages (prefill)
+constexpr int DEC_SMEM = DEC_STAGES * 2 * PAGE * HD * 2 + 1024;
 
 // Number of KV splits the decode launcher will use and the scratch it needs.
 FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ctx, long long* part_o_bytes,
@@ -392,6 +436,7 @@ FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ct
   // costs little
   const int target = 148 * 3 * 4;
   if (ctas < target) nsplit = (target + ctas - 1) / ctas;
+  if (const char* ev = getenv("FF_ATTN_NSPLIT")) { const int v = atoi(ev); if (v > 0) nsplit = v; }
   if (nsplit > pages) nsplit = pages;
   if (nsplit < 1) nsplit = 1;
   if (nsplit > 64) nsplit = 64;
@@ -409,12 +454,18 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
   if (ldq % 8 || nsplit < 1) return FF_HOST_BAD_ALIGN;
   if (nsplit > 1 && (!part_o || !part_ml)) return FF_HOST_BAD_SHAPE;
   static bool attr = false;
-  if (!attr) { if (int r = opt_in_smem(attn_decode_kernel, ATTN_SMEM)) return r; attr = true; }
+  constexpr int NW = DEC_WARPS;
+  if (!attr) { if (int r = opt_in_smem(attn_decode_kernel<NW>, DEC_SMEM)) return r; attr = true; }
   const float scale_log2 = scale * 1.4426950408889634f;
   const int row_tiles = (nq * (hq / hkv) + 15) / 16;
   dim3 grid(nsplit, hkv * row_tiles, batch);
-  if (int lr_ = launch_pdl(attn_decode_kernel, dim3(grid), dim3(128), ATTN_SMEM, s, 0, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache,
-      (const __nv_bfloat16*)vcache, block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
+  // the caches as [blocks * hkv * 64 rows][128]; a box is one half (64 dims) of one page of one head
+  CUtensorMap tmK, tmV;
+  const uint64_t cache_rows = (uint64_t)num_blocks * hkv * PAGE;
+  if (int r = make_tmap_2d(&tmK, kcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, HD, cache_rows, HD * 2, 64, PAGE)) return r;
+  if (int r = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, HD, cache_rows, HD * 2, 64, PAGE)) return r;
+  if (int lr_ = launch_pdl(attn_decode_kernel<NW>, dim3(grid), dim3(32 * NW), DEC_SMEM, s, 0, tmK, tmV, (const __nv_bfloat16*)q,
+      block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
       ldq, max_blocks, num_blocks, nsplit, scale_log2, status)) return lr_;
   if (int r = launch_result()) return r;
   if (nsplit > 1) {
