@@ -52,14 +52,18 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 // epi: 0 = store bf16; 1 = SwiGLU (every 128 columns of a tile are 64 gate then the matching 64 up columns; output
 // has N/2 columns); 2 = store fp32.
 // COMM (tensor-parallel prefill, rows split evenly over the ranks in 128-row blocks):
-//   1 = all-gather -> GEMM : A is row-sharded. The epilogue warps first push this rank's shard into
-//       every peer's arena (peer stores, one flag per 128-row block), the TMA producer waits for
-//       the block's flag before loading it from the LOCAL arena copy; own rows are scheduled first
-//       so the transfer of the other shards overlaps the math.
-//   2 = GEMM -> reduce-scatter : every finished tile is stored straight into the arena slot of the
-//       rank that owns those rows (peer stores from the epilogue); when all column tiles of a row
-//       block are out, its flag goes to the owner. After its tiles a CTA reduces owned row blocks:
-//       waits for the block's flags from all ranks and sums the slots in rank order.
+//   1 = all-gather -> GEMM : A is row-sharded. Four extra warps per CTA (all CTAs together) push this
+//       rank's shard into every peer's arena with plain peer stores, a quarter of a 128-row block at a
+//       time, eight 16-byte vectors in flight per thread; the CTA that completes a block (counter)
+//       flags it on every peer. The TMA producer reads own rows straight from the shard and the other
+//       ranks' rows from the LOCAL arena copy once the block's flag is there; own rows are scheduled
+//       first so the transfer overlaps the math.
+//   2 = GEMM -> reduce-scatter : every finished tile goes into the arena slot of the rank that owns
+//       those rows. The epilogue stages 64 columns at a time through shared memory so that each row
+//       leaves as 128 contiguous bytes (16-byte peer stores scattered over rows waste most of a
+//       NVLink packet); when all column tiles of a row block are out, its flag goes to the owner.
+//       After its tiles every CTA reduces quarter row blocks this rank owns: waits for the block's
+//       flags from all ranks and sums the slots in rank order.
 struct CommArgs {
   PeerArena ar;
   int rows_per_rank;                  // multiple of 128; M == rows_per_rank * world
@@ -77,10 +81,12 @@ __device__ __forceinline__ int comm_tm(int tm, int tiles_per_rank, int rank, int
   return ((rank + j) % world) * tiles_per_rank + r;
 }
 
+constexpr int COMM_PARTS = 4;       // a 128-row block is pushed (COMM 1) / reduced (COMM 2) in this many pieces
+
 template <int BN, int STAGES, int COMM>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(COMM == 1 ? 320 : 192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA1,
-                 const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout, int M, int N, int K, int ldc, int epi,
+                 const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout, int M, int N, int K, int ldc, int epi,
                  int* status, CommArgs ca) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
@@ -120,7 +126,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
         tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world);
         const int src = tm / tiles_per_rank, rb = tm - src * tiles_per_rank;
-        if (COMM == 1) {
+        if (COMM == 1 && src != ca.ar.rank) {
           // the rows of this tile must have arrived in the local arena copy
           if (!wait_flag(arena_flag(ca.ar, ca.ar.rank, src, rb), epoch, status, KID_AG_GEMM, src)) {
             bars.abort_flag = 1; ok = false; break;
@@ -132,7 +138,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag, status, KID_GEMM_BF16, 1)) { ok = false; break; }
           mbar_expect_tx(&bars.full[s], STAGE_BYTES);
           uint8_t* sa = smem + s * STAGE_BYTES;
-          if (COMM == 1) tma_load_3d(sa, parity ? &tmA1 : &tmA, &bars.full[s], kb * BK, rb * BM, src);
+          if (COMM == 1 && src == ca.ar.rank) tma_load_2d(sa, &tmX, &bars.full[s], kb * BK, rb * BM);
+          else if (COMM == 1) tma_load_3d(sa, parity ? &tmA1 : &tmA, &bars.full[s], kb * BK, rb * BM, src);
           else tma_load_2d(sa, &tmA, &bars.full[s], kb * BK, tm * BM);
           tma_load_2d(sa + A_BYTES, &tmB, &bars.full[s], kb * BK, tn * BN);
         }
@@ -165,31 +172,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (ok) umma_commit(&bars.tmem_full[acc]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // epilogue warps 2..5 ; TMEM lane quarter = warp % 4
     const int q = warp & 3;
     const int e = (warp - 2) * 32 + lane;
     uint32_t tile_it = 0;
     bool ok = true;
-    if (COMM == 1) {
-      // push my activation shard, 128-row block by block, to every rank (myself included)
-      const int kvec = K >> 3;
-      for (int rb = blockIdx.x; rb < tiles_per_rank; rb += gridDim.x) {
-        for (int pi = 0; pi < ca.ar.world; ++pi) {
-          const int p = (ca.ar.rank + pi) % ca.ar.world;
-          uint4* dst = reinterpret_cast<uint4*>(arena_slot(ca.ar, p, parity, ca.ar.rank)) + (size_t)rb * BM * kvec;
-          for (int idx = e; idx < BM * kvec; idx += 128) {
-            const int r = idx / kvec, c = idx - r * kvec;
-            dst[idx] = reinterpret_cast<const uint4*>(ca.x_shard + (size_t)(rb * BM + r) * ca.ldx)[c];
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (e == 0) {
-          __threadfence_system();
-          for (int p = 0; p < ca.ar.world; ++p) st_release_sys(arena_flag(ca.ar, p, ca.ar.rank, rb), epoch);
-        }
-      }
-    }
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
       int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
       tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world);
@@ -255,11 +243,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + (size_t)row * ldc + (size_t)tn * BN;
         if (COMM == 2) {
-          // the rows of this tile belong to rank `owner`: store into its arena slot for source = me
+          // the rows of this tile belong to rank `owner`: they go into its arena slot for source = me,
+          // 64 columns at a time through a warp-private staging tile [32 rows][128 bytes] (16-byte
+          // chunks XORed by row % 8) so that eight lanes write one row's 128 contiguous bytes
           const int owner = tm / tiles_per_rank;
-          crow = reinterpret_cast<__nv_bfloat16*>(arena_slot(ca.ar, owner, parity, ca.ar.rank)) +
-                 (size_t)(row - owner * ca.rows_per_rank) * N + (size_t)tn * BN;
-        }
+          __nv_bfloat16* tile_dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ca.ar, owner, parity, ca.ar.rank)) +
+                                    (size_t)(tm * BM + q * 32 - owner * ca.rows_per_rank) * N + (size_t)tn * BN;
+          uint4* stg = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + q * 4096);
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 64) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t r[32];
+              tmem_ld_x32(taddr + c + 32 * h, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                stg[lane * 8 + ((4 * h + j) ^ (lane & 7))] =
+                    make_uint4(pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1])),
+                               pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                               pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                               pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int it8 = 0; it8 < 8; ++it8) {
+              const int rr = 4 * it8 + (lane >> 3), ch = lane & 7;
+              const int col = tn * BN + c + ch * 8;
+              if (tm * BM + q * 32 + rr < M && col < N)
+                *reinterpret_cast<uint4*>(tile_dst + (size_t)rr * N + c + ch * 8) = stg[rr * 8 + (ch ^ (rr & 7))];
+            }
+            __syncwarp();
+          }
+        } else
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -300,30 +316,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     if (COMM == 2 && ok) {
-      // reduce the row blocks this rank owns: slots of all source ranks, in rank order
+      // reduce the row blocks this rank owns, a quarter block per step and CTA: slots of all source
+      // ranks, in rank order, four 16-byte vectors of every slot in flight per thread
       const int nvec = N >> 3;
-      for (int i = blockIdx.x; i < tiles_per_rank; i += gridDim.x) {
+      const int blk_vecs = BM * nvec, piece = (blk_vecs + COMM_PARTS - 1) / COMM_PARTS;
+      for (int part = blockIdx.x; part < tiles_per_rank * COMM_PARTS; part += gridDim.x) {
+        const int i = part / COMM_PARTS, ps = part - i * COMM_PARTS;
         if (e == 0) bars.is_last = 1;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (e < ca.ar.world)
           if (!wait_flag(arena_flag(ca.ar, ca.ar.rank, e, i), epoch, status, KID_GEMM_RS, e)) bars.is_last = 0;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (bars.is_last) {
-          for (int idx = e; idx < BM * nvec; idx += 128) {
-            const size_t off = (size_t)i * BM * nvec + idx;
-            float a8[8];
+          const int v0 = ps * piece, v1 = min(blk_vecs, v0 + piece);
+          for (int base = v0 + e; base < v1; base += 128 * 4) {
+            float a8[4][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a8[j] = 0.f;
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int j = 0; j < 8; ++j) a8[u][j] = 0.f;
             for (int r = 0; r < ca.ar.world; ++r) {
-              const uint4 d = reinterpret_cast<const uint4*>(arena_slot(ca.ar, ca.ar.rank, parity, r))[off];
-              const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d);
+              const uint4* slot = reinterpret_cast<const uint4*>(arena_slot(ca.ar, ca.ar.rank, parity, r)) + (size_t)i * blk_vecs;
+              uint4 d[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[2 * j] += f.x; a8[2 * j + 1] += f.y; }
+              for (int u = 0; u < 4; ++u) d[u] = (base + 128 * u < v1) ? slot[base + 128 * u] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d[u]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[u][2 * j] += f.x; a8[u][2 * j + 1] += f.y; }
+              }
             }
-            uint4 o;
-            o.x = pack_bf16x2(a8[0], a8[1]); o.y = pack_bf16x2(a8[2], a8[3]);
-            o.z = pack_bf16x2(a8[4], a8[5]); o.w = pack_bf16x2(a8[6], a8[7]);
-            reinterpret_cast<uint4*>(ca.rs_out)[off] = o;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (base + 128 * u < v1) {
+                uint4 o;
+                o.x = pack_bf16x2(a8[u][0], a8[u][1]); o.y = pack_bf16x2(a8[u][2], a8[u][3]);
+                o.z = pack_bf16x2(a8[u][4], a8[u][5]); o.w = pack_bf16x2(a8[u][6], a8[u][7]);
+                reinterpret_cast<uint4*>(ca.rs_out)[(size_t)i * blk_vecs + base + 128 * u] = o;
+              }
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -336,6 +367,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         *arena_done(ca.ar) = 0;
         __threadfence();
         *reinterpret_cast<volatile int*>(arena_epoch(ca.ar)) = epoch;
+      }
+    }
+  }
+
+  if (COMM == 1 && warp >= 6) {
+    // ---- communication warps 6..9: push this rank's shard to every peer --------------------------
+    const int ce = threadIdx.x - 192;                    // 0..127
+    const int kvec = K >> 3;
+    const int blk_vecs = BM * kvec, piece = (blk_vecs + COMM_PARTS - 1) / COMM_PARTS;
+    for (int part = blockIdx.x; part < tiles_per_rank * COMM_PARTS; part += gridDim.x) {
+      const int rb = part / COMM_PARTS, ps = part - rb * COMM_PARTS;
+      const int v0 = ps * piece, v1 = min(blk_vecs, v0 + piece);
+      for (int pi = 1; pi < ca.ar.world; ++pi) {
+        const int p = (ca.ar.rank + pi) % ca.ar.world;
+        uint4* dst = reinterpret_cast<uint4*>(arena_slot(ca.ar, p, parity, ca.ar.rank)) + (size_t)rb * blk_vecs;
+        for (int base = v0 + ce; base < v1; base += 128 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int idx = base + 128 * j;
+            if (idx < v1) {
+              const int r = idx / kvec, c = idx - r * kvec;
+              v[j] = reinterpret_cast<const uint4*>(ca.x_shard + (size_t)(rb * BM + r) * ca.ldx)[c];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) if (base + 128 * j < v1) dst[base + 128 * j] = v[j];
+        }
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ce == 0) {
+        __threadfence_system();
+        const int prev = atomicAdd(&ca.tile_counters[rb], 1);
+        if (prev == COMM_PARTS - 1) {                      // the last piece of this row block is out
+          ca.tile_counters[rb] = 0;
+          __threadfence_system();
+          for (int pi = 1; pi < ca.ar.world; ++pi)
+            st_release_sys(arena_flag(ca.ar, (ca.ar.rank + pi) % ca.ar.world, ca.ar.rank, rb), epoch);
+        }
       }
     }
   }
@@ -379,7 +449,7 @@ FF_EXPORT int ff_gemm_bf16(const void* X, const void* W, void* Y, int M, int N, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   CommArgs none = {};
-  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmB, Y, M, N, K, ldy, epi, status, none);
+  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmA, tmB, Y, M, N, K, ldy, epi, status, none);
   return launch_result();
 }
 
@@ -399,7 +469,7 @@ static int fill_comm(CommArgs& ca, const unsigned long long* ptrs, int rank, int
 // Y[M, N] = gather(X_shards)[M, K] · W[N, K]ᵀ, X_shard = this rank's rows [M/world, K].
 FF_EXPORT int ff_ag_gemm(const unsigned long long* ptrs, int rank, int world, long long half_bytes, long long slot_bytes,
                          const void* x_shard, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
-                         int epi, int* status, cudaStream_t stream) {
+                         int epi, int* block_counters, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return FF_HOST_BAD_SHAPE;
   if (epi == 1 && (N % 256)) return FF_HOST_BAD_SHAPE;
   if (epi == 2) return FF_HOST_UNSUPPORTED;
@@ -408,9 +478,13 @@ FF_EXPORT int ff_ag_gemm(const unsigned long long* ptrs, int rank, int world, lo
   CommArgs ca = {};
   int r = fill_comm(ca, ptrs, rank, world, half_bytes, slot_bytes, M, (long long)(M / world) * K * 2);
   if (r) return r;
+  if (!block_counters) return FF_HOST_BAD_SHAPE;
   ca.x_shard = reinterpret_cast<const __nv_bfloat16*>(x_shard); ca.ldx = ldx;
+  ca.tile_counters = block_counters;          // one int32 per 128-row block of the shard, zero between launches
   constexpr int BN = 256, STAGES = 4;
-  CUtensorMap tmA0, tmA1, tmB;
+  CUtensorMap tmA0, tmA1, tmX, tmB;
+  r = make_tmap_2d(&tmX, x_shard, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, ca.rows_per_rank, (uint64_t)ldx * 2, BK, BM);
+  if (r) return r;
   uint8_t* data = reinterpret_cast<uint8_t*>(ptrs[rank]) + DATA_OFF;
   r = make_tmap_3d(&tmA0, data, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, ca.rows_per_rank, world, (uint64_t)K * 2,
                    (uint64_t)slot_bytes, BK, BM, 1);
@@ -426,7 +500,7 @@ FF_EXPORT int ff_ag_gemm(const unsigned long long* ptrs, int rank, int world, lo
   if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 192, smem, stream>>>(tmA0, tmA1, tmB, Y, M, N, K, ldy, epi, status, ca);
+  kern<<<grid, 320, smem, stream>>>(tmA0, tmA1, tmX, tmB, Y, M, N, K, ldy, epi, status, ca);
   return launch_result();
 }
 
@@ -447,13 +521,13 @@ FF_EXPORT int ff_gemm_rs(const unsigned long long* ptrs, int rank, int world, lo
   if (r) return r;
   r = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, BK, BN);
   if (r) return r;
-  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * 4096 + 1024;   // + staging tiles of the epilogue warps
   auto kern = gemm_bf16_kernel<BN, STAGES, 2>;
   static bool attr_done = false;
   if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmB, nullptr, M, N, K, N, 0, status, ca);
+  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmA, tmB, nullptr, M, N, K, N, 0, status, ca);
   return launch_result();
 }
 

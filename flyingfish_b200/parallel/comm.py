@@ -173,7 +173,8 @@ class TPComm:
         out = torch.empty(m, n // 2 if swiglu else n, dtype=torch.bfloat16, device=x_shard.device)
         rc = oplib.kernels().ff_ag_gemm(*self.arena.args(), oplib.ptr(x_shard), oplib.ptr(w), oplib.ptr(out), m, n, k,
                                         x_shard.stride(0), w.stride(0), out.stride(0), 1 if swiglu else 0,
-                                        oplib.ptr(oplib.status_tensor(x_shard.device)), oplib.stream_ptr())
+                                        oplib.ptr(self.tile_counters), oplib.ptr(oplib.status_tensor(x_shard.device)),
+                                        oplib.stream_ptr())
         oplib.check(rc, "ff_ag_gemm")
         self.stats["ag_gemm"] += 1
         ops._count()

@@ -90,7 +90,8 @@ def test_tp2_sequence_parallel_fused_prefill(tmp_path):
         pytest.skip("needs 2 GPUs")
     res = _launch(2, "cuda", "sp", tmp_path, 29516)
     assert res["ok"], res["errs"]
-    assert res["stats"]["ag_gemm"] > 18 and res["stats"]["gemm_rs"] > 18, "the model's prefill must take the fused path"
+    # nine direct calls of each kernel above; anything beyond that comes from the model's prefill
+    assert res["stats"]["ag_gemm"] > 9 and res["stats"]["gemm_rs"] > 9, "the model's prefill must take the fused path"
     from flyingfish_b200.api import Model
     from flyingfish_b200.config import Settings
     m = Model.load("tiny-llama", Settings(capacity=1024, max_batch=4, graph=False), device="cuda", seed=0)
