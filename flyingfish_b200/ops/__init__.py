@@ -73,7 +73,9 @@ class _Workspace:
         self.attn_ml = torch.empty(1 << 18, dtype=torch.float32, device=device)
 
     def ensure(self, name: str, numel: int) -> torch.Tensor:
-        t = getattr(self, name)
+        t = getattr(self, name, None)
+        if t is None:                      # scratch of an optional operator family: FP32, created on first use
+            t = torch.empty(0, dtype=torch.float32, device=self.device)
         if t.numel() < numel:
             _require(not torch.cuda.is_current_stream_capturing(), f"workspace {name} too small during graph capture")
             t = torch.empty(int(numel * 1.25), dtype=t.dtype, device=self.device)
