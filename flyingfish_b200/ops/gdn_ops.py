@@ -1,0 +1,72 @@
+"""Gated DeltaNet operators: depthwise causal conv + SiLU with carried history, q/k preparation, and the
+recurrent state update. CUDA: ``csrc/gdn.cu``; CPU: FP32 oracles (reference: kernels/gdn/gdn_conv.cu:1-8,
+gdn_prep.cu:1-4, gdn_recurrent.cuh:1-16)."""
+from __future__ import annotations
+
+from ctypes import c_float
+
+import torch
+
+from . import _count
+from .lib import check, kernels, ptr, stream_ptr
+
+BF16 = torch.bfloat16
+D = 128
+
+
+def conv(x: torch.Tensor, weight: torch.Tensor, history: torch.Tensor, commit: bool = True) -> torch.Tensor:
+    """x [rows, channels] bf16 (rows of one sequence in order), weight [channels, 4] bf16, history
+    [channels, 3] f32 (updated in place when ``commit``)."""
+    rows, ch = x.shape
+    if not x.is_cuda:
+        full = torch.cat([history.t(), x.float()], dim=0)                          # [3 + rows, ch]
+        w = weight.float()
+        acc = sum(full[t: t + rows] * w[:, t] for t in range(4))
+        y = acc.to(BF16).float()
+        out = (y * torch.sigmoid(y)).to(BF16)
+        if commit:
+            history.copy_(full[rows: rows + 3].t())
+        return out
+    out = torch.empty_like(x)
+    check(kernels().ff_gdn_conv(ptr(x), ptr(weight), ptr(history), ptr(out), rows, ch, int(commit), stream_ptr()), "ff_gdn_conv")
+    _count()
+    return out
+
+
+def prep(conv_out: torch.Tensor, heads: int, kheads: int, eps: float = 1e-6):
+    """conv_out [rows, (2*kheads + heads) * 128] bf16 -> q, k, v [rows, heads, 128] f32."""
+    rows = conv_out.shape[0]
+    if not conv_out.is_cuda:
+        x = conv_out.float()
+        qk = x[:, : 2 * kheads * D].reshape(rows, 2, kheads, D)
+        rep = heads // kheads
+        q = qk[:, 0].repeat_interleave(rep, dim=1); k = qk[:, 1].repeat_interleave(rep, dim=1)
+        q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + eps) * (D ** -0.5)
+        k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + eps)
+        return q.contiguous(), k.contiguous(), x[:, 2 * kheads * D:].reshape(rows, heads, D).contiguous()
+    q = torch.empty(rows, heads, D, dtype=torch.float32, device=conv_out.device); k = torch.empty_like(q); v = torch.empty_like(q)
+    check(kernels().ff_gdn_prep(ptr(conv_out), ptr(q), ptr(k), ptr(v), rows, heads, kheads, c_float(eps), stream_ptr()), "ff_gdn_prep")
+    _count()
+    return q, k, v
+
+
+def recurrent(q, k, v, beta, g, state: torch.Tensor, row_start: torch.Tensor) -> torch.Tensor:
+    """q, k, v [rows, heads, 128] f32, beta / g [rows, heads] f32, state [sequences, heads, 128, 128] f32 (updated
+    in place), row_start [sequences + 1] int32 -> out [rows, heads, 128] bf16."""
+    rows, heads, _ = q.shape
+    if not q.is_cuda:
+        out = torch.zeros(rows, heads, D)
+        for s in range(row_start.numel() - 1):
+            for r in range(int(row_start[s]), int(row_start[s + 1])):
+                S = state[s] * torch.exp(g[r])[:, None, None]
+                kv = torch.einsum("hk,hkv->hv", k[r], S)
+                delta = (v[r] - kv) * beta[r][:, None]
+                S = S + k[r][:, :, None] * delta[:, None, :]
+                out[r] = torch.einsum("hk,hkv->hv", q[r], S)
+                state[s] = S
+        return out.to(BF16)
+    out = torch.empty(rows, heads, D, dtype=BF16, device=q.device)
+    check(kernels().ff_gdn_recurrent(ptr(q), ptr(k), ptr(v), ptr(beta), ptr(g), ptr(state), ptr(out), ptr(row_start),
+                                     row_start.numel() - 1, heads, stream_ptr()), "ff_gdn_recurrent")
+    _count()
+    return out
