@@ -164,7 +164,33 @@ argmax_rows_kernel(const T* __restrict__ logits, int* __restrict__ out_ids, floa
   float best = -INFINITY; int bi = 0x7fffffff;
   bool nonfinite = false;
   const T* p = logits + (size_t)row * ld;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  int i0 = 0;
+  if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    // 16-byte vectors, two in flight per thread: a row of 128 K logits is 256 KB read by one CTA
+    const int nvec = vocab >> 3;
+    const uint4* pv = reinterpret_cast<const uint4*>(p);
+    for (int i = threadIdx.x; i < nvec; i += 2 * blockDim.x) {
+      uint4 u[2];
+      u[0] = pv[i];
+      const bool second = i + blockDim.x < nvec;
+      u[1] = second ? pv[i + blockDim.x] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (h == 1 && !second) break;
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&u[h]);
+        const int base = (i + h * blockDim.x) * 8;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          if (!(fabsf(f.x) <= 3.4e38f) || !(fabsf(f.y) <= 3.4e38f)) nonfinite = true;
+          if (f.x > best || (f.x == best && base + 2 * j < bi)) { best = f.x; bi = base + 2 * j; }
+          if (f.y > best || (f.y == best && base + 2 * j + 1 < bi)) { best = f.y; bi = base + 2 * j + 1; }
+        }
+      }
+    }
+    i0 = nvec << 3;
+  }
+  for (int i = i0 + threadIdx.x; i < vocab; i += blockDim.x) {
     const float v = to_f<T>(p[i]);
     if (!(fabsf(v) <= 3.4e38f)) nonfinite = true;
     if (v > best || (v == best && i < bi)) { best = v; bi = i; }
