@@ -71,6 +71,7 @@ class _Workspace:
         self.gemm_counters = torch.zeros(4096, dtype=torch.int32, device=device)
         self.attn_o = torch.empty(4 << 20, dtype=torch.float32, device=device)             # 16 MiB
         self.attn_ml = torch.empty(1 << 18, dtype=torch.float32, device=device)
+        self.attn_counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)     # one per (sequence, kv head, row tile)
 
     def ensure(self, name: str, numel: int) -> torch.Tensor:
         t = getattr(self, name, None)
@@ -102,6 +103,7 @@ SKINNY_MAX_M = 128
 # decode-shape epilogue fusions (FLYINGFISH_FUSE_SWIGLU=0 / FLYINGFISH_FUSE_ROPE=0 fall back to separate kernels)
 FUSE_SWIGLU = os.environ.get("FLYINGFISH_FUSE_SWIGLU", "1") != "0"
 FUSE_ROPE = os.environ.get("FLYINGFISH_FUSE_ROPE", "1") != "0"
+FUSE_ATTN_MERGE = os.environ.get("FLYINGFISH_FUSE_ATTN_MERGE", "0") == "1"
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
@@ -412,11 +414,15 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, blo
         out = torch.empty(rows, hq * dim, dtype=BF16, device=q.device)
     if tree_mask is not None:
         _require(tree_mask.dtype == torch.int64 and tree_mask.numel() == batch * nq, "attn_decode: tree mask int64")
+    # optionally the last split of a (sequence, kv head, row tile) merges in place of a second kernel; measured
+    # slower on B200 (81.8 vs 75.6 us at batch 64 / context 1100: every CTA pays a fence and an atomic), so off
+    items = batch * hkv * ((nq * (hq // hkv) + 15) // 16)
+    counters = ws.attn_counters if (FUSE_ATTN_MERGE and nsplit > 1 and items <= ws.attn_counters.numel()) else None
     rc = lib.ff_attn_decode(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(tree_mask),
                             ptr(out), ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, nq, ldq, block_table.shape[1],
-                            nb, nsplit, c_float(scale), ptr(status_tensor(q.device)), stream_ptr())
+                            nb, nsplit, c_float(scale), ptr(counters), ptr(status_tensor(q.device)), stream_ptr())
     check(rc, "ff_attn_decode")
-    _count(2 if nsplit > 1 else 1)
+    _count(1 if (nsplit == 1 or counters is not None) else 2)
     return out
 
 

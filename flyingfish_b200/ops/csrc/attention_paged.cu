@@ -198,7 +198,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                    const int* __restrict__ ctx_lens, const unsigned long long* __restrict__ tree_mask,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
-                   int* status) {
+                   int* status, int* __restrict__ split_counters) {
   pdl_trigger();
   if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 0);
   pdl_wait();
@@ -316,6 +316,38 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const size_t pr = ((size_t)b * nsplit + split) * (nq * hq) + (size_t)qi * hq + hh;
         part_o[pr * HD + d] = acc;
         if (d == 0) { part_ml[pr * 2] = M; part_ml[pr * 2 + 1] = L; }
+      }
+    }
+  }
+  if (nsplit > 1 && split_counters != nullptr) {
+    // the split that arrives last merges the partials of this (sequence, kv head, row tile): no second launch
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    const int item = b * gridDim.y + blockIdx.y;
+    if (threadIdx.x == 0) {
+      const int prev = atomicAdd(&split_counters[item], 1);
+      s_last = (prev == nsplit - 1);
+      if (s_last) split_counters[item] = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int r = 0; r < rows_used; ++r) {
+        const int rg = rt * 16 + r, qi = rg / G, hh = kvh * G + rg % G;
+        const size_t row = (size_t)qi * hq + hh;
+        float M = NEG_BIG;
+        for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, __ldcg(&part_ml[(((size_t)b * nsplit + sp) * (nq * hq) + row) * 2]));
+        for (int d = threadIdx.x; d < HD; d += 32 * NW) {
+          float L = 0.f, acc = 0.f;
+          for (int sp = 0; sp < nsplit; ++sp) {
+            const size_t pr = ((size_t)b * nsplit + sp) * (nq * hq) + row;
+            const float sc = exp2f(__ldcg(&part_ml[pr * 2]) - M);
+            L += __ldcg(&part_ml[pr * 2 + 1]) * sc;
+            acc += __ldcg(&part_o[pr * HD + d]) * sc;
+          }
+          out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+        }
       }
     }
   }
@@ -448,7 +480,7 @@ FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ct
 FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcache, const int* block_table,
                              const int* ctx_lens, const unsigned long long* tree_mask, void* out, float* part_o,
                              float* part_ml, int batch, int hq, int hkv, int head_dim, int nq, int ldq, int max_blocks,
-                             int num_blocks, int nsplit, float scale, int* status, cudaStream_t s) {
+                             int num_blocks, int nsplit, float scale, int* split_counters, int* status, cudaStream_t s) {
   if (head_dim != HD || batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv) return FF_HOST_BAD_SHAPE;
   if (nq < 1 || nq > 64) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || nsplit < 1) return FF_HOST_BAD_ALIGN;
@@ -466,9 +498,9 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
   if (int r = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, HD, cache_rows, HD * 2, 64, PAGE)) return r;
   if (int lr_ = launch_pdl(attn_decode_kernel<NW>, dim3(grid), dim3(32 * NW), DEC_SMEM, s, 0, tmK, tmV, (const __nv_bfloat16*)q,
       block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
-      ldq, max_blocks, num_blocks, nsplit, scale_log2, status)) return lr_;
+      ldq, max_blocks, num_blocks, nsplit, scale_log2, status, split_counters)) return lr_;
   if (int r = launch_result()) return r;
-  if (nsplit > 1) {
+  if (nsplit > 1 && split_counters == nullptr) {
     if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * nq * hq), dim3(128), 0, s, 0, part_o, part_ml, (__nv_bfloat16*)out, nq * hq, nsplit)) return lr_;
     return launch_result();
   }
