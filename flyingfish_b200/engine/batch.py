@@ -55,6 +55,7 @@ class ForwardBatch:
         self.max_ctx = 0
         self.n_logit_rows = 0
         self.use_tree_mask = False
+        self._bt_sig: list = []           # block list last written to each block-table row of the host buffer
 
     # -- device views (fixed addresses) ------------------------------------------------------
     def _v(self, off: int, n: int) -> torch.Tensor:
@@ -108,10 +109,22 @@ class ForwardBatch:
         self.n_logit_rows = len(logit_rows)
         h[L.logit_rows: L.logit_rows + len(logit_rows)] = torch.as_tensor(logit_rows, dtype=torch.int32)
         bt = h[L.block_table: L.block_table + L.max_batch * L.max_blocks].view(L.max_batch, L.max_blocks)
+        # a decode batch keeps the same sequences in the same rows for many steps and a block list changes only when
+        # a sequence crosses a block boundary: rows whose list is unchanged are not rewritten (the pinned buffer
+        # still holds them), which takes most of the host time out of a decode step
+        sig = self._bt_sig
         for i, row in enumerate(block_rows):
-            n = len(row)
+            t = tuple(row)
+            if i < len(sig) and sig[i] == t:
+                continue
+            n = len(t)
             assert n <= L.max_blocks
-            bt[i, :n] = torch.as_tensor(row, dtype=torch.int32)
+            if n:
+                bt[i, :n] = torch.as_tensor(t, dtype=torch.int32)
+            if i < len(sig):
+                sig[i] = t
+            else:
+                sig.extend([None] * (i - len(sig)) + [t])
         self.max_q_len = int(max(q_lens)) if batch else 0
         self.max_ctx = int(max(ctx_lens)) if batch else 0
         self.use_tree_mask = tree_mask is not None
