@@ -137,7 +137,7 @@ FF_EXPORT int ff_arena_max_flags() { return MAX_FLAGS; }
 FF_EXPORT int ff_allreduce_oneshot(const unsigned long long* ptrs, int rank, int world, long long half_bytes,
                                    long long slot_bytes, const void* x, void* out, long long numel, int* status,
                                    cudaStream_t s) {
-  PeerArena a;
+  PeerArena a = {};
   if (int r = fill_arena(a, ptrs, rank, world, half_bytes, slot_bytes)) return r;
   if (numel <= 0 || numel % 8 || numel * 2 > slot_bytes) return FF_HOST_TOO_LARGE;
   const long long nvec = numel / 8;
@@ -153,7 +153,7 @@ FF_EXPORT int ff_allreduce_oneshot(const unsigned long long* ptrs, int rank, int
 
 FF_EXPORT int ff_allgather_push(const unsigned long long* ptrs, int rank, int world, long long half_bytes,
                                 long long slot_bytes, const void* x, void* out, int bytes, int* status, cudaStream_t s) {
-  PeerArena a;
+  PeerArena a = {};
   if (int r = fill_arena(a, ptrs, rank, world, half_bytes, slot_bytes)) return r;
   if (bytes <= 0 || bytes % 16 || bytes > slot_bytes) return FF_HOST_TOO_LARGE;
   allgather_push_kernel<<<1, 256, 0, s>>>(a, (const uint8_t*)x, (uint8_t*)out, bytes, status);
@@ -162,7 +162,7 @@ FF_EXPORT int ff_allgather_push(const unsigned long long* ptrs, int rank, int wo
 
 FF_EXPORT int ff_transport_fill(const unsigned long long* ptrs, int rank, int world, long long half_bytes,
                                 long long slot_bytes, int words, unsigned salt, cudaStream_t s) {
-  PeerArena a;
+  PeerArena a = {};
   if (int r = fill_arena(a, ptrs, rank, world, half_bytes, slot_bytes)) return r;
   if ((long long)words * 4 > slot_bytes) return FF_HOST_TOO_LARGE;
   transport_fill_kernel<<<32, 256, 0, s>>>(a, words, salt);
@@ -171,7 +171,7 @@ FF_EXPORT int ff_transport_fill(const unsigned long long* ptrs, int rank, int wo
 
 FF_EXPORT int ff_transport_verify(const unsigned long long* ptrs, int rank, int world, long long half_bytes,
                                   long long slot_bytes, int words, unsigned salt, int* mismatches, cudaStream_t s) {
-  PeerArena a;
+  PeerArena a = {};
   if (int r = fill_arena(a, ptrs, rank, world, half_bytes, slot_bytes)) return r;
   transport_verify_kernel<<<32, 256, 0, s>>>(a, words, salt, mismatches);
   return launch_result();

@@ -36,6 +36,7 @@ struct PeerArena {
   int world;
   long long half_bytes;         // bytes of one parity half of the data area
   long long slot_bytes;         // bytes of one source-rank slot inside a half
+  uint8_t* mc_base;             // NVLS multicast mapping of the same arena (null: plain peer stores only)
 };
 
 __device__ __forceinline__ int* arena_epoch(const PeerArena& a) { return reinterpret_cast<int*>(a.base[a.rank]); }
@@ -55,6 +56,29 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 }
 __device__ __forceinline__ int ld_volatile(const int* p) {
   int v; asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+
+// ---- NVLS (multimem) accessors: one instruction acts on the same arena offset of every rank ------------
+// multicast address of a location given by its address in this rank's own mapping
+template <typename T>
+__device__ __forceinline__ T* arena_mc(const PeerArena& a, T* local) {
+  return reinterpret_cast<T*>(a.mc_base + (reinterpret_cast<uint8_t*>(local) - a.base[a.rank]));
+}
+// sum over all ranks of eight BF16 values, accumulated in FP32 inside the switch
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+// store eight BF16 values to every rank
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// release-store of a flag word to every rank
+__device__ __forceinline__ void multimem_st_release(int* mc, int v) {
+  asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
 }
 
 // Bounded wait until *flag has reached `epoch` (wrap-safe comparison).

@@ -85,6 +85,12 @@ struct TileSink {
       for (int j = 0; j < 8 && col + j < N; ++j) dst[j] = ob[j];
     } else {
       // N % 8 == 0 and 16-byte aligned slots are checked by the host
+      if (ar.mc_base != nullptr) {
+        // NVLS: the contribution stays in this rank's own slot 0; the switch sums the ranks' copies
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, ar.rank, parity, 0)) + (size_t)t * N + col;
+        *reinterpret_cast<uint4*>(dst) = o;
+        return;
+      }
       for (int pi = 0; pi < ar.world; ++pi) {
         const int p = (ar.rank + pi) % ar.world;
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, p, parity, ar.rank)) + (size_t)t * N + col;
@@ -172,6 +178,59 @@ __device__ __forceinline__ void emit_pair(const SkinnyEpi& ep, __nv_bfloat16* __
 __device__ __forceinline__ void allreduce_tile(const TileSink<true>& sink, int M, int tile, int tile_rows, int flag_idx,
                                                int row0, int row_step, int e, SkinnyBars& bars, int ar_epoch, int* status) {
   const PeerArena& ar = sink.ar;
+  if (ar.mc_base != nullptr) {
+    // ---- NVLS two-shot: every rank flags its contribution on all ranks with one multicast store; the owner of
+    // this chunk (flag_idx % world) lets the switch sum the ranks' copies (multimem.ld_reduce, FP32 accumulate) and
+    // multicasts the BF16 result into slot 1 of every rank, then flags it; every rank copies its result to Y.
+    // One rank reduces a chunk, so all ranks see the same bits.
+    const int owner = flag_idx % ar.world;
+    const int vec_per_row = tile_rows / 8;
+    const int rows = (M - row0 + row_step - 1) / row_step;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (e == 0) {
+      __threadfence_system();
+      multimem_st_release(arena_mc(ar, arena_flag(ar, ar.rank, ar.rank, flag_idx)), ar_epoch);
+      bars.flag_b = 1;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (ar.rank == owner) {
+      if (e < ar.world && e != ar.rank)
+        if (!wait_flag(arena_flag(ar, ar.rank, e, flag_idx), ar_epoch, status, KID_GEMM_AR, e)) bars.flag_b = 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (bars.flag_b) {
+        for (int i = e; i < rows * vec_per_row; i += 128) {
+          const int t = row0 + (i / vec_per_row) * row_step;
+          const int col = tile * tile_rows + (i % vec_per_row) * 8;
+          if (col >= sink.N) continue;
+          const size_t off = (size_t)t * sink.N + col;
+          __nv_bfloat16* src = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, ar.rank, sink.parity, 0)) + off;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, ar.rank, sink.parity, 1)) + off;
+          multimem_st_bf16x8(arena_mc(ar, dst), multimem_ld_reduce_bf16x8(arena_mc(ar, src)));
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (e == 0 && bars.flag_b) {
+        __threadfence_system();
+        multimem_st_release(arena_mc(ar, arena_flag(ar, ar.rank, ar.rank, flag_idx + MAX_FLAGS / 2)), ar_epoch);
+      }
+    }
+    if (e == 0)
+      if (!wait_flag(arena_flag(ar, ar.rank, owner, flag_idx + MAX_FLAGS / 2), ar_epoch, status, KID_GEMM_AR, 100 + owner)) bars.flag_b = 0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (bars.flag_b) {
+      for (int i = e; i < rows * vec_per_row; i += 128) {
+        const int t = row0 + (i / vec_per_row) * row_step;
+        const int col = tile * tile_rows + (i % vec_per_row) * 8;
+        if (col >= sink.N) continue;
+        // written by the owner's multicast store: read past L1
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
+            reinterpret_cast<const __nv_bfloat16*>(arena_slot(ar, ar.rank, sink.parity, 1)) + (size_t)t * sink.N + col));
+        *reinterpret_cast<uint4*>(sink.Y + (size_t)t * sink.ldy + col) = v;
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // flag_b is reused by the next tile
+    return;
+  }
   asm volatile("bar.sync 1, 128;" ::: "memory");
   if (e == 0) {
     __threadfence_system();
@@ -735,11 +794,11 @@ static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int 
   const long long total = (long long)cfg.tiles * ((K + SBK - 1) / SBK);
   if (cl > 1) {
     if (grid != cfg.tiles * cl) return FF_HOST_BAD_SHAPE;
-    if (arena != nullptr && cfg.tiles * cl > MAX_FLAGS) return FF_HOST_TOO_LARGE;
+    if (arena != nullptr && cfg.tiles * cl > MAX_FLAGS / 2) return FF_HOST_TOO_LARGE;
   } else {
     if (grid < 1 || grid > 1024 || (grid > 1 && (scratch == nullptr || counters == nullptr))) return FF_HOST_BAD_SHAPE;
     if (grid > total) return FF_HOST_BAD_SHAPE;
-    if (arena != nullptr && cfg.tiles > MAX_FLAGS) return FF_HOST_TOO_LARGE;
+    if (arena != nullptr && cfg.tiles > MAX_FLAGS / 2) return FF_HOST_TOO_LARGE;
   }
   const int ntok = (M + 15) / 16 * 16;
   CUtensorMap tmX, tmW;
@@ -801,13 +860,17 @@ FF_EXPORT int ff_gemm_skinny_rope_kv(const void* X, const void* W, void* Y, int 
 // Y = sum over ranks of X_r · W_rᵀ, identical bits on every rank. ptrs: arena base of every rank.
 FF_EXPORT int ff_gemm_ar(const unsigned long long* ptrs, int rank, int world, long long half_bytes,
                          long long slot_bytes, const void* X, const void* W, void* Y, int M, int N, int K, int ldx,
-                         int ldw, int ldy, int grid, float* scratch, int* counters, int* status, cudaStream_t stream) {
+                         int ldw, int ldy, int grid, float* scratch, int* counters, unsigned long long mc_ptr, int* status,
+                         cudaStream_t stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return FF_HOST_BAD_SHAPE;
   if (N % 8 || (long long)M * N * 2 > slot_bytes || half_bytes < slot_bytes * world) return FF_HOST_TOO_LARGE;
   if ((reinterpret_cast<uintptr_t>(Y) & 15) || (ldy % 8) || (slot_bytes % 16)) return FF_HOST_BAD_ALIGN;
-  PeerArena a;
+  PeerArena a = {};
   for (int i = 0; i < MAX_RANKS; ++i) a.base[i] = i < world ? reinterpret_cast<uint8_t*>(ptrs[i]) : nullptr;
   a.rank = rank; a.world = world; a.half_bytes = half_bytes; a.slot_bytes = slot_bytes;
+  // mc_ptr != 0: the arena's NVLS multicast mapping; the exchange then goes through the switch (two-shot)
+  a.mc_base = reinterpret_cast<uint8_t*>(mc_ptr);
+  if (mc_ptr != 0 && world < 2) a.mc_base = nullptr;
   return gemm_skinny_launch(X, W, Y, M, N, K, ldx, ldw, ldy, grid, scratch, counters, status, stream, &a);
 }
 

@@ -18,6 +18,7 @@ arrived (the reference verifies its transport the same way, src/backend/cuda/mod
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_longlong, c_ulonglong
 
 import torch
@@ -96,6 +97,13 @@ class TPComm:
         self.fused = arena is not None
         self.stats = {"gemm_ar": 0, "oneshot_ar": 0, "nccl_ar": 0, "ag_gemm": 0, "gemm_rs": 0}
         self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=device) if arena is not None else None
+        # NVLS: with FLYINGFISH_NVLS=1 the fused GEMM + all-reduce exchanges through the switch (multimem, two
+        # flag rounds) when the arena has a multicast mapping. Off by default: at two ranks the one-shot exchange
+        # over plain peer stores measured 33 us against 45 us for the switch path on the 4096x4096 projection.
+        # Always off with NCCL_NVLS_ENABLE=0 (tests in which a rank may leave run on plain peer stores: a rank
+        # that dies while bound to a multicast object faults its peers).
+        self.nvls = bool(arena is not None and arena.multicast_ptr and os.environ.get("FLYINGFISH_NVLS", "0") == "1"
+                         and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0")
 
     @classmethod
     def create(cls, group: dist.ProcessGroup, device: torch.device | str, fused: bool = True,
@@ -149,6 +157,7 @@ class TPComm:
             out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
             rc = lib.ff_gemm_ar(*self.arena.args(), oplib.ptr(x), oplib.ptr(w), oplib.ptr(out), m, n, k, x.stride(0),
                                 w.stride(0), n, grid, oplib.ptr(scratch), oplib.ptr(ws.gemm_counters),
+                                ctypes.c_ulonglong(self.arena.multicast_ptr if self.nvls else 0),
                                 oplib.ptr(oplib.status_tensor(x.device)), oplib.stream_ptr())
             oplib.check(rc, "ff_gemm_ar")
             self.stats["gemm_ar"] += 1
