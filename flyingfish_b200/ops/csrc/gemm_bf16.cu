@@ -47,6 +47,46 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gsz;
 }
 
+// Grouped mode (mixture-of-experts prefill): the rows of A are expert segments (segment e starts at row
+// seg_off[e], a multiple of 16, and holds counts[e] rows), B stacks the experts' weights (expert e at row
+// e * N). Segment e contributes ceil(counts[e] / 128) row tiles x tiles_n column tiles, row tile fastest,
+// so the CTAs working side by side share one weight tile and the segment's rows stay in L2. A row tile may
+// reach past its segment: those rows are computed and not stored.
+struct GroupArgs {
+  const int* seg_off;                 // nullptr: dense problem
+  const int* counts;
+  int E;
+};
+
+struct TileWalk { int e = 0, base = 0; };
+
+// Operand rows of linear tile t of this CTA's loop (t grows monotonically); false when the problem is done.
+__device__ __forceinline__ bool next_tile(const GroupArgs& g, TileWalk& w, int t, int tiles_m, int tiles_n,
+                                          int M, int N, int BN, int& tm, int& tn, int& a_row0, int& b_row0,
+                                          int& row_end) {
+  if (g.seg_off == nullptr) {
+    if (t >= tiles_m * tiles_n) return false;
+    tile_coords(t, tiles_m, tiles_n, tm, tn);
+    a_row0 = tm * BM; b_row0 = tn * BN; row_end = M;
+    return true;
+  }
+  while (w.e < g.E) {
+    const int cnt = g.counts[w.e];
+    const int tme = (cnt + BM - 1) / BM;
+    const int n = tme * tiles_n;
+    if (t < w.base + n) {
+      const int tl = t - w.base;
+      tm = tl % tme; tn = tl / tme;
+      a_row0 = g.seg_off[w.e] + tm * BM;
+      b_row0 = w.e * N + tn * BN;
+      row_end = g.seg_off[w.e] + cnt;
+      return true;
+    }
+    w.base += n; ++w.e;
+  }
+  return false;
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 // epi: 0 = store bf16; 1 = SwiGLU (every 128 columns of a tile are 64 gate then the matching 64 up columns; output
@@ -87,7 +127,7 @@ template <int BN, int STAGES, int COMM>
 __global__ void __launch_bounds__(COMM == 1 ? 320 : 192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA1,
                  const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cout, int M, int N, int K, int ldc, int epi,
-                 int* status, CommArgs ca) {
+                 int* status, CommArgs ca, GroupArgs ga) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ PipeBars bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -97,7 +137,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   constexpr uint32_t TMEM_COLS = 2 * BN;   // 256 or 512, power of two
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
   const int kblocks = (K + BK - 1) / BK;
   const int tiles_per_rank = COMM ? ca.rows_per_rank / BM : 1;
   int epoch = 0;
@@ -122,9 +161,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
-        tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world);
+      TileWalk walk;
+      for (int t = blockIdx.x; ok; t += gridDim.x) {
+        int tm, tn, a_row0, b_row0, row_end;
+        if (!next_tile(ga, walk, t, tiles_m, tiles_n, M, N, BN, tm, tn, a_row0, b_row0, row_end)) break;
+        if (COMM) { tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world); a_row0 = tm * BM; }
         const int src = tm / tiles_per_rank, rb = tm - src * tiles_per_rank;
         if (COMM == 1 && src != ca.ar.rank) {
           // the rows of this tile must have arrived in the local arena copy
@@ -140,8 +181,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem + s * STAGE_BYTES;
           if (COMM == 1 && src == ca.ar.rank) tma_load_2d(sa, &tmX, &bars.full[s], kb * BK, rb * BM);
           else if (COMM == 1) tma_load_3d(sa, parity ? &tmA1 : &tmA, &bars.full[s], kb * BK, rb * BM, src);
-          else tma_load_2d(sa, &tmA, &bars.full[s], kb * BK, tm * BM);
-          tma_load_2d(sa + A_BYTES, &tmB, &bars.full[s], kb * BK, tn * BN);
+          else tma_load_2d(sa, &tmA, &bars.full[s], kb * BK, a_row0);
+          tma_load_2d(sa + A_BYTES, &tmB, &bars.full[s], kb * BK, b_row0);
         }
       }
     }
@@ -150,7 +191,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = umma_idesc(1, 1, 0, 0, BM, BN);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
+      TileWalk walk;
+      for (int t = blockIdx.x; ok; t += gridDim.x, ++tile_it) {
+        int tm_, tn_, a_, b_, re_;
+        if (!next_tile(ga, walk, t, tiles_m, tiles_n, M, N, BN, tm_, tn_, a_, b_, re_)) break;
         const int acc = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
         if (!mbar_wait(&bars.tmem_empty[acc], aph ^ 1, abort_flag, status, KID_GEMM_BF16, 2)) { ok = false; break; }
         tc_fence_after();
@@ -178,13 +222,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int e = (warp - 2) * 32 + lane;
     uint32_t tile_it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
-      int tm, tn; tile_coords(t, tiles_m, tiles_n, tm, tn);
-      tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world);
+    TileWalk walk;
+    for (int t = blockIdx.x; ok; t += gridDim.x, ++tile_it) {
+      int tm, tn, a_row0, b_row0, row_end;
+      if (!next_tile(ga, walk, t, tiles_m, tiles_n, M, N, BN, tm, tn, a_row0, b_row0, row_end)) break;
+      if (COMM) { tm = comm_tm<COMM>(tm, tiles_per_rank, ca.ar.rank, ca.ar.world); a_row0 = tm * BM; }
       const int acc = tile_it & 1; const uint32_t aph = (tile_it >> 1) & 1;
       if (!mbar_wait(&bars.tmem_full[acc], aph, abort_flag, status, KID_GEMM_BF16, 4)) { ok = false; break; }
       tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
+      const int row = a_row0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
       if (epi == 1) {
         constexpr int HALF = BN / 2;
@@ -197,7 +243,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_x16(taddr + gc, g);
           tmem_ld_x16(taddr + gc + 64, u);
           tmem_ld_wait();
-          if (row < M) {
+          if (row < row_end) {
             uint32_t o[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -230,7 +276,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t r[16];
           tmem_ld_x16(taddr + c, r);
           tmem_ld_wait();
-          if (row < M) {
+          if (row < row_end) {
             if (tn * BN + c + 16 <= N) {
               uint4* dst = reinterpret_cast<uint4*>(crow + c);
 #pragma unroll
@@ -281,7 +327,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t r[32];
           tmem_ld_x32(taddr + c, r);
           tmem_ld_wait();
-          if (row < M) {
+          if (row < row_end) {
             if (tn * BN + c + 32 <= N) {
               uint4* dst = reinterpret_cast<uint4*>(crow + c);
 #pragma unroll
@@ -449,7 +495,33 @@ FF_EXPORT int ff_gemm_bf16(const void* X, const void* W, void* Y, int M, int N, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   CommArgs none = {};
-  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmA, tmB, Y, M, N, K, ldy, epi, status, none);
+  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmA, tmB, Y, M, N, K, ldy, epi, status, none, GroupArgs{});
+  return launch_result();
+}
+
+// Grouped GEMM over expert segments with 128-row token tiles (prefill sizes; the swap-AB kernel of moe.cu serves
+// segments of a few rows): Y[seg rows, Nw] = Xs[seg rows, K] · W[e][Nw, K]ᵀ. Xs [capacity, K] and Y rows are
+// addressed by seg_off / counts (device arrays, no host read-back); W is [E_local * Nw, K]. epi 0 / 1 as above.
+FF_EXPORT int ff_moe_grouped_gemm_tiled(const void* Xs, const void* W, void* Y, const int* seg_off, const int* counts,
+                                        int E_local, int Nw, int K, int capacity, int ldy, int epi, int* status,
+                                        cudaStream_t stream) {
+  if (E_local <= 0 || Nw <= 0 || K <= 0 || capacity <= 0 || !seg_off || !counts) return FF_HOST_BAD_SHAPE;
+  if ((K % 8) || (epi != 0 && epi != 1) || (epi == 1 && (Nw % 256))) return FF_HOST_BAD_SHAPE;
+  const int out_cols = (epi == 1) ? Nw / 2 : Nw;
+  if (((size_t)ldy * 2) % 16 || ldy < out_cols || (reinterpret_cast<uintptr_t>(Y) & 15)) return FF_HOST_BAD_ALIGN;
+  CUtensorMap tmA, tmB;
+  constexpr int BN = 256, STAGES = 4;
+  int r = make_tmap_2d(&tmA, Xs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, capacity, (uint64_t)K * 2, BK, BM);
+  if (r) return r;
+  r = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, (uint64_t)E_local * Nw, (uint64_t)K * 2, BK, BN);
+  if (r) return r;
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
+  auto kern = gemm_bf16_kernel<BN, STAGES, 0>;
+  static bool attr_done = false;
+  if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
+  CommArgs none = {};
+  GroupArgs ga = {seg_off, counts, E_local};
+  kern<<<sm_count(), 192, smem, stream>>>(tmA, tmA, tmA, tmB, Y, capacity, Nw, K, ldy, epi, status, none, ga);
   return launch_result();
 }
 
@@ -500,7 +572,7 @@ FF_EXPORT int ff_ag_gemm(const unsigned long long* ptrs, int rank, int world, lo
   if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 320, smem, stream>>>(tmA0, tmA1, tmX, tmB, Y, M, N, K, ldy, epi, status, ca);
+  kern<<<grid, 320, smem, stream>>>(tmA0, tmA1, tmX, tmB, Y, M, N, K, ldy, epi, status, ca, GroupArgs{});
   return launch_result();
 }
 
@@ -527,7 +599,7 @@ FF_EXPORT int ff_gemm_rs(const unsigned long long* ptrs, int rank, int world, lo
   if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmA, tmB, nullptr, M, N, K, N, 0, status, ca);
+  kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmA, tmB, nullptr, M, N, K, N, 0, status, ca, GroupArgs{});
   return launch_result();
 }
 

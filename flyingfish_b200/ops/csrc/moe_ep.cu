@@ -6,8 +6,8 @@
 //   2. ep_dispatch     : publishes the counts into every peer's count matrix (peer stores + flag),
 //                        waits for all ranks' counts, derives every expert segment's offset on its
 //                        owner (segments padded to 16 rows, sources in rank order), then scatters
-//                        the token rows of the top-k assignments straight into the owners' expert
-//                        input buffers with 16-byte peer stores; the last CTA flags "dispatch
+//                        the token rows (read once per row, stored to each of its top-k owners) straight
+//                        into the owners' expert input buffers with 16-byte peer stores; the last CTA flags "dispatch
 //                        complete" to every peer. The owner's seg_off / counts arrays for the
 //                        grouped GEMM are written by CTA 0 (no host involvement anywhere).
 //   3. ep_wait         : the owner waits (bounded) until every source has flagged completion.
@@ -115,21 +115,40 @@ ep_dispatch_kernel(EpArena a, const __nv_bfloat16* __restrict__ x, const int* __
     if (run > a.capacity) set_status(status, KID_MOE_DISPATCH, FF_ERR_CAPACITY, run, a.capacity);
   }
   __syncthreads();
-  // 4. scatter rows: one warp per assignment -----------------------------------------------------
+  // 4. scatter rows: one warp per token row. Lane j < top_k claims the slot of assignment j; the row is
+  //    read once into registers (16 vectors per lane per pass) and stored to each of its k owners.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  const int n_assign = rows * top_k;
   const int nvec = a.hidden >> 3;
-  for (int i = blockIdx.x * wpb + warp; i < n_assign; i += gridDim.x * wpb) {
-    const int e = ids[i];
-    int slot = 0;
-    if (lane == 0) slot = s_base[e] + atomicAdd(&cursors[e], 1);
-    slot = __shfl_sync(0xffffffffu, slot, 0);
-    const int d = e / El;
-    if (slot >= a.capacity) { if (lane == 0) pos[i] = -1; continue; }
-    if (lane == 0) pos[i] = d * a.capacity + slot;
-    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(i / top_k) * ldx);
-    uint4* dst = reinterpret_cast<uint4*>(a.base[d] + a.off_x) + (size_t)slot * nvec;
-    for (int v = lane; v < nvec; v += 32) dst[v] = src[v];
+  for (int r = blockIdx.x * wpb + warp; r < rows; r += gridDim.x * wpb) {
+    int slot = -1, d = 0;
+    if (lane < top_k) {
+      const int e = ids[(size_t)r * top_k + lane];
+      if (e >= 0 && e < E) {
+        d = e / El;
+        slot = s_base[e] + atomicAdd(&cursors[e], 1);
+        if (slot >= a.capacity) slot = -1;
+      }
+      pos[(size_t)r * top_k + lane] = slot < 0 ? -1 : d * a.capacity + slot;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r * ldx);
+    for (int v0 = 0; v0 < nvec; v0 += 32 * 16) {
+      uint4 reg[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int v = v0 + u * 32 + lane;
+        if (v < nvec) reg[u] = __ldg(src + v);
+      }
+      for (int j = 0; j < top_k; ++j) {
+        const int sj = __shfl_sync(0xffffffffu, slot, j), dj = __shfl_sync(0xffffffffu, d, j);
+        if (sj < 0) continue;
+        uint4* dst = reinterpret_cast<uint4*>(a.base[dj] + a.off_x) + (size_t)sj * nvec;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int v = v0 + u * 32 + lane;
+          if (v < nvec) dst[v] = reg[u];
+        }
+      }
+    }
   }
   // 5. completion: last CTA flags every peer -------------------------------------------------------
   __syncthreads();
@@ -183,15 +202,26 @@ ep_combine_kernel(EpArena a, const int* __restrict__ pos, const int* __restrict_
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int j = 0; j < top_k; ++j) {
-        const int p = s_pos[j];
-        if (p < 0) continue;
-        const int d = p / a.capacity, slot = p - d * a.capacity;
-        const uint4 dd = (reinterpret_cast<const uint4*>(a.base[d] + a.off_y) + (size_t)slot * nvec)[v];
-        const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dd);
-        const float ww = s_w[j];
+      // all peer loads of a batch of 8 contributions are in flight before the first is used
+      for (int j0 = 0; j0 < top_k; j0 += 8) {
+        uint4 dd[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 f = unpack_bf16x2(dp[i]); acc[2 * i] += ww * f.x; acc[2 * i + 1] += ww * f.y; }
+        for (int u = 0; u < 8; ++u) {
+          const int p = j0 + u < top_k ? s_pos[j0 + u] : -1;
+          dd[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (p >= 0) {
+            const int d = p / a.capacity, slot = p - d * a.capacity;
+            dd[u] = __ldcg(reinterpret_cast<const uint4*>(a.base[d] + a.off_y) + (size_t)slot * nvec + v);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (j0 + u >= top_k || s_pos[j0 + u] < 0) continue;
+          const uint32_t* dp = reinterpret_cast<const uint32_t*>(&dd[u]);
+          const float ww = s_w[j0 + u];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { const float2 f = unpack_bf16x2(dp[i]); acc[2 * i] += ww * f.x; acc[2 * i + 1] += ww * f.y; }
+        }
       }
       uint4 o;
       o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
@@ -257,7 +287,7 @@ FF_EXPORT int ff_ep_dispatch(const EpArenaHost* h, const void* x, const int* ids
   if (e != cudaSuccess) return (int)e;
   const int n = rows * top_k;
   ep_count_kernel<<<(n + 255) / 256, 256, 0, s>>>(ids, n, a.E, counts_scratch, status);
-  int ctas = (n + 7) / 8;
+  int ctas = (rows + 7) / 8;
   if (ctas > 296) ctas = 296;
   if (ctas < 1) ctas = 1;
   ep_dispatch_kernel<<<ctas, 256, 0, s>>>(a, (const __nv_bfloat16*)x, ids, counts_scratch, cursors, pos, rows, top_k,

@@ -3,6 +3,8 @@ device-side dispatch (count / scan / permute), grouped tcgen05 GEMMs with SwiGLU
 epilogue, deterministic combine -- ``csrc/moe.cu``."""
 from __future__ import annotations
 
+import os
+
 from ctypes import c_float
 
 import torch
@@ -87,12 +89,20 @@ def dispatch_local(x, ids, n_experts_total: int, e_lo: int, e_hi: int):
     return sorted_x, pos, seg_off, counts, capacity
 
 
-def grouped_gemm(xs, w, seg_off, counts, capacity: int, epi: int) -> torch.Tensor:
+TILED_MIN_ROWS = int(os.environ.get("FF_MOE_TILED_MIN", "96"))
+
+
+def grouped_gemm(xs, w, seg_off, counts, capacity: int, epi: int, rows_per_expert: float = 0.0) -> torch.Tensor:
+    """``rows_per_expert`` is the caller's estimate of the mean segment length (assignments / local experts; the
+    true counts stay on the device): from ``TILED_MIN_ROWS`` on, the 128-row-tile kernel (tokens on the UMMA M
+    side, double-buffered accumulators) runs instead of the swap-AB kernel that streams each weight slice once."""
     el, nw, k = w.shape
     n_out = nw // 2 if epi == 1 else nw
     y = torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs.device)
-    rc = kernels().ff_moe_grouped_gemm(ptr(xs), ptr(w), ptr(y), ptr(seg_off), ptr(counts), el, nw, k, capacity, n_out,
-                                       epi, ptr(status_tensor(xs.device)), stream_ptr())
+    tiled = rows_per_expert >= TILED_MIN_ROWS and (epi == 0 or nw % 256 == 0)
+    fn = kernels().ff_moe_grouped_gemm_tiled if tiled else kernels().ff_moe_grouped_gemm
+    rc = fn(ptr(xs), ptr(w), ptr(y), ptr(seg_off), ptr(counts), el, nw, k, capacity, n_out, epi,
+            ptr(status_tensor(xs.device)), stream_ptr())
     check(rc, "ff_moe_grouped_gemm")
     _count()
     return y
@@ -119,6 +129,7 @@ def experts_forward(x, weights, ids, w_gate_up, w_down, mode, e_lo: int = 0, n_e
     total = n_experts_total if n_experts_total is not None else el
     wgu = _gu_interleaved(w_gate_up)
     xs, pos, seg_off, counts, cap = dispatch_local(x.contiguous(), ids.contiguous(), total, e_lo, e_lo + el)
-    h = grouped_gemm(xs, wgu, seg_off, counts, cap, epi=1)
-    y = grouped_gemm(h, w_down, seg_off, counts, cap, epi=0)
+    rpe = rows * ids.shape[1] / max(total, 1)
+    h = grouped_gemm(xs, wgu, seg_off, counts, cap, epi=1, rows_per_expert=rpe)
+    y = grouped_gemm(h, w_down, seg_off, counts, cap, epi=0, rows_per_expert=rpe)
     return combine(y, pos, ids, weights.contiguous(), rows, hidden)

@@ -79,34 +79,57 @@ class EPComm:
         return self._baseline(x, weights, ids, lw, mode)
 
     def _fused(self, x, weights, ids, lw, mode):
-        from ..ops import moe_cuda
+        pos = self.dispatch(x, ids)
+        self.experts(lw)
+        out = self.combine(pos, ids, weights, x.shape[0])
+        self.stats["fused_calls"] += 1
+        return out
+
+    # The three phases of the fused path (also timed one by one by ``utils/epbench.py``). Every rank must call
+    # all three, in this order, once per layer call: the kernels wait (bounded) on one another's flags.
+    def dispatch(self, x: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """Scatters the local rows into the owners' expert input buffers; returns ``pos`` [rows * top_k]."""
         lib = oplib.kernels()
         rows, top_k = ids.shape
         E, El = self.E, self.El
         counts_s, cursors = self.scratch[:E], self.scratch[E: 2 * E]
-        seg_off, counts = self.scratch[2 * E: 2 * E + El + 1], self.scratch[2 * E + El + 1:]
+        self._seg_off, self._counts = self.scratch[2 * E: 2 * E + El + 1], self.scratch[2 * E + El + 1:]
         pos = torch.empty(rows * top_k, dtype=torch.int32, device=x.device)
-        st = oplib.status_tensor(x.device)
-        x = x.contiguous(); ids = ids.contiguous(); weights = weights.contiguous()
+        self._rows_per_expert = rows * top_k / El        # expected segment length when every rank sends as many rows
+        x = x.contiguous(); ids = ids.contiguous()
         rc = lib.ff_ep_dispatch(ctypes.byref(self.arena), oplib.ptr(x), oplib.ptr(ids), rows, top_k, x.stride(0),
-                                oplib.ptr(counts_s), oplib.ptr(cursors), oplib.ptr(pos), oplib.ptr(seg_off),
-                                oplib.ptr(counts), oplib.ptr(st), oplib.stream_ptr())
+                                oplib.ptr(counts_s), oplib.ptr(cursors), oplib.ptr(pos), oplib.ptr(self._seg_off),
+                                oplib.ptr(self._counts), oplib.ptr(oplib.status_tensor(x.device)), oplib.stream_ptr())
         oplib.check(rc, "ff_ep_dispatch")
         ops._count(3)
+        return pos
+
+    def experts(self, lw) -> None:
+        """Grouped gate/up (+SwiGLU) and down GEMMs of this rank's experts over the received rows."""
+        from ..ops import moe_cuda
+        lib = oplib.kernels()
         wgu = moe_cuda._gu_interleaved(lw.experts_gu)
-        h = moe_cuda.grouped_gemm(self.recv_x, wgu, seg_off, counts, self.capacity, epi=1)
+        h = moe_cuda.grouped_gemm(self.recv_x, wgu, self._seg_off, self._counts, self.capacity, epi=1,
+                                  rows_per_expert=self._rows_per_expert)
         # the down projection writes into the symmetric output buffer the peers read from
-        f = h.shape[1]
-        rc = lib.ff_moe_grouped_gemm(oplib.ptr(h), oplib.ptr(lw.experts_down), oplib.ptr(self.out_y), oplib.ptr(seg_off),
-                                     oplib.ptr(counts), El, self.hidden, f, self.capacity, self.hidden, 0,
-                                     oplib.ptr(st), oplib.stream_ptr())
+        fn = lib.ff_moe_grouped_gemm_tiled if self._rows_per_expert >= moe_cuda.TILED_MIN_ROWS else lib.ff_moe_grouped_gemm
+        rc = fn(oplib.ptr(h), oplib.ptr(lw.experts_down), oplib.ptr(self.out_y),
+                                     oplib.ptr(self._seg_off), oplib.ptr(self._counts), self.El, self.hidden, h.shape[1],
+                                     self.capacity, self.hidden, 0, oplib.ptr(oplib.status_tensor(h.device)),
+                                     oplib.stream_ptr())
         oplib.check(rc, "ff_moe_grouped_gemm(down)")
-        out = torch.empty(rows, self.hidden, dtype=torch.bfloat16, device=x.device)
+        ops._count(1)
+
+    def combine(self, pos: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, rows: int) -> torch.Tensor:
+        """Weighted sum, in ascending expert id, of the expert outputs read out of the owners' memory."""
+        lib = oplib.kernels()
+        out = torch.empty(rows, self.hidden, dtype=torch.bfloat16, device=pos.device)
+        ids = ids.contiguous(); weights = weights.contiguous()
         rc = lib.ff_ep_combine(ctypes.byref(self.arena), oplib.ptr(pos), oplib.ptr(ids), oplib.ptr(weights),
-                               oplib.ptr(out), rows, top_k, oplib.ptr(st), oplib.stream_ptr())
+                               oplib.ptr(out), rows, ids.shape[1], oplib.ptr(oplib.status_tensor(pos.device)),
+                               oplib.stream_ptr())
         oplib.check(rc, "ff_ep_combine")
-        ops._count(2)
-        self.stats["fused_calls"] += 1
+        ops._count(1)
         return out
 
     def _baseline(self, x, weights, ids, lw, mode):

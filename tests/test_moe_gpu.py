@@ -43,7 +43,7 @@ def test_route_ties_go_to_lower_id():
 
 
 @pytest.mark.parametrize("rows,E,k,h,f", [(5, 8, 2, 256, 128), (300, 16, 4, 512, 256), (64, 32, 8, 1024, 512),
-                                          (1000, 4, 2, 256, 192)])
+                                          (1000, 4, 2, 256, 192), (2000, 8, 2, 512, 256), (3000, 8, 4, 512, 384)])
 def test_experts_forward(rows, E, k, h, f):
     x = _rand((rows, h), 5)
     wgu, wd = _rand((E, 2 * f, h), 6, 0.05), _rand((E, h, f), 7, 0.05)
