@@ -44,6 +44,7 @@ class Model:
         self.name = name or spec.name
         self._seq: Sequence | None = None
         self.load_ms = 0.0
+        self.vision = None                 # models.vision.VisionTower of vision-language checkpoints
 
     # -- construction ------------------------------------------------------------------------
     @classmethod
@@ -88,6 +89,15 @@ class Model:
         log_json("prefill_memory_plan", verbose_only=True, **plan.to_json())
         engine = Engine(net, spec, settings, plan.kv_blocks, device, max_prefill_rows=plan.prefill_chunk)
         m = cls(engine, spec, settings, tokenizer, name)
+        if spec.extra.get("vision"):
+            from .models.vision import VisionSpec, VisionTower
+            vspec = VisionSpec(**spec.extra["vision"])
+            if path.is_dir() and not random_init:
+                from .loaders.checkpoint import load_prefixed_tensors
+                m.vision = VisionTower(vspec, load_prefixed_tensors(path, ("visual.", "model.visual.")), device)
+            else:
+                m.vision = VisionTower.random(vspec, device, seed + 1)
+            engine.mm_encoder = m.encode_images
         m.load_ms = (time.perf_counter() - t0) * 1e3
         log_json("backend_device", verbose_only=True, device=str(device), model=name, load_ms=m.load_ms)
         return m
@@ -102,6 +112,30 @@ class Model:
         if self._seq is not None:
             self.engine.free_sequence(self._seq.seq_id)
         self._seq = self.engine.add_sequence(ids)
+        return self.engine.prefill([self._seq])[0]
+
+    def encode_images(self, ids: list[int], images: list) -> tuple[list[int], list[int], torch.Tensor]:
+        """Runs the vision tower over ``images`` (``serve.image.Image``) and expands every image placeholder of
+        ``ids`` to the span the tower fills. Returns (expanded ids, placeholder positions, embedding rows)."""
+        from .serve.image import expand_image_tokens, image_token_count, pack_patches
+        if self.vision is None:
+            raise ValueError("this model has no vision tower")
+        vs = self.vision.spec
+        packed = [pack_patches(im, patch=vs.patch, merge=vs.merge, temporal=vs.temporal) for im in images]
+        patches = [torch.from_numpy(p) for p, _ in packed]
+        grids = [g for _, g in packed]
+        embeds = torch.cat(self.vision.forward(patches, grids), 0)
+        token = int(self.spec.extra["image_token_id"])
+        out = expand_image_tokens(ids, token, [image_token_count(g, vs.merge) for g in grids])
+        positions = [i for i, t in enumerate(out) if t == token]
+        return out, positions, embeds
+
+    def prefill_multimodal(self, ids: list[int], images: list) -> int:
+        """Like :meth:`prefill` for a prompt with one image placeholder token per image."""
+        ids, positions, embeds = self.encode_images(ids, images)
+        if self._seq is not None:
+            self.engine.free_sequence(self._seq.seq_id)
+        self._seq = self.engine.add_sequence(ids, positions, embeds)
         return self.engine.prefill([self._seq])[0]
 
     def decode(self) -> int:

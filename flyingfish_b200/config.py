@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl
     layers: int
     hidden: int
     heads: int
@@ -164,8 +164,19 @@ def qwen3_moe_tiny() -> ModelSpec:
         moe=MoeSpec(num_experts=16, top_k=4, expert_ffn=256, score="softmax"))
 
 
+def tiny_vl() -> ModelSpec:
+    """Small vision-language shape: the tiny dense decoder plus a vision tower (``extra["vision"]`` holds the
+    fields of ``models.vision.VisionSpec``; ``extra["image_token_id"]`` marks the rows the tower fills)."""
+    spec = tiny_llama()
+    spec.name, spec.arch = "tiny-vl", "qwen3_vl"
+    spec.extra = {"image_token_id": 2047,
+                  "vision": {"hidden": 256, "heads": 2, "depth": 2, "intermediate": 512, "patch": 16, "temporal": 2,
+                             "merge": 2, "out_hidden": spec.hidden, "pos_side": 16}}
+    return spec
+
+
 NAMED_SHAPES = {
-    "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
+    "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }

@@ -46,6 +46,8 @@ class Sequence:
     prefilled: int = 0                 # prompt tokens whose KV is committed
     pending: int | None = None         # token sampled but not yet fed through the model
     finished: bool = False
+    mm_positions: list[int] | None = None      # prompt indices whose embedding row comes from ``mm_embeds``
+    mm_embeds: torch.Tensor | None = None      # [len(mm_positions), hidden] (vision-tower output)
 
     @property
     def all_tokens(self) -> list[int]:
@@ -88,7 +90,10 @@ class Engine:
         self.fail_next_step = False      # host-side fault injection hook for tests
 
     # -- sequence management ---------------------------------------------------------------
-    def add_sequence(self, prompt: list[int]) -> Sequence:
+    def add_sequence(self, prompt: list[int], mm_positions: list[int] | None = None,
+                     mm_embeds: torch.Tensor | None = None) -> Sequence:
+        """``mm_positions`` / ``mm_embeds``: prompt indices whose embedding rows are supplied by the caller (the
+        vision tower's output for image placeholder tokens) instead of the embedding table."""
         self._check()
         if len(prompt) == 0:
             raise ValueError("empty prompt")
@@ -97,6 +102,10 @@ class Engine:
         sid = self._next_id
         self._next_id += 1
         s = Sequence(sid, list(prompt))
+        if mm_positions:
+            if mm_embeds is None or mm_embeds.shape[0] != len(mm_positions) or mm_embeds.shape[1] != self.spec.hidden:
+                raise ValueError("mm_embeds must hold one hidden-sized row per mm position")
+            s.mm_positions, s.mm_embeds = list(mm_positions), mm_embeds
         self.seqs[sid] = s
         self.kv.add_sequence(sid)
         return s
@@ -174,7 +183,7 @@ class Engine:
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
                 logit_rows=logit_rows, is_decode=False)
         fb.upload()
-        out = self.model.forward(fb, self.kv)
+        out = self.model.forward(fb, self.kv, inputs_embeds=self._mm_embeds(part, fb, len(ids)))
         toks = [int(t) for t in out.cpu().tolist()]
         self._after_sync()
         for s, take in part:
@@ -182,6 +191,25 @@ class Engine:
             s.prefilled += take
         self.stats["prefill_tokens"] += row
         return toks
+
+    def _mm_embeds(self, part: list[tuple[Sequence, int]], fb: ForwardBatch, rows: int) -> torch.Tensor | None:
+        """Embedding rows of a prefill chunk with the multimodal rows replaced, or None for text-only chunks."""
+        dst, src_rows, row = [], [], 0
+        for s, take in part:
+            if s.mm_positions:
+                lo, hi = s.prefilled, s.prefilled + take
+                for j, p in enumerate(s.mm_positions):
+                    if lo <= p < hi:
+                        dst.append(row + p - lo)
+                        src_rows.append(s.mm_embeds[j])
+            row += take
+        if not dst:
+            return None
+        from .. import ops
+        w = self.model.w
+        emb = ops.embed(fb.ids, w.embed)
+        emb[torch.tensor(dst, dtype=torch.long, device=emb.device)] = torch.stack(src_rows).to(emb.dtype).to(emb.device)
+        return emb
 
     # -- decode ------------------------------------------------------------------------------
     def _fill_decode(self, fb: ForwardBatch, seqs: list[Sequence], bucket: int) -> None:

@@ -37,6 +37,9 @@ class Request:
     arrival: float = field(default_factory=time.perf_counter)
     first_token_time: float | None = None
     error: str | None = None
+    images: list | None = None        # decoded images, one per image placeholder token of ``prompt``
+    mm_positions: list[int] | None = None
+    mm_embeds: object | None = None
 
     @property
     def ttft_ms(self) -> float | None:
@@ -54,6 +57,12 @@ class Scheduler:
 
     # -- API -----------------------------------------------------------------------------------
     def submit(self, req: Request) -> Request:
+        if req.images and req.mm_positions is None:
+            # runs on the engine thread: vision tower over the images, placeholders expanded to their spans
+            enc = getattr(self.engine, "mm_encoder", None)
+            if enc is None:
+                raise ValueError("this model has no vision tower: image input is not supported")
+            req.prompt, req.mm_positions, req.mm_embeds = enc(req.prompt, req.images)
         if len(req.prompt) + req.max_tokens > self.engine.settings.capacity:
             raise ValueError(f"prompt ({len(req.prompt)}) + max_tokens ({req.max_tokens}) exceeds the KV capacity "
                              f"{self.engine.settings.capacity}")
@@ -97,7 +106,10 @@ class Scheduler:
             free -= need
             self.waiting.popleft()
             # a preempted request resumes by recomputing prompt + what it already produced
-            req.seq = self.engine.add_sequence(req.prompt + req.output)
+            if req.mm_positions:
+                req.seq = self.engine.add_sequence(req.prompt + req.output, req.mm_positions, req.mm_embeds)
+            else:
+                req.seq = self.engine.add_sequence(req.prompt + req.output)
             req.state = "running"
             admitted.append(req)
             self.stats["admitted"] += 1

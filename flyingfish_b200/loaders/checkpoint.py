@@ -116,9 +116,29 @@ def audit(ckpt: MappedCheckpoint, spec: ModelSpec, allow_extra: tuple[str, ...] 
             raise CheckpointError(f"{name}: shape {tuple(info.shape)} != expected {tuple(shape)}")
         if info.dtype not in _CLASS[cls]:
             raise CheckpointError(f"{name}: dtype {info.dtype} not allowed here ({cls})")
-    extra = sorted(n for n in have - set(exp) if not any(n.endswith(a) for a in allow_extra))
+    vision = ("visual.", "model.visual.") if spec.extra.get("vision") else ()
+    extra = sorted(n for n in have - set(exp)
+                   if not any(n.endswith(a) for a in allow_extra) and not n.startswith(vision or ("\0",)))
     if extra:
         raise CheckpointError(f"checkpoint holds {len(extra)} unexpected tensors, e.g. {extra[:3]}")
+
+
+def load_prefixed_tensors(model_dir: str | Path, prefixes: tuple[str, ...]) -> dict[str, torch.Tensor]:
+    """All tensors whose name starts with one of ``prefixes`` (first match), keyed without the prefix -- the
+    vision tower of a vision-language checkpoint lives under ``visual.``."""
+    ck = MappedCheckpoint(model_dir)
+    try:
+        out: dict[str, torch.Tensor] = {}
+        for n in ck.names():
+            for pre in prefixes:
+                if n.startswith(pre):
+                    out.setdefault(n[len(pre):], ck.tensor(n).clone())
+                    break
+        if not out:
+            raise CheckpointError(f"no tensors under {prefixes}")
+        return out
+    finally:
+        ck.close()
 
 
 def has_mtp_component(model_dir: str | Path) -> bool:

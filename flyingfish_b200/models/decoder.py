@@ -181,8 +181,9 @@ class DecoderModel:
         ids = ops.argmax_rows(logits, id_offset=self.w.vocab_shard[0], out_vals=vals)
         return self.comm.argmax_merge(vals, ids)
 
-    def forward(self, b: ForwardBatch, kv: PagedKVCache, return_logits: bool = False) -> torch.Tensor:
-        n = self.hidden_states(b, kv)
+    def forward(self, b: ForwardBatch, kv: PagedKVCache, return_logits: bool = False,
+                inputs_embeds: torch.Tensor | None = None) -> torch.Tensor:
+        n = self.hidden_states(b, kv, inputs_embeds)
         lg = self.logits(n, b)
         if self.trace is not None:
             self.trace.record("logits", lg)

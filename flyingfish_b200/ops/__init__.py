@@ -429,7 +429,8 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, blo
 def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                  q_start: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, max_q_len: int, hq: int,
                  hkv: int, dim: int, scale: float, window: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Causal chunked-prefill attention of packed query rows against the paged cache."""
+    """Causal chunked-prefill attention of packed query rows against the paged cache. ``window < 0`` makes it
+    bidirectional: every query row sees all ``ctx_lens`` keys of its sequence (encoders, vision towers)."""
     if not _is_cuda(q):
         return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale,
                                    None, window)

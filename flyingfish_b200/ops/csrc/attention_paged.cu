@@ -382,7 +382,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
                     const int* __restrict__ q_start, const int* __restrict__ q_lens, const int* __restrict__ ctx_lens,
                     __nv_bfloat16* __restrict__ out, int hq, int hkv, int ldq, int ldo, int max_blocks, int num_blocks,
-                    float scale_log2, int window, int* status) {
+                    float scale_log2, int window, int causal, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int b = blockIdx.z, h = blockIdx.y;
   const int qlen = q_lens[b];
@@ -397,17 +397,17 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   for (int e = 0; e < 2; ++e) {
     const int i = tile0 + warp * 16 + g + e * 8;
     rowi[e] = i;
-    if (i < qlen) { qp[e] = q + (size_t)(qs + i) * ldq + (size_t)h * HD; lim[e] = past + i; }
+    if (i < qlen) { qp[e] = q + (size_t)(qs + i) * ldq + (size_t)h * HD; lim[e] = causal ? past + i : ctx - 1; }
     else { qp[e] = nullptr; lim[e] = -1; }
   }
   uint32_t qf[8][4];
   load_q_frags(qf, qp[0], qp[1]);
   RowState st; init_state(st);
-  const int last_key = past + min(qlen, tile0 + 64) - 1;
+  const int last_key = causal ? past + min(qlen, tile0 + 64) - 1 : ctx - 1;   // bidirectional: every key
   int first_key = 0;
   if (window > 0) first_key = max(0, past + tile0 - window + 1);
   const int p0 = first_key / PAGE, p1 = last_key / PAGE + 1;
-  const int warp_last = past + min(qlen - 1, tile0 + warp * 16 + 15);
+  const int warp_last = causal ? past + min(qlen - 1, tile0 + warp * 16 + 15) : ctx - 1;
 
   uint8_t* sKbuf[2] = {smem, smem + 2 * PAGE * HD * 2};
   uint8_t* sVbuf[2] = {smem + PAGE * HD * 2, smem + 3 * PAGE * HD * 2};
@@ -507,6 +507,8 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
   return 0;
 }
 
+// window > 0: sliding window (whole pages trimmed); 0: causal; < 0: bidirectional (every query sees all ctx keys:
+// encoder / vision-tower attention over a segment stored in the paged layout).
 FF_EXPORT int ff_attn_prefill(const void* q, const void* kcache, const void* vcache, const int* block_table,
                               const int* q_start, const int* q_lens, const int* ctx_lens, void* out, int batch,
                               int max_q_len, int hq, int hkv, int head_dim, int ldq, int ldo, int max_blocks,
@@ -519,6 +521,6 @@ FF_EXPORT int ff_attn_prefill(const void* q, const void* kcache, const void* vca
   dim3 grid((max_q_len + 63) / 64, hq, batch);
   attn_prefill_kernel<<<grid, 128, ATTN_SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache,
       (const __nv_bfloat16*)vcache, block_table, q_start, q_lens, ctx_lens, (__nv_bfloat16*)out, hq, hkv, ldq, ldo,
-      max_blocks, num_blocks, scale_log2, window, status);
+      max_blocks, num_blocks, scale_log2, window < 0 ? 0 : window, window < 0 ? 0 : 1, status);
   return launch_result();
 }

@@ -20,7 +20,7 @@ __global__ void rope_kv_paged_kernel(__nv_bfloat16* __restrict__ qkv, const int*
                                      const int* __restrict__ slots, __nv_bfloat16* __restrict__ kcache,
                                      __nv_bfloat16* __restrict__ vcache, const float* __restrict__ inv_freq_tab,
                                      int rows, int hq, int hkv, int dim, int rot_dim, int block_size, int num_blocks,
-                                     float theta, int ldqkv, int* status) {
+                                     float theta, int ldqkv, int* status, const float2* __restrict__ cos_sin) {
   pdl_trigger();
   if (threadIdx.x == 0) FF_TL(status, KID_ROPE_KV, 0);
   pdl_wait();
@@ -39,7 +39,7 @@ __global__ void rope_kv_paged_kernel(__nv_bfloat16* __restrict__ qkv, const int*
   uint4 hi = reinterpret_cast<uint4*>(base + half)[c];
   const bool is_v = head >= hq + hkv;
   if (!is_v) {
-    const int pos = positions[row];
+    const int pos = cos_sin ? 0 : positions[row];
     uint32_t* lp = reinterpret_cast<uint32_t*>(&lo);
     uint32_t* hp = reinterpret_cast<uint32_t*>(&hi);
     const int rhalf = rot_dim >> 1;
@@ -51,10 +51,15 @@ __global__ void rope_kv_paged_kernel(__nv_bfloat16* __restrict__ qkv, const int*
       for (int e = 0; e < 2; ++e) {
         const int i = c * 8 + j * 2 + e;               // index inside the half
         if (i < rhalf) {
-          const float inv = inv_freq_tab ? inv_freq_tab[i] : 1.0f / powf(theta, (float)(2 * i) / (float)rot_dim);
           float sn, cs;
-          sincosf((float)pos * inv, &sn, &cs);
-          cs = bf16r(cs); sn = bf16r(sn);               // cos/sin rounded to BF16
+          if (cos_sin) {                                // per-row table (2-D / multi-axis rotary): already BF16-rounded
+            const float2 t = cos_sin[(size_t)row * rhalf + i];
+            cs = t.x; sn = t.y;
+          } else {
+            const float inv = inv_freq_tab ? inv_freq_tab[i] : 1.0f / powf(theta, (float)(2 * i) / (float)rot_dim);
+            sincosf((float)pos * inv, &sn, &cs);
+            cs = bf16r(cs); sn = bf16r(sn);             // cos/sin rounded to BF16
+          }
           const float x1 = ao[e], x2 = bo[e];
           // BF16 arithmetic: every product and the final sum/difference round to BF16
           ao[e] = bf16r(bf16r(x1 * cs) - bf16r(x2 * sn));
@@ -373,7 +378,21 @@ FF_EXPORT int ff_rope_kv_paged(void* qkv, const int* positions, const int* slots
   const long long total = (long long)rows * (hq + 2 * hkv) * (dim / 16);
   if (int lr_ = launch_pdl(rope_kv_paged_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)qkv, positions, slots,
       (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, inv_freq, rows, hq, hkv, dim, rot_dim, block_size, num_blocks,
-      theta, ldqkv, status)) return lr_;
+      theta, ldqkv, status, (const float2*)nullptr)) return lr_;
+  return launch_result();
+}
+
+// Same with the angles given as a table: cos_sin [rows, rot_dim/2] (cos, sin) FP32 holding BF16-rounded values.
+// Serves rotary schemes whose angle is not position * inv_freq[i]: 2-D (row, column) rotary of vision towers and
+// multi-axis rotary of vision-language decoders. slots / caches may be null (rotation only, hkv = 0).
+FF_EXPORT int ff_rope_kv_paged_table(void* qkv, const float* cos_sin, const int* slots, void* kcache, void* vcache,
+                                     int rows, int hq, int hkv, int dim, int rot_dim, int block_size, int num_blocks,
+                                     int ldqkv, int* status, cudaStream_t s) {
+  if (rows <= 0 || dim % 16 || rot_dim > dim || rot_dim % 2 || ldqkv % 8 || !cos_sin) return FF_HOST_BAD_SHAPE;
+  const long long total = (long long)rows * (hq + 2 * hkv) * (dim / 16);
+  if (int lr_ = launch_pdl(rope_kv_paged_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)qkv,
+      (const int*)nullptr, slots, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, (const float*)nullptr, rows, hq, hkv, dim,
+      rot_dim, block_size, num_blocks, 1.0f, ldqkv, status, reinterpret_cast<const float2*>(cos_sin))) return lr_;
   return launch_result();
 }
 

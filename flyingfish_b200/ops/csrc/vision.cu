@@ -1,0 +1,394 @@
+// Vision-tower and 3-D compute operators (no graphics API anywhere):
+//   layernorm        : y = (x - mean) * rsqrt(var + eps) * w + b, FP32 statistics, one BF16 rounding
+//   bias_act         : y = act(x + bias) in place; act 0 none, 1 tanh-GELU, 2 quick-GELU (x * sigmoid(1.702 x)),
+//                      3 erf-GELU, 4 SiLU. The sum is rounded to BF16 before the activation (the projection's
+//                      output dtype), the result once more.
+//   voxel hash       : open-addressing table over (batch, x, y, z) keys built with atomicCAS (bounded probing),
+//                      value = lowest row index holding the key (deterministic under duplicates)
+//   neighbor_map     : for every site and every kernel offset, the row index of the neighbouring site or -1
+//   sparse_gather    : rows gathered through a neighbour map into the im2col operand of a sparse convolution
+//                      [sites, offsets * channels] (missing neighbours are zero rows); the convolution itself is one
+//                      tensor-core GEMM with FP32 accumulation over offsets * channels
+//   voxelize         : points -> integer voxel coordinates inside a grid (or -1 outside)
+//   rotate_quant     : block-diagonal regular Hadamard rotation (kron of H4 / 2) of every `group` activations,
+//                      per-row absmax INT8 quantisation: s = max(|xR|, 1e-12) / 127, q = rint(xR / s)
+//   int8_linear      : y = bf16(dot_i32(q_x, q_w) * s_x[row] * s_w[col]) with dp4a
+// The reference's counterparts are kernels/vision_ops.cu (sparse_gather*, vision_bias_gelu_f32,
+// vision_bias_quick_gelu_f32), src/sparse.rs (site tables) and src/convrot.rs:1-60 (rotation and quantiser).
+#include "ptx.cuh"
+#include "host_util.h"
+
+namespace ff {
+
+// ------------------------------------------------------------------------------------------------
+// layernorm: one CTA (128 threads) per row, row cached in registers (<= 8 vectors of 8 per thread)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_sum_128(float v, float* s_red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) s_red[warp] = v;
+  __syncthreads();
+  return s_red[0] + s_red[1] + s_red[2] + s_red[3];
+}
+
+constexpr int LN_MAX_VEC = 8;          // hidden <= 128 * 8 * 8 = 8192
+
+__global__ void __launch_bounds__(128)
+layernorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                 const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y, int hidden, int ldx, int ldy,
+                 float eps) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float s_red[4];
+  const int row = blockIdx.x, nvec = hidden >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+  uint4 v[LN_MAX_VEC];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * 128;
+    if (idx < nvec) {
+      v[i] = src[idx];
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&v[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(p[j]); sum += f.x + f.y; }
+    }
+  }
+  const float mean = block_sum_128(sum, s_red) / (float)hidden;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * 128;
+    if (idx < nvec) {
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&v[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(p[j]);
+        sq += (f.x - mean) * (f.x - mean) + (f.y - mean) * (f.y - mean);
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum_128(sq, s_red) / (float)hidden + eps);
+  uint4* dst = reinterpret_cast<uint4*>(y + (size_t)row * ldy);
+#pragma unroll
+  for (int i = 0; i < LN_MAX_VEC; ++i) {
+    const int idx = threadIdx.x + i * 128;
+    if (idx < nvec) {
+      const uint4 wv = reinterpret_cast<const uint4*>(w)[idx];
+      uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+      if (b) bv = reinterpret_cast<const uint4*>(b)[idx];
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(&v[i]);
+      const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
+      const uint32_t* bp = reinterpret_cast<const uint32_t*>(&bv);
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(p[j]), ww = unpack_bf16x2(wp[j]), bb = unpack_bf16x2(bp[j]);
+        o[j] = pack_bf16x2((f.x - mean) * rstd * ww.x + bb.x, (f.y - mean) * rstd * ww.y + bb.y);
+      }
+      dst[idx] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// bias + activation, in place, 8 elements per thread
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float bfr_v(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+__device__ __forceinline__ float act_apply(float x, int act) {
+  switch (act) {
+    case 1: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    case 2: return x / (1.f + __expf(-1.702f * x));
+    case 3: return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+    case 4: return x / (1.f + __expf(-x));
+    default: return x;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bias_act_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ bias, long long rows, int n, int ldx,
+                int act) {
+  pdl_trigger();
+  pdl_wait();
+  const int nvec = n >> 3;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= rows * nvec) return;
+  const long long row = gid / nvec;
+  const int c = (int)(gid - row * nvec);
+  uint4* p = reinterpret_cast<uint4*>(x + (size_t)row * ldx) + c;
+  uint4 v = *p;
+  uint4 bv = make_uint4(0u, 0u, 0u, 0u);
+  if (bias) bv = reinterpret_cast<const uint4*>(bias)[c];
+  uint32_t* vp = reinterpret_cast<uint32_t*>(&v);
+  const uint32_t* bp = reinterpret_cast<const uint32_t*>(&bv);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_bf16x2(vp[j]), bb = unpack_bf16x2(bp[j]);
+    vp[j] = pack_bf16x2(act_apply(bfr_v(f.x + bb.x), act), act_apply(bfr_v(f.y + bb.y), act));
+  }
+  *p = v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// voxel hash table. key = (b:16 | x:16 | y:16 | z:16) of non-negative coordinates < 65536; slot value =
+// lowest row index with that key. Empty key = all ones.
+// ------------------------------------------------------------------------------------------------
+constexpr unsigned long long HASH_EMPTY = ~0ull;
+
+__device__ __forceinline__ unsigned long long voxel_key(int4 c) {
+  return ((unsigned long long)(c.x & 0xffff) << 48) | ((unsigned long long)(c.y & 0xffff) << 32) |
+         ((unsigned long long)(c.z & 0xffff) << 16) | (unsigned long long)(c.w & 0xffff);
+}
+__device__ __forceinline__ unsigned int hash64(unsigned long long k) {
+  k ^= k >> 33; k *= 0xff51afd7ed558ccdull; k ^= k >> 33; k *= 0xc4ceb9fe1a85ec53ull; k ^= k >> 33;
+  return (unsigned int)k;
+}
+__device__ __forceinline__ bool coord_ok(int4 c) {
+  return c.x >= 0 && c.y >= 0 && c.z >= 0 && c.w >= 0 && c.x < 65536 && c.y < 65536 && c.z < 65536 && c.w < 65536;
+}
+
+__global__ void hash_build_kernel(const int4* __restrict__ coords, int n, unsigned long long* __restrict__ keys,
+                                  int* __restrict__ vals, unsigned int cap_mask, int* status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int4 c = coords[i];
+  if (!coord_ok(c)) return;                                   // rows outside the key range are never found
+  const unsigned long long k = voxel_key(c);
+  unsigned int h = hash64(k) & cap_mask;
+  for (unsigned int probe = 0; probe <= cap_mask; ++probe) {
+    const unsigned long long prev = atomicCAS(&keys[h], HASH_EMPTY, k);
+    if (prev == HASH_EMPTY || prev == k) { atomicMin(&vals[h], i); return; }
+    h = (h + 1) & cap_mask;
+  }
+  set_status(status, KID_VISION, FF_ERR_CAPACITY, i, (int)cap_mask);
+}
+
+__device__ __forceinline__ int hash_find(const unsigned long long* __restrict__ keys, const int* __restrict__ vals,
+                                         unsigned int cap_mask, int4 c) {
+  if (!coord_ok(c)) return -1;
+  const unsigned long long k = voxel_key(c);
+  unsigned int h = hash64(k) & cap_mask;
+  for (unsigned int probe = 0; probe <= cap_mask; ++probe) {
+    const unsigned long long cur = keys[h];
+    if (cur == k) return vals[h];
+    if (cur == HASH_EMPTY) return -1;
+    h = (h + 1) & cap_mask;
+  }
+  return -1;
+}
+
+// nbr [n_off, n]: row of the site at coords[i] + offsets[o] (same batch), or -1
+__global__ void neighbor_map_kernel(const int4* __restrict__ coords, int n, const int4* __restrict__ offsets, int n_off,
+                                    const unsigned long long* __restrict__ keys, const int* __restrict__ vals,
+                                    unsigned int cap_mask, int* __restrict__ nbr) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= (long long)n * n_off) return;
+  const int o = (int)(gid / n), i = (int)(gid - (long long)o * n);
+  const int4 c = coords[i], d = offsets[o];
+  nbr[gid] = hash_find(keys, vals, cap_mask, make_int4(c.x, c.y + d.y, c.z + d.z, c.w + d.w));
+}
+
+// first[i] = 1 when row i is the lowest row with its key (unique-site selection)
+__global__ void hash_first_kernel(const int4* __restrict__ coords, int n, const unsigned long long* __restrict__ keys,
+                                  const int* __restrict__ vals, unsigned int cap_mask, int* __restrict__ first) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  first[i] = hash_find(keys, vals, cap_mask, coords[i]) == i ? 1 : 0;
+}
+
+// out [n, n_off * C]: block o of row i = feat[nbr[o, i]] or zeros. One thread per 16-byte vector.
+__global__ void __launch_bounds__(256)
+sparse_gather_kernel(const __nv_bfloat16* __restrict__ feat, const int* __restrict__ nbr, int n, int n_off, int C,
+                     int n_src, __nv_bfloat16* __restrict__ out, int* status) {
+  const int cvec = C >> 3;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)n * n_off * cvec;
+  if (gid >= total) return;
+  const int v = (int)(gid % cvec);
+  const int o = (int)((gid / cvec) % n_off);
+  const int i = (int)(gid / ((long long)cvec * n_off));
+  const int src = nbr[(size_t)o * n + i];
+  uint4 val = make_uint4(0u, 0u, 0u, 0u);
+  if (src >= n_src) set_status(status, KID_VISION, FF_ERR_BOUNDS, i, src);
+  else if (src >= 0) val = __ldg(reinterpret_cast<const uint4*>(feat + (size_t)src * C) + v);
+  reinterpret_cast<uint4*>(out + ((size_t)i * n_off + o) * C)[v] = val;
+}
+
+// coords[i] = (batch[i], floor((p - origin) / voxel)) when inside [0, dims), else (-1, -1, -1, -1)
+__global__ void voxelize_kernel(const float* __restrict__ pts, const int* __restrict__ batch, int n, float ox, float oy,
+                                float oz, float inv_voxel, int dx, int dy, int dz, int4* __restrict__ coords) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int x = (int)floorf((pts[3 * i] - ox) * inv_voxel);
+  const int y = (int)floorf((pts[3 * i + 1] - oy) * inv_voxel);
+  const int z = (int)floorf((pts[3 * i + 2] - oz) * inv_voxel);
+  const bool in = x >= 0 && y >= 0 && z >= 0 && x < dx && y < dy && z < dz;
+  coords[i] = in ? make_int4(batch ? batch[i] : 0, x, y, z) : make_int4(-1, -1, -1, -1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Hadamard rotate + INT8 quantise: one CTA (128 threads) per row, the row in shared memory as FP32.
+// Stage with stride s: every quadruple (i, i+s, i+2s, i+3s) inside a block of 4s -> H4 / 2 times it.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+rotate_quant_kernel(const __nv_bfloat16* __restrict__ x, int k, int group, int ldx, int8_t* __restrict__ codes,
+                    float* __restrict__ scales) {
+  extern __shared__ float rq_s[];
+  __shared__ float s_red[4];
+  const int row = blockIdx.x;
+  for (int i = threadIdx.x; i < k; i += 128) rq_s[i] = __bfloat162float(x[(size_t)row * ldx + i]);
+  __syncthreads();
+  for (int s = group >> 2; s >= 1; s >>= 2) {
+    for (int q = threadIdx.x; q < (k >> 2); q += 128) {
+      const int blk = q / s, in = q - blk * s;
+      const int i0 = blk * 4 * s + in;
+      const float a = rq_s[i0], b = rq_s[i0 + s], c = rq_s[i0 + 2 * s], d = rq_s[i0 + 3 * s];
+      // column j of H4 = [[1,1,1,-1],[1,1,-1,1],[1,-1,1,1],[-1,1,1,1]] applied to the row vector (a b c d)
+      rq_s[i0] = 0.5f * (a + b + c - d);
+      rq_s[i0 + s] = 0.5f * (a + b - c + d);
+      rq_s[i0 + 2 * s] = 0.5f * (a - b + c + d);
+      rq_s[i0 + 3 * s] = 0.5f * (-a + b + c + d);
+    }
+    __syncthreads();
+  }
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < k; i += 128) {
+    const float r = bfr_v(rq_s[i]);                            // the rotated activation is a BF16 value
+    rq_s[i] = r;
+    amax = fmaxf(amax, fabsf(r));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+  const float sc = fmaxf(amax, 1e-12f) / 127.f;
+  if (threadIdx.x == 0) scales[row] = sc;
+  for (int i = threadIdx.x; i < k; i += 128) {
+    const float q = rintf(rq_s[i] / sc);
+    codes[(size_t)row * k + i] = (int8_t)fminf(fmaxf(q, -127.f), 127.f);
+  }
+}
+
+// y[row, col] = bf16(dot_i32 * sx[row] * sw[col]); one warp per (row, 4 columns), lanes split k in 16-byte vectors
+__global__ void __launch_bounds__(256)
+int8_linear_kernel(const int8_t* __restrict__ qx, const float* __restrict__ sx, const int8_t* __restrict__ qw,
+                   const float* __restrict__ sw, __nv_bfloat16* __restrict__ y, int rows, int n, int k, int ldy) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int col_groups = (n + 3) >> 2;
+  if (warp >= rows * col_groups) return;
+  const int row = warp / col_groups, c0 = (warp - row * col_groups) * 4;
+  const int4* xv = reinterpret_cast<const int4*>(qx + (size_t)row * k);
+  int acc[4] = {0, 0, 0, 0};
+  for (int v = lane; v < (k >> 4); v += 32) {
+    const int4 a = xv[v];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (c0 + j < n) {
+        const int4 b = __ldg(reinterpret_cast<const int4*>(qw + (size_t)(c0 + j) * k) + v);
+        acc[j] = __dp4a(a.x, b.x, acc[j]); acc[j] = __dp4a(a.y, b.y, acc[j]);
+        acc[j] = __dp4a(a.z, b.z, acc[j]); acc[j] = __dp4a(a.w, b.w, acc[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+  }
+  if (lane < 4 && c0 + lane < n)
+    y[(size_t)row * ldy + c0 + lane] = __float2bfloat16((float)acc[lane] * sx[row] * sw[c0 + lane]);
+}
+
+}  // namespace ff
+using namespace ff;
+
+FF_EXPORT int ff_layernorm(const void* x, const void* w, const void* b, void* y, int rows, int hidden, int ldx, int ldy,
+                           float eps, cudaStream_t s) {
+  if (rows <= 0 || hidden <= 0 || hidden % 8 || hidden > 128 * 8 * LN_MAX_VEC || ldx % 8 || ldy % 8) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(layernorm_kernel, dim3(rows), dim3(128), 0, s, 0, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                          (const __nv_bfloat16*)b, (__nv_bfloat16*)y, hidden, ldx, ldy, eps)) return lr;
+  return launch_result();
+}
+
+FF_EXPORT int ff_bias_act(void* x, const void* bias, long long rows, int n, int ldx, int act, cudaStream_t s) {
+  if (rows <= 0 || n <= 0 || n % 8 || ldx % 8 || act < 0 || act > 4) return FF_HOST_BAD_SHAPE;
+  const long long total = rows * (n / 8);
+  if (int lr = launch_pdl(bias_act_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)x,
+                          (const __nv_bfloat16*)bias, rows, n, ldx, act)) return lr;
+  return launch_result();
+}
+
+// keys: uint64[capacity], vals: int32[capacity]; capacity a power of two >= 2 * n. Both are initialised here.
+FF_EXPORT int ff_voxel_hash_build(const int* coords, int n, unsigned long long* keys, int* vals, int capacity,
+                                  int* status, cudaStream_t s) {
+  if (n <= 0 || capacity < 2 * n || (capacity & (capacity - 1))) return FF_HOST_BAD_SHAPE;
+  cudaError_t e = cudaMemsetAsync(keys, 0xff, (size_t)capacity * 8, s);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemsetAsync(vals, 0x7f, (size_t)capacity * 4, s);
+  if (e != cudaSuccess) return (int)e;
+  hash_build_kernel<<<(n + 255) / 256, 256, 0, s>>>(reinterpret_cast<const int4*>(coords), n, keys, vals,
+                                                    (unsigned int)capacity - 1, status);
+  return launch_result();
+}
+
+FF_EXPORT int ff_voxel_neighbor_map(const int* coords, int n, const int* offsets, int n_off, const unsigned long long* keys,
+                                    const int* vals, int capacity, int* nbr, cudaStream_t s) {
+  if (n <= 0 || n_off <= 0 || (capacity & (capacity - 1))) return FF_HOST_BAD_SHAPE;
+  const long long total = (long long)n * n_off;
+  neighbor_map_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(reinterpret_cast<const int4*>(coords), n,
+      reinterpret_cast<const int4*>(offsets), n_off, keys, vals, (unsigned int)capacity - 1, nbr);
+  return launch_result();
+}
+
+FF_EXPORT int ff_voxel_first(const int* coords, int n, const unsigned long long* keys, const int* vals, int capacity,
+                             int* first, cudaStream_t s) {
+  if (n <= 0 || (capacity & (capacity - 1))) return FF_HOST_BAD_SHAPE;
+  hash_first_kernel<<<(n + 255) / 256, 256, 0, s>>>(reinterpret_cast<const int4*>(coords), n, keys, vals,
+                                                    (unsigned int)capacity - 1, first);
+  return launch_result();
+}
+
+FF_EXPORT int ff_sparse_gather(const void* feat, const int* nbr, int n, int n_off, int C, int n_src, void* out, int* status,
+                               cudaStream_t s) {
+  if (n <= 0 || n_off <= 0 || C <= 0 || C % 8) return FF_HOST_BAD_SHAPE;
+  const long long total = (long long)n * n_off * (C / 8);
+  sparse_gather_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)feat, nbr, n, n_off, C, n_src,
+                                                                       (__nv_bfloat16*)out, status);
+  return launch_result();
+}
+
+FF_EXPORT int ff_voxelize(const float* pts, const int* batch, int n, float ox, float oy, float oz, float voxel, int dx,
+                          int dy, int dz, int* coords, cudaStream_t s) {
+  if (n <= 0 || !(voxel > 0.f) || dx <= 0 || dy <= 0 || dz <= 0 || dx > 65536 || dy > 65536 || dz > 65536)
+    return FF_HOST_BAD_SHAPE;
+  voxelize_kernel<<<(n + 255) / 256, 256, 0, s>>>(pts, batch, n, ox, oy, oz, 1.0f / voxel, dx, dy, dz,
+                                                  reinterpret_cast<int4*>(coords));
+  return launch_result();
+}
+
+FF_EXPORT int ff_rotate_quant(const void* x, int rows, int k, int group, int ldx, signed char* codes, float* scales,
+                              cudaStream_t s) {
+  bool pow4 = group >= 4 && !(group & (group - 1));
+  if (pow4) { int t = 0; for (int g = group; g > 1; g >>= 1) ++t; pow4 = (t % 2) == 0; }
+  if (rows <= 0 || k <= 0 || !pow4 || k % group || k * 4 > 200 * 1024) return FF_HOST_BAD_SHAPE;
+  static int smem_set = 0;
+  if (k * 4 > 48 * 1024 && smem_set < k * 4) {
+    if (int r = opt_in_smem(rotate_quant_kernel, k * 4)) return r;
+    smem_set = k * 4;
+  }
+  rotate_quant_kernel<<<rows, 128, (size_t)k * 4, s>>>((const __nv_bfloat16*)x, k, group, ldx, (int8_t*)codes, scales);
+  return launch_result();
+}
+
+FF_EXPORT int ff_int8_linear(const signed char* qx, const float* sx, const signed char* qw, const float* sw, void* y,
+                             int rows, int n, int k, int ldy, cudaStream_t s) {
+  if (rows <= 0 || n <= 0 || k <= 0 || k % 16) return FF_HOST_BAD_SHAPE;
+  const long long warps = (long long)rows * ((n + 3) / 4);
+  int8_linear_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>((const int8_t*)qx, sx, (const int8_t*)qw, sw,
+                                                                           (__nv_bfloat16*)y, rows, n, k, ldy);
+  return launch_result();
+}

@@ -4,6 +4,7 @@ epilogue, deterministic combine -- ``csrc/moe.cu``."""
 from __future__ import annotations
 
 import os
+import weakref
 
 from ctypes import c_float
 
@@ -40,15 +41,20 @@ def interleave64(w_gate_up: torch.Tensor) -> torch.Tensor:
     return torch.cat([g, u], dim=2).reshape(e, two_f, h).contiguous()
 
 
-_i64_cache: dict[int, torch.Tensor] = {}
+_i64_cache: dict[int, tuple[weakref.ref, torch.Tensor]] = {}
 
 
 def _gu_interleaved(w_gate_up: torch.Tensor) -> torch.Tensor:
+    """Per-64 interleaved copy of an expert gate/up stack, cached per source tensor OBJECT: an address alone can be
+    reused by a later tensor of the same shape once the first one is freed."""
     key = w_gate_up.data_ptr()
-    t = _i64_cache.get(key)
-    if t is None or t.shape != w_gate_up.shape:
-        t = interleave64(w_gate_up)
-        _i64_cache[key] = t
+    hit = _i64_cache.get(key)
+    if hit is not None and hit[0]() is w_gate_up:
+        return hit[1]
+    for k in [k for k, (r, _) in _i64_cache.items() if r() is None]:
+        del _i64_cache[k]
+    t = interleave64(w_gate_up)
+    _i64_cache[key] = (weakref.ref(w_gate_up), t)
     return t
 
 

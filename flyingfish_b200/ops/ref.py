@@ -203,7 +203,7 @@ def attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
         s = torch.einsum("qhd,khd->hqk", qb, k) * scale
         pos_q = torch.arange(ql)[:, None] + (ctx - ql)
         pos_k = torch.arange(ctx)[None, :]
-        vis = pos_k <= pos_q
+        vis = pos_k <= pos_q if window >= 0 else torch.ones(ql, ctx, dtype=torch.bool)   # window < 0: bidirectional
         if window > 0:
             vis &= pos_k > pos_q - window
         if tree_mask is not None:

@@ -66,7 +66,8 @@ class Backend:
         self._thread.join(timeout=10)
 
     # -- called from the event loop thread --------------------------------------------------
-    def add_request(self, prompt: list[int], max_tokens: int, ignore_eos: bool = False) -> tuple[Request, asyncio.Queue]:
+    def add_request(self, prompt: list[int], max_tokens: int, ignore_eos: bool = False,
+                    images: list | None = None) -> tuple[Request, asyncio.Queue]:
         if self.state == "unavailable":
             raise Unavailable("engine is unavailable after an earlier failure")
         with self._lock:
@@ -74,7 +75,8 @@ class Backend:
                 raise Busy("busy: too many requests in flight")
             loop = asyncio.get_running_loop()
             q: asyncio.Queue = asyncio.Queue()
-            req = Request(prompt=prompt, max_tokens=max_tokens, eos_ids=self.eos_ids, ignore_eos=ignore_eos)
+            req = Request(prompt=prompt, max_tokens=max_tokens, eos_ids=self.eos_ids, ignore_eos=ignore_eos,
+                          images=images or None)
             req.on_tokens = self._on_tokens
             req.on_finish = self._on_finish
             self._inflight[req.req_id] = (req, q, loop)

@@ -90,9 +90,11 @@ def resolve_max_tokens(p: dict) -> int:
 
 class Server:
     def __init__(self, backend: Backend, tokenizer, model_name: str, chat_template: str | None = None,
-                 capacity: int = 4096, allow_sampling: bool = False):
+                 capacity: int = 4096, allow_sampling: bool = False, image_placeholder: str | None = None):
         self.backend, self.tk, self.model_name = backend, tokenizer, model_name
         self.capacity = capacity
+        # text of the image placeholder token (vision-language models only); None refuses image parts
+        self.image_placeholder = image_placeholder
         self.allow_sampling = allow_sampling
         self._seq = itertools.count()
         self.template = None
@@ -133,7 +135,9 @@ class Server:
             return list(prompt)
         raise bad_request("prompt must be a string or a flat array of token ids")
 
-    def _render_chat(self, messages, options: dict) -> str:
+    def _render_chat(self, messages, options: dict, images: list | None = None) -> str:
+        """``images`` collects the decoded images of ``image_url`` parts in prompt order; each leaves the model's
+        image placeholder in the text (models without a vision tower refuse image parts)."""
         if not isinstance(messages, list) or not messages:
             raise bad_request("messages must be a non-empty array")
         norm = []
@@ -153,10 +157,19 @@ class Server:
                         if not url.startswith("data:image/png;base64,") and not url.startswith("data:image/jpeg;base64,"):
                             raise bad_request("image_url must be a base64 data URL of a PNG or JPEG")
                         try:
-                            base64.b64decode(url.split(",", 1)[1], validate=True)
+                            raw = base64.b64decode(url.split(",", 1)[1], validate=True)
                         except Exception:
                             raise bad_request("image_url is not valid base64")
-                        raise bad_request("this model has no vision tower: image input is not supported")
+                        if self.image_placeholder is None or images is None:
+                            raise bad_request("this model has no vision tower: image input is not supported")
+                        if not url.startswith("data:image/png"):
+                            raise bad_request("only PNG images are decoded by this server")
+                        try:
+                            from .image import decode_png
+                            images.append(decode_png(raw))
+                        except Exception as e:
+                            raise bad_request(f"image_url does not decode: {e}")
+                        parts.append(self.image_placeholder)
                     else:
                         raise bad_request(f"unsupported content part type {part.get('type')!r}")
                 content = "".join(parts)
@@ -210,10 +223,15 @@ class Server:
             opts = body.get("chat_template_kwargs") or {}
             if not isinstance(opts, dict) or any(k != "enable_thinking" for k in opts):
                 raise bad_request("chat_template_kwargs only accepts enable_thinking")
-            text = self._render_chat(body.get("messages"), opts)
+            images: list = []
+            text = self._render_chat(body.get("messages"), opts, images)
             ids = self.tk.encode(text)
+            if images:
+                token = self.backend.engine.spec.extra.get("image_token_id")
+                if sum(1 for t in ids if t == token) != len(images):
+                    raise bad_request("the rendered prompt does not hold one image placeholder token per image")
             self._check_validity(ids, max_tokens)
-            return await self._respond(request, ids, max_tokens, bool(body.get("stream")), chat=True)
+            return await self._respond(request, ids, max_tokens, bool(body.get("stream")), chat=True, images=images)
         except HttpError as e:
             return e.response()
 
@@ -221,13 +239,13 @@ class Server:
         return f"{'chatcmpl' if chat else 'cmpl'}-{int(time.time())}-{next(self._seq)}"
 
     async def _respond(self, request: web.Request, ids: list[int], max_tokens: int, stream: bool,
-                       chat: bool) -> web.StreamResponse:
+                       chat: bool, images: list | None = None) -> web.StreamResponse:
         rid = self._new_id(chat)
         created = int(time.time())
         if max_tokens == 0:
             return web.json_response(self._final_body(rid, created, chat, "", "length", len(ids), 0))
         try:
-            req, q = self.backend.add_request(ids, max_tokens)
+            req, q = self.backend.add_request(ids, max_tokens, images=images)
         except Busy as e:
             return HttpError(409, str(e), etype="server_busy").response()
         except Unavailable as e:
@@ -322,8 +340,11 @@ def run(model, port: int = 8080, host: str = "127.0.0.1", allow_sampling: bool =
     tk = model.tokenizer or ByteTokenizer(model.spec.vocab)
     backend = Backend(model.engine, eos_ids=eos)
     backend.start()
+    placeholder = None
+    if getattr(model, "vision", None) is not None:
+        placeholder = tk.decode([int(model.spec.extra["image_token_id"])])
     server = Server(backend, tk, model.name, chat_template or getattr(tk, "chat_template", None),
-                    capacity=model.settings.capacity, allow_sampling=allow_sampling)
+                    capacity=model.settings.capacity, allow_sampling=allow_sampling, image_placeholder=placeholder)
     try:
         web.run_app(server.app(), host=host, port=port, print=None)
     finally:

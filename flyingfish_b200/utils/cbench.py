@@ -67,6 +67,7 @@ def main() -> None:
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--decode-rows", type=int, default=64)
     ap.add_argument("--prefill-rows", type=int, default=8192, help="total rows of the sequence-parallel prefill chunk")
+    ap.add_argument("--kernels", default="gemm_ar,ag_gemm,gemm_rs", help="comma-separated subset to run")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -95,7 +96,8 @@ def main() -> None:
 
     # ---- decode: row-parallel projection + all-reduce ---------------------------------------
     m = args.decode_rows
-    for (n, k_total, label) in [(h, h, "o_proj"), (h, f, "down_proj")]:
+    want = set(args.kernels.split(","))
+    for (n, k_total, label) in [(h, h, "o_proj"), (h, f, "down_proj")] if "gemm_ar" in want else []:
         k = k_total // world
         x, w = rnd(m, k), rnd(n, k)
         t = timed(lambda: comm.row_linear(x, w), args.iters, args.warmup, flush, device)
@@ -111,7 +113,7 @@ def main() -> None:
     # ---- prefill: all-gather -> GEMM (column-parallel) and GEMM -> reduce-scatter (row-parallel)
     mt = args.prefill_rows
     if comm.sp_ok(mt, h, h):
-        for (n_total, label) in [(3 * h // 2, "qkv"), (2 * f, "gate_up")]:
+        for (n_total, label) in [(3 * h // 2, "qkv"), (2 * f, "gate_up")] if "ag_gemm" in want else []:
             n = n_total // world
             xs, w = rnd(rpr, h), rnd(n, h)
             t = timed(lambda: comm.ag_linear(xs, w), max(args.iters // 3, 5), 3, flush, device)
@@ -121,7 +123,7 @@ def main() -> None:
             tu = timed(unfused_ag, max(args.iters // 3, 5), 3, flush, device)
             report("ag_gemm", f"{label} M{mt} N{n} K{h}", t, 2.0 * mt * n * h, (n * h + mt * h + mt * n) * 2.0,
                    (world - 1) * rpr * h * 2.0, tu)
-        for (k_total, label) in [(h, "o_proj"), (f, "down_proj")]:
+        for (k_total, label) in [(h, "o_proj"), (f, "down_proj")] if "gemm_rs" in want else []:
             k = k_total // world
             x, w = rnd(mt, k), rnd(h, k)
             t = timed(lambda: comm.rs_linear(x, w), max(args.iters // 3, 5), 3, flush, device)
