@@ -58,6 +58,11 @@ def _global_parser() -> argparse.ArgumentParser:
     g.add_argument("--dump")
     g.add_argument("--trace-layer", type=int, default=None)
     g.add_argument("--ignore-eos", action="store_true")
+    g.add_argument("--diffusion-steps", type=int, default=0,
+                   help="masked-diffusion models: number of denoising passes (default: one per 4 new tokens)")
+    g.add_argument("--diffusion-block", type=int, default=0, help="denoise the canvas in blocks of this many tokens")
+    g.add_argument("--image", action="append", default=[],
+                   help="PNG file for each image placeholder of the prompt (vision-language models)")
 
     s = sub.add_parser("serve")
     s.add_argument("--port", type=int, default=8080)
@@ -189,6 +194,17 @@ def cmd_generate(args) -> dict:
         from .utils.trace import Trace
         trace = Trace(device=str(model.engine.device), only_layer=args.trace_layer)
         model.engine.model.trace = trace
+    if model.spec.arch == "diffusion_lm":
+        from .spec.diffusion import DiffusionTrace, diffusion_generate
+        tr = DiffusionTrace()
+        steps = args.diffusion_steps or max(1, args.max_new_tokens // 4)
+        toks = diffusion_generate(model, ids, args.max_new_tokens, steps, block=args.diffusion_block or None, trace=tr)
+        return {"mode": "diffusion", "tokens": toks, "text": tk.decode(toks), "passes": tr.passes}
+    if args.image:
+        from .serve.image import decode_png
+        first = model.prefill_multimodal(ids, [decode_png(Path(f).read_bytes()) for f in args.image])
+        toks = [first] + [model.decode() for _ in range(args.max_new_tokens - 1)]
+        return {"mode": "multimodal", "tokens": toks, "text": tk.decode(toks), "images": len(args.image)}
     depth = resolve_mtp_depth(args.mtp, model.spec.mtp_layers > 0, model.spec.arch)
     mode = "plain"
     extra = {}
@@ -315,8 +331,13 @@ def cmd_embed(args) -> dict:
     from .loaders.tokenizer import ByteTokenizer
     model = _load(args)
     tk = model.tokenizer or ByteTokenizer(model.spec.vocab)
-    from .models.embedding import embed_text
-    vec = embed_text(model, tk.encode(args.prompt))
+    if model.spec.extra.get("bidirectional"):
+        # embedding encoders: bidirectional attention, mean pooling, dense head, L2 normalisation
+        from .models.encoder import embed_texts
+        vec = [float(v) for v in embed_texts(model, [tk.encode(args.prompt)])[0].cpu().tolist()]
+    else:
+        from .models.embedding import embed_text
+        vec = embed_text(model, tk.encode(args.prompt))
     return {"dim": len(vec), "embedding": vec}
 
 

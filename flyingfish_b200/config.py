@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl | embedding | diffusion_lm
     layers: int
     hidden: int
     heads: int
@@ -175,8 +175,24 @@ def tiny_vl() -> ModelSpec:
     return spec
 
 
+def tiny_embed() -> ModelSpec:
+    """Small bidirectional text encoder (embedding model): mean pooling, optional dense head, L2 normalisation."""
+    spec = tiny_llama()
+    spec.name, spec.arch = "tiny-embed", "embedding"
+    spec.extra = {"bidirectional": True, "embed_dense": [1024, 256]}
+    return spec
+
+
+def tiny_diffusion() -> ModelSpec:
+    """Small masked-diffusion language model: a bidirectional decoder stack that denoises a canvas of mask tokens."""
+    spec = tiny_llama()
+    spec.name, spec.arch = "tiny-diffusion", "diffusion_lm"
+    spec.extra = {"bidirectional": True, "mask_token_id": 2046}
+    return spec
+
+
 NAMED_SHAPES = {
-    "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
+    "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }

@@ -55,6 +55,9 @@ class DecoderModel:
         self.capture_slab: torch.Tensor | None = None
         self.normed_sink: list | None = None      # when a list: every forward appends its final-normed rows
         self._rope_cs: torch.Tensor | None = None  # per-forward cos/sin table of the fused QKV kernels
+        # encoders and diffusion language models attend in both directions inside a sequence; they run whole
+        # sequences in one prefill chunk and never decode
+        self.bidirectional = bool(self.spec.extra.get("bidirectional"))
 
     # -- pieces ----------------------------------------------------------------------------
     def _attention(self, i: int, n: torch.Tensor, b: ForwardBatch, kv: PagedKVCache) -> torch.Tensor:
@@ -71,7 +74,7 @@ class DecoderModel:
                                 self.scale, nq=b.nq, tree_mask=b.tree_mask, max_ctx=b.max_ctx)
         else:
             a = ops.attn_prefill(qkv, kv.k[i], kv.v[i], b.block_table, b.q_start, b.q_lens, b.ctx_lens, b.max_q_len,
-                                 self.hq, self.hkv, self.d, self.scale)
+                                 self.hq, self.hkv, self.d, self.scale, window=-1 if self.bidirectional else 0)
         if self.trace is not None:
             self.trace.record(f"layer.{i}.attn", a)
         return self.comm.row_linear(a, lw.wo)
@@ -136,6 +139,8 @@ class DecoderModel:
     def _sequence_parallel(self, b: ForwardBatch) -> bool:
         c = self.comm
         if getattr(c, "size", 1) < 2 or b.is_decode or not getattr(c, "fused", False) or self.trace is not None:
+            return False
+        if self.bidirectional:
             return False
         if any(lw.router is not None or not lw.wgu_interleaved for lw in self.w.layers) or self.spec.qk_norm:
             return False
