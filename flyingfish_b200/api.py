@@ -81,6 +81,9 @@ class Model:
         if spec.mla is not None:
             from .models.deepseek import DeepseekModel
             net = DeepseekModel(weights, comm=comm)
+        elif spec.extra.get("gdn"):
+            from .models.hybrid import HybridModel
+            net = HybridModel(weights, comm=comm, max_sequences=settings.max_batch, seed=seed)
         else:
             net = DecoderModel(weights, comm=comm)
         if ep is not None:

@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl | embedding | diffusion_lm
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text
     layers: int
     hidden: int
     heads: int
@@ -191,8 +191,16 @@ def tiny_diffusion() -> ModelSpec:
     return spec
 
 
+def tiny_hybrid() -> ModelSpec:
+    """Small hybrid shape: gated-delta-net mixers with full attention in every fourth layer."""
+    spec = tiny_llama()
+    spec.name, spec.arch, spec.layers = "tiny-hybrid", "qwen35_text", 4
+    spec.extra = {"gdn": {"v_heads": 4, "k_heads": 2, "full_attention_interval": 4}}
+    return spec
+
+
 NAMED_SHAPES = {
-    "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
+    "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }

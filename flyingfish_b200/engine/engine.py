@@ -46,6 +46,7 @@ class Sequence:
     prefilled: int = 0                 # prompt tokens whose KV is committed
     pending: int | None = None         # token sampled but not yet fed through the model
     finished: bool = False
+    state_slot: int = -1               # slot of the per-sequence recurrent state (hybrid linear-attention models)
     mm_positions: list[int] | None = None      # prompt indices whose embedding row comes from ``mm_embeds``
     mm_embeds: torch.Tensor | None = None      # [len(mm_positions), hidden] (vision-tower output)
 
@@ -85,6 +86,13 @@ class Engine:
         self._next_id = 0
         self.poisoned = False
         self.use_graph = settings.graph and self.device.type == "cuda"
+        # models with per-sequence recurrent state (gated-delta-net mixers) address it by slot; the last slot
+        # is scratch for the padding rows of a decode bucket. Their step is not graph-captured.
+        self.state_slots: list[int] | None = None
+        if getattr(model, "state_slot_count", 0):
+            self.state_slots = list(range(model.state_slot_count - 1))
+            self.scratch_slot = model.state_slot_count - 1
+            self.use_graph = False
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "decode_tokens": 0, "graph_replays": 0,
                       "captures": 0, "h2d_bytes": 0, "d2h_bytes": 0}
         self.fail_next_step = False      # host-side fault injection hook for tests
@@ -106,12 +114,20 @@ class Engine:
             if mm_embeds is None or mm_embeds.shape[0] != len(mm_positions) or mm_embeds.shape[1] != self.spec.hidden:
                 raise ValueError("mm_embeds must hold one hidden-sized row per mm position")
             s.mm_positions, s.mm_embeds = list(mm_positions), mm_embeds
+        if self.state_slots is not None:
+            if not self.state_slots:
+                raise ValueError("no free recurrent-state slot: too many live sequences")
+            s.state_slot = self.state_slots.pop()
+            self.model.reset_state(s.state_slot)
         self.seqs[sid] = s
         self.kv.add_sequence(sid)
         return s
 
     def free_sequence(self, seq_id: int) -> None:
-        self.seqs.pop(seq_id, None)
+        s = self.seqs.pop(seq_id, None)
+        if s is not None and self.state_slots is not None and s.state_slot >= 0:
+            self.state_slots.append(s.state_slot)
+            s.state_slot = -1
         if seq_id in self.kv.seqs:
             self.kv.free_sequence(seq_id)
 
@@ -119,6 +135,8 @@ class Engine:
         for sid in list(self.kv.seqs):
             self.kv.free_sequence(sid)
         self.seqs.clear()
+        if self.state_slots is not None:
+            self.state_slots = list(range(self.model.state_slot_count - 1))
         self.poisoned = False
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
@@ -183,6 +201,7 @@ class Engine:
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
                 logit_rows=logit_rows, is_decode=False)
         fb.upload()
+        fb.state_slots = [s.state_slot for s, _ in part]
         out = self.model.forward(fb, self.kv, inputs_embeds=self._mm_embeds(part, fb, len(ids)))
         toks = [int(t) for t in out.cpu().tolist()]
         self._after_sync()
@@ -229,6 +248,8 @@ class Engine:
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
                 logit_rows=list(range(bucket)), is_decode=True, nq=1)
         fb.max_ctx = self.settings.capacity      # fixed launch geometry (graph-stable)
+        if self.state_slots is not None:
+            fb.state_slots = [s.state_slot for s in seqs] + [self.scratch_slot] * pad
 
     def _decode_batch(self, bucket: int) -> ForwardBatch:
         fb = self.eager_decode_batch.get(bucket)

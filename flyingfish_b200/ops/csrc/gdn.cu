@@ -45,6 +45,32 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
   if (commit) { history[c * 3] = h0; history[c * 3 + 1] = h1; history[c * 3 + 2] = h2; }
 }
 
+// Batched form: sequence s owns rows row_start[s] .. row_start[s+1] of x (row pitch ldx elements) and the history
+// slab history[slot[s]] ([channels, 3] f32 each). grid (channel blocks, sequences).
+__global__ void gdn_conv_batched_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ weight,
+                                        float* __restrict__ history, __nv_bfloat16* __restrict__ out,
+                                        const int* __restrict__ row_start, const int* __restrict__ slot, int channels,
+                                        int ldx, int commit) {
+  pdl_trigger();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
+  if (c >= channels) return;
+  float w[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) w[t] = __bfloat162float(weight[c * 4 + t]);
+  float* hist = history + ((size_t)slot[s] * channels + c) * 3;
+  float h0 = hist[0], h1 = hist[1], h2 = hist[2];
+  for (int r = row_start[s]; r < row_start[s + 1]; ++r) {
+    const float cur = __bfloat162float(x[(size_t)r * ldx + c]);
+    float acc = 0.f;
+    acc = fmaf(w[0], h0, acc); acc = fmaf(w[1], h1, acc); acc = fmaf(w[2], h2, acc); acc = fmaf(w[3], cur, acc);
+    const float y = gdn_bf16r(acc);
+    out[(size_t)r * channels + c] = __float2bfloat16_rn(y / (1.0f + expf(-y)));
+    h0 = h1; h1 = h2; h2 = cur;
+  }
+  if (commit) { hist[0] = h0; hist[1] = h1; hist[2] = h2; }
+}
+
 // conv_out [rows, (2*kheads + heads) * 128] bf16 = q | k | v ; q,k have kheads heads. Writes FP32 q, k
 // [rows, heads, 128] (expanded to value heads, normalised, q scaled) and v [rows, heads, 128].
 __global__ void gdn_prep_kernel(const __nv_bfloat16* __restrict__ conv_out, float* __restrict__ q, float* __restrict__ k,
@@ -77,12 +103,14 @@ __global__ void gdn_prep_kernel(const __nv_bfloat16* __restrict__ conv_out, floa
 __global__ void __launch_bounds__(128)
 gdn_recurrent_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                      const float* __restrict__ beta, const float* __restrict__ g, float* __restrict__ S,
-                     __nv_bfloat16* __restrict__ out, const int* __restrict__ row_start, int heads) {
+                     __nv_bfloat16* __restrict__ out, const int* __restrict__ row_start, int heads,
+                     const int* __restrict__ state_slot) {
   pdl_trigger();
   pdl_wait();
   __shared__ float sq[GDN_D], sk[GDN_D];
   const int h = blockIdx.x, s = blockIdx.y, j = threadIdx.x;
-  float* Sp = S + (((size_t)s * heads + h) * GDN_D) * GDN_D + j;     // column j: element kk at Sp[kk * 128]
+  const int ss = state_slot ? state_slot[s] : s;              // state slab of this sequence
+  float* Sp = S + (((size_t)ss * heads + h) * GDN_D) * GDN_D + j;     // column j: element kk at Sp[kk * 128]
   float st[GDN_D];
 #pragma unroll
   for (int kk = 0; kk < GDN_D; ++kk) st[kk] = Sp[(size_t)kk * GDN_D];
@@ -128,6 +156,25 @@ FF_EXPORT int ff_gdn_recurrent(const float* q, const float* k, const float* v, c
                                void* out, const int* row_start, int sequences, int heads, cudaStream_t s) {
   if (sequences <= 0 || heads <= 0) return FF_HOST_BAD_SHAPE;
   if (int lr = launch_pdl(gdn_recurrent_kernel, dim3(heads, sequences), dim3(128), 0, s, 0, q, k, v, beta, g, S,
-                          (__nv_bfloat16*)out, row_start, heads)) return lr;
+                          (__nv_bfloat16*)out, row_start, heads, (const int*)nullptr)) return lr;
+  return launch_result();
+}
+
+// Batched forms for a model's forward: sequences address their state through slot indices.
+FF_EXPORT int ff_gdn_recurrent_slots(const float* q, const float* k, const float* v, const float* beta, const float* g,
+                                     float* S, void* out, const int* row_start, const int* state_slot, int sequences,
+                                     int heads, cudaStream_t s) {
+  if (sequences <= 0 || heads <= 0 || !state_slot) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(gdn_recurrent_kernel, dim3(heads, sequences), dim3(128), 0, s, 0, q, k, v, beta, g, S,
+                          (__nv_bfloat16*)out, row_start, heads, state_slot)) return lr;
+  return launch_result();
+}
+
+FF_EXPORT int ff_gdn_conv_batched(const void* x, const void* weight, float* history, void* out, const int* row_start,
+                                  const int* slot, int sequences, int channels, int ldx, int commit, cudaStream_t s) {
+  if (sequences <= 0 || channels <= 0 || ldx < channels) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(gdn_conv_batched_kernel, dim3((channels + 255) / 256, sequences), dim3(256), 0, s, 0,
+                          (const __nv_bfloat16*)x, (const __nv_bfloat16*)weight, history, (__nv_bfloat16*)out, row_start,
+                          slot, channels, ldx, commit)) return lr;
   return launch_result();
 }

@@ -70,3 +70,45 @@ def recurrent(q, k, v, beta, g, state: torch.Tensor, row_start: torch.Tensor) ->
                                      row_start.numel() - 1, heads, stream_ptr()), "ff_gdn_recurrent")
     _count()
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# batched forms used by a model's forward: packed rows of several sequences, state addressed by slot
+# ------------------------------------------------------------------------------------------------
+def conv_batched(x: torch.Tensor, weight: torch.Tensor, history: torch.Tensor, row_start: torch.Tensor,
+                 slots: torch.Tensor, commit: bool = True) -> torch.Tensor:
+    """x [rows, >= channels] bf16 (the first ``channels`` columns are convolved), history [slots, channels, 3] f32,
+    row_start [sequences + 1] / slots [sequences] int32 -> [rows, channels] bf16."""
+    ch = weight.shape[0]
+    if not x.is_cuda:
+        out = torch.empty(x.shape[0], ch, dtype=BF16)
+        for s in range(slots.numel()):
+            r0, r1 = int(row_start[s]), int(row_start[s + 1])
+            if r1 > r0:
+                out[r0:r1] = conv(x[r0:r1, :ch].contiguous(), weight, history[int(slots[s])], commit)
+        return out
+    out = torch.empty(x.shape[0], ch, dtype=BF16, device=x.device)
+    check(kernels().ff_gdn_conv_batched(ptr(x), ptr(weight), ptr(history), ptr(out), ptr(row_start), ptr(slots),
+                                        slots.numel(), ch, x.stride(0), int(commit), stream_ptr()), "ff_gdn_conv_batched")
+    _count()
+    return out
+
+
+def recurrent_slots(q, k, v, beta, g, state: torch.Tensor, row_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """Like :func:`recurrent` with sequence s using ``state[slots[s]]``."""
+    if not q.is_cuda:
+        rows, heads, _ = q.shape
+        out = torch.zeros(rows, heads, D, dtype=BF16)
+        for s in range(slots.numel()):
+            r0, r1 = int(row_start[s]), int(row_start[s + 1])
+            if r1 > r0:
+                sl = int(slots[s])
+                out[r0:r1] = recurrent(q[r0:r1], k[r0:r1], v[r0:r1], beta[r0:r1], g[r0:r1], state[sl: sl + 1],
+                                       torch.tensor([0, r1 - r0], dtype=torch.int32))
+        return out
+    rows, heads, _ = q.shape
+    out = torch.empty(rows, heads, D, dtype=BF16, device=q.device)
+    check(kernels().ff_gdn_recurrent_slots(ptr(q), ptr(k), ptr(v), ptr(beta), ptr(g), ptr(state), ptr(out), ptr(row_start),
+                                           ptr(slots), slots.numel(), heads, stream_ptr()), "ff_gdn_recurrent_slots")
+    _count()
+    return out
