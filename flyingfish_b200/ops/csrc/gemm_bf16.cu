@@ -99,9 +99,9 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 //       ranks' rows from the LOCAL arena copy once the block's flag is there; own rows are scheduled
 //       first so the transfer overlaps the math.
 //   2 = GEMM -> reduce-scatter : every finished tile goes into the arena slot of the rank that owns
-//       those rows. The epilogue stages 64 columns at a time through shared memory so that each row
-//       leaves as 128 contiguous bytes (16-byte peer stores scattered over rows waste most of a
-//       NVLink packet); when all column tiles of a row block are out, its flag goes to the owner.
+//       those rows. The epilogue stages 64 columns at a time through shared memory and every lane hands
+//       its row to the copy engine as one 128-byte bulk store (cp.async.bulk shared -> peer global).
+//       When all column tiles of a row block are out, its flag goes to the owner.
 //       After its tiles every CTA reduces quarter row blocks this rank owns: waits for the block's
 //       flags from all ranks and sums the slots in rank order.
 struct CommArgs {
@@ -121,6 +121,7 @@ __device__ __forceinline__ int comm_tm(int tm, int tiles_per_rank, int rank, int
   return ((rank + j) % world) * tiles_per_rank + r;
 }
 
+constexpr int RS_STG_PITCH = 144, RS_STG_BYTES = 32 * RS_STG_PITCH;   // COMM 2 epilogue staging, per warp
 constexpr int COMM_PARTS = 4;       // a 128-row block is pushed (COMM 1) / reduced (COMM 2) in this many pieces
 
 template <int BN, int STAGES, int COMM>
@@ -290,14 +291,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + (size_t)row * ldc + (size_t)tn * BN;
         if (COMM == 2) {
           // the rows of this tile belong to rank `owner`: they go into its arena slot for source = me,
-          // 64 columns at a time through a warp-private staging tile [32 rows][128 bytes] (16-byte
-          // chunks XORed by row % 8) so that eight lanes write one row's 128 contiguous bytes
+          // 64 columns at a time through a warp-private staging tile
           const int owner = tm / tiles_per_rank;
           __nv_bfloat16* tile_dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ca.ar, owner, parity, ca.ar.rank)) +
                                     (size_t)(tm * BM + q * 32 - owner * ca.rows_per_rank) * N + (size_t)tn * BN;
-          uint4* stg = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + q * 4096);
+          // staging: lane = row, 64 columns (128 bytes) per pass at a 144-byte pitch (16-byte stores of the 32
+          // lanes then fall into distinct bank groups). Each lane hands its own row to the copy engine as one
+          // 128-byte bulk store; the staging row is reused as soon as the engine has READ it.
+          uint8_t* stg = smem + STAGES * STAGE_BYTES + q * RS_STG_BYTES + lane * RS_STG_PITCH;
+          const bool row_ok = tm * BM + q * 32 + lane < M;
 #pragma unroll 1
           for (int c = 0; c < BN; c += 64) {
+            if (c) tma_store_wait_read<0>();
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               uint32_t r[32];
@@ -305,22 +310,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                stg[lane * 8 + ((4 * h + j) ^ (lane & 7))] =
+                reinterpret_cast<uint4*>(stg)[4 * h + j] =
                     make_uint4(pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1])),
                                pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
                                pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
                                pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
             }
-            __syncwarp();
-#pragma unroll
-            for (int it8 = 0; it8 < 8; ++it8) {
-              const int rr = 4 * it8 + (lane >> 3), ch = lane & 7;
-              const int col = tn * BN + c + ch * 8;
-              if (tm * BM + q * 32 + rr < M && col < N)
-                *reinterpret_cast<uint4*>(tile_dst + (size_t)rr * N + c + ch * 8) = stg[rr * 8 + (ch ^ (rr & 7))];
+            fence_proxy_async_smem();
+            const int col = tn * BN + c;
+            if (row_ok && col + 64 <= N) {
+              bulk_store(tile_dst + (size_t)lane * N + c, stg, 128);
+            } else if (row_ok) {
+              for (int ch = 0; ch < 8; ++ch)
+                if (col + ch * 8 < N)
+                  *reinterpret_cast<uint4*>(tile_dst + (size_t)lane * N + c + ch * 8) = reinterpret_cast<uint4*>(stg)[ch];
             }
-            __syncwarp();
+            tma_store_commit();
           }
+          tma_store_wait<0>();                              // every row of this tile has landed in the owner's slot
+          asm volatile("fence.proxy.async;" ::: "memory");
         } else
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -363,7 +371,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     if (COMM == 2 && ok) {
       // reduce the row blocks this rank owns, a quarter block per step and CTA: slots of all source
-      // ranks, in rank order, four 16-byte vectors of every slot in flight per thread
+      // ranks, in rank order, sixteen 16-byte vectors in flight per thread
       const int nvec = N >> 3;
       const int blk_vecs = BM * nvec, piece = (blk_vecs + COMM_PARTS - 1) / COMM_PARTS;
       for (int part = blockIdx.x; part < tiles_per_rank * COMM_PARTS; part += gridDim.x) {
@@ -375,26 +383,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (bars.is_last) {
           const int v0 = ps * piece, v1 = min(blk_vecs, v0 + piece);
-          for (int base = v0 + e; base < v1; base += 128 * 4) {
-            float a8[4][8];
+          // eight vectors per thread and slot, the next slot's loads issued before the current one is summed:
+          // with one CTA per SM the reduction is bound by loads in flight, not by bandwidth
+          constexpr int U = 8;
+          for (int base = v0 + e; base < v1; base += 128 * U) {
+            float a8[U][8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < U; ++u)
 #pragma unroll
               for (int j = 0; j < 8; ++j) a8[u][j] = 0.f;
+            uint4 cur[U], nxt[U];
+            const uint4* slot0 = reinterpret_cast<const uint4*>(arena_slot(ca.ar, ca.ar.rank, parity, 0)) + (size_t)i * blk_vecs;
+#pragma unroll
+            for (int u = 0; u < U; ++u) cur[u] = (base + 128 * u < v1) ? __ldcg(slot0 + base + 128 * u) : make_uint4(0, 0, 0, 0);
             for (int r = 0; r < ca.ar.world; ++r) {
-              const uint4* slot = reinterpret_cast<const uint4*>(arena_slot(ca.ar, ca.ar.rank, parity, r)) + (size_t)i * blk_vecs;
-              uint4 d[4];
+              if (r + 1 < ca.ar.world) {
+                const uint4* slot = reinterpret_cast<const uint4*>(arena_slot(ca.ar, ca.ar.rank, parity, r + 1)) + (size_t)i * blk_vecs;
 #pragma unroll
-              for (int u = 0; u < 4; ++u) d[u] = (base + 128 * u < v1) ? slot[base + 128 * u] : make_uint4(0, 0, 0, 0);
+                for (int u = 0; u < U; ++u) nxt[u] = (base + 128 * u < v1) ? __ldcg(slot + base + 128 * u) : make_uint4(0, 0, 0, 0);
+              }
 #pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const uint32_t* dp = reinterpret_cast<const uint32_t*>(&d[u]);
+              for (int u = 0; u < U; ++u) {
+                const uint32_t* dp = reinterpret_cast<const uint32_t*>(&cur[u]);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { const float2 f = unpack_bf16x2(dp[j]); a8[u][2 * j] += f.x; a8[u][2 * j + 1] += f.y; }
               }
+#pragma unroll
+              for (int u = 0; u < U; ++u) cur[u] = nxt[u];
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < U; ++u)
               if (base + 128 * u < v1) {
                 uint4 o;
                 o.x = pack_bf16x2(a8[u][0], a8[u][1]); o.y = pack_bf16x2(a8[u][2], a8[u][3]);
@@ -593,7 +611,7 @@ FF_EXPORT int ff_gemm_rs(const unsigned long long* ptrs, int rank, int world, lo
   if (r) return r;
   r = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, BK, BN);
   if (r) return r;
-  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * 4096 + 1024;   // + staging tiles of the epilogue warps
+  const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * RS_STG_BYTES + 1024;   // + staging of the epilogue warps
   auto kern = gemm_bf16_kernel<BN, STAGES, 2>;
   static bool attr_done = false;
   if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }

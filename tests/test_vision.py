@@ -245,14 +245,25 @@ def test_http_chat_with_image():
 
 
 @cuda
-def test_multimodal_gpu_matches_cpu():
+def test_multimodal_gpu():
+    """The decoder's random weights are drawn on the device they live on, so CPU and GPU models differ; what must
+    agree is the tower (same host-drawn weights) and the GPU path with itself."""
     from flyingfish_b200.serve.image import decode_png
-    img = decode_png(_png(96, 64, 4))
+    img, other = decode_png(_png(96, 64, 4)), decode_png(_png(96, 64, 5))
     tok = 2047
     ids = [5, 6, tok, 7, 8]
     cpu, gpu = _vl_model(), _vl_model("cuda")
-    la, lb = _last_logits(cpu, ids, img), _last_logits(gpu, ids, img)
-    cos = torch.nn.functional.cosine_similarity(la.flatten(), lb.flatten(), dim=0).item()
-    assert cos > 0.995 and (la - lb).abs().max() < 0.15 * la.abs().max(), (cos, (la - lb).abs().max().item(), la.abs().max().item())
+    ec, pc, mc = cpu.encode_images(ids, [img])
+    eg, pg, mg = gpu.encode_images(ids, [img])
+    assert ec == eg and pc == pg
+    cos = torch.nn.functional.cosine_similarity(mc.float().flatten(), mg.float().cpu().flatten(), dim=0).item()
+    assert cos > 0.999, cos
     first = gpu.prefill_multimodal(ids, [img])
-    assert isinstance(first, int) and [gpu.decode() for _ in range(3)]
+    rest = [gpu.decode() for _ in range(3)]
+    gpu.engine.settings.chunk = 16
+    assert gpu.prefill_multimodal(ids, [img]) == first and [gpu.decode() for _ in range(3)] == rest
+    gpu.engine.settings.chunk = 0
+    la, lb = _last_logits(gpu, ids, img), _last_logits(gpu, ids, other)
+    assert (la - lb).abs().max() > 1e-3
+    from flyingfish_b200 import ops
+    ops.check_status()
