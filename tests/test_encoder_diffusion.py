@@ -58,12 +58,19 @@ def test_diffusion_commits_every_position_by_confidence():
 
 
 @pytest.mark.gpu
-def test_bidirectional_gpu_matches_cpu():
-    ids = [[5, 6, 7, 8, 9, 10, 11] * 11, [3, 4, 5]]
-    a = run_whole(_load("tiny-embed"), ids)
-    b = run_whole(_load("tiny-embed", "cuda"), ids)
-    for x, y in zip(a, b):
-        cos = torch.nn.functional.cosine_similarity(x.float().flatten(), y.float().cpu().flatten(), dim=0).item()
-        assert cos > 0.995, cos
+def test_bidirectional_gpu():
+    """(The decoder's random weights are drawn on the device they live on, so a CPU and a GPU model differ: the GPU
+    path is checked against itself; the bidirectional kernel against its oracle in tests/test_vision.py.)"""
+    m = _load("tiny-embed", "cuda")
+    long = [5, 6, 7, 8, 9, 10, 11] * 11
+    a = run_whole(m, [long, [3, 4, 5]])
+    b = run_whole(m, [long[:-1] + [99]])
+    assert (a[0][0].float() - b[0][0].float()).abs().max() > 1e-3          # row 0 sees the last token
+    alone = run_whole(m, [[3, 4, 5]])[0]
+    assert torch.allclose(a[1].float(), alone.float(), atol=2e-2)          # packed sequences do not mix
+    e = embed_texts(m, [long, [3, 4, 5]])
+    assert all(abs(float(v.norm()) - 1.0) < 1e-3 for v in e)
     out = diffusion_generate(_load("tiny-diffusion", "cuda"), [11, 12, 13], length=8, steps=4)
     assert len(out) == 8 and 2046 not in out
+    from flyingfish_b200 import ops
+    ops.check_status()

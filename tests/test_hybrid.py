@@ -55,5 +55,9 @@ def test_hybrid_gpu_runs_and_is_self_consistent():
     assert m.prefill(prompt + out[:3]) == out[3]
     from flyingfish_b200 import ops
     ops.check_status()
-    cpu = generate_plain(_load(), prompt, 6, ignore_eos=True, graph=False).ids
-    assert sum(int(x == y) for x, y in zip(cpu, out)) >= 4      # bf16 kernels vs FP32-accumulating oracles
+    # (CPU and GPU models draw different random weights; the GDN kernels meet their oracles in tests/test_gdn.py)
+    m.reset()
+    a, b = [5, 9, 100, 33], [7, 7, 8, 250, 11, 12, 90]
+    together = m.generate_batch([a, b], 5)
+    m.reset()
+    assert together[0] == generate_plain(m, a, 5, ignore_eos=True, graph=False).ids
