@@ -7,6 +7,7 @@ calls (``generate_batch``) expose continuous batching.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -78,6 +79,10 @@ class Model:
             else:
                 weights = random_decoder_weights(spec, seed, device, tp, epi)
             name = spec.name
+        if (spec.moe is not None and spec.moe.expert_format == "nvfp4" and device.type == "cuda" and spec.mla is None
+                and ep is None and os.environ.get("FLYINGFISH_FP4_EXPERTS", "1") != "0"):
+            from .ops.moe_cuda import pack_experts_nvfp4
+            log_json("nvfp4_experts_packed", verbose_only=True, bytes=pack_experts_nvfp4(weights))
         if spec.mla is not None:
             from .models.deepseek import DeepseekModel
             net = DeepseekModel(weights, comm=comm)

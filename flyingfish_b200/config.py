@@ -199,8 +199,16 @@ def tiny_hybrid() -> ModelSpec:
     return spec
 
 
+def qwen3_moe_fp4_tiny() -> ModelSpec:
+    """The tiny MoE shape with NVFP4 experts (decode reads the packed experts, prefill their BF16 expansion)."""
+    spec = qwen3_moe_tiny()
+    spec.name = "qwen3-moe-fp4-tiny"
+    spec.moe.expert_format = "nvfp4"
+    return spec
+
+
 NAMED_SHAPES = {
-    "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
+    "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }

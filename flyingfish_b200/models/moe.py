@@ -15,6 +15,11 @@ from .. import ops
 from ..ops import moe_ops
 
 
+def moe_cuda_mod():
+    from ..ops import moe_cuda
+    return moe_cuda
+
+
 def moe_ffn(model, layer: int, n: torch.Tensor) -> torch.Tensor:
     lw = model.w.layers[layer]
     moe = model.spec.moe
@@ -27,8 +32,13 @@ def moe_ffn(model, layer: int, n: torch.Tensor) -> torch.Tensor:
         routed = ep.dispatch_ffn_combine(n, weights, ids, lw, model.spec.swiglu_mode)
     else:
         provider = getattr(model, "expert_provider", None)
+        fp4 = lw.extra.get("experts_fp4")
         if provider is not None:
             routed = provider.forward(layer, n, weights, ids)
+        elif (fp4 is not None and n.is_cuda
+              and n.shape[0] * moe.top_k <= moe_cuda_mod().FP4_DECODE_MAX_ROWS * fp4[0].experts):
+            # decode-sized call: packed NVFP4 experts expanded inside the grouped GEMM (a quarter of the bytes)
+            routed = moe_cuda_mod().experts_forward_nvfp4(n, weights, ids, fp4[0], fp4[1])
         else:
             routed = moe_ops.experts_forward(n, weights, ids, lw.experts_gu, lw.experts_down, model.spec.swiglu_mode)
     if lw.shared_gu is not None:

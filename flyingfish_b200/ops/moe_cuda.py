@@ -139,3 +139,86 @@ def experts_forward(x, weights, ids, w_gate_up, w_down, mode, e_lo: int = 0, n_e
     h = grouped_gemm(xs, wgu, seg_off, counts, cap, epi=1, rows_per_expert=rpe)
     y = grouped_gemm(h, w_down, seg_off, counts, cap, epi=0, rows_per_expert=rpe)
     return combine(y, pos, ids, weights.contiguous(), rows, hidden)
+
+
+# ------------------------------------------------------------------------------------------------
+# NVFP4 experts (W4A16): weights stay packed in HBM, csrc/moe_fp4.cu expands them inside the GEMM
+# ------------------------------------------------------------------------------------------------
+class Nvfp4Experts:
+    """Packed expert stack: ``codes`` [E, N, K/2] uint8 (two E2M1 per byte, low nibble first), ``scales`` [E, N, K/16]
+    uint8 (E4M3 per 16 weights), ``global_scale`` [E] f32. Gate/up stacks are kept interleaved per 64 rows (the
+    order the SwiGLU epilogue expects); the interleave is a row permutation, so it applies to codes and scales alike."""
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor, gate_up: bool = False):
+        _require(codes.dtype == torch.uint8 and scales.dtype == torch.uint8 and codes.dim() == 3, "nvfp4 experts: uint8 stacks")
+        if gate_up:
+            codes, scales = interleave64(codes), interleave64(scales)
+        self.codes, self.scales = codes.contiguous(), scales.contiguous()
+        self.global_scale = global_scale.to(torch.float32).reshape(-1).contiguous()
+        self.experts, self.n, self.k = codes.shape[0], codes.shape[1], codes.shape[2] * 2
+        _require(self.global_scale.numel() == self.experts and scales.shape == (self.experts, self.n, self.k // 16),
+                 "nvfp4 experts: scale shapes")
+
+    @classmethod
+    def quantize(cls, w: torch.Tensor, gate_up: bool = False) -> "Nvfp4Experts":
+        """[E, N, K] weights -> packed stack on the same device: per-expert global scale ``amax / (6 * 448)``, E4M3
+        scale per 16 relative to it (device quantiser ``ff_quant_fp4`` on CUDA, ``loaders.quant`` on the host)."""
+        if not w.is_cuda:
+            from ..loaders import quant
+            parts = [quant.quantize_nvfp4(w[e].float()) for e in range(w.shape[0])]
+            return cls(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]),
+                       torch.stack([p[2] for p in parts]), gate_up)
+        from .quant_ops import quant_fp4
+        gs = (w.float().abs().amax(dim=(1, 2)).clamp_min(1e-12) / (6.0 * 448.0)).contiguous()
+        codes, scales = [], []
+        for e in range(w.shape[0]):
+            c, sc = quant_fp4(w[e].to(torch.bfloat16).contiguous(), "nvfp4", gs[e])
+            codes.append(c)
+            scales.append(sc)
+        return cls(torch.stack(codes), torch.stack(scales), gs, gate_up)
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scales.numel() + 4 * self.experts
+
+    def supported(self) -> bool:
+        return self.n % 128 == 0 and self.k % 256 == 0
+
+
+def grouped_gemm_nvfp4(xs, w: Nvfp4Experts, seg_off, counts, capacity: int, epi: int) -> torch.Tensor:
+    n_out = w.n // 2 if epi == 1 else w.n
+    y = torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs.device)
+    rc = kernels().ff_moe_grouped_gemm_nvfp4(ptr(xs), ptr(w.codes), ptr(w.scales), ptr(w.global_scale), ptr(y), ptr(seg_off),
+                                             ptr(counts), w.experts, w.n, w.k, capacity, n_out, epi,
+                                             ptr(status_tensor(xs.device)), stream_ptr())
+    check(rc, "ff_moe_grouped_gemm_nvfp4")
+    _count()
+    return y
+
+
+def experts_forward_nvfp4(x, weights, ids, gate_up: Nvfp4Experts, down: Nvfp4Experts, e_lo: int = 0,
+                          n_experts_total: int | None = None) -> torch.Tensor:
+    """Routed experts with packed NVFP4 weights: dispatch -> gate/up (+SwiGLU) -> down -> combine, the weights
+    expanded inside the two grouped GEMMs."""
+    rows, hidden = x.shape
+    total = n_experts_total if n_experts_total is not None else gate_up.experts
+    xs, pos, seg_off, counts, cap = dispatch_local(x.contiguous(), ids.contiguous(), total, e_lo, e_lo + gate_up.experts)
+    h = grouped_gemm_nvfp4(xs, gate_up, seg_off, counts, cap, epi=1)
+    y = grouped_gemm_nvfp4(h, down, seg_off, counts, cap, epi=0)
+    return combine(y, pos, ids, weights.contiguous(), rows, hidden)
+
+
+FP4_DECODE_MAX_ROWS = int(os.environ.get("FF_FP4_MAX_ROWS_PER_EXPERT", "48"))
+
+
+def pack_experts_nvfp4(weights) -> int:
+    """Adds a packed NVFP4 copy of every MoE layer's routed experts (``lw.extra["experts_fp4"]``); decode-sized calls
+    then read a quarter of the expert bytes. The BF16 stacks stay for prefill-sized calls. Returns the packed bytes."""
+    total = 0
+    for lw in weights.layers:
+        if lw.router is None or lw.experts_gu is None or not lw.experts_gu.is_cuda:
+            continue
+        gu, dn = Nvfp4Experts.quantize(lw.experts_gu, gate_up=True), Nvfp4Experts.quantize(lw.experts_down)
+        if gu.supported() and dn.supported():
+            lw.extra["experts_fp4"] = (gu, dn)
+            total += gu.nbytes() + dn.nbytes()
+    return total

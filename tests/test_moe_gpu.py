@@ -73,3 +73,66 @@ def test_moe_model_gpu_matches_cpu(name):
     m.reset()
     b = generate_plain(m, ids, 8, ignore_eos=True, graph=True).ids
     assert a == b, "eager and graph decode must agree bitwise"
+
+
+@pytest.mark.parametrize("rows,E,k,h,f", [(7, 8, 2, 512, 256), (64, 16, 4, 1024, 512), (200, 4, 2, 256, 256)])
+def test_experts_forward_nvfp4(rows, E, k, h, f):
+    """Packed NVFP4 experts expanded inside the grouped GEMM against the oracle on the dequantised weights."""
+    from flyingfish_b200.loaders import quant
+    from flyingfish_b200.ops import moe_cuda
+    x = _rand((rows, h), 5)
+    wgu, wd = _rand((E, 2 * f, h), 6, 0.05), _rand((E, h, f), 7, 0.05)
+    g = torch.Generator().manual_seed(8)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(rows)]).to(torch.int32)
+    wts = torch.rand(rows, k, generator=g)
+    wts = wts / wts.sum(-1, keepdim=True)
+    qgu = [quant.quantize_nvfp4(wgu[e].float()) for e in range(E)]
+    qd = [quant.quantize_nvfp4(wd[e].float()) for e in range(E)]
+    dq_gu = torch.stack([quant.dequantize_nvfp4(*q) for q in qgu])
+    dq_d = torch.stack([quant.dequantize_nvfp4(*q) for q in qd])
+    st = lambda qs, i: torch.stack([q[i] for q in qs]).cuda()
+    gu = moe_cuda.Nvfp4Experts(st(qgu, 0), st(qgu, 1), st(qgu, 2), gate_up=True)
+    dn = moe_cuda.Nvfp4Experts(st(qd, 0), st(qd, 1), st(qd, 2))
+    assert gu.supported() and dn.supported() and gu.nbytes() * 3 < wgu.numel() * 2
+    got = moe_cuda.experts_forward_nvfp4(x.cuda(), wts.cuda(), ids.cuda(), gu, dn)
+    torch.cuda.synchronize()
+    ops.check_status()
+    expect = ref.moe_forward(x, wts, ids, dq_gu, dq_d, None, None, 0)
+    err = (got.float().cpu() - expect.float()).abs()
+    # the kernel applies the per-expert global scale in FP32, the oracle folds it into BF16-rounded weights
+    tol = 4e-2 + 4e-2 * expect.float().abs()
+    assert (err <= tol).all(), f"max err {err.max().item()}"
+    again = moe_cuda.experts_forward_nvfp4(x.cuda(), wts.cuda(), ids.cuda(), gu, dn)
+    assert torch.equal(got, again)
+
+
+def test_model_with_packed_nvfp4_experts():
+    """Decode steps of an NVFP4-expert model run on the packed experts (prefill on their BF16 expansion)."""
+    from flyingfish_b200.api import Model, generate_plain
+    from flyingfish_b200.config import Settings
+    from flyingfish_b200.ops import moe_cuda
+    m = Model.load("qwen3-moe-fp4-tiny", Settings(capacity=256, max_batch=4, graph=False), device="cuda", seed=0)
+    lw = m.engine.model.w.layers[0]
+    gu, dn = lw.extra["experts_fp4"]
+    assert gu.codes.shape == (16, 512, 256) and dn.codes.shape == (16, 512, 128)
+    # the packed stack reproduces the BF16 experts to FP4 precision
+    from flyingfish_b200.ops.quant_ops import dequant_nvfp4
+    back = dequant_nvfp4(dn.codes[3], dn.scales[3], dn.global_scale[3])
+    rel = (back.float() - lw.experts_down[3].float()).abs().mean() / lw.experts_down[3].float().abs().mean()
+    assert rel < 0.15, rel
+    calls = {"n": 0}
+    orig = moe_cuda.experts_forward_nvfp4
+
+    def spy(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+    moe_cuda.experts_forward_nvfp4 = spy
+    try:
+        ids = list(range(3, 40))
+        a = generate_plain(m, ids, 6, ignore_eos=True, graph=False).ids
+        m.reset()
+        b = generate_plain(m, ids, 6, ignore_eos=True, graph=False).ids
+    finally:
+        moe_cuda.experts_forward_nvfp4 = orig
+    assert a == b and calls["n"] >= 2 * 5            # five decode steps x two MoE layers per run, at least
+    ops.check_status()
