@@ -1,6 +1,6 @@
 """Quantised number formats of the published checkpoints, host side: E4M3 / E2M1 / E8M0 codecs,
 block-scale shapes, reference quantisers and reference linears. These are the oracles for the
-device kernels (``csrc/quantize.cu``, ``csrc/gemm_fp8.cu``, ``csrc/gemm_nvfp4.cu``) and the code the
+device kernels (``csrc/quantize.cu``, ``csrc/gemm_fp8.cu``, ``csrc/moe_fp4.cu``) and the code the
 loaders use to validate scale tensor shapes (the reference's src/fp8.rs:69-147, 245-345).
 
 Formats

@@ -5,17 +5,18 @@
 // global : FP32 per expert (ModelOpt `weight_scale_2`)
 // The decode-sized MoE layer is bound by expert weight bytes, so the weights stay packed in HBM (a quarter of the
 // BF16 bytes) and are expanded on the way into the tensor-core operand:
-//   * four converter warps read the packed codes of a 128-row x 256-wide K block (coalesced: a warp-wide load covers
-//     four whole 128-byte rows) and its scales straight from global memory, two K blocks ahead in registers,
-//     expand them to BF16 (one shared-memory table look-up per byte = two weights, one BF16x2 multiply by the
-//     group's scale; e2m1 * e4m3 is exact in BF16: 2 + 4 significant bits) and write the four 64-wide
+//   * four converter warps read the packed codes of a 128-row x 128-wide K block (a warp-wide load covers eight
+//     whole 64-byte row pieces) and its scales straight from global memory, two K blocks ahead in registers,
+//     expand them to BF16 (byte-permute look-ups in registers, four codes at a time, one BF16x2 multiply by the
+//     group's scale; e2m1 * e4m3 is exact in BF16: 2 + 4 significant bits) and write the two 64-wide
 //     128-byte-swizzled sub-tiles that tcgen05.mma reads as its A operand;
-//   * one thread streams the tokens of the segment (the UMMA N side, up to 64 per pass) with TMA;
+//   * one thread streams the tokens of the segment (the UMMA N side, up to 32 per pass) with TMA;
 //   * one thread issues the MMAs into a TMEM accumulator; the per-expert global scale is applied in FP32 in the
 //     epilogue (more exact than folding it into a BF16 weight), with the optional SwiGLU of gate/up stacks
-//     interleaved per 64 rows.
-// Swap-AB like the BF16 grouped kernel of moe.cu (weights = UMMA M, tokens = UMMA N). Segments longer than 64 tokens
-// are processed in passes of 64 that each re-expand the weights, so this kernel is meant for decode-sized segments;
+//     interleaved per 64 rows. Two CTAs share an SM (97 KiB of shared memory, <= 168 registers), so one CTA's
+//     prologue, pipeline fill and epilogue overlap the other's main loop.
+// Swap-AB like the BF16 grouped kernel of moe.cu (weights = UMMA M, tokens = UMMA N). Segments longer than 32 tokens
+// are processed in passes of 32 that each re-expand the weights, so this kernel is meant for decode-sized segments;
 // prefill-sized calls expand the weights once (quantize.cu) and use the tiled grouped GEMM.
 // Format: kernels/nvfp4_linear.cu and src/fp8.rs:124-147 of the reference.
 #include "ptx.cuh"
@@ -25,12 +26,13 @@
 namespace ff {
 
 constexpr int F4_BM = 128;           // weight rows per CTA (UMMA M)
-constexpr int F4_KB = 256;           // K per pipeline stage = four 64-wide UMMA sub-tiles
-constexpr int F4_TOK = 64;           // tokens per pass (UMMA N)
+constexpr int F4_KB = 128;           // K per pipeline stage = two 64-wide UMMA sub-tiles
+constexpr int F4_NSUB = F4_KB / 64;
+constexpr int F4_TOK = 32;           // tokens per pass (UMMA N)
 constexpr int F4_STAGES = 2;
 constexpr int F4_SUB = F4_BM * 64 * 2;               // one converted sub-tile: 16 KiB
-constexpr int F4_A_BYTES = 4 * F4_SUB;               // 64 KiB
-constexpr int F4_X_BYTES = 4 * F4_TOK * 128;         // 32 KiB
+constexpr int F4_A_BYTES = F4_NSUB * F4_SUB;         // 32 KiB
+constexpr int F4_X_BYTES = F4_NSUB * F4_TOK * 128;   // 8 KiB
 constexpr int F4_STAGE_BYTES = F4_A_BYTES + F4_X_BYTES;
 constexpr int F4_EPI_TOK = 32;
 constexpr int F4_STAGING = F4_EPI_TOK * F4_BM * 4;   // FP32 transpose tile of the epilogue: 16 KiB
@@ -59,15 +61,13 @@ __device__ __forceinline__ float f4_value(uint32_t code) {
 }
 
 // grid (Nw / 128, E_local), 192 threads: warp 0 token TMA, warp 1 MMA, warps 2..5 converters + epilogue
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 moe_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ Wq,
                        const uint8_t* __restrict__ Wsc, const float* __restrict__ Wglobal, __nv_bfloat16* __restrict__ Y,
                        const int* __restrict__ seg_off, const int* __restrict__ counts, int Nw, int K, int ldy, int epi,
                        int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ Fp4Bars bars;
-  __shared__ uint32_t lut_w[256];       // packed byte -> BF16 pair (low nibble, high nibble)
-  __shared__ uint32_t lut_s[256];       // E4M3 scale code -> BF16 pair (s, s); scales are unsigned in this format
   const int e = blockIdx.y, tn = blockIdx.x;
   const int cnt = counts[e];
   if (cnt <= 0) return;                                   // uniform for the CTA
@@ -85,11 +85,6 @@ moe_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* _
     bars.abort_flag = 0;
     mbar_fence_init();
   }
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-    lut_w[i] = pack_bf16x2(f4_value(i & 0xfu), f4_value((uint32_t)i >> 4));
-    const float sv = (i & 0x7f) == 0x7f ? 0.f : f4_e4m3((uint32_t)i);      // NaN codes never scale anything
-    lut_s[i] = pack_bf16x2(sv, sv);
-  }
   if (warp == 1) { tmem_alloc(&bars.tmem_base, 64); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -106,9 +101,9 @@ moe_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* _
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % F4_STAGES; const uint32_t ph = (it / F4_STAGES) & 1;
           if (!mbar_wait(&bars.empty[s], ph ^ 1, abort_flag, status, KID_MOE_GEMM, 11)) { ok = false; break; }
-          mbar_expect_tx(&bars.full[s], 4 * ntok * 128);
+          mbar_expect_tx(&bars.full[s], F4_NSUB * ntok * 128);
           uint8_t* sx = pipe + s * F4_STAGE_BYTES + F4_A_BYTES;
-          for (int j = 0; j < 4; ++j)
+          for (int j = 0; j < F4_NSUB; ++j)
             for (int r = 0; r < ntok; r += 16)
               tma_load_2d(sx + j * (F4_TOK * 128) + r * 128, &tmX, &bars.full[s], kb * F4_KB + j * 64,
                           row0 + p * F4_TOK + r);
@@ -129,7 +124,7 @@ moe_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* _
           tc_fence_after();
           const uint32_t sa = smem_u32(pipe + s * F4_STAGE_BYTES);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < F4_NSUB; ++j) {
             const uint64_t da = umma_desc_sw128(sa + j * F4_SUB, 16, 1024);
             const uint64_t db = umma_desc_sw128(sa + F4_A_BYTES + j * (F4_TOK * 128), 16, 1024);
 #pragma unroll
@@ -142,48 +137,57 @@ moe_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* _
     }
   } else {
     // ---- converter + epilogue warps. Converter warp cw owns weight rows cw*32 .. cw*32+31 of the tile; load i of
-    // a K block gives lane l the 16 packed bytes (32 weights) of chunk l%8 of row cw*32 + i*4 + l/8, so a warp-wide
-    // load covers four whole 128-byte rows. ------------------------------------------------------------------
+    // a K block gives lane l the 16 packed bytes (32 weights) of chunk l%4 of row cw*32 + i*8 + l/4, so a warp-wide
+    // load covers eight whole 64-byte row pieces. ------------------------------------------------------------------
     const int wr = threadIdx.x - 64;                                    // 0..127 (epilogue indexing)
     const int q = warp & 3;                                             // TMEM lane quarter of this warp
-    const int cw = warp - 2, pc = lane & 7;
-    const size_t grow = (size_t)e * Nw + (size_t)tn * F4_BM + cw * 32 + (lane >> 3);
+    const int cw = warp - 2, pc = lane & 3;
+    const size_t grow = (size_t)e * Nw + (size_t)tn * F4_BM + cw * 32 + (lane >> 2);
     const uint8_t* wq = Wq + grow * (size_t)(K / 2) + pc * 16;
     const uint8_t* ws = Wsc + grow * (size_t)(K / 16) + pc * 2;
-    const size_t wq_step = (size_t)4 * (K / 2), ws_step = (size_t)4 * (K / 16);      // four rows further per load
+    const size_t wq_step = (size_t)8 * (K / 2), ws_step = (size_t)8 * (K / 16);      // eight rows further per load
     const float gscale = Wglobal[e];
     const int total = passes * kblocks;
     // register prefetch, two K blocks ahead (two named register sets: no dynamic indexing)
-    uint4 pk0[8], pk1[8];
-    uint32_t sc0[8], sc1[8];
-    auto fetch = [&](uint4 (&pk)[8], uint32_t (&sc)[8], int it) {
+    uint4 pk0[4], pk1[4];
+    uint32_t sc0[4], sc1[4];
+    auto fetch = [&](uint4 (&pk)[4], uint32_t (&sc)[4], int it) {
       const int kb = it % kblocks;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        pk[i] = __ldg(reinterpret_cast<const uint4*>(wq + i * wq_step + (size_t)kb * 128));
-        sc[i] = __ldg(reinterpret_cast<const unsigned short*>(ws + i * ws_step + (size_t)kb * 16));
+      for (int i = 0; i < 4; ++i) {
+        pk[i] = __ldg(reinterpret_cast<const uint4*>(wq + i * wq_step + (size_t)kb * (F4_KB / 2)));
+        sc[i] = __ldg(reinterpret_cast<const unsigned short*>(ws + i * ws_step + (size_t)kb * (F4_KB / 16)));
       }
     };
-    // one byte (two codes) -> BF16 pair through the table, times the group's scale (exact in BF16)
+    // 8 codes of a 32-bit word -> four BF16 pairs times the group's scale (exact in BF16). The magnitude of a code
+    // indexes two 8-entry byte tables (high and low byte of the BF16 value) held in registers: prmt looks up four
+    // codes at once, two more prmt interleave the bytes into BF16 pairs, the sign bits are moved into place.
     auto expand4 = [&](uint32_t w, __nv_bfloat162 sv) -> uint4 {
+      const uint32_t mag = w & 0x77777777u;
+      const uint32_t hi_a = __byte_perm(0x3f3f3f00u, 0x40404040u, mag);            // codes 0..3: high bytes
+      const uint32_t lo_a = __byte_perm(0xc0800000u, 0xc0804000u, mag);            //             low bytes
+      const uint32_t hi_b = __byte_perm(0x3f3f3f00u, 0x40404040u, mag >> 16);      // codes 4..7
+      const uint32_t lo_b = __byte_perm(0xc0800000u, 0xc0804000u, mag >> 16);
       uint32_t o[4];
+      o[0] = __byte_perm(lo_a, hi_a, 0x5140) | ((w & 0x00000008u) << 12) | ((w & 0x00000080u) << 24);
+      o[1] = __byte_perm(lo_a, hi_a, 0x7362) | ((w & 0x00000800u) << 4) | ((w & 0x00008000u) << 16);
+      o[2] = __byte_perm(lo_b, hi_b, 0x5140) | ((w & 0x00080000u) >> 4) | ((w & 0x00800000u) << 8);
+      o[3] = __byte_perm(lo_b, hi_b, 0x7362) | ((w & 0x08000000u) >> 12) | (w & 0x80000000u);
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const uint32_t t = lut_w[(w >> (8 * b)) & 0xffu];
-        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&t), sv);
-        o[b] = *reinterpret_cast<const uint32_t*>(&r);
+      for (int b2 = 0; b2 < 4; ++b2) {
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&o[b2]), sv);
+        o[b2] = *reinterpret_cast<const uint32_t*>(&r);
       }
       return make_uint4(o[0], o[1], o[2], o[3]);
     };
-    auto convert = [&](const uint4 (&pk)[8], const uint32_t (&sc)[8], uint8_t* stage) {
+    auto convert = [&](const uint4 (&pk)[4], const uint32_t (&sc)[4], uint8_t* stage) {
       uint8_t* sub = stage + (pc >> 1) * F4_SUB;                        // 64 weights of a row = one sub-tile row
       const int ch0 = (pc & 1) * 4;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int r = cw * 32 + i * 4 + (lane >> 3);
-        const uint32_t t0 = lut_s[sc[i] & 0xffu], t1 = lut_s[sc[i] >> 8];
-        const __nv_bfloat162 s0 = *reinterpret_cast<const __nv_bfloat162*>(&t0);
-        const __nv_bfloat162 s1 = *reinterpret_cast<const __nv_bfloat162*>(&t1);
+      for (int i = 0; i < 4; ++i) {
+        const int r = cw * 32 + i * 8 + (lane >> 2);
+        const __nv_bfloat162 s0 = __float2bfloat162_rn(f4_e4m3(sc[i] & 0xffu));
+        const __nv_bfloat162 s1 = __float2bfloat162_rn(f4_e4m3(sc[i] >> 8));
         uint8_t* rowp = sub + r * 128;
         const int x = r & 7;
         *reinterpret_cast<uint4*>(rowp + (((ch0 + 0) ^ x) << 4)) = expand4(pk[i].x, s0);

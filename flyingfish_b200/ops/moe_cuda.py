@@ -181,7 +181,7 @@ class Nvfp4Experts:
         return self.codes.numel() + self.scales.numel() + 4 * self.experts
 
     def supported(self) -> bool:
-        return self.n % 128 == 0 and self.k % 256 == 0
+        return self.n % 128 == 0 and self.k % 128 == 0
 
 
 def grouped_gemm_nvfp4(xs, w: Nvfp4Experts, seg_off, counts, capacity: int, epi: int) -> torch.Tensor:
@@ -207,7 +207,7 @@ def experts_forward_nvfp4(x, weights, ids, gate_up: Nvfp4Experts, down: Nvfp4Exp
     return combine(y, pos, ids, weights.contiguous(), rows, hidden)
 
 
-FP4_DECODE_MAX_ROWS = int(os.environ.get("FF_FP4_MAX_ROWS_PER_EXPERT", "48"))
+FP4_DECODE_MAX_ROWS = int(os.environ.get("FF_FP4_MAX_ROWS_PER_EXPERT", "32"))
 
 
 def pack_experts_nvfp4(weights) -> int:
