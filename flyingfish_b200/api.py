@@ -86,6 +86,9 @@ class Model:
         if spec.mla is not None:
             from .models.deepseek import DeepseekModel
             net = DeepseekModel(weights, comm=comm)
+        elif spec.extra.get("gemma"):
+            from .models.gemma import GemmaModel
+            net = GemmaModel(weights, comm=comm, seed=seed)
         elif spec.extra.get("gdn"):
             from .models.hybrid import HybridModel
             net = HybridModel(weights, comm=comm, max_sequences=settings.max_batch, seed=seed)

@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
     layers: int
     hidden: int
     heads: int
@@ -207,8 +207,17 @@ def qwen3_moe_fp4_tiny() -> ModelSpec:
     return spec
 
 
+def tiny_gemma() -> ModelSpec:
+    """Small Gemma-layout shape: five local layers (window 48) per global layer, tanh-GELU gate, soft-capped logits."""
+    spec = tiny_llama()
+    spec.name, spec.arch, spec.layers = "tiny-gemma", "gemma", 6
+    spec.qk_norm, spec.swiglu_mode, spec.tie_embeddings, spec.rope_theta = True, 2, True, 1e6
+    spec.extra = {"gemma": {"window": 48, "global_every": 6, "local_rope_theta": 1e4, "final_softcap": 30.0}}
+    return spec
+
+
 NAMED_SHAPES = {
-    "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
+    "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }

@@ -156,9 +156,12 @@ def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tenso
     m, ldx = _rows2d(x)
     n, ldw = _rows2d(w_interleaved)
     k = x.shape[1]
-    _require(n % 256 == 0 and mode == 0, "linear_swiglu: N must be a multiple of 256 and mode 0")
+    _require(n % 256 == 0, "linear_swiglu: N must be a multiple of 256")
     if out is None:
         out = torch.empty(m, n // 2, dtype=BF16, device=x.device)
+    if mode != 0:
+        # the GEMM epilogues implement rounding mode 0; other gates (tanh-GELU, clamped) run as the activation kernel
+        return silu_mul_interleaved(linear(x, w_interleaved), out, mode)
     if m <= SKINNY_MAX_M and not FUSE_SWIGLU:
         return silu_mul_interleaved(linear(x, w_interleaved), out)
     if m <= SKINNY_MAX_M:
@@ -386,16 +389,19 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
 def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                 ctx_lens: torch.Tensor, hq: int, hkv: int, dim: int, scale: float, nq: int = 1,
                 tree_mask: torch.Tensor | None = None, max_ctx: int | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, window: int = 0) -> torch.Tensor:
     """Decode / multi-row verify attention. ``q`` holds ``batch * nq`` rows (heads at columns
     ``h*dim``; it may be the packed QKV buffer). ``ctx_lens[b]`` counts the keys visible to the last
-    of the ``nq`` rows. Returns ``[batch*nq, hq*dim]``."""
+    of the ``nq`` rows. ``window > 0``: every row sees only its last ``window`` keys (local-attention
+    layers; not together with a tree mask). Returns ``[batch*nq, hq*dim]``."""
     batch = block_table.shape[0]
+    _require(not (window > 0 and tree_mask is not None), "attn_decode: window and tree mask are exclusive")
     if not _is_cuda(q):
         q_start = torch.arange(batch, dtype=torch.int32) * nq
         q_lens = torch.full((batch,), nq, dtype=torch.int32)
         tm = None if tree_mask is None else tree_mask.view(batch, nq)
-        return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale, tm)
+        return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale, tm,
+                                   window)
     rows, ldq = _rows2d(q)
     _require(rows == batch * nq, "attn_decode: q rows must equal batch * nq")
     _require(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attn_decode: block table int32")
@@ -418,9 +424,15 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, blo
     # slower on B200 (81.8 vs 75.6 us at batch 64 / context 1100: every CTA pays a fence and an atomic), so off
     items = batch * hkv * ((nq * (hq // hkv) + 15) // 16)
     counters = ws.attn_counters if (FUSE_ATTN_MERGE and nsplit > 1 and items <= ws.attn_counters.numel()) else None
-    rc = lib.ff_attn_decode(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(tree_mask),
-                            ptr(out), ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, nq, ldq, block_table.shape[1],
-                            nb, nsplit, c_float(scale), ptr(counters), ptr(status_tensor(q.device)), stream_ptr())
+    if window > 0:
+        rc = lib.ff_attn_decode_window(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(out),
+                                       ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, nq, ldq, block_table.shape[1], nb,
+                                       nsplit, c_float(scale), window, ptr(counters), ptr(status_tensor(q.device)),
+                                       stream_ptr())
+    else:
+        rc = lib.ff_attn_decode(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(tree_mask),
+                                ptr(out), ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, nq, ldq, block_table.shape[1],
+                                nb, nsplit, c_float(scale), ptr(counters), ptr(status_tensor(q.device)), stream_ptr())
     check(rc, "ff_attn_decode")
     _count(1 if (nsplit == 1 or counters is not None) else 2)
     return out

@@ -198,7 +198,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                    const int* __restrict__ ctx_lens, const unsigned long long* __restrict__ tree_mask,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
-                   int* status, int* __restrict__ split_counters) {
+                   int* status, int* __restrict__ split_counters, int window) {
   pdl_trigger();
   if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 0);
   pdl_wait();
@@ -212,8 +212,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int ctx = ctx_lens[b];
   const int pages = (ctx + PAGE - 1) / PAGE;
-  const int per = (pages + nsplit - 1) / nsplit;
-  const int p0 = split * per, p1 = min(pages, p0 + per);
+  // sliding window (models with local-attention layers; not combined with tree masks): the query at position pos
+  // sees keys pos - window + 1 .. pos, so the pages before the earliest bound of the nq queries are not visited
+  const int pfirst = window > 0 ? max(0, ctx - nq - window + 1) / PAGE : 0;
+  const int per = (pages - pfirst + nsplit - 1) / nsplit;
+  const int p0 = pfirst + split * per, p1 = min(pages, p0 + per);
   const int rows_total = nq * G;
   const int rows_used = min(16, rows_total - rt * 16);
 
@@ -273,9 +276,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     constexpr int KPW = PAGE / NW;                     // keys per warp
     const int key0 = p * PAGE + warp * KPW;
     const uint32_t sk = smem_u32(smem + buf * STAGE_BYTES);
-    if (ok && key0 < ctx)
-      warp_tile<KPW / 8>(qf, st, sk, sk + PAGE * HD * 2, warp * KPW, key0, lim[0], lim[1],
-                   tree_mask != nullptr, ctx - nq, mk[0], mk[1], scale_log2);
+    if (ok && key0 < ctx) {
+      bool um = tree_mask != nullptr;
+      int ts = ctx - nq;
+      unsigned long long a0 = mk[0], a1 = mk[1];
+      if (window > 0 && !um) {                         // lower bound of each row as a visibility set over this warp's keys
+        const int lo0 = lim[0] - window + 1 - key0, lo1 = lim[1] - window + 1 - key0;
+        um = true; ts = key0;
+        a0 = lo0 <= 0 ? ~0ull : (lo0 >= 64 ? 0ull : (~0ull << lo0));
+        a1 = lo1 <= 0 ? ~0ull : (lo1 >= 64 ? 0ull : (~0ull << lo1));
+      }
+      warp_tile<KPW / 8>(qf, st, sk, sk + PAGE * HD * 2, warp * KPW, key0, lim[0], lim[1], um, ts, a0, a1, scale_log2);
+    }
     __syncthreads();
   }
   if (bad) set_status(status, KID_ATTN_DECODE, FF_ERR_BOUNDS, b, split);
@@ -427,10 +439,16 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     __syncthreads();
     if (p * PAGE <= warp_last) {
       int l0 = lim[0], l1 = lim[1];
-      // sliding window: keys older than (pos - window + 1) are hidden by raising the lower
-      // bound; implemented by masking through the ancestor-set path is not needed for the
-      // causal models served here, so window only trims whole pages (first_key).
-      warp_tile<8>(qf, st, smem_u32(sKbuf[buf]), smem_u32(sVbuf[buf]), 0, p * PAGE, l0, l1, false, 0, 0ull, 0ull,
+      // sliding window: a row at position pos sees keys pos - window + 1 .. pos. Whole pages before the tile's
+      // earliest bound are skipped (first_key); inside a page the lower bound goes through the per-row 64-bit
+      // visibility set of the tile routine (bit i = key page_start + i visible).
+      unsigned long long m0 = ~0ull, m1 = ~0ull;
+      if (window > 0) {
+        const int lo0 = l0 - window + 1 - p * PAGE, lo1 = l1 - window + 1 - p * PAGE;
+        m0 = lo0 <= 0 ? ~0ull : (lo0 >= 64 ? 0ull : (~0ull << lo0));
+        m1 = lo1 <= 0 ? ~0ull : (lo1 >= 64 ? 0ull : (~0ull << lo1));
+      }
+      warp_tile<8>(qf, st, smem_u32(sKbuf[buf]), smem_u32(sVbuf[buf]), 0, p * PAGE, l0, l1, window > 0, p * PAGE, m0, m1,
                    scale_log2);
     }
     __syncthreads();
@@ -477,10 +495,12 @@ FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ct
   return nsplit;
 }
 
-FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcache, const int* block_table,
-                             const int* ctx_lens, const unsigned long long* tree_mask, void* out, float* part_o,
-                             float* part_ml, int batch, int hq, int hkv, int head_dim, int nq, int ldq, int max_blocks,
-                             int num_blocks, int nsplit, float scale, int* split_counters, int* status, cudaStream_t s) {
+static int attn_decode_launch(const void* q, const void* kcache, const void* vcache, const int* block_table,
+                              const int* ctx_lens, const unsigned long long* tree_mask, void* out, float* part_o,
+                              float* part_ml, int batch, int hq, int hkv, int head_dim, int nq, int ldq, int max_blocks,
+                              int num_blocks, int nsplit, float scale, int* split_counters, int* status, cudaStream_t s,
+                              int window) {
+  if (window > 0 && tree_mask) return FF_HOST_UNSUPPORTED;
   if (head_dim != HD || batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv) return FF_HOST_BAD_SHAPE;
   if (nq < 1 || nq > 64) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || nsplit < 1) return FF_HOST_BAD_ALIGN;
@@ -498,7 +518,7 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
   if (int r = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, HD, cache_rows, HD * 2, 64, PAGE)) return r;
   if (int lr_ = launch_pdl(attn_decode_kernel<NW>, dim3(grid), dim3(32 * NW), DEC_SMEM, s, 0, tmK, tmV, (const __nv_bfloat16*)q,
       block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
-      ldq, max_blocks, num_blocks, nsplit, scale_log2, status, split_counters)) return lr_;
+      ldq, max_blocks, num_blocks, nsplit, scale_log2, status, split_counters, window)) return lr_;
   if (int r = launch_result()) return r;
   if (nsplit > 1 && split_counters == nullptr) {
     if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * nq * hq), dim3(128), 0, s, 0, part_o, part_ml, (__nv_bfloat16*)out, nq * hq, nsplit)) return lr_;
@@ -507,7 +527,25 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
   return 0;
 }
 
-// window > 0: sliding window (whole pages trimmed); 0: causal; < 0: bidirectional (every query sees all ctx keys:
+FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcache, const int* block_table,
+                             const int* ctx_lens, const unsigned long long* tree_mask, void* out, float* part_o,
+                             float* part_ml, int batch, int hq, int hkv, int head_dim, int nq, int ldq, int max_blocks,
+                             int num_blocks, int nsplit, float scale, int* split_counters, int* status, cudaStream_t s) {
+  return attn_decode_launch(q, kcache, vcache, block_table, ctx_lens, tree_mask, out, part_o, part_ml, batch, hq, hkv,
+                            head_dim, nq, ldq, max_blocks, num_blocks, nsplit, scale, split_counters, status, s, 0);
+}
+
+// Decode attention of a local-attention layer: every query sees its last `window` keys.
+FF_EXPORT int ff_attn_decode_window(const void* q, const void* kcache, const void* vcache, const int* block_table,
+                                    const int* ctx_lens, void* out, float* part_o, float* part_ml, int batch, int hq,
+                                    int hkv, int head_dim, int nq, int ldq, int max_blocks, int num_blocks, int nsplit,
+                                    float scale, int window, int* split_counters, int* status, cudaStream_t s) {
+  if (window <= 0) return FF_HOST_BAD_SHAPE;
+  return attn_decode_launch(q, kcache, vcache, block_table, ctx_lens, nullptr, out, part_o, part_ml, batch, hq, hkv,
+                            head_dim, nq, ldq, max_blocks, num_blocks, nsplit, scale, split_counters, status, s, window);
+}
+
+// window > 0: sliding window (exact); 0: causal; < 0: bidirectional (every query sees all ctx keys:
 // encoder / vision-tower attention over a segment stored in the paged layout).
 FF_EXPORT int ff_attn_prefill(const void* q, const void* kcache, const void* vcache, const int* block_table,
                               const int* q_start, const int* q_lens, const int* ctx_lens, void* out, int batch,

@@ -290,3 +290,44 @@ def test_attn_decode_many_rows_tree():
     expect = ref.attention_paged(q.cpu(), kc.cpu(), vc.cpu(), bt.cpu(), qs, ql, ctx.cpu(), hq, hkv, d, 0.088,
                                  tree_mask=masks)
     _close(out, expect, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("window", [1, 37, 64, 100, 200])
+def test_attn_prefill_sliding_window_is_exact(window):
+    """Every row sees exactly its last ``window`` keys, also when the bound falls inside a page."""
+    g = torch.Generator().manual_seed(21)
+    hq, hkv, d, bs = 4, 2, 128, 64
+    lens = [150, 70]
+    nb = 8
+    kc = (torch.randn(nb, hkv, bs, d, generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(nb, hkv, bs, d, generator=g) * 0.5).to(torch.bfloat16)
+    bt = torch.tensor([[0, 1, 2, 3], [4, 5, 6, 7]], dtype=torch.int32)
+    rows = sum(lens)
+    q = (torch.randn(rows, hq * d, generator=g) * 0.5).to(torch.bfloat16)
+    q_start = torch.tensor([0, lens[0]], dtype=torch.int32)
+    q_lens = torch.tensor(lens, dtype=torch.int32)
+    ctx = torch.tensor([lens[0] + 40, lens[1]], dtype=torch.int32)          # the first sequence has 40 cached keys
+    want = ops.attn_prefill(q, kc, vc, bt, q_start, q_lens, ctx, max(lens), hq, hkv, d, d ** -0.5, window=window)
+    got = ops.attn_prefill(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), q_start.cuda(), q_lens.cuda(), ctx.cuda(), max(lens),
+                           hq, hkv, d, d ** -0.5, window=window)
+    ops.check_status()
+    assert torch.allclose(got.float().cpu(), want.float(), rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("window", [1, 50, 64, 130])
+def test_attn_decode_sliding_window(window):
+    g = torch.Generator().manual_seed(22)
+    hq, hkv, d, bs, batch = 8, 2, 128, 64, 3
+    nb = 12
+    kc = (torch.randn(nb, hkv, bs, d, generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(nb, hkv, bs, d, generator=g) * 0.5).to(torch.bfloat16)
+    bt = torch.arange(nb, dtype=torch.int32).reshape(batch, 4)
+    ctx = torch.tensor([200, 64, 7], dtype=torch.int32)
+    q = (torch.randn(batch, hq * d, generator=g) * 0.5).to(torch.bfloat16)
+    want = ops.attn_decode(q, kc, vc, bt, ctx, hq, hkv, d, d ** -0.5, window=window)
+    got = ops.attn_decode(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), ctx.cuda(), hq, hkv, d, d ** -0.5, window=window)
+    ops.check_status()
+    assert torch.allclose(got.float().cpu(), want.float(), rtol=3e-2, atol=3e-2)
+    full = ops.attn_decode(q, kc, vc, bt, ctx, hq, hkv, d, d ** -0.5)
+    if window < 200:
+        assert not torch.allclose(want[0].float(), full[0].float(), atol=1e-3)      # the window really hides keys
