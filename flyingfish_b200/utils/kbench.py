@@ -125,10 +125,44 @@ def bench_attn_prefill(args) -> dict:
     return r
 
 
+def bench_moe(args) -> dict:
+    """Routed experts of one MoE layer on one GPU (dispatch + gate/up GEMM with SwiGLU + down GEMM + combine), BF16
+    expert stacks or packed NVFP4 stacks (``--fp4``; random codes: the timing does not depend on the values)."""
+    from ..ops import moe_cuda, moe_ops
+    dev = torch.device("cuda")
+    rows, E, k, h, f = args.rows, args.experts, args.top_k, args.hidden, args.ffn
+    g = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(rows, h, generator=g, device=dev, dtype=torch.bfloat16) * 0.5
+    gc = torch.Generator().manual_seed(2)
+    ids = torch.stack([torch.randperm(E, generator=gc)[:k] for _ in range(rows)]).to(torch.int32).to(dev)
+    wts = torch.softmax(torch.randn(rows, k, generator=gc), -1).to(dev)
+    if args.fp4:
+        rnd = lambda *shape: torch.randint(0, 256, shape, device=dev, dtype=torch.uint8)
+        sc = lambda *shape: torch.randint(40, 60, shape, device=dev, dtype=torch.uint8)
+        gs = torch.full((E,), 1e-3, device=dev)
+        gu = moe_cuda.Nvfp4Experts(rnd(E, 2 * f, h // 2), sc(E, 2 * f, h // 16), gs, gate_up=True)
+        dn = moe_cuda.Nvfp4Experts(rnd(E, h, f // 2), sc(E, h, f // 16), gs)
+        fn = lambda: moe_cuda.experts_forward_nvfp4(x, wts, ids, gu, dn)
+        byts = gu.nbytes() + dn.nbytes()
+    else:
+        wgu = torch.randn(E, 2 * f, h, generator=g, device=dev, dtype=torch.bfloat16) * 0.02
+        wd = torch.randn(E, h, f, generator=g, device=dev, dtype=torch.bfloat16) * 0.02
+        fn = lambda: moe_ops.experts_forward(x, wts, ids, wgu, wd, 0)
+        byts = (wgu.numel() + wd.numel()) * 2
+    r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
+    pk = peaks()
+    t = r["us_mean"] * 1e-6
+    r.update(op="moe_fp4" if args.fp4 else "moe", rows=rows, experts=E, top_k=k, hidden=h, ffn=f, expert_bytes=byts,
+             gbs=byts / t / 1e9, tflops=2.0 * rows * k * 3 * f * h / t / 1e12)
+    r["frac_hbm"] = r["gbs"] / pk["hbm_gbs"]
+    r["peaks"] = pk["source"]
+    return r
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="kbench")
     sub = ap.add_subparsers(dest="op", required=True)
-    for name in ("gemm", "attn_decode", "attn_prefill"):
+    for name in ("gemm", "attn_decode", "attn_prefill", "moe"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
@@ -138,13 +172,20 @@ def main(argv=None) -> None:
             p.add_argument("--n", type=int, default=4096)
             p.add_argument("--k", type=int, default=4096)
             p.add_argument("--torch", action="store_true", help="time torch.matmul (cuBLAS) instead, as the baseline")
+        elif name == "moe":
+            p.add_argument("--rows", type=int, default=128)
+            p.add_argument("--experts", type=int, default=128)
+            p.add_argument("--top-k", type=int, default=8)
+            p.add_argument("--hidden", type=int, default=4096)
+            p.add_argument("--ffn", type=int, default=1536)
+            p.add_argument("--fp4", action="store_true", help="packed NVFP4 expert stacks expanded inside the GEMM")
         else:
             p.add_argument("--batch", type=int, default=64)
             p.add_argument("--ctx", type=int, default=1024)
             p.add_argument("--hq", type=int, default=32)
             p.add_argument("--hkv", type=int, default=8)
     args = ap.parse_args(argv)
-    fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill}[args.op]
+    fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "moe": bench_moe}[args.op]
     print(json.dumps(fn(args)))
     ops.check_status()
 
