@@ -97,12 +97,16 @@ class TPComm:
         self.fused = arena is not None
         self.stats = {"gemm_ar": 0, "oneshot_ar": 0, "nccl_ar": 0, "ag_gemm": 0, "gemm_rs": 0}
         self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=device) if arena is not None else None
-        # NVLS: with FLYINGFISH_NVLS=1 the fused GEMM + all-reduce exchanges through the switch (multimem, two
-        # flag rounds) when the arena has a multicast mapping. Off by default: at two ranks the one-shot exchange
-        # over plain peer stores measured 33 us against 45 us for the switch path on the 4096x4096 projection.
-        # Always off with NCCL_NVLS_ENABLE=0 (tests in which a rank may leave run on plain peer stores: a rank
-        # that dies while bound to a multicast object faults its peers).
-        self.nvls = bool(arena is not None and arena.multicast_ptr and os.environ.get("FLYINGFISH_NVLS", "0") == "1"
+        # NVLS: the fused GEMM + all-reduce can exchange through the switch (multimem ld_reduce / st, two flag
+        # rounds) when the arena has a multicast mapping. Measured on the decode step of the 8-B shape: at two
+        # ranks the one-shot exchange over plain peer stores wins (33 us against 45 us per projection, 5.05 ms
+        # against 5.78 ms per step), at eight ranks the switch path wins (4.11 ms against 4.97 ms per step: a
+        # rank no longer stores to seven peers and reads seven partials). FLYINGFISH_NVLS=auto (default): on
+        # from eight ranks; 1 / 0 force it. Always off with NCCL_NVLS_ENABLE=0 (tests in which a rank may leave
+        # run on plain peer stores: a rank that dies while bound to a multicast object faults its peers).
+        mode = os.environ.get("FLYINGFISH_NVLS", "auto")
+        want = mode == "1" or (mode == "auto" and self.size >= 8)
+        self.nvls = bool(arena is not None and arena.multicast_ptr and want
                          and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0")
 
     @classmethod
