@@ -157,3 +157,28 @@ def test_closure_state_machine_and_calibration_cache(tmp_path):
     assert not d1["cached"] and d1["disk_bytes_s"] > 0 and "cpu_service" in d1
     assert calibrate("qwen3-moe-tiny", st, cpu=True)["cached"]
     assert not calibrate("qwen3-moe-tiny", st, force=True, cpu=True)["cached"]
+
+
+def test_generate_for_the_other_model_families(tmp_path, capsys):
+    """Diffusion canvas, embedding encoder, image input, hybrid and Gemma layouts through the command line."""
+    import sys as _sys
+    from pathlib import Path
+    _sys.path.insert(0, str(Path(__file__).parent))
+    from test_vision import _png
+    base = ["--cpu", "--capacity", "256"]
+
+    def run(*argv):
+        return _run(list(argv), capsys)
+
+    d = run(*base, "--model", "tiny-diffusion", "generate", "--tokens", "5,6,7", "--max-new-tokens", "8",
+            "--diffusion-steps", "2")
+    assert d["mode"] == "diffusion" and len(d["tokens"]) == 8 and d["passes"] == 2 and 2046 not in d["tokens"]
+    e = run(*base, "--model", "tiny-embed", "embed", "--prompt", "hello")
+    assert e["dim"] == 256 and abs(sum(v * v for v in e["embedding"]) - 1.0) < 1e-3
+    img = tmp_path / "a.png"
+    img.write_bytes(_png(64, 64, 9))
+    v = run(*base, "--model", "tiny-vl", "generate", "--tokens", "5,2047,7", "--image", str(img), "--max-new-tokens", "3")
+    assert v["mode"] == "multimodal" and len(v["tokens"]) == 3 and v["images"] == 1
+    for name in ("tiny-hybrid", "tiny-gemma"):
+        g = run(*base, "--model", name, "generate", "--tokens", "5,6,7,8", "--max-new-tokens", "4", "--ignore-eos")
+        assert len(g["generated_ids"]) == 4
