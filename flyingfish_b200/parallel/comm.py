@@ -100,7 +100,7 @@ class TPComm:
         # NVLS: the fused GEMM + all-reduce can exchange through the switch (multimem ld_reduce / st, two flag
         # rounds) when the arena has a multicast mapping. Measured on the decode step of the 8-B shape: at two
         # ranks the one-shot exchange over plain peer stores wins (33 us against 45 us per projection, 5.05 ms
-        # against 5.78 ms per step), at eight ranks the switch path wins (4.11 ms against 4.97 ms per step: a
+        # against 5.78 ms per step) and at four (4.59 against 4.92 ms), at eight ranks the switch path wins (4.11 ms against 4.97 ms per step: a
         # rank no longer stores to seven peers and reads seven partials). FLYINGFISH_NVLS=auto (default): on
         # from eight ranks; 1 / 0 force it. Always off with NCCL_NVLS_ENABLE=0 (tests in which a rank may leave
         # run on plain peer stores: a rank that dies while bound to a multicast object faults its peers).
