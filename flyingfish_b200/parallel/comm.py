@@ -108,6 +108,13 @@ class TPComm:
         want = mode == "1" or (mode == "auto" and self.size >= 8)
         self.nvls = bool(arena is not None and arena.multicast_ptr and want
                          and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0")
+        # Sequence-parallel prefill pair (all-gather -> GEMM, GEMM -> reduce-scatter): the one-kernel forms win at
+        # two ranks (1.03-1.38 x the GEMM + NCCL collective) but at eight ranks, where 7/8 of every tile crosses
+        # NVLink, their tile pushes reached a quarter of the link rate and NCCL's collectives around the same GEMM
+        # were faster (944 us against 1235 us per layer of 8192 rows). FLYINGFISH_SP_FUSED=auto (default): one
+        # kernel up to four ranks, GEMM + NCCL collective from eight; 1 / 0 force either.
+        sp = os.environ.get("FLYINGFISH_SP_FUSED", "auto")
+        self.sp_fused = sp == "1" or (sp == "auto" and self.size <= 4)
 
     @classmethod
     def create(cls, group: dist.ProcessGroup, device: torch.device | str, fused: bool = True,
@@ -183,6 +190,10 @@ class TPComm:
         rpr, k = x_shard.shape
         n = w.shape[0]
         m = rpr * self.size
+        if not self.sp_fused:
+            full = self.all_gather_rows(x_shard)
+            self.stats["nccl_ag"] = self.stats.get("nccl_ag", 0) + 1
+            return ops.linear_swiglu(full, w) if swiglu else ops.linear(full, w)
         out = torch.empty(m, n // 2 if swiglu else n, dtype=torch.bfloat16, device=x_shard.device)
         rc = oplib.kernels().ff_ag_gemm(*self.arena.args(), oplib.ptr(x_shard), oplib.ptr(w), oplib.ptr(out), m, n, k,
                                         x_shard.stride(0), w.stride(0), out.stride(0), 1 if swiglu else 0,
@@ -199,6 +210,10 @@ class TPComm:
         m, k = x.shape
         n = w.shape[0]
         out = torch.empty(m // self.size, n, dtype=torch.bfloat16, device=x.device)
+        if not self.sp_fused:
+            dist.reduce_scatter_tensor(out, ops.linear(x, w), group=self.group)
+            self.stats["nccl_rs"] = self.stats.get("nccl_rs", 0) + 1
+            return out
         rc = oplib.kernels().ff_gemm_rs(*self.arena.args(), oplib.ptr(x), oplib.ptr(w), oplib.ptr(out), m, n, k,
                                         x.stride(0), w.stride(0), oplib.ptr(self.tile_counters),
                                         oplib.ptr(oplib.status_tensor(x.device)), oplib.stream_ptr())
