@@ -80,6 +80,7 @@ def main() -> None:
     h, f = args.hidden, args.ffn
     rpr = args.prefill_rows // world
     comm = TPComm.create(dist.group.WORLD, device, slot_bytes=rpr * h * 2)
+    comm.sp_fused = True          # this tool times the one-kernel forms at every world size
     pk = peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     g = torch.Generator(device="cpu").manual_seed(3)
