@@ -110,8 +110,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
            out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``y[M,N] = x[M,K] @ w[N,K].T`` (BF16 operands, FP32 accumulation).
 
-    CUDA path: tcgen05 kernels of ``csrc/gemm_bf16.cu`` -- the swap-AB split-K kernel for
-    M <= 128, the persistent 128x256x64 kernel otherwise."""
+    CUDA path: tcgen05 kernels -- the weight-streaming decode kernel of ``csrc/gemm_skinny.cu`` (tokens on
+    the UMMA M side, cluster split-K or stream-K) for M <= 128, the persistent 128x256x64 kernel of
+    ``csrc/gemm_bf16.cu`` otherwise."""
     if not _is_cuda(x):
         y = ref.linear(x, w, out_dtype)
         if out is not None:

@@ -505,9 +505,8 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
   if (nq < 1 || nq > 64) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || nsplit < 1) return FF_HOST_BAD_ALIGN;
   if (nsplit > 1 && (!part_o || !part_ml)) return FF_HOST_BAD_SHAPE;
-  static bool attr = false;
   constexpr int NW = DEC_WARPS;
-  if (!attr) { if (int r = opt_in_smem(attn_decode_kernel<NW>, DEC_SMEM)) return r; attr = true; }
+  if (int r = opt_in_smem(attn_decode_kernel<NW>, DEC_SMEM)) return r;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int row_tiles = (nq * (hq / hkv) + 15) / 16;
   dim3 grid(nsplit, hkv * row_tiles, batch);
@@ -553,8 +552,7 @@ FF_EXPORT int ff_attn_prefill(const void* q, const void* kcache, const void* vca
                               int num_blocks, float scale, int window, int* status, cudaStream_t s) {
   if (head_dim != HD || batch <= 0 || max_q_len <= 0 || hq % hkv) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || ldo % 2) return FF_HOST_BAD_ALIGN;
-  static bool attr = false;
-  if (!attr) { if (int r = opt_in_smem(attn_prefill_kernel, ATTN_SMEM)) return r; attr = true; }
+  if (int r = opt_in_smem(attn_prefill_kernel, ATTN_SMEM)) return r;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid((max_q_len + 63) / 64, hq, batch);
   attn_prefill_kernel<<<grid, 128, ATTN_SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache,

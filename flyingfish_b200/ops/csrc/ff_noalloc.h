@@ -11,12 +11,13 @@
 // Rules for the caller:
 //   * X, W, Y are device pointers owned by the caller; ldx/ldw/ldy are row pitches in elements
 //     (multiples of 8); `status` may be null or point to int32[4] in device memory.
-//   * The partial-sum slots (the scratch size ff_gemm_skinny_plan(M, N, K) reports: 2 * grid * M * 256 * 4
-//     bytes for problems it runs as stream-K, none for cluster split-K) must fit in
-//     FF_NOALLOC_SCRATCH_BYTES and the weight tiles in FF_NOALLOC_MAX_TILES; otherwise, and for
-//     M > 128, the call returns -5 and launches nothing.
+//   * The partial-sum slots (the scratch size ff_gemm_skinny_plan(M, N, K) reports: 2 * grid * M * 128 * 4
+//     bytes for problems it runs as stream-K over 128-row weight tiles with grid <= 148 CTAs, none
+//     for cluster split-K) must fit in FF_NOALLOC_SCRATCH_BYTES and the weight tiles in
+//     FF_NOALLOC_MAX_TILES; otherwise, and for M > 128, the call returns -5 and launches nothing.
+//     For a layer wide enough to occupy all 148 CTAs the limit is reached above M = 55 tokens.
 //   * The first call on each device looks up the array's device address; issue it before any
-//     stream capture begins on that device.
+//     stream capture begins on that device, with the device that owns `stream` current.
 //   * All calls share the array, so calls that can overlap on the GPU race; order them on one
 //     stream (or with events).
 //   * Returns 0, a negative host-side refusal code, or a positive cudaError_t.

@@ -2,17 +2,13 @@
 // (activations row-major, weights in the checkpoint's [out, in] layout, FP32 accumulation,
 // one BF16 rounding at the end).
 //
-// Two kernels share one warp-specialised pipeline (TMA producer warp -> mbarrier ring ->
-// single-thread tcgen05.mma issuer -> TMEM accumulator -> 4 epilogue warps):
-//   * gemm_bf16_kernel   : M >= 128-ish. Persistent, 128 x BN x 64 tiles, double-buffered
-//                          TMEM accumulators so the epilogue of tile i overlaps the mainloop
-//                          of tile i+1. Optional fused SwiGLU epilogue (gate|up interleaved
-//                          per 128 columns in the weight).
-//   * gemm_skinny_kernel : decode shapes (M <= 256). Swap-AB: the weight tile is the 128-row
-//                          UMMA "A" operand and the tokens are the UMMA N dimension, so a
-//                          16-token batch does not waste a 128-row tile; split-K with a
-//                          deterministic in-kernel fix-up (last CTA of a column tile sums the
-//                          FP32 partials in split order) spreads the weight stream over all SMs.
+// gemm_bf16_kernel serves M > 128 (prefill, verification batches): a warp-specialised pipeline
+// (TMA producer warp -> mbarrier ring -> single-thread tcgen05.mma issuer -> TMEM accumulator ->
+// 4 epilogue warps), persistent over 128 x BN x 64 tiles with double-buffered TMEM accumulators so
+// the epilogue of tile i overlaps the mainloop of tile i+1. Optional fused SwiGLU epilogue
+// (gate|up interleaved per 64 rows of the weight), grouped mode for expert segments, and the
+// tensor-parallel forms (all-gather -> GEMM, GEMM -> reduce-scatter) with peer stores in the same
+// kernel. Decode shapes (M <= 128) are served by gemm_skinny.cu.
 // This replaces the reference's cuBLAS/cuBLASLt calls (src/backend/cuda/blas.rs:852-1080)
 // and its mma.sync skinny kernel (kernels/gemm_skinny.cu).
 #include "ptx.cuh"
@@ -508,8 +504,7 @@ FF_EXPORT int ff_gemm_bf16(const void* X, const void* W, void* Y, int M, int N, 
   if (r) return r;
   const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
   auto kern = gemm_bf16_kernel<BN, STAGES, 0>;
-  static bool attr_done = false;
-  if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
+  r = opt_in_smem(kern, smem); if (r) return r;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   CommArgs none = {};
@@ -535,8 +530,7 @@ FF_EXPORT int ff_moe_grouped_gemm_tiled(const void* Xs, const void* W, void* Y, 
   if (r) return r;
   const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
   auto kern = gemm_bf16_kernel<BN, STAGES, 0>;
-  static bool attr_done = false;
-  if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
+  r = opt_in_smem(kern, smem); if (r) return r;
   CommArgs none = {};
   GroupArgs ga = {seg_off, counts, E_local};
   kern<<<sm_count(), 192, smem, stream>>>(tmA, tmA, tmA, tmB, Y, capacity, Nw, K, ldy, epi, status, none, ga);
@@ -586,8 +580,7 @@ FF_EXPORT int ff_ag_gemm(const unsigned long long* ptrs, int rank, int world, lo
   if (r) return r;
   const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
   auto kern = gemm_bf16_kernel<BN, STAGES, 1>;
-  static bool attr_done = false;
-  if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
+  r = opt_in_smem(kern, smem); if (r) return r;
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, 320, smem, stream>>>(tmA0, tmA1, tmX, tmB, Y, M, N, K, ldy, epi, status, ca, GroupArgs{});
@@ -613,8 +606,7 @@ FF_EXPORT int ff_gemm_rs(const unsigned long long* ptrs, int rank, int world, lo
   if (r) return r;
   const int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 4 * RS_STG_BYTES + 1024;   // + staging of the epilogue warps
   auto kern = gemm_bf16_kernel<BN, STAGES, 2>;
-  static bool attr_done = false;
-  if (!attr_done) { r = opt_in_smem(kern, smem); if (r) return r; attr_done = true; }
+  r = opt_in_smem(kern, smem); if (r) return r;
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, 192, smem, stream>>>(tmA, tmA, tmA, tmB, nullptr, M, N, K, N, 0, status, ca, GroupArgs{});

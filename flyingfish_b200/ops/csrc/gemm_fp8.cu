@@ -259,8 +259,7 @@ FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, 
   const int staging = F_TOK * FBM * 2 + ((K / 128) * F_TOK * 4 + 1023) / 1024 * 1024;
   int pipe_bytes = 200 * 1024 - staging;
   const int smem = staging + pipe_bytes + 1024;
-  static bool attr = false;
-  if (!attr) { r = opt_in_smem(gemm_fp8_kernel, 201 * 1024); if (r) return r; attr = true; }
+  r = opt_in_smem(gemm_fp8_kernel, 201 * 1024); if (r) return r;
   dim3 grid((Nw + FBM - 1) / FBM, splits, experts);
   gemm_fp8_kernel<<<grid, 192, smem, s>>>(tmW, tmX, w_scale, x_scale, (__nv_bfloat16*)y, seg_off, counts, M, Nw, K, ldy,
                                           epi, splits, pipe_bytes, staging, scratch, tile_counters, status);

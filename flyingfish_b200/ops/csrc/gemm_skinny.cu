@@ -642,8 +642,11 @@ constexpr int SK_SMEM_LIMIT = 200 * 1024;       // pipeline bytes a CTA may use 
 // Largest number of co-resident clusters of `s` CTAs of this kernel (0 when such a cluster cannot be
 // launched); queried once per cluster size.
 static int skinny_max_clusters(int s) {
-  static int cached[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+  static int cache[FF_MAX_DEVICES][9];
+  static bool cache_init = false;
+  if (!cache_init) { for (auto& row : cache) for (int& v : row) v = -1; cache_init = true; }
   if (s < 2 || s > 8) return 0;
+  int* cached = cache[current_device()];
   if (cached[s] >= 0) return cached[s];
   auto kern = gemm_skinny_kernel<false>;
   if (opt_in_smem(kern, SK_SMEM_LIMIT + 1024)) return 0;
@@ -811,15 +814,13 @@ static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int 
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
   if (arena == nullptr) {
     auto kern = gemm_skinny_kernel<false>;
-    static bool attr_done = false;
-    if (!attr_done) { r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r; attr_done = true; }
+    r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r;
     PeerArena none = {};
     return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
                       cfg.stages, cl, cfg.pipe_off, scratch, counters, status, none, ep);
   }
   auto kern = gemm_skinny_kernel<true>;
-  static bool attr_done_ar = false;
-  if (!attr_done_ar) { r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r; attr_done_ar = true; }
+  r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r;
   return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
                     cfg.stages, cl, cfg.pipe_off, scratch, counters, status, *arena, ep);
 }
@@ -883,14 +884,16 @@ FF_EXPORT int ff_gemm_ar(const unsigned long long* ptrs, int rank, int world, lo
 // only owns its input and output buffers). For them the split-K partial sums and the per-tile
 // arrival counters live in a fixed array inside this library instead of caller scratch.
 //
-//  * Limit: the partial-sum slots (2 * grid * M * 256 * 4 bytes, grid <= 148 persistent CTAs; none when
-//    the problem runs as cluster split-K) must fit in FF_NOALLOC_SCRATCH_BYTES (8 MiB) and the weight
-//    tiles in FF_NOALLOC_MAX_TILES (2048); larger problems are refused with FF_HOST_TOO_LARGE (in
-//    practice M <= 27 tokens for wide layers), and so is M > 128.
+//  * Limit: the partial-sum slots (2 * grid * M * 128 * 4 bytes for a problem that runs as stream-K over
+//    128-row weight tiles, grid <= 148 persistent CTAs; none when the problem runs as cluster
+//    split-K) must fit in FF_NOALLOC_SCRATCH_BYTES (8 MiB) and the weight tiles in
+//    FF_NOALLOC_MAX_TILES (2048); larger problems are refused with FF_HOST_TOO_LARGE (for wide layers
+//    that fill all 148 CTAs this means M <= 55 tokens), and so is M > 128.
 //    Every GPU that loads this library holds the 8 MiB until exit.
 //  * The first call on a device resolves the device addresses of the arrays
 //    (cudaGetSymbolAddress, with that device current) and caches them; make that first call
-//    before starting any stream capture.
+//    before starting any stream capture. The current device must be the one `stream` belongs to.
+//    The per-device cache is guarded by a mutex, so first calls may come from several host threads.
 //  * All calls share the one array: two calls that may overlap on the GPU (different streams,
 //    no ordering between them) race on it. Calls on one stream are safe. The counters are
 //    cleared by every call before the kernel runs, so a call does not depend on how the
@@ -904,7 +907,8 @@ static __device__ __align__(256) float g_noalloc_scratch[FF_NOALLOC_SCRATCH_BYTE
 static __device__ __align__(256) int g_noalloc_counters[FF_NOALLOC_MAX_TILES];
 
 struct NoAllocPtrs { float* scratch; int* counters; bool ready; };
-static NoAllocPtrs g_noalloc_ptrs[64] = {};
+static NoAllocPtrs g_noalloc_ptrs[FF_MAX_DEVICES] = {};
+static std::mutex g_noalloc_mu;
 }  // namespace ff
 
 FF_EXPORT int ff_gemm_skinny_noalloc(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
@@ -918,16 +922,21 @@ FF_EXPORT int ff_gemm_skinny_noalloc(const void* X, const void* W, void* Y, int 
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 0 || dev >= 64) return FF_HOST_UNSUPPORTED;
-  NoAllocPtrs& p = g_noalloc_ptrs[dev];
-  if (!p.ready) {
-    // In host code the array names are host-side stand-ins; the kernel needs the device address.
-    void* ps = nullptr; void* pc = nullptr;
-    e = cudaGetSymbolAddress(&ps, g_noalloc_scratch);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    e = cudaGetSymbolAddress(&pc, g_noalloc_counters);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    p.scratch = static_cast<float*>(ps); p.counters = static_cast<int*>(pc); p.ready = true;
+  if (dev < 0 || dev >= FF_MAX_DEVICES) return FF_HOST_UNSUPPORTED;
+  NoAllocPtrs p;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocPtrs& slot = g_noalloc_ptrs[dev];
+    if (!slot.ready) {
+      // In host code the array names are host-side stand-ins; the kernel needs the device address.
+      void* ps = nullptr; void* pc = nullptr;
+      e = cudaGetSymbolAddress(&ps, g_noalloc_scratch);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      e = cudaGetSymbolAddress(&pc, g_noalloc_counters);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      slot.scratch = static_cast<float*>(ps); slot.counters = static_cast<int*>(pc); slot.ready = true;
+    }
+    p = slot;
   }
   e = cudaMemsetAsync(p.counters, 0, (size_t)counter_bytes, stream);
   if (e != cudaSuccess) return static_cast<int>(e);

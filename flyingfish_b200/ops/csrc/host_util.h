@@ -6,6 +6,9 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <map>
+#include <mutex>
+#include <utility>
 
 namespace ff {
 
@@ -75,14 +78,25 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   return r == CUDA_SUCCESS ? FF_HOST_OK : FF_HOST_TMAP_FAIL;
 }
 
+constexpr int FF_MAX_DEVICES = 64;
+
+// index of the current device, clamped into the per-device caches below
+inline int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return dev < 0 ? 0 : (dev >= FF_MAX_DEVICES ? FF_MAX_DEVICES - 1 : dev);
+}
+
+// SM count of the current device (cached per device: one process may drive several GPUs)
 inline int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  static int n[FF_MAX_DEVICES] = {};
+  const int dev = current_device();
+  if (n[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
   }
-  return n;
+  return n[dev];
 }
 
 inline int launch_result() {
@@ -124,10 +138,21 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
   return FF_HOST_OK;
 }
 
+// Opt a kernel in to `bytes` of dynamic shared memory on the CURRENT device. The attribute is per
+// device, so the "already done" record is keyed by (device, kernel); launchers call this before
+// every launch and pay a map look-up when nothing is to be done. Safe from several host threads.
 template <typename K>
 inline int opt_in_smem(K kernel, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> done;
+  const std::pair<int, const void*> key(current_device(), reinterpret_cast<const void*>(kernel));
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = done.find(key);
+  if (it != done.end() && it->second >= bytes) return FF_HOST_OK;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  return e == cudaSuccess ? FF_HOST_OK : static_cast<int>(e);
+  if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
+  done[key] = bytes;
+  return FF_HOST_OK;
 }
 
 }  // namespace ff

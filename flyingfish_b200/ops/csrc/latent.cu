@@ -297,8 +297,7 @@ FF_EXPORT int ff_latent_window_attention(const void* q, const void* codes, const
   if (rope_tail < 0 || rope_tail > D || rope_tail % 2 || !(scale > 0.f)) return FF_HOST_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(codes) & 15)) return FF_HOST_BAD_ALIGN;
   const int smem = 16 * D * 2 + LW_KEYS * D * 2 + 16 * LW_KEYS * 4 + 16 * LW_KEYS * 2 + 3 * 16 * 4;
-  static int attr_smem = 0;
-  if (smem > attr_smem) { if (int r = opt_in_smem(latent_window_attention_kernel<0>, smem)) return r; attr_smem = smem; }
+  if (int r = opt_in_smem(latent_window_attention_kernel<0>, smem)) return r;
   dim3 grid((heads + 15) / 16, batch);
   if (int lr = launch_pdl(latent_window_attention_kernel<0>, grid, dim3(128), smem, s, 0, (const __nv_bfloat16*)q,
                           (const uint8_t*)codes, (const uint8_t*)scales, ring_ids, positions, sink, inv_rotary,
@@ -317,8 +316,7 @@ FF_EXPORT int ff_latent_sparse_attention(const void* q, const void* latent, cons
   if (!(scale > 0.f)) return FF_HOST_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(latent) & 15)) return FF_HOST_BAD_ALIGN;
   const int smem = 16 * D * 2 + LW_KEYS * D * 2 + 16 * LW_KEYS * 4 + 16 * LW_KEYS * 2 + 3 * 16 * 4;
-  static int attr_smem = 0;
-  if (smem > attr_smem) { if (int r = opt_in_smem(latent_window_attention_kernel<1>, smem)) return r; attr_smem = smem; }
+  if (int r = opt_in_smem(latent_window_attention_kernel<1>, smem)) return r;
   dim3 grid((heads + 15) / 16, rows);
   if (int lr = launch_pdl(latent_window_attention_kernel<1>, grid, dim3(128), smem, s, 0, (const __nv_bfloat16*)q,
                           (const uint8_t*)nullptr, (const uint8_t*)nullptr, (const int*)nullptr, (const int*)nullptr, sink,

@@ -146,8 +146,7 @@ FF_EXPORT int ff_mhc_mixes(const void* stream, const void* fn, const float* base
     return FF_HOST_BAD_SHAPE;
   const int smem = mult * hidden * 2;
   if (smem > 200 * 1024) return FF_HOST_TOO_LARGE;
-  static int attr = 0;
-  if (smem > attr) { if (int r = opt_in_smem(mhc_mixes_kernel, smem)) return r; attr = smem; }
+  if (int r = opt_in_smem(mhc_mixes_kernel, smem)) return r;
   if (int lr = launch_pdl(mhc_mixes_kernel, dim3(rows), dim3(256), smem, s, 0, (const __nv_bfloat16*)stream, (const __nv_bfloat16*)fn,
                           base, scale, mult, hidden, iters, eps, norm_eps, pre, post, comb)) return lr;
   return launch_result();

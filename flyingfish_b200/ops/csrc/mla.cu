@@ -250,8 +250,7 @@ FF_EXPORT int ff_mla_attn(const void* q, const void* cache, const int* block_tab
                           int max_blocks, int num_blocks, int nsplit, float scale, int* status, cudaStream_t s) {
   if (batch <= 0 || heads <= 0 || max_q <= 0 || nsplit < 1) return FF_HOST_BAD_SHAPE;
   if (nsplit > 1 && (!part_o || !part_ml)) return FF_HOST_BAD_SHAPE;
-  static bool attr = false;
-  if (!attr) { if (int r = opt_in_smem(mla::mla_attn_kernel, MLA_SMEM)) return r; attr = true; }
+  if (int r = opt_in_smem(mla::mla_attn_kernel, MLA_SMEM)) return r;
   const int max_rows = max_q * heads;
   dim3 grid((max_rows + 15) / 16, nsplit, batch);
   mla::mla_attn_kernel<<<grid, 128, MLA_SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table,

@@ -425,8 +425,7 @@ FF_EXPORT int ff_moe_grouped_gemm(const void* xs, const void* w, void* y, const 
   const int staging = 64 * GBM * 4;                      // 32 KiB
   const int pipe_bytes = 3 * (GBM * GBK * 2 + G_TOK * GBK * 2);   // 3 full-width stages = 144 KiB
   const int smem = staging + pipe_bytes + 1024;
-  static bool attr = false;
-  if (!attr) { r = opt_in_smem(moe_grouped_gemm_kernel, 200 * 1024); if (r) return r; attr = true; }
+  r = opt_in_smem(moe_grouped_gemm_kernel, 200 * 1024); if (r) return r;
   dim3 grid(Nw / GBM, E_local);
   moe_grouped_gemm_kernel<<<grid, 192, smem, s>>>(tmW, tmX, (__nv_bfloat16*)y, seg_off, counts, Nw, K, ldy, epi,
                                                   pipe_bytes, staging, status);

@@ -288,8 +288,7 @@ FF_EXPORT int ff_moe_grouped_gemm_nvfp4(const void* xs, const void* wq, const vo
   int r = make_tmap_2d(&tmX, xs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, capacity, (uint64_t)K * 2, 64, 16);
   if (r) return r;
   const int smem = F4_STAGING + F4_STAGES * F4_STAGE_BYTES + 1024;
-  static bool attr = false;
-  if (!attr) { r = opt_in_smem(moe_fp4_grouped_kernel, smem); if (r) return r; attr = true; }
+  r = opt_in_smem(moe_fp4_grouped_kernel, smem); if (r) return r;
   dim3 grid(Nw / F4_BM, E_local);
   moe_fp4_grouped_kernel<<<grid, 192, smem, s>>>(tmX, (const uint8_t*)wq, (const uint8_t*)wsc, wglobal, (__nv_bfloat16*)y,
                                                  seg_off, counts, Nw, K, ldy, epi, status);

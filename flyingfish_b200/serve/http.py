@@ -99,8 +99,11 @@ class Server:
         self._seq = itertools.count()
         self.template = None
         if chat_template:
+            # the template comes from the checkpoint directory, i.e. from whoever published the model: render it
+            # in the immutable sandbox so it cannot reach Python internals (``__class__``, ``__globals__`` ...)
             import jinja2
-            env = jinja2.Environment(loader=jinja2.BaseLoader(), trim_blocks=False, lstrip_blocks=False)
+            from jinja2.sandbox import ImmutableSandboxedEnvironment
+            env = ImmutableSandboxedEnvironment(loader=jinja2.BaseLoader(), trim_blocks=False, lstrip_blocks=False)
 
             def raise_exception(msg):
                 raise jinja2.TemplateError(msg)

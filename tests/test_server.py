@@ -144,3 +144,26 @@ def test_engine_failure_marks_backend_unavailable(model):
         r = await client.post("/v1/completions", json={"prompt": "after", "max_tokens": 2})
         assert r.status == 500 and "unavailable" in (await r.text())
     _run(model, go)
+
+
+def test_chat_template_is_sandboxed(model):
+    """A template shipped with a checkpoint must not reach Python internals: the attribute walk below executes code
+    under a plain jinja2 environment; the sandboxed one refuses it and the request ends as a 422."""
+    hostile = "{{ messages.__class__.__base__.__subclasses__() }}"
+
+    async def main():
+        backend = Backend(model.engine, eos_ids=(257,))
+        backend.start()
+        srv = Server(backend, ByteTokenizer(model.spec.vocab), "tiny-llama", hostile, capacity=256)
+        client = TestClient(TestServer(srv.app()))
+        await client.start_server()
+        try:
+            r = await client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}]})
+            assert r.status == 422
+            body = await r.json()
+            assert "chat template render" in json.dumps(body)
+        finally:
+            await client.close()
+            backend.shutdown()
+            model.engine.reset()
+    asyncio.run(main())
