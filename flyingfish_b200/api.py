@@ -49,7 +49,7 @@ class Model:
 
     # -- construction ------------------------------------------------------------------------
     @classmethod
-    def load(cls, model: str, settings: Settings | None = None, device: str | torch.device | None = None,
+    def load(cls, model: "str | ModelSpec", settings: Settings | None = None, device: str | torch.device | None = None,
              random_init: bool | None = None, seed: int = 0, comm=None, ep=None) -> "Model":
         """Load a checkpoint directory, or a named shape with seeded random weights
         (``random_init``; implied when ``model`` names a shape rather than a directory)."""
@@ -59,10 +59,13 @@ class Model:
             device = f"cuda:{settings.device}" if torch.cuda.is_available() else "cpu"
         device = torch.device(device)
         tokenizer = None
+        preset: ModelSpec | None = None
+        if isinstance(model, ModelSpec):          # an explicit (possibly modified) shape: random-init weights
+            preset, model = model, model.name
         path = Path(model)
         tp = TPInfo(comm.rank, comm.size) if comm is not None else TPInfo()
         epi = TPInfo(ep.rank, ep.size) if ep is not None else TPInfo()
-        if path.is_dir() and not random_init:
+        if preset is None and path.is_dir() and not random_init:
             from .loaders.checkpoint import load_decoder_weights
             from .loaders.tokenizer import load_tokenizer
             spec = read_model_spec(path)
@@ -70,7 +73,7 @@ class Model:
             tokenizer = load_tokenizer(path)
             name = path.name
         else:
-            spec = read_model_spec(path) if path.is_dir() else named_shape(model)
+            spec = preset if preset is not None else (read_model_spec(path) if path.is_dir() else named_shape(model))
             if spec.mla is not None:
                 from .models.deepseek import build_deepseek_weights
                 from .models.weights import DTYPES, synthetic_source
