@@ -141,6 +141,8 @@ class Engine:
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
             ops.read_status(self.device)
+            from ..ops import chain
+            chain.reset_workspace(self.device)      # phase counters of the decode chain, in case a step timed out
 
     def _check(self) -> None:
         if self.poisoned:

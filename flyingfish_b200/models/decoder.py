@@ -108,6 +108,8 @@ class DecoderModel:
         self._rope_cs = None
         if inputs_embeds is None and self._sequence_parallel(b):
             return self._hidden_states_sp(b, kv)
+        if self._chain_ok(b):
+            return self._hidden_states_chain(b, kv, inputs_embeds)
         if b.positions.is_cuda and b.positions.shape[0] <= ops.SKINNY_MAX_M and self.d == 128 and not s.qk_norm:
             # one cos/sin table per step for the fused QKV + rotary + KV-write kernels of all layers
             self._rope_cs = ops.rope_table(b.positions, self.d, s.rope_theta)
@@ -130,6 +132,50 @@ class DecoderModel:
             n = ops.add_rmsnorm(dn, x, next_w, s.rms_eps, capture=cap)
             if self.trace is not None:
                 self.trace.record(f"layer.{i}", x)
+        self.last_residual = x
+        if self.normed_sink is not None:
+            self.normed_sink.append(n)
+        return n
+
+    # -- decode through the per-layer projection chain ------------------------------------------
+    def _chain_ok(self, b: ForwardBatch) -> bool:
+        """Decode batches of a dense layer stack on one GPU run every layer's projections and norms as one
+        persistent kernel (``ops/chain.py``); everything it does not cover takes the operator-by-operator path."""
+        from ..ops import chain
+        s = self.spec
+        if not (chain.ENABLED and b.is_decode and b.positions.is_cuda and b.rows <= chain.MAX_ROWS):
+            return False
+        if getattr(self.comm, "size", 1) != 1 or self.trace is not None or self.capture_taps or s.qk_norm:
+            return False
+        if self.d != 128 or s.hidden > chain.MAX_HIDDEN or s.hidden % 128 or s.swiglu_mode != 0:
+            return False
+        for lw in self.w.layers:
+            if lw.router is not None or not lw.wgu_interleaved or lw.wgu.shape[0] % 256 or lw.wdown.shape[1] % 8:
+                return False
+        return True
+
+    def _hidden_states_chain(self, b: ForwardBatch, kv: PagedKVCache, inputs_embeds: torch.Tensor | None) -> torch.Tensor:
+        from ..ops import chain
+        w, s = self.w, self.spec
+        cs = ops.rope_table(b.positions, self.d, s.rope_theta)
+        if inputs_embeds is None:
+            x, n = ops.embed_rmsnorm(b.ids, w.embed, w.layers[0].input_ln, s.rms_eps)
+        else:
+            x = inputs_embeds.clone()
+            n = ops.rmsnorm(x, w.layers[0].input_ln, s.rms_eps)
+        qkv = ops.linear_rope_kv(n, w.layers[0].wqkv, b.positions, b.slots, kv.k[0], kv.v[0], self.hq, self.hkv, self.d,
+                                 s.rope_theta, cos_sin=cs)
+        for i in range(s.layers):
+            lw = w.layers[i]
+            a = ops.attn_decode(qkv, kv.k[i], kv.v[i], b.block_table, b.ctx_lens, self.hq, self.hkv, self.d, self.scale,
+                                nq=b.nq, tree_mask=b.tree_mask, max_ctx=b.max_ctx)
+            last = i + 1 == s.layers
+            rope = None if last else {"cos_sin": cs, "slots": b.slots, "kcache": kv.k[i + 1], "vcache": kv.v[i + 1],
+                                      "hq": self.hq, "hkv": self.hkv, "rot_dim": self.d}
+            n, qkv = chain.layer_chain(a, x, lw.wo, lw.post_ln, lw.wgu, lw.wdown,
+                                       w.final_norm if last else w.layers[i + 1].input_ln, s.rms_eps,
+                                       None if last else w.layers[i + 1].wqkv, rope)
+            ops._count()
         self.last_residual = x
         if self.normed_sink is not None:
             self.normed_sink.append(n)

@@ -35,6 +35,7 @@ enum KernelId : int {
   KID_MOE_DISPATCH = 15, KID_MOE_GEMM = 16, KID_MOE_COMBINE = 17, KID_QUANT = 18,
   KID_GEMM_FP8 = 19, KID_GEMM_NVFP4 = 20, KID_MLA = 21, KID_VERIFY = 22, KID_KV = 23,
   KID_DSA = 24, KID_LATENT = 25, KID_GDN = 26, KID_MHC = 27, KID_MARKOV = 28, KID_VISION = 29,
+  KID_CHAIN = 30,
 };
 
 __device__ __forceinline__ void set_status(int* status, int kid, int code, int d0 = 0, int d1 = 0) {

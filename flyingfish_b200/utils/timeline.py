@@ -25,7 +25,7 @@ import numpy as np
 import torch
 
 KERNEL_NAMES = {1: "gemm_bf16", 2: "gemm_skinny", 3: "embed", 4: "norm", 5: "rope_kv", 6: "act", 7: "attn_decode",
-                8: "attn_prefill", 9: "sample", 10: "allreduce", 11: "gemm_ar"}
+                8: "attn_prefill", 9: "sample", 10: "allreduce", 11: "gemm_ar", 30: "chain"}
 
 
 def reset(device=None) -> None:
