@@ -178,7 +178,7 @@ __device__ __forceinline__ void allreduce_tile(const TileSink<true>& sink, int M
 // cl_size == 1: persistent stream-K over gridDim.x CTAs.  cl_size > 1: cluster split-K, cluster c
 // owns weight tile c, CTA r of it the k-blocks [kblocks*r/S, kblocks*(r+1)/S).
 template <bool FUSE_AR>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldy, int ntok, int tile_rows, int stages,
                    int cl_size, int pipe_off, float* __restrict__ scratch, int* __restrict__ counters, int* status,
@@ -192,7 +192,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   // cluster mode: receive buffer [source CTA][owned row][tile_rows + SP_PAD] FP32 for the partials of this CTA's rows
   float* recv = reinterpret_cast<float*>(smem);
   uint8_t* pipe = smem + pipe_off;
-  constexpr int A_BYTES = STOK * SBK * 2;            // activation tile region (ntok rows of it are loaded)
+  // activation rows of a stage: only the ntok loaded rows take space; the UMMA reads 128 rows, i.e. on into the
+  // stage's own weight tile (and the next stage; the launcher leaves slack behind the last one), and those
+  // accumulator lanes are never read back
+  const int A_BYTES = ntok * SBK * 2;
   const int stage_bytes = A_BYTES + tile_rows * SBK * 2;
   const int tx_bytes = (ntok + tile_rows) * SBK * 2;
   uint32_t tmem_cols = 32; while ((int)tmem_cols < 2 * tile_rows) tmem_cols <<= 1;
@@ -544,7 +547,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 }  // namespace ff
 using namespace ff;
 
-constexpr int SK_SMEM_LIMIT = 200 * 1024;       // pipeline bytes a CTA may use (one CTA per SM)
+// Pipeline (and cluster receive buffer) bytes a CTA may use: one CTA per SM. FF_SKINNY_SMEM_KB=110 leaves room
+// for two, so that under programmatic dependent launch the next kernel's CTAs are resident (barriers, tensor memory,
+// first weight stages ready) while this kernel still streams; measured slower (6.82 against 6.13 ms per Llama-3-8B
+// decode step at batch 64): the waiting CTAs' polling and early weight requests take more from the running kernel
+// than their head start gives back.
+static int sk_smem_limit() {
+  static int v = 0;
+  if (v == 0) {
+    v = 200 * 1024;
+    if (const char* ev = getenv("FF_SKINNY_SMEM_KB")) { const int kb = atoi(ev); if (kb >= 64 && kb <= 200) v = kb * 1024; }
+  }
+  return v;
+}
+constexpr int SK_SMEM_FULL = 200 * 1024;        // budget of a CTA that has its SM to itself (more than 64 tokens)
+// budget for a launch of M tokens: the split of a problem is chosen for 64 tokens under the small budget and kept for
+// every M (a row's bits must not depend on the batch it is computed in); only the pipeline depth follows M
+static int sk_smem_for(int M) { return M <= 64 ? sk_smem_limit() : SK_SMEM_FULL; }
 
 // Largest number of co-resident clusters of `s` CTAs of this kernel (0 when such a cluster cannot be
 // launched); queried once per cluster size.
@@ -556,9 +575,9 @@ static int skinny_max_clusters(int s) {
   int* cached = cache[current_device()];
   if (cached[s] >= 0) return cached[s];
   auto kern = gemm_skinny_kernel<false>;
-  if (opt_in_smem(kern, SK_SMEM_LIMIT + 1024)) return 0;
+  if (opt_in_smem(kern, SK_SMEM_FULL + 1024)) return 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(s * 64); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = SK_SMEM_LIMIT + 1024;
+  cfg.gridDim = dim3(s * 64); cfg.blockDim = dim3(192); cfg.dynamicSmemBytes = SK_SMEM_FULL + 1024;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = s; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
@@ -573,8 +592,15 @@ static int skinny_max_clusters(int s) {
 // cluster > 1: cluster split-K, one cluster per tile, `tiles` clusters.
 struct SkinnyConfig { int cluster, tile_rows, tiles, stages, pipe_off; };
 
-static int skinny_stages(int tile_rows, int reserved = 0) {
-  int st = (SK_SMEM_LIMIT - reserved) / (STOK * SBK * 2 + tile_rows * SBK * 2);
+// bytes behind the last stage that the 128-row UMMA read of its activation tile may still touch
+static int skinny_tail_slack(int ntok, int tile_rows) {
+  const int stage = (ntok + tile_rows) * SBK * 2;
+  return stage >= STOK * SBK * 2 ? 0 : STOK * SBK * 2 - stage;
+}
+
+static int skinny_stages(int tile_rows, int reserved = 0, int ntok = 64, int limit = 0) {
+  if (limit == 0) limit = sk_smem_limit();
+  int st = (limit - reserved - skinny_tail_slack(ntok, tile_rows)) / ((ntok + tile_rows) * SBK * 2);
   if (st > SK_MAX_STAGES) st = SK_MAX_STAGES;
   if (const char* ev = getenv("FF_SKINNY_STAGES")) { const int v = atoi(ev); if (v >= 2 && v < st) st = v; }
   return st;
@@ -599,7 +625,7 @@ static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
   // than the ~1.5 us load latency / st, and all CTAs together cannot beat HBM (~5.9 TB/s on reads).
   // The choice must not depend on M: the K split fixes the order of the FP32 additions, and a
   // row's bits may not change with the batch it is computed in. So the model assumes 64 tokens and
-  // the receive buffer is sized for 128.
+  // the receive buffer is sized for those 64 (more tokens get the larger shared-memory budget and the same split).
   const int ntok = 64;
   (void)M;
   auto model = [&](int rows, int kb_per_cta, int st, double ctas) {
@@ -627,7 +653,7 @@ static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
       const int tiles = (N + rows - 1) / rows;
       if (tiles > maxc) continue;
       // receive buffer: S slots x ceil(M/S) rows of (rows + pad) floats, in front of the pipeline
-      const int recv = (s * ((STOK + s - 1) / s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
+      const int recv = (s * ((ntok + s - 1) / s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
       const int st = skinny_stages(rows, recv);
       if (st < 3) continue;
       const double c = model(rows, (kblocks + s - 1) / s, st, (double)tiles * s);
@@ -639,7 +665,9 @@ static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
     // follow the actual M
     const int s = best.cluster;
     best.pipe_off = (s * ((M + s - 1) / s) * (best.tile_rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
-    best.stages = skinny_stages(best.tile_rows, best.pipe_off);
+    best.stages = skinny_stages(best.tile_rows, best.pipe_off, (M + 15) / 16 * 16, sk_smem_for(M));
+  } else {
+    best.stages = skinny_stages(best.tile_rows, 0, (M + 15) / 16 * 16, sk_smem_for(M));
   }
   return best;
 }
@@ -717,17 +745,17 @@ static int gemm_skinny_launch(const void* X, const void* W, void* Y, int M, int 
   r = make_tmap_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, (uint64_t)ldw * 2, SBK, cfg.tile_rows);
   if (r) return r;
   if (cfg.stages < 2) return FF_HOST_TOO_LARGE;
-  const int smem = cfg.pipe_off + cfg.stages * (STOK * SBK * 2 + cfg.tile_rows * SBK * 2) + 1024;
+  const int smem = cfg.pipe_off + cfg.stages * (ntok + cfg.tile_rows) * SBK * 2 + skinny_tail_slack(ntok, cfg.tile_rows) + 1024;
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(Y);
   if (arena == nullptr) {
     auto kern = gemm_skinny_kernel<false>;
-    r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r;
+    r = opt_in_smem(kern, SK_SMEM_FULL + 1024); if (r) return r;
     PeerArena none = {};
     return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
                       cfg.stages, cl, cfg.pipe_off, scratch, counters, status, none, ep);
   }
   auto kern = gemm_skinny_kernel<true>;
-  r = opt_in_smem(kern, SK_SMEM_LIMIT + 1024); if (r) return r;
+  r = opt_in_smem(kern, SK_SMEM_FULL + 1024); if (r) return r;
   return launch_pdl(kern, dim3(grid), dim3(192), smem, stream, cl, tmX, tmW, y, M, N, K, ldy, ntok, cfg.tile_rows,
                     cfg.stages, cl, cfg.pipe_off, scratch, counters, status, *arena, ep);
 }
