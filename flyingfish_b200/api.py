@@ -125,8 +125,25 @@ class Model:
         """Start a sequence with ``ids``; returns the first generated token."""
         if self._seq is not None:
             self.engine.free_sequence(self._seq.seq_id)
-        self._seq = self.engine.add_sequence(ids)
-        return self.engine.prefill([self._seq])[0]
+            self._seq = None
+        store = self.prefix_store()
+        if store is not None:
+            self._seq = store.restore(self, ids)
+        if self._seq is None:
+            self._seq = self.engine.add_sequence(ids)
+        first = self.engine.prefill([self._seq])[0]
+        if store is not None:
+            store.store(self, self._seq)
+        return first
+
+    def prefix_store(self):
+        """The on-disk prefix cache of ``--prefix-cache true`` (under the runtime directory), or None."""
+        if not self.settings.prefix_cache:
+            return None
+        if getattr(self, "_prefix_store", None) is None:
+            from .utils.prefix_cache import PrefixStore
+            self._prefix_store = PrefixStore(self.settings.resolved_runtime_dir() / "prefix")
+        return self._prefix_store
 
     def encode_images(self, ids: list[int], images: list) -> tuple[list[int], list[int], torch.Tensor]:
         """Runs the vision tower over ``images`` (``serve.image.Image``) and expands every image placeholder of

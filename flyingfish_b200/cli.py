@@ -42,7 +42,7 @@ def _global_parser() -> argparse.ArgumentParser:
     p.add_argument("--dram-gb-s", type=float, default=6550.0)
     p.add_argument("--gemm-tflops", type=float, default=1385.0)
     p.add_argument("--max-batch", type=int, default=64)
-    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (the command re-launches itself, one process per GPU)")
     p.add_argument("--cpu", action="store_true", help="run on the host (tiny shapes / debugging)")
     p.add_argument("--seed", type=int, default=0)
     sub = p.add_subparsers(dest="command", required=True)
@@ -163,6 +163,44 @@ def resolve_mtp_depth(requested: int | None, has_mtp: bool, arch: str) -> int:
     return 0 if arch == "deepseek_v3" else 4
 
 
+def check_flags(args) -> None:
+    """Every flag either changes behaviour or is refused: nothing is parsed and then ignored."""
+    if args.kv_format != "bf16":
+        raise SystemExit("--kv-format affine8: the 8-bit cache format is implemented as pack/unpack kernels and byte "
+                         "accounting only; no attention kernel reads its codes yet, so serving from it is refused")
+    if args.tp < 1 or (args.tp > 1 and args.cpu):
+        raise SystemExit("--tp needs one CUDA device per rank")
+    if args.tp > 1 and args.command not in ("generate", "bench", "serve"):
+        raise SystemExit(f"--tp applies to generate, bench and serve, not to {args.command}")
+    if args.draft_model and args.command != "generate":
+        raise SystemExit("--draft-model applies to generate")
+    if args.draft_model and args.tp > 1:
+        raise SystemExit("--draft-model with --tp is not supported")
+    if args.spec_budget != "chain" and not args.draft_model:
+        raise SystemExit("--spec-budget needs --draft-model")
+    if args.prefix_cache and args.command != "generate":
+        raise SystemExit("--prefix-cache applies to generate (the server's batched scheduler does not consult the store)")
+    if not args.spec_graph and not args.draft_model:
+        raise SystemExit("--spec-graph applies to --draft-model speculation")
+    if args.prefix_cache and args.tp > 1:
+        raise SystemExit("--prefix-cache with --tp is not supported")
+
+
+def _world() -> tuple[int, int, int]:
+    return int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def relaunch_tp(args, argv: list[str]) -> int | None:
+    """``--tp N`` outside a launcher: start N ranks of this same command line (rank 0 prints the result)."""
+    if args.tp <= 1 or _world()[0] > 1:
+        return None
+    import subprocess
+    port = int(os.environ.get("FLYINGFISH_MASTER_PORT", "29517"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.tp}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "flyingfish_b200.cli", *argv]
+    return subprocess.call(cmd)
+
+
 def _load(args):
     import torch
     from .api import Model
@@ -170,9 +208,26 @@ def _load(args):
     if not args.model:
         raise SystemExit("--model (or FLYINGFISH_MODEL) is required before the subcommand")
     st = settings_from(args)
-    device = "cpu" if args.cpu or not torch.cuda.is_available() else f"cuda:{args.device}"
+    world, rank, local = _world()
+    comm = None
+    if args.tp > 1:
+        if world != args.tp:
+            raise SystemExit(f"--tp {args.tp} but the launcher started {world} ranks")
+        import torch.distributed as dist
+        from .parallel.comm import TPComm
+        from .config import named_shape, read_model_spec
+        torch.cuda.set_device(local)
+        if not dist.is_initialized():
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        spec = read_model_spec(args.model) if Path(args.model).is_dir() else named_shape(args.model)
+        comm = TPComm.create(dist.group.WORLD, torch.device("cuda", local), slot_bytes=(8192 // world) * spec.hidden * 2)
+        device = f"cuda:{local}"
+        st.device = local
+    else:
+        device = "cpu" if args.cpu or not torch.cuda.is_available() else f"cuda:{args.device}"
     with with_verbose(args.verbose):
-        return Model.load(args.model, st, device=device, seed=args.seed)
+        return Model.load(args.model, st, device=device, seed=args.seed, comm=comm)
 
 
 def cmd_generate(args) -> dict:
@@ -208,7 +263,25 @@ def cmd_generate(args) -> dict:
     depth = resolve_mtp_depth(args.mtp, model.spec.mtp_layers > 0, model.spec.arch)
     mode = "plain"
     extra = {}
-    if depth > 0:
+    if args.draft_model:
+        # a small model drafts, the target verifies: a chain of k tokens, or a token tree under ancestor masks
+        from .api import Model
+        st = settings_from(args)
+        st.graph = bool(args.spec_graph)         # --spec-graph false: the draft model decodes eagerly
+        draft = Model.load(args.draft_model, st, device=str(model.engine.device), seed=args.seed + 1)
+        if args.spec_budget == "chain":
+            from .spec.chain import ChainSpeculator
+            sp = ChainSpeculator(model, draft, k=4)
+            mode = "draft-chain"
+        else:
+            from .spec.tree_spec import TreeSpeculator
+            sp = TreeSpeculator(model, draft, budget=args.spec_budget, builder=args.tree_builder)
+            mode = f"draft-{args.spec_budget}"
+        out = sp.generate(ids, args.max_new_tokens, ignore_eos=True)
+        extra = {"draft_model": args.draft_model, "spec_budget": args.spec_budget, "tree_builder": args.tree_builder,
+                 "rounds": sp.stats.rounds, "acceptance_rate": sp.stats.acceptance_rate,
+                 "tokens_per_round": sp.stats.tokens_per_round}
+    elif depth > 0:
         from .spec.mtp import generate_mtp
         out = generate_mtp(model, ids, args.max_new_tokens, depth=depth, ignore_eos=args.ignore_eos)
         mode = "mtp"
@@ -216,6 +289,9 @@ def cmd_generate(args) -> dict:
                  "accepted_per_round": out.extra.get("accepted_per_round")}
     else:
         out = generate_plain(model, ids, args.max_new_tokens, ignore_eos=args.ignore_eos, graph=args.graph)
+        store = model.prefix_store()
+        if store is not None:
+            extra = {"prefix_cache": {"hits": store.hits, "stored": store.stored, "dir": str(store.root)}}
     if trace is not None:
         trace.save(args.dump)
     return {"input_ids": ids, "generated_ids": out.ids, "text": tk.decode(out.ids), "load_ms": model.load_ms,
@@ -345,8 +421,25 @@ def cmd_serve(args) -> None:
     from .loaders.tokenizer import read_chat_template
     from .serve.http import run
     model = _load(args)
+    depth = resolve_mtp_depth(args.mtp, model.spec.mtp_layers > 0, model.spec.arch) if args.mtp is not None else 0
+    if depth > 0 and args.tp > 1:
+        raise SystemExit("serve --mtp with --tp is not supported")
     tmpl = read_chat_template(args.model) if Path(args.model).is_dir() else None
-    run(model, port=args.port, allow_sampling=args.allow_sampling, chat_template=tmpl)
+    engine = None
+    if args.tp > 1:
+        # rank 0 serves; the other ranks execute the engine calls it announces
+        import torch.distributed as dist
+        from .parallel.driver import EngineLeader, follow
+        host_group = dist.new_group(backend="gloo")
+        if _world()[1] != 0:
+            follow(model.engine, host_group)
+            return
+        engine = EngineLeader(model.engine, host_group)
+    try:
+        run(model, port=args.port, allow_sampling=args.allow_sampling, chat_template=tmpl, mtp_depth=depth, engine=engine)
+    finally:
+        if engine is not None:
+            engine.stop()
 
 
 def cmd_verify(args) -> dict:
@@ -366,7 +459,12 @@ def cmd_spec(args) -> dict:
 
 
 def main(argv: list[str] | None = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
     args = _global_parser().parse_args(argv)
+    check_flags(args)
+    rc = relaunch_tp(args, argv)
+    if rc is not None:
+        return rc
     handlers = {"generate": cmd_generate, "bench": cmd_bench, "profile": cmd_profile, "inspect": cmd_inspect,
                 "tokenize": cmd_tokenize, "calibrate": cmd_calibrate, "embed": cmd_embed, "verify": cmd_verify,
                 "compare-prefill": cmd_verify, "compare-log": cmd_compare_log, "verify-spec": cmd_spec,
@@ -375,7 +473,8 @@ def main(argv: list[str] | None = None) -> int:
         cmd_serve(args)
         return 0
     out = handlers[args.command](args)
-    print(json.dumps(out, default=str))
+    if _world()[1] == 0:
+        print(json.dumps(out, default=str))
     return 0
 
 

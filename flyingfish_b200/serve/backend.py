@@ -155,3 +155,83 @@ class Backend:
             return None
         s = sorted(self.ttft_ms)
         return s[len(s) // 2]
+
+
+class MtpBackend(Backend):
+    """Server backend for ``ff serve --mtp N``: every request is generated by multi-token-prediction speculation
+    (draft with the MTP head, verify with one multi-row target forward). Speculation rounds are per sequence, so
+    admission is the reference's single slot (src/serve/mod.rs:41-59, ``run_mtp`` :144-161): a second request while
+    one runs is answered 409."""
+
+    def __init__(self, model, depth: int, eos_ids: tuple[int, ...] = ()):
+        super().__init__(model.engine, eos_ids=eos_ids, max_inflight=1)
+        from ..spec.mtp import MtpSpeculator
+        self.spec = MtpSpeculator(model, depth=depth)
+        self.depth = depth
+
+    def _loop(self) -> None:
+        try:
+            while not self._stop:
+                try:
+                    cmd, req = self._cmd.get(timeout=0.05)
+                except queue.Empty:
+                    self.state = "idle"
+                    continue
+                if cmd == "stop":
+                    break
+                if cmd == "abort":
+                    req.state = "aborted"
+                    continue
+                if cmd != "add" or req.state == "aborted":
+                    continue
+                self.state = "running"
+                req.state = "running"
+
+                def on_tokens(toks, req=req):
+                    if req.first_token_time is None:
+                        req.first_token_time = time.perf_counter()
+                    req.output.extend(toks)
+                    self._on_tokens(req, toks)
+
+                def should_stop(req=req):
+                    # an abort for this request may be waiting in the queue
+                    try:
+                        while True:
+                            c, r = self._cmd.get_nowait()
+                            if c == "abort" and r is req:
+                                req.state = "aborted"
+                            elif c == "stop":
+                                self._stop = True
+                                req.state = "aborted"
+                            else:
+                                self._cmd.put((c, r))
+                                break
+                    except queue.Empty:
+                        pass
+                    return req.state == "aborted"
+
+                if len(req.prompt) + req.max_tokens + self.depth + 1 > self.engine.settings.capacity:
+                    req.state, req.error = "failed", "prompt + max_tokens exceeds the KV capacity"
+                    self._post(req, EngineEvent("failed", message=req.error))
+                    with self._lock:
+                        self._inflight.pop(req.req_id, None)
+                    continue
+                out = self.spec.generate(req.prompt, req.max_tokens, ignore_eos=req.ignore_eos, on_tokens=on_tokens,
+                                         should_stop=should_stop)
+                if req.state == "aborted":
+                    req.finish_reason = "aborted"
+                else:
+                    last = out.ids[-1] if out.ids else None
+                    req.state = "finished"
+                    req.finish_reason = "stop" if (not req.ignore_eos and last in self.eos_ids) else "length"
+                self._on_finish(req)
+        except Exception as e:
+            self.state = "unavailable"
+            msg = f"{type(e).__name__}: {e}"
+            log_json("engine_failure", error=msg, trace=traceback.format_exc()[-2000:])
+            with self._lock:
+                items = list(self._inflight.values())
+                self._inflight.clear()
+            for req, q, loop in items:
+                req.state = "failed"
+                loop.call_soon_threadsafe(q.put_nowait, EngineEvent("failed", message=msg))

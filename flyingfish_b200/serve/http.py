@@ -336,12 +336,17 @@ class Server:
 
 
 def run(model, port: int = 8080, host: str = "127.0.0.1", allow_sampling: bool = False,
-        chat_template: str | None = None) -> None:
+        chat_template: str | None = None, mtp_depth: int = 0, engine=None) -> None:
     """Blocking server entry point (``ff serve``). Ctrl-C shuts down gracefully."""
     eos = tuple(model.spec.extra.get("eos_token_ids", [model.spec.eos_token_id] if model.spec.eos_token_id is not None else []))
     from ..loaders.tokenizer import ByteTokenizer
     tk = model.tokenizer or ByteTokenizer(model.spec.vocab)
-    backend = Backend(model.engine, eos_ids=eos)
+    if mtp_depth > 0:
+        from .backend import MtpBackend
+        backend = MtpBackend(model, mtp_depth, eos_ids=eos)
+    else:
+        # ``engine``: a stand-in for the model's engine with the same methods (the tensor-parallel leader proxy)
+        backend = Backend(engine if engine is not None else model.engine, eos_ids=eos)
     backend.start()
     placeholder = None
     if getattr(model, "vision", None) is not None:

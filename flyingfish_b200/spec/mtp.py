@@ -120,7 +120,10 @@ class MtpSpeculator:
         return [int(t) for t in toks.cpu().tolist()], n
 
     # -- generation ---------------------------------------------------------------------------------
-    def generate(self, ids: list[int], count: int, ignore_eos: bool = True) -> GenerationOutput:
+    def generate(self, ids: list[int], count: int, ignore_eos: bool = True, on_tokens=None,
+                 should_stop=None) -> GenerationOutput:
+        """``on_tokens(list)`` receives every batch of emitted tokens (first token, then one call per round);
+        ``should_stop()`` is polled between rounds (client disconnect)."""
         te = self.target.engine
         spec = self.target.spec
         eos = tuple(spec.extra.get("eos_token_ids", [spec.eos_token_id] if spec.eos_token_id is not None else []))
@@ -142,11 +145,18 @@ class MtpSpeculator:
                 self._mtp_rows(ids[1:], hid[:-1], commit=len(ids) - 1)
             h_prev = hid[-1:]
             out = [first]
+            if on_tokens:
+                on_tokens([first])
             t1 = time.perf_counter()
             while len(out) < count and not (not ignore_eos and eos and out[-1] in eos):
+                if should_stop is not None and should_stop():
+                    break
                 k = min(self.depth, count - len(out))
                 emitted, h_prev = self._round(ts, h_prev, k, eos, ignore_eos)
+                emitted = emitted[: count - len(out)]
                 out.extend(emitted)
+                if on_tokens and emitted:
+                    on_tokens(emitted)
             out = out[:count]
             t2 = time.perf_counter()
             return GenerationOutput(ids=out, prefill_ms=(t1 - t0) * 1e3, decode_ms=(t2 - t1) * 1e3,

@@ -80,9 +80,9 @@ def save_prefix(model, seq, directory: str | Path) -> Path:
     return d
 
 
-def restore_prefix(model, directory: str | Path):
-    """Create a sequence whose cache holds the snapshot's prefix. Returns the sequence; its
-    ``prefilled`` equals the prefix length, so a longer prompt continues from there."""
+def restore_prefix(model, directory: str | Path, limit: int | None = None):
+    """Create a sequence whose cache holds the snapshot's prefix (its first ``limit`` tokens when given). Returns the
+    sequence; its ``prefilled`` equals the restored length, so a longer prompt continues from there."""
     d = Path(directory)
     try:
         man = json.loads((d / "manifest.json").read_text())
@@ -98,9 +98,11 @@ def restore_prefix(model, directory: str | Path):
     eng = model.engine
     if (man["layers"], man["kv_heads"], man["head_dim"]) != (eng.kv.layers, eng.kv.kv_heads, eng.kv.head_dim):
         raise PrefixError("prefix package geometry differs from the engine's cache")
-    n = man["length"]
-    seq = eng.add_sequence(list(man["tokens"]) + [0])       # placeholder next token; caller replaces the prompt
-    seq.prompt = list(man["tokens"])
+    n = man["length"] if limit is None else min(man["length"], limit)
+    if n <= 0:
+        raise PrefixError("nothing to restore")
+    seq = eng.add_sequence(list(man["tokens"][:n]) + [0])   # placeholder next token; caller replaces the prompt
+    seq.prompt = list(man["tokens"][:n])
     eng.kv.reserve(seq.seq_id, n)
     kvs = eng.kv.seqs[seq.seq_id]
     bs = eng.kv.block_size
@@ -113,10 +115,69 @@ def restore_prefix(model, directory: str | Path):
             for tag, cache in (("k", eng.kv.k[l]), ("v", eng.kv.v[l])):
                 if cache is None:
                     continue
-                rows = f.tensor(f"layer.{l}.{tag}").to(eng.device)          # [heads, n, dim]
+                rows = f.tensor(f"layer.{l}.{tag}")[:, :n].to(eng.device)   # [heads, n, dim]
                 cache[blk, :, off, :] = rows.permute(1, 0, 2).to(cache.dtype)
     finally:
         f.close()
     eng.kv.commit(seq.seq_id, n)
     seq.prefilled = n
     return seq
+
+
+class PrefixStore:
+    """Directory of prefix packages with an index, behind ``--prefix-cache true``: before a prompt is prefilled the
+    longest stored prefix of it is restored (only the rest is computed), afterwards the prompt's own cache is stored
+    (the reference wires its prefix state the same way around prefill, src/backend/cuda/engine.rs:3543-4007)."""
+
+    def __init__(self, root: str | Path):
+        self.root = Path(root)
+        self.root.mkdir(parents=True, exist_ok=True)
+        self.hits = 0
+        self.stored = 0
+
+    def _index(self) -> list[dict]:
+        p = self.root / "index.json"
+        try:
+            return json.loads(p.read_text())
+        except (OSError, json.JSONDecodeError):
+            return []
+
+    def lookup(self, model, ids: list[int]) -> tuple[Path, int] | None:
+        """Longest stored package whose tokens are a prefix of ``ids`` (at most ``len(ids) - 1`` tokens are used: the
+        last prompt token is always computed, it produces the first output)."""
+        digest = identity_for(model).digest()
+        best = None
+        for ent in self._index():
+            n = min(ent["length"], len(ids) - 1)
+            if ent["identity"] != digest or n <= 0:
+                continue
+            if ent["length"] <= len(ids) and token_hash(ids[: ent["length"]]) == ent["token_hash"]:
+                if best is None or n > best[1]:
+                    best = (self.root / ent["dir"], n)
+        return best
+
+    def restore(self, model, ids: list[int]):
+        """A sequence for ``ids`` whose first tokens come from the store, or None on a miss. The caller prefills it."""
+        hit = self.lookup(model, ids)
+        if hit is None:
+            return None
+        seq = restore_prefix(model, hit[0], limit=hit[1])
+        seq.prompt = list(ids)
+        self.hits += 1
+        return seq
+
+    def store(self, model, seq) -> Path | None:
+        """Store the committed prompt of ``seq`` unless an identical package exists."""
+        n = min(model.engine.kv.seqs[seq.seq_id].length, len(seq.prompt))
+        tokens = seq.prompt[:n]
+        th = token_hash(tokens)
+        index = self._index()
+        digest = identity_for(model).digest()
+        if n == 0 or any(e["token_hash"] == th and e["identity"] == digest for e in index):
+            return None
+        name = f"{th[:16]}-{n}"
+        d = save_prefix(model, seq, self.root / name)
+        index.append({"dir": name, "length": n, "token_hash": th, "identity": digest})
+        (self.root / "index.json").write_text(json.dumps(index))
+        self.stored += 1
+        return d

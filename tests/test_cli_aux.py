@@ -182,3 +182,125 @@ def test_generate_for_the_other_model_families(tmp_path, capsys):
     for name in ("tiny-hybrid", "tiny-gemma"):
         g = run(*base, "--model", name, "generate", "--tokens", "5,6,7,8", "--max-new-tokens", "4", "--ignore-eos")
         assert len(g["generated_ids"]) == 4
+
+
+# ---- every flag changes behaviour or is refused ---------------------------------------------------------------------
+BASE = ["--model", "tiny-llama", "--cpu", "--capacity", "256"]
+GEN = ["generate", "--tokens", "5,6,7,8,9,10,11", "--max-new-tokens", "9", "--ignore-eos"]
+
+
+def test_flags_without_an_implementation_are_refused(capsys):
+    for extra in (["--kv-format", "affine8"], ["--tp", "2"], ["--spec-budget", "tree16"], ["--spec-graph", "false"]):
+        with pytest.raises(SystemExit):
+            cli.main(BASE + extra + GEN)
+    with pytest.raises(SystemExit):      # a draft model only makes sense for generate
+        cli.main(BASE + ["--draft-model", "tiny-llama", "tokenize", "--prompt", "x"])
+    with pytest.raises(SystemExit):      # the server's scheduler does not consult the prefix store
+        cli.main(BASE + ["--prefix-cache", "true", "serve"])
+
+
+def test_draft_model_flags_select_the_speculator(capsys):
+    plain = _run(BASE + GEN, capsys)
+    chain = _run(BASE + ["--draft-model", "tiny-llama"] + GEN, capsys)
+    assert chain["mode"] == "draft-chain" and chain["rounds"] > 0
+    assert chain["generated_ids"] == plain["generated_ids"]         # speculation never changes greedy output
+    for builder in ("waves", "serial"):
+        tree = _run(BASE + ["--draft-model", "tiny-llama", "--spec-budget", "tree16", "--tree-builder", builder] + GEN, capsys)
+        assert tree["mode"] == "draft-tree16" and tree["tree_builder"] == builder
+        assert tree["generated_ids"] == plain["generated_ids"]
+
+
+def test_prefix_cache_flag_restores_a_stored_prompt(capsys, tmp_path):
+    args = BASE + ["--prefix-cache", "true", "--runtime-dir", str(tmp_path)]
+    plain = _run(BASE + GEN, capsys)
+    first = _run(args + GEN, capsys)
+    assert first["prefix_cache"] == {"hits": 0, "stored": 1, "dir": str(tmp_path / "prefix")}
+    second = _run(args + GEN, capsys)
+    assert second["prefix_cache"]["hits"] == 1 and second["prefix_cache"]["stored"] == 0
+    assert first["generated_ids"] == second["generated_ids"] == plain["generated_ids"]
+    # a longer prompt that starts with the stored one restores it and computes only the rest
+    longer = ["generate", "--tokens", "5,6,7,8,9,10,11,12,13", "--max-new-tokens", "4", "--ignore-eos"]
+    a = _run(BASE + longer, capsys)
+    b = _run(args + longer, capsys)
+    assert b["prefix_cache"]["hits"] == 1 and a["generated_ids"] == b["generated_ids"]
+
+
+def test_mtp_backend_serves_one_request_at_a_time():
+    """``serve --mtp``: requests are generated by MTP speculation (same tokens as plain greedy decoding), one at a
+    time; a second request while one runs is refused as busy."""
+    import asyncio
+    from flyingfish_b200.serve.backend import Busy, MtpBackend
+    model = Model.load("tiny-llama", Settings(capacity=256, max_batch=2, graph=False), device="cpu", seed=0)
+    ids = list(range(7, 27))
+    plain = generate_plain(model, ids, 10, ignore_eos=True, graph=False).ids
+    model.reset()
+
+    async def main():
+        be = MtpBackend(model, depth=2)
+        be.start()
+        try:
+            req, q = be.add_request(ids, 10, ignore_eos=True)
+            with pytest.raises(Busy):
+                be.add_request(ids, 4, ignore_eos=True)
+            toks = []
+            while True:
+                ev = await asyncio.wait_for(q.get(), timeout=60)
+                if ev.kind == "tokens":
+                    toks += ev.tokens
+                else:
+                    assert ev.kind == "done" and ev.finish_reason == "length"
+                    break
+            assert toks == plain
+            assert be.spec.stats.rounds > 0
+        finally:
+            be.shutdown()
+    asyncio.run(main())
+
+
+def test_engine_leader_and_follower_execute_the_same_calls():
+    """Tensor-parallel serving: rank 0 announces every engine call, the follower executes it on its own engine. Two
+    gloo ranks, each with its own CPU engine, must end with identical sequences."""
+    # process groups are per process, so the two ranks are child processes
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_driver_rank, args=(r, 29631, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=180) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+    by_rank = dict(got)
+    assert by_rank[0] == by_rank[1] and len(by_rank[0]) == 2 and all(len(o) == 6 for o in by_rank[0])
+
+
+def _driver_rank(rank, port, q):
+    import os
+    import torch.distributed as dist
+    from flyingfish_b200.engine.scheduler import Request, Scheduler
+    from flyingfish_b200.parallel.driver import EngineLeader, follow
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="2")
+    dist.init_process_group("gloo", rank=rank, world_size=2)
+    model = Model.load("tiny-llama", Settings(capacity=128, max_batch=4, graph=False), device="cpu", seed=0)
+    eng = model.engine
+    if rank == 0:
+        lead = EngineLeader(eng, dist.group.WORLD)
+        sch = Scheduler(lead)
+        reqs = [Request(prompt=list(range(3 + i, 20 + i)), max_tokens=6, ignore_eos=True) for i in range(2)]
+        for r in reqs:
+            sch.submit(r)
+        sch.run_until_idle()
+        lead.stop()
+        q.put((0, [r.output for r in reqs]))
+    else:
+        outs = {}
+        orig_free = eng.free_sequence
+
+        def free(seq_id):                 # keep what the follower generated before the leader frees the sequence
+            if seq_id in eng.seqs:
+                outs[seq_id] = list(eng.seqs[seq_id].output)
+            orig_free(seq_id)
+        eng.free_sequence = free
+        follow(eng, dist.group.WORLD)
+        q.put((1, [outs[k] for k in sorted(outs)]))
+    dist.destroy_process_group()
