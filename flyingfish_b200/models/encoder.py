@@ -37,6 +37,7 @@ def run_whole(model, seqs_ids: list[list[int]], want: str = "hidden") -> list[to
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
                 logit_rows=list(range(total)) if want == "logits" else [total - 1], is_decode=False)
         fb.upload()
+        fb.state_slots = [s.state_slot for s in seqs]      # models with per-sequence recurrent state address it by slot
         net = eng.model
         if want == "logits":
             out = net.forward(fb, eng.kv, return_logits=True)

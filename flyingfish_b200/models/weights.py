@@ -37,11 +37,21 @@ def random_tensor(seed: int, name: str, shape: tuple[int, ...], dtype: torch.dty
                   std: float = 0.02, ones: bool = False) -> torch.Tensor:
     if ones:
         return torch.ones(shape, dtype=dtype, device=device)
-    g = torch.Generator(device=device)
+    numel = 1
+    for d in shape:
+        numel *= d
+    # Small tensors are always drawn on the host and copied, so a model of a test-sized shape has the same weights on
+    # every device (a GPU run can be compared with the CPU oracle); only the tensors of the large benchmark shapes,
+    # which would take minutes to draw on the host, come from the device generator.
+    draw_dev = device if numel > CPU_DRAW_MAX else torch.device("cpu")
+    g = torch.Generator(device=draw_dev)
     g.manual_seed(tensor_seed(seed, name))
-    t = torch.empty(shape, dtype=torch.float32 if device.type == "cpu" else dtype, device=device)
+    t = torch.empty(shape, dtype=torch.float32 if draw_dev.type == "cpu" else dtype, device=draw_dev)
     t.normal_(0.0, std, generator=g)
-    return t.to(dtype)
+    return t.to(dtype).to(device)
+
+
+CPU_DRAW_MAX = 1 << 22      # elements; larger random tensors are drawn on their device
 
 
 TensorSource = Callable[[str, tuple[int, ...]], torch.Tensor]

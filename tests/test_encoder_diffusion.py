@@ -59,8 +59,8 @@ def test_diffusion_commits_every_position_by_confidence():
 
 @pytest.mark.gpu
 def test_bidirectional_gpu():
-    """(The decoder's random weights are drawn on the device they live on, so a CPU and a GPU model differ: the GPU
-    path is checked against itself; the bidirectional kernel against its oracle in tests/test_vision.py.)"""
+    """Structural properties of the bidirectional path on the GPU; the numbers are compared with the CPU oracle in
+    test_bidirectional_gpu_matches_cpu_oracle."""
     m = _load("tiny-embed", "cuda")
     long = [5, 6, 7, 8, 9, 10, 11] * 11
     a = run_whole(m, [long, [3, 4, 5]])
@@ -74,3 +74,15 @@ def test_bidirectional_gpu():
     assert len(out) == 8 and 2046 not in out
     from flyingfish_b200 import ops
     ops.check_status()
+
+
+@pytest.mark.gpu
+def test_bidirectional_gpu_matches_cpu_oracle():
+    from _oracle import assert_hidden_close
+    long = [5, 6, 7, 8, 9, 10, 11] * 11
+    assert_hidden_close(_load("tiny-embed", "cpu"), _load("tiny-embed", "cuda"), [long, [3, 4, 5]])
+    ec = embed_texts(_load("tiny-embed", "cpu"), [long, [3, 4, 5]])
+    eg = embed_texts(_load("tiny-embed", "cuda"), [long, [3, 4, 5]])
+    for a, b in zip(ec, eg):
+        assert torch.nn.functional.cosine_similarity(a.float().cpu(), b.float().cpu(), dim=0).item() > 0.995
+    assert_hidden_close(_load("tiny-diffusion", "cpu"), _load("tiny-diffusion", "cuda"), [[11, 12, 13, 2046, 2046, 2046]])

@@ -44,3 +44,11 @@ def test_gemma_gpu_window_consistency():
     from flyingfish_b200 import ops
     _check(_load("cuda"))
     ops.check_status()
+
+
+@pytest.mark.gpu
+def test_gemma_gpu_matches_cpu_oracle():
+    from _oracle import assert_hidden_close
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, 2000, (120,), generator=g).tolist()
+    assert_hidden_close(_load(), _load("cuda"), [prompt, [4, 5, 6, 7]])

@@ -55,9 +55,15 @@ def test_hybrid_gpu_runs_and_is_self_consistent():
     assert m.prefill(prompt + out[:3]) == out[3]
     from flyingfish_b200 import ops
     ops.check_status()
-    # (CPU and GPU models draw different random weights; the GDN kernels meet their oracles in tests/test_gdn.py)
     m.reset()
     a, b = [5, 9, 100, 33], [7, 7, 8, 250, 11, 12, 90]
     together = m.generate_batch([a, b], 5)
     m.reset()
     assert together[0] == generate_plain(m, a, 5, ignore_eos=True, graph=False).ids
+
+
+@pytest.mark.gpu
+def test_hybrid_gpu_matches_cpu_oracle():
+    from _oracle import assert_hidden_close
+    prompts = [[5, 9, 100, 33, 7, 8, 250, 11, 12, 90, 14], [3, 4, 5]]
+    assert_hidden_close(_load("cpu"), _load("cuda"), prompts)

@@ -52,10 +52,17 @@ def test_tp2_model_gpu(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     res = _launch(2, "cuda", "model", tmp_path, 29513)
-    # TP changes the summation order of the row-parallel projections, so compare against the
-    # single-GPU run with a tolerance on agreement: the first tokens must match exactly
+    # TP changes the summation order of the row-parallel projections: every token must equal the single-GPU
+    # run's, except that a near-tie in the logits may resolve the other way (checked against the logits)
+    from _oracle import assert_tokens_equal_up_to_ties
+    from flyingfish_b200.api import Model
+    from flyingfish_b200.config import Settings
     single = _single("cuda")
-    assert res["tokens"][0][:3] == single[0][:3]
+    m = Model.load("tiny-llama", Settings(capacity=256, max_batch=4, graph=False), device="cuda", seed=0)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (40, 9)]
+    for p, want, got in zip(prompts, single, res["tokens"]):
+        assert_tokens_equal_up_to_ties(m, p, want, got)
     assert res["stats"]["gemm_ar"] > 0
 
 
@@ -98,4 +105,6 @@ def test_tp2_sequence_parallel_fused_prefill(tmp_path):
     g = torch.Generator().manual_seed(8)
     prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (300, 150)]
     single = m.generate_batch(prompts, 6)
-    assert res["tokens"][0][:2] == single[0][:2] and res["tokens"][1][:2] == single[1][:2]
+    from _oracle import assert_tokens_equal_up_to_ties
+    for p, want, got in zip(prompts, single, res["tokens"]):
+        assert_tokens_equal_up_to_ties(m, p, want, got)
