@@ -150,6 +150,15 @@ def deepseek_v3_mini() -> ModelSpec:
                     n_groups=4, topk_groups=2, routed_scaling=2.5, first_dense_layers=1, dense_ffn=1024))
 
 
+def deepseek_v3_fp8_mini() -> ModelSpec:
+    """:func:`deepseek_v3_mini` with the published quantisation of DeepSeek-V3: every projection and expert as E4M3
+    codes with 128x128 block scales (activations quantised 1x128 inside the linears), plus one MTP module."""
+    s = deepseek_v3_mini()
+    s.name, s.layers, s.linear_format, s.mtp_layers = "deepseek-v3-fp8-mini", 3, "fp8_block", 1
+    s.moe.expert_format = "fp8_block"
+    return s
+
+
 def qwen3_moe_235b() -> ModelSpec:
     return ModelSpec(
         name="qwen3-moe-235b-shape", arch="qwen3_moe", layers=94, hidden=4096, heads=64, kv_heads=4, head_dim=128,
@@ -219,6 +228,7 @@ def tiny_gemma() -> ModelSpec:
 NAMED_SHAPES = {
     "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
+    "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }
 

@@ -45,7 +45,13 @@ def build_deepseek_weights(spec: ModelSpec, source, device, tp: TPInfo | None = 
     stub = copy.copy(spec)
     stub.heads, stub.kv_heads, stub.head_dim = 1, 1, 16
     stub.qk_norm = False
-    w = build_decoder_weights(stub, source_with_stub_attention(source, device), device, tp, ep)
+    fp8 = spec.linear_format == "fp8_block"
+    fp8_experts = spec.moe is not None and spec.moe.expert_format == "fp8_block"
+    if fp8 != fp8_experts and spec.moe is not None:
+        raise ValueError("FP8 DeepSeek-style checkpoints quantise the linears and the experts together")
+    from .weights import pack_ffn_fp8
+    w = build_decoder_weights(stub, source_with_stub_attention(source, device), device, tp, ep, fuse_swiglu=not fp8,
+                              layer_hook=pack_ffn_fp8 if fp8 else None)
     w.spec = spec
     h = spec.hidden
     qk = a.qk_nope_dim + a.qk_rope_dim
@@ -66,7 +72,14 @@ def build_deepseek_weights(spec: ModelSpec, source, device, tp: TPInfo | None = 
         w_uk = kv_b[:, : a.qk_nope_dim]                         # [heads, nope, kv_lora]
         w_uv = kv_b[:, a.qk_nope_dim:].contiguous()             # [heads, v, kv_lora]
         wo = source(p + "o_proj.weight", (h, heads * a.v_head_dim))
-        lw.extra["mla"] = MlaWeights(q_a, q_a_ln, q_b, kv_a, kv_a_ln, w_uk.transpose(1, 2).contiguous(), w_uv, wo)
+        w_uk_t = w_uk.transpose(1, 2).contiguous()
+        if fp8:
+            # the projections stay in the checkpoint's E4M3 block format; the two absorbed factors of kv_b are small
+            # and are applied per head in BF16
+            from ..ops.quant_ops import Fp8Weight
+            q_a = Fp8Weight.from_dense(q_a) if q_a is not None else None
+            q_b, kv_a, wo = Fp8Weight.from_dense(q_b), Fp8Weight.from_dense(kv_a), Fp8Weight.from_dense(wo)
+        lw.extra["mla"] = MlaWeights(q_a, q_a_ln, q_b, kv_a, kv_a_ln, w_uk_t, w_uv, wo)
         lw.wo = wo
     return w
 

@@ -35,6 +35,10 @@ def moe_ffn(model, layer: int, n: torch.Tensor) -> torch.Tensor:
         fp4 = lw.extra.get("experts_fp4")
         if provider is not None:
             routed = provider.forward(layer, n, weights, ids)
+        elif not isinstance(lw.experts_gu, torch.Tensor):
+            # FP8-resident experts: grouped W8A8 GEMMs over the dispatched rows
+            from ..ops import quant_ops
+            routed = quant_ops.experts_forward_fp8(n, weights, ids, lw.experts_gu, lw.experts_down)
         elif (fp4 is not None and n.is_cuda
               and n.shape[0] * moe.top_k <= moe_cuda_mod().FP4_DECODE_MAX_ROWS * fp4[0].experts):
             # decode-sized call: packed NVFP4 experts expanded inside the grouped GEMM (a quarter of the bytes)

@@ -109,6 +109,14 @@ class ModelWeights:
             nonlocal total
             if isinstance(t, torch.Tensor):
                 total += t.numel() * t.element_size()
+            elif hasattr(t, "nbytes") and callable(t.nbytes):      # FP8-resident weights
+                total += t.nbytes()
+            elif isinstance(t, dict):
+                for v in t.values():
+                    add(v)
+            elif hasattr(t, "__dataclass_fields__"):
+                for v in vars(t).values():
+                    add(v)
         add(self.embed); add(self.final_norm); add(self.lm_head)
         for l in self.layers:
             for v in vars(l).values():
@@ -122,9 +130,28 @@ def shard_range(n: int, rank: int, size: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
+def pack_ffn_fp8(lw: "LayerWeights") -> None:
+    """Re-encode a layer's feed-forward matrices as FP8-resident weights (E4M3 codes + 128x128 block scales): the
+    dense gate/up and down projections, the shared expert, and the routed experts (gate/up interleaved per 64 rows,
+    the layout the grouped kernel's SwiGLU epilogue reads). Done layer by layer while a model is assembled, so only
+    one layer ever exists in BF16."""
+    from ..ops.quant_ops import Fp8Experts, Fp8Weight
+    if isinstance(lw.wgu, torch.Tensor):
+        assert not lw.wgu_interleaved, "FP8 dense FFN weights keep the [gate | up] row order of the checkpoint"
+        lw.wgu = Fp8Weight.from_dense(lw.wgu)
+        lw.wdown = Fp8Weight.from_dense(lw.wdown)
+    if isinstance(lw.shared_gu, torch.Tensor):
+        lw.shared_gu = Fp8Weight.from_dense(lw.shared_gu)
+        lw.shared_down = Fp8Weight.from_dense(lw.shared_down)
+    if isinstance(lw.experts_gu, torch.Tensor):
+        lw.experts_gu = Fp8Experts.from_dense(lw.experts_gu, interleave=True)
+        lw.experts_down = Fp8Experts.from_dense(lw.experts_down)
+
+
 def build_decoder_weights(spec: ModelSpec, source: TensorSource, device: torch.device, tp: TPInfo | None = None,
-                          ep: TPInfo | None = None, fuse_swiglu: bool = True) -> ModelWeights:
-    """Assemble fused / sharded weights for a GQA decoder (dense or MoE FFN)."""
+                          ep: TPInfo | None = None, fuse_swiglu: bool = True, layer_hook=None) -> ModelWeights:
+    """Assemble fused / sharded weights for a GQA decoder (dense or MoE FFN). ``layer_hook(layer_weights)`` runs on
+    every finished layer (format conversion that should not wait for the whole model to exist)."""
     tp = tp or TPInfo()
     ep = ep or TPInfo()
     h, d = spec.hidden, spec.head_dim
@@ -187,6 +214,8 @@ def build_decoder_weights(spec: ModelSpec, source: TensorSource, device: torch.d
                 lw.shared_gu = torch.cat([source(q + "gate_proj.weight", (sf, h))[s0:s1],
                                           source(q + "up_proj.weight", (sf, h))[s0:s1]], 0).contiguous()
                 lw.shared_down = source(q + "down_proj.weight", (h, sf))[:, s0:s1].contiguous()
+        if layer_hook is not None:
+            layer_hook(lw)
         layers.append(lw)
     embed = source("model.embed_tokens.weight", (spec.vocab, h))
     final_norm = source("model.norm.weight", (h,))

@@ -112,7 +112,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
 
     CUDA path: tcgen05 kernels -- the weight-streaming decode kernel of ``csrc/gemm_skinny.cu`` (tokens on
     the UMMA M side, cluster split-K or stream-K) for M <= 128, the persistent 128x256x64 kernel of
-    ``csrc/gemm_bf16.cu`` otherwise."""
+    ``csrc/gemm_bf16.cu`` otherwise. ``w`` may be an FP8-resident weight (``quant_ops.Fp8Weight``): the block-scaled
+    W8A8 GEMM of ``csrc/gemm_fp8.cu`` (CPU: its oracle) runs instead."""
+    if not isinstance(w, torch.Tensor):
+        from . import quant_ops
+        y = quant_ops.linear_fp8(x, w.codes, w.scale)
+        if out_dtype is not None and y.dtype != out_dtype:
+            y = y.to(out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
     if not _is_cuda(x):
         y = ref.linear(x, w, out_dtype)
         if out is not None:

@@ -53,16 +53,123 @@ def linear_fp8(x: torch.Tensor, w_codes: torch.Tensor, w_scale: torch.Tensor) ->
     return y
 
 
-def grouped_gemm_fp8(xs_codes, xs_scale, w_codes, w_scale, seg_off, counts, capacity: int, epi: int) -> torch.Tensor:
+def grouped_gemm_fp8(xs_codes, xs_scale, w_codes, w_scale, seg_off, counts, capacity: int, epi: int,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
     """Grouped W8A8 GEMM over 16-row padded expert segments (see moe_cuda.dispatch_local)."""
     el, nw, k = w_codes.shape
     n_out = nw // 2 if epi == 1 else nw
-    y = torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs_codes.device)
+    y = out if out is not None else torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs_codes.device)
     rc = kernels().ff_gemm_fp8(ptr(xs_codes), ptr(xs_scale), ptr(w_codes), ptr(w_scale), ptr(y), ptr(seg_off), ptr(counts),
                                el, capacity, nw, k, n_out, epi, 1, None, None, ptr(status_tensor(y.device)), stream_ptr())
     check(rc, "ff_gemm_fp8(grouped)")
     _count()
     return y
+
+
+# ------------------------------------------------------------------------------------------
+# FP8-resident weights: what a model holds when ``linear_format`` / ``expert_format`` is fp8_block
+# ------------------------------------------------------------------------------------------
+class Fp8Weight:
+    """[N, K] linear weight kept as E4M3 codes + one FP32 scale per 128x128 block (the published DeepSeek-V3 layout,
+    the reference's ``LinearWeightRef::Fp8Block``, src/backend/cuda/linear.rs). ``ops.linear`` accepts it in place
+    of a BF16 matrix and runs the W8A8 block-scaled GEMM."""
+
+    def __init__(self, codes: torch.Tensor, scale: torch.Tensor):
+        assert codes.dtype == torch.uint8 and codes.dim() == 2 and scale.dtype == torch.float32
+        self.codes, self.scale = codes.contiguous(), scale.contiguous()
+
+    @classmethod
+    def from_dense(cls, w: torch.Tensor) -> "Fp8Weight":
+        q, s = qref.quantize_fp8_block_weight(w)
+        return cls(q, s)
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return tuple(self.codes.shape)
+
+    @property
+    def device(self) -> torch.device:
+        return self.codes.device
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scale.numel() * 4
+
+    def dense(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        return dequant_fp8_block(self.codes, self.scale).to(dtype)
+
+    def stride(self, dim: int) -> int:
+        return self.codes.stride(dim)
+
+
+class Fp8Experts:
+    """Stacked expert matrices [E, N, K] as E4M3 codes with [E, N/128, K/128] FP32 block scales. ``interleaved``:
+    gate/up rows alternate in groups of 64 (what the grouped kernel's SwiGLU epilogue expects)."""
+
+    def __init__(self, codes: torch.Tensor, scale: torch.Tensor, interleaved: bool = False):
+        self.codes, self.scale, self.interleaved = codes.contiguous(), scale.contiguous(), interleaved
+
+    @classmethod
+    def from_dense(cls, w: torch.Tensor, interleave: bool = False) -> "Fp8Experts":
+        if interleave:
+            e, n2, k = w.shape
+            f = n2 // 2
+            w = torch.stack([w[:, :f].reshape(e, f // 64, 64, k), w[:, f:].reshape(e, f // 64, 64, k)], dim=2).reshape(e, n2, k)
+        qs = [qref.quantize_fp8_block_weight(w[i]) for i in range(w.shape[0])]
+        return cls(torch.stack([q for q, _ in qs]), torch.stack([s for _, s in qs]), interleave)
+
+    @property
+    def shape(self) -> tuple[int, int, int]:
+        return tuple(self.codes.shape)
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scale.numel() * 4
+
+    def expert(self, i: int) -> Fp8Weight:
+        return Fp8Weight(self.codes[i], self.scale[i])
+
+
+def _deinterleave_cols(gu: torch.Tensor) -> torch.Tensor:
+    """[rows, 2f] with gate/up alternating per 64 columns -> [gate | up]."""
+    m, n = gu.shape
+    g = gu.view(m, n // 128, 2, 64)
+    return torch.cat([g[:, :, 0].reshape(m, n // 2), g[:, :, 1].reshape(m, n // 2)], dim=1)
+
+
+def experts_forward_fp8(x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor, gate_up: Fp8Experts, down: Fp8Experts,
+                        e_lo: int = 0, n_experts_total: int | None = None) -> torch.Tensor:
+    """Routed experts with FP8-resident weights. CUDA: dispatch -> 1x128 activation quantisation -> grouped W8A8
+    GEMM with SwiGLU -> quantisation -> grouped W8A8 down GEMM -> combine in ascending expert id. CPU: the same
+    program with the oracle linears, expert by expert."""
+    rows, hidden = x.shape
+    el = gate_up.shape[0]
+    total = n_experts_total if n_experts_total is not None else el
+    if not x.is_cuda:
+        from . import ref
+        acc = torch.zeros(rows, ids.shape[1], hidden, dtype=torch.float32)
+        for le in range(el):
+            r, c = torch.nonzero(ids == e_lo + le, as_tuple=True)
+            if r.numel() == 0:
+                continue
+            gu = qref.fp8_block_linear(x[r], gate_up.codes[le], gate_up.scale[le])
+            if gate_up.interleaved:
+                gu = _deinterleave_cols(gu)
+            h = ref.silu_mul(gu, 0)
+            y = qref.fp8_block_linear(h, down.codes[le], down.scale[le])
+            acc[r, c] = y.to(torch.float32) * weights[r, c, None]
+        order = torch.argsort(ids.long(), dim=-1, stable=True)
+        ordered = torch.gather(acc, 1, order[:, :, None].expand_as(acc))
+        out = torch.zeros(rows, hidden, dtype=torch.float32)
+        for j in range(ids.shape[1]):
+            out = out + ordered[:, j]
+        return out.to(x.dtype)
+    from . import moe_cuda
+    _require(gate_up.interleaved, "experts_forward_fp8: the gate/up experts must be interleaved per 64 rows")
+    xs, pos, seg_off, counts, cap = moe_cuda.dispatch_local(x.contiguous(), ids.contiguous(), total, e_lo, e_lo + el)
+    xq, xsc = quant_fp8_act(xs)
+    h = grouped_gemm_fp8(xq, xsc, gate_up.codes, gate_up.scale, seg_off, counts, cap, epi=1)
+    hq, hsc = quant_fp8_act(h)
+    y = grouped_gemm_fp8(hq, hsc, down.codes, down.scale, seg_off, counts, cap, epi=0)
+    return moe_cuda.combine(y, pos, ids, weights.contiguous(), rows, hidden)
 
 
 def dequant_fp8_block(codes: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:

@@ -158,7 +158,8 @@ class TPComm:
         if self.size == 1:
             return ops.linear(x, w)
         m, n = x.shape[0], w.shape[0]
-        if self.fused and x.is_cuda and m <= ops.SKINNY_MAX_M and n % 8 == 0 and m * n * 2 <= self.arena.slot_bytes:
+        if self.fused and x.is_cuda and isinstance(w, torch.Tensor) and m <= ops.SKINNY_MAX_M and n % 8 == 0 \
+                and m * n * 2 <= self.arena.slot_bytes:
             lib = oplib.kernels()
             k = x.shape[1]
             sb, cb = c_longlong(0), c_longlong(0)

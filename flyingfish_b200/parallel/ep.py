@@ -108,6 +108,17 @@ class EPComm:
         """Grouped gate/up (+SwiGLU) and down GEMMs of this rank's experts over the received rows."""
         from ..ops import moe_cuda
         lib = oplib.kernels()
+        if not isinstance(lw.experts_gu, torch.Tensor):
+            # FP8-resident experts: the received BF16 rows are quantised 1x128 on arrival and both grouped GEMMs
+            # run W8A8; the down projection writes into the symmetric output buffer the peers read from
+            from ..ops import quant_ops
+            xq, xs = quant_ops.quant_fp8_act(self.recv_x)
+            h = quant_ops.grouped_gemm_fp8(xq, xs, lw.experts_gu.codes, lw.experts_gu.scale, self._seg_off, self._counts,
+                                           self.capacity, epi=1)
+            hq, hs = quant_ops.quant_fp8_act(h)
+            quant_ops.grouped_gemm_fp8(hq, hs, lw.experts_down.codes, lw.experts_down.scale, self._seg_off, self._counts,
+                                       self.capacity, epi=0, out=self.out_y)
+            return
         wgu = moe_cuda._gu_interleaved(lw.experts_gu)
         h = moe_cuda.grouped_gemm(self.recv_x, wgu, self._seg_off, self._counts, self.capacity, epi=1,
                                   rows_per_expert=self._rows_per_expert)
@@ -161,8 +172,15 @@ class EPComm:
             r, c = torch.nonzero(aid == e0 + le, as_tuple=True)
             if r.numel() == 0:
                 continue
-            y = ref.expert_ffn(ax[r], lw.experts_gu[le], lw.experts_down[le], mode) if not x.is_cuda else \
-                ops.linear(ops.silu_mul(ops.linear(ax[r].contiguous(), lw.experts_gu[le]), mode), lw.experts_down[le])
+            if not isinstance(lw.experts_gu, torch.Tensor):
+                from ..ops import quant_ops
+                gu = ops.linear(ax[r].contiguous(), lw.experts_gu.expert(le))
+                if lw.experts_gu.interleaved:
+                    gu = quant_ops._deinterleave_cols(gu)
+                y = ops.linear(ops.silu_mul(gu, mode), lw.experts_down.expert(le))
+            else:
+                y = ref.expert_ffn(ax[r], lw.experts_gu[le], lw.experts_down[le], mode) if not x.is_cuda else \
+                    ops.linear(ops.silu_mul(ops.linear(ax[r].contiguous(), lw.experts_gu[le]), mode), lw.experts_down[le])
             contrib[r, c] = y.to(torch.float32) * aw[r, c, None]
         dist.all_reduce(contrib, group=self.group)
         start = sum(counts[: self.rank])

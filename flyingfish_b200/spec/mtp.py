@@ -67,7 +67,12 @@ def build_mtp_weights(target_w: ModelWeights, source, device) -> MtpWeights:
             return target_w.embed if name == "model.embed_tokens.weight" else target_w.lm_head
         return t
 
-    layer = build_decoder_weights(one, src, device, target_w.tp)
+    if spec.mla is not None:
+        # DeepSeek-style targets: the module is a full MLA + MoE layer in the target's weight formats
+        from ..models.deepseek import build_deepseek_weights
+        layer = build_deepseek_weights(one, src, device, target_w.tp)
+    else:
+        layer = build_decoder_weights(one, src, device, target_w.tp)
     layer.embed, layer.lm_head, layer.vocab_shard = target_w.embed, target_w.lm_head, target_w.vocab_shard
     h = spec.hidden
     p = f"model.layers.{L}."
@@ -88,10 +93,16 @@ class MtpSpeculator:
         if weights is None:
             weights = build_mtp_weights(tw, synthetic_source(tw.spec, seed, dev, DTYPES[tw.spec.dtype]), dev)
         self.w = weights
-        self.net = DecoderModel(weights.layer, comm=te.model.comm)
         spec = weights.layer.spec
-        hkv = max(1, spec.kv_heads // tw.tp.size)
-        self.kv = PagedKVCache(1, hkv, spec.head_dim, te.max_blocks + 1, te.settings.kv_block, tw.embed.dtype, dev)
+        if spec.mla is not None:
+            from ..models.deepseek import DeepseekModel
+            self.net = DeepseekModel(weights.layer, comm=te.model.comm)
+            self.kv = PagedKVCache(1, 1, spec.mla.kv_lora_rank + spec.mla.qk_rope_dim, te.max_blocks + 1,
+                                   te.settings.kv_block, tw.embed.dtype, dev, v_head_dim=0)
+        else:
+            self.net = DecoderModel(weights.layer, comm=te.model.comm)
+            hkv = max(1, spec.kv_heads // tw.tp.size)
+            self.kv = PagedKVCache(1, hkv, spec.head_dim, te.max_blocks + 1, te.settings.kv_block, tw.embed.dtype, dev)
         self.fb = ForwardBatch(BatchLayout(1, max(te.max_prefill_rows, 8), te.max_blocks), dev)
         self.stats = SpecStats()
         self.fault = Fault.NONE

@@ -68,15 +68,22 @@ def bench_gemm(args) -> dict:
     x = (torch.randn(m, k, device=dev) * 1.0).to(torch.bfloat16)
     w = (torch.randn(n, k, device=dev) * 0.05).to(torch.bfloat16)
     out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    byts = (m * k + n * k + m * n) * 2
     if args.torch:
         fn = lambda: torch.matmul(x, w.t(), out=out)
+    elif getattr(args, "fp8", False):
+        # block-scaled W8A8 linear: activation quantisation (1x128) + the tcgen05 FP8 GEMM, weights E4M3-resident
+        from ..ops import quant_ops
+        wq = quant_ops.Fp8Weight.from_dense(w)
+        del w
+        fn = lambda: ops.linear(x, wq, out=out)
+        byts = m * k * 2 + wq.nbytes() + m * n * 2
     else:
         fn = lambda: ops.linear(x, w, out=out)
-    byts = (m * k + n * k + m * n) * 2
     r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
     pk = peaks()
     t = r["us_median"] * 1e-6
-    r.update(op="gemm_torch" if args.torch else "gemm", m=m, n=n, k=k, gbs=byts / t / 1e9,
+    r.update(op="gemm_torch" if args.torch else "gemm_fp8" if getattr(args, "fp8", False) else "gemm", m=m, n=n, k=k, gbs=byts / t / 1e9,
              tflops=2.0 * m * n * k / t / 1e12)
     r["frac_hbm"] = r["gbs"] / pk["hbm_gbs"]
     r["frac_tensor"] = r["tflops"] / pk["bf16_tflops"]
@@ -172,6 +179,7 @@ def main(argv=None) -> None:
             p.add_argument("--n", type=int, default=4096)
             p.add_argument("--k", type=int, default=4096)
             p.add_argument("--torch", action="store_true", help="time torch.matmul (cuBLAS) instead, as the baseline")
+            p.add_argument("--fp8", action="store_true", help="FP8-resident weight (E4M3, 128x128 scales), W8A8 kernel")
         elif name == "moe":
             p.add_argument("--rows", type=int, default=128)
             p.add_argument("--experts", type=int, default=128)

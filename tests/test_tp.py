@@ -12,12 +12,12 @@ import torch
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _launch(nproc, device, mode, tmp_path, port):
+def _launch(nproc, device, mode, tmp_path, port, model=None):
     out = tmp_path / f"res_{device}_{mode}.json"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "tp_worker.py"),
-           "--device", device, "--out", str(out), "--mode", mode]
+           "--device", device, "--out", str(out), "--mode", mode] + (["--model", model] if model else [])
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     return json.loads(out.read_text())
@@ -66,10 +66,10 @@ def test_tp2_model_gpu(tmp_path):
     assert res["stats"]["gemm_ar"] > 0
 
 
-def _single_moe(device, prompts):
+def _single_moe(device, prompts, model="qwen3-moe-tiny"):
     from flyingfish_b200.api import Model
     from flyingfish_b200.config import Settings
-    m = Model.load("qwen3-moe-tiny", Settings(capacity=256, max_batch=4, graph=False), device=device, seed=0)
+    m = Model.load(model, Settings(capacity=256, max_batch=4, graph=False), device=device, seed=0)
     return m.generate_batch(prompts, 8)
 
 
@@ -108,3 +108,27 @@ def test_tp2_sequence_parallel_fused_prefill(tmp_path):
     from _oracle import assert_tokens_equal_up_to_ties
     for p, want, got in zip(prompts, single, res["tokens"]):
         assert_tokens_equal_up_to_ties(m, p, want, got)
+
+
+def test_ep2_fp8_experts_gloo_matches_single_rank(tmp_path):
+    """DeepSeek-style model with FP8-resident projections and experts (E4M3 codes, 128x128 block scales, activations
+    quantised 1x128) under expert parallelism: two ranks must produce what one rank holding all experts produces."""
+    res = _launch(2, "cpu", "ep", tmp_path, 29518, model="deepseek-v3-fp8-mini")
+    for r in res["per_rank"]:
+        assert r["tokens"] == _single_moe("cpu", r["prompts"], "deepseek-v3-fp8-mini")
+
+
+@pytest.mark.gpu
+def test_ep2_fp8_experts_gpu(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from _oracle import assert_tokens_equal_up_to_ties
+    from flyingfish_b200.api import Model
+    from flyingfish_b200.config import Settings
+    res = _launch(2, "cuda", "ep", tmp_path, 29519, model="deepseek-v3-fp8-mini")
+    assert res["stats"]["fused_calls"] > 0
+    m = Model.load("deepseek-v3-fp8-mini", Settings(capacity=256, max_batch=4, graph=False), device="cuda", seed=0)
+    for r in res["per_rank"]:
+        single = _single_moe("cuda", r["prompts"], "deepseek-v3-fp8-mini")
+        for p, want, got in zip(r["prompts"], single, r["tokens"]):
+            assert_tokens_equal_up_to_ties(m, p, want, got)

@@ -16,6 +16,7 @@ def main():
     ap.add_argument("--device", default="cpu")
     ap.add_argument("--out", required=True)
     ap.add_argument("--mode", default="model")
+    ap.add_argument("--model", default="qwen3-moe-tiny")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -107,9 +108,9 @@ def main():
     elif args.mode == "ep":
         from flyingfish_b200.parallel.ep import EPComm
         from flyingfish_b200.config import named_shape
-        spec = named_shape("qwen3-moe-tiny")
+        spec = named_shape(args.model)
         ep = EPComm(dist.group.WORLD, device, spec.moe.num_experts, spec.hidden, max_rows=128, top_k=spec.moe.top_k)
-        m = Model.load("qwen3-moe-tiny", Settings(capacity=256, max_batch=4, graph=False), device=device, seed=0, ep=ep)
+        m = Model.load(args.model, Settings(capacity=256, max_batch=4, graph=False), device=device, seed=0, ep=ep)
         g = torch.Generator().manual_seed(100 + rank)       # every rank serves its own sequences
         prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (33, 12)]
         toks = m.generate_batch(prompts, 8)
