@@ -34,7 +34,15 @@ def _single(device):
 
 def test_tp2_gloo_matches_single_rank(tmp_path):
     res = _launch(2, "cpu", "model", tmp_path, 29511)
-    assert res["tokens"] == _single("cpu")
+    # splitting K over two ranks changes the order of the FP32 sums: equal up to logit near-ties
+    from _oracle import assert_tokens_equal_up_to_ties
+    from flyingfish_b200.api import Model
+    from flyingfish_b200.config import Settings
+    m = Model.load("tiny-llama", Settings(capacity=256, max_batch=4, graph=False), device="cpu", seed=0)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (40, 9)]
+    for p, want, got in zip(prompts, _single("cpu"), res["tokens"]):
+        assert_tokens_equal_up_to_ties(m, p, want, got)
 
 
 @pytest.mark.gpu
