@@ -179,7 +179,49 @@ class Engine:
             raise
         return [first[s.seq_id] for s in seqs if s.seq_id in first]
 
+    def prefill_some(self, seqs: list[Sequence], max_rows: int) -> list[Sequence]:
+        """ONE packed prefill chunk of at most ``max_rows`` prompt rows over ``seqs`` (in order, each contributing as
+        many of its remaining prompt tokens as fit). Returns the sequences whose prompt was completed by this chunk;
+        their first generated token is in ``pending`` / ``output``. This is the unit the scheduler interleaves with
+        decode steps, so that a long prompt does not stall the sequences that are already generating."""
+        self._check()
+        rows_left = min(max_rows, self.max_prefill_rows)
+        part: list[tuple[Sequence, int]] = []
+        for s in seqs:
+            if rows_left <= 0 or len(part) >= self.max_batch:
+                break
+            rem = len(s.prompt) - s.prefilled
+            if rem <= 0:
+                continue
+            take = min(rem, rows_left)
+            part.append((s, take))
+            rows_left -= take
+        if not part:
+            return []
+        try:
+            toks = self._prefill_chunk(part)
+        except OutOfBlocks:
+            raise
+        except Exception:
+            self.poisoned = True
+            raise
+        done = []
+        for (s, _), t in zip(part, toks):
+            if s.prefilled == len(s.prompt):
+                s.pending = t
+                s.output.append(t)
+                done.append(s)
+        return done
+
+    def _need_blocks(self, items: list[tuple[int, int]]) -> None:
+        """Refuse a step before it reserves anything when the (sequence, new tokens) pairs do not all fit: a step
+        either reserves for every sequence or for none."""
+        need = sum(self.kv.blocks_needed(sid, n) for sid, n in items)
+        if need > self.kv.alloc.free_blocks:
+            raise OutOfBlocks(f"step needs {need} KV blocks, {self.kv.alloc.free_blocks} free")
+
     def _prefill_chunk(self, part: list[tuple[Sequence, int]]) -> list[int]:
+        self._need_blocks([(s.seq_id, take) for s, take in part])
         fb = self.prefill_batch
         ids, positions, slots, q_lens, ctx_lens, block_rows, logit_rows = [], [], [], [], [], [], []
         row = 0
@@ -234,6 +276,7 @@ class Engine:
 
     # -- decode ------------------------------------------------------------------------------
     def _fill_decode(self, fb: ForwardBatch, seqs: list[Sequence], bucket: int) -> None:
+        self._need_blocks([(s.seq_id, 1) for s in seqs])
         ids, positions, slots, q_lens, ctx_lens, block_rows = [], [], [], [], [], []
         for s in seqs:
             kvs = self.kv.seqs[s.seq_id]
@@ -332,6 +375,8 @@ class Engine:
             self.stats["decode_steps"] += 1
             self.stats["decode_tokens"] += n
             return toks
+        except OutOfBlocks:
+            raise                      # nothing was reserved or launched: the caller may preempt and retry
         except Exception:
             self.poisoned = True
             raise

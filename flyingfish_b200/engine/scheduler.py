@@ -2,10 +2,12 @@
 
 The reference serves one request at a time through a single admission slot
 (src/serve/mod.rs:41-59; busy -> HTTP 409). A 180 GB part with a paged cache can hold hundreds of
-sequences, so this build schedules many: every iteration admits waiting requests while KV blocks
-and batch slots are free, runs one packed prefill chunk for sequences that still have prompt
-tokens to process, then one decode step for every running sequence. Requests can be aborted at
-any iteration (client disconnect), which frees their blocks immediately.
+sequences, so this build schedules many. Every iteration has a token budget shared by the decode
+batch and ONE packed prefill chunk: waiting requests are admitted while KV blocks and batch slots
+are free, every sequence that is already generating decodes one token, and the rest of the budget
+goes to prompt rows of the sequences still prefilling (oldest first). A long prompt is therefore
+spread over several iterations and never stalls the running streams for more than one chunk.
+Requests can be aborted at any iteration (client disconnect), which frees their blocks at once.
 
 The scheduler is synchronous and engine-agnostic (it only needs ``add_sequence / prefill /
 decode / free_sequence``), so its policy is unit-tested on CPU with a scripted fake engine.
@@ -47,10 +49,13 @@ class Request:
 
 
 class Scheduler:
-    def __init__(self, engine, max_running: int | None = None, prefill_chunk: int | None = None):
+    def __init__(self, engine, max_running: int | None = None, prefill_chunk: int | None = None,
+                 token_budget: int | None = None):
         self.engine = engine
         self.max_running = max_running or engine.max_batch
         self.prefill_chunk = prefill_chunk
+        # rows one iteration may process: decode rows first, the remainder is the prefill chunk
+        self.token_budget = token_budget or prefill_chunk or getattr(engine, "max_prefill_rows", 8192)
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self.stats = {"admitted": 0, "finished": 0, "aborted": 0, "iterations": 0, "preempted": 0}
@@ -138,37 +143,46 @@ class Scheduler:
             req.on_finish(req)
         return True
 
+    def _preempt_youngest(self) -> None:
+        """Out of KV blocks: the youngest running request goes back to the queue (it will be recomputed from its
+        prompt plus what it already produced)."""
+        victim = self.running.pop()
+        self.engine.free_sequence(victim.seq.seq_id)
+        victim.state, victim.seq = "waiting", None
+        self.waiting.appendleft(victim)
+        self.stats["preempted"] += 1
+
     def step(self) -> int:
         """Run one scheduling iteration; returns the number of tokens produced."""
         self.stats["iterations"] += 1
         produced = 0
-        new = self._admit()
-        if new:
-            self.engine.prefill([r.seq for r in new], chunk=self.prefill_chunk)
-            for r in new:
-                self._emit(r, [r.seq.output[-1]])
-                produced += 1
-            self.running.extend(new)
-            self.running = [r for r in self.running if not self._maybe_finish(r)]
-            return produced
-        if self.running:
-            batch = self.running[: self.engine.max_batch]
+        self.running.extend(self._admit())
+        decoding = [r for r in self.running if r.seq.prefilled >= len(r.seq.prompt)][: self.engine.max_batch]
+        prefilling = [r for r in self.running if r.seq.prefilled < len(r.seq.prompt)]
+        # ---- decode step of every generating sequence ----
+        if decoding:
             try:
-                toks = self.engine.decode([r.seq for r in batch])
+                toks = self.engine.decode([r.seq for r in decoding])
             except OutOfBlocks:
-                # out of KV: preempt the youngest sequence (its request goes back to the queue and
-                # will be recomputed), then retry next iteration
-                victim = self.running.pop()
-                self.engine.free_sequence(victim.seq.seq_id)
-                self.engine.poisoned = False
-                victim.state, victim.seq = "waiting", None
-                self.waiting.appendleft(victim)
-                self.stats["preempted"] += 1
+                self._preempt_youngest()
                 return 0
-            for r, t in zip(batch, toks):
+            for r, t in zip(decoding, toks):
                 self._emit(r, [t])
                 produced += 1
-            self.running = [r for r in self.running if r.state == "running" and not (r in batch and self._maybe_finish(r))]
+        # ---- one prefill chunk with what is left of the budget ----
+        rows = self.token_budget - len(decoding)
+        if prefilling and rows > 0:
+            try:
+                done = self.engine.prefill_some([r.seq for r in prefilling], rows)
+            except OutOfBlocks:
+                self._preempt_youngest()
+                return produced
+            finished_ids = {s.seq_id for s in done}
+            for r in prefilling:
+                if r.seq.seq_id in finished_ids:
+                    self._emit(r, [r.seq.output[-1]])
+                    produced += 1
+        self.running = [r for r in self.running if r.state == "running" and not (r.output and self._maybe_finish(r))]
         return produced
 
     def run_until_idle(self, max_iters: int = 1_000_000) -> None:

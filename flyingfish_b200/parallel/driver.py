@@ -19,7 +19,7 @@ from typing import Any
 import torch.distributed as dist
 
 STOP = "__stop__"
-_FORWARDED = ("add_sequence", "free_sequence", "prefill", "decode", "reset", "capture")
+_FORWARDED = ("add_sequence", "free_sequence", "prefill", "prefill_some", "decode", "reset", "capture")
 
 
 def _bcast(group, obj: Any, src: int = 0) -> Any:

@@ -43,9 +43,10 @@ class Unavailable(RuntimeError):
 class Backend:
     """Thread-safe front of the engine thread."""
 
-    def __init__(self, engine, eos_ids: tuple[int, ...] = (), max_inflight: int | None = None):
+    def __init__(self, engine, eos_ids: tuple[int, ...] = (), max_inflight: int | None = None,
+                 token_budget: int | None = None):
         self.engine = engine
-        self.scheduler = Scheduler(engine)
+        self.scheduler = Scheduler(engine, token_budget=token_budget)
         self.eos_ids = eos_ids
         self.max_inflight = max_inflight or 4 * engine.max_batch
         self.state = "idle"            # idle | running | unavailable
