@@ -3,17 +3,22 @@ tier (CPU expert FFN for this token, promotion later) and the NVMe tier (direct-
 
 Per MoE layer call (the reference's decode executor, src/backend/cuda/engine_moe.rs:1404-1830):
 
-1. the routed ids / weights are read back to the host (one small D2H: the only host round trip,
-   skipped entirely when every expert is resident),
-2. ``Residency.dispatch`` splits the routes into slot hits, host misses and disk misses,
-3. hits run on the device: ids are remapped to slot numbers (misses become -1 and are skipped by
-   the dispatch kernels), then dispatch -> grouped GEMMs over the slot arena,
-4. misses run on the host worker pool with the host copy of the weights (disk-tier experts are
-   first read through the direct-IO ring); their outputs are uploaded behind the device outputs,
+1. on the device the routed ids are remapped to slot numbers through the layer's slot table (misses
+   become -1, the dispatch kernels skip them) and a fixed-size summary is built: number of misses,
+   bitmap of routed experts, the missed (position, expert) pairs compacted to the front; ONE small
+   device-to-host copy carries it,
+2. meanwhile the hits run on the device: dispatch -> grouped GEMMs over the slot arena (BF16 slots, or
+   packed NVFP4 slots expanded inside the GEMM),
+3. the host reads the summary and updates the residency scores in array form (``Residency.account``;
+   the CPU path of the tests still walks ``Residency.dispatch`` route by route),
+4. misses (if any) run on the host worker pool with the host copy of the weights (disk-tier experts
+   are first read through the direct-IO ring); their outputs are uploaded behind the device outputs,
 5. ONE combine sums every contribution of a row in ascending expert id.
 
 At token end ``finish_token`` returns the admissions; the provider copies those experts into their
-slots and updates the slot table (slot generations guard against stale tables).
+slots on a copy stream and records one event per layer, which the next token's call for that layer
+waits on (copies for late layers overlap the early layers' compute; the reference orders slot
+lifetimes with events the same way, src/experts/arena.rs:485-560).
 """
 from __future__ import annotations
 
@@ -28,12 +33,18 @@ from .runtime import EMPTY, Move, Residency, Route
 
 class ExpertStore:
     """Host-side home of one layer's expert weights: a pinned tensor for the host tier, optionally a
-    disk reader for experts that do not fit."""
+    disk reader for experts that do not fit. ``packed``: (gate/up, down) packed NVFP4 stacks on the host (gate/up
+    already interleaved for the SwiGLU epilogue) that are uploaded into slots instead of the BF16 matrices; the BF16
+    tensors then hold the dequantised (effective) weights the host FFN computes with."""
 
-    def __init__(self, gate_up: torch.Tensor, down: torch.Tensor, pin: bool = False, disk=None):
+    def __init__(self, gate_up: torch.Tensor, down: torch.Tensor, pin: bool = False, disk=None, packed=None):
         self.gate_up = gate_up.pin_memory() if pin and not gate_up.is_pinned() else gate_up     # [E, 2f, h]
         self.down = down.pin_memory() if pin and not down.is_pinned() else down                 # [E, h, f]
         self.disk = disk                                                                        # DiskExperts or None
+        self.packed = packed
+        if packed is not None and pin:
+            for st in packed:
+                st.codes, st.scales = st.codes.pin_memory(), st.scales.pin_memory()
 
     def weights(self, layer: int, expert: int) -> tuple[torch.Tensor, torch.Tensor]:
         if self.disk is not None and self.disk.on_disk(layer, expert):
@@ -51,38 +62,83 @@ class TieredExpertProvider:
         self.hidden, self.ffn, self.swiglu_mode = hidden, ffn, swiglu_mode
         self.res = Residency(geo, cap, adm, mode=mode, host_backed=True, disk_experts=disk_experts)
         dt = stores[0].gate_up.dtype
-        self.arena_gu = [torch.zeros(cap.slots_per_layer[l], 2 * ffn, hidden, dtype=dt, device=self.device)
-                         for l in range(geo.layers)]
-        self.arena_down = [torch.zeros(cap.slots_per_layer[l], hidden, ffn, dtype=dt, device=self.device)
-                           for l in range(geo.layers)]
+        self.fp4 = stores[0].packed is not None and self.device.type == "cuda"
+        if self.fp4:
+            from ..ops.moe_cuda import Nvfp4Experts
+            u8 = dict(dtype=torch.uint8, device=self.device)
+
+            def arena(n, rows, cols):
+                return Nvfp4Experts(torch.zeros(n, rows, cols // 2, **u8), torch.zeros(n, rows, cols // 16, **u8),
+                                    torch.ones(n, device=self.device))
+            self.arena_gu = [arena(cap.slots_per_layer[l], 2 * ffn, hidden) for l in range(geo.layers)]
+            self.arena_down = [arena(cap.slots_per_layer[l], hidden, ffn) for l in range(geo.layers)]
+        else:
+            self.arena_gu = [torch.zeros(cap.slots_per_layer[l], 2 * ffn, hidden, dtype=dt, device=self.device)
+                             for l in range(geo.layers)]
+            self.arena_down = [torch.zeros(cap.slots_per_layer[l], hidden, ffn, dtype=dt, device=self.device)
+                               for l in range(geo.layers)]
         self.table = [torch.full((geo.experts_per_layer,), EMPTY, dtype=torch.int32, device=self.device)
                       for _ in range(geo.layers)]
         self.pool = ExpertPool(threads) if dt == torch.bfloat16 else None
         self.layer_index: dict[int, int] = {}      # model layer number -> MoE layer ordinal
         self.copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
-        self.stats = {"cpu_rows": 0, "gpu_rows": 0, "h2d_expert_bytes": 0, "layers_all_hit": 0, "layer_calls": 0}
+        self.layer_event: list = [None] * geo.layers     # slot copies of a layer still in flight on the copy stream
+        self.summary_host: torch.Tensor | None = None    # pinned landing buffer of the per-layer summary
+        self.stats = {"cpu_rows": 0, "gpu_rows": 0, "h2d_expert_bytes": 0, "layers_all_hit": 0, "layer_calls": 0,
+                      "d2h_summary_bytes": 0}
         self.freq = [[0.0] * geo.experts_per_layer for _ in range(geo.layers)]
         self.collect_freq = False
 
     # -- slot maintenance ----------------------------------------------------------------------
     def apply_moves(self, moves: list[Move]) -> None:
+        if not moves:
+            return
+        cuda = self.device.type == "cuda"
+        if cuda:
+            # the copies may start once the compute queued so far (which still reads the old slot contents) is done
+            self.copy_stream.wait_stream(torch.cuda.current_stream(self.device))
+        touched = set()
         for m in moves:
-            wgu, wd = self.stores[m.layer].weights(m.layer, m.expert_in)
-            if self.device.type == "cuda":
-                from ..ops import moe_cuda
+            st = self.stores[m.layer]
+            if self.fp4:
+                pg, pd = st.packed
                 with torch.cuda.stream(self.copy_stream):
-                    g = wgu.to(self.device, non_blocking=True)
-                    self.arena_gu[m.layer][m.slot].copy_(moe_cuda.interleave64(g[None])[0])
-                    self.arena_down[m.layer][m.slot].copy_(wd.to(self.device, non_blocking=True))
+                    ag, ad = self.arena_gu[m.layer], self.arena_down[m.layer]
+                    ag.codes[m.slot].copy_(pg.codes[m.expert_in], non_blocking=True)
+                    ag.scales[m.slot].copy_(pg.scales[m.expert_in], non_blocking=True)
+                    ag.global_scale[m.slot: m.slot + 1].copy_(pg.global_scale[m.expert_in: m.expert_in + 1], non_blocking=True)
+                    ad.codes[m.slot].copy_(pd.codes[m.expert_in], non_blocking=True)
+                    ad.scales[m.slot].copy_(pd.scales[m.expert_in], non_blocking=True)
+                    ad.global_scale[m.slot: m.slot + 1].copy_(pd.global_scale[m.expert_in: m.expert_in + 1], non_blocking=True)
             else:
-                self.arena_gu[m.layer][m.slot].copy_(wgu)
-                self.arena_down[m.layer][m.slot].copy_(wd)
-            if m.expert_out != EMPTY:
-                self.table[m.layer][m.expert_out] = EMPTY
-            self.table[m.layer][m.expert_in] = m.slot
+                wgu, wd = st.weights(m.layer, m.expert_in)
+                if cuda:
+                    from ..ops import moe_cuda
+                    with torch.cuda.stream(self.copy_stream):
+                        g = wgu.to(self.device, non_blocking=True)
+                        self.arena_gu[m.layer][m.slot].copy_(moe_cuda.interleave64(g[None])[0])
+                        self.arena_down[m.layer][m.slot].copy_(wd.to(self.device, non_blocking=True))
+                else:
+                    self.arena_gu[m.layer][m.slot].copy_(wgu)
+                    self.arena_down[m.layer][m.slot].copy_(wd)
+            if cuda:
+                with torch.cuda.stream(self.copy_stream):     # the table entry changes together with the slot
+                    if m.expert_out != EMPTY:
+                        self.table[m.layer][m.expert_out] = EMPTY
+                    self.table[m.layer][m.expert_in] = m.slot
+            else:
+                if m.expert_out != EMPTY:
+                    self.table[m.layer][m.expert_out] = EMPTY
+                self.table[m.layer][m.expert_in] = m.slot
             self.stats["h2d_expert_bytes"] += self.geo.slot_bytes
-        if moves and self.copy_stream is not None:
-            torch.cuda.current_stream(self.device).wait_stream(self.copy_stream)
+            touched.add(m.layer)
+        if cuda:
+            # one event per touched layer (copies are queued in move order, so a layer's event also covers it when a
+            # later layer's copies follow): the next call for that layer waits on it, nobody else does
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+            for l in touched:
+                self.layer_event[l] = ev
 
     def begin_request(self, prefill_freq: list[list[float]] | None = None) -> None:
         f = prefill_freq if prefill_freq is not None else self.freq
@@ -100,6 +156,8 @@ class TieredExpertProvider:
         l = self.layer_index[model_layer]
         rows, k = ids.shape
         self.stats["layer_calls"] += 1
+        if self.device.type == "cuda":
+            return self._forward_cuda_vec(l, x, weights, ids)
         ids_h = ids.cpu()
         w_h = weights.cpu()
         if self.collect_freq:
@@ -162,6 +220,95 @@ class TieredExpertProvider:
             acc = acc + ordered[:, j]
         return acc.to(x.dtype)
 
+    def _forward_cuda_vec(self, l: int, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """Device-resolved form of a layer call: no per-route host objects, one small D2H (the summary) per call, a
+        second one (the activations of the missed rows) only when something missed."""
+        import numpy as np
+        from ..ops import moe_cuda
+        rows, k = ids.shape
+        E = self.geo.experts_per_layer
+        n_assign = rows * k
+        dev = self.device
+        cur = torch.cuda.current_stream(dev)
+        if self.layer_event[l] is not None:
+            cur.wait_event(self.layer_event[l])
+            self.layer_event[l] = None
+        flat = ids.reshape(-1).long()
+        slot_ids = self.table[l][flat].to(torch.int32).view(rows, k)              # misses -> -1
+        miss = slot_ids.reshape(-1) < 0
+        routed = torch.zeros(E, dtype=torch.int32, device=dev)
+        routed[flat] = 1
+        order = torch.argsort(miss.to(torch.int8), descending=True, stable=True)    # missed positions first, ascending
+        summary = torch.cat([miss.sum().reshape(1).to(torch.int32), routed, order.to(torch.int32),
+                             flat[order].to(torch.int32)])
+        need = 1 + E + 2 * n_assign
+        if self.summary_host is None or self.summary_host.numel() < need:
+            self.summary_host = torch.empty(max(need, 4096), dtype=torch.int32, pin_memory=True)
+        self.summary_host[:need].copy_(summary, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self.stats["d2h_summary_bytes"] += 4 * need
+        # hits on the device while the summary travels
+        n_slots = self.cap.slots_per_layer[l]
+        xs, pos, seg_off, counts, cap_rows = moe_cuda.dispatch_local(x.contiguous(), slot_ids.contiguous(), n_slots, 0, n_slots)
+        if self.fp4:
+            h = moe_cuda.grouped_gemm_nvfp4(xs, self.arena_gu[l], seg_off, counts, cap_rows, epi=1)
+            y = moe_cuda.grouped_gemm_nvfp4(h, self.arena_down[l], seg_off, counts, cap_rows, epi=0)
+        else:
+            h = moe_cuda.grouped_gemm(xs, self.arena_gu[l], seg_off, counts, cap_rows, epi=1)
+            y = moe_cuda.grouped_gemm(h, self.arena_down[l], seg_off, counts, cap_rows, epi=0)
+        ev.synchronize()
+        sh = self.summary_host.numpy()
+        n_miss = int(sh[0])
+        routed_e = np.nonzero(sh[1: 1 + E])[0]
+        miss_pos = sh[1 + E: 1 + E + n_miss].copy()
+        miss_exp = sh[1 + E + n_assign: 1 + E + n_assign + n_miss].copy()
+        if self.collect_freq:
+            f = self.freq[l]
+            for e in sh[1 + E + n_assign: 1 + E + 2 * n_assign].tolist():        # every assignment's expert
+                f[e] += 1.0
+        opened = False
+        if not self.res.in_token:          # prefill chunks: no decay / admission, plain accounting
+            self.res.in_token = True
+            self.res.routed[l].clear()
+            opened = True
+        self.res.account(l, routed_e, n_assign - n_miss, miss_exp)
+        if opened:
+            self.res.in_token = False
+        self.stats["cpu_rows"] += n_miss
+        self.stats["gpu_rows"] += n_assign - n_miss
+        if n_miss == 0:
+            self.stats["layers_all_hit"] += 1
+        else:
+            # host FFN of the missed assignments, grouped by expert with array operations
+            miss_rows = miss_pos // k
+            x_host = x.cpu()
+            by = np.argsort(miss_exp, kind="stable")
+            y_cpu = torch.empty(n_miss, self.hidden, dtype=x.dtype)
+            jobs, i = [], 0
+            exp_sorted = miss_exp[by]
+            while i < n_miss:
+                j = i
+                while j < n_miss and exp_sorted[j] == exp_sorted[i]:
+                    j += 1
+                sel = by[i:j]
+                wgu, wd = self.stores[l].weights(l, int(exp_sorted[i]))
+                xs_h = x_host[torch.from_numpy(miss_rows[sel].astype(np.int64))].contiguous()
+                if self.pool is not None:
+                    out = torch.empty(j - i, self.hidden, dtype=torch.bfloat16)
+                    jobs.append((xs_h, wgu.contiguous(), wd.contiguous(), out, sel))
+                else:
+                    y_cpu[torch.from_numpy(sel.astype(np.int64))] = ref.expert_ffn(xs_h, wgu, wd, self.swiglu_mode).to(x.dtype)
+                i = j
+            if jobs:
+                self.pool.run([(a, b, c, d) for a, b, c, d, _ in jobs], self.swiglu_mode)
+                for _, _, _, out, sel in jobs:
+                    y_cpu[torch.from_numpy(sel.astype(np.int64))] = out
+            y = torch.cat([y, y_cpu.to(dev, non_blocking=True)], dim=0)
+            idx = torch.from_numpy(miss_pos.astype(np.int64)).to(dev, non_blocking=True)
+            pos[idx] = torch.arange(cap_rows, cap_rows + n_miss, dtype=torch.int32, device=dev)
+        return moe_cuda.combine(y, pos, ids.contiguous(), weights.contiguous(), rows, self.hidden)
+
     def _forward_cuda(self, l, x, weights, ids, misses) -> torch.Tensor:
         from ..ops import moe_cuda
         rows, k = ids.shape
@@ -181,8 +328,45 @@ class TieredExpertProvider:
         return moe_cuda.combine(y, pos, ids.contiguous(), weights.contiguous(), rows, self.hidden)
 
 
+def rates_from_calibration(model, settings, device):
+    """(TransferRates, CpuService) from ``ff calibrate``'s cache for this model and device (largest measured copy size,
+    one-row host FFN time), or the defaults when the cache does not exist."""
+    from .plan import CpuService, TransferRates
+    rates, cpu = TransferRates(), CpuService()
+    if settings is None:
+        return rates, cpu
+    try:
+        from ..planner.calibrate import load_calibration
+        cal = load_calibration(getattr(model.spec, "name", None), settings, torch.device(device))
+    except Exception:
+        cal = None
+    if not cal:
+        return rates, cpu
+    copies = cal.get("copy_rates") or {}
+    if copies:
+        big = copies[max(copies, key=lambda k: int(k))]
+        rates.h2d_bytes_s, rates.d2h_bytes_s = float(big["h2d_bytes_s"]), float(big["d2h_bytes_s"])
+    if cal.get("copy_engines"):
+        rates.copy_engines = int(cal["copy_engines"])
+    if cal.get("disk_bytes_s"):
+        rates.disk_bytes_s = float(cal["disk_bytes_s"])
+    svc = cal.get("cpu_service") or {}
+    table = svc.get("seconds_per_expert_by_rows") or {}
+    if table:
+        cpu.per_expert_s = float(table[min(table, key=lambda k: int(k))])
+        cpu.workers = int(svc.get("workers", cpu.workers))
+    return rates, cpu
+
+
+def _deinterleave64_rows(t: torch.Tensor) -> torch.Tensor:
+    """Inverse of the per-64 gate/up row interleave: [2f, ...] rows back to [gate | up]."""
+    n = t.shape[0]
+    g = t.view(n // 128, 2, 64, *t.shape[1:])
+    return torch.cat([g[:, 0].reshape(n // 2, *t.shape[1:]), g[:, 1].reshape(n // 2, *t.shape[1:])], dim=0)
+
+
 def build_provider_from_weights(model, resident_fraction: float, device=None, mode: str = "score", threads: int = 8,
-                                admission_cap: int | None = None) -> TieredExpertProvider:
+                                admission_cap: int | None = None, settings=None) -> TieredExpertProvider:
     """Move a loaded model's routed experts to the host tier and serve them through GPU slots
     holding ``resident_fraction`` of them (the Qwen3-MoE benchmark runs with 0.5)."""
     from .plan import CpuService, TransferRates, admission_budget, plan_capacity
@@ -192,17 +376,40 @@ def build_provider_from_weights(model, resident_fraction: float, device=None, mo
     moe_layers = [i for i, lw in enumerate(w.layers) if lw.router is not None]
     e_local = w.layers[moe_layers[0]].experts_gu.shape[0]
     f = spec.moe.expert_ffn
+    nvfp4 = spec.moe.expert_format == "nvfp4" and device.type == "cuda" and f % 128 == 0 and spec.hidden % 128 == 0
     slot_bytes = 3 * f * spec.hidden * w.embed.element_size()
+    if nvfp4:
+        slot_bytes = 3 * f * spec.hidden // 2 + 3 * f * spec.hidden // 16 + 8       # packed codes + E4M3 scales
     geo = ExpertGeometry(len(moe_layers), e_local, spec.moe.top_k, slot_bytes)
-    cap = plan_capacity(geo, device_expert_bytes=1 << 62, host_bytes=1 << 62, rates=TransferRates(),
+    # transfer and host-FFN rates: the calibration cache of this machine when there is one, defaults otherwise
+    rates, cpu = rates_from_calibration(model, settings, device)
+    cap = plan_capacity(geo, device_expert_bytes=1 << 62, host_bytes=1 << 62, rates=rates,
                         resident_fraction=resident_fraction)
-    adm = admission_budget(geo, TransferRates(), CpuService())
+    adm = admission_budget(geo, rates, cpu)
     if admission_cap is not None:
         adm = Admission(adm.bytes_per_token, admission_cap)
     stores = []
     for i in moe_layers:
         lw = w.layers[i]
-        stores.append(ExpertStore(lw.experts_gu.cpu(), lw.experts_down.cpu(), pin=device.type == "cuda"))
+        packed = None
+        gu_h, dn_h = lw.experts_gu.cpu(), lw.experts_down.cpu()
+        if nvfp4:
+            # slots hold the packed codes; the host tier computes with the same effective (dequantised) weights
+            from ..loaders import quant as qref
+            from ..ops import moe_cuda
+            fp4 = lw.extra.pop("experts_fp4", None)
+            if fp4 is None:
+                fp4 = (moe_cuda.Nvfp4Experts.quantize(lw.experts_gu, gate_up=True), moe_cuda.Nvfp4Experts.quantize(lw.experts_down))
+            pg, pd = fp4
+            inv = _deinterleave64_rows
+            gu_h = torch.stack([qref.dequantize_nvfp4(inv(pg.codes[e].cpu()), inv(pg.scales[e].cpu()), pg.global_scale[e].cpu(),
+                                                      torch.bfloat16) for e in range(e_local)])
+            dn_h = torch.stack([qref.dequantize_nvfp4(pd.codes[e].cpu(), pd.scales[e].cpu(), pd.global_scale[e].cpu(),
+                                                      torch.bfloat16) for e in range(e_local)])
+            for st in (pg, pd):
+                st.codes, st.scales, st.global_scale = st.codes.cpu(), st.scales.cpu(), st.global_scale.cpu()
+            packed = (pg, pd)
+        stores.append(ExpertStore(gu_h, dn_h, pin=device.type == "cuda", packed=packed))
     prov = TieredExpertProvider(geo, cap, adm, stores, device, spec.hidden, f, mode=mode,
                                 swiglu_mode=spec.swiglu_mode, threads=threads)
     prov.layer_index = {ml: j for j, ml in enumerate(moe_layers)}

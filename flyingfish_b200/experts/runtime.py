@@ -155,6 +155,25 @@ class Residency:
                 self.stats["host_misses"] += 1
         return d
 
+    def account(self, layer: int, routed_experts, n_hits: int, miss_experts) -> tuple[list[int], list[int]]:
+        """Array form of :meth:`dispatch` for callers that resolved the slots on the device: ``routed_experts`` are the
+        distinct experts the token rows named (+1 score each, marked as routed this token), ``n_hits`` the
+        assignments served from slots, ``miss_experts`` the expert of every missed assignment. Returns the positions
+        (into ``miss_experts``) that go to the host tier and to the disk tier."""
+        assert self.in_token, "account outside begin_token / finish_token"
+        sc, rt = self.score[layer], self.routed[layer]
+        for e in routed_experts:
+            e = int(e)
+            sc[e] += 1.0
+            rt.add(e)
+        host, disk = [], []
+        for i, e in enumerate(miss_experts):
+            (disk if (layer, int(e)) in self.disk else host).append(i)
+        self.stats["hits"] += int(n_hits)
+        self.stats["host_misses"] += len(host)
+        self.stats["disk_misses"] += len(disk)
+        return host, disk
+
     def finish_token(self) -> list[Move]:
         """Admit up to ``hard_cap`` experts across all layers; returns the slot moves."""
         assert self.in_token
