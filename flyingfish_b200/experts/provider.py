@@ -79,6 +79,10 @@ class TieredExpertProvider:
                                for l in range(geo.layers)]
         self.table = [torch.full((geo.experts_per_layer,), EMPTY, dtype=torch.int32, device=self.device)
                       for _ in range(geo.layers)]
+        # the inverse map, slot -> expert (EMPTY for a free slot): expert-parallel owners run their grouped GEMMs
+        # over the slots and pick each slot's row segment through it
+        self.slot_expert = [torch.full((cap.slots_per_layer[l],), EMPTY, dtype=torch.int32, device=self.device)
+                            for l in range(geo.layers)]
         self.pool = ExpertPool(threads) if dt == torch.bfloat16 else None
         self.layer_index: dict[int, int] = {}      # model layer number -> MoE layer ordinal
         self.copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
@@ -126,10 +130,12 @@ class TieredExpertProvider:
                     if m.expert_out != EMPTY:
                         self.table[m.layer][m.expert_out] = EMPTY
                     self.table[m.layer][m.expert_in] = m.slot
+                    self.slot_expert[m.layer][m.slot] = m.expert_in
             else:
                 if m.expert_out != EMPTY:
                     self.table[m.layer][m.expert_out] = EMPTY
                 self.table[m.layer][m.expert_in] = m.slot
+                self.slot_expert[m.layer][m.slot] = m.expert_in
             self.stats["h2d_expert_bytes"] += self.geo.slot_bytes
             touched.add(m.layer)
         if cuda:
@@ -308,6 +314,72 @@ class TieredExpertProvider:
             idx = torch.from_numpy(miss_pos.astype(np.int64)).to(dev, non_blocking=True)
             pos[idx] = torch.arange(cap_rows, cap_rows + n_miss, dtype=torch.int32, device=dev)
         return moe_cuda.combine(y, pos, ids.contiguous(), weights.contiguous(), rows, self.hidden)
+
+    def ep_experts(self, model_layer: int, recv_x: torch.Tensor, seg_off: torch.Tensor, counts: torch.Tensor,
+                   capacity: int, out_y: torch.Tensor) -> None:
+        """Expert phase of an expert-parallel layer on a rank that tiers its own experts. ``recv_x`` holds the rows
+        that arrived for this rank's experts, one 16-row padded segment per local expert (``seg_off`` / ``counts`` on
+        the device). Resident experts run as grouped GEMMs over the slot arena (slot s takes the segment of the expert
+        it holds); the segments of experts that are not resident are computed by the host FFN and written into
+        ``out_y`` (the symmetric buffer the peers combine from) behind them. One small D2H (counts and offsets)."""
+        import numpy as np
+        from ..ops import moe_cuda
+        l = self.layer_index[model_layer]
+        dev = self.device
+        cur = torch.cuda.current_stream(dev)
+        if self.layer_event[l] is not None:
+            cur.wait_event(self.layer_event[l])
+            self.layer_event[l] = None
+        self.stats["layer_calls"] += 1
+        el = self.geo.experts_per_layer
+        meta_h = torch.cat([counts[:el], seg_off[:el]]).cpu().numpy()         # the one synchronising copy
+        self.stats["d2h_summary_bytes"] += 8 * el
+        counts_h, off_h = meta_h[:el], meta_h[el:]
+        # slot-ordered segment arrays for the grouped GEMMs over the arena
+        se = self.slot_expert[l].long()
+        live = se >= 0
+        sel = se.clamp_min(0)
+        counts_s = torch.where(live, counts[:el][sel], torch.zeros_like(sel, dtype=counts.dtype)).to(torch.int32).contiguous()
+        off_s = seg_off[:el][sel].to(torch.int32).contiguous()
+        if self.fp4:
+            h = moe_cuda.grouped_gemm_nvfp4(recv_x, self.arena_gu[l], off_s, counts_s, capacity, epi=1)
+            moe_cuda.grouped_gemm_nvfp4(h, self.arena_down[l], off_s, counts_s, capacity, epi=0, out=out_y)
+        else:
+            h = moe_cuda.grouped_gemm(recv_x, self.arena_gu[l], off_s, counts_s, capacity, epi=1)
+            moe_cuda.grouped_gemm(h, self.arena_down[l], off_s, counts_s, capacity, epi=0, out=out_y)
+        # accounting and the host tier
+        slot_of = self.res.slot_of[l]
+        routed = np.nonzero(counts_h > 0)[0]
+        miss_e = [int(e) for e in routed if slot_of[int(e)] == EMPTY]
+        n_hit = int(sum(int(counts_h[e]) for e in routed if slot_of[int(e)] != EMPTY))
+        opened = False
+        if not self.res.in_token:
+            self.res.in_token = True
+            self.res.routed[l].clear()
+            opened = True
+        miss_rows = [e for e in miss_e for _ in range(int(counts_h[e]))]
+        self.res.account(l, routed, n_hit, miss_rows)
+        if opened:
+            self.res.in_token = False
+        self.stats["gpu_rows"] += n_hit
+        self.stats["cpu_rows"] += len(miss_rows)
+        if not miss_e:
+            self.stats["layers_all_hit"] += 1
+            return
+        jobs = []
+        for e in miss_e:
+            o, c = int(off_h[e]), int(counts_h[e])
+            xs_h = recv_x[o: o + c].cpu()
+            wgu, wd = self.stores[l].weights(l, e)
+            if self.pool is not None:
+                out = torch.empty(c, self.hidden, dtype=torch.bfloat16)
+                jobs.append((xs_h.contiguous(), wgu.contiguous(), wd.contiguous(), out, o))
+            else:
+                out_y[o: o + c].copy_(ref.expert_ffn(xs_h, wgu, wd, self.swiglu_mode).to(out_y.dtype))
+        if jobs:
+            self.pool.run([(a, b, c_, d) for a, b, c_, d, _ in jobs], self.swiglu_mode)
+            for _, _, _, out, o in jobs:
+                out_y[o: o + out.shape[0]].copy_(out.to(dev, non_blocking=True))
 
     def _forward_cuda(self, l, x, weights, ids, misses) -> torch.Tensor:
         from ..ops import moe_cuda

@@ -29,7 +29,7 @@ def moe_ffn(model, layer: int, n: torch.Tensor) -> torch.Tensor:
         model.route_hook(layer, ids, weights)
     ep = getattr(model, "ep", None)
     if ep is not None and ep.size > 1:
-        routed = ep.dispatch_ffn_combine(n, weights, ids, lw, model.spec.swiglu_mode)
+        routed = ep.dispatch_ffn_combine(n, weights, ids, lw, model.spec.swiglu_mode, layer=layer)
     else:
         provider = getattr(model, "expert_provider", None)
         fp4 = lw.extra.get("experts_fp4")

@@ -98,13 +98,14 @@ def dispatch_local(x, ids, n_experts_total: int, e_lo: int, e_hi: int):
 TILED_MIN_ROWS = int(os.environ.get("FF_MOE_TILED_MIN", "96"))
 
 
-def grouped_gemm(xs, w, seg_off, counts, capacity: int, epi: int, rows_per_expert: float = 0.0) -> torch.Tensor:
+def grouped_gemm(xs, w, seg_off, counts, capacity: int, epi: int, rows_per_expert: float = 0.0,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
     """``rows_per_expert`` is the caller's estimate of the mean segment length (assignments / local experts; the
     true counts stay on the device): from ``TILED_MIN_ROWS`` on, the 128-row-tile kernel (tokens on the UMMA M
     side, double-buffered accumulators) runs instead of the swap-AB kernel that streams each weight slice once."""
     el, nw, k = w.shape
     n_out = nw // 2 if epi == 1 else nw
-    y = torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs.device)
+    y = out if out is not None else torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs.device)
     tiled = rows_per_expert >= TILED_MIN_ROWS and (epi == 0 or nw % 256 == 0)
     fn = kernels().ff_moe_grouped_gemm_tiled if tiled else kernels().ff_moe_grouped_gemm
     rc = fn(ptr(xs), ptr(w), ptr(y), ptr(seg_off), ptr(counts), el, nw, k, capacity, n_out, epi,
@@ -184,9 +185,10 @@ class Nvfp4Experts:
         return self.n % 128 == 0 and self.k % 128 == 0
 
 
-def grouped_gemm_nvfp4(xs, w: Nvfp4Experts, seg_off, counts, capacity: int, epi: int) -> torch.Tensor:
+def grouped_gemm_nvfp4(xs, w: Nvfp4Experts, seg_off, counts, capacity: int, epi: int,
+                       out: torch.Tensor | None = None) -> torch.Tensor:
     n_out = w.n // 2 if epi == 1 else w.n
-    y = torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs.device)
+    y = out if out is not None else torch.empty(capacity, n_out, dtype=torch.bfloat16, device=xs.device)
     rc = kernels().ff_moe_grouped_gemm_nvfp4(ptr(xs), ptr(w.codes), ptr(w.scales), ptr(w.global_scale), ptr(y), ptr(seg_off),
                                              ptr(counts), w.experts, w.n, w.k, capacity, n_out, epi,
                                              ptr(status_tensor(xs.device)), stream_ptr())

@@ -38,6 +38,7 @@ class EPComm:
         assert num_experts % self.size == 0, "experts must divide evenly over the expert-parallel ranks"
         self.E, self.El, self.hidden = num_experts, num_experts // self.size, hidden
         self.stats = {"fused_calls": 0, "baseline_calls": 0}
+        self.provider = None          # experts.provider.TieredExpertProvider when this rank tiers its own experts
         self.arena = None
         if self.device.type == "cuda" and self.size > 1:
             self._setup_arena(max_rows, top_k)
@@ -71,16 +72,22 @@ class EPComm:
         self.scratch = torch.zeros(2 * self.E + 2 * self.El + 1, dtype=torch.int32, device=self.device)
 
     # -- one MoE layer ---------------------------------------------------------------------------
-    def dispatch_ffn_combine(self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor, lw, mode: int
-                             ) -> torch.Tensor:
-        """Routed-expert output for the local rows ``x`` (shared expert not included)."""
+    def dispatch_ffn_combine(self, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor, lw, mode: int,
+                             layer: int = -1) -> torch.Tensor:
+        """Routed-expert output for the local rows ``x`` (shared expert not included). ``layer``: the model's layer
+        number, needed when this rank serves its experts from tiers."""
         if self.arena is not None and x.is_cuda:
-            return self._fused(x, weights, ids, lw, mode)
+            return self._fused(x, weights, ids, lw, mode, layer)
+        if self.provider is not None:
+            raise RuntimeError("tiered experts under expert parallelism need the CUDA peer-memory path")
         return self._baseline(x, weights, ids, lw, mode)
 
-    def _fused(self, x, weights, ids, lw, mode):
+    def _fused(self, x, weights, ids, lw, mode, layer: int = -1):
         pos = self.dispatch(x, ids)
-        self.experts(lw)
+        if self.provider is not None:
+            self.provider.ep_experts(layer, self.recv_x, self._seg_off, self._counts, self.capacity, self.out_y)
+        else:
+            self.experts(lw)
         out = self.combine(pos, ids, weights, x.shape[0])
         self.stats["fused_calls"] += 1
         return out

@@ -140,3 +140,26 @@ def test_ep2_fp8_experts_gpu(tmp_path):
         single = _single_moe("cuda", r["prompts"], "deepseek-v3-fp8-mini")
         for p, want, got in zip(r["prompts"], single, r["tokens"]):
             assert_tokens_equal_up_to_ties(m, p, want, got)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("model", ["qwen3-moe-tiny", "qwen3-moe-fp4-tiny"])
+def test_ep2_with_tiered_experts_gpu(tmp_path, model):
+    """Expert parallelism composed with expert tiering: each of two ranks owns half of the experts and keeps half of
+    those in GPU slots (packed NVFP4 slots for the NVFP4-expert model); rows for the other experts are computed by the
+    owner's host FFN. Tokens must follow the single-GPU all-resident run up to the first near-tie."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _launch(2, "cuda", "ep_tier", tmp_path, 29520, model=model)
+    assert res["stats"]["fused_calls"] > 0
+    for r in res["per_rank"]:
+        assert r["fp4"] == (model == "qwen3-moe-fp4-tiny")
+        assert r["res"]["hits"] > 0 and r["res"]["tokens"] == 7 and r["prov"]["gpu_rows"] > 0
+        single = _single_moe("cuda", r["prompts"], model)[0]
+        agree = 0
+        for a, b in zip(r["tokens"][0], single):
+            if a != b:
+                break
+            agree += 1
+        assert agree >= (4 if model == "qwen3-moe-tiny" else 1), (r["tokens"][0], single)
+    assert sum(r["prov"]["cpu_rows"] for r in res["per_rank"]) > 0        # the host tier served something

@@ -120,6 +120,32 @@ def main():
             torch.cuda.synchronize()
             ops.check_status(device)
         result.update(per_rank=gathered, stats=ep.stats)
+    elif args.mode == "ep_tier":
+        # expert parallelism with every rank serving its own experts from tiers: half of them in GPU slots, the rest
+        # through the host FFN
+        from flyingfish_b200.parallel.ep import EPComm
+        from flyingfish_b200.config import named_shape
+        from flyingfish_b200.experts.provider import build_provider_from_weights
+        spec = named_shape(args.model)
+        ep = EPComm(dist.group.WORLD, device, spec.moe.num_experts, spec.hidden, max_rows=128, top_k=spec.moe.top_k)
+        m = Model.load(args.model, Settings(capacity=256, max_batch=4, graph=False), device=device, seed=0, ep=ep)
+        prov = build_provider_from_weights(m.engine.model, resident_fraction=0.5, threads=2, admission_cap=2)
+        ep.provider = prov
+        g = torch.Generator().manual_seed(100 + rank)
+        prompt = torch.randint(0, 2048, (33,), generator=g).tolist()
+        eng = m.engine
+        prov.collect_freq = True
+        seq = eng.add_sequence(prompt)
+        first = eng.prefill([seq])[0]
+        prov.collect_freq = False
+        prov.begin_request()
+        toks = [first] + [eng.decode([seq])[0] for _ in range(7)]
+        gathered = [None] * world
+        dist.all_gather_object(gathered, {"prompts": [prompt], "tokens": [toks], "res": dict(prov.res.stats),
+                                          "prov": dict(prov.stats), "fp4": prov.fp4})
+        torch.cuda.synchronize()
+        ops.check_status(device)
+        result.update(per_rank=gathered, stats=ep.stats)
     if rank == 0:
         Path(args.out).write_text(json.dumps(result))
     dist.barrier()
