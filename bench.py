@@ -44,8 +44,15 @@ from pathlib import Path
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 
 CONFIGS = {
-    2: {"model": "llama3-8b-shape", "batch": 64, "prompt": 1024, "batches": (1, 8, 64)},
-    3: {"model": "llama3-70b-shape", "batch": 32, "prompt": 4096, "batches": (1, 32, 128)},
+    2: {"model": "llama3-8b-shape", "batch": 64, "prompt": 1024, "batches": (1, 8, 64), "parallelism": "tp"},
+    3: {"model": "llama3-70b-shape", "batch": 32, "prompt": 4096, "batches": (1, 32, 128), "parallelism": "tp"},
+    # DeepSeek-V3 shape: FP8 E4M3 weights with 128x128 block scales, MLA, expert parallel over the N GPUs (attention
+    # data parallel: every rank serves batch / N sequences), one MTP module
+    4: {"model": "deepseek-v3-shape", "batch": 64, "prompt": 1024, "batches": (1, 64, 256), "parallelism": "ep"},
+    # Qwen3-MoE-235B shape: NVFP4 experts, expert parallel, half of every rank's experts resident in GPU slots and
+    # the rest in the pinned host tier
+    5: {"model": "qwen3-moe-235b-shape", "batch": 128, "prompt": 1024, "batches": (128,), "parallelism": "ep",
+        "resident": 0.5},
 }
 
 
@@ -60,7 +67,9 @@ def parse() -> argparse.Namespace:
     p.add_argument("--batch", type=int, default=None)
     p.add_argument("--prompt", type=int, default=None)
     p.add_argument("--layers", type=int, default=None, help="run a reduced-depth variant (reported in config)")
-    p.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
+    p.add_argument("--parallelism", default=None, choices=["tp", "dp", "ep"])
+    p.add_argument("--resident", type=float, default=None, help="fraction of the experts kept in GPU slots (config 5)")
+    p.add_argument("--mtp", type=int, default=0, help="also time MTP speculation of this depth (config 4)")
     p.add_argument("--no-graph", action="store_true")
     p.add_argument("--skip-e2e", action="store_true")
     p.add_argument("--skip-baseline", action="store_true")
@@ -72,6 +81,11 @@ def parse() -> argparse.Namespace:
     a.batch = a.batch or c["batch"]
     a.prompt = a.prompt or c["prompt"]
     a.batches = c["batches"]
+    a.parallelism = a.parallelism or c["parallelism"]
+    if a.resident is None:
+        a.resident = c.get("resident")
+    if a.parallelism == "ep":
+        a.skip_baseline = True          # the library-call arm models the dense decoder only
     return a
 
 
@@ -231,19 +245,35 @@ def run_ours(cx: Ctx) -> dict:
 
     world, rank, device, on_gpu = cx.world, cx.rank, cx.device, cx.on_gpu
     spec0 = spec_for(args)
-    comm = None
+    comm, ep = None, None
     if world > 1 and args.parallelism == "tp":
         from flyingfish_b200.parallel.comm import TPComm
         comm = TPComm.create(dist.group.WORLD, device, slot_bytes=(8192 // world) * spec0.hidden * 2)
     tp = world if comm is not None else 1
-    global_batch = args.batch if (args.parallelism == "tp" or world == 1) else args.batch * world
-    local_batch = args.batch
+    if args.parallelism == "ep":
+        # experts sharded over the ranks, attention data parallel: the batch is split over the ranks
+        global_batch = args.batch
+        local_batch = max(1, args.batch // world)
+        if world > 1:
+            from flyingfish_b200.parallel.ep import EPComm
+            ep = EPComm(dist.group.WORLD, device, spec0.moe.num_experts, spec0.hidden,
+                        max_rows=max(local_batch, 8192 // 8), top_k=spec0.moe.top_k)
+    else:
+        global_batch = args.batch if (args.parallelism == "tp" or world == 1) else args.batch * world
+        local_batch = args.batch
     max_batch = max([local_batch] + ([] if args.skip_extras else list(args.batches)))
     capacity = ((args.prompt + 2 * (args.warmup + args.steps) + 8 + 63) // 64) * 64
     settings = Settings(device=cx.local_rank, capacity=capacity, max_batch=max_batch, graph=not args.no_graph, tp=tp)
     model = Model.load(args.model if not args.layers else spec0, settings, device=device, random_init=True, seed=0,
-                       comm=comm)
+                       comm=comm, ep=ep)
     eng, spec = model.engine, model.spec
+    provider = None
+    if args.resident is not None and spec.moe is not None:
+        from flyingfish_b200.experts.provider import build_provider_from_weights
+        provider = build_provider_from_weights(eng.model, resident_fraction=args.resident, threads=8, settings=settings)
+        if ep is not None:
+            ep.provider = provider
+        provider.collect_freq = True
     g = torch.Generator().manual_seed(1 + (rank if comm is None else 0))
 
     def new_prompts(n: int) -> list[list[int]]:
@@ -268,6 +298,12 @@ def run_ours(cx: Ctx) -> dict:
 
     # ---- prefill (reported, not the headline) ---------------------------------------------------------------------
     prefill_ms, _ = cx.timed(lambda i: eng.prefill(seqs), 1)
+    if provider is not None:
+        # slots are filled by the prefill's routing frequency, as at a request boundary
+        provider.collect_freq = False
+        provider.begin_request()
+        for k in ("hits", "host_misses", "disk_misses"):
+            provider.res.stats[k] = 0
 
     # ---- e2e: public API, per-step H2D of metadata + D2H of ids -----------------------------------------------------
     e2e = None
@@ -319,25 +355,52 @@ def run_ours(cx: Ctx) -> dict:
             ops.check_status(device)
         return ms, clk, staged[total_steps - 1], bucket
 
-    ms_per_step, clocks, last_meta, bucket = device_timed(seqs, local_batch, args.warmup, args.steps)
+    if provider is not None:
+        # the host tier is serviced inside every step (a device-to-host summary per MoE layer), so there is no
+        # host-free form of the step: the device-timed value is the engine step itself
+        for _ in range(args.warmup):
+            eng.decode(seqs)
+        ms_per_step, clocks = cx.timed(lambda i: eng.decode(seqs), args.steps)
+        bucket, last_meta = bucket_for(local_batch), None
+    else:
+        ms_per_step, clocks, last_meta, bucket = device_timed(seqs, local_batch, args.warmup, args.steps)
 
     # launches of this library's kernels per step: counted during one eager step
     was_graph = eng.use_graph
     eng.use_graph = False
     ops.reset_launch_count()
-    fb2 = eng._decode_batch(bucket)
-    fb2.host.copy_(last_meta); fb2.rows = bucket; fb2.batch = bucket; fb2.n_logit_rows = bucket
-    fb2.is_decode = True; fb2.nq = 1; fb2.max_ctx = capacity; fb2.use_tree_mask = False
-    fb2.upload()
-    eng.model.forward(fb2, eng.kv)
+    if last_meta is None:
+        eng.decode(seqs)
+    else:
+        fb2 = eng._decode_batch(bucket)
+        fb2.host.copy_(last_meta); fb2.rows = bucket; fb2.batch = bucket; fb2.n_logit_rows = bucket
+        fb2.is_decode = True; fb2.nq = 1; fb2.max_ctx = capacity; fb2.use_tree_mask = False
+        fb2.upload()
+        eng.model.forward(fb2, eng.kv)
     if on_gpu:
         torch.cuda.synchronize(device)
     launches_per_step = ops.launch_count()
     eng.use_graph = was_graph
 
+    # ---- MTP speculation (config 4): tokens per second of one sequence with the MTP module drafting ---------------
+    mtp = None
+    if args.mtp > 0:
+        from flyingfish_b200.spec.mtp import MtpSpeculator
+        eng.reset()
+        sp = MtpSpeculator(model, depth=args.mtp, seed=11)
+        n_new = max(8, args.steps)
+        cx.barrier()
+        t0 = time.perf_counter()
+        out = sp.generate(new_prompts(1)[0], n_new)
+        cx.barrier()
+        dt = time.perf_counter() - t0
+        mtp = {"depth": args.mtp, "tokens": len(out.ids), "tokens_per_s": len(out.ids) / max(dt - out.prefill_ms / 1e3, 1e-9),
+               "rounds": sp.stats.rounds, "acceptance_rate": sp.stats.acceptance_rate,
+               "note": "random-init MTP module: acceptance is near zero, the figure is the cost of a round"}
+
     # ---- the other batch sizes of the config (device-timed only) ----------------------------------------------------
     others = {}
-    if not args.skip_extras:
+    if not args.skip_extras and provider is None and args.mtp == 0:
         for b in args.batches:
             if b == local_batch or b > max_batch:
                 continue
@@ -360,7 +423,8 @@ def run_ours(cx: Ctx) -> dict:
     out = {
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if args.parallelism == "tp" else "weak", "vs_baseline": None, "dtype": "bf16",
+        "scaling": "strong" if args.parallelism in ("tp", "ep") else "weak", "vs_baseline": None,
+        "dtype": "bf16" if spec.linear_format == "bf16" else f"{spec.linear_format} weights (W8A8), bf16 activations",
         "data": "synthetic (seeded uniform token ids, random-init N(0,0.02) weights)",
         "config": {"model": args.model, "layers": spec.layers, "global_batch": global_batch, "seq_len": args.prompt,
                    "new_tokens_timed": args.steps, "kv_block": 64,
@@ -373,6 +437,19 @@ def run_ours(cx: Ctx) -> dict:
         "hbm_gbs_achieved": roof, "hbm_frac_of_measured": roof / hbm,
         "impl": "ours",
     }
+    if spec.moe is not None:
+        out["config"].update(experts=spec.moe.num_experts, top_k=spec.moe.top_k, expert_format=spec.moe.expert_format,
+                             linear_format=spec.linear_format)
+        out.pop("hbm_gbs_achieved"); out.pop("hbm_frac_of_measured")        # the byte model above is the dense decoder's
+    if provider is not None:
+        st = provider.res.stats
+        out["experts"] = {"resident_fraction": args.resident, "slots": "nvfp4" if provider.fp4 else "bf16",
+                          "hit_rate": provider.res.hit_rate(), "hits": st["hits"], "host_misses": st["host_misses"],
+                          "admitted": st["admitted"], "evicted": st["evicted"], "cpu_rows": provider.stats["cpu_rows"],
+                          "gpu_rows": provider.stats["gpu_rows"], "h2d_expert_bytes": provider.stats["h2d_expert_bytes"],
+                          "d2h_summary_bytes": provider.stats["d2h_summary_bytes"]}
+    if mtp is not None:
+        out["mtp"] = mtp
     # release the engine before the comparison arm allocates its own weights
     del model, eng, seqs
     return out

@@ -464,8 +464,9 @@ def build_provider_from_weights(model, resident_fraction: float, device=None, mo
     for i in moe_layers:
         lw = w.layers[i]
         packed = None
-        gu_h, dn_h = lw.experts_gu.cpu(), lw.experts_down.cpu()
-        if nvfp4:
+        if not nvfp4:
+            gu_h, dn_h = lw.experts_gu.cpu(), lw.experts_down.cpu()
+        else:
             # slots hold the packed codes; the host tier computes with the same effective (dequantised) weights
             from ..loaders import quant as qref
             from ..ops import moe_cuda
@@ -474,10 +475,10 @@ def build_provider_from_weights(model, resident_fraction: float, device=None, mo
                 fp4 = (moe_cuda.Nvfp4Experts.quantize(lw.experts_gu, gate_up=True), moe_cuda.Nvfp4Experts.quantize(lw.experts_down))
             pg, pd = fp4
             inv = _deinterleave64_rows
-            gu_h = torch.stack([qref.dequantize_nvfp4(inv(pg.codes[e].cpu()), inv(pg.scales[e].cpu()), pg.global_scale[e].cpu(),
-                                                      torch.bfloat16) for e in range(e_local)])
-            dn_h = torch.stack([qref.dequantize_nvfp4(pd.codes[e].cpu(), pd.scales[e].cpu(), pd.global_scale[e].cpu(),
-                                                      torch.bfloat16) for e in range(e_local)])
+            from ..ops.quant_ops import dequant_nvfp4
+            gu_h = torch.stack([dequant_nvfp4(inv(pg.codes[e]), inv(pg.scales[e]), pg.global_scale[e]).cpu()
+                                for e in range(e_local)])
+            dn_h = torch.stack([dequant_nvfp4(pd.codes[e], pd.scales[e], pd.global_scale[e]).cpu() for e in range(e_local)])
             for st in (pg, pd):
                 st.codes, st.scales, st.global_scale = st.codes.cpu(), st.scales.cpu(), st.global_scale.cpu()
             packed = (pg, pd)
