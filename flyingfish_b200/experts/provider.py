@@ -15,12 +15,21 @@ Per MoE layer call (the reference's decode executor, src/backend/cuda/engine_moe
    are first read through the direct-IO ring); their outputs are uploaded behind the device outputs,
 5. ONE combine sums every contribution of a row in ascending expert id.
 
+Calls with many assignments (prefill chunks, large decode batches: ``FF_EXPERT_STREAM_MIN`` or more) do not use
+the host FFN at all: the layer's non-resident experts are streamed from the pinned host tier into a staging arena
+(two arenas: the next MoE layer's experts are copied while this layer computes), one dispatch covers resident
+slots and staged experts, and nothing is read back inside the step (the accounting summary is copied
+asynchronously and processed at the token's end). The reference's prefill streams experts through the device the
+same way (src/backend/cuda/moe/prefill.rs).
+
 At token end ``finish_token`` returns the admissions; the provider copies those experts into their
 slots on a copy stream and records one event per layer, which the next token's call for that layer
 waits on (copies for late layers overlap the early layers' compute; the reference orders slot
 lifetimes with events the same way, src/experts/arena.rs:485-560).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -92,6 +101,18 @@ class TieredExpertProvider:
                       "d2h_summary_bytes": 0}
         self.freq = [[0.0] * geo.experts_per_layer for _ in range(geo.layers)]
         self.collect_freq = False
+        # streaming mode (calls with many assignments): staging arenas for a layer's non-resident experts
+        self.stream_min = int(os.environ.get("FF_EXPERT_STREAM_MIN", "64"))
+        self.stage = None
+        self.stage_layer = [-1, -1]
+        self.stage_ready: list = [None, None]          # copies into the buffer done (copy stream)
+        self.stage_free: list = [None, None]           # last GEMMs reading the buffer done (compute stream)
+        self.vtable: list = [None] * geo.layers        # expert -> virtual slot (resident slot, or slots + staged index)
+        self.nonres: list = [None] * geo.layers
+        self.nonres_dev: list = [None] * geo.layers
+        self.pending_acc: dict[int, tuple] = {}        # layer -> (pinned summary, event, assignments) of this token
+        self.freq_dev = None
+        self.stats.update(streamed_bytes=0, stream_calls=0)
 
     # -- slot maintenance ----------------------------------------------------------------------
     def apply_moves(self, moves: list[Move]) -> None:
@@ -138,6 +159,10 @@ class TieredExpertProvider:
                 self.slot_expert[m.layer][m.slot] = m.expert_in
             self.stats["h2d_expert_bytes"] += self.geo.slot_bytes
             touched.add(m.layer)
+            self.vtable[m.layer] = None                 # the layer's resident set changed
+            for b in range(2):
+                if self.stage_layer[b] == m.layer:
+                    self.stage_layer[b] = -1
         if cuda:
             # one event per touched layer (copies are queued in move order, so a layer's event also covers it when a
             # later layer's copies follow): the next call for that layer waits on it, nobody else does
@@ -147,6 +172,10 @@ class TieredExpertProvider:
                 self.layer_event[l] = ev
 
     def begin_request(self, prefill_freq: list[list[float]] | None = None) -> None:
+        if prefill_freq is None and self.freq_dev is not None:
+            fd = self.freq_dev.cpu().tolist()             # routing counts gathered on the device by streamed calls
+            self.freq = [[a + b for a, b in zip(fa, fb)] for fa, fb in zip(self.freq, fd)]
+            self.freq_dev.zero_()
         f = prefill_freq if prefill_freq is not None else self.freq
         self.apply_moves(self.res.begin_request(f))
         self.res.freeze_prefill_rank(f)
@@ -155,7 +184,154 @@ class TieredExpertProvider:
         self.res.begin_token()
 
     def finish_token(self) -> None:
+        self._drain_accounting()
         self.apply_moves(self.res.finish_token())
+
+    # -- streaming mode ------------------------------------------------------------------------
+    def _drain_accounting(self) -> None:
+        """Summaries of this token's streamed layer calls (copied asynchronously while the step ran)."""
+        import numpy as np
+        for l, (host, ev, n_assign) in sorted(self.pending_acc.items()):
+            ev.synchronize()
+            sh = host.numpy()                              # [misses, assignments, routed bitmap]
+            if self.res.in_token:
+                self.res.account_counts(l, np.nonzero(sh[2:])[0], int(sh[1]) - int(sh[0]), int(sh[0]))
+        self.pending_acc.clear()
+
+    def _arena_like(self, n: int):
+        if self.fp4:
+            from ..ops.moe_cuda import Nvfp4Experts
+            u8 = dict(dtype=torch.uint8, device=self.device)
+            return (Nvfp4Experts(torch.zeros(n, 2 * self.ffn, self.hidden // 2, **u8),
+                                 torch.zeros(n, 2 * self.ffn, self.hidden // 16, **u8), torch.ones(n, device=self.device)),
+                    Nvfp4Experts(torch.zeros(n, self.hidden, self.ffn // 2, **u8),
+                                 torch.zeros(n, self.hidden, self.ffn // 16, **u8), torch.ones(n, device=self.device)))
+        dt = self.stores[0].gate_up.dtype
+        return (torch.zeros(n, 2 * self.ffn, self.hidden, dtype=dt, device=self.device),
+                torch.zeros(n, self.hidden, self.ffn, dtype=dt, device=self.device))
+
+    @staticmethod
+    def _first(arena, n: int):
+        """The first ``n`` experts of an arena as the grouped kernels' operand."""
+        if isinstance(arena, torch.Tensor):
+            return arena[:n]
+        from ..ops.moe_cuda import Nvfp4Experts
+        return Nvfp4Experts(arena.codes[:n], arena.scales[:n], arena.global_scale[:n])
+
+    def _virtual_table(self, l: int) -> None:
+        E, n_slots = self.geo.experts_per_layer, self.cap.slots_per_layer[l]
+        slot_of = self.res.slot_of[l]
+        nonres = [e for e in range(E) if slot_of[e] == EMPTY]
+        vt = list(slot_of)
+        for i, e in enumerate(nonres):
+            vt[e] = n_slots + i
+        self.nonres[l] = nonres
+        self.vtable[l] = torch.tensor(vt, dtype=torch.int32, device=self.device)
+        self.nonres_dev[l] = torch.tensor(nonres, dtype=torch.long, device=self.device)
+
+    def _stage_fill(self, l: int, b: int) -> None:
+        """Copy layer ``l``'s non-resident experts from the pinned host tier into staging buffer ``b`` (copy stream)."""
+        if self.vtable[l] is None:
+            self._virtual_table(l)
+        if self.stage is None:
+            n_stage = max(self.geo.experts_per_layer - s for s in self.cap.slots_per_layer)
+            self.stage = [self._arena_like(max(n_stage, 1)), self._arena_like(max(n_stage, 1))]
+        gu, dn = self.stage[b]
+        st = self.stores[l]
+        cs = self.copy_stream
+        if self.stage_free[b] is not None:
+            cs.wait_event(self.stage_free[b])
+        with torch.cuda.stream(cs):
+            for i, e in enumerate(self.nonres[l]):
+                if self.fp4:
+                    pg, pd = st.packed
+                    gu.codes[i].copy_(pg.codes[e], non_blocking=True); gu.scales[i].copy_(pg.scales[e], non_blocking=True)
+                    dn.codes[i].copy_(pd.codes[e], non_blocking=True); dn.scales[i].copy_(pd.scales[e], non_blocking=True)
+                else:
+                    from ..ops import moe_cuda
+                    wgu, wd = st.weights(l, e)
+                    gu[i].copy_(moe_cuda.interleave64(wgu.to(self.device, non_blocking=True)[None])[0])
+                    dn[i].copy_(wd, non_blocking=True)
+            if self.fp4 and self.nonres[l]:
+                idx = torch.tensor(self.nonres[l], dtype=torch.long)
+                n = len(self.nonres[l])
+                gu.global_scale[:n].copy_(st.packed[0].global_scale[idx], non_blocking=True)
+                dn.global_scale[:n].copy_(st.packed[1].global_scale[idx], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(cs)
+        self.stage_ready[b], self.stage_layer[b] = ev, l
+        self.stats["streamed_bytes"] += len(self.nonres[l]) * self.geo.slot_bytes
+
+    def _stage_for(self, l: int) -> int:
+        """Buffer holding layer ``l``'s non-resident experts (filled now if it is not there), with the next MoE
+        layer's copy started into the other buffer."""
+        if self.vtable[l] is None:
+            self._virtual_table(l)
+        b = 0 if self.stage_layer[0] == l else 1 if self.stage_layer[1] == l else (0 if self.stage_layer[0] == -1 else 1)
+        if self.stage_layer[b] != l:
+            self._stage_fill(l, b)
+        nxt = (l + 1) % self.geo.layers
+        if nxt != l and self.stage_layer[1 - b] != nxt:
+            self._stage_fill(nxt, 1 - b)
+        return b
+
+    def _grouped(self, xs, arena, seg_off, counts, capacity, epi, out=None):
+        from ..ops import moe_cuda
+        if isinstance(arena, torch.Tensor):
+            return moe_cuda.grouped_gemm(xs, arena, seg_off, counts, capacity, epi=epi, out=out)
+        return moe_cuda.grouped_gemm_nvfp4(xs, arena, seg_off, counts, capacity, epi=epi, out=out)
+
+    def _note_routing(self, l: int, flat: torch.Tensor, n_miss: torch.Tensor, n_assign: int) -> None:
+        """Asynchronous accounting summary [misses | routed bitmap] of a streamed call; read at the token's end."""
+        E = self.geo.experts_per_layer
+        if self.collect_freq:
+            if self.freq_dev is None:
+                self.freq_dev = torch.zeros(self.geo.layers, E, dtype=torch.float32, device=self.device)
+            self.freq_dev[l] += torch.bincount(flat, minlength=E).to(torch.float32)
+        if not self.res.in_token:
+            return
+        routed = torch.zeros(E, dtype=torch.int32, device=self.device)
+        routed[flat] = 1
+        host = torch.empty(2 + E, dtype=torch.int32, pin_memory=True)
+        host.copy_(torch.cat([n_miss.reshape(1).to(torch.int32),
+                              torch.tensor([n_assign], dtype=torch.int32, device=self.device), routed]), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self.pending_acc[l] = (host, ev, n_assign)
+        self.stats["d2h_summary_bytes"] += 4 * (1 + E)
+
+    def _forward_stream(self, l: int, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        from ..ops import moe_cuda
+        rows, k = ids.shape
+        E, n_slots = self.geo.experts_per_layer, self.cap.slots_per_layer[l]
+        cur = torch.cuda.current_stream(self.device)
+        if self.layer_event[l] is not None:
+            cur.wait_event(self.layer_event[l])
+            self.layer_event[l] = None
+        b = self._stage_for(l)
+        cur.wait_event(self.stage_ready[b])
+        flat = ids.reshape(-1).long()
+        vs = self.vtable[l][flat].view(rows, k)
+        self._note_routing(l, flat, (vs.reshape(-1) >= n_slots).sum(), rows * k)
+        xs, pos, seg_off, counts, cap_rows = moe_cuda.dispatch_local(x.contiguous(), vs.contiguous(), E, 0, E)
+        n_stage = E - n_slots
+        gu_s, dn_s = self.stage[b]
+        h = torch.empty(cap_rows, self.ffn, dtype=torch.bfloat16, device=self.device)
+        y = torch.empty(cap_rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        if n_slots:
+            self._grouped(xs, self._first(self.arena_gu[l], n_slots), seg_off, counts, cap_rows, 1, out=h)
+        if n_stage:
+            self._grouped(xs, self._first(gu_s, n_stage), seg_off[n_slots:], counts[n_slots:], cap_rows, 1, out=h)
+        if n_slots:
+            self._grouped(h, self._first(self.arena_down[l], n_slots), seg_off, counts, cap_rows, 0, out=y)
+        if n_stage:
+            self._grouped(h, self._first(dn_s, n_stage), seg_off[n_slots:], counts[n_slots:], cap_rows, 0, out=y)
+        fe = torch.cuda.Event()
+        fe.record(cur)
+        self.stage_free[b] = fe
+        self.stats["stream_calls"] += 1
+        self.stats["gpu_rows"] += rows * k
+        return moe_cuda.combine(y, pos, ids.contiguous(), weights.contiguous(), rows, self.hidden)
 
     # -- one layer -----------------------------------------------------------------------------
     def forward(self, model_layer: int, x: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
@@ -163,6 +339,8 @@ class TieredExpertProvider:
         rows, k = ids.shape
         self.stats["layer_calls"] += 1
         if self.device.type == "cuda":
+            if rows * k >= self.stream_min:
+                return self._forward_stream(l, x, weights, ids)
             return self._forward_cuda_vec(l, x, weights, ids)
         ids_h = ids.cpu()
         w_h = weights.cpu()
@@ -316,7 +494,7 @@ class TieredExpertProvider:
         return moe_cuda.combine(y, pos, ids.contiguous(), weights.contiguous(), rows, self.hidden)
 
     def ep_experts(self, model_layer: int, recv_x: torch.Tensor, seg_off: torch.Tensor, counts: torch.Tensor,
-                   capacity: int, out_y: torch.Tensor) -> None:
+                   capacity: int, out_y: torch.Tensor, expected_rows: float = 0.0) -> None:
         """Expert phase of an expert-parallel layer on a rank that tiers its own experts. ``recv_x`` holds the rows
         that arrived for this rank's experts, one 16-row padded segment per local expert (``seg_off`` / ``counts`` on
         the device). Resident experts run as grouped GEMMs over the slot arena (slot s takes the segment of the expert
@@ -332,6 +510,46 @@ class TieredExpertProvider:
             self.layer_event[l] = None
         self.stats["layer_calls"] += 1
         el = self.geo.experts_per_layer
+        if expected_rows >= self.stream_min:
+            # many rows: the non-resident experts are streamed through the staging arena, nothing is read back
+            b = self._stage_for(l)
+            cur.wait_event(self.stage_ready[b])
+            n_slots = self.cap.slots_per_layer[l]
+            se = self.slot_expert[l].long()
+            live = se >= 0
+            sel = se.clamp_min(0)
+            cnt = counts[:el]
+            counts_s = torch.where(live, cnt[sel], torch.zeros_like(sel, dtype=cnt.dtype)).to(torch.int32).contiguous()
+            off_s = seg_off[:el][sel].to(torch.int32).contiguous()
+            nr = self.nonres_dev[l]
+            counts_n = cnt[nr].to(torch.int32).contiguous()
+            off_n = seg_off[:el][nr].to(torch.int32).contiguous()
+            gu_s, dn_s = self.stage[b]
+            h = torch.empty(capacity, self.ffn, dtype=torch.bfloat16, device=dev)
+            if n_slots:
+                self._grouped(recv_x, self._first(self.arena_gu[l], n_slots), off_s, counts_s, capacity, 1, out=h)
+            if nr.numel():
+                self._grouped(recv_x, self._first(gu_s, nr.numel()), off_n, counts_n, capacity, 1, out=h)
+            if n_slots:
+                self._grouped(h, self._first(self.arena_down[l], n_slots), off_s, counts_s, capacity, 0, out=out_y)
+            if nr.numel():
+                self._grouped(h, self._first(dn_s, nr.numel()), off_n, counts_n, capacity, 0, out=out_y)
+            fe = torch.cuda.Event()
+            fe.record(cur)
+            self.stage_free[b] = fe
+            self.stats["stream_calls"] += 1
+            if self.collect_freq:
+                if self.freq_dev is None:
+                    self.freq_dev = torch.zeros(self.geo.layers, el, dtype=torch.float32, device=dev)
+                self.freq_dev[l] += cnt.to(torch.float32)
+            if self.res.in_token:
+                host = torch.empty(2 + el, dtype=torch.int32, pin_memory=True)
+                host.copy_(torch.cat([counts_n.sum().reshape(1).to(torch.int32), cnt.sum().reshape(1).to(torch.int32),
+                                      (cnt > 0).to(torch.int32)]), non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                self.pending_acc[l] = (host, ev, 0)
+            return
         meta_h = torch.cat([counts[:el], seg_off[:el]]).cpu().numpy()         # the one synchronising copy
         self.stats["d2h_summary_bytes"] += 8 * el
         counts_h, off_h = meta_h[:el], meta_h[el:]

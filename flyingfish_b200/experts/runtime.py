@@ -155,6 +155,18 @@ class Residency:
                 self.stats["host_misses"] += 1
         return d
 
+    def account_counts(self, layer: int, routed_experts, n_hits: int, n_miss: int) -> None:
+        """Accounting of a layer call whose misses were served by streaming the experts through the staging arena:
+        scores and routed marks as in :meth:`account`, misses counted against the host tier."""
+        assert self.in_token
+        sc, rt = self.score[layer], self.routed[layer]
+        for e in routed_experts:
+            e = int(e)
+            sc[e] += 1.0
+            rt.add(e)
+        self.stats["hits"] += int(n_hits)
+        self.stats["host_misses"] += int(n_miss)
+
     def account(self, layer: int, routed_experts, n_hits: int, miss_experts) -> tuple[list[int], list[int]]:
         """Array form of :meth:`dispatch` for callers that resolved the slots on the device: ``routed_experts`` are the
         distinct experts the token rows named (+1 score each, marked as routed this token), ``n_hits`` the

@@ -100,6 +100,7 @@ def workspace(device: torch.device) -> _Workspace:
 # linear
 # ------------------------------------------------------------------------------------------
 SKINNY_MAX_M = 128
+FP8_DENSE_ROWS = 256         # more rows than this: FP8-resident weights are expanded to BF16 for the call
 # decode-shape epilogue fusions (FLYINGFISH_FUSE_SWIGLU=0 / FLYINGFISH_FUSE_ROPE=0 fall back to separate kernels)
 FUSE_SWIGLU = os.environ.get("FLYINGFISH_FUSE_SWIGLU", "1") != "0"
 FUSE_ROPE = os.environ.get("FLYINGFISH_FUSE_ROPE", "1") != "0"
@@ -116,6 +117,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
     W8A8 GEMM of ``csrc/gemm_fp8.cu`` (CPU: its oracle) runs instead."""
     if not isinstance(w, torch.Tensor):
         from . import quant_ops
+        if x.shape[0] > FP8_DENSE_ROWS:
+            # prefill-sized calls: the weight is expanded to BF16 for this call and the large-tile BF16 GEMM runs
+            # (W8A16), as the reference does for many rows (kernels/fp8_linear.cu materialises + cuBLAS); the W8A8
+            # kernel keeps tokens on the narrow UMMA side and is meant for decode batches
+            return linear(x, w.dense(), out=out, out_dtype=out_dtype)
         y = quant_ops.linear_fp8(x, w.codes, w.scale)
         if out_dtype is not None and y.dtype != out_dtype:
             y = y.to(out_dtype)

@@ -85,7 +85,8 @@ class EPComm:
     def _fused(self, x, weights, ids, lw, mode, layer: int = -1):
         pos = self.dispatch(x, ids)
         if self.provider is not None:
-            self.provider.ep_experts(layer, self.recv_x, self._seg_off, self._counts, self.capacity, self.out_y)
+            self.provider.ep_experts(layer, self.recv_x, self._seg_off, self._counts, self.capacity, self.out_y,
+                                     expected_rows=self._rows_per_expert * self.El)
         else:
             self.experts(lw)
         out = self.combine(pos, ids, weights, x.shape[0])
