@@ -234,8 +234,9 @@ class TieredExpertProvider:
         if self.vtable[l] is None:
             self._virtual_table(l)
         if self.stage is None:
-            n_stage = max(self.geo.experts_per_layer - s for s in self.cap.slots_per_layer)
-            self.stage = [self._arena_like(max(n_stage, 1)), self._arena_like(max(n_stage, 1))]
+            # sized for a whole layer: before the first request boundary no slot is filled and everything is staged
+            n_stage = self.geo.experts_per_layer
+            self.stage = [self._arena_like(n_stage), self._arena_like(n_stage)]
         gu, dn = self.stage[b]
         st = self.stores[l]
         cs = self.copy_stream
