@@ -314,8 +314,10 @@ class TieredExpertProvider:
         flat = ids.reshape(-1).long()
         vs = self.vtable[l][flat].view(rows, k)
         self._note_routing(l, flat, (vs.reshape(-1) >= n_slots).sum(), rows * k)
-        xs, pos, seg_off, counts, cap_rows = moe_cuda.dispatch_local(x.contiguous(), vs.contiguous(), E, 0, E)
-        n_stage = E - n_slots
+        # virtual slots: the layer's resident slots (some may still be empty) followed by the staged experts
+        n_stage = len(self.nonres[l])
+        nv = n_slots + n_stage
+        xs, pos, seg_off, counts, cap_rows = moe_cuda.dispatch_local(x.contiguous(), vs.contiguous(), nv, 0, nv)
         gu_s, dn_s = self.stage[b]
         h = torch.empty(cap_rows, self.ffn, dtype=torch.bfloat16, device=self.device)
         y = torch.empty(cap_rows, self.hidden, dtype=torch.bfloat16, device=self.device)
