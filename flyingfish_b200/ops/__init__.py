@@ -106,6 +106,8 @@ FP8_MAX_K = 16384            # deepest reduction the W8A8 kernel stages activati
 FUSE_SWIGLU = os.environ.get("FLYINGFISH_FUSE_SWIGLU", "1") != "0"
 FUSE_ROPE = os.environ.get("FLYINGFISH_FUSE_ROPE", "1") != "0"
 FUSE_ATTN_MERGE = os.environ.get("FLYINGFISH_FUSE_ATTN_MERGE", "0") == "1"
+# prefill attention: the tcgen05 kernel (csrc/attention_tc.cu); FF_ATTN_PREFILL=mma selects the mma.sync kernel
+ATTN_PREFILL_TC = os.environ.get("FF_ATTN_PREFILL", "tc") != "mma"
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
@@ -470,6 +472,15 @@ def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, bl
         out = torch.empty(rows, hq * dim, dtype=BF16, device=q.device)
     nb = kcache.shape[0]
     _require(kcache.shape[2] == 64 and dim == 128, "attn_prefill: block 64 / head_dim 128 only")
+    if ATTN_PREFILL_TC and out.stride(0) % 8 == 0 and ldq % 8 == 0:
+        # tcgen05 kernel: Q Kᵀ and P V on the tensor cores with S and O in tensor memory
+        rc = kernels().ff_attn_prefill_tc(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(q_start), ptr(q_lens),
+                                          ptr(ctx_lens), ptr(out), batch, rows, max_q_len, hq, hkv, dim, ldq, out.stride(0),
+                                          block_table.shape[1], nb, c_float(scale), window,
+                                          ptr(status_tensor(q.device)), stream_ptr())
+        check(rc, "ff_attn_prefill_tc")
+        _count()
+        return out
     rc = kernels().ff_attn_prefill(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(q_start), ptr(q_lens),
                                    ptr(ctx_lens), ptr(out), batch, max_q_len, hq, hkv, dim, ldq, out.stride(0),
                                    block_table.shape[1], nb, c_float(scale), window, ptr(status_tensor(q.device)),

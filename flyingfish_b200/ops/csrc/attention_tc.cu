@@ -1,0 +1,311 @@
+// Prefill attention on 5th-generation tensor cores: paged KV, 128-dim heads, GQA, causal / sliding-window /
+// bidirectional masks, chunked prefill (query rows are the last q_len positions of a context of ctx_len).
+//
+// One CTA per (sequence, query head, tile of 128 query rows). Both contractions run as tcgen05.mma with
+// FP32 accumulators in tensor memory:
+//
+//   S = Q Kᵀ      A = Q tile  [128 rows x 128 d]   (K-major, two 64-column blocks, 128-byte swizzle, TMA)
+//                 B = K tile  [128 keys x 128 d]   (K-major, two pages of the cache, TMA)
+//                 D = S       TMEM, 128 lanes x 128 columns, double-buffered so that Q K(j+1)ᵀ runs while the
+//                             softmax warps work on tile j
+//   O += P V      A = P tile  [128 rows x 128 keys] BF16, written by the softmax warps into 128-byte-swizzled
+//                             shared memory (K-major over keys)
+//                 B = V tile  [128 keys x 128 d]    exactly as the cache stores it: d contiguous = MN-major
+//                 D = O       TMEM, 128 lanes x 128 columns, lives across all KV tiles
+//
+// Warp roles: warp 0 = TMA producer (Q once, then K/V tiles through a ring of stages, block ids read from the
+// block table), warp 1 = MMA issuer, warps 2-5 = softmax: thread t owns query row t (TMEM lane t), reads its S
+// row with tcgen05.ld, applies scale and mask, keeps the running maximum and sum in the base-2 domain, and
+// rescales O in TMEM only when the maximum has moved by more than 2^8 (the stale maximum stays exact: P and
+// the sum use the same reference, the final division cancels it).
+//
+// Every wait is bounded; a time-out records FF_ERR_TIMEOUT and the CTA leaves through the abort flag, frees
+// its tensor memory and returns. Replaces the mma.sync prefill kernel of attention_paged.cu (kept for
+// comparison) and the reference's FlashAttention-2 adapter / Rust-PTX prefill kernels
+// (third_party/flash-attention/adapter.cu:147-162, device/src/lib.rs:422-940).
+#include "ptx.cuh"
+#include "host_util.h"
+
+namespace ff {
+
+constexpr int TC_HD = 128, TC_PAGE = 64, TC_BM = 128, TC_BN = 128;
+constexpr int TC_STAGES = 2;
+constexpr int TC_Q_BYTES = TC_BM * TC_HD * 2;             // 32 KiB
+constexpr int TC_P_BYTES = TC_BM * TC_BN * 2;             // 32 KiB
+constexpr int TC_KV_BYTES = TC_BN * TC_HD * 2;            // 32 KiB per operand per stage
+constexpr int TC_SMEM = TC_Q_BYTES + TC_P_BYTES + TC_STAGES * 2 * TC_KV_BYTES + 1024;
+constexpr float TC_RESCALE_THRESHOLD = 8.0f;              // log2 units
+
+struct alignas(8) TcBars {
+  uint64_t q_full;
+  uint64_t kv_full[TC_STAGES];
+  uint64_t kv_empty[TC_STAGES];
+  uint64_t s_full[2];
+  uint64_t s_empty[2];
+  uint64_t p_full;
+  uint64_t p_empty;
+  uint64_t o_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const int* __restrict__ block_table,
+                       const int* __restrict__ q_start, const int* __restrict__ q_lens,
+                       const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, int hq, int hkv, int ldo,
+                       int max_blocks, int num_blocks, float scale_log2, int window, int causal, int* status) {
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qlen = q_lens[b];
+  const int r0 = blockIdx.x * TC_BM;
+  if (r0 >= qlen) return;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ TcBars bars;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sP = smem + TC_Q_BYTES;
+  uint8_t* sKV = smem + TC_Q_BYTES + TC_P_BYTES;          // stage s: K at s*64K, V at s*64K + 32K
+  const int ctx = ctx_lens[b], qs = q_start[b];
+  const int kvh = h / (hq / hkv);
+  const int past = ctx - qlen;
+  const int real = min(TC_BM, qlen - r0);
+  // key range of this tile
+  const int last_key = causal ? past + r0 + real - 1 : ctx - 1;
+  const int first_key = window > 0 ? max(0, past + r0 - window + 1) : 0;
+  const int t0 = first_key / TC_BN, t1 = last_key / TC_BN + 1;
+  const int ntiles = t1 - t0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    mbar_init(&bars.q_full, 1);
+    for (int i = 0; i < TC_STAGES; ++i) { mbar_init(&bars.kv_full[i], 1); mbar_init(&bars.kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 4); }
+    mbar_init(&bars.p_full, 1); mbar_init(&bars.p_empty, 1); mbar_init(&bars.o_done, 1);
+    bars.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars.tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars.tmem_base;
+  const uint32_t tmem_o = tmem_base + 256;
+  volatile int* abort_flag = &bars.abort_flag;
+
+  if (warp == 0) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      mbar_expect_tx(&bars.q_full, TC_Q_BYTES);
+      // rows past the sequence's own belong to the next sequence of the packed batch (or are out of range and read
+      // as zero): their lanes are computed and never stored
+      tma_load_2d(sQ, &tmQ, &bars.q_full, h * TC_HD, qs + r0);
+      tma_load_2d(sQ + TC_BM * 128, &tmQ, &bars.q_full, h * TC_HD + 64, qs + r0);
+      bool ok = true, bad = false;
+      const int nblk = (ctx + TC_PAGE - 1) / TC_PAGE;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j % TC_STAGES; const uint32_t ph = (j / TC_STAGES) & 1;
+        if (!mbar_wait(&bars.kv_empty[s], ph ^ 1, abort_flag, status, KID_ATTN_PREFILL, 1)) { ok = false; break; }
+        mbar_expect_tx(&bars.kv_full[s], 2 * TC_KV_BYTES);
+        uint8_t* sK = sKV + s * 2 * TC_KV_BYTES;
+        uint8_t* sV = sK + TC_KV_BYTES;
+        for (int pg = 0; pg < 2; ++pg) {
+          int page = (t0 + j) * 2 + pg;
+          if (page >= nblk) page = nblk - 1;                 // past the context: any valid page, its keys are masked
+          int blk = block_table[(size_t)b * max_blocks + page];
+          if (blk < 0 || blk >= num_blocks) { bad = true; blk = 0; }
+          const int row = (blk * hkv + kvh) * TC_PAGE;
+          // layout of a tile: block d0 = [128 keys x 64 d] (16 KiB), then block d1; a page is 64 keys of each
+          tma_load_2d(sK + pg * 8192, &tmK, &bars.kv_full[s], 0, row);
+          tma_load_2d(sK + 16384 + pg * 8192, &tmK, &bars.kv_full[s], 64, row);
+          tma_load_2d(sV + pg * 8192, &tmV, &bars.kv_full[s], 0, row);
+          tma_load_2d(sV + 16384 + pg * 8192, &tmV, &bars.kv_full[s], 64, row);
+        }
+      }
+      if (bad) set_status(status, KID_ATTN_PREFILL, FF_ERR_BOUNDS, b, blockIdx.x);
+    }
+  } else if (warp == 1) {
+    // ================================ MMA issuer ================================
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc(1, 1, 0, 0, TC_BM, TC_BN);      // Q (K-major) x K (K-major)
+      const uint32_t idesc_o = umma_idesc(1, 1, 0, 1, TC_BM, TC_HD);      // P (K-major) x V (MN-major)
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = mbar_wait(&bars.q_full, 0, abort_flag, status, KID_ATTN_PREFILL, 2);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % TC_STAGES; const uint32_t ph = (j / TC_STAGES) & 1;
+        const int sb = j & 1; const uint32_t sph = (j >> 1) & 1;
+        if (!mbar_wait(&bars.kv_full[s], ph, abort_flag, status, KID_ATTN_PREFILL, 3)) return false;
+        if (!mbar_wait(&bars.s_empty[sb], sph ^ 1, abort_flag, status, KID_ATTN_PREFILL, 4)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sKV + s * 2 * TC_KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_f16(tmem_base + sb * TC_BN, umma_desc_sw128(q_addr + off, 16, 1024), umma_desc_sw128(k_addr + off, 16, 1024),
+                   idesc_s, k != 0);
+        }
+        umma_commit(&bars.s_full[sb]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        if (j + 1 < ntiles) { ok = issue_s(j + 1); if (!ok) break; }
+        if (!mbar_wait(&bars.p_full, j & 1, abort_flag, status, KID_ATTN_PREFILL, 5)) { ok = false; break; }
+        tc_fence_after();
+        const int s = j % TC_STAGES;
+        const uint32_t v_addr = smem_u32(sKV + s * 2 * TC_KV_BYTES + TC_KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // P: 16 keys of k-step k sit in 64-key block k/4 at byte (k%4)*32 of each row; V: 16 key rows = 2 KiB
+          const uint64_t da = umma_desc_sw128(p_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t db = umma_desc_sw128(v_addr + (k >> 2) * 8192 + (k & 3) * 2048, 16384, 1024);
+          umma_f16(tmem_o, da, db, idesc_o, (j > 0) || (k != 0));
+        }
+        umma_commit(&bars.p_empty);
+        umma_commit(&bars.kv_empty[s]);
+      }
+      if (ok) umma_commit(&bars.o_done);
+    }
+  } else {
+    // ================================ softmax warps 2..5 ================================
+    const int q = warp & 3;
+    const int row = q * 32 + lane;                // query row of the tile = TMEM lane
+    const int e = (warp - 2) * 32 + lane;
+    const bool live = row < real;
+    const int pos = past + r0 + row;              // absolute position of the row
+    const int hi = live ? (causal ? pos : ctx - 1) : -1;
+    const int lo = (live && window > 0) ? max(0, pos - window + 1) : 0;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    const uint32_t lane_base = (uint32_t(q * 32) << 16);
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int sb = j & 1; const uint32_t sph = (j >> 1) & 1;
+      if (!mbar_wait(&bars.s_full[sb], sph, abort_flag, status, KID_ATTN_PREFILL, 6)) { ok = false; break; }
+      tc_fence_after();
+      float sv[TC_BN];
+#pragma unroll
+      for (int c = 0; c < TC_BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_x32(tmem_base + lane_base + sb * TC_BN + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
+      const int k0 = (t0 + j) * TC_BN;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < TC_BN; ++i) {
+        const int key = k0 + i;
+        const float t = (key >= lo && key <= hi) ? sv[i] * scale_log2 : -INFINITY;
+        sv[i] = t;
+        mx = fmaxf(mx, t);
+      }
+      // the previous P V must be done before P is overwritten or O is rescaled
+      if (!mbar_wait(&bars.p_empty, (j & 1) ^ 1, abort_flag, status, KID_ATTN_PREFILL, 7)) { ok = false; break; }
+      tc_fence_after();
+      float alpha = 1.f;
+      bool need = false;
+      if (mx > m_ref + TC_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY)) {
+        alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
+        m_ref = mx;
+        need = j > 0;                              // O holds nothing before the first P V
+      }
+      if (__any_sync(0xffffffffu, need)) {
+        // rescale this warp's 32 lanes of O (lanes that did not move keep alpha = 1)
+#pragma unroll
+        for (int c = 0; c < TC_HD; c += 16) {
+          uint32_t r[16];
+          tmem_ld_x16(tmem_o + lane_base + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_x16(tmem_o + lane_base + c, r);
+        }
+        tmem_st_wait();
+      }
+      l_sum *= alpha;
+      // P = 2^(t - m_ref), BF16, into 128-byte-swizzled K-major shared memory: row `row`, 16-byte chunk c of 64-key
+      // block kb at (row / 8) * 1024 + (row % 8) * 128 + ((c ^ (row % 8)) * 16)
+      const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
+      uint8_t* prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = exp2f(sv[c * 8 + 2 * i] - mr), p1 = exp2f(sv[c * 8 + 2 * i + 1] - mr);
+          pk[i] = pack_bf16x2(p0, p1);
+          const float2 back = unpack_bf16x2(pk[i]);          // the sum uses the rounded values the MMA will see
+          l_sum += back.x + back.y;
+        }
+        const int kb = c >> 3, cc = c & 7;
+        *reinterpret_cast<uint4*>(prow + kb * 16384 + ((cc ^ (row & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (e == 0) mbar_arrive(&bars.p_full);
+    }
+    if (ok) ok = mbar_wait(&bars.o_done, 0, abort_flag, status, KID_ATTN_PREFILL, 8);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      __nv_bfloat16* orow = out + (size_t)(qs + r0 + row) * ldo + (size_t)h * TC_HD;
+#pragma unroll
+      for (int c = 0; c < TC_HD; c += 16) {
+        uint32_t r[16];
+        tmem_ld_x16(tmem_o + lane_base + c, r);
+        tmem_ld_wait();
+        if (live) {
+          uint4 o0, o1;
+          o0.x = pack_bf16x2(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          o0.y = pack_bf16x2(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          o0.z = pack_bf16x2(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          o0.w = pack_bf16x2(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          o1.x = pack_bf16x2(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+          o1.y = pack_bf16x2(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+          o1.z = pack_bf16x2(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+          o1.w = pack_bf16x2(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+          *reinterpret_cast<uint4*>(orow + c) = o0;
+          *reinterpret_cast<uint4*>(orow + c + 8) = o1;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (bars.abort_flag) {
+    const uint64_t t0w = globaltimer_ns();
+    while (globaltimer_ns() - t0w < 200000ull) { __nanosleep(1000); }
+  }
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+}  // namespace ff
+using namespace ff;
+
+// Same contract as ff_attn_prefill (attention_paged.cu). q: packed rows [rows, ldq] with head h at columns h*128;
+// out rows 16-byte aligned (ldo % 8 == 0). window > 0 sliding, 0 causal, < 0 bidirectional.
+FF_EXPORT int ff_attn_prefill_tc(const void* q, const void* kcache, const void* vcache, const int* block_table,
+                                 const int* q_start, const int* q_lens, const int* ctx_lens, void* out, int batch,
+                                 int total_rows, int max_q_len, int hq, int hkv, int head_dim, int ldq, int ldo,
+                                 int max_blocks, int num_blocks, float scale, int window, int* status, cudaStream_t s) {
+  if (head_dim != TC_HD || batch <= 0 || max_q_len <= 0 || hq <= 0 || hkv <= 0 || hq % hkv || total_rows <= 0) return FF_HOST_BAD_SHAPE;
+  if (ldq % 8 || ldo % 8 || (reinterpret_cast<uintptr_t>(out) & 15)) return FF_HOST_BAD_ALIGN;
+  CUtensorMap tmQ, tmK, tmV;
+  if (int r = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)ldq, (uint64_t)total_rows,
+                           (uint64_t)ldq * 2, 64, TC_BM)) return r;
+  const uint64_t cache_rows = (uint64_t)num_blocks * hkv * TC_PAGE;
+  if (int r = make_tmap_2d(&tmK, kcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, TC_HD, cache_rows, TC_HD * 2, 64, TC_PAGE)) return r;
+  if (int r = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, TC_HD, cache_rows, TC_HD * 2, 64, TC_PAGE)) return r;
+  if (int r = opt_in_smem(attn_prefill_tc_kernel, TC_SMEM)) return r;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid((max_q_len + TC_BM - 1) / TC_BM, hq, batch);
+  attn_prefill_tc_kernel<<<grid, 192, TC_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
+                                                    (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
+                                                    window < 0 ? 0 : window, window < 0 ? 0 : 1, status);
+  return launch_result();
+}
