@@ -57,7 +57,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                        int max_blocks, int num_blocks, float scale_log2, int window, int causal, int* status) {
   const int b = blockIdx.z, h = blockIdx.y;
   const int qlen = q_lens[b];
-  const int r0 = blockIdx.x * TC_BM;
+  // later query tiles of a causal prefill see more keys: they are scheduled first so that the long CTAs do not form the tail
+  const int r0 = (gridDim.x - 1 - blockIdx.x) * TC_BM;
   if (r0 >= qlen) return;
   extern __shared__ uint8_t smem_raw[];
   __shared__ TcBars bars;
@@ -122,7 +123,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           tma_load_2d(sV + 16384 + pg * 8192, &tmV, &bars.kv_full[s], 64, row);
         }
       }
-      if (bad) set_status(status, KID_ATTN_PREFILL, FF_ERR_BOUNDS, b, blockIdx.x);
+      if (bad) set_status(status, KID_ATTN_PREFILL, FF_ERR_BOUNDS, b, r0 / TC_BM);
     }
   } else if (warp == 1) {
     // ================================ MMA issuer ================================
