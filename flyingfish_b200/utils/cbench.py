@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 NVLINK_GBS = 770.0          # measured peer copy, per direction per GPU
+NVLINK_NOMINAL_GBS = 900.0  # NVLink 5 nominal, per direction per GPU: fractions are reported against both
 ROOT = Path(__file__).resolve().parents[2]
 
 
@@ -90,9 +91,11 @@ def main() -> None:
     def report(name, shape, t_us, flops, hbm_bytes, nvl_bytes, t_unfused):
         t_c, t_h, t_n = flops / (pk["tflops"] * 1e6), hbm_bytes / (pk["hbm_gbs"] * 1e3), nvl_bytes / (NVLINK_GBS * 1e3)
         roof = max(t_c, t_h, t_n)
+        roof900 = max(t_c, t_h, nvl_bytes / (NVLINK_NOMINAL_GBS * 1e3))
         rows.append({"kernel": name, "shape": shape, "world": world, "us": round(t_us, 2), "unfused_us": round(t_unfused, 2),
                      "roof_us": round(roof, 2), "bound": ["tensor", "hbm", "nvlink"][[t_c, t_h, t_n].index(roof)],
-                     "frac_of_roofline": round(roof / t_us, 3), "speedup_vs_unfused": round(t_unfused / t_us, 2),
+                     "frac_of_roofline": round(roof / t_us, 3), "frac_of_roofline_900": round(roof900 / t_us, 3),
+                     "speedup_vs_unfused": round(t_unfused / t_us, 2),
                      "peaks": pk["source"]})
 
     # ---- decode: row-parallel projection + all-reduce ---------------------------------------
