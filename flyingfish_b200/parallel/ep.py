@@ -48,10 +48,18 @@ class EPComm:
         import torch.distributed._symmetric_memory as symm
         lib = oplib.kernels()
         lib.ff_ep_arena_layout.restype = c_longlong
-        # worst case every rank sends all its assignments to one owner; 2x the balanced share is
-        # the default budget, overflow is reported through the status word
-        cap = max(256, 2 * max_rows * top_k + 16 * self.El)
+        # Real routers are skewed, so the receive buffers are sized for the worst case -- every rank sends all of its
+        # assignments to this owner -- whenever that fits the byte budget (FF_EP_ARENA_MAX_GIB, default 4 GiB for the
+        # two row buffers; decode batches and the benchmark prefill chunks do). Only beyond it the budget falls back
+        # to a multiple of the balanced share (at least 2x), and an overflow is reported through the status word.
+        import os
+        budget = float(os.environ.get("FF_EP_ARENA_MAX_GIB", "4")) * (1 << 30)
+        balanced = max_rows * top_k
+        worst = self.size * balanced
+        fit = int(budget // (2 * self.hidden * 2))
+        cap = max(256, min(worst, max(2 * balanced, fit)) + 16 * self.El)
         cap = (cap + 15) // 16 * 16
+        self.capacity_is_worst_case = cap >= worst + 16 * self.El
         offs = [c_longlong(0) for _ in range(4)]
         total = lib.ff_ep_arena_layout(self.size, self.E, self.hidden, cap, *[ctypes.byref(o) for o in offs])
         self.buf = symm.empty(int(total), dtype=torch.uint8, device=self.device)
