@@ -27,7 +27,7 @@ Three arms (``--impl``):
 
 The weights read per step (16 GB at N=1) are far larger than the 126 MB L2, so no explicit L2
 flush is needed between steps. SM clocks and throttle reasons are sampled with nvidia-smi every
-20 ms from before the warm-up on; the samples that fall inside each timed region are summarised.
+10 ms from before the warm-up on; the samples that fall inside each timed region are summarised.
 """
 from __future__ import annotations
 
@@ -98,7 +98,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, gpu_index: int, period_ms: int = 20):
+    def __init__(self, gpu_index: int, period_ms: int = 10):
         self.gpu, self.period_ms = gpu_index, period_ms
         self.proc = None
         self.samples: list[tuple[float, float, float, tuple[str, ...]]] = []
@@ -173,6 +173,8 @@ class Ctx:
         self.device = torch.device("cuda", self.local_rank) if self.on_gpu else torch.device("cpu")
         if self.world > 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            # NCCL's own log lines (version banner) go to stderr: stdout carries exactly one JSON line
+            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
             dist.init_process_group("nccl" if self.on_gpu else "gloo", device_id=self.device if self.on_gpu else None)
         self.sampler = ClockSampler(self.local_rank)
         if self.on_gpu:
