@@ -37,6 +37,7 @@ struct PeerArena {
   long long half_bytes;         // bytes of one parity half of the data area
   long long slot_bytes;         // bytes of one source-rank slot inside a half
   uint8_t* mc_base;             // NVLS multicast mapping of the same arena (null: plain peer stores only)
+  int mc_oneshot;               // with mc_base: every rank multicasts its partial to all ranks (one flag round) and sums locally
 };
 
 __device__ __forceinline__ int* arena_epoch(const PeerArena& a) { return reinterpret_cast<int*>(a.base[a.rank]); }

@@ -65,6 +65,12 @@ struct TileSink {
       for (int j = 0; j < 8 && col + j < N; ++j) dst[j] = ob[j];
     } else {
       // N % 8 == 0 and 16-byte aligned slots are checked by the host
+      if (ar.mc_base != nullptr && ar.mc_oneshot) {
+        // NVLS one-shot: ONE multicast store puts the contribution into this rank's slot on every rank
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, ar.rank, parity, ar.rank)) + (size_t)t * N + col;
+        multimem_st_bf16x8(arena_mc(ar, dst), o);
+        return;
+      }
       if (ar.mc_base != nullptr) {
         // NVLS: the contribution stays in this rank's own slot 0; the switch sums the ranks' copies
         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(arena_slot(ar, ar.rank, parity, 0)) + (size_t)t * N + col;
@@ -85,7 +91,7 @@ struct TileSink {
 __device__ __forceinline__ void allreduce_tile(const TileSink<true>& sink, int M, int tile, int tile_rows, int flag_idx,
                                                int row0, int row_step, int e, SkinnyBars& bars, int ar_epoch, int* status) {
   const PeerArena& ar = sink.ar;
-  if (ar.mc_base != nullptr) {
+  if (ar.mc_base != nullptr && !ar.mc_oneshot) {
     // ---- NVLS two-shot: every rank flags its contribution on all ranks with one multicast store; the owner of
     // this chunk (flag_idx % world) lets the switch sum the ranks' copies (multimem.ld_reduce, FP32 accumulate) and
     // multicasts the BF16 result into slot 1 of every rank, then flags it; every rank copies its result to Y.
@@ -141,12 +147,18 @@ __device__ __forceinline__ void allreduce_tile(const TileSink<true>& sink, int M
   asm volatile("bar.sync 1, 128;" ::: "memory");
   if (e == 0) {
     __threadfence_system();
-    for (int pi = 1; pi < ar.world; ++pi)
-      st_release_sys(arena_flag(ar, (ar.rank + pi) % ar.world, ar.rank, flag_idx), ar_epoch);
+    if (ar.mc_base != nullptr) {
+      // NVLS one-shot: one release store flags every rank (the data went out as multicast stores too)
+      multimem_st_release(arena_mc(ar, arena_flag(ar, ar.rank, ar.rank, flag_idx)), ar_epoch);
+    } else {
+      for (int pi = 1; pi < ar.world; ++pi)
+        st_release_sys(arena_flag(ar, (ar.rank + pi) % ar.world, ar.rank, flag_idx), ar_epoch);
+    }
     bars.flag_b = 1;
   }
   asm volatile("bar.sync 1, 128;" ::: "memory");
-  if (e < ar.world && e != ar.rank)
+  // with multicast stores this rank's own copy also travels through the switch: its flag is waited for like a peer's
+  if (e < ar.world && (e != ar.rank || ar.mc_base != nullptr))
     if (!wait_flag(arena_flag(ar, ar.rank, e, flag_idx), ar_epoch, status, KID_GEMM_AR, e)) bars.flag_b = 0;
   asm volatile("bar.sync 1, 128;" ::: "memory");
   if (bars.flag_b) {
@@ -807,6 +819,10 @@ FF_EXPORT int ff_gemm_ar(const unsigned long long* ptrs, int rank, int world, lo
   // mc_ptr != 0: the arena's NVLS multicast mapping; the exchange then goes through the switch (two-shot)
   a.mc_base = reinterpret_cast<uint8_t*>(mc_ptr);
   if (mc_ptr != 0 && world < 2) a.mc_base = nullptr;
+  // one-shot (default): every rank multicasts its partial (multimem.st) and one flag, then sums all slots locally: one
+  // flag round instead of the two of the reduce-in-the-switch exchange (FF_NVLS_ONESHOT=0 selects that one)
+  static const int oneshot = [] { const char* ev = getenv("FF_NVLS_ONESHOT"); return (ev && ev[0] == '0') ? 0 : 1; }();
+  a.mc_oneshot = a.mc_base != nullptr ? oneshot : 0;
   return gemm_skinny_launch(X, W, Y, M, N, K, ldx, ldw, ldy, grid, scratch, counters, status, stream, &a);
 }
 

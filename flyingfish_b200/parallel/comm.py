@@ -97,15 +97,18 @@ class TPComm:
         self.fused = arena is not None
         self.stats = {"gemm_ar": 0, "oneshot_ar": 0, "nccl_ar": 0, "ag_gemm": 0, "gemm_rs": 0}
         self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=device) if arena is not None else None
-        # NVLS: the fused GEMM + all-reduce can exchange through the switch (multimem ld_reduce / st, two flag
-        # rounds) when the arena has a multicast mapping. Measured on the decode step of the 8-B shape: at two
-        # ranks the one-shot exchange over plain peer stores wins (33 us against 45 us per projection, 5.05 ms
-        # against 5.78 ms per step) and at four (4.59 against 4.92 ms), at eight ranks the switch path wins (4.11 ms against 4.97 ms per step: a
-        # rank no longer stores to seven peers and reads seven partials). FLYINGFISH_NVLS=auto (default): on
-        # from eight ranks; 1 / 0 force it. Always off with NCCL_NVLS_ENABLE=0 (tests in which a rank may leave
-        # run on plain peer stores: a rank that dies while bound to a multicast object faults its peers).
+        # NVLS: when the arena has a multicast mapping the fused GEMM + all-reduce exchanges through the switch. Two
+        # forms (FF_NVLS_ONESHOT): one-shot (default) -- every rank multicasts its partial tile and one flag with
+        # multimem.st, then sums all slots locally: one flag round, one store per value instead of world-1; two-shot
+        # (=0) -- partials stay local, the owner of a chunk sums them inside the switch (multimem.ld_reduce) and
+        # multicasts the result: two flag rounds. Measured per projection at M 64 (o_proj / down) and per decode step of
+        # the 8-B shape: 8 ranks: one-shot 35 / 38 us and 3.56 ms, two-shot 46 / 49 us and 4.13 ms, plain peer stores
+        # 68 / 62 us and 4.97 ms (GEMM + NCCL all-reduce: 47-68 us); 2 ranks: one-shot 32 / 41 us = plain peer stores
+        # 32 / 40 us, two-shot 44 / 54 us. FLYINGFISH_NVLS=auto (default): on from four ranks; 1 / 0 force it. Always
+        # off with NCCL_NVLS_ENABLE=0 (tests in which a rank may leave run on plain peer stores: a rank that dies while
+        # bound to a multicast object faults its peers).
         mode = os.environ.get("FLYINGFISH_NVLS", "auto")
-        want = mode == "1" or (mode == "auto" and self.size >= 8)
+        want = mode == "1" or (mode == "auto" and self.size >= 4)
         self.nvls = bool(arena is not None and arena.multicast_ptr and want
                          and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0")
         # Sequence-parallel prefill pair (all-gather -> GEMM, GEMM -> reduce-scatter): the one-kernel forms win at

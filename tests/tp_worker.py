@@ -34,7 +34,7 @@ def main():
     from flyingfish_b200 import ops
     comm = TPComm.create(dist.group.WORLD, device, slot_bytes=8 << 20)
     # routing chosen by world size: one-kernel prefill pair up to four ranks, switch-side all-reduce from eight
-    assert comm.sp_fused == (comm.size <= 4) and (not comm.nvls or comm.size >= 8)
+    assert comm.sp_fused == (comm.size <= 4) and (not comm.nvls or comm.size >= 4)
     result = {}
     if args.mode == "model":
         m = Model.load("tiny-llama", Settings(capacity=256, max_batch=4, graph=(args.device == "cuda")), device=device,
