@@ -157,6 +157,21 @@ class PagedKVCache:
         s = self.seqs[seq_id]
         bs = self.block_size
         dev = self.device
+        if dev.type == "cuda" and self.k[0].dtype == torch.bfloat16 and self.head_dim % 8 == 0 and \
+                (self.v[0] is None or self.v[0].shape == self.k[0].shape):
+            # two launches for all layers and both tensors (csrc/kv_util.cu)
+            from ..ops.lib import check, kernels, ptr, status_tensor, stream_ptr
+            if getattr(self, "_cache_ptrs", None) is None:
+                ptrs = [t.data_ptr() for layer in range(self.layers) for t in (self.k[layer], self.v[layer]) if t is not None]
+                self._cache_ptrs = torch.tensor(ptrs, dtype=torch.int64, device=dev)
+            n, tensors = len(src_positions), self._cache_ptrs.numel()
+            slot = lambda ps: torch.tensor([s.blocks[p // bs] * bs + p % bs for p in ps], dtype=torch.int32, device=dev)
+            staging = torch.empty(n * tensors * self.kv_heads * self.head_dim, dtype=torch.bfloat16, device=dev)
+            rc = kernels().ff_kv_move_rows(ptr(self._cache_ptrs), tensors, ptr(slot(src_positions)), ptr(slot(dst_positions)), n,
+                                           ptr(staging), self.kv_heads, bs, self.head_dim, self.k[0].shape[0],
+                                           ptr(status_tensor(dev)), stream_ptr())
+            check(rc, "ff_kv_move_rows")
+            return
         sb = torch.tensor([s.blocks[p // bs] for p in src_positions], device=dev)
         so = torch.tensor([p % bs for p in src_positions], device=dev)
         db = torch.tensor([s.blocks[p // bs] for p in dst_positions], device=dev)

@@ -331,3 +331,29 @@ def test_attn_decode_sliding_window(window):
     full = ops.attn_decode(q, kc, vc, bt, ctx, hq, hkv, d, d ** -0.5)
     if window < 200:
         assert not torch.allclose(want[0].float(), full[0].float(), atol=1e-3)      # the window really hides keys
+
+
+def test_kv_move_rows_kernel_matches_indexing():
+    """Compaction of tree-verification rows: the two-launch kernel over all layers equals gather-then-scatter by tensor
+    indexing, also when source and destination positions overlap."""
+    from flyingfish_b200.engine.kv_cache import PagedKVCache
+    dev = torch.device("cuda", 0)
+    kv = PagedKVCache(3, 2, 128, 8, 64, torch.bfloat16, dev)
+    g = torch.Generator().manual_seed(9)
+    for l in range(3):
+        kv.k[l].copy_(torch.randn(kv.k[l].shape, generator=g).to(torch.bfloat16))
+        kv.v[l].copy_(torch.randn(kv.v[l].shape, generator=g).to(torch.bfloat16))
+    kv.add_sequence(0)
+    kv.reserve(0, 150); kv.commit(0, 150)
+    src, dst = [70, 71, 75, 130, 64], [64, 65, 66, 67, 68]          # 64 is both read and written
+    want_k = [t.clone() for t in kv.k]; want_v = [t.clone() for t in kv.v]
+    blocks = kv.seqs[0].blocks
+    for cache in want_k + want_v:
+        rows = torch.stack([cache[blocks[p // 64], :, p % 64, :].clone() for p in src])
+        for i, p in enumerate(dst):
+            cache[blocks[p // 64], :, p % 64, :] = rows[i]
+    kv.move_rows(0, src, dst)
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    for l in range(3):
+        assert torch.equal(kv.k[l], want_k[l]) and torch.equal(kv.v[l], want_v[l])
