@@ -382,7 +382,8 @@ class Engine:
             raise
 
     # -- speculative verification --------------------------------------------------------------
-    def verify(self, seqs: list[Sequence], drafts: list[list[int]], return_hidden: bool = False):
+    def verify(self, seqs: list[Sequence], drafts: list[list[int]], return_hidden: bool = False,
+               device_out: bool = False):
         """Feed every sequence's pending token plus its draft tokens (same count k for all) through
         the target in ONE forward of k+1 rows per sequence and return the target's greedy token
         after each row: ``[[t_0 .. t_k]]`` per sequence. Nothing is committed; call
@@ -418,6 +419,10 @@ class Engine:
             fb.upload()
             n = self.model.hidden_states(fb, self.kv)
             out = self.model.greedy(self.model.logits(n, fb))
+            if device_out:
+                # the caller decides acceptance on the device and reads one verdict back (then calls _after_sync)
+                self.stats["verify_rows"] = self.stats.get("verify_rows", 0) + rows
+                return out
             toks = [int(t) for t in out.cpu().tolist()]
             self._after_sync()
             self.stats["verify_rows"] = self.stats.get("verify_rows", 0) + rows

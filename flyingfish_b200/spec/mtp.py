@@ -121,10 +121,10 @@ class MtpSpeculator:
                 is_decode=False)
         fb.upload()
         w, spec = self.w, self.net.spec
-        emb = ops.embed(fb.ids, self.w.layer.embed)
-        e = ops.rmsnorm(emb, w.enorm, spec.rms_eps)
-        hn = ops.rmsnorm(hidden.contiguous(), w.hnorm, spec.rms_eps)
-        x0 = ops.linear(torch.cat([e, hn], dim=1).contiguous(), w.eh_proj)
+        # [norm(embedding) | norm(previous hidden)] in one launch, then the mixing projection
+        from ..ops import spec_ops
+        x0 = ops.linear(spec_ops.mtp_mix(fb.ids, self.w.layer.embed, hidden.contiguous(), w.enorm, w.hnorm, spec.rms_eps),
+                        w.eh_proj)
         n = self.net.hidden_states(fb, self.kv, inputs_embeds=x0)
         toks = self.net.greedy(self.net.logits(n, fb))
         self.kv.commit(0, commit)
@@ -198,14 +198,20 @@ class MtpSpeculator:
         sink: list = []
         te.model.normed_sink = sink
         try:
-            target_toks = te.verify([ts], [drafts])[0]
+            target_dev = te.verify([ts], [drafts], device_out=True)         # int32 [k + 1], still on the device
         except Exception:
             self.kv.truncate(0, base)
             raise
         finally:
             te.model.normed_sink = None
         true_h = sink[0]                                     # [k+1, hidden]
-        acc = accept_chain(drafts, target_toks, eos, ignore_eos)
+        # acceptance on the device; one small read-back carries the verdict
+        from ..ops import spec_ops
+        from .accept import Accepted
+        d_dev = torch.tensor([drafts], dtype=torch.int32, device=target_dev.device)
+        verdict = spec_ops.accept_chain(d_dev, target_dev.view(1, -1).to(torch.int32), eos, ignore_eos)[0].cpu().tolist()
+        te._after_sync()
+        acc = Accepted(verdict[3: 3 + verdict[1]], verdict[0], bool(verdict[2]))
         if self.fault is Fault.COMMIT:
             self.kv.truncate(0, base)
             raise SpecFault("injected commit failure")

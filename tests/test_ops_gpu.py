@@ -357,3 +357,33 @@ def test_kv_move_rows_kernel_matches_indexing():
     ops.check_status(dev)
     for l in range(3):
         assert torch.equal(kv.k[l], want_k[l]) and torch.equal(kv.v[l], want_v[l])
+
+
+def test_mtp_mix_and_device_accept_match_oracles():
+    from flyingfish_b200.ops import spec_ops
+    from flyingfish_b200.spec.accept import accept_chain
+    g = torch.Generator().manual_seed(4)
+    rows, h, vocab = 9, 1024, 500
+    table = torch.randn(vocab, h, generator=g).to(torch.bfloat16)
+    hidden = torch.randn(rows, h, generator=g).to(torch.bfloat16)
+    en = (1 + 0.1 * torch.randn(h, generator=g)).to(torch.bfloat16)
+    hn = (1 + 0.1 * torch.randn(h, generator=g)).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (rows,), generator=g).to(torch.int32)
+    want = spec_ops.mtp_mix(ids, table, hidden, en, hn, 1e-6).float()
+    got = spec_ops.mtp_mix(ids.cuda(), table.cuda(), hidden.cuda(), en.cuda(), hn.cuda(), 1e-6).float().cpu()
+    assert (want - got).abs().max().item() <= 2e-2
+    # acceptance: every prefix length, with and without an end-of-sequence token inside the accepted prefix
+    k = 4
+    drafts, targets = [], []
+    for n_match in range(k + 1):
+        d = [10 + j for j in range(k)]
+        t = [10 + j for j in range(n_match)] + [99] * (k + 1 - n_match)
+        drafts.append(d); targets.append(t)
+    drafts.append([10, 7, 12, 13]); targets.append([10, 7, 12, 13, 14])          # 7 is an end-of-sequence id
+    dd, tt = torch.tensor(drafts, dtype=torch.int32), torch.tensor(targets, dtype=torch.int32)
+    for ignore in (True, False):
+        out = spec_ops.accept_chain(dd.cuda(), tt.cuda(), (7,), ignore).cpu().tolist()
+        for b, row in enumerate(out):
+            a = accept_chain(drafts[b], targets[b], (7,), ignore)
+            assert row[0] == a.n_draft_accepted and row[1] == len(a.tokens) and bool(row[2]) == a.hit_eos
+            assert row[3: 3 + row[1]] == a.tokens
