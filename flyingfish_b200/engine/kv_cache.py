@@ -167,7 +167,8 @@ class PagedKVCache:
             n, tensors = len(src_positions), self._cache_ptrs.numel()
             slot = lambda ps: torch.tensor([s.blocks[p // bs] * bs + p % bs for p in ps], dtype=torch.int32, device=dev)
             staging = torch.empty(n * tensors * self.kv_heads * self.head_dim, dtype=torch.bfloat16, device=dev)
-            rc = kernels().ff_kv_move_rows(ptr(self._cache_ptrs), tensors, ptr(slot(src_positions)), ptr(slot(dst_positions)), n,
+            src_slots, dst_slots = slot(src_positions), slot(dst_positions)       # both alive until the launches are queued
+            rc = kernels().ff_kv_move_rows(ptr(self._cache_ptrs), tensors, ptr(src_slots), ptr(dst_slots), n,
                                            ptr(staging), self.kv_heads, bs, self.head_dim, self.k[0].shape[0],
                                            ptr(status_tensor(dev)), stream_ptr())
             check(rc, "ff_kv_move_rows")
