@@ -5,7 +5,8 @@ subcommand (``ff --model M generate --prompt ...``), ``--model`` falls back to
 ``FLYINGFISH_MODEL``, results are one JSON object on stdout, decisions are JSON lines on stderr.
 Subcommands: calibrate, generate, serve, bench, profile, inspect, tokenize, embed, verify,
 compare-prefill, compare-log, plus the speculative-decoding tools (verify-spec, bench-spec,
-profile-spec). ``--model`` accepts a checkpoint directory or one of the named random-init shapes
+profile-spec for MTP; replay-draft, replay-tree, check-tree-greedy, compare-tree-builders,
+compare-tree-padding, compare-spec-graph for a draft model). ``--model`` accepts a checkpoint directory or one of the named random-init shapes
 (``ff inspect --shapes`` lists them).
 
 Writes never go inside a model directory or under a path component named ``models`` and never
@@ -22,6 +23,10 @@ import time
 from pathlib import Path
 
 from .config import NAMED_SHAPES, Settings
+
+
+DSPARK_TOOLS = ("replay-draft", "replay-tree", "check-tree-greedy", "compare-tree-builders", "compare-tree-padding",
+                "compare-spec-graph")
 
 
 def _global_parser() -> argparse.ArgumentParser:
@@ -104,6 +109,13 @@ def _global_parser() -> argparse.ArgumentParser:
     cl.add_argument("--a", required=True)
     cl.add_argument("--b", required=True)
 
+    for name in DSPARK_TOOLS:
+        dp = sub.add_parser(name)
+        dp.add_argument("--prompt-tokens", type=int, default=48)
+        dp.add_argument("--max-new-tokens", type=int, default=24)
+        dp.add_argument("--trace", help="replay tools: trace file to write (first run) or to reproduce (later runs)")
+        dp.add_argument("--strict", action="store_true")
+
     for name in ("verify-spec", "bench-spec", "profile-spec"):
         sp = sub.add_parser(name)
         sp.add_argument("--prompt-tokens", type=int, default=64)
@@ -172,10 +184,14 @@ def check_flags(args) -> None:
         raise SystemExit("--tp needs one CUDA device per rank")
     if args.tp > 1 and args.command not in ("generate", "bench", "serve"):
         raise SystemExit(f"--tp applies to generate, bench and serve, not to {args.command}")
-    if args.draft_model and args.command != "generate":
-        raise SystemExit("--draft-model applies to generate")
+    if args.command in DSPARK_TOOLS and not args.draft_model:
+        raise SystemExit(f"{args.command} needs --draft-model")
+    if args.draft_model and args.command != "generate" and args.command not in DSPARK_TOOLS:
+        raise SystemExit("--draft-model applies to generate and the draft-model tools")
     if args.draft_model and args.tp > 1:
         raise SystemExit("--draft-model with --tp is not supported")
+    if args.command in ("check-tree-greedy", "replay-tree", "compare-tree-builders") and args.spec_budget == "chain":
+        args.spec_budget = "tree16"
     if args.spec_budget != "chain" and not args.draft_model:
         raise SystemExit("--spec-budget needs --draft-model")
     if args.prefix_cache and args.command != "generate":
@@ -458,6 +474,20 @@ def cmd_spec(args) -> dict:
     return run_spec_tool(args.command, model, args.prompt_tokens, args.max_new_tokens, args.mtp, args.strict)
 
 
+def cmd_dspark(args) -> dict:
+    from .api import Model
+    from .spec.drivers import run_dspark_tool
+    if getattr(args, "trace", None) and not Path(args.trace).exists():
+        check_output_path(args.trace, args.model)
+    model = _load(args)
+    st = settings_from(args)
+    st.graph = bool(args.spec_graph)
+    draft = Model.load(args.draft_model, st, device=str(model.engine.device), seed=args.seed + 1)
+    budget = args.spec_budget if args.spec_budget != "chain" else "tree16"
+    return run_dspark_tool(args.command, model, draft, args.prompt_tokens, args.max_new_tokens, budget=budget,
+                           builder=args.tree_builder, trace_path=getattr(args, "trace", None), strict=args.strict)
+
+
 def main(argv: list[str] | None = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     args = _global_parser().parse_args(argv)
@@ -468,7 +498,7 @@ def main(argv: list[str] | None = None) -> int:
     handlers = {"generate": cmd_generate, "bench": cmd_bench, "profile": cmd_profile, "inspect": cmd_inspect,
                 "tokenize": cmd_tokenize, "calibrate": cmd_calibrate, "embed": cmd_embed, "verify": cmd_verify,
                 "compare-prefill": cmd_verify, "compare-log": cmd_compare_log, "verify-spec": cmd_spec,
-                "bench-spec": cmd_spec, "profile-spec": cmd_spec}
+                "bench-spec": cmd_spec, "profile-spec": cmd_spec, **{t: cmd_dspark for t in DSPARK_TOOLS}}
     if args.command == "serve":
         cmd_serve(args)
         return 0

@@ -304,3 +304,26 @@ def _driver_rank(rank, port, q):
         follow(eng, dist.group.WORLD)
         q.put((1, [outs[k] for k in sorted(outs)]))
     dist.destroy_process_group()
+
+
+def test_draft_model_tools(capsys, tmp_path):
+    """The draft-model tools: each reports that speculation leaves greedy decoding unchanged; the replay tools write a
+    trace on the first run and reproduce it on the second."""
+    base = BASE + ["--draft-model", "tiny-llama"]
+    small = ["--prompt-tokens", "20", "--max-new-tokens", "10"]
+    out = _run(base + ["check-tree-greedy"] + small + ["--strict"], capsys)
+    assert out["identical_to_greedy"] and out["budget"] == "tree16" and out["rounds"] > 0
+    out = _run(base + ["compare-tree-builders"] + small, capsys)
+    assert out["identical_to_greedy"] and set(out["builders"]) == {"waves", "serial"}
+    out = _run(base + ["compare-tree-padding"] + small, capsys)
+    assert out["identical_to_greedy"] and [out["budgets"][b]["rows"] for b in ("tree16", "tree32", "tree64")] == [16, 32, 64]
+    out = _run(base + ["compare-spec-graph"] + small, capsys)
+    assert out["identical"] and out["identical_to_greedy"]
+    for tool in ("replay-draft", "replay-tree"):
+        trace = tmp_path / f"{tool}.json"
+        first = _run(base + [tool] + small + ["--trace", str(trace)], capsys)
+        assert first["identical_to_greedy"] and first["trace_written"] == str(trace)
+        second = _run(base + [tool] + small + ["--trace", str(trace)], capsys)
+        assert second["replay_matches_trace"] is True
+    with pytest.raises(SystemExit):
+        cli.main(BASE + ["check-tree-greedy"])            # needs a draft model
