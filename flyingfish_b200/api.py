@@ -74,7 +74,12 @@ class Model:
             name = path.name
         else:
             spec = preset if preset is not None else (read_model_spec(path) if path.is_dir() else named_shape(model))
-            if spec.mla is not None:
+            if spec.extra.get("v41"):
+                from .models.deepseek_v41 import build_v41_weights
+                from .models.weights import DTYPES, synthetic_source
+                weights = build_v41_weights(spec, seed, device, synthetic_source(spec, seed, device, DTYPES[spec.dtype]),
+                                            tp, epi)
+            elif spec.mla is not None:
                 from .models.deepseek import build_deepseek_weights
                 from .models.weights import DTYPES, synthetic_source
                 weights = build_deepseek_weights(spec, synthetic_source(spec, seed, device, DTYPES[spec.dtype]),
@@ -89,6 +94,10 @@ class Model:
         if spec.mla is not None:
             from .models.deepseek import DeepseekModel
             net = DeepseekModel(weights, comm=comm)
+        elif spec.extra.get("v41"):
+            from .models.deepseek_v41 import DeepseekV41Model
+            net = DeepseekV41Model(weights, comm=comm, max_sequences=settings.max_batch, max_len=settings.capacity,
+                                   max_chunk=min(settings.chunk or 256, 256), seed=seed)
         elif spec.extra.get("gemma"):
             from .models.gemma import GemmaModel
             net = GemmaModel(weights, comm=comm, seed=seed)

@@ -20,7 +20,7 @@ class MoeSpec:
     num_experts: int
     top_k: int
     expert_ffn: int
-    score: str = "softmax"            # softmax | sigmoid | noaux | sqrtsoftplus
+    score: str = "softmax"            # softmax | sigmoid | noaux | sqrt_softplus
     n_shared: int = 0                 # shared experts (each of width shared_ffn)
     shared_ffn: int = 0
     n_groups: int = 1
@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | deepseek_v41 | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
     layers: int
     hidden: int
     heads: int
@@ -225,10 +225,25 @@ def tiny_gemma() -> ModelSpec:
     return spec
 
 
+def deepseek_v41_tiny() -> ModelSpec:
+    """Small DeepSeek-V4.1-style shape: four hyper-connection streams, a latent mixer with an FP8 window ring (window 32),
+    one top-k sparse layer with a pooled indexer, n-gram memory rows in the first layer, shared + routed experts with
+    square-root-soft-plus routing after a dense first layer."""
+    return ModelSpec(
+        name="deepseek-v41-tiny", arch="deepseek_v41", layers=3, hidden=256, heads=4, kv_heads=1, head_dim=128, ffn=512,
+        vocab=2048, rope_theta=1e4, rms_eps=1e-6,
+        moe=MoeSpec(num_experts=8, top_k=2, expert_ffn=128, score="sqrt_softplus", n_shared=1, shared_ffn=128,
+                    routed_scaling=1.5, first_dense_layers=1, dense_ffn=512),
+        extra={"v41": {"hc_mult": 4, "hc_iters": 3, "hc_eps": 1e-6, "q_lora": 128, "rope_tail": 32, "window": 32,
+                       "o_groups": 2, "o_rank": 128, "sparse_layers": [1], "index_topk": 4,
+                       "engram": {"layers": [0], "ngram": 3, "heads": 2, "compressed_vocab": 512, "table_rows": 509,
+                                  "cache_rows": 256}}})
+
+
 NAMED_SHAPES = {
     "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
-    "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini,
+    "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini, "deepseek-v41-tiny": deepseek_v41_tiny,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }
 

@@ -73,11 +73,16 @@ class Engine:
         if spec.mla is not None:       # one latent row per token: [kv_lora | rope key], no separate V
             self.kv = PagedKVCache(spec.layers, 1, spec.mla.kv_lora_rank + spec.mla.qk_rope_dim, num_blocks,
                                    settings.kv_block, dtype, self.device, v_head_dim=0)
+        elif getattr(model, "owns_token_state", False):
+            # the model keeps its per-token state itself (latent rings, sparse tables): the block cache only accounts
+            # for positions and capacity
+            self.kv = PagedKVCache(spec.layers, 1, 8, num_blocks, settings.kv_block, dtype, self.device, v_head_dim=0)
         else:
             self.kv = PagedKVCache(spec.layers, hkv, spec.head_dim, num_blocks, settings.kv_block, dtype, self.device)
         self.max_blocks = (settings.capacity + settings.kv_block - 1) // settings.kv_block
         self.max_batch = max(settings.max_batch, 1)
         self.max_prefill_rows = max_prefill_rows
+        self.take_limit = getattr(model, "prefill_take_limit", None) or max_prefill_rows   # rows of ONE sequence per chunk
         self.prefill_batch = ForwardBatch(BatchLayout(self.max_batch, max(max_prefill_rows, self.max_batch),
                                                       self.max_blocks), self.device)
         self.graphs: dict[tuple[int, int], _Graph] = {}
@@ -164,7 +169,7 @@ class Engine:
                 for s in pending:
                     if rows_left <= 0 or len(part) >= self.max_batch:
                         break
-                    take = min(len(s.prompt) - s.prefilled, rows_left)
+                    take = min(len(s.prompt) - s.prefilled, rows_left, self.take_limit)
                     part.append((s, take))
                     rows_left -= take
                 toks = self._prefill_chunk(part)
@@ -193,7 +198,7 @@ class Engine:
             rem = len(s.prompt) - s.prefilled
             if rem <= 0:
                 continue
-            take = min(rem, rows_left)
+            take = min(rem, rows_left, self.take_limit)
             part.append((s, take))
             rows_left -= take
         if not part:

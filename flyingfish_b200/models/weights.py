@@ -195,7 +195,7 @@ def build_decoder_weights(spec: ModelSpec, source: TensorSource, device: torch.d
             lw.wdown = source(p + "mlp.down_proj.weight", (h, f))[:, f0:f1].contiguous()
         else:
             lw.router = source(p + "mlp.gate.weight", (moe.num_experts, h))
-            if moe.score == "noaux":
+            if moe.score in ("noaux", "sqrt_softplus"):
                 lw.router_bias = torch.zeros(moe.num_experts, dtype=torch.float32, device=device)
             e0, e1 = shard_range(moe.num_experts, ep.rank, ep.size)
             f = moe.expert_ffn

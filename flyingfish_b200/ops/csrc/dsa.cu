@@ -206,6 +206,28 @@ __global__ void dsa_expand_kernel(const int* __restrict__ selected, const int* _
   }
 }
 
+// Checkpoint of per-token state rows for speculative rollback: save (RESTORE = false) or put back the rows
+// `rows[0 .. n)` of every state table (latent rows, index keys, pooling logits, pooled keys: one base pointer and one
+// row size per table) in a single launch. snapshot layout: [table][n][max_vecs] 16-byte vectors. grid (n, tables).
+// The counterpart of the reference's dsa_checkpoint (kernels/dsa.cu:427-481), which saves and restores the ring slots a
+// draft round overwrites; here the tables are addressed by global row.
+template <bool RESTORE>
+__global__ void dsa_checkpoint_kernel(const unsigned long long* __restrict__ tables, const int* __restrict__ row_vecs,
+                                      const int* __restrict__ table_rows, const int* __restrict__ rows,
+                                      uint4* __restrict__ snap, int max_vecs, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int j = blockIdx.x, c = blockIdx.y;
+  const int r = rows[j];
+  if (r < 0 || r >= table_rows[c]) { if (threadIdx.x == 0) set_status(status, KID_DSA, FF_ERR_BOUNDS, j, r); return; }
+  const int nv = row_vecs[c];
+  uint4* base = reinterpret_cast<uint4*>(tables[c]) + (size_t)r * nv;
+  uint4* sn = snap + ((size_t)c * gridDim.x + j) * max_vecs;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    if (RESTORE) base[i] = sn[i]; else sn[i] = base[i];
+  }
+}
+
 }  // namespace ff
 using namespace ff;
 
@@ -239,4 +261,20 @@ FF_EXPORT int ff_dsa_expand(const int* selected, const int* seq_base, const int*
   if (rows <= 0 || k <= 0 || k > DSA_MAXK) return FF_HOST_BAD_SHAPE;
   if (int lr = launch_pdl(dsa_expand_kernel, dim3(rows), dim3(128), 0, s, 0, selected, seq_base, pos, k, indices)) return lr;
   return launch_result();
+}
+
+// tables / row_vecs / table_rows: device arrays of `n_tables` entries (base pointer, 16-byte vectors per row, rows in
+// the table); rows: device int32[n]; snapshot: n_tables * n * max_vecs * 16 bytes.
+FF_EXPORT int ff_dsa_checkpoint(const unsigned long long* tables, const int* row_vecs, const int* table_rows, int n_tables,
+                                const int* rows, int n, void* snapshot, int max_vecs, int restore, int* status,
+                                cudaStream_t s) {
+  if (n_tables <= 0 || n <= 0 || max_vecs <= 0) return FF_HOST_BAD_SHAPE;
+  if (reinterpret_cast<uintptr_t>(snapshot) & 15) return FF_HOST_BAD_ALIGN;
+  dim3 grid(n, n_tables);
+  const int threads = max_vecs >= 128 ? 128 : 32;
+  if (restore)
+    return launch_pdl(dsa_checkpoint_kernel<true>, grid, dim3(threads), 0, s, 0, tables, row_vecs, table_rows, rows,
+                      static_cast<uint4*>(snapshot), max_vecs, status);
+  return launch_pdl(dsa_checkpoint_kernel<false>, grid, dim3(threads), 0, s, 0, tables, row_vecs, table_rows, rows,
+                    static_cast<uint4*>(snapshot), max_vecs, status);
 }

@@ -92,7 +92,7 @@ latent_window_attention_kernel(const __nv_bfloat16* __restrict__ q, const uint8_
                                const uint8_t* __restrict__ scales, const int* __restrict__ ring_ids,
                                const int* __restrict__ positions, const float* __restrict__ sink,
                                const float* __restrict__ inv_rotary, __nv_bfloat16* __restrict__ out, int heads, int D,
-                               int window, int rings, int rope_tail, float scale, int round_p, int* status,
+                               int window, int visible, int rings, int rope_tail, float scale, int round_p, int* status,
                                const __nv_bfloat16* __restrict__ rows_bf16, const int* __restrict__ indices) {
   pdl_trigger();
   pdl_wait();
@@ -113,8 +113,10 @@ latent_window_attention_kernel(const __nv_bfloat16* __restrict__ q, const uint8_
   if (SRC == 0) {
     const int ring = ring_ids[b], pos = positions[b];
     if (ring < 0 || ring >= rings || pos < 0) { if (tid == 0) set_status(status, KID_LATENT, FF_ERR_BOUNDS, b, ring); return; }
-    nvis = min(pos + 1, window);
-    first = (pos + 1 >= window) ? (pos + 1) % window : 0;
+    // the last `visible` positions up to `pos`; a ring longer than that keeps the rows of later positions of the same
+    // launch (prefill chunks) out of the way of the rows an earlier query still reads
+    nvis = min(pos + 1, visible);
+    first = (pos + 1 - nvis) % window;
     rc = codes + (size_t)ring * window * D;
     rs = scales + (size_t)ring * window * (D / 32);
   } else {
@@ -272,6 +274,28 @@ latent_window_attention_kernel(const __nv_bfloat16* __restrict__ q, const uint8_
   (void)round_p;
 }
 
+// Rotary embedding on the tail of every head: x [rows, heads * D] bf16 (row stride ldx), the adjacent pairs
+// (2p, 2p + 1) of the last `tail` dims of a head are rotated by the angle whose (cos, sin) is cs[row, 2p .. 2p + 1].
+// The forward rotation of the queries and of the latent key row before the ring write (the reference's
+// rope_pair_rows / rope_pair_tail, kernels/rope_kv.cu); the attention kernel above applies the inverse to its output.
+__global__ void rope_pair_tail_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cs, long long rows, int heads,
+                                      int D, int ldx, int tail) {
+  pdl_trigger();
+  pdl_wait();
+  const int half = tail / 2;
+  const long long total = rows * heads * half;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(i % half);
+    const long long rh = i / half;
+    const int h = (int)(rh % heads);
+    const long long row = rh / heads;
+    __nv_bfloat162* ptr = reinterpret_cast<__nv_bfloat162*>(x + row * ldx + (size_t)h * D + (D - tail) + 2 * p);
+    const float2 c = *reinterpret_cast<const float2*>(cs + row * tail + 2 * p);
+    const float2 v = __bfloat1622float2(*ptr);
+    *ptr = __floats2bfloat162_rn(v.x * c.x - v.y * c.y, v.x * c.y + v.y * c.x);
+  }
+}
+
 }  // namespace ff
 using namespace ff;
 
@@ -291,9 +315,10 @@ FF_EXPORT int ff_latent_quant(const void* x, void* codes, void* scales, const in
 
 FF_EXPORT int ff_latent_window_attention(const void* q, const void* codes, const void* scales, const int* ring_ids,
                                          const int* positions, const float* sink, const float* inv_rotary, void* out,
-                                         int batch, int heads, int D, int window, int rings, int rope_tail, float scale,
-                                         int* status, cudaStream_t s) {
+                                         int batch, int heads, int D, int window, int visible, int rings, int rope_tail,
+                                         float scale, int* status, cudaStream_t s) {
   if (batch <= 0 || heads <= 0 || D <= 0 || D % 64 || D > LW_MAXD || window <= 0 || rings <= 0) return FF_HOST_BAD_SHAPE;
+  if (visible <= 0 || visible > window) return FF_HOST_BAD_SHAPE;
   if (rope_tail < 0 || rope_tail > D || rope_tail % 2 || !(scale > 0.f)) return FF_HOST_BAD_SHAPE;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(codes) & 15)) return FF_HOST_BAD_ALIGN;
   const int smem = 16 * D * 2 + LW_KEYS * D * 2 + 16 * LW_KEYS * 4 + 16 * LW_KEYS * 2 + 3 * 16 * 4;
@@ -301,7 +326,8 @@ FF_EXPORT int ff_latent_window_attention(const void* q, const void* codes, const
   dim3 grid((heads + 15) / 16, batch);
   if (int lr = launch_pdl(latent_window_attention_kernel<0>, grid, dim3(128), smem, s, 0, (const __nv_bfloat16*)q,
                           (const uint8_t*)codes, (const uint8_t*)scales, ring_ids, positions, sink, inv_rotary,
-                          (__nv_bfloat16*)out, heads, D, window, rings, rope_tail, scale, 1, status, nullptr, nullptr)) return lr;
+                          (__nv_bfloat16*)out, heads, D, window, visible, rings, rope_tail, scale, 1, status, nullptr,
+                          nullptr)) return lr;
   return launch_result();
 }
 
@@ -320,7 +346,20 @@ FF_EXPORT int ff_latent_sparse_attention(const void* q, const void* latent, cons
   dim3 grid((heads + 15) / 16, rows);
   if (int lr = launch_pdl(latent_window_attention_kernel<1>, grid, dim3(128), smem, s, 0, (const __nv_bfloat16*)q,
                           (const uint8_t*)nullptr, (const uint8_t*)nullptr, (const int*)nullptr, (const int*)nullptr, sink,
-                          (const float*)nullptr, (__nv_bfloat16*)out, heads, D, width, num_rows, 0, scale, 1, status,
+                          (const float*)nullptr, (__nv_bfloat16*)out, heads, D, width, width, num_rows, 0, scale, 1, status,
                           (const __nv_bfloat16*)latent, indices)) return lr;
+  return launch_result();
+}
+
+// In-place rotary on the last `tail` dims of every head (adjacent pairs); cs [rows, tail] f32 = (cos, sin) per pair.
+FF_EXPORT int ff_rope_pair_tail(void* x, const float* cs, long long rows, int heads, int D, int ldx, int tail,
+                                cudaStream_t s) {
+  if (rows <= 0 || heads <= 0 || D <= 0 || tail <= 0 || tail > D || (tail & 1) || (D & 1) || (ldx & 1) || ldx < heads * D)
+    return FF_HOST_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 3) || (reinterpret_cast<uintptr_t>(cs) & 7)) return FF_HOST_BAD_ALIGN;
+  const long long total = rows * heads * (tail / 2);
+  const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148 * 8);
+  if (int lr = launch_pdl(rope_pair_tail_kernel, dim3(blocks), dim3(256), 0, s, 0, (__nv_bfloat16*)x, cs, rows, heads, D,
+                          ldx, tail)) return lr;
   return launch_result();
 }

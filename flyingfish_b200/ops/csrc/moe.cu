@@ -19,7 +19,7 @@ namespace ff {
 
 // ---------------------------------------------------------------------------------------
 // routing: one warp per row, scores in shared memory
-// score_mode: 0 softmax, 1 sigmoid, 2 noaux (sigmoid + bias for selection, groups)
+// score_mode: 0 softmax, 1 sigmoid, 2 noaux (sigmoid + bias for selection, groups), 3 as 2 with sqrt(softplus(x)) scores
 // ---------------------------------------------------------------------------------------
 constexpr int ROUTE_WARPS = 4;
 constexpr int ROUTE_MAX_E = 512;
@@ -56,13 +56,14 @@ moe_topk_kernel(const __nv_bfloat16* __restrict__ logits, const float* __restric
     for (int e = lane; e < E; e += 32) { sc[e] *= inv; sel[e] = sc[e]; }
   } else {
     for (int e = lane; e < E; e += 32) {
-      const float v = 1.0f / (1.0f + expf(-__bfloat162float(lg[e])));
+      const float x = __bfloat162float(lg[e]);
+      const float v = (score_mode == 3) ? sqrtf(x > 20.f ? x : log1pf(expf(x))) : 1.0f / (1.0f + expf(-x));
       sc[e] = v;
-      sel[e] = (score_mode == 2 && bias) ? v + bias[e] : v;
+      sel[e] = (score_mode >= 2 && bias) ? v + bias[e] : v;
     }
   }
   __syncwarp();
-  if (score_mode == 2 && n_groups > 1) {
+  if (score_mode >= 2 && n_groups > 1) {
     const int gsz = E / n_groups;
     // group score = sum of the two best selection scores of the group
     float gscore = -INFINITY;

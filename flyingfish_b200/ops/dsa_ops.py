@@ -150,3 +150,49 @@ def sparse_attention(q: torch.Tensor, latent: torch.Tensor, indices: torch.Tenso
     check(rc, "ff_latent_sparse_attention")
     _count()
     return out
+
+
+class StateSnapshot:
+    """Rows of a set of per-token state tables, saved by :func:`checkpoint_save`."""
+    def __init__(self, tables, rows, data, meta):
+        self.tables, self.rows, self.data, self.meta = tables, rows, data, meta
+
+
+def _table_meta(tables: list[torch.Tensor]):
+    dev = tables[0].device
+    vecs = [t.shape[1] * t.element_size() // 16 for t in tables]
+    ptrs = torch.tensor([t.data_ptr() for t in tables], dtype=torch.int64, device=dev)
+    return ptrs, torch.tensor(vecs, dtype=torch.int32, device=dev), torch.tensor([t.shape[0] for t in tables],
+                                                                                   dtype=torch.int32, device=dev), max(vecs)
+
+
+def checkpoint_save(tables: list[torch.Tensor], rows: torch.Tensor) -> StateSnapshot:
+    """Save rows ``rows`` (int32 [n], global row ids) of every 2-D table (any dtype, row bytes a multiple of 16) so that
+    a speculative round that overwrites them can be rolled back: one launch for all tables."""
+    n = rows.numel()
+    if not tables[0].is_cuda:
+        return StateSnapshot(tables, rows.clone(), [t[rows.long()].clone() for t in tables], None)
+    for t in tables:
+        _require(t.dim() == 2 and t.is_contiguous() and (t.shape[1] * t.element_size()) % 16 == 0, "checkpoint: table layout")
+    meta = _table_meta(tables)
+    ptrs, vecs, trows, mx = meta
+    data = torch.empty(len(tables) * n * mx * 16, dtype=torch.uint8, device=rows.device)
+    rows = rows.to(torch.int32).contiguous()
+    rc = kernels().ff_dsa_checkpoint(ptr(ptrs), ptr(vecs), ptr(trows), len(tables), ptr(rows), n, ptr(data), mx, 0,
+                                     ptr(status_tensor(rows.device)), stream_ptr())
+    check(rc, "ff_dsa_checkpoint(save)")
+    _count()
+    return StateSnapshot(tables, rows, data, meta)
+
+
+def checkpoint_restore(snap: StateSnapshot) -> None:
+    """Write the saved rows back into their tables."""
+    if snap.meta is None:
+        for t, d in zip(snap.tables, snap.data):
+            t[snap.rows.long()] = d
+        return
+    ptrs, vecs, trows, mx = snap.meta
+    rc = kernels().ff_dsa_checkpoint(ptr(ptrs), ptr(vecs), ptr(trows), len(snap.tables), ptr(snap.rows), snap.rows.numel(),
+                                     ptr(snap.data), mx, 1, ptr(status_tensor(snap.rows.device)), stream_ptr())
+    check(rc, "ff_dsa_checkpoint(restore)")
+    _count()

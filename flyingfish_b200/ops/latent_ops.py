@@ -70,22 +70,47 @@ def ring_write(k: torch.Tensor, ring_ids: torch.Tensor, positions: torch.Tensor,
     _count()
 
 
-def inverse_rotary(positions: torch.Tensor, rope_tail: int, theta: float) -> torch.Tensor:
-    """[B, rope_tail] FP32: (cos, sin) of the inverse angle of every adjacent pair of the tail."""
+def rotary_table(positions: torch.Tensor, rope_tail: int, theta: float, inverse: bool = False) -> torch.Tensor:
+    """[B, rope_tail] FP32: (cos, sin) of the (inverse) angle of every adjacent pair of the tail."""
     i = torch.arange(rope_tail // 2, dtype=torch.float32, device=positions.device)
     inv = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32, device=positions.device), 2 * i / max(rope_tail, 1))
-    ang = -positions.float()[:, None] * inv[None, :]
+    ang = positions.float()[:, None] * inv[None, :]
+    if inverse:
+        ang = -ang
     return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).reshape(positions.shape[0], rope_tail).contiguous()
 
 
-def window_attention_ref(q, codes, scales, ring_ids, positions, sink, inv_rot, rope_tail, scale):
+def inverse_rotary(positions: torch.Tensor, rope_tail: int, theta: float) -> torch.Tensor:
+    return rotary_table(positions, rope_tail, theta, inverse=True)
+
+
+def rope_pair_tail(x: torch.Tensor, cs: torch.Tensor, heads: int, d: int, rope_tail: int) -> None:
+    """In place: rotate the adjacent pairs of the last ``rope_tail`` dims of every head of x [rows, heads * d] by the
+    angles of ``cs`` [rows, rope_tail] (:func:`rotary_table`); FP32 arithmetic, one rounding to BF16."""
+    rows = x.shape[0]
+    if not x.is_cuda:
+        v = x.view(rows, heads, d)[:, :, d - rope_tail:].float().reshape(rows, heads, rope_tail // 2, 2)
+        c = cs.reshape(rows, 1, rope_tail // 2, 2)
+        a, b = v[..., 0], v[..., 1]
+        rot = torch.stack([a * c[..., 0] - b * c[..., 1], a * c[..., 1] + b * c[..., 0]], -1).reshape(rows, heads, rope_tail)
+        x.view(rows, heads, d)[:, :, d - rope_tail:] = rot.to(x.dtype)
+        return
+    _require(x.dtype == torch.bfloat16 and x.stride(1) == 1 and cs.is_contiguous() and cs.dtype == torch.float32
+             and cs.shape == (rows, rope_tail), "rope_pair_tail: layout")
+    rc = kernels().ff_rope_pair_tail(ptr(x), ptr(cs), c_longlong(rows), heads, d, x.stride(0), rope_tail, stream_ptr())
+    check(rc, "ff_rope_pair_tail")
+    _count()
+
+
+def window_attention_ref(q, codes, scales, ring_ids, positions, sink, inv_rot, rope_tail, scale, visible=None):
     b_, heads, d = q.shape
     window = codes.shape[1]
+    visible = visible or window
     out = torch.zeros(b_, heads, d, dtype=torch.float32)
     for b in range(b_):
         pos, ring = int(positions[b]), int(ring_ids[b])
-        nvis = min(pos + 1, window)
-        first = (pos + 1) % window if pos + 1 >= window else 0
+        nvis = min(pos + 1, visible)
+        first = (pos + 1 - nvis) % window
         slots = [(first + j) % window for j in range(nvis)]
         k = dequant32(codes[ring, slots], scales[ring, slots]).to(torch.bfloat16).float()      # [nvis, d]
         s = (q[b].float() @ k.t()) * scale                                                     # [heads, nvis]
@@ -116,20 +141,27 @@ def window_attention_ref(q, codes, scales, ring_ids, positions, sink, inv_rot, r
 
 def window_attention(q: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, ring_ids: torch.Tensor,
                      positions: torch.Tensor, sink: torch.Tensor, rope_tail: int, theta: float,
-                     scale: float | None = None) -> torch.Tensor:
+                     scale: float | None = None, visible: int | None = None, inv_rot: torch.Tensor | None = None
+                     ) -> torch.Tensor:
     """q [B, heads, D] bf16 post-RoPE -> out [B, heads, D] bf16 (value = K content, inverse rotary on the
-    last ``rope_tail`` dims). The query's own K row must already be in its ring."""
+    last ``rope_tail`` dims). The query's own K row must already be in its ring. ``visible`` (default: the ring
+    length) is the attention window; a ring longer than the window lets one launch serve the rows of a prefill chunk
+    (row of position p in slot p % ring length, every query reading the ``visible`` positions up to its own).
+    ``inv_rot``: the table of :func:`inverse_rotary` when the caller already has it."""
     b_, heads, d = q.shape
     rings, window, _ = codes.shape
     scale = scale if scale is not None else d ** -0.5
-    inv_rot = inverse_rotary(positions, rope_tail, theta) if rope_tail else torch.zeros(b_, 0, device=q.device)
+    visible = visible or window
+    _require(0 < visible <= window, "window_attention: visible")
+    if inv_rot is None:
+        inv_rot = inverse_rotary(positions, rope_tail, theta) if rope_tail else torch.zeros(b_, 0, device=q.device)
     if not q.is_cuda:
-        return window_attention_ref(q, codes, scales, ring_ids, positions, sink, inv_rot, rope_tail, scale)
+        return window_attention_ref(q, codes, scales, ring_ids, positions, sink, inv_rot, rope_tail, scale, visible)
     _require(q.is_contiguous() and q.dtype == torch.bfloat16 and d % 64 == 0 and d <= 512, "window_attention: q layout")
     _require(codes.is_contiguous() and scales.is_contiguous() and sink.dtype == torch.float32, "window_attention: ring layout")
     out = torch.empty_like(q)
     rc = kernels().ff_latent_window_attention(ptr(q), ptr(codes), ptr(scales), ptr(ring_ids), ptr(positions), ptr(sink),
-                                              ptr(inv_rot), ptr(out), b_, heads, d, window, rings, rope_tail,
+                                              ptr(inv_rot), ptr(out), b_, heads, d, window, visible, rings, rope_tail,
                                               c_float(scale), ptr(status_tensor(q.device)), stream_ptr())
     check(rc, "ff_latent_window_attention")
     _count()

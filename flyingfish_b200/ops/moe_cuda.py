@@ -13,7 +13,7 @@ import torch
 from . import _count, _require, linear, workspace
 from .lib import check, kernels, ptr, status_tensor, stream_ptr
 
-SCORE_MODES = {"softmax": 0, "sigmoid": 1, "noaux": 2}
+SCORE_MODES = {"softmax": 0, "sigmoid": 1, "noaux": 2, "sqrt_softplus": 3}
 
 
 def route(x, w_router, top_k, score, bias, n_groups, topk_groups, routed_scaling, renormalize):

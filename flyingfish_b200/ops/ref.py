@@ -317,7 +317,8 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top_k: int, score: str = 
     * ``sigmoid``: sigmoid scores, top-k, renormalise;
     * ``noaux``: selection on ``sigmoid(logit) + bias`` restricted to the ``topk_groups`` best of
       ``n_groups`` groups (group score = sum of its two best biased scores), weights are the
-      unbiased scores renormalised and multiplied by ``routed_scaling``.
+      unbiased scores renormalised and multiplied by ``routed_scaling``;
+    * ``sqrt_softplus``: as ``noaux`` with scores ``sqrt(softplus(logit))`` (the DeepSeek-V4.1 router).
     Returns (weights FP32 [rows, k], ids int32 [rows, k]) with ids in selection order."""
     dt = logits_dtype or x.dtype
     logits = _r((x.to(torch.float64) @ w_router.to(torch.float64).t()).to(F32), dt)
@@ -327,8 +328,8 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top_k: int, score: str = 
     elif score == "sigmoid":
         s = torch.sigmoid(logits)
         w, ids = topk_lower_tie(s, top_k)
-    elif score == "noaux":
-        s = torch.sigmoid(logits)
+    elif score in ("noaux", "sqrt_softplus"):
+        s = torch.sigmoid(logits) if score == "noaux" else torch.sqrt(torch.nn.functional.softplus(logits))
         sb = s + (bias.to(F32) if bias is not None else 0.0)
         rows, e = sb.shape
         if n_groups > 1:
