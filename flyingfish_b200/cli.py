@@ -38,7 +38,7 @@ def _global_parser() -> argparse.ArgumentParser:
     p.add_argument("--capacity", type=int, default=4096)
     p.add_argument("--chunk", type=int, default=None)
     p.add_argument("--device-budget-gib", type=float, default=None)
-    p.add_argument("--tree-builder", choices=["waves", "serial"], default="waves")
+    p.add_argument("--tree-builder", choices=["waves", "serial", "markov"], default="waves")
     p.add_argument("--spec-budget", choices=["chain", "tree16", "tree32", "tree64"], default="chain")
     p.add_argument("--spec-graph", type=lambda s: s.lower() != "false", default=True)
     p.add_argument("--prefix-cache", type=lambda s: s.lower() == "true", default=False)

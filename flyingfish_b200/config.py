@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | deepseek_v41 | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | deepseek_v41 | glm5_next | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
     layers: int
     hidden: int
     heads: int
@@ -240,10 +240,20 @@ def deepseek_v41_tiny() -> ModelSpec:
                                   "cache_rows": 256}}})
 
 
+def glm5_next_tiny() -> ModelSpec:
+    """Small GLM-5-style shape: the hyper-connection program with every stage collapsing on its own pre-mix, top-k sparse
+    attention with the pooled indexer in every layer, sigmoid routing with selection bias."""
+    s = deepseek_v41_tiny()
+    s.name, s.arch = "glm5-next-tiny", "glm5_next"
+    s.moe.score, s.moe.routed_scaling = "noaux", 1.0
+    s.extra = {"v41": dict(s.extra["v41"], hc_policy="own", sparse_layers=[0, 1, 2], engram=None)}
+    return s
+
+
 NAMED_SHAPES = {
     "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
-    "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini, "deepseek-v41-tiny": deepseek_v41_tiny,
+    "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini, "deepseek-v41-tiny": deepseek_v41_tiny, "glm5-next-tiny": glm5_next_tiny,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }
 
@@ -353,7 +363,7 @@ class Settings:
     chunk: int | None = None              # prefill chunk rows (planner-derived when None)
     device_budget_gib: float | None = None
     draft_model: str | None = None
-    tree_builder: str = "waves"           # waves | serial
+    tree_builder: str = "waves"           # waves | serial | markov
     spec_budget: str = "chain"            # chain | tree16 | tree32 | tree64
     spec_graph: bool = True
     prefix_cache: bool = False

@@ -145,6 +145,11 @@ class DeepseekV41Model(DecoderModel):
         self.groups = int(c["o_groups"])
         self.index_topk = int(c.get("index_topk", dsa_ops.TOPK))
         self.sparse_layers = set(c.get("sparse_layers", []))
+        # which pre-mix collapses the stream before a sublayer: "carried" (DeepSeek: the attention stage uses the
+        # previous layer's FFN pre, the FFN stage the attention's own) or "own" (GLM: every stage its own, nothing
+        # carried across layers) -- src/model.rs:459-482 of the reference
+        self.hc_policy = str(c.get("hc_policy", "carried"))
+        assert self.hc_policy in ("carried", "own")
         self.prefill_take_limit = max_chunk                      # rows of one sequence per launch (ring headroom)
         self.ring = self.window + max_chunk - 1
         self.max_len = (max_len + dsa_ops.POOL - 1) // dsa_ops.POOL * dsa_ops.POOL
@@ -338,11 +343,11 @@ class DeepseekV41Model(DecoderModel):
                 mem = ops.linear(memory[i], v.w_engram).to(BF16)
                 stream = (stream.float() + mem.float()[:, None, :]).to(BF16)
             pre_a, post_a, comb_a = self._hc(stream, v.hc_attn)
-            xa = mhc_ops.collapse(stream, carried).to(dt)
+            xa = mhc_ops.collapse(stream, carried if self.hc_policy == "carried" else pre_a).to(dt)
             a = self._mixer(i, ops.rmsnorm(xa, lw.input_ln, s.rms_eps), b)
             stream = mhc_ops.update(a.to(BF16), stream, post_a, comb_a)
             pre_f, post_f, comb_f = self._hc(stream, v.hc_ffn)
-            xf = mhc_ops.collapse(stream, pre_a).to(dt)
+            xf = mhc_ops.collapse(stream, pre_a if self.hc_policy == "carried" else pre_f).to(dt)
             f = self._ffn(i, ops.rmsnorm(xf, lw.post_ln, s.rms_eps))
             stream = mhc_ops.update(f.to(BF16), stream, post_f, comb_f)
             carried = pre_f

@@ -65,22 +65,26 @@ SHORT_WAIT_NS = 5_000_000      # bound of every device-side wait in the short-wa
 
 
 def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False, timeline: bool = False,
-                  short_wait: bool = False) -> Path:
+                  short_wait: bool = False, debug_checks: bool = False) -> Path:
     """Compile all ``csrc/*.cu`` into ``_ff_kernels.so`` (no-op when up to date).
 
     ``timeline=True`` builds the tracing variant ``_ff_kernels_tl.so`` (``-DFF_TIMELINE``): kernels
     record (time, SM, phase) stamps into the enlarged status buffer, see ``utils/timeline.py``.
     ``short_wait=True`` builds ``_ff_kernels_sw.so`` with every bounded device wait cut to 5 ms: the
-    tests of the time-out paths load it, so that a wait nobody answers runs out at once."""
-    lib = HERE / ("_ff_kernels_tl.so" if timeline else "_ff_kernels_sw.so" if short_wait else "_ff_kernels.so")
+    tests of the time-out paths load it, so that a wait nobody answers runs out at once.
+    ``debug_checks=True`` builds ``_ff_kernels_dbg.so`` (``-DFF_DEBUG_CHECKS``): scratch with a single-writer
+    contract claims its elements in a ledger and a second claim inside one launch raises a status error; extra
+    in-kernel bounds words are compiled in."""
+    tag = "tl" if timeline else "sw" if short_wait else "dbg" if debug_checks else ""
+    lib = HERE / (f"_ff_kernels_{tag}.so" if tag else "_ff_kernels.so")
     srcs = kernel_sources()
     deps = srcs + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
     base_flags = list(NVCC_FLAGS) + (["-DFF_TIMELINE"] if timeline else []) + \
-        ([f"-DFF_WAIT_NS={SHORT_WAIT_NS}ull"] if short_wait else [])
+        ([f"-DFF_WAIT_NS={SHORT_WAIT_NS}ull"] if short_wait else []) + (["-DFF_DEBUG_CHECKS"] if debug_checks else [])
     stamp = _hash(deps, " ".join(base_flags))
     if not force and _up_to_date(lib, stamp):
         return lib
-    build_dir = BUILD / "tl" if timeline else BUILD / "sw" if short_wait else BUILD
+    build_dir = BUILD / tag if tag else BUILD
     build_dir.mkdir(parents=True, exist_ok=True)
     flags = base_flags + (["-Xptxas", "-v"] if ptxas_info else [])
 
@@ -135,6 +139,7 @@ def build_host(verbose: bool = False, force: bool = False) -> Path | None:
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_kernels(verbose=verbose, force=force)
     build_kernels(verbose=verbose, force=force, short_wait=True)
+    build_kernels(verbose=verbose, force=force, debug_checks=True)
     build_host(verbose=verbose, force=force)
 
 

@@ -327,7 +327,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       } else {
         const size_t pr = ((size_t)b * nsplit + split) * (nq * hq) + (size_t)qi * hq + hh;
         part_o[pr * HD + d] = acc;
-        if (d == 0) { part_ml[pr * 2] = M; part_ml[pr * 2 + 1] = L; }
+        if (d == 0) {
+          part_ml[pr * 2] = M; part_ml[pr * 2 + 1] = L;
+          dbg_write_once(status, KID_ATTN_DECODE, DBG_ATTN_PARTIAL, (long long)pr);
+        }
       }
     }
   }

@@ -392,6 +392,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       // partial tile: FP32 slot 2*cta + (1 if this segment starts the tile), layout [t][tile_rows]
       const size_t slot_elems = (size_t)M * tile_rows;
       float* part = scratch + (size_t)(2 * blockIdx.x + (sg.kb0 == 0 ? 1 : 0)) * slot_elems;
+      if (row_live && t_own < M)      // single-writer contract of the partial slots: one claim per (slot, token row)
+        dbg_write_once(status, KID_GEMM_SKINNY, DBG_GEMM_PARTIAL, (long long)(2 * blockIdx.x + (sg.kb0 == 0 ? 1 : 0)) * M + t_own);
       if (row_live) {
         for (int c = 0; c < tile_rows; c += 16) {
           uint32_t r[16];

@@ -26,6 +26,7 @@ enum StatusCode : int {
   FF_ERR_BOUNDS = 3,       // index outside a table (bad token id, bad block id ...)
   FF_ERR_NONFINITE = 4,    // non-finite value seen by a sticky scan
   FF_ERR_CAPACITY = 5,     // a device-side buffer would overflow
+  FF_ERR_DOUBLE_WRITE = 6, // debug build: an element with a single-writer contract was written twice in one launch
 };
 
 enum KernelId : int {
@@ -45,6 +46,28 @@ __device__ __forceinline__ void set_status(int* status, int kid, int code, int d
     __threadfence_system();
   }
 }
+
+// ---------------------------------------------------------------------------------------
+// Debug build (-DFF_DEBUG_CHECKS): single-writer ledger. Scratch with the contract "every element is written by
+// exactly one block per launch" (split-K partial rows, attention split partials, the KV-cache rows of a step) claims
+// its element here; a second claim in the same launch epoch sets FF_ERR_DOUBLE_WRITE with (region, index). The host
+// enlarges the status buffer: word 9 = epoch (bumped before every launch), word 10 = entries per region, word 11 =
+// claims that fell outside a region (not checked), ledger from word 16 on, DBG_REGIONS regions. Compiled out otherwise.
+// ---------------------------------------------------------------------------------------
+enum DbgRegion : int { DBG_GEMM_PARTIAL = 0, DBG_ATTN_PARTIAL = 1, DBG_KV_K = 2, DBG_KV_V = 3, DBG_REGIONS = 4 };
+#ifdef FF_DEBUG_CHECKS
+__device__ __forceinline__ void dbg_write_once(int* status, int kid, int region, long long index) {
+  if (status == nullptr) return;
+  const int len = status[10], epoch = status[9];
+  if (len <= 0 || index < 0 || index >= len || region < 0 || region >= DBG_REGIONS) { atomicAdd(&status[11], 1); return; }
+  const int prev = atomicExch(&status[16 + (size_t)region * len + index], epoch);
+  if (prev == epoch) set_status(status, kid, FF_ERR_DOUBLE_WRITE, region, (int)index);
+}
+#define FF_DBG_CHECK(cond, status, kid, d0, d1) do { if (!(cond)) set_status((status), (kid), FF_ERR_BOUNDS, (d0), (d1)); } while (0)
+#else
+__device__ __forceinline__ void dbg_write_once(int*, int, int, long long) {}
+#define FF_DBG_CHECK(cond, status, kid, d0, d1) do {} while (0)
+#endif
 
 #ifndef FF_WAIT_NS
 #define FF_WAIT_NS 2000000000ull   // 2 s: far above any legitimate wait in this library

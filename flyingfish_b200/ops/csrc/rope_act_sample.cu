@@ -78,6 +78,8 @@ __global__ void rope_kv_paged_kernel(__nv_bfloat16* __restrict__ qkv, const int*
     const int blk = slot / block_size, off = slot - blk * block_size;
     if (blk >= num_blocks) { set_status(status, KID_ROPE_KV, FF_ERR_BOUNDS, row, slot); return; }
     const int kvh = is_v ? head - hq - hkv : head - hq;
+    if (c == 0) dbg_write_once(status, KID_ROPE_KV, is_v ? DBG_KV_V : DBG_KV_K, (long long)slot * hkv + kvh);
+    FF_DBG_CHECK(off >= 0 && off < block_size && kvh >= 0 && kvh < hkv, status, KID_ROPE_KV, row, kvh);
     __nv_bfloat16* dst = (is_v ? vcache : kcache) + (((size_t)blk * hkv + kvh) * block_size + off) * dim;
     reinterpret_cast<uint4*>(dst)[c] = lo;
     reinterpret_cast<uint4*>(dst + half)[c] = hi;

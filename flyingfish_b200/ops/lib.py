@@ -20,6 +20,10 @@ _HERE = Path(__file__).resolve().parent
 # (word 8 = record count, 16-byte records from word 16 on; see utils/timeline.py).
 TIMELINE = os.environ.get("FLYINGFISH_TIMELINE", "0") == "1"
 TIMELINE_CAP = 1 << 18
+# FLYINGFISH_DEBUG_CHECKS=1 loads the checking build: single-writer ledger (word 9 = launch epoch, word 10 = entries
+# per region, word 11 = claims outside a region, ledger from word 16 on) and extra in-kernel bounds words.
+DEBUG_CHECKS = os.environ.get("FLYINGFISH_DEBUG_CHECKS", "0") == "1"
+DEBUG_REGIONS, DEBUG_REGION_LEN = 4, 1 << 19
 _lock = threading.Lock()
 _kernels: ctypes.CDLL | None = None
 _host: ctypes.CDLL | None = None
@@ -41,9 +45,29 @@ def kernels() -> ctypes.CDLL:
         with _lock:
             if _kernels is None:
                 from . import build
-                path = build.build_kernels(timeline=TIMELINE)
-                _kernels = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+                path = build.build_kernels(timeline=TIMELINE, debug_checks=DEBUG_CHECKS and not TIMELINE)
+                lib = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+                _kernels = _EpochProxy(lib) if DEBUG_CHECKS and not TIMELINE else lib
     return _kernels
+
+
+class _EpochProxy:
+    """Checking build only: every launcher call first bumps the launch epoch of the current device's status buffer, so
+    that the single-writer ledger tells a second write inside one launch from the write of the next launch."""
+
+    def __init__(self, lib: ctypes.CDLL):
+        self._lib = lib
+
+    def __getattr__(self, name: str):
+        fn = getattr(self._lib, name)
+        if not name.startswith("ff_") or name.endswith("_plan") or name.endswith("_workspace"):
+            return fn
+
+        def call(*args):
+            if torch.cuda.is_available():
+                status_tensor()[9:10].add_(1)
+            return fn(*args)
+        return call
 
 
 def host() -> ctypes.CDLL:
@@ -80,7 +104,17 @@ def stream_ptr() -> ctypes.c_void_p:
 # ------------------------------------------------------------------------------------------
 _status: dict[int, torch.Tensor] = {}
 
-STATUS_CODES = {0: "ok", 1: "timeout", 2: "contract", 3: "bounds", 4: "non-finite", 5: "capacity"}
+STATUS_CODES = {0: "ok", 1: "timeout", 2: "contract", 3: "bounds", 4: "non-finite", 5: "capacity", 6: "double write"}
+
+
+def debug_ledger_stats(device=None) -> dict:
+    """Checking build: launch epochs so far, entries claimed at least once per region, claims that fell outside a
+    region (synchronising)."""
+    t = status_tensor(device)
+    if not DEBUG_CHECKS or t.numel() < 16 + DEBUG_REGIONS * DEBUG_REGION_LEN:
+        return {}
+    led = t[16:].view(DEBUG_REGIONS, DEBUG_REGION_LEN)
+    return {"epoch": int(t[9]), "claimed": [int((led[r] != 0).sum()) for r in range(DEBUG_REGIONS)], "uncovered": int(t[11])}
 
 
 class DeviceStatusError(RuntimeError):
@@ -96,7 +130,15 @@ def status_tensor(device: torch.device | int | None = None) -> torch.Tensor:
         dev = torch.cuda.current_device()
     t = _status.get(dev)
     if t is None:
-        t = torch.zeros(16 + 4 * TIMELINE_CAP if TIMELINE else 4, dtype=torch.int32, device=f"cuda:{dev}")
+        if TIMELINE:
+            n = 16 + 4 * TIMELINE_CAP
+        elif DEBUG_CHECKS:
+            n = 16 + DEBUG_REGIONS * DEBUG_REGION_LEN
+        else:
+            n = 4
+        t = torch.zeros(n, dtype=torch.int32, device=f"cuda:{dev}")
+        if DEBUG_CHECKS and not TIMELINE:
+            t[9], t[10] = 1, DEBUG_REGION_LEN
         _status[dev] = t
     return t
 

@@ -76,7 +76,7 @@ def _record_tree(target, draft, ids, n, budget: str, builder: str) -> dict:
     dt = (time.perf_counter() - t0) * 1e3
     target.reset(); draft.reset()
     return {"ids": out.ids, "accepted_per_round": list(sp.stats.accepted_per_round), "stats": sp.stats, "ms": dt,
-            "rows": sp.rows}
+            "rows": sp.rows, "draft_forwards": sp.draft_forwards}
 
 
 def run_dspark_tool(tool: str, target, draft, prompt_tokens: int, max_new_tokens: int, budget: str = "tree16",
@@ -113,10 +113,10 @@ def run_dspark_tool(tool: str, target, draft, prompt_tokens: int, max_new_tokens
         res.update(identical_to_greedy=rec["ids"] == plain.ids, rounds=len(rec["accepted_per_round"]),
                    tokens_per_round=rec["stats"].tokens_per_round, budget=budget, builder=builder)
     elif tool == "compare-tree-builders":
-        runs = {b: _record_tree(target, draft, ids, max_new_tokens, budget, b) for b in ("waves", "serial")}
+        runs = {b: _record_tree(target, draft, ids, max_new_tokens, budget, b) for b in ("waves", "serial", "markov")}
         res.update(budget=budget, identical_to_greedy=all(r["ids"] == plain.ids for r in runs.values()),
                    builders={b: {"rounds": len(r["accepted_per_round"]), "tokens_per_round": r["stats"].tokens_per_round,
-                                 "ms": r["ms"]} for b, r in runs.items()})
+                                 "ms": r["ms"], "draft_forwards": r["draft_forwards"]} for b, r in runs.items()})
     elif tool == "compare-tree-padding":
         # the same run under every verification-row budget: more rows cost more per round and accept more per round
         runs = {b: _record_tree(target, draft, ids, max_new_tokens, b, builder) for b in ("tree16", "tree32", "tree64")}

@@ -204,7 +204,7 @@ def test_draft_model_flags_select_the_speculator(capsys):
     chain = _run(BASE + ["--draft-model", "tiny-llama"] + GEN, capsys)
     assert chain["mode"] == "draft-chain" and chain["rounds"] > 0
     assert chain["generated_ids"] == plain["generated_ids"]         # speculation never changes greedy output
-    for builder in ("waves", "serial"):
+    for builder in ("waves", "serial", "markov"):
         tree = _run(BASE + ["--draft-model", "tiny-llama", "--spec-budget", "tree16", "--tree-builder", builder] + GEN, capsys)
         assert tree["mode"] == "draft-tree16" and tree["tree_builder"] == builder
         assert tree["generated_ids"] == plain["generated_ids"]
@@ -314,7 +314,9 @@ def test_draft_model_tools(capsys, tmp_path):
     out = _run(base + ["check-tree-greedy"] + small + ["--strict"], capsys)
     assert out["identical_to_greedy"] and out["budget"] == "tree16" and out["rounds"] > 0
     out = _run(base + ["compare-tree-builders"] + small, capsys)
-    assert out["identical_to_greedy"] and set(out["builders"]) == {"waves", "serial"}
+    assert out["identical_to_greedy"] and set(out["builders"]) == {"waves", "serial", "markov"}
+    # the Markov head needs one draft forward per depth and round, the per-node builders one per expanded node
+    assert out["builders"]["markov"]["draft_forwards"] < out["builders"]["waves"]["draft_forwards"]
     out = _run(base + ["compare-tree-padding"] + small, capsys)
     assert out["identical_to_greedy"] and [out["budgets"][b]["rows"] for b in ("tree16", "tree32", "tree64")] == [16, 32, 64]
     out = _run(base + ["compare-spec-graph"] + small, capsys)

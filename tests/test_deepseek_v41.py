@@ -51,6 +51,18 @@ def test_window_layers_forget_and_sparse_layer_remembers():
     assert sorted(net.sparse_layers) == [1] and net.pooled[1].abs().sum() > 0
 
 
+def test_glm_style_shape_all_sparse_layers_cpu():
+    """GLM-style variant: own pre-mix at every stage, sparse attention in all layers, no window ring, no n-gram rows."""
+    m = Model.load("glm5-next-tiny", Settings(capacity=256, max_batch=4, graph=False), device="cpu", seed=0)
+    net = m.engine.model
+    assert net.hc_policy == "own" and not net.codes and sorted(net.sparse_layers) == [0, 1, 2] and net.engram is None
+    p = _prompts([45])
+    want = m.generate_batch(p, 6)
+    again = Model.load("glm5-next-tiny", Settings(capacity=256, max_batch=4, graph=False, chunk=16), device="cpu", seed=0)
+    from _oracle import assert_tokens_equal_up_to_ties
+    assert_tokens_equal_up_to_ties(m, p[0], want[0], again.generate_batch(p, 6)[0])
+
+
 def test_router_sqrt_softplus_oracle():
     g = torch.Generator().manual_seed(0)
     x = torch.randn(5, 64, generator=g).to(torch.bfloat16)
@@ -148,3 +160,8 @@ def test_v41_model_gpu_matches_cpu_oracle():
     chunked = _load("cuda", chunk=16).generate_batch(p, 8)
     for pr, w, g in zip(p, want, chunked):
         assert_tokens_equal_up_to_ties(cpu, pr, w, g)
+    st = Settings(capacity=256, max_batch=4, graph=False)
+    c2, g2 = (Model.load("glm5-next-tiny", st, device=d, seed=0) for d in ("cpu", "cuda"))
+    for pr, w, g in zip(p, c2.generate_batch(p, 8), g2.generate_batch(p, 8)):
+        assert_tokens_equal_up_to_ties(c2, pr, w, g)
+    ops.check_status()
