@@ -108,6 +108,15 @@ class Model:
             net = DecoderModel(weights, comm=comm)
         if ep is not None:
             net.ep = ep
+        if device.type == "cuda":
+            # measured kernel choices of an earlier ``ff calibrate`` for this model, device and kernel build
+            try:
+                from .planner.calibrate import apply_kernel_choices, load_calibration
+                applied = apply_kernel_choices(load_calibration(str(model), settings, device))
+                if applied:
+                    log_json("kernel_choices_applied", verbose_only=True, count=applied)
+            except (OSError, ValueError, RuntimeError):
+                pass
         plan = plan_engine(spec, settings, device, weights_bytes=weights.nbytes(), tp=tp.size)
         log_json("prefill_memory_plan", verbose_only=True, **plan.to_json())
         engine = Engine(net, spec, settings, plan.kv_blocks, device, max_prefill_rows=plan.prefill_chunk)

@@ -479,6 +479,14 @@ using namespace ff;
 constexpr int ATTN_SMEM = 4 * PAGE * HD * 2;   // 64 KiB: two stages of K and V pages (prefill)
 constexpr int DEC_SMEM = DEC_STAGES * 2 * PAGE * HD * 2 + 1024;
 
+// Waves of CTAs the split-KV plan aims for (calibrated; default four).
+static int g_attn_waves = 4;
+FF_EXPORT int ff_attn_decode_set_waves(int waves) {
+  if (waves < 1 || waves > 16) return FF_HOST_BAD_SHAPE;
+  g_attn_waves = waves;
+  return 0;
+}
+
 // Number of KV splits the decode launcher will use and the scratch it needs.
 FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ctx, long long* part_o_bytes,
                                   long long* part_ml_bytes) {
@@ -487,7 +495,7 @@ FF_EXPORT int ff_attn_decode_plan(int batch, int hq, int hkv, int nq, int max_ct
   int nsplit = 1;
   // three 64-KiB CTAs fit on one SM; aim for at least four full waves so the ragged last wave
   // costs little
-  const int target = 148 * 3 * 4;
+  const int target = 148 * 3 * g_attn_waves;
   if (ctas < target) nsplit = (target + ctas - 1) / ctas;
   if (const char* ev = getenv("FF_ATTN_NSPLIT")) { const int v = atoi(ev); if (v > 0) nsplit = v; }
   if (nsplit > pages) nsplit = pages;

@@ -28,6 +28,8 @@
 #include "ptx.cuh"
 #include "comm.cuh"
 #include "host_util.h"
+#include <mutex>
+#include <vector>
 #include "skinny_common.cuh"
 
 namespace ff {
@@ -620,6 +622,21 @@ static int skinny_stages(int tile_rows, int reserved = 0, int ntok = 64, int lim
   return st;
 }
 
+// Calibrated decompositions: (N, K, epi) -> (cluster size, tile rows), written by the calibration run (or loaded from
+// its cache) and consulted before the time model below. Keyed without M on purpose: a row's bits must not depend on
+// the batch it is computed in. The counterpart of the reference's measured linear choices
+// (src/backend/cuda/linear_calibrate.rs, src/backend/setup.rs:223-256).
+struct SkinnyChoice { int N, K, epi, s, rows; };
+static std::mutex g_choice_mu;
+static std::vector<SkinnyChoice> g_choices;
+
+static bool skinny_choice(int N, int K, int epi, int* s, int* rows) {
+  std::lock_guard<std::mutex> lk(g_choice_mu);
+  for (const SkinnyChoice& c : g_choices)
+    if (c.N == N && c.K == K && c.epi == epi) { *s = c.s; *rows = c.rows; return true; }
+  return false;
+}
+
 // epi != 0 (row-wise epilogue): tiles are exactly 128 rows.
 static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
   const int kblocks = (K + SBK - 1) / SBK;
@@ -634,6 +651,28 @@ static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
   if (env_r > 0 && env_s == 1 && epi == 0) rows1 = env_r;
   SkinnyConfig best = {1, rows1, (N + rows1 - 1) / rows1, skinny_stages(rows1), 0};
   if (env_s == 1) return best;
+  int cal_s = 0, cal_r = 0;
+  if (env_s <= 0 && skinny_choice(N, K, epi, &cal_s, &cal_r)) {
+    if (cal_s == 1) {
+      if (epi == 0 && cal_r >= 16 && cal_r <= SBN && cal_r % 16 == 0 && N >= cal_r)
+        best = {1, cal_r, (N + cal_r - 1) / cal_r, skinny_stages(cal_r), 0};
+      best.stages = skinny_stages(best.tile_rows, 0, (M + 15) / 16 * 16, sk_smem_for(M));
+      return best;
+    }
+    // a cluster choice is taken only while it is launchable here (the table may come from another device)
+    const int rows = epi != 0 ? 128 : cal_r;
+    const int tiles = rows > 0 ? (N + rows - 1) / rows : 0;
+    const int maxc = (cal_s >= 2 && cal_s <= 8) ? skinny_max_clusters(cal_s) - (cal_s > 2 ? 1 : 0) : 0;
+    if (rows >= 64 && rows <= SBN && rows % 16 == 0 && kblocks / cal_s >= 2 && tiles <= maxc) {
+      const int recv64 = (cal_s * ((64 + cal_s - 1) / cal_s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
+      if (skinny_stages(rows, recv64) >= 3) {
+        best = {cal_s, rows, tiles, 0, 0};
+        best.pipe_off = (cal_s * ((M + cal_s - 1) / cal_s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
+        best.stages = skinny_stages(rows, best.pipe_off, (M + 15) / 16 * 16, sk_smem_for(M));
+        return best;
+      }
+    }
+  }
   // Time model (microseconds). A CTA takes in at most ~60 GB/s (weights plus the activation tile it
   // re-reads from L2 for every k-block), a pipeline of `st` stages cannot turn a k-block around faster
   // than the ~1.5 us load latency / st, and all CTAs together cannot beat HBM (~5.9 TB/s on reads).
@@ -694,6 +733,17 @@ FF_EXPORT int ff_gemm_skinny_config(int M, int N, int K, int epi, int* out) {
   out[0] = c.cluster; out[1] = c.tile_rows; out[2] = c.tiles; out[3] = c.stages;
   out[4] = (c.cluster > 1) ? c.tiles * c.cluster : 0;
   (void)sb; (void)cb;
+  return 0;
+}
+
+// Record (s >= 1) or forget (s == 0) the calibrated decomposition of every decode GEMM with this (N, K, epi):
+// s = 1 stream-K with `rows`-row tiles, s = 2..8 cluster split-K. A choice that is not launchable is ignored at plan time.
+FF_EXPORT int ff_gemm_skinny_set_choice(int N, int K, int epi, int s, int rows) {
+  if (N <= 0 || K <= 0 || s < 0 || s > 8) return FF_HOST_BAD_SHAPE;
+  std::lock_guard<std::mutex> lk(g_choice_mu);
+  for (size_t i = 0; i < g_choices.size(); ++i)
+    if (g_choices[i].N == N && g_choices[i].K == K && g_choices[i].epi == epi) { g_choices.erase(g_choices.begin() + i); break; }
+  if (s > 0) g_choices.push_back({N, K, epi, s, rows});
   return 0;
 }
 

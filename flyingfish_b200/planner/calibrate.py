@@ -194,6 +194,106 @@ def measure_disk_rate(runtime_dir: Path, nbytes: int = 64 << 20) -> float:
     return nbytes / dt
 
 
+# ------------------------------------------------------------------------------------------------
+# Kernel choices: decode-GEMM decompositions and the split-KV plan of decode attention, measured on the shapes of
+# the model (the reference's linear-algorithm and decode-attention-plan calibration, src/backend/cuda/calibrate.rs:396-580,
+# src/backend/cuda/linear_calibrate.rs). The winners go into the calibration file; ``apply_kernel_choices`` hands
+# them to the kernel library when a model is loaded.
+# ------------------------------------------------------------------------------------------------
+def decode_linear_shapes(spec, tp: int = 1) -> list[tuple[str, int, int, int]]:
+    """(name, N, K, epilogue id) of the decode projections of a dense / GQA layer on one rank of ``tp``."""
+    d, h = spec.head_dim, spec.hidden
+    hq, hkv = spec.heads // tp, max(1, spec.kv_heads // tp)
+    f = spec.ffn // tp
+    fused_rope = d == 128 and not spec.qk_norm
+    return [("qkv", (hq + 2 * hkv) * d, h, 2 if fused_rope else 0), ("o", h, hq * d, 0), ("gate_up", 2 * f, h, 1),
+            ("down", h, f, 0)]
+
+
+def linear_candidates(epi: int) -> list[tuple[int, int]]:
+    rows = (128,) if epi else (64, 96, 128)
+    return [(1, 128)] + [(s, r) for s in (2, 4, 8) for r in rows]
+
+
+def measure_linear_choices(spec, tp: int = 1, m: int = 64, iters: int = 12) -> dict:
+    """Times every launchable decomposition of every decode projection at ``m`` rows (cold L2) and returns
+    {name: {"n", "k", "epi", "s", "rows", "us", "default_us", "tried"}}. Leaves the winners installed."""
+    from .. import ops
+    from ..ops.lib import kernels
+    from ..utils.kbench import Flusher, time_op
+    import ctypes
+    dev = torch.device("cuda")
+    lib, flush, out = kernels(), Flusher(dev), {}
+    for name, n, k, epi in decode_linear_shapes(spec, tp):
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        w = (torch.randn(n, k, device=dev) * 0.05).to(torch.bfloat16)
+        # the rotary epilogue is timed through the plain epilogue with its tile constraint (128-row tiles)
+        fn = (lambda: ops.linear_swiglu(x, w)) if epi == 1 and n % 256 == 0 else (lambda: ops.linear(x, w))
+        lib.ff_gemm_skinny_set_choice(n, k, epi, 0, 0)
+        cfg = (ctypes.c_int * 5)()
+        lib.ff_gemm_skinny_config(m, n, k, epi, cfg)
+        key_epi = epi if (epi == 1 and n % 256 == 0) else 0
+        default_us = time_op(fn, iters, 3, flush)["us_median"]
+        best, tried = (cfg[0], cfg[1], default_us), 0
+        for s_, r_ in linear_candidates(epi):
+            lib.ff_gemm_skinny_set_choice(n, k, key_epi, s_, r_)
+            got = (ctypes.c_int * 5)()
+            lib.ff_gemm_skinny_config(m, n, k, key_epi, got)
+            if (got[0], got[1]) != (s_, r_):               # not launchable on this device: the plan ignored it
+                continue
+            tried += 1
+            us = time_op(fn, iters, 3, flush)["us_median"]
+            if us < best[2] * 0.97:                         # a change must win by more than the timer's noise
+                best = (s_, r_, us)
+        lib.ff_gemm_skinny_set_choice(n, k, key_epi, 0, 0)
+        if best[2] < default_us:
+            for e in {epi, key_epi}:
+                lib.ff_gemm_skinny_set_choice(n, k, e, best[0], best[1])
+        out[name] = {"n": n, "k": k, "epi": epi, "s": best[0], "rows": best[1], "us": best[2], "default_us": default_us,
+                     "tried": tried, "calibrated": best[2] < default_us}
+    return out
+
+
+def measure_attention_plan(spec, tp: int = 1, cases=((64, 1100), (8, 4096), (1, 8192)), iters: int = 10) -> dict:
+    """Times the split-KV decode attention for every wave target and returns the one with the least total time."""
+    from ..ops.lib import kernels
+    from ..utils import kbench
+    lib, res = kernels(), {}
+    hq, hkv = spec.heads // tp, max(1, spec.kv_heads // tp)
+    for waves in (1, 2, 4, 8):
+        lib.ff_attn_decode_set_waves(waves)
+        tot = 0.0
+        for batch, ctx in cases:
+            class B: pass
+            b = B(); b.batch, b.ctx, b.hq, b.hkv, b.iters, b.warmup, b.no_flush = batch, ctx, hq, hkv, iters, 2, False
+            tot += kbench.bench_attn_decode(b)["us_median"]
+        res[str(waves)] = tot
+    best = min(res, key=lambda w: res[w])
+    if res[best] > res["4"] * 0.97:
+        best = "4"
+    lib.ff_attn_decode_set_waves(int(best))
+    return {"waves": int(best), "total_us_by_waves": res, "cases": [list(c) for c in cases]}
+
+
+def apply_kernel_choices(data: dict | None) -> int:
+    """Install the choices of a calibration record into the kernel library; returns how many were applied."""
+    if not data or not torch.cuda.is_available():
+        return 0
+    from ..ops.lib import kernels
+    lib, n = kernels(), 0
+    for c in (data.get("linear_choices") or {}).values():
+        if c.get("calibrated"):
+            key_epi = c["epi"] if (c["epi"] == 1 and c["n"] % 256 == 0) else 0
+            for e in {c["epi"], key_epi}:
+                lib.ff_gemm_skinny_set_choice(int(c["n"]), int(c["k"]), int(e), int(c["s"]), int(c["rows"]))
+            n += 1
+    plan = data.get("attention_plan")
+    if plan and int(plan.get("waves", 4)) != 4:
+        lib.ff_attn_decode_set_waves(int(plan["waves"]))
+        n += 1
+    return n
+
+
 def calibrate(model: str | None, settings: Settings, force: bool = False, cpu: bool = False) -> dict:
     device = torch.device("cpu") if cpu or not torch.cuda.is_available() else torch.device("cuda", settings.device)
     rt = check_runtime_dir(settings.resolved_runtime_dir())
@@ -240,6 +340,11 @@ def calibrate(model: str | None, settings: Settings, force: bool = False, cpu: b
             b = B(); b.batch, b.ctx, b.hq, b.hkv, b.iters, b.warmup, b.no_flush = 1, cap, 32, 8, 5, 2, False
             att[str(cap)] = kbench.bench_attn_decode(b)["us_median"]
         data["decode_attention_us_by_capacity"] = att
+        if spec is not None and spec.mla is None and spec.head_dim == 128 and not spec.extra.get("v41"):
+            closure.measure("linear_choices")
+            data["linear_choices"] = measure_linear_choices(spec, max(settings.tp, 1))
+            closure.measure("attention_plan")
+            data["attention_plan"] = measure_attention_plan(spec, max(settings.tp, 1))
     closure.freeze()
     data["measurements"] = closure.measurements
     path.write_text(json.dumps(data, indent=1))

@@ -191,3 +191,35 @@ def test_catalogue_disk_tier_and_span_plan(tmp_path):
     assert plan.classes[0] == ExpertClass.RESIDENT and plan.classes[2] == ExpertClass.STAGED
     assert plan.classes[1] == ExpertClass.CPU and 3 not in plan.classes
     assert [c.experts for c in plan.cohorts] == [[2]] and plan.cpu_rows == 1
+
+
+def test_quantised_slot_layouts():
+    """Slot layouts of the quantised expert formats: slice sizes, 16-byte alignment, pack / view round trip."""
+    import torch
+    from flyingfish_b200.experts.catalogue import FORMATS, pack_slot, quant_slot_layout, slot_views
+    f, h = 96, 160
+    sizes = {}
+    for fmt in FORMATS:
+        lay = quant_slot_layout(fmt, f, h)
+        assert all(b % 16 == 0 for b, _ in lay.slices.values()) and lay.total % 16 == 0
+        sizes[fmt] = lay.total
+    assert sizes["bf16"] == sizes["bf16_separate"] == 3 * f * h * 2
+    lay = quant_slot_layout("fp8_block", f, h)
+    assert lay.code_bytes == 3 * f * h and lay.range("gate_scale")[1] - lay.range("gate_scale")[0] == 1 * 2 * 4
+    assert lay.range("down_scale")[1] - lay.range("down_scale")[0] == 2 * 1 * 4
+    assert quant_slot_layout("fp8_channel", f, h).scale_bytes == (f + f + h) * 4
+    e2 = quant_slot_layout("e2m1_block", f, h)
+    assert e2.code_bytes == 3 * f * h // 2 and e2.scale_bytes == 2 * f * (h // 32) + h * (f // 32)
+    nv = quant_slot_layout("nvfp4", f, h)
+    assert nv.scale_bytes == 2 * f * (h // 16) + h * (f // 16) + 12 and sizes["nvfp4"] < sizes["fp8_block"] < sizes["bf16"]
+    with pytest.raises(ValueError):
+        quant_slot_layout("e2m1_block", 100, 160)
+    g = torch.Generator().manual_seed(0)
+    t = {n: torch.randint(0, 255, (e - b,), generator=g, dtype=torch.uint8) for n, (b, e) in e2.slices.items()}
+    views = slot_views(e2, pack_slot(e2, t))
+    assert views["gate"].shape == (f, h // 2) and views["down_scale"].shape == (h, f // 32)
+    assert torch.equal(views["up"].reshape(-1), t["up"]) and torch.equal(views["gate_scale"].reshape(-1), t["gate_scale"])
+    fb = quant_slot_layout("fp8_block", 256, 384)
+    tb = {n: torch.randint(0, 255, (e - b,), generator=g, dtype=torch.uint8) for n, (b, e) in fb.slices.items()}
+    vb = slot_views(fb, pack_slot(fb, tb))
+    assert vb["gate_scale"].shape == (2, 3) and vb["down_scale"].shape == (3, 2) and vb["gate"].shape == (256, 384)
