@@ -637,6 +637,17 @@ static bool skinny_choice(int N, int K, int epi, int* s, int* rows) {
   return false;
 }
 
+static void skinny_fit_cluster(SkinnyConfig& c, int M, int N, int epi) {
+  const int s = c.cluster, ntok = (M + 15) / 16 * 16;
+  while (true) {
+    c.pipe_off = (s * ((M + s - 1) / s) * (c.tile_rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
+    c.stages = skinny_stages(c.tile_rows, c.pipe_off, ntok, sk_smem_for(M));
+    if (c.stages >= 3 || epi != 0 || c.tile_rows <= 64) break;
+    c.tile_rows = (c.tile_rows / 2 + 15) / 16 * 16;
+    c.tiles = (N + c.tile_rows - 1) / c.tile_rows;
+  }
+}
+
 // epi != 0 (row-wise epilogue): tiles are exactly 128 rows.
 static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
   const int kblocks = (K + SBK - 1) / SBK;
@@ -667,8 +678,7 @@ static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
       const int recv64 = (cal_s * ((64 + cal_s - 1) / cal_s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
       if (skinny_stages(rows, recv64) >= 3) {
         best = {cal_s, rows, tiles, 0, 0};
-        best.pipe_off = (cal_s * ((M + cal_s - 1) / cal_s) * (rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
-        best.stages = skinny_stages(rows, best.pipe_off, (M + 15) / 16 * 16, sk_smem_for(M));
+        skinny_fit_cluster(best, M, N, epi);
         return best;
       }
     }
@@ -714,11 +724,11 @@ static SkinnyConfig skinny_config(int M, int N, int K, int epi = 0) {
     }
   }
   if (best.cluster > 1) {
-    // the split (cluster, tile_rows) is fixed above for every M; the receive buffer and with it the pipeline depth
-    // follow the actual M
-    const int s = best.cluster;
-    best.pipe_off = (s * ((M + s - 1) / s) * (best.tile_rows + SP_PAD) * 4 + 1023) / 1024 * 1024;
-    best.stages = skinny_stages(best.tile_rows, best.pipe_off, (M + 15) / 16 * 16, sk_smem_for(M));
+    // the K split (cluster size) is fixed above for every M: it alone decides the order of the FP32 additions of an
+    // output element. The receive buffer and with it the pipeline depth follow the actual M; where many tokens and a
+    // wide tile leave fewer than three stages, the tile is narrowed (more clusters, possibly a second wave; the bits
+    // of every output stay the same)
+    skinny_fit_cluster(best, M, N, epi);
   } else {
     best.stages = skinny_stages(best.tile_rows, 0, (M + 15) / 16 * 16, sk_smem_for(M));
   }

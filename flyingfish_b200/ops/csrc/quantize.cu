@@ -39,6 +39,8 @@ __device__ __forceinline__ uint32_t e2m1_code(float v) {
 // one warp per (row, 128-group): lane holds 4 consecutive elements
 __global__ void quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                        float* __restrict__ scale, int rows, int K, int ldx, int ue8m0) {
+  pdl_trigger();
+  pdl_wait();
   const int groups = K >> 7;
   const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -130,8 +132,8 @@ FF_EXPORT int ff_quant_fp8_1x128(const void* x, void* q, float* scale, int rows,
                                  cudaStream_t s) {
   if (rows <= 0 || K <= 0 || K % 128 || ldx % 4) return FF_HOST_BAD_SHAPE;
   const long long warps = (long long)rows * (K / 128);
-  quant_fp8_1x128_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, s>>>((const __nv_bfloat16*)x, (uint8_t*)q, scale,
-                                                                              rows, K, ldx, ue8m0);
+  if (int lr = launch_pdl(quant_fp8_1x128_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, s, 0,
+                          (const __nv_bfloat16*)x, (uint8_t*)q, scale, rows, K, ldx, ue8m0)) return lr;
   return launch_result();
 }
 

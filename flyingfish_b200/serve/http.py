@@ -165,11 +165,9 @@ class Server:
                             raise bad_request("image_url is not valid base64")
                         if self.image_placeholder is None or images is None:
                             raise bad_request("this model has no vision tower: image input is not supported")
-                        if not url.startswith("data:image/png"):
-                            raise bad_request("only PNG images are decoded by this server")
                         try:
-                            from .image import decode_png
-                            images.append(decode_png(raw))
+                            from .image import decode_image
+                            images.append(decode_image(raw, url[5:].split(";")[0]))
                         except Exception as e:
                             raise bad_request(f"image_url does not decode: {e}")
                         parts.append(self.image_placeholder)

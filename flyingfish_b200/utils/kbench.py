@@ -42,10 +42,23 @@ class Flusher:
             self.buf.zero_()
 
 
-def time_op(fn, iters: int, warmup: int, flush: Flusher | None) -> dict:
+def time_op(fn, iters: int, warmup: int, flush: Flusher | None, graph: bool = False) -> dict:
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if graph:
+        # an operator of several launches: replayed from a CUDA graph so that host time between its launches (Python,
+        # allocator) does not sit inside the timed region, as in a captured decode step
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        fn = g.replay
     times = []
     for _ in range(iters):
         if flush is not None:
@@ -80,7 +93,7 @@ def bench_gemm(args) -> dict:
         byts = m * k * 2 + wq.nbytes() + m * n * 2
     else:
         fn = lambda: ops.linear(x, w, out=out)
-    r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
+    r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None, graph=getattr(args, "graph", False))
     pk = peaks()
     t = r["us_median"] * 1e-6
     r.update(op="gemm_torch" if args.torch else "gemm_fp8" if getattr(args, "fp8", False) else "gemm", m=m, n=n, k=k, gbs=byts / t / 1e9,
@@ -180,6 +193,7 @@ def main(argv=None) -> None:
             p.add_argument("--k", type=int, default=4096)
             p.add_argument("--torch", action="store_true", help="time torch.matmul (cuBLAS) instead, as the baseline")
             p.add_argument("--fp8", action="store_true", help="FP8-resident weight (E4M3, 128x128 scales), W8A8 kernel")
+            p.add_argument("--graph", action="store_true", help="replay the operator from a CUDA graph (no host gaps)")
         elif name == "moe":
             p.add_argument("--rows", type=int, default=128)
             p.add_argument("--experts", type=int, default=128)

@@ -64,3 +64,20 @@ def test_measure_and_apply_choices_on_a_small_shape():
             kernels().ff_gemm_skinny_set_choice(v["n"], v["k"], e, 0, 0)
     kernels().ff_attn_decode_set_waves(4)
     ops.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(128, 8192, 1024), (128, 8192, 3584), (96, 8192, 3584), (128, 6144, 4096)])
+def test_many_tokens_on_a_wide_cluster_tile(m, n, k):
+    """A cluster split chosen for 64 tokens with 256-row tiles leaves too little shared memory for 128 tokens: the
+    tile is narrowed for that launch, the K split (and with it every output bit) stays the same."""
+    from flyingfish_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    y = ops.linear(x, w)
+    want = x.float() @ w.float().t()
+    assert (y.float() - want).abs().max() <= 2e-2 * want.abs().max()
+    assert torch.equal(ops.linear(x[:7].contiguous(), w), y[:7])
+    assert torch.equal(ops.linear(x[:64].contiguous(), w), y[:64])
+    ops.check_status()
