@@ -198,7 +198,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                    const int* __restrict__ ctx_lens, const unsigned long long* __restrict__ tree_mask,
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
-                   int* status, int* __restrict__ split_counters, int window) {
+                   int* status, int* __restrict__ split_counters, int window, const int* __restrict__ kv_start,
+                   int pstride) {
   pdl_trigger();
   if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 0);
   pdl_wait();
@@ -214,7 +215,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int pages = (ctx + PAGE - 1) / PAGE;
   // sliding window (models with local-attention layers; not combined with tree masks): the query at position pos
   // sees keys pos - window + 1 .. pos, so the pages before the earliest bound of the nq queries are not visited
-  const int pfirst = window > 0 ? max(0, ctx - nq - window + 1) / PAGE : 0;
+  // kv_start (mixed cache formats): keys below kv_start[b] (a multiple of the page size) are not in BF16 pages any
+  // more; another kernel covers them and writes its partials behind this kernel's splits (stride pstride)
+  int pfirst = window > 0 ? max(0, ctx - nq - window + 1) / PAGE : 0;
+  if (kv_start != nullptr) pfirst = max(pfirst, min(kv_start[b], ctx) / PAGE);
   const int per = (pages - pfirst + nsplit - 1) / nsplit;
   const int p0 = pfirst + split * per, p1 = min(pages, p0 + per);
   const int rows_total = nq * G;
@@ -322,10 +326,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       float acc = 0.f;
 #pragma unroll
       for (int w = 0; w < NW; ++w) acc += so[(w * 16 + r) * HD + d] * sc[w];
-      if (nsplit == 1) {
+      if (nsplit == 1 && pstride == 0) {
         out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
       } else {
-        const size_t pr = ((size_t)b * nsplit + split) * (nq * hq) + (size_t)qi * hq + hh;
+        const size_t pr = ((size_t)b * (pstride ? pstride : nsplit) + split) * (nq * hq) + (size_t)qi * hq + hh;
         part_o[pr * HD + d] = acc;
         if (d == 0) {
           part_ml[pr * 2] = M; part_ml[pr * 2 + 1] = L;
@@ -334,7 +338,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     }
   }
-  if (nsplit > 1 && split_counters != nullptr) {
+  if (nsplit > 1 && split_counters != nullptr && pstride == 0) {
     // the split that arrives last merges the partials of this (sequence, kv head, row tile): no second launch
     __shared__ int s_last;
     __threadfence();
@@ -510,8 +514,9 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
                               const int* ctx_lens, const unsigned long long* tree_mask, void* out, float* part_o,
                               float* part_ml, int batch, int hq, int hkv, int head_dim, int nq, int ldq, int max_blocks,
                               int num_blocks, int nsplit, float scale, int* split_counters, int* status, cudaStream_t s,
-                              int window) {
+                              int window, const int* kv_start = nullptr, int pstride = 0) {
   if (window > 0 && tree_mask) return FF_HOST_UNSUPPORTED;
+  if (pstride != 0 && (pstride < nsplit || !part_o || !part_ml)) return FF_HOST_BAD_SHAPE;
   if (head_dim != HD || batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv) return FF_HOST_BAD_SHAPE;
   if (nq < 1 || nq > 64) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || nsplit < 1) return FF_HOST_BAD_ALIGN;
@@ -528,8 +533,9 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
   if (int r = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, HD, cache_rows, HD * 2, 64, PAGE)) return r;
   if (int lr_ = launch_pdl(attn_decode_kernel<NW>, dim3(grid), dim3(32 * NW), DEC_SMEM, s, 0, tmK, tmV, (const __nv_bfloat16*)q,
       block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
-      ldq, max_blocks, num_blocks, nsplit, scale_log2, status, split_counters, window)) return lr_;
+      ldq, max_blocks, num_blocks, nsplit, scale_log2, status, split_counters, window, kv_start, pstride)) return lr_;
   if (int r = launch_result()) return r;
+  if (pstride != 0) return 0;                      // partials only: the caller merges after the other kernel has added its own
   if (nsplit > 1 && split_counters == nullptr) {
     if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * nq * hq), dim3(128), 0, s, 0, part_o, part_ml, (__nv_bfloat16*)out, nq * hq, nsplit)) return lr_;
     return launch_result();
@@ -543,6 +549,27 @@ FF_EXPORT int ff_attn_decode(const void* q, const void* kcache, const void* vcac
                              int num_blocks, int nsplit, float scale, int* split_counters, int* status, cudaStream_t s) {
   return attn_decode_launch(q, kcache, vcache, block_table, ctx_lens, tree_mask, out, part_o, part_ml, batch, hq, hkv,
                             head_dim, nq, ldq, max_blocks, num_blocks, nsplit, scale, split_counters, status, s, 0);
+}
+
+// BF16 part of a decode step over a cache whose older keys are sealed in the 8-bit store: visits the pages from
+// kv_start[b] on and writes partials only, at split indices [0, nsplit) of a buffer with `pstride` splits per
+// sequence; ff_attn_merge finishes after the sealed-part kernel has written the other splits.
+FF_EXPORT int ff_attn_decode_partial(const void* q, const void* kcache, const void* vcache, const int* block_table,
+                                     const int* ctx_lens, const int* kv_start, float* part_o, float* part_ml, int batch,
+                                     int hq, int hkv, int head_dim, int ldq, int max_blocks, int num_blocks, int nsplit,
+                                     int pstride, float scale, int* status, cudaStream_t s) {
+  if (!kv_start || pstride < 1) return FF_HOST_BAD_SHAPE;
+  return attn_decode_launch(q, kcache, vcache, block_table, ctx_lens, nullptr, nullptr, part_o, part_ml, batch, hq, hkv,
+                            head_dim, 1, ldq, max_blocks, num_blocks, nsplit, scale, nullptr, status, s, 0, kv_start, pstride);
+}
+
+// Merge `nsplit` partials per (sequence row, head) into out [rows * hq, 128] bf16.
+FF_EXPORT int ff_attn_merge(const float* part_o, const float* part_ml, void* out, int batch, int rows_per_seq, int nsplit,
+                            cudaStream_t s) {
+  if (batch <= 0 || rows_per_seq <= 0 || nsplit < 1) return FF_HOST_BAD_SHAPE;
+  if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * rows_per_seq), dim3(128), 0, s, 0, part_o, part_ml,
+                           (__nv_bfloat16*)out, rows_per_seq, nsplit)) return lr_;
+  return launch_result();
 }
 
 // Decode attention of a local-attention layer: every query sees its last `window` keys.

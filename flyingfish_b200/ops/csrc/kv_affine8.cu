@@ -80,6 +80,204 @@ __global__ void kv_unpack_kernel(const uint8_t* __restrict__ codes, const float*
   dst[at] = __float2bfloat16_rn(__fadd_rn(__fmul_rn((float)codes[at], stats[si + 1]), stats[si]));
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Paged compact store. The engine seals whole 128-token groups of a sequence that have left the recent window: the
+// two BF16 blocks of a group are packed into one slot of a per-layer pool and given back to the block allocator (all
+// but block 0: the first 64 tokens, the sink, stay BF16).
+//   pool k_codes / v_codes [slots, hkv, 128, D] uint8 ; k_stats [slots, hkv, D, 2] ; v_stats [slots, hkv, 128, 2]
+// ---------------------------------------------------------------------------------------------------------------
+// grid (n, hkv), 128 threads; blk_a / blk_b / slot: int32[n] (the two cache blocks of a group and its pool slot).
+__global__ void __launch_bounds__(128)
+kv_seal_groups_kernel(const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
+                      const int* __restrict__ blk_a, const int* __restrict__ blk_b, const int* __restrict__ slot,
+                      uint8_t* __restrict__ k_codes, uint8_t* __restrict__ v_codes, float* __restrict__ k_stats,
+                      float* __restrict__ v_stats, int hkv, int D, int num_blocks, int slots, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ba = blk_a[i], bb = blk_b[i], sl = slot[i];
+  if (ba < 0 || ba >= num_blocks || bb < 0 || bb >= num_blocks || sl < 0 || sl >= slots) {
+    if (tid == 0) set_status(status, KID_KV, FF_ERR_BOUNDS, i, sl);
+    return;
+  }
+  const size_t obase = ((size_t)sl * hkv + h) * KV_GROUP;           // token row base inside the pool
+  // K: thread = channel (D <= 128 per pass)
+  for (int d = tid; d < D; d += 128) {
+    float lo = 3.402823466e38f, hi = -3.402823466e38f;
+    for (int r = 0; r < KV_GROUP; ++r) {
+      const int blk = r < 64 ? ba : bb;
+      const float x = __bfloat162float(kcache[(((size_t)blk * hkv + h) * 64 + (r & 63)) * D + d]);
+      lo = fminf(lo, x); hi = fmaxf(hi, x);
+    }
+    if (!(fabsf(lo) <= 3.4e38f) || !(fabsf(hi) <= 3.4e38f)) { set_status(status, KID_KV, FF_ERR_NONFINITE, h, sl); lo = 0.f; hi = 0.f; }
+    const float span = __fsub_rn(hi, lo), scale = span == 0.f ? 1.f : __fdiv_rn(span, 255.f);
+    k_stats[(((size_t)sl * hkv + h) * D + d) * 2] = lo;
+    k_stats[(((size_t)sl * hkv + h) * D + d) * 2 + 1] = scale;
+    for (int r = 0; r < KV_GROUP; ++r) {
+      const int blk = r < 64 ? ba : bb;
+      const float x = __bfloat162float(kcache[(((size_t)blk * hkv + h) * 64 + (r & 63)) * D + d]);
+      k_codes[(obase + r) * D + d] = kv_code(x, lo, scale);
+    }
+  }
+  // V: one warp per token
+  for (int r = warp; r < KV_GROUP; r += 4) {
+    const int blk = r < 64 ? ba : bb;
+    const __nv_bfloat16* src = vcache + (((size_t)blk * hkv + h) * 64 + (r & 63)) * D;
+    float lo = 3.402823466e38f, hi = -3.402823466e38f;
+    for (int d = lane; d < D; d += 32) { const float x = __bfloat162float(src[d]); lo = fminf(lo, x); hi = fmaxf(hi, x); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o)); }
+    if (!(fabsf(lo) <= 3.4e38f) || !(fabsf(hi) <= 3.4e38f)) { if (lane == 0) set_status(status, KID_KV, FF_ERR_NONFINITE, h, sl); lo = 0.f; hi = 0.f; }
+    const float span = __fsub_rn(hi, lo), scale = span == 0.f ? 1.f : __fdiv_rn(span, 255.f);
+    if (lane == 0) { v_stats[(obase + r) * 2] = lo; v_stats[(obase + r) * 2 + 1] = scale; }
+    for (int d = lane; d < D; d += 32) v_codes[(obase + r) * D + d] = kv_code(__bfloat162float(src[d]), lo, scale);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Decode attention over the sealed groups of every sequence (one query row per sequence, head_dim 128): the partial
+// (max, sum, weighted values) of each chunk of groups goes into the split-KV partial buffers of the BF16 decode
+// kernel, behind its own splits, and the common merge kernel finishes. Keys and values are the dequantised rows
+// bf16(code * scale + lo); scores and the soft-max run in FP32 in the base-2 domain like the BF16 kernel. The first 64
+// tokens of group 0 (the sink) are read from BF16 block `block_table[b][0]`.
+//   grid (chunks, hkv, batch), 128 threads; group_table [batch, max_groups] pool slots; sealed [batch] tokens sealed
+//   part index: ((b * pstride + split_base + chunk) * hq + head)
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int SEAL_MAXG = 16;      // query heads per KV head
+
+__global__ void __launch_bounds__(128)
+attn_sealed_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t* __restrict__ k_codes, const uint8_t* __restrict__ v_codes,
+                   const float* __restrict__ k_stats, const float* __restrict__ v_stats,
+                   const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
+                   const int* __restrict__ block_table, const int* __restrict__ group_table, const int* __restrict__ sealed,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, int hq, int hkv, int ldq, int max_blocks,
+                   int num_blocks, int max_groups, int slots, int groups_per_chunk, int split_base, int pstride,
+                   float scale_log2, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int D = 128;
+  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = hq / hkv;
+  __shared__ float sq[SEAL_MAXG][D];          // queries * scale (base-2)
+  __shared__ float sk_lo[D], sk_sc[D];
+  __shared__ float sp[SEAL_MAXG][KV_GROUP];   // probabilities of the current group
+  __shared__ float sv_lo[KV_GROUP], sv_sc[KV_GROUP];
+  __shared__ float sred[4][SEAL_MAXG];
+  __shared__ float sm_new[SEAL_MAXG], scorr[SEAL_MAXG];
+  const int ngroups = min(sealed[b] / KV_GROUP, max_groups);
+  const int g0 = chunk * groups_per_chunk, g1 = min(ngroups, g0 + groups_per_chunk);
+  for (int i = tid; i < G * D; i += 128) {
+    const int g = i / D, c = i - g * D;
+    sq[g][c] = __bfloat162float(q[(size_t)b * ldq + (size_t)(kvh * G + g) * D + c]) * scale_log2;
+  }
+  float m[SEAL_MAXG], l[SEAL_MAXG], acc[SEAL_MAXG];
+#pragma unroll
+  for (int g = 0; g < SEAL_MAXG; ++g) { m[g] = -3.0e38f; l[g] = 0.f; acc[g] = 0.f; }
+  __syncthreads();
+  for (int grp = g0; grp < g1; ++grp) {
+    const int sl = group_table[(size_t)b * max_groups + grp];
+    if (sl < 0 || sl >= slots) { if (tid == 0) set_status(status, KID_KV, FF_ERR_BOUNDS, b, grp); break; }
+    const size_t tb = ((size_t)sl * hkv + kvh) * KV_GROUP;
+    sk_lo[tid] = k_stats[(((size_t)sl * hkv + kvh) * D + tid) * 2];
+    sk_sc[tid] = k_stats[(((size_t)sl * hkv + kvh) * D + tid) * 2 + 1];
+    sv_lo[tid] = v_stats[(tb + tid) * 2];
+    sv_sc[tid] = v_stats[(tb + tid) * 2 + 1];
+    __syncthreads();
+    // scores of token `tid` for every head
+    float s[SEAL_MAXG];
+#pragma unroll
+    for (int g = 0; g < SEAL_MAXG; ++g) s[g] = 0.f;
+    const bool sink = grp == 0 && tid < 64;
+    int blk0 = 0;
+    if (grp == 0) {
+      blk0 = block_table[(size_t)b * max_blocks];
+      if (blk0 < 0 || blk0 >= num_blocks) { if (tid == 0) set_status(status, KID_KV, FF_ERR_BOUNDS, b, blk0); blk0 = 0; }
+    }
+    if (sink) {
+      const uint4* kr = reinterpret_cast<const uint4*>(kcache + (((size_t)blk0 * hkv + kvh) * 64 + tid) * D);
+      for (int c8 = 0; c8 < D / 8; ++c8) {
+        const uint4 v = kr[c8];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 kk = __bfloat1622float2(h2[j]);
+#pragma unroll
+          for (int g = 0; g < SEAL_MAXG; ++g)
+            if (g < G) s[g] += sq[g][c8 * 8 + 2 * j] * kk.x + sq[g][c8 * 8 + 2 * j + 1] * kk.y;
+        }
+      }
+    } else {
+      const uint4* kr = reinterpret_cast<const uint4*>(k_codes + (tb + tid) * D);
+      for (int c16 = 0; c16 < D / 16; ++c16) {
+        const uint4 v = kr[c16];
+        const uint8_t* cb = reinterpret_cast<const uint8_t*>(&v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int c = c16 * 16 + j;
+          const float kk = __bfloat162float(__float2bfloat16_rn(__fadd_rn(__fmul_rn((float)cb[j], sk_sc[c]), sk_lo[c])));
+#pragma unroll
+          for (int g = 0; g < SEAL_MAXG; ++g)
+            if (g < G) s[g] += sq[g][c] * kk;
+        }
+      }
+    }
+    // block maximum per head
+#pragma unroll
+    for (int g = 0; g < SEAL_MAXG; ++g) {
+      if (g < G) {
+        float v = s[g];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+        if (lane == 0) sred[warp][g] = v;
+      }
+    }
+    __syncthreads();
+    if (tid < G) {
+      const float bm = fmaxf(fmaxf(sred[0][tid], sred[1][tid]), fmaxf(sred[2][tid], sred[3][tid]));
+      sm_new[tid] = bm;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < SEAL_MAXG; ++g) {
+      if (g < G) {
+        const float mn = fmaxf(m[g], sm_new[g]);
+        const float corr = exp2f(m[g] - mn);
+        const float p = exp2f(s[g] - mn);
+        sp[g][tid] = p;
+        float ps = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        if (lane == 0) sred[warp][g] = ps;
+        l[g] *= corr; acc[g] *= corr; m[g] = mn;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < SEAL_MAXG; ++g)
+      if (g < G) l[g] += sred[0][g] + sred[1][g] + sred[2][g] + sred[3][g];
+    // values: thread = channel
+    for (int t = 0; t < KV_GROUP; ++t) {
+      float vv;
+      if (grp == 0 && t < 64) vv = __bfloat162float(vcache[(((size_t)blk0 * hkv + kvh) * 64 + t) * D + tid]);
+      else vv = __bfloat162float(__float2bfloat16_rn(__fadd_rn(__fmul_rn((float)v_codes[(tb + t) * D + tid], sv_sc[t]), sv_lo[t])));
+#pragma unroll
+      for (int g = 0; g < SEAL_MAXG; ++g)
+        if (g < G) acc[g] += sp[g][t] * vv;
+    }
+    __syncthreads();
+  }
+  // partials: every thread holds (m, l) of all heads (identical across threads) and channel `tid` of the values
+#pragma unroll
+  for (int g = 0; g < SEAL_MAXG; ++g) {
+    if (g < G) {
+      const size_t pr = ((size_t)b * pstride + split_base + chunk) * hq + (size_t)kvh * G + g;
+      part_o[pr * D + tid] = acc[g];
+      if (tid == 0) { part_ml[pr * 2] = m[g]; part_ml[pr * 2 + 1] = l[g]; }
+    }
+  }
+}
+
 }  // namespace ff
 using namespace ff;
 
@@ -108,5 +306,36 @@ FF_EXPORT int ff_kv_unpack(const void* codes, const float* stats, void* dst, int
   const size_t total = (size_t)heads * tokens * D;
   if (int lr = launch_pdl(kv_unpack_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (const uint8_t*)codes, stats,
                           (__nv_bfloat16*)dst, capacity, D, heads, pos0, tokens, is_k)) return lr;
+  return launch_result();
+}
+
+// Seal n groups of one layer: blocks (blk_a[i], blk_b[i]) -> pool slot slot[i]. head_dim D (multiple of 32, <= 256).
+FF_EXPORT int ff_kv_seal_groups(const void* kcache, const void* vcache, const int* blk_a, const int* blk_b, const int* slot,
+                                int n, void* k_codes, void* v_codes, float* k_stats, float* v_stats, int hkv, int D,
+                                int num_blocks, int slots, int* status, cudaStream_t s) {
+  if (n <= 0 || hkv <= 0 || D <= 0 || D % 32 || D > 256 || num_blocks <= 0 || slots <= 0) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(kv_seal_groups_kernel, dim3(n, hkv), dim3(128), 0, s, 0, (const __nv_bfloat16*)kcache,
+                          (const __nv_bfloat16*)vcache, blk_a, blk_b, slot, (uint8_t*)k_codes, (uint8_t*)v_codes, k_stats,
+                          v_stats, hkv, D, num_blocks, slots, status)) return lr;
+  return launch_result();
+}
+
+// Partials of the sealed part of a decode step (see attn_sealed_kernel). chunks = ceil(max_groups / groups_per_chunk)
+// splits are written for every (sequence, head), neutral where a sequence has nothing sealed there.
+FF_EXPORT int ff_attn_sealed(const void* q, const void* k_codes, const void* v_codes, const float* k_stats,
+                             const float* v_stats, const void* kcache, const void* vcache, const int* block_table,
+                             const int* group_table, const int* sealed, float* part_o, float* part_ml, int batch, int hq,
+                             int hkv, int head_dim, int ldq, int max_blocks, int num_blocks, int max_groups, int slots,
+                             int groups_per_chunk, int split_base, int pstride, float scale, int* status, cudaStream_t s) {
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv || hq / hkv > SEAL_MAXG || head_dim != 128) return FF_HOST_BAD_SHAPE;
+  if (max_groups <= 0 || groups_per_chunk <= 0 || slots <= 0 || !(scale > 0.f)) return FF_HOST_BAD_SHAPE;
+  const int chunks = (max_groups + groups_per_chunk - 1) / groups_per_chunk;
+  if (split_base < 0 || split_base + chunks > pstride) return FF_HOST_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(k_codes) & 15) || (reinterpret_cast<uintptr_t>(kcache) & 15)) return FF_HOST_BAD_ALIGN;
+  if (int lr = launch_pdl(attn_sealed_kernel, dim3(chunks, hkv, batch), dim3(128), 0, s, 0, (const __nv_bfloat16*)q,
+                          (const uint8_t*)k_codes, (const uint8_t*)v_codes, k_stats, v_stats, (const __nv_bfloat16*)kcache,
+                          (const __nv_bfloat16*)vcache, block_table, group_table, sealed, part_o, part_ml, hq, hkv, ldq,
+                          max_blocks, num_blocks, max_groups, slots, groups_per_chunk, split_base, pstride,
+                          scale * 1.4426950408889634f, status)) return lr;
   return launch_result();
 }
