@@ -43,6 +43,7 @@ def _global_parser() -> argparse.ArgumentParser:
     p.add_argument("--spec-graph", type=lambda s: s.lower() != "false", default=True)
     p.add_argument("--prefix-cache", type=lambda s: s.lower() == "true", default=False)
     p.add_argument("--kv-format", choices=["bf16", "affine8"], default="bf16")
+    p.add_argument("--kv-recent", type=int, default=2048, help="affine8: newest tokens kept in BF16 (older 128-token groups are sealed)")
     p.add_argument("--runtime-dir", default=os.environ.get("FLYINGFISH_RUNTIME_DIR"))
     p.add_argument("--dram-gb-s", type=float, default=6550.0)
     p.add_argument("--gemm-tflops", type=float, default=1385.0)
@@ -158,7 +159,7 @@ def settings_from(args) -> Settings:
                     device_budget_gib=args.device_budget_gib, draft_model=args.draft_model,
                     tree_builder=args.tree_builder,
                     spec_budget=args.spec_budget if args.draft_model else "chain",
-                    spec_graph=args.spec_graph, prefix_cache=args.prefix_cache, kv_format=args.kv_format,
+                    spec_graph=args.spec_graph, prefix_cache=args.prefix_cache, kv_format=args.kv_format, kv_recent=args.kv_recent,
                     runtime_dir=args.runtime_dir, dram_gb_s=args.dram_gb_s, gemm_tflops=args.gemm_tflops,
                     verbose=args.verbose, max_batch=args.max_batch, tp=args.tp)
 
@@ -178,8 +179,11 @@ def resolve_mtp_depth(requested: int | None, has_mtp: bool, arch: str) -> int:
 def check_flags(args) -> None:
     """Every flag either changes behaviour or is refused: nothing is parsed and then ignored."""
     if args.kv_format != "bf16":
-        raise SystemExit("--kv-format affine8: the 8-bit cache format is implemented as pack/unpack kernels and byte "
-                         "accounting only; no attention kernel reads its codes yet, so serving from it is refused")
+        # the sealed 8-bit store is read by plain decode steps only
+        if args.draft_model or args.prefix_cache or args.command in DSPARK_TOOLS + ("verify-spec", "bench-spec", "profile-spec") \
+                or (args.command == "serve" and getattr(args, "mtp", None) not in (None, 0)):
+            raise SystemExit("--kv-format affine8 does not combine with speculative decoding or the prefix cache "
+                             "(verification rows and shared prefixes read BF16 pages)")
     if args.tp < 1 or (args.tp > 1 and args.cpu):
         raise SystemExit("--tp needs one CUDA device per rank")
     if args.tp > 1 and args.command not in ("generate", "bench", "serve"):
@@ -308,6 +312,9 @@ def cmd_generate(args) -> dict:
         store = model.prefix_store()
         if store is not None:
             extra = {"prefix_cache": {"hits": store.hits, "stored": store.stored, "dir": str(store.root)}}
+    if model.engine.kv.compact is not None:
+        c = model.engine.kv.compact
+        extra = dict(extra, kv={"format": "affine8", "recent": c.recent, **c.stats})
     if trace is not None:
         trace.save(args.dump)
     return {"input_ids": ids, "generated_ids": out.ids, "text": tk.decode(out.ids), "load_ms": model.load_ms,

@@ -368,6 +368,7 @@ class Settings:
     spec_graph: bool = True
     prefix_cache: bool = False
     kv_format: str = "bf16"               # bf16 | affine8
+    kv_recent: int = 2048                 # affine8: tokens behind the newest that stay BF16 (groups older than that are sealed)
     runtime_dir: str | None = None
     dram_gb_s: float = 6550.0             # roofline denominators (measured on the target box)
     gemm_tflops: float = 1385.0

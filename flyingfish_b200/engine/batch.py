@@ -21,6 +21,7 @@ class BatchLayout:
     max_batch: int
     max_rows: int
     max_blocks: int
+    max_groups: int = 0               # > 0: the sequences may have sealed 8-bit groups (kv_start + group table fields)
 
     def __post_init__(self) -> None:
         o = 0
@@ -34,6 +35,8 @@ class BatchLayout:
         self.logit_rows = o; o += self.n_logit
         self.block_table = o; o += self.max_batch * self.max_blocks
         self.tree_mask = o; o += 2 * self.max_rows        # int64 per row, stored as two int32
+        self.kv_start = o; o += self.max_batch if self.max_groups else 0
+        self.groups = o; o += self.max_batch * self.max_groups
         self.total = o
 
 
@@ -80,6 +83,16 @@ class ForwardBatch:
         L = self.layout
         return self.dev[L.block_table: L.block_table + L.max_batch * L.max_blocks].view(L.max_batch, L.max_blocks)[: self.batch]
     @property
+    def kv_start(self) -> torch.Tensor | None:
+        L = self.layout
+        return self._v(L.kv_start, self.batch) if L.max_groups else None
+    @property
+    def group_table(self) -> torch.Tensor | None:
+        L = self.layout
+        if not L.max_groups:
+            return None
+        return self.dev[L.groups: L.groups + L.max_batch * L.max_groups].view(L.max_batch, L.max_groups)[: self.batch]
+    @property
     def tree_mask(self) -> torch.Tensor | None:
         if not self.use_tree_mask:
             return None
@@ -88,7 +101,7 @@ class ForwardBatch:
 
     # -- host fill -----------------------------------------------------------------------------
     def fill(self, *, ids, positions, slots, q_lens, ctx_lens, block_rows, logit_rows, is_decode: bool, nq: int = 1,
-             tree_mask=None) -> None:
+             tree_mask=None, kv_start=None, group_rows=None) -> None:
         """Write one step's metadata into the pinned host buffer (lists of ints)."""
         L = self.layout
         h = self.host
@@ -125,6 +138,16 @@ class ForwardBatch:
                 sig[i] = t
             else:
                 sig.extend([None] * (i - len(sig)) + [t])
+        if L.max_groups:
+            ks = torch.zeros(batch, dtype=torch.int32)
+            if kv_start is not None:
+                ks[: len(kv_start)] = torch.as_tensor(kv_start, dtype=torch.int32)
+            h[L.kv_start: L.kv_start + batch] = ks
+            gt = h[L.groups: L.groups + L.max_batch * L.max_groups].view(L.max_batch, L.max_groups)
+            for i, row in enumerate(group_rows or []):
+                if row:
+                    assert len(row) <= L.max_groups
+                    gt[i, : len(row)] = torch.as_tensor(row, dtype=torch.int32)
         self.max_q_len = int(max(q_lens)) if batch else 0
         self.max_ctx = int(max(ctx_lens)) if batch else 0
         self.use_tree_mask = tree_mask is not None

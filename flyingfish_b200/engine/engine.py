@@ -79,6 +79,16 @@ class Engine:
             self.kv = PagedKVCache(spec.layers, 1, 8, num_blocks, settings.kv_block, dtype, self.device, v_head_dim=0)
         else:
             self.kv = PagedKVCache(spec.layers, hkv, spec.head_dim, num_blocks, settings.kv_block, dtype, self.device)
+        # 8-bit store behind the block cache: groups that leave the recent window are sealed after every step
+        self.max_groups = 0
+        if settings.kv_format == "affine8":
+            from .kv_compact import CompactKV
+            if spec.mla is not None or getattr(model, "state_slot_count", 0) or getattr(model, "owns_token_state", False) \
+                    or spec.head_dim != 128 or settings.kv_block != 64 or spec.extra.get("gemma"):
+                raise ValueError("--kv-format affine8 needs a GQA decoder with 128-wide heads and 64-token blocks")
+            self.kv.compact = CompactKV(spec.layers, hkv, spec.head_dim, max(num_blocks // 2, 1), self.device,
+                                        recent=settings.kv_recent)
+            self.max_groups = max(settings.capacity // 128, 1)
         self.max_blocks = (settings.capacity + settings.kv_block - 1) // settings.kv_block
         self.max_batch = max(settings.max_batch, 1)
         self.max_prefill_rows = max_prefill_rows
@@ -295,8 +305,13 @@ class Engine:
         pad = bucket - len(seqs)
         ids += [0] * pad; positions += [0] * pad; slots += [-1] * pad
         q_lens += [1] * pad; ctx_lens += [0] * pad; block_rows += [[]] * pad
+        kv_start = group_rows = None
+        if self.kv.compact is not None:
+            c = self.kv.compact
+            kv_start = [c.sealed_tokens(s.seq_id) for s in seqs]
+            group_rows = [c.groups.get(s.seq_id, []) for s in seqs]
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
-                logit_rows=list(range(bucket)), is_decode=True, nq=1)
+                logit_rows=list(range(bucket)), is_decode=True, nq=1, kv_start=kv_start, group_rows=group_rows)
         fb.max_ctx = self.settings.capacity      # fixed launch geometry (graph-stable)
         if self.state_slots is not None:
             fb.state_slots = [s.state_slot for s in seqs] + [self.scratch_slot] * pad
@@ -304,7 +319,7 @@ class Engine:
     def _decode_batch(self, bucket: int) -> ForwardBatch:
         fb = self.eager_decode_batch.get(bucket)
         if fb is None:
-            fb = ForwardBatch(BatchLayout(bucket, bucket, self.max_blocks), self.device)
+            fb = ForwardBatch(BatchLayout(bucket, bucket, self.max_blocks, self.max_groups), self.device)
             self.eager_decode_batch[bucket] = fb
         return fb
 
@@ -377,6 +392,7 @@ class Engine:
                 self.kv.commit(s.seq_id, 1)
                 s.pending = t
                 s.output.append(t)
+            self._seal(seqs)
             self.stats["decode_steps"] += 1
             self.stats["decode_tokens"] += n
             return toks
@@ -385,6 +401,20 @@ class Engine:
         except Exception:
             self.poisoned = True
             raise
+
+    def _seal(self, seqs: list[Sequence]) -> None:
+        """Affine8 cache: pack the groups that left the recent window and give their BF16 blocks back. Runs between
+        steps on the launching stream; prompts are sealed once they are complete (prefill chunks read BF16 only)."""
+        c = self.kv.compact
+        if c is None:
+            return
+        for s in seqs:
+            if s.prefilled >= len(s.prompt):
+                c.seal(self.kv, s.seq_id)
+
+    def _no_compact(self, what: str) -> None:
+        if self.kv.compact is not None:
+            raise ValueError(f"{what} reads BF16 pages only and is not available with --kv-format affine8")
 
     # -- speculative verification --------------------------------------------------------------
     def verify(self, seqs: list[Sequence], drafts: list[list[int]], return_hidden: bool = False,
@@ -397,6 +427,7 @@ class Engine:
         cache needs no copy-back, unlike the reference's gather/scatter of tree rows,
         kernels/tree/meta.cu)."""
         self._check()
+        self._no_compact("speculative verification")
         if self.fail_next_step:
             self.fail_next_step = False
             self.poisoned = True
@@ -445,6 +476,7 @@ class Engine:
         returns the logits (or greedy ids) of every row. The K/V rows written stay behind the
         committed length and are overwritten by whatever runs next."""
         self._check()
+        self._no_compact("an uncommitted multi-row forward")
         kvs = self.kv.seqs[seq.seq_id]
         n = len(tokens)
         sl = self.kv.reserve(seq.seq_id, n)
@@ -460,6 +492,7 @@ class Engine:
         ancestor-or-self) restricts what it sees among the tree rows. Returns the target's greedy
         token after every row."""
         self._check()
+        self._no_compact("tree verification")
         try:
             kvs = self.kv.seqs[seq.seq_id]
             n = len(tokens)

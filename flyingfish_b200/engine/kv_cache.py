@@ -79,6 +79,7 @@ class PagedKVCache:
                   for _ in range(layers)] if vd > 0 else [None] * layers
         self.alloc = BlockAllocator(num_blocks)
         self.seqs: dict[int, SequenceKV] = {}
+        self.compact = None                 # engine.kv_compact.CompactKV when the cache format is affine8
 
     # -- sizing ----------------------------------------------------------------------------
     @staticmethod
@@ -97,7 +98,10 @@ class PagedKVCache:
     def free_sequence(self, seq_id: int) -> None:
         s = self.seqs.pop(seq_id)
         for b in s.blocks:
-            self.alloc.release(b)
+            if b >= 0:                      # -1: sealed into the compact store and released then
+                self.alloc.release(b)
+        if self.compact is not None:
+            self.compact.free_sequence(seq_id)
 
     def blocks_needed(self, seq_id: int, new_tokens: int) -> int:
         s = self.seqs[seq_id]

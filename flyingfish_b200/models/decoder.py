@@ -69,7 +69,11 @@ class DecoderModel:
         else:
             qkv = ops.linear_rope_kv(n, lw.wqkv, b.positions, b.slots, kv.k[i], kv.v[i], self.hq, self.hkv, self.d,
                                      s.rope_theta, cos_sin=self._rope_cs)
-        if b.is_decode:
+        if b.is_decode and kv.compact is not None and b.kv_start is not None:
+            # older keys live in the sealed 8-bit store: BF16 pages + sealed groups, one merge
+            a = ops.attn_decode_mixed(qkv, kv.k[i], kv.v[i], kv.compact, i, b.block_table, b.ctx_lens, b.kv_start,
+                                      b.group_table, self.hq, self.hkv, self.d, self.scale, max_ctx=b.max_ctx)
+        elif b.is_decode:
             a = ops.attn_decode(qkv, kv.k[i], kv.v[i], b.block_table, b.ctx_lens, self.hq, self.hkv, self.d,
                                 self.scale, nq=b.nq, tree_mask=b.tree_mask, max_ctx=b.max_ctx)
         else:
@@ -144,6 +148,8 @@ class DecoderModel:
         from ..ops import chain
         s = self.spec
         if not (chain.ENABLED and b.is_decode and b.positions.is_cuda and b.rows <= chain.MAX_ROWS):
+            return False
+        if getattr(b, "kv_start", None) is not None:
             return False
         if getattr(self.comm, "size", 1) != 1 or self.trace is not None or self.capture_taps or s.qk_norm:
             return False

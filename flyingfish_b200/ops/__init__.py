@@ -458,6 +458,73 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, blo
     return out
 
 
+def attn_decode_mixed(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, compact, layer: int,
+                      block_table: torch.Tensor, ctx_lens: torch.Tensor, kv_start: torch.Tensor, group_table: torch.Tensor,
+                      hq: int, hkv: int, dim: int, scale: float, max_ctx: int | None = None) -> torch.Tensor:
+    """Decode attention (one query row per sequence) over a cache whose older keys are sealed in the 8-bit store
+    ``compact`` (``engine.kv_compact.CompactKV``): keys ``[0, 64)`` and ``[kv_start[b], ctx)`` come from BF16 pages,
+    keys ``[64, kv_start[b])`` from the sealed groups named by ``group_table[b]`` (dequantised as
+    ``bf16(code * scale + lo)``). CUDA: the paged BF16 kernel writes its split partials, ``csrc/kv_affine8.cu`` adds
+    one partial per chunk of sealed groups, one merge. Returns ``[batch, hq * dim]``."""
+    batch = block_table.shape[0]
+    max_groups = group_table.shape[1]
+    if not _is_cuda(q):
+        out = torch.zeros(batch, hq * dim, dtype=q.dtype)
+        g = hq // hkv
+        for b in range(batch):
+            ctx, ks = int(ctx_lens[b]), int(kv_start[b])
+            if ctx == 0:
+                continue
+            kk, vv = [], []
+            for p0 in range(0, ctx, 64):
+                n = min(64, ctx - p0)
+                if p0 >= 64 and p0 < ks:
+                    slot = int(group_table[b, p0 // 128])
+                    kd, vd = compact.dequant(layer, slot)
+                    o = p0 % 128
+                    kk.append(kd[:, o: o + n]); vv.append(vd[:, o: o + n])
+                else:
+                    blk = int(block_table[b, p0 // 64])
+                    kk.append(kcache[blk][:, :n].to(torch.bfloat16)); vv.append(vcache[blk][:, :n].to(torch.bfloat16))
+            k = torch.cat(kk, 1).float(); v = torch.cat(vv, 1).float()            # [hkv, ctx, D]
+            qb = q[b, : hq * dim].float().view(hkv, g, dim)
+            sc = torch.einsum("hgd,htd->hgt", qb, k) * scale
+            p = torch.softmax(sc, dim=-1)
+            out[b] = torch.einsum("hgt,htd->hgd", p, v).reshape(hq * dim).to(q.dtype)
+        return out
+    rows, ldq = _rows2d(q)
+    _require(rows == batch and dim == 128 and kcache.shape[2] == 64, "attn_decode_mixed: one row per sequence, block 64, d128")
+    _require(block_table.dtype == torch.int32 and kv_start.dtype == torch.int32 and group_table.dtype == torch.int32
+             and group_table.is_contiguous(), "attn_decode_mixed: int32 metadata")
+    from ..engine.kv_compact import GROUPS_PER_CHUNK
+    if max_ctx is None:
+        max_ctx = block_table.shape[1] * 64
+    lib = kernels()
+    nsplit = lib.ff_attn_decode_plan(batch, hq, hkv, 1, max_ctx, None, None)
+    chunks = (max_groups + GROUPS_PER_CHUNK - 1) // GROUPS_PER_CHUNK
+    pstride = nsplit + chunks
+    ws = workspace(q.device)
+    part_o = ws.ensure("attn_o", batch * pstride * hq * dim)
+    part_ml = ws.ensure("attn_ml", batch * pstride * hq * 2)
+    out = torch.empty(rows, hq * dim, dtype=BF16, device=q.device)
+    st = status_tensor(q.device)
+    nb = kcache.shape[0]
+    rc = lib.ff_attn_decode_partial(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(kv_start),
+                                    ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, ldq, block_table.shape[1], nb, nsplit,
+                                    pstride, c_float(scale), ptr(st), stream_ptr())
+    check(rc, "ff_attn_decode_partial")
+    rc = lib.ff_attn_sealed(ptr(q), ptr(compact.k_codes[layer]), ptr(compact.v_codes[layer]), ptr(compact.k_stats[layer]),
+                            ptr(compact.v_stats[layer]), ptr(kcache), ptr(vcache), ptr(block_table), ptr(group_table),
+                            ptr(kv_start), ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, ldq, block_table.shape[1], nb,
+                            max_groups, compact.slots, GROUPS_PER_CHUNK, nsplit, pstride, c_float(scale), ptr(st),
+                            stream_ptr())
+    check(rc, "ff_attn_sealed")
+    rc = lib.ff_attn_merge(ptr(part_o), ptr(part_ml), ptr(out), batch, hq, pstride, stream_ptr())
+    check(rc, "ff_attn_merge")
+    _count(3)
+    return out
+
+
 def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                  q_start: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, max_q_len: int, hq: int,
                  hkv: int, dim: int, scale: float, window: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -179,10 +179,46 @@ def bench_moe(args) -> dict:
     return r
 
 
+def bench_attn_mixed(args) -> dict:
+    """Decode attention over the affine8 cache (sink + sealed 8-bit groups + ``--recent`` BF16 tokens) against the same
+    contexts held entirely in BF16 pages."""
+    from ..engine.kv_cache import PagedKVCache
+    from ..engine.kv_compact import CompactKV
+    dev = torch.device("cuda")
+    b, ctx, hq, hkv, d = args.batch, args.ctx, args.hq, args.hkv, 128
+    per = (ctx + 63) // 64
+    kv = PagedKVCache(1, hkv, d, b * per + 1, 64, torch.bfloat16, dev)
+    kv.k[0].normal_(); kv.v[0].normal_()
+    q = torch.randn(b, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16)
+    cl = torch.full((b,), ctx, dtype=torch.int32, device=dev)
+    for i in range(b):
+        kv.add_sequence(i); kv.reserve(i, ctx); kv.commit(i, ctx)
+    bt_full = torch.tensor([kv.seqs[i].blocks for i in range(b)], dtype=torch.int32, device=dev)
+    flush = Flusher(dev) if not args.no_flush else None
+    plain = time_op(lambda: ops.attn_decode(q, kv.k[0], kv.v[0], bt_full, cl, hq, hkv, d, 1 / math.sqrt(d), max_ctx=ctx),
+                    args.iters, args.warmup, flush)
+    c = CompactKV(1, hkv, d, b * (ctx // 128) + 1, dev, recent=args.recent)
+    kv.compact = c
+    for i in range(b):
+        c.seal(kv, i)
+    mg = max(ctx // 128, 1)
+    bt = torch.tensor([[x if x >= 0 else 0 for x in kv.seqs[i].blocks] for i in range(b)], dtype=torch.int32, device=dev)
+    gt = torch.tensor([c.groups[i] + [0] * (mg - len(c.groups[i])) for i in range(b)], dtype=torch.int32, device=dev)
+    ks = torch.tensor([c.sealed_tokens(i) for i in range(b)], dtype=torch.int32, device=dev)
+    mixed = time_op(lambda: ops.attn_decode_mixed(q, kv.k[0], kv.v[0], c, 0, bt, cl, ks, gt, hq, hkv, d, 1 / math.sqrt(d),
+                                                  max_ctx=ctx), args.iters, args.warmup, flush)
+    sealed = int(ks[0])
+    bytes_bf16 = 2 * b * ctx * hkv * d * 2
+    bytes_mixed = 2 * b * hkv * ((ctx - sealed + 64) * d * 2 + (sealed - 64) * d) + b * hkv * (sealed // 128) * (d * 8 + 128 * 8)
+    return {"op": "attn_mixed", "batch": b, "ctx": ctx, "recent": args.recent, "sealed_tokens": sealed,
+            "bf16_us": plain["us_median"], "mixed_us": mixed["us_median"], "bf16_bytes": bytes_bf16, "mixed_bytes": bytes_mixed,
+            "bf16_gbs": bytes_bf16 / plain["us_median"] / 1e3, "mixed_gbs": bytes_mixed / mixed["us_median"] / 1e3}
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="kbench")
     sub = ap.add_subparsers(dest="op", required=True)
-    for name in ("gemm", "attn_decode", "attn_prefill", "moe"):
+    for name in ("gemm", "attn_decode", "attn_prefill", "attn_mixed", "moe"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
@@ -206,8 +242,11 @@ def main(argv=None) -> None:
             p.add_argument("--ctx", type=int, default=1024)
             p.add_argument("--hq", type=int, default=32)
             p.add_argument("--hkv", type=int, default=8)
+            if name == "attn_mixed":
+                p.add_argument("--recent", type=int, default=2048)
     args = ap.parse_args(argv)
-    fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "moe": bench_moe}[args.op]
+    fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "attn_mixed": bench_attn_mixed,
+          "moe": bench_moe}[args.op]
     print(json.dumps(fn(args)))
     ops.check_status()
 

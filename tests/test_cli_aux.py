@@ -190,13 +190,31 @@ GEN = ["generate", "--tokens", "5,6,7,8,9,10,11", "--max-new-tokens", "9", "--ig
 
 
 def test_flags_without_an_implementation_are_refused(capsys):
-    for extra in (["--kv-format", "affine8"], ["--tp", "2"], ["--spec-budget", "tree16"], ["--spec-graph", "false"]):
+    for extra in (["--kv-format", "affine8", "--draft-model", "tiny-llama"], ["--kv-format", "affine8", "--prefix-cache", "true"],
+                  ["--tp", "2"], ["--spec-budget", "tree16"], ["--spec-graph", "false"]):
         with pytest.raises(SystemExit):
             cli.main(BASE + extra + GEN)
     with pytest.raises(SystemExit):      # a draft model only makes sense for generate
         cli.main(BASE + ["--draft-model", "tiny-llama", "tokenize", "--prompt", "x"])
     with pytest.raises(SystemExit):      # the server's scheduler does not consult the prefix store
         cli.main(BASE + ["--prefix-cache", "true", "serve"])
+
+
+def test_kv_format_affine8_seals_old_groups_and_keeps_decoding(capsys):
+    """``--kv-format affine8 --kv-recent 128``: groups older than the recent window move to the 8-bit store (their BF16
+    blocks are released) and decoding goes on over sink + sealed groups + recent pages."""
+    g = torch.Generator().manual_seed(21)
+    long = ["generate", "--tokens", ",".join(map(str, torch.randint(0, 2048, (300,), generator=g).tolist())),
+            "--max-new-tokens", "40", "--ignore-eos"]
+    base = ["--model", "tiny-llama", "--cpu", "--capacity", "1024"]
+    plain = _run(base + long, capsys)
+    packed = _run(base + ["--kv-format", "affine8", "--kv-recent", "128"] + long, capsys)
+    assert len(packed["generated_ids"]) == 40 and "kv" not in plain
+    # 300 + 40 tokens with 128 recent: positions below 128 are sealed (1 group, block 1 released; block 0 is the sink)
+    assert packed["kv"]["format"] == "affine8" and packed["kv"]["sealed_groups"] == 1 and packed["kv"]["released_blocks"] == 1
+    # 8-bit keys and values perturb the logits slightly: the continuations agree at the start
+    agree = next((i for i, (a, b) in enumerate(zip(plain["generated_ids"], packed["generated_ids"])) if a != b), 40)
+    assert agree >= 3, (plain["generated_ids"], packed["generated_ids"])
 
 
 def test_draft_model_flags_select_the_speculator(capsys):
