@@ -8,6 +8,7 @@
 // The reference fixes D = 256 and 4 KV heads; these kernels take any D that is a multiple of 32.
 #include "ptx.cuh"
 #include "host_util.h"
+#include "mma_sync.cuh"
 
 namespace ff {
 
@@ -139,13 +140,18 @@ kv_seal_groups_kernel(const __nv_bfloat16* __restrict__ kcache, const __nv_bfloa
 // Decode attention over the sealed groups of every sequence (one query row per sequence, head_dim 128): the partial
 // (max, sum, weighted values) of each chunk of groups goes into the split-KV partial buffers of the BF16 decode
 // kernel, behind its own splits, and the common merge kernel finishes. Keys and values are the dequantised rows
-// bf16(code * scale + lo); scores and the soft-max run in FP32 in the base-2 domain like the BF16 kernel. The first 64
+// bf16(code * scale + lo); the soft-max runs in FP32 in the base-2 domain like the BF16 kernel. The first 64
 // tokens of group 0 (the sink) are read from BF16 block `block_table[b][0]`.
 //   grid (chunks, hkv, batch), 128 threads; group_table [batch, max_groups] pool slots; sealed [batch] tokens sealed
 //   part index: ((b * pstride + split_base + chunk) * hq + head)
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int SEAL_MAXG = 16;      // query heads per KV head
+constexpr int SEAL_MAXG = 16;      // query heads per KV head (rows of the 16-row MMA tile)
+constexpr int SEAL_KEYS = 64;      // keys per soft-max block
 
+// Tensor-core form: the code rows of 64 tokens are de-quantised once into BF16 tiles in shared memory (K with the
+// per-channel statistics of the group, V with the per-token ones) and Q Kᵀ and P V run as mma.sync m16n8k16 with the
+// G query heads of the KV head as the 16 rows; online soft-max over 64-key blocks in the base-2 domain, P rounded to BF16.
+// 128 threads: warp w owns keys 16w .. 16w + 15 of a block in Q Kᵀ and output dims 32w .. 32w + 31 in P V.
 __global__ void __launch_bounds__(128)
 attn_sealed_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t* __restrict__ k_codes, const uint8_t* __restrict__ v_codes,
                    const float* __restrict__ k_stats, const float* __restrict__ v_stats,
@@ -156,124 +162,163 @@ attn_sealed_kernel(const __nv_bfloat16* __restrict__ q, const uint8_t* __restric
                    float scale_log2, int* status) {
   pdl_trigger();
   pdl_wait();
-  constexpr int D = 128;
+  constexpr int D = 128, CH = D / 8;
+  __shared__ __align__(128) uint8_t sQ[16 * D * 2];
+  __shared__ __align__(128) uint8_t sK[SEAL_KEYS * D * 2];
+  __shared__ __align__(128) uint8_t sV[SEAL_KEYS * D * 2];
+  __shared__ float sS[16 * SEAL_KEYS];
+  __shared__ __align__(16) __nv_bfloat16 sP[16 * SEAL_KEYS];
+  __shared__ float sM[16], sL[16], sR[16];
+  __shared__ float sk_sc[D], sk_lo[D], sv_sc[SEAL_KEYS], sv_lo[SEAL_KEYS];
   const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
   const int G = hq / hkv;
-  __shared__ float sq[SEAL_MAXG][D];          // queries * scale (base-2)
-  __shared__ float sk_lo[D], sk_sc[D];
-  __shared__ float sp[SEAL_MAXG][KV_GROUP];   // probabilities of the current group
-  __shared__ float sv_lo[KV_GROUP], sv_sc[KV_GROUP];
-  __shared__ float sred[4][SEAL_MAXG];
-  __shared__ float sm_new[SEAL_MAXG], scorr[SEAL_MAXG];
   const int ngroups = min(sealed[b] / KV_GROUP, max_groups);
   const int g0 = chunk * groups_per_chunk, g1 = min(ngroups, g0 + groups_per_chunk);
-  for (int i = tid; i < G * D; i += 128) {
-    const int g = i / D, c = i - g * D;
-    sq[g][c] = __bfloat162float(q[(size_t)b * ldq + (size_t)(kvh * G + g) * D + c]) * scale_log2;
+  // Q tile: row r = query head kvh * G + r (rows beyond G are zero)
+  for (int i = tid; i < 16 * CH; i += 128) {
+    const int r = i / CH, c = i - r * CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) v = *reinterpret_cast<const uint4*>(q + (size_t)b * ldq + (size_t)(kvh * G + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(sQ + ms_off(r, c, CH)) = v;
   }
-  float m[SEAL_MAXG], l[SEAL_MAXG], acc[SEAL_MAXG];
+  if (tid < 16) { sM[tid] = -3.0e38f; sL[tid] = 0.f; }
+  float o[4][4];
 #pragma unroll
-  for (int g = 0; g < SEAL_MAXG; ++g) { m[g] = -3.0e38f; l[g] = 0.f; acc[g] = 0.f; }
+  for (int i = 0; i < 4; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const uint32_t sQa = smem_u32(sQ), sKa = smem_u32(sK), sVa = smem_u32(sV), sPa = smem_u32(sP);
   __syncthreads();
+
   for (int grp = g0; grp < g1; ++grp) {
     const int sl = group_table[(size_t)b * max_groups + grp];
     if (sl < 0 || sl >= slots) { if (tid == 0) set_status(status, KID_KV, FF_ERR_BOUNDS, b, grp); break; }
     const size_t tb = ((size_t)sl * hkv + kvh) * KV_GROUP;
     sk_lo[tid] = k_stats[(((size_t)sl * hkv + kvh) * D + tid) * 2];
     sk_sc[tid] = k_stats[(((size_t)sl * hkv + kvh) * D + tid) * 2 + 1];
-    sv_lo[tid] = v_stats[(tb + tid) * 2];
-    sv_sc[tid] = v_stats[(tb + tid) * 2 + 1];
-    __syncthreads();
-    // scores of token `tid` for every head
-    float s[SEAL_MAXG];
+    for (int half = 0; half < 2; ++half) {
+      const bool sink = grp == 0 && half == 0;            // tokens 0..63 of the sequence: BF16 block 0
+      __syncthreads();                                    // the previous block's tiles are no longer read; K statistics visible
+      if (sink) {
+        int blk0 = block_table[(size_t)b * max_blocks];
+        if (blk0 < 0 || blk0 >= num_blocks) { if (tid == 0) set_status(status, KID_KV, FF_ERR_BOUNDS, b, blk0); blk0 = 0; }
+        const uint4* ks = reinterpret_cast<const uint4*>(kcache + ((size_t)blk0 * hkv + kvh) * 64 * D);
+        const uint4* vs = reinterpret_cast<const uint4*>(vcache + ((size_t)blk0 * hkv + kvh) * 64 * D);
+        for (int i = tid; i < SEAL_KEYS * CH; i += 128) {
+          const int key = i / CH, c = i - key * CH;
+          *reinterpret_cast<uint4*>(sK + ms_off(key, c, CH)) = ks[i];
+          *reinterpret_cast<uint4*>(sV + ms_off(key, c, CH)) = vs[i];
+        }
+      } else {
+        const size_t row0 = tb + (size_t)half * SEAL_KEYS;
+        if (tid < SEAL_KEYS) { sv_lo[tid] = v_stats[(row0 + tid) * 2]; sv_sc[tid] = v_stats[(row0 + tid) * 2 + 1]; }
+        // issue all code loads of this thread first (8 x 16 bytes), then convert
+        uint4 kc[4], vc[4];
 #pragma unroll
-    for (int g = 0; g < SEAL_MAXG; ++g) s[g] = 0.f;
-    const bool sink = grp == 0 && tid < 64;
-    int blk0 = 0;
-    if (grp == 0) {
-      blk0 = block_table[(size_t)b * max_blocks];
-      if (blk0 < 0 || blk0 >= num_blocks) { if (tid == 0) set_status(status, KID_KV, FF_ERR_BOUNDS, b, blk0); blk0 = 0; }
-    }
-    if (sink) {
-      const uint4* kr = reinterpret_cast<const uint4*>(kcache + (((size_t)blk0 * hkv + kvh) * 64 + tid) * D);
-      for (int c8 = 0; c8 < D / 8; ++c8) {
-        const uint4 v = kr[c8];
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+        for (int u = 0; u < 4; ++u) {
+          const int i = tid + u * 128;                                   // key = i / 8, 16-code vector = i % 8
+          kc[u] = reinterpret_cast<const uint4*>(k_codes + row0 * D)[i];
+          vc[u] = reinterpret_cast<const uint4*>(v_codes + row0 * D)[i];
+        }
+        __syncthreads();                                                  // V statistics visible
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = tid + u * 128, key = i >> 3, v16 = i & 7;
+          const uint8_t* kb = reinterpret_cast<const uint8_t*>(&kc[u]);
+          const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vc[u]);
+          const float vsc = sv_sc[key], vlo = sv_lo[key];
+          uint32_t kw[8], vw[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c = v16 * 16 + 2 * j;
+            kw[j] = pack_bf16x2(fmaf((float)kb[2 * j], sk_sc[c], sk_lo[c]), fmaf((float)kb[2 * j + 1], sk_sc[c + 1], sk_lo[c + 1]));
+            vw[j] = pack_bf16x2(fmaf((float)vb[2 * j], vsc, vlo), fmaf((float)vb[2 * j + 1], vsc, vlo));
+          }
+          *reinterpret_cast<uint4*>(sK + ms_off(key, 2 * v16, CH)) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+          *reinterpret_cast<uint4*>(sK + ms_off(key, 2 * v16 + 1, CH)) = make_uint4(kw[4], kw[5], kw[6], kw[7]);
+          *reinterpret_cast<uint4*>(sV + ms_off(key, 2 * v16, CH)) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+          *reinterpret_cast<uint4*>(sV + ms_off(key, 2 * v16 + 1, CH)) = make_uint4(vw[4], vw[5], vw[6], vw[7]);
+        }
+      }
+      __syncthreads();
+      // S[16 heads][16 keys of this warp]
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4], b0, b1, b2, b3;
+        ms_ldsm4(sQa + ms_off((lane & 7) + (((lane >> 3) & 1) << 3), 2 * kk + (lane >> 4), CH), a[0], a[1], a[2], a[3]);
+        ms_ldsm4(sKa + ms_off(warp * 16 + ((lane >> 4) << 3) + (lane & 7), 2 * kk + ((lane >> 3) & 1), CH), b0, b1, b2, b3);
+        ms_mma(s[0], a, b0, b1);
+        ms_mma(s[1], a, b2, b3);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 kk = __bfloat1622float2(h2[j]);
+          const int key = warp * 16 + i * 8 + 2 * t + (j & 1), row = g + ((j >> 1) << 3);
+          sS[row * SEAL_KEYS + key] = s[i][j] * scale_log2;
+        }
+      __syncthreads();
+      {   // soft-max bookkeeping: 8 threads per head row, 8 keys each
+        const int row = tid >> 3, part = tid & 7;
+        float sc8[8], mx = -3.0e38f;
 #pragma unroll
-          for (int g = 0; g < SEAL_MAXG; ++g)
-            if (g < G) s[g] += sq[g][c8 * 8 + 2 * j] * kk.x + sq[g][c8 * 8 + 2 * j + 1] * kk.y;
+        for (int j = 0; j < 8; ++j) { sc8[j] = sS[row * SEAL_KEYS + part * 8 + j]; mx = fmaxf(mx, sc8[j]); }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        const float mprev = sM[row], bmax = fmaxf(mprev, mx);
+        float bsum = 0.f;
+        uint32_t pw[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float p0 = exp2f(sc8[j] - bmax), p1 = exp2f(sc8[j + 1] - bmax);
+          bsum += p0 + p1;
+          pw[j >> 1] = pack_bf16x2(p0, p1);
+        }
+        bsum += __shfl_xor_sync(0xffffffffu, bsum, 1); bsum += __shfl_xor_sync(0xffffffffu, bsum, 2);
+        bsum += __shfl_xor_sync(0xffffffffu, bsum, 4);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sP) + ms_off(row, part, 8)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        __syncwarp();
+        if (part == 0) {
+          const float resc = exp2f(mprev - bmax);
+          sR[row] = resc;
+          sL[row] = sL[row] * resc + bsum;
+          sM[row] = bmax;
         }
       }
-    } else {
-      const uint4* kr = reinterpret_cast<const uint4*>(k_codes + (tb + tid) * D);
-      for (int c16 = 0; c16 < D / 16; ++c16) {
-        const uint4 v = kr[c16];
-        const uint8_t* cb = reinterpret_cast<const uint8_t*>(&v);
+      __syncthreads();
+      {   // O[16][32 dims of this warp] = O * rescale + P V
+        const float r0 = sR[g], r1 = sR[g + 8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int c = c16 * 16 + j;
-          const float kk = __bfloat162float(__float2bfloat16_rn(__fadd_rn(__fmul_rn((float)cb[j], sk_sc[c]), sk_lo[c])));
+        for (int i = 0; i < 4; ++i) { o[i][0] *= r0; o[i][1] *= r0; o[i][2] *= r1; o[i][3] *= r1; }
 #pragma unroll
-          for (int g = 0; g < SEAL_MAXG; ++g)
-            if (g < G) s[g] += sq[g][c] * kk;
+        for (int ks = 0; ks < SEAL_KEYS / 16; ++ks) {
+          uint32_t pa[4];
+          ms_ldsm4(sPa + ms_off((lane & 7) + (((lane >> 3) & 1) << 3), 2 * ks + (lane >> 4), 8), pa[0], pa[1], pa[2], pa[3]);
+          const int key = ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+          for (int dp = 0; dp < 2; ++dp) {
+            uint32_t b0, b1, b2, b3;
+            ms_ldsm4t(sVa + ms_off(key, warp * 4 + dp * 2 + (lane >> 4), CH), b0, b1, b2, b3);
+            ms_mma(o[2 * dp], pa, b0, b1);
+            ms_mma(o[2 * dp + 1], pa, b2, b3);
+          }
         }
       }
     }
-    // block maximum per head
-#pragma unroll
-    for (int g = 0; g < SEAL_MAXG; ++g) {
-      if (g < G) {
-        float v = s[g];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-        if (lane == 0) sred[warp][g] = v;
-      }
-    }
-    __syncthreads();
-    if (tid < G) {
-      const float bm = fmaxf(fmaxf(sred[0][tid], sred[1][tid]), fmaxf(sred[2][tid], sred[3][tid]));
-      sm_new[tid] = bm;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < SEAL_MAXG; ++g) {
-      if (g < G) {
-        const float mn = fmaxf(m[g], sm_new[g]);
-        const float corr = exp2f(m[g] - mn);
-        const float p = exp2f(s[g] - mn);
-        sp[g][tid] = p;
-        float ps = p;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-        if (lane == 0) sred[warp][g] = ps;
-        l[g] *= corr; acc[g] *= corr; m[g] = mn;
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < SEAL_MAXG; ++g)
-      if (g < G) l[g] += sred[0][g] + sred[1][g] + sred[2][g] + sred[3][g];
-    // values: thread = channel
-    for (int t = 0; t < KV_GROUP; ++t) {
-      float vv;
-      if (grp == 0 && t < 64) vv = __bfloat162float(vcache[(((size_t)blk0 * hkv + kvh) * 64 + t) * D + tid]);
-      else vv = __bfloat162float(__float2bfloat16_rn(__fadd_rn(__fmul_rn((float)v_codes[(tb + t) * D + tid], sv_sc[t]), sv_lo[t])));
-#pragma unroll
-      for (int g = 0; g < SEAL_MAXG; ++g)
-        if (g < G) acc[g] += sp[g][t] * vv;
-    }
-    __syncthreads();
   }
-  // partials: every thread holds (m, l) of all heads (identical across threads) and channel `tid` of the values
+  __syncthreads();
+  // partials of the G heads: (max, sum) and the un-normalised values
 #pragma unroll
-  for (int g = 0; g < SEAL_MAXG; ++g) {
-    if (g < G) {
-      const size_t pr = ((size_t)b * pstride + split_base + chunk) * hq + (size_t)kvh * G + g;
-      part_o[pr * D + tid] = acc[g];
-      if (tid == 0) { part_ml[pr * 2] = m[g]; part_ml[pr * 2 + 1] = l[g]; }
+  for (int e = 0; e < 2; ++e) {
+    const int row = g + 8 * e;
+    if (row < G) {
+      const size_t pr = ((size_t)b * pstride + split_base + chunk) * hq + (size_t)kvh * G + row;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int d = warp * 32 + i * 8 + 2 * t;
+        *reinterpret_cast<float2*>(part_o + pr * D + d) = make_float2(o[i][2 * e], o[i][2 * e + 1]);
+      }
+      if (warp == 0 && t == 0) { part_ml[pr * 2] = sM[row]; part_ml[pr * 2 + 1] = sL[row]; }
     }
   }
 }
