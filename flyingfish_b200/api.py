@@ -98,6 +98,9 @@ class Model:
             from .models.deepseek_v41 import DeepseekV41Model
             net = DeepseekV41Model(weights, comm=comm, max_sequences=settings.max_batch, max_len=settings.capacity,
                                    max_chunk=min(settings.chunk or 256, 256), seed=seed)
+        elif spec.extra.get("flint"):
+            from .models.flint import FlintModel
+            net = FlintModel(weights, comm=comm, seed=seed)
         elif spec.extra.get("gemma"):
             from .models.gemma import GemmaModel
             net = GemmaModel(weights, comm=comm, seed=seed)

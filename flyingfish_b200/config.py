@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | deepseek_v41 | glm5_next | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | deepseek_v41 | glm5_next | flint | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
     layers: int
     hidden: int
     heads: int
@@ -240,6 +240,17 @@ def deepseek_v41_tiny() -> ModelSpec:
                                   "cache_rows": 256}}})
 
 
+def flint_tiny() -> ModelSpec:
+    """Small Flint-style shape: local layers (window 33, rotary) and global layers without positions, QK-norm, a
+    learnable soft-max sink per head, two dense layers then sigmoid-routed experts with a shared expert."""
+    return ModelSpec(
+        name="flint-tiny", arch="flint", layers=5, hidden=512, heads=4, kv_heads=1, head_dim=128, ffn=1024, vocab=2048,
+        rope_theta=1e4, rms_eps=1e-6, qk_norm=True,
+        moe=MoeSpec(num_experts=8, top_k=2, expert_ffn=128, score="sigmoid", n_shared=1, shared_ffn=256,
+                    first_dense_layers=2, dense_ffn=1024),
+        extra={"flint": {"window": 33, "no_rope_layers": [0, 1, 4]}})
+
+
 def glm5_next_tiny() -> ModelSpec:
     """Small GLM-5-style shape: the hyper-connection program with every stage collapsing on its own pre-mix, top-k sparse
     attention with the pooled indexer in every layer, sigmoid routing with selection bias."""
@@ -253,7 +264,7 @@ def glm5_next_tiny() -> ModelSpec:
 NAMED_SHAPES = {
     "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
-    "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini, "deepseek-v41-tiny": deepseek_v41_tiny, "glm5-next-tiny": glm5_next_tiny,
+    "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini, "deepseek-v41-tiny": deepseek_v41_tiny, "glm5-next-tiny": glm5_next_tiny, "flint-tiny": flint_tiny,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }
 

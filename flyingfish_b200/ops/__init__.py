@@ -409,19 +409,21 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
 def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                 ctx_lens: torch.Tensor, hq: int, hkv: int, dim: int, scale: float, nq: int = 1,
                 tree_mask: torch.Tensor | None = None, max_ctx: int | None = None,
-                out: torch.Tensor | None = None, window: int = 0) -> torch.Tensor:
+                out: torch.Tensor | None = None, window: int = 0, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Decode / multi-row verify attention. ``q`` holds ``batch * nq`` rows (heads at columns
     ``h*dim``; it may be the packed QKV buffer). ``ctx_lens[b]`` counts the keys visible to the last
     of the ``nq`` rows. ``window > 0``: every row sees only its last ``window`` keys (local-attention
-    layers; not together with a tree mask). Returns ``[batch*nq, hq*dim]``."""
+    layers; not together with a tree mask). ``sinks`` (float32 [hq]): learnable soft-max, one sink logit per head in the
+    denominator. Returns ``[batch*nq, hq*dim]``."""
     batch = block_table.shape[0]
     _require(not (window > 0 and tree_mask is not None), "attn_decode: window and tree mask are exclusive")
+    _require(not (sinks is not None and tree_mask is not None), "attn_decode: sinks and tree mask are exclusive")
     if not _is_cuda(q):
         q_start = torch.arange(batch, dtype=torch.int32) * nq
         q_lens = torch.full((batch,), nq, dtype=torch.int32)
         tm = None if tree_mask is None else tree_mask.view(batch, nq)
         return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale, tm,
-                                   window)
+                                   window, sinks)
     rows, ldq = _rows2d(q)
     _require(rows == batch * nq, "attn_decode: q rows must equal batch * nq")
     _require(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attn_decode: block table int32")
@@ -444,7 +446,14 @@ def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, blo
     # slower on B200 (81.8 vs 75.6 us at batch 64 / context 1100: every CTA pays a fence and an atomic), so off
     items = batch * hkv * ((nq * (hq // hkv) + 15) // 16)
     counters = ws.attn_counters if (FUSE_ATTN_MERGE and nsplit > 1 and items <= ws.attn_counters.numel()) else None
-    if window > 0:
+    if sinks is not None:
+        _require(sinks.dtype == torch.float32 and sinks.numel() == hq and sinks.is_contiguous(), "attn_decode: sinks float32 [hq]")
+        counters = None
+        rc = lib.ff_attn_decode_sink(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(out),
+                                     ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, nq, ldq, block_table.shape[1], nb,
+                                     nsplit, c_float(scale), max(window, 0), ptr(sinks), ptr(status_tensor(q.device)),
+                                     stream_ptr())
+    elif window > 0:
         rc = lib.ff_attn_decode_window(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(ctx_lens), ptr(out),
                                        ptr(part_o), ptr(part_ml), batch, hq, hkv, dim, nq, ldq, block_table.shape[1], nb,
                                        nsplit, c_float(scale), window, ptr(counters), ptr(status_tensor(q.device)),
@@ -527,23 +536,28 @@ def attn_decode_mixed(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tenso
 
 def attn_prefill(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                  q_start: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, max_q_len: int, hq: int,
-                 hkv: int, dim: int, scale: float, window: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+                 hkv: int, dim: int, scale: float, window: int = 0, out: torch.Tensor | None = None,
+                 sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Causal chunked-prefill attention of packed query rows against the paged cache. ``window < 0`` makes it
-    bidirectional: every query row sees all ``ctx_lens`` keys of its sequence (encoders, vision towers)."""
+    bidirectional: every query row sees all ``ctx_lens`` keys of its sequence (encoders, vision towers). ``sinks``
+    (float32 [hq]): learnable soft-max, one sink logit per head in the denominator (tcgen05 kernel only)."""
     if not _is_cuda(q):
         return ref.attention_paged(q, kcache, vcache, block_table, q_start, q_lens, ctx_lens, hq, hkv, dim, scale,
-                                   None, window)
+                                   None, window, sinks)
     rows, ldq = _rows2d(q)
     batch = block_table.shape[0]
     if out is None:
         out = torch.empty(rows, hq * dim, dtype=BF16, device=q.device)
     nb = kcache.shape[0]
     _require(kcache.shape[2] == 64 and dim == 128, "attn_prefill: block 64 / head_dim 128 only")
-    if ATTN_PREFILL_TC and out.stride(0) % 8 == 0 and ldq % 8 == 0:
+    if sinks is not None:
+        _require(sinks.dtype == torch.float32 and sinks.numel() == hq and sinks.is_contiguous(), "attn_prefill: sinks float32 [hq]")
+        _require(out.stride(0) % 8 == 0 and ldq % 8 == 0, "attn_prefill: sinks need the tcgen05 kernel (16-byte aligned rows)")
+    if (ATTN_PREFILL_TC or sinks is not None) and out.stride(0) % 8 == 0 and ldq % 8 == 0:
         # tcgen05 kernel: Q Kᵀ and P V on the tensor cores with S and O in tensor memory
         rc = kernels().ff_attn_prefill_tc(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), ptr(q_start), ptr(q_lens),
                                           ptr(ctx_lens), ptr(out), batch, rows, max_q_len, hq, hkv, dim, ldq, out.stride(0),
-                                          block_table.shape[1], nb, c_float(scale), window,
+                                          block_table.shape[1], nb, c_float(scale), window, ptr(sinks),
                                           ptr(status_tensor(q.device)), stream_ptr())
         check(rc, "ff_attn_prefill_tc")
         _count()

@@ -199,7 +199,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                    __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int hq,
                    int hkv, int nq, int ldq, int max_blocks, int num_blocks, int nsplit, float scale_log2,
                    int* status, int* __restrict__ split_counters, int window, const int* __restrict__ kv_start,
-                   int pstride) {
+                   int pstride, const float* __restrict__ sinks) {
   pdl_trigger();
   if (threadIdx.x == 0) FF_TL(status, KID_ATTN_DECODE, 0);
   pdl_wait();
@@ -327,7 +327,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 #pragma unroll
       for (int w = 0; w < NW; ++w) acc += so[(w * 16 + r) * HD + d] * sc[w];
       if (nsplit == 1 && pstride == 0) {
-        out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+        // learnable soft-max: the head's sink logit enters the denominator only
+        const float Ls = sinks ? L + exp2f(sinks[hh] * 1.4426950408889634f - M) : L;
+        out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(Ls > 0.f ? acc / Ls : 0.f);
       } else {
         const size_t pr = ((size_t)b * (pstride ? pstride : nsplit) + split) * (nq * hq) + (size_t)qi * hq + hh;
         part_o[pr * HD + d] = acc;
@@ -365,6 +367,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             L += __ldcg(&part_ml[pr * 2 + 1]) * sc;
             acc += __ldcg(&part_o[pr * HD + d]) * sc;
           }
+          if (sinks) L += exp2f(sinks[hh] * 1.4426950408889634f - M);
           out[((size_t)(b * nq + qi) * hq + hh) * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
         }
       }
@@ -375,7 +378,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 // grid (B * nq * hq), 128 threads
 __global__ void __launch_bounds__(128)
 attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                  int rows_per_seq, int nsplit) {
+                  int rows_per_seq, int nsplit, const float* __restrict__ sinks, int hq) {
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x, b = row / rows_per_seq, r = row % rows_per_seq, d = threadIdx.x;
@@ -388,6 +391,7 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
     L += part_ml[pr * 2 + 1] * sc;
     acc += part_o[pr * HD + d] * sc;
   }
+  if (sinks) L += exp2f(sinks[r % hq] * 1.4426950408889634f - M);
   out[(size_t)row * HD + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
 }
 
@@ -514,7 +518,7 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
                               const int* ctx_lens, const unsigned long long* tree_mask, void* out, float* part_o,
                               float* part_ml, int batch, int hq, int hkv, int head_dim, int nq, int ldq, int max_blocks,
                               int num_blocks, int nsplit, float scale, int* split_counters, int* status, cudaStream_t s,
-                              int window, const int* kv_start = nullptr, int pstride = 0) {
+                              int window, const int* kv_start = nullptr, int pstride = 0, const float* sinks = nullptr) {
   if (window > 0 && tree_mask) return FF_HOST_UNSUPPORTED;
   if (pstride != 0 && (pstride < nsplit || !part_o || !part_ml)) return FF_HOST_BAD_SHAPE;
   if (head_dim != HD || batch <= 0 || hq <= 0 || hkv <= 0 || hq % hkv) return FF_HOST_BAD_SHAPE;
@@ -533,11 +537,11 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
   if (int r = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, HD, cache_rows, HD * 2, 64, PAGE)) return r;
   if (int lr_ = launch_pdl(attn_decode_kernel<NW>, dim3(grid), dim3(32 * NW), DEC_SMEM, s, 0, tmK, tmV, (const __nv_bfloat16*)q,
       block_table, ctx_lens, tree_mask, (__nv_bfloat16*)out, part_o, part_ml, hq, hkv, nq,
-      ldq, max_blocks, num_blocks, nsplit, scale_log2, status, split_counters, window, kv_start, pstride)) return lr_;
+      ldq, max_blocks, num_blocks, nsplit, scale_log2, status, split_counters, window, kv_start, pstride, sinks)) return lr_;
   if (int r = launch_result()) return r;
   if (pstride != 0) return 0;                      // partials only: the caller merges after the other kernel has added its own
   if (nsplit > 1 && split_counters == nullptr) {
-    if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * nq * hq), dim3(128), 0, s, 0, part_o, part_ml, (__nv_bfloat16*)out, nq * hq, nsplit)) return lr_;
+    if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * nq * hq), dim3(128), 0, s, 0, part_o, part_ml, (__nv_bfloat16*)out, nq * hq, nsplit, sinks, hq)) return lr_;
     return launch_result();
   }
   return 0;
@@ -568,8 +572,20 @@ FF_EXPORT int ff_attn_merge(const float* part_o, const float* part_ml, void* out
                             cudaStream_t s) {
   if (batch <= 0 || rows_per_seq <= 0 || nsplit < 1) return FF_HOST_BAD_SHAPE;
   if (int lr_ = launch_pdl(attn_merge_kernel, dim3(batch * rows_per_seq), dim3(128), 0, s, 0, part_o, part_ml,
-                           (__nv_bfloat16*)out, rows_per_seq, nsplit)) return lr_;
+                           (__nv_bfloat16*)out, rows_per_seq, nsplit, (const float*)nullptr, rows_per_seq)) return lr_;
   return launch_result();
+}
+
+// Decode attention with a learnable soft-max (one sink logit per query head in the denominator, sinks: float[hq]) and an
+// optional sliding window (window = 0: full attention). No tree mask.
+FF_EXPORT int ff_attn_decode_sink(const void* q, const void* kcache, const void* vcache, const int* block_table,
+                                  const int* ctx_lens, void* out, float* part_o, float* part_ml, int batch, int hq,
+                                  int hkv, int head_dim, int nq, int ldq, int max_blocks, int num_blocks, int nsplit,
+                                  float scale, int window, const float* sinks, int* status, cudaStream_t s) {
+  if (window < 0 || sinks == nullptr) return FF_HOST_BAD_SHAPE;
+  return attn_decode_launch(q, kcache, vcache, block_table, ctx_lens, nullptr, out, part_o, part_ml, batch, hq, hkv,
+                            head_dim, nq, ldq, max_blocks, num_blocks, nsplit, scale, nullptr, status, s, window, nullptr, 0,
+                            sinks);
 }
 
 // Decode attention of a local-attention layer: every query sees its last `window` keys.

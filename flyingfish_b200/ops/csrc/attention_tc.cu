@@ -54,7 +54,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                        const __grid_constant__ CUtensorMap tmV, const int* __restrict__ block_table,
                        const int* __restrict__ q_start, const int* __restrict__ q_lens,
                        const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, int hq, int hkv, int ldo,
-                       int max_blocks, int num_blocks, float scale_log2, int window, int causal, int* status) {
+                       int max_blocks, int num_blocks, float scale_log2, int window, int causal, int* status,
+                       const float* __restrict__ sinks) {
   const int b = blockIdx.z, h = blockIdx.y;
   const int qlen = q_lens[b];
   // later query tiles of a causal prefill see more keys: they are scheduled first so that the long CTAs do not form the tail
@@ -253,6 +254,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (ok) ok = mbar_wait(&bars.o_done, 0, abort_flag, status, KID_ATTN_PREFILL, 8);
     if (ok) {
       tc_fence_after();
+      // learnable soft-max: one extra logit per head that enters the denominator only
+      if (sinks != nullptr) l_sum += (m_ref == -INFINITY) ? 1.f : exp2f(sinks[h] * 1.4426950408889634f - m_ref);
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       __nv_bfloat16* orow = out + (size_t)(qs + r0 + row) * ldo + (size_t)h * TC_HD;
 #pragma unroll
@@ -293,7 +296,8 @@ using namespace ff;
 FF_EXPORT int ff_attn_prefill_tc(const void* q, const void* kcache, const void* vcache, const int* block_table,
                                  const int* q_start, const int* q_lens, const int* ctx_lens, void* out, int batch,
                                  int total_rows, int max_q_len, int hq, int hkv, int head_dim, int ldq, int ldo,
-                                 int max_blocks, int num_blocks, float scale, int window, int* status, cudaStream_t s) {
+                                 int max_blocks, int num_blocks, float scale, int window, const float* sinks, int* status,
+                                 cudaStream_t s) {
   if (head_dim != TC_HD || batch <= 0 || max_q_len <= 0 || hq <= 0 || hkv <= 0 || hq % hkv || total_rows <= 0) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || ldo % 8 || (reinterpret_cast<uintptr_t>(out) & 15)) return FF_HOST_BAD_ALIGN;
   CUtensorMap tmQ, tmK, tmV;
@@ -307,6 +311,6 @@ FF_EXPORT int ff_attn_prefill_tc(const void* q, const void* kcache, const void* 
   dim3 grid((max_q_len + TC_BM - 1) / TC_BM, hq, batch);
   attn_prefill_tc_kernel<<<grid, 192, TC_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
                                                     (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
-                                                    window < 0 ? 0 : window, window < 0 ? 0 : 1, status);
+                                                    window < 0 ? 0 : window, window < 0 ? 0 : 1, status, sinks);
   return launch_result();
 }

@@ -181,8 +181,10 @@ def gather_kv(cache: torch.Tensor, block_table_row: torch.Tensor, ctx: int) -> t
 
 def attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                     q_start: torch.Tensor, q_lens: torch.Tensor, ctx_lens: torch.Tensor, hq: int, hkv: int,
-                    dim: int, scale: float, tree_mask: torch.Tensor | None = None, window: int = 0) -> torch.Tensor:
-    """Causal attention of packed query rows against the paged cache.
+                    dim: int, scale: float, tree_mask: torch.Tensor | None = None, window: int = 0,
+                    sinks: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of packed query rows against the paged cache. ``sinks`` (float [hq]): learnable soft-max, one
+    extra logit per head that takes probability mass but contributes no value.
 
     q: [rows, >= hq*dim] (head h at columns h*dim). Sequence b owns rows
     ``q_start[b] : q_start[b]+q_lens[b]`` and ``ctx_lens[b]`` cached keys; its query i sits at
@@ -213,8 +215,12 @@ def attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
             anc = ((bits[:, None] >> rel[None, :]) & 1).bool()  # [q, tail keys]
             vis[:, tail:] &= anc
         s = s.masked_fill(~vis[None].to(s.device), float("-inf"))
+        if sinks is not None:
+            s = torch.cat([s, sinks.to(F32)[:, None, None].expand(hq, ql, 1)], dim=-1)
         p = torch.softmax(s, dim=-1)
         p = torch.nan_to_num(p, nan=0.0)
+        if sinks is not None:
+            p = p[..., :-1]
         o = torch.einsum("hqk,khd->qhd", p, v)
         out[qs: qs + ql] = o.reshape(ql, hq * dim).to(q.dtype)
     return out
