@@ -416,6 +416,47 @@ class Engine:
         if self.kv.compact is not None:
             raise ValueError(f"{what} reads BF16 pages only and is not available with --kv-format affine8")
 
+    def capture_verify(self, bucket: int, nq: int) -> _Graph:
+        """Capture the verification step of ``nq`` rows per sequence for a batch bucket (decode-style attention over
+        ``nq`` query rows; the reference captures its draft and verify steps per row count,
+        src/backend/cuda/engine.rs:5347-5440). The graph's outputs are the greedy token of every row and the
+        residual rows (for multi-token-prediction heads)."""
+        key = (bucket, nq)
+        g = self.graphs.get(key)
+        if g is not None:
+            return g
+        t0 = time.perf_counter()
+        g = _Graph()
+        rows = bucket * nq
+        fb = ForwardBatch(BatchLayout(bucket, rows, self.max_blocks), self.device)
+        fb.fill(ids=[0] * rows, positions=[0] * rows, slots=[-1] * rows, q_lens=[nq] * bucket, ctx_lens=[0] * bucket,
+                block_rows=[[]] * bucket, logit_rows=list(range(rows)), is_decode=True, nq=nq)
+        fb.max_ctx = self.settings.capacity
+        fb.upload()
+
+        def step():
+            n = self.model.hidden_states(fb, self.kv)
+            return self.model.greedy(self.model.logits(n, fb)), self.model.last_residual, n
+        # a caller may be collecting the final-normed rows of every forward (multi-token prediction): the warm-up and
+        # capture passes are not its forwards; replays hand it the captured rows instead
+        sink, self.model.normed_sink = getattr(self.model, "normed_sink", None), None
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out, hid, normed = step()
+        self.model.normed_sink = sink
+        g.graph, g.batch, g.out, g.hidden, g.normed = graph, fb, out, hid, normed
+        self.graphs[key] = g
+        self.stats["captures"] += 1
+        self.stats["capture_ms"] = self.stats.get("capture_ms", 0.0) + (time.perf_counter() - t0) * 1e3
+        return g
+
     # -- speculative verification --------------------------------------------------------------
     def verify(self, seqs: list[Sequence], drafts: list[list[int]], return_hidden: bool = False,
                device_out: bool = False):
@@ -436,7 +477,12 @@ class Engine:
             k = len(drafts[0])
             assert all(len(d) == k for d in drafts), "all sequences must carry the same number of drafts"
             nq = k + 1
-            fb = self.prefill_batch
+            # graph path: decode-style batch of nq rows per sequence in a bucket, replayed from a capture per (bucket, nq)
+            graphed = (self.use_graph and getattr(self.model, "expert_provider", None) is None and nq <= 8
+                       and self.state_slots is None and self.settings.spec_graph)
+            bucket = bucket_for(len(seqs)) if graphed else len(seqs)
+            g = self.capture_verify(bucket, nq) if graphed else None
+            fb = g.batch if graphed else self.prefill_batch
             ids, positions, slots, q_lens, ctx_lens, block_rows = [], [], [], [], [], []
             for s, d in zip(seqs, drafts):
                 kvs = self.kv.seqs[s.seq_id]
@@ -450,11 +496,27 @@ class Engine:
                 ctx_lens.append(kvs.length + nq)
                 block_rows.append(list(kvs.blocks))
             rows = len(ids)
-            fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
-                    logit_rows=list(range(rows)), is_decode=False)
-            fb.upload()
-            n = self.model.hidden_states(fb, self.kv)
-            out = self.model.greedy(self.model.logits(n, fb))
+            if graphed:
+                pad = bucket - len(seqs)
+                ids += [0] * (pad * nq); positions += [0] * (pad * nq); slots += [-1] * (pad * nq)
+                q_lens += [nq] * pad; ctx_lens += [0] * pad; block_rows += [[]] * pad
+                fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
+                        logit_rows=list(range(bucket * nq)), is_decode=True, nq=nq)
+                fb.max_ctx = self.settings.capacity
+                fb.upload()
+                g.graph.replay()
+                out, hid_all = g.out[:rows], g.hidden
+                if getattr(self.model, "normed_sink", None) is not None:
+                    self.model.normed_sink.append(g.normed[:rows])
+                self.stats["graph_replays"] += 1
+                self.stats["verify_graph_replays"] = self.stats.get("verify_graph_replays", 0) + 1
+            else:
+                fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
+                        logit_rows=list(range(rows)), is_decode=False)
+                fb.upload()
+                n = self.model.hidden_states(fb, self.kv)
+                out = self.model.greedy(self.model.logits(n, fb))
+                hid_all = self.model.last_residual
             if device_out:
                 # the caller decides acceptance on the device and reads one verdict back (then calls _after_sync)
                 self.stats["verify_rows"] = self.stats.get("verify_rows", 0) + rows
@@ -464,7 +526,7 @@ class Engine:
             self.stats["verify_rows"] = self.stats.get("verify_rows", 0) + rows
             res = [toks[i * nq: (i + 1) * nq] for i in range(len(seqs))]
             if return_hidden:
-                hid = self.model.last_residual
+                hid = hid_all
                 return res, [hid[i * nq: (i + 1) * nq] for i in range(len(seqs))]
             return res
         except Exception:

@@ -106,3 +106,29 @@ def test_speculation_on_gpu_equals_greedy():
     tree = TreeSpeculator(t, d, "tree32", "waves")
     assert tree.generate(ids, 16).ids == plain
     assert tree.stats.accepted > 0
+
+
+def test_verification_replays_from_a_cuda_graph():
+    """With graphs on, the multi-row verification step of chain / MTP speculation is captured per (bucket, rows) and
+    replayed (decode-style attention over the rows); the emitted stream is still plain greedy decoding."""
+    from flyingfish_b200.spec.chain import ChainSpeculator
+    from flyingfish_b200.spec.mtp import MtpSpeculator
+    ids = _prompt(2048, 35, 9)
+    t = _load("cuda", graph=True)
+    d = _load("cuda", graph=True)
+    plain = generate_plain(t, ids, 16, ignore_eos=True, graph=True).ids
+    t.reset()
+    spec = ChainSpeculator(t, d, k=4)
+    assert spec.generate(ids, 16).ids == plain
+    assert t.engine.stats.get("verify_graph_replays", 0) > 0 and (1, 5) in t.engine.graphs
+    t.reset(); d.reset()
+    before = t.engine.stats["verify_graph_replays"]
+    assert MtpSpeculator(t, depth=2, seed=3).generate(ids, 16).ids == plain
+    assert t.engine.stats["verify_graph_replays"] > before
+    # eager verification of the same drafts gives the same tokens
+    t.reset()
+    e = _load("cuda", graph=False)
+    sa, sb = t.engine.add_sequence(ids), e.engine.add_sequence(ids)
+    t.engine.prefill([sa]); e.engine.prefill([sb])
+    drafts = [plain[1:4]]                              # the true continuation: every row's successor is known
+    assert t.engine.verify([sa], drafts) == e.engine.verify([sb], drafts) == [plain[1:5]]
