@@ -35,6 +35,8 @@ class BatchLayout:
         self.logit_rows = o; o += self.n_logit
         self.block_table = o; o += self.max_batch * self.max_blocks
         self.tree_mask = o; o += 2 * self.max_rows        # int64 per row, stored as two int32
+        self.row_start = o; o += self.max_batch + 1          # first row of every sequence, then the row count
+        self.state_slots = o; o += self.max_batch            # per-sequence state slot (models with recurrent state)
         self.kv_start = o; o += self.max_batch if self.max_groups else 0
         self.groups = o; o += self.max_batch * self.max_groups
         self.total = o
@@ -83,6 +85,10 @@ class ForwardBatch:
         L = self.layout
         return self.dev[L.block_table: L.block_table + L.max_batch * L.max_blocks].view(L.max_batch, L.max_blocks)[: self.batch]
     @property
+    def row_start(self) -> torch.Tensor: return self._v(self.layout.row_start, self.batch + 1)
+    @property
+    def state_slots_dev(self) -> torch.Tensor: return self._v(self.layout.state_slots, self.batch)
+    @property
     def kv_start(self) -> torch.Tensor | None:
         L = self.layout
         return self._v(L.kv_start, self.batch) if L.max_groups else None
@@ -101,7 +107,7 @@ class ForwardBatch:
 
     # -- host fill -----------------------------------------------------------------------------
     def fill(self, *, ids, positions, slots, q_lens, ctx_lens, block_rows, logit_rows, is_decode: bool, nq: int = 1,
-             tree_mask=None, kv_start=None, group_rows=None) -> None:
+             tree_mask=None, kv_start=None, group_rows=None, state_slots=None) -> None:
         """Write one step's metadata into the pinned host buffer (lists of ints)."""
         L = self.layout
         h = self.host
@@ -118,6 +124,11 @@ class ForwardBatch:
         if batch > 1:
             qs[1:] = torch.cumsum(ql, 0)[:-1].to(torch.int32)
         h[L.q_start: L.q_start + batch] = qs
+        h[L.row_start: L.row_start + batch] = qs
+        h[L.row_start + batch] = int(ql.sum()) if batch else 0
+        if state_slots is not None:
+            h[L.state_slots: L.state_slots + batch] = torch.as_tensor(state_slots, dtype=torch.int32)
+            self.state_slots = list(state_slots)
         h[L.ctx_lens: L.ctx_lens + batch] = torch.as_tensor(ctx_lens, dtype=torch.int32)
         self.n_logit_rows = len(logit_rows)
         h[L.logit_rows: L.logit_rows + len(logit_rows)] = torch.as_tensor(logit_rows, dtype=torch.int32)

@@ -107,7 +107,9 @@ class Engine:
         if getattr(model, "state_slot_count", 0):
             self.state_slots = list(range(model.state_slot_count - 1))
             self.scratch_slot = model.state_slot_count - 1
-            self.use_graph = False
+            # a model whose state kernels take their slots from the packed step metadata can be captured
+            if not getattr(model, "graph_safe_state", False):
+                self.use_graph = False
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "decode_tokens": 0, "graph_replays": 0,
                       "captures": 0, "h2d_bytes": 0, "d2h_bytes": 0}
         self.fail_next_step = False      # host-side fault injection hook for tests
@@ -258,7 +260,8 @@ class Engine:
             pad = (row + mult - 1) // mult * mult - row
             ids += [0] * pad; positions += [0] * pad; slots += [-1] * pad
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
-                logit_rows=logit_rows, is_decode=False)
+                logit_rows=logit_rows, is_decode=False,
+                state_slots=[s.state_slot for s, _ in part] if self.state_slots is not None else None)
         fb.upload()
         fb.state_slots = [s.state_slot for s, _ in part]
         out = self.model.forward(fb, self.kv, inputs_embeds=self._mm_embeds(part, fb, len(ids)))
@@ -310,11 +313,13 @@ class Engine:
             c = self.kv.compact
             kv_start = [c.sealed_tokens(s.seq_id) for s in seqs]
             group_rows = [c.groups.get(s.seq_id, []) for s in seqs]
-        fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
-                logit_rows=list(range(bucket)), is_decode=True, nq=1, kv_start=kv_start, group_rows=group_rows)
-        fb.max_ctx = self.settings.capacity      # fixed launch geometry (graph-stable)
+        st = None
         if self.state_slots is not None:
-            fb.state_slots = [s.state_slot for s in seqs] + [self.scratch_slot] * pad
+            st = [s.state_slot for s in seqs] + [self.scratch_slot] * pad
+        fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
+                logit_rows=list(range(bucket)), is_decode=True, nq=1, kv_start=kv_start, group_rows=group_rows,
+                state_slots=st)
+        fb.max_ctx = self.settings.capacity      # fixed launch geometry (graph-stable)
 
     def _decode_batch(self, bucket: int) -> ForwardBatch:
         fb = self.eager_decode_batch.get(bucket)
@@ -334,7 +339,8 @@ class Engine:
         g = _Graph()
         fb = self._decode_batch(bucket)
         fb.fill(ids=[0] * bucket, positions=[0] * bucket, slots=[-1] * bucket, q_lens=[1] * bucket,
-                ctx_lens=[0] * bucket, block_rows=[[]] * bucket, logit_rows=list(range(bucket)), is_decode=True)
+                ctx_lens=[0] * bucket, block_rows=[[]] * bucket, logit_rows=list(range(bucket)), is_decode=True,
+                state_slots=[self.scratch_slot] * bucket if self.state_slots is not None else None)
         fb.max_ctx = self.settings.capacity
         fb.upload()
         side = torch.cuda.Stream(self.device)

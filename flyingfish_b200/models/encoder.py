@@ -35,7 +35,8 @@ def run_whole(model, seqs_ids: list[list[int]], want: str = "hidden") -> list[to
             ctx_lens.append(n)
             block_rows.append(list(eng.kv.seqs[s.seq_id].blocks))
         fb.fill(ids=ids, positions=positions, slots=slots, q_lens=q_lens, ctx_lens=ctx_lens, block_rows=block_rows,
-                logit_rows=list(range(total)) if want == "logits" else [total - 1], is_decode=False)
+                logit_rows=list(range(total)) if want == "logits" else [total - 1], is_decode=False,
+                state_slots=[s.state_slot for s in seqs] if eng.state_slots is not None else None)
         fb.upload()
         fb.state_slots = [s.state_slot for s in seqs]      # models with per-sequence recurrent state address it by slot
         net = eng.model

@@ -12,8 +12,8 @@ A gated-delta-net layer:
 Per-sequence state (conv history [conv_dim, 3], S [v_heads, 128, 128], both FP32) lives in slot-indexed slabs; the
 engine hands every sequence a slot and names the slots of a batch in ``ForwardBatch.state_slots``. The step is
 the same for prefill chunks and decode rows (the kernels walk each sequence's rows in order), so a chunked
-prefill and token-by-token decoding produce the same state. Not supported with this mixer: CUDA-graph replay,
-speculative rollback, tensor parallelism.
+prefill and token-by-token decoding produce the same state. Decode steps replay from CUDA graphs (slots and row
+ranges are views of the packed step metadata). Not supported with this mixer: speculative rollback, tensor parallelism.
 """
 from __future__ import annotations
 
@@ -86,17 +86,25 @@ class HybridModel(DecoderModel):
     def state_bytes_per_sequence(self) -> int:
         return len(self.gdn_layers) * 4 * (self.conv_dim * 3 + self.vh * D * D)
 
+    graph_safe_state = True          # slots and row ranges come from the packed step metadata (fixed device addresses)
+
     def hidden_states(self, b, kv, inputs_embeds=None):
-        # row ranges and state slots of the sequences in this batch, shared by every gated-delta-net layer
-        lens = b.q_lens.cpu().tolist() if not isinstance(b.q_lens, list) else b.q_lens
-        starts, acc = [0], 0
-        for n in lens:
-            acc += int(n)
-            starts.append(acc)
-        slots = list(getattr(b, "state_slots", None) or [])
-        assert len(slots) == len(lens), "the engine must name a state slot per sequence of the batch"
-        dev = self.w.embed.device
-        self._meta = (torch.tensor(starts, dtype=torch.int32, device=dev), torch.tensor(slots, dtype=torch.int32, device=dev))
+        # row ranges and state slots of the sequences in this batch, shared by every gated-delta-net layer: views of
+        # the packed metadata buffer, so a captured decode step sees each step's values
+        if getattr(b, "layout", None) is not None and hasattr(b, "row_start"):
+            assert getattr(b, "state_slots", None) is not None and len(b.state_slots) == b.batch, \
+                "the engine must name a state slot per sequence of the batch"
+            self._meta = (b.row_start, b.state_slots_dev)
+        else:
+            lens = b.q_lens.cpu().tolist() if not isinstance(b.q_lens, list) else b.q_lens
+            starts, acc = [0], 0
+            for n in lens:
+                acc += int(n)
+                starts.append(acc)
+            slots = list(getattr(b, "state_slots", None) or [])
+            assert len(slots) == len(lens), "the engine must name a state slot per sequence of the batch"
+            dev = self.w.embed.device
+            self._meta = (torch.tensor(starts, dtype=torch.int32, device=dev), torch.tensor(slots, dtype=torch.int32, device=dev))
         return super().hidden_states(b, kv, inputs_embeds)
 
     def _attention(self, i, n, b, kv):

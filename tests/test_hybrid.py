@@ -67,3 +67,21 @@ def test_hybrid_gpu_matches_cpu_oracle():
     from _oracle import assert_hidden_close
     prompts = [[5, 9, 100, 33, 7, 8, 250, 11, 12, 90, 14], [3, 4, 5]]
     assert_hidden_close(_load("cpu"), _load("cuda"), prompts)
+
+
+@pytest.mark.gpu
+def test_hybrid_decode_replays_from_cuda_graphs():
+    """State slots and row ranges are views of the packed step metadata, so the decode step of the hybrid model is
+    captured per bucket; graph replays give the tokens of eager launches."""
+    from flyingfish_b200.api import Model
+    from flyingfish_b200.config import Settings
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (33, 7, 18)]
+    eager = Model.load("tiny-hybrid", Settings(capacity=256, max_batch=4, graph=False), device="cuda", seed=0)
+    graph = Model.load("tiny-hybrid", Settings(capacity=256, max_batch=4, graph=True), device="cuda", seed=0)
+    assert graph.engine.use_graph
+    want, got = eager.generate_batch(prompts, 12), graph.generate_batch(prompts, 12)
+    assert got == want and graph.engine.stats["graph_replays"] > 0
+    # a second batch reuses the capture with other slots
+    again = graph.generate_batch(prompts[::-1], 12)
+    assert again == want[::-1]
