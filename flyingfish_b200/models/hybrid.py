@@ -122,7 +122,10 @@ class HybridModel(DecoderModel):
         ba = proj[:, self.conv_dim + self.value_dim: self.conv_dim + self.value_dim + 2 * self.vh].float()
         beta = torch.sigmoid(ba[:, : self.vh]).contiguous()
         dec = (-torch.exp(g.a_log)[None, :] * F.softplus(ba[:, self.vh:] + g.dt_bias[None, :])).contiguous()
-        o = gdn_ops.recurrent_slots(q, k, v, beta, dec, self.rec_state[i], row_start, slots)      # [rows, vh, 128] bf16
+        # prefill chunks go through the chunked (tensor-core) form of the recurrence, decode rows through the
+        # token-by-token kernel
+        step = gdn_ops.chunked_slots if (not b.is_decode and b.max_q_len >= gdn_ops.CHUNK_MIN_ROWS) else gdn_ops.recurrent_slots
+        o = step(q, k, v, beta, dec, self.rec_state[i], row_start, slots)                         # [rows, vh, 128] bf16
         on = ops.rmsnorm(o.reshape(rows * self.vh, D).to(g.norm_w.dtype), g.norm_w, self.spec.rms_eps)
         y = (on.reshape(rows, self.value_dim).float() * F.silu(z.float())).to(g.w_out.dtype)
         if self.trace is not None:

@@ -112,3 +112,23 @@ def recurrent_slots(q, k, v, beta, g, state: torch.Tensor, row_start: torch.Tens
                                            ptr(slots), slots.numel(), heads, stream_ptr()), "ff_gdn_recurrent_slots")
     _count()
     return out
+
+
+CHUNK_MIN_ROWS = 32          # shortest sequence segment of a launch for which the chunked form is used
+
+
+def chunked_slots(q, k, v, beta, g, state: torch.Tensor, row_start: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """Prefill form of :func:`recurrent_slots`: the same recurrence evaluated 64 tokens at a time through the WY
+    representation on tensor cores (``csrc/gdn_chunk.cu``; reference: kernels/gdn/gdn_chunkwise_p1.cu, gdn_cw_p2.cu).
+    Matrix products take BF16 operands, so results agree with the token-by-token form to BF16 accuracy, not bit for
+    bit. CPU tensors run the recurrent oracle."""
+    if not q.is_cuda:
+        return recurrent_slots(q, k, v, beta, g, state, row_start, slots)
+    rows, heads, d = q.shape
+    assert d == D and state.shape[-2:] == (D, D)
+    out = torch.empty(rows, heads, D, dtype=BF16, device=q.device)
+    check(kernels().ff_gdn_chunked_slots(ptr(q.contiguous()), ptr(k.contiguous()), ptr(v.contiguous()), ptr(beta), ptr(g),
+                                         ptr(state), ptr(out), ptr(row_start), ptr(slots), slots.numel(), heads, stream_ptr()),
+          "ff_gdn_chunked_slots")
+    _count()
+    return out

@@ -215,10 +215,33 @@ def bench_attn_mixed(args) -> dict:
             "bf16_gbs": bytes_bf16 / plain["us_median"] / 1e3, "mixed_gbs": bytes_mixed / mixed["us_median"] / 1e3}
 
 
+def bench_gdn(args) -> dict:
+    """Gated delta rule over packed prefill rows: the token-by-token kernel against the chunked tensor-core form."""
+    from ..ops import gdn_ops
+    dev = torch.device("cuda")
+    b, n, heads = args.batch, args.ctx, args.hq
+    rows = b * n
+    q = torch.randn(rows, heads, 128, device=dev); k = torch.randn(rows, heads, 128, device=dev)
+    q = q / q.norm(dim=-1, keepdim=True) * 128 ** -0.5
+    k = k / k.norm(dim=-1, keepdim=True)
+    v = torch.randn(rows, heads, 128, device=dev)
+    beta = torch.sigmoid(torch.randn(rows, heads, device=dev)); dec = -torch.rand(rows, heads, device=dev) * 0.3
+    state = torch.zeros(b, heads, 128, 128, device=dev)
+    rs = (torch.arange(b + 1, dtype=torch.int32, device=dev) * n)
+    slots = torch.arange(b, dtype=torch.int32, device=dev)
+    flush = Flusher(dev) if not args.no_flush else None
+    rec = time_op(lambda: gdn_ops.recurrent_slots(q, k, v, beta, dec, state, rs, slots), args.iters, args.warmup, flush)
+    state.zero_()
+    chk = time_op(lambda: gdn_ops.chunked_slots(q, k, v, beta, dec, state, rs, slots), args.iters, args.warmup, flush)
+    return {"op": "gdn", "sequences": b, "tokens": n, "heads": heads, "recurrent_us": rec["us_median"],
+            "chunked_us": chk["us_median"], "speedup": rec["us_median"] / chk["us_median"],
+            "chunked_us_per_chunk": chk["us_median"] / max(n // 64, 1)}
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="kbench")
     sub = ap.add_subparsers(dest="op", required=True)
-    for name in ("gemm", "attn_decode", "attn_prefill", "attn_mixed", "moe"):
+    for name in ("gemm", "attn_decode", "attn_prefill", "attn_mixed", "gdn", "moe"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
@@ -245,7 +268,7 @@ def main(argv=None) -> None:
             if name == "attn_mixed":
                 p.add_argument("--recent", type=int, default=2048)
     args = ap.parse_args(argv)
-    fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "attn_mixed": bench_attn_mixed,
+    fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "attn_mixed": bench_attn_mixed, "gdn": bench_gdn,
           "moe": bench_moe}[args.op]
     print(json.dumps(fn(args)))
     ops.check_status()
