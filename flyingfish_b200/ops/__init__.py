@@ -101,7 +101,7 @@ def workspace(device: torch.device) -> _Workspace:
 # ------------------------------------------------------------------------------------------
 SKINNY_MAX_M = 128
 FP8_DENSE_ROWS = 256         # more rows than this: FP8-resident weights are expanded to BF16 for the call
-FP8_MAX_K = 16384            # deepest reduction the W8A8 kernel stages activation scales for
+FP8_MAX_K = 32768            # deepest reduction the W8A8 kernel stages activation scales for
 # decode-shape epilogue fusions (FLYINGFISH_FUSE_SWIGLU=0 / FLYINGFISH_FUSE_ROPE=0 fall back to separate kernels)
 FUSE_SWIGLU = os.environ.get("FLYINGFISH_FUSE_SWIGLU", "1") != "0"
 FUSE_ROPE = os.environ.get("FLYINGFISH_FUSE_ROPE", "1") != "0"
@@ -120,7 +120,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
     W8A8 GEMM of ``csrc/gemm_fp8.cu`` (CPU: its oracle) runs instead."""
     if not isinstance(w, torch.Tensor):
         from . import quant_ops
-        if x.shape[0] > FP8_DENSE_ROWS or w.shape[1] > FP8_MAX_K:
+        tok = min(128, (x.shape[0] + 15) // 16 * 16)
+        if x.shape[0] > FP8_DENSE_ROWS or w.shape[1] > FP8_MAX_K or (w.shape[1] // 128) * tok * 4 > 64 * 1024:
             # prefill-sized calls: the weight is expanded to BF16 for this call and the large-tile BF16 GEMM runs
             # (W8A16), as the reference does for many rows (kernels/fp8_linear.cu materialises + cuBLAS); the W8A8
             # kernel keeps tokens on the narrow UMMA side and is meant for decode batches

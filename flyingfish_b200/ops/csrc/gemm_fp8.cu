@@ -37,8 +37,8 @@ __device__ __forceinline__ float bfr8(float x) { return __bfloat162float(__float
 // Promotion of P consecutive k-blocks for a warp that owns `nb` (<= U) 16-column blocks: all tensor-memory loads are
 // issued before the single wait, so the fixed latency of the wait -> load -> arrive chain is paid once per call.
 // acc[16 u + j] += partial[u][j] * scale[u][j], k-blocks in order (the summation order of the contract).
-template <int U, int P, int OFF>
-__device__ __forceinline__ void fp8_promote(float (&acc)[F_TOK / 2], const uint32_t (&taddr)[2], const float* const (&sp)[2],
+template <int U, int P, int OFF, int NACC>
+__device__ __forceinline__ void fp8_promote(float (&acc)[NACC], const uint32_t (&taddr)[2], const float* const (&sp)[2],
                                             int nb) {
   uint32_t r[P][U][16];
 #pragma unroll
@@ -65,7 +65,11 @@ __device__ __forceinline__ void fp8_promote(float (&acc)[F_TOK / 2], const uint3
 }
 
 // epi: 0 store, 1 SwiGLU over 64/64 interleaved rows (grouped gate/up)
-__global__ void __launch_bounds__(320, 1)
+// TOK: tokens per chunk. 128 for prefill-sized and dense calls (one CTA per SM); 32 for decode-sized grouped calls, where a
+// CTA needs few registers and half the shared memory so that two CTAs share an SM and one streams while the other sets up
+// or drains (an expert tile of a decode batch is short: 16 to 56 k-blocks).
+template <int TOK>
+__global__ void __launch_bounds__(320, TOK <= 32 ? 2 : 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                 const float* __restrict__ w_scale, const float* __restrict__ x_scale, __nv_bfloat16* __restrict__ Y,
                 const int* __restrict__ seg_off, const int* __restrict__ counts, int M, int Nw, int K, int ldy,
@@ -88,10 +92,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const int per = (kblocks_total + splits - 1) / splits;
   const int kb0 = split * per, kb1 = min(kblocks_total, kb0 + per);
   const int nkb = max(0, kb1 - kb0);
-  const int ntok_max = min(F_TOK, ((cnt + 15) / 16) * 16);
+  const int ntok_max = min(TOK, ((cnt + 15) / 16) * 16);
   const int stage_bytes = A_BYTES + ntok_max * FBK;
   const int stages = min(F_STAGES_MAX, pipe_bytes / stage_bytes);
-  const int chunks = (cnt + F_TOK - 1) / F_TOK;
+  const int chunks = (cnt + TOK - 1) / TOK;
   // accumulators in tensor memory: four of 64 columns when the launch has at most 64 tokens per chunk, else two of 128.
   // The multiplies of up to three k-blocks run ahead of the promotion of the first, which hides the commit -> wait ->
   // load -> arrive latency chain between the MMA thread and the promoting warps.
@@ -120,7 +124,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       uint32_t it = 0; bool ok = true;
       // the weights do not depend on the kernel before this one (which produced the activation codes and scales):
       // the weight tiles of the first stages are requested before the dependency wait, the activation tiles after it
-      const int ntok0 = min(F_TOK, ((cnt + 15) / 16) * 16);
+      const int ntok0 = min(TOK, ((cnt + 15) / 16) * 16);
       const int pre = min(stages, nkb);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&bars.full[i], A_BYTES + ntok0 * FBK);
@@ -131,7 +135,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         for (int r = 0; r < ntok0; r += 16)
           tma_load_2d(pipe + i * stage_bytes + A_BYTES + r * FBK, &tmX, &bars.full[i], (kb0 + i) * FBK, row0 + r);
       for (int c = 0; c < chunks && ok; ++c) {
-        const int ntok = min(F_TOK, ((cnt - c * F_TOK + 15) / 16) * 16);
+        const int ntok = min(TOK, ((cnt - c * TOK + 15) / 16) * 16);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           if (c == 0 && kb - kb0 < pre) continue;                 // requested above
           const int s = it % stages; const uint32_t ph = (it / stages) & 1;
@@ -141,7 +145,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           uint8_t* sa = pipe + s * stage_bytes;
           tma_load_2d(sa, &tmW, &bars.full[s], kb * FBK, e * Nw + tn * FBM);
           for (int r = 0; r < ntok; r += 16)
-            tma_load_2d(sa + A_BYTES + r * FBK, &tmX, &bars.full[s], kb * FBK, row0 + c * F_TOK + r);
+            tma_load_2d(sa + A_BYTES + r * FBK, &tmX, &bars.full[s], kb * FBK, row0 + c * TOK + r);
         }
       }
     }
@@ -149,7 +153,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     if (lane == 0) {
       uint32_t it = 0, kit = 0; bool ok = true;
       for (int c = 0; c < chunks && ok; ++c) {
-        const int ntok = min(F_TOK, ((cnt - c * F_TOK + 15) / 16) * 16);
+        const int ntok = min(TOK, ((cnt - c * TOK + 15) / 16) * 16);
         const uint32_t idesc = umma_idesc(0, 0, 0, 0, FBM, ntok);        // E4M3 x E4M3 -> FP32
         for (int kb = kb0; kb < kb1; ++kb, ++it, ++kit) {
           const int b = kit % nbuf; const uint32_t bph = (kit / nbuf) & 1;
@@ -180,9 +184,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     uint32_t kit = 0; bool ok = true;
     pdl_wait();                                   // activation scales, scratch, counters and Y belong to earlier kernels until here
     for (int c = 0; c < chunks && ok; ++c) {
-      const int ntok = min(F_TOK, ((cnt - c * F_TOK + 15) / 16) * 16);
-      const int real = min(F_TOK, cnt - c * F_TOK);
-      const int grow0 = row0 + c * F_TOK;
+      const int ntok = min(TOK, ((cnt - c * TOK + 15) / 16) * 16);
+      const int real = min(TOK, cnt - c * TOK);
+      const int grow0 = row0 + c * TOK;
       const int nblk = ntok / 16;                           // 16-column blocks of this chunk
       const int blk0 = half == 0 ? 0 : (nblk + 1) / 2;      // this warp's blocks: [blk0, blk1)
       const int blk1 = half == 0 ? (nblk + 1) / 2 : nblk;
@@ -207,9 +211,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         }
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      float acc[F_TOK / 2];                                 // columns (blk0 + i / 16) * 16 + i % 16
+      float acc[TOK / 2];                                 // columns (blk0 + i / 16) * 16 + i % 16
 #pragma unroll
-      for (int i = 0; i < F_TOK / 2; ++i) acc[i] = 0.f;
+      for (int i = 0; i < TOK / 2; ++i) acc[i] = 0.f;
       const int nb = blk1 - blk0;
       for (int kb = 0; kb < nkb && ok; ++kb, ++kit) {
         const int b0 = kit % nbuf;
@@ -221,7 +225,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const float* const sp[2] = {sXs + kb * ntok + blk0 * 16, nullptr};
         // (promoting two k-blocks per round was measured: the extra registers spill under the 168-register cap of a
         // ten-warp CTA and the kernel gets slower)
-        fp8_promote<4, 1, 0>(acc, taddr, sp, nb);
+        fp8_promote<TOK / 32, 1, 0, TOK / 2>(acc, taddr, sp, nb);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars.tmem_empty[b0]);
@@ -231,14 +235,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       bool final_here = true;
       if (splits == 1) {
 #pragma unroll
-        for (int i = 0; i < F_TOK / 2; ++i) {
+        for (int i = 0; i < TOK / 2; ++i) {
           const int t = blk0 * 16 + i;
           if (t < blk1 * 16) sT[t * FBM + nl] = __float2bfloat16(acc[i]);
         }
       } else {
         float* part = scratch + ((size_t)split * M) * Nw;
 #pragma unroll
-        for (int i = 0; i < F_TOK / 2; ++i) {
+        for (int i = 0; i < TOK / 2; ++i) {
           const int t = blk0 * 16 + i;
           if (t < blk1 * 16 && t < real && n < Nw) part[(size_t)(grow0 + t) * Nw + n] = acc[i];
         }
@@ -335,7 +339,7 @@ using namespace ff;
 FF_EXPORT int ff_gemm_fp8_plan(int M, int N, int K, long long* scratch_bytes, long long* counter_bytes) {
   const int tiles = (N + FBM - 1) / FBM;
   const int kblocks = (K + FBK - 1) / FBK;
-  const int chunks = (M + F_TOK - 1) / F_TOK;
+  const int chunks = (M + F_TOK - 1) / F_TOK;      // dense calls always use 128-token chunks
   int splits = 1;
   if (tiles * chunks < 148) {
     splits = 148 / (tiles * chunks);
@@ -358,7 +362,9 @@ FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, 
   if (splits < 1 || (splits > 1 && (!scratch || !tile_counters || experts > 1))) return FF_HOST_BAD_SHAPE;
   if (epi == 1 && (Nw % 128 || ldy < Nw / 2)) return FF_HOST_BAD_SHAPE;
   if (ldy % 8 || (reinterpret_cast<uintptr_t>(y) & 15)) return FF_HOST_BAD_ALIGN;
-  const int tok_cap = experts > 1 ? F_TOK : (M >= F_TOK ? F_TOK : (M + 15) / 16 * 16);
+  // decode-sized grouped calls (on average at most 24 padded rows per expert): 32-token chunks, two CTAs per SM
+  const bool small = experts > 1 && (long long)M <= 24ll * experts;
+  const int tok_cap = small ? 32 : (experts > 1 ? F_TOK : (M >= F_TOK ? F_TOK : (M + 15) / 16 * 16));
   const int per = ((K / 128) + splits - 1) / splits;                     // k-blocks of one split
   if (per * tok_cap * 4 > 64 * 1024) return FF_HOST_TOO_LARGE;           // scale staging
   CUtensorMap tmW, tmX;
@@ -367,11 +373,20 @@ FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, 
   r = make_tmap_2d(&tmX, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, (uint64_t)K, FBK, 16);
   if (r) return r;
   const int staging = (tok_cap * FBM * 2 + per * tok_cap * 4 + 1023) / 1024 * 1024;
-  int pipe_bytes = 224 * 1024 - staging;
+  const int budget = small ? 110 * 1024 : 224 * 1024;
+  int pipe_bytes = budget - staging;
   const int smem = staging + pipe_bytes + 1024;
-  r = opt_in_smem(gemm_fp8_kernel, 225 * 1024); if (r) return r;
   dim3 grid((Nw + FBM - 1) / FBM, splits, experts);
-  if (int lr = launch_pdl(gemm_fp8_kernel, grid, dim3(320), smem, s, 0, tmW, tmX, w_scale, x_scale, (__nv_bfloat16*)y, seg_off,
-                          counts, M, Nw, K, ldy, epi, splits, pipe_bytes, staging, tok_cap, scratch, tile_counters, status)) return lr;
+  if (small) {
+    r = opt_in_smem(gemm_fp8_kernel<32>, 111 * 1024); if (r) return r;
+    if (int lr = launch_pdl(gemm_fp8_kernel<32>, grid, dim3(320), smem, s, 0, tmW, tmX, w_scale, x_scale, (__nv_bfloat16*)y,
+                            seg_off, counts, M, Nw, K, ldy, epi, splits, pipe_bytes, staging, tok_cap, scratch, tile_counters,
+                            status)) return lr;
+    return launch_result();
+  }
+  r = opt_in_smem(gemm_fp8_kernel<F_TOK>, 225 * 1024); if (r) return r;
+  if (int lr = launch_pdl(gemm_fp8_kernel<F_TOK>, grid, dim3(320), smem, s, 0, tmW, tmX, w_scale, x_scale, (__nv_bfloat16*)y,
+                          seg_off, counts, M, Nw, K, ldy, epi, splits, pipe_bytes, staging, tok_cap, scratch, tile_counters,
+                          status)) return lr;
   return launch_result();
 }

@@ -164,15 +164,24 @@ def bench_moe(args) -> dict:
         dn = moe_cuda.Nvfp4Experts(rnd(E, h, f // 2), sc(E, h, f // 16), gs)
         fn = lambda: moe_cuda.experts_forward_nvfp4(x, wts, ids, gu, dn)
         byts = gu.nbytes() + dn.nbytes()
+    elif getattr(args, "fp8", False):
+        # FP8-resident experts (E4M3 codes + 128x128 scales; random codes: the timing does not depend on the values)
+        from ..ops import quant_ops
+        codes = lambda *shape: torch.randint(0, 120, shape, device=dev, dtype=torch.uint8)
+        sc = lambda *shape: torch.full(shape, 1e-2, device=dev, dtype=torch.float32)
+        gu = quant_ops.Fp8Experts(codes(E, 2 * f, h), sc(E, (2 * f + 127) // 128, h // 128), interleaved=True)
+        dn = quant_ops.Fp8Experts(codes(E, h, f), sc(E, (h + 127) // 128, f // 128), interleaved=False)
+        fn = lambda: quant_ops.experts_forward_fp8(x, wts, ids, gu, dn)
+        byts = E * 3 * f * h
     else:
         wgu = torch.randn(E, 2 * f, h, generator=g, device=dev, dtype=torch.bfloat16) * 0.02
         wd = torch.randn(E, h, f, generator=g, device=dev, dtype=torch.bfloat16) * 0.02
         fn = lambda: moe_ops.experts_forward(x, wts, ids, wgu, wd, 0)
         byts = (wgu.numel() + wd.numel()) * 2
-    r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
+    r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None, graph=getattr(args, "graph", False))
     pk = peaks()
     t = r["us_mean"] * 1e-6
-    r.update(op="moe_fp4" if args.fp4 else "moe", rows=rows, experts=E, top_k=k, hidden=h, ffn=f, expert_bytes=byts,
+    r.update(op="moe_fp4" if args.fp4 else "moe_fp8" if getattr(args, "fp8", False) else "moe", rows=rows, experts=E, top_k=k, hidden=h, ffn=f, expert_bytes=byts,
              gbs=byts / t / 1e9, tflops=2.0 * rows * k * 3 * f * h / t / 1e12)
     r["frac_hbm"] = r["gbs"] / pk["hbm_gbs"]
     r["peaks"] = pk["source"]
@@ -260,6 +269,8 @@ def main(argv=None) -> None:
             p.add_argument("--hidden", type=int, default=4096)
             p.add_argument("--ffn", type=int, default=1536)
             p.add_argument("--fp4", action="store_true", help="packed NVFP4 expert stacks expanded inside the GEMM")
+            p.add_argument("--fp8", action="store_true", help="FP8-resident expert stacks (E4M3, 128x128 scales), W8A8 grouped GEMMs")
+            p.add_argument("--graph", action="store_true", help="replay the operator from a CUDA graph (no host gaps)")
         else:
             p.add_argument("--batch", type=int, default=64)
             p.add_argument("--ctx", type=int, default=1024)
