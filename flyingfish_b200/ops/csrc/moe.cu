@@ -424,7 +424,11 @@ FF_EXPORT int ff_moe_grouped_gemm(const void* xs, const void* w, void* y, const 
   r = make_tmap_2d(&tmX, xs, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, capacity, (uint64_t)K * 2, GBK, 16);
   if (r) return r;
   const int staging = 64 * GBM * 4;                      // 32 KiB
-  const int pipe_bytes = 3 * (GBM * GBK * 2 + G_TOK * GBK * 2);   // 3 full-width stages = 144 KiB
+  // decode-sized calls (on average at most 24 padded rows per expert): an expert tile is short, so half the pipeline
+  // memory per CTA lets two CTAs share an SM and one streams while the other sets up or drains (FF_MOE_SMALL=0: off)
+  static const int small_on = [] { const char* ev = getenv("FF_MOE_SMALL"); return (ev && ev[0] == '0') ? 0 : 1; }();
+  const bool small = small_on && (long long)capacity <= 24ll * E_local;
+  const int pipe_bytes = small ? 76 * 1024 : 3 * (GBM * GBK * 2 + G_TOK * GBK * 2);   // 3 full-width stages = 144 KiB
   const int smem = staging + pipe_bytes + 1024;
   r = opt_in_smem(moe_grouped_gemm_kernel, 200 * 1024); if (r) return r;
   dim3 grid(Nw / GBM, E_local);
