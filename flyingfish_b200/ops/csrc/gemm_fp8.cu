@@ -363,8 +363,8 @@ FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, 
   if (epi == 1 && (Nw % 128 || ldy < Nw / 2)) return FF_HOST_BAD_SHAPE;
   if (ldy % 8 || (reinterpret_cast<uintptr_t>(y) & 15)) return FF_HOST_BAD_ALIGN;
   // decode-sized grouped calls (on average at most 24 padded rows per expert): 32-token chunks, two CTAs per SM
-  const bool small = experts > 1 && (long long)M <= 24ll * experts;
-  const int tok_cap = small ? 32 : (experts > 1 ? F_TOK : (M >= F_TOK ? F_TOK : (M + 15) / 16 * 16));
+  const bool small = experts > 1 ? (long long)M <= 24ll * experts : M <= 32;
+  const int tok_cap = small ? (experts > 1 ? 32 : (M + 15) / 16 * 16) : (experts > 1 ? F_TOK : (M >= F_TOK ? F_TOK : (M + 15) / 16 * 16));
   const int per = ((K / 128) + splits - 1) / splits;                     // k-blocks of one split
   if (per * tok_cap * 4 > 64 * 1024) return FF_HOST_TOO_LARGE;           // scale staging
   CUtensorMap tmW, tmX;
