@@ -44,25 +44,30 @@ __device__ __forceinline__ uint32_t toff(int r, int c) { return (uint32_t)((r * 
 // q       : [total rows][heads][576] bf16 (row = query position, packed per sequence via q_start)
 // out     : [total rows][heads][512] bf16
 // part_o  : fp32 [B][nsplit][max_rows][512], part_ml fp32 [B][nsplit][max_rows][2]  (max_rows = max_q * heads)
-// grid (row tiles, nsplit, B), 128 threads
-__global__ void __launch_bounds__(128)
+// grid (pairs of 16-row tiles, nsplit, B), 256 threads
+__global__ void __launch_bounds__(256)
 mla_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                 const int* __restrict__ block_table, const int* __restrict__ q_start, const int* __restrict__ q_lens,
                 const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                 float* __restrict__ part_ml, int heads, int max_blocks, int num_blocks, int nsplit, int max_rows,
                 float scale_log2, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  const int rt = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  // two 16-row tiles per CTA (warps 0-3 and 4-7) share the K pages in shared memory: half the page traffic and twice
+  // the warps per SM of a one-tile CTA
+  const int split = blockIdx.y, b = blockIdx.z;
   const int qlen = q_lens[b], ctx = ctx_lens[b], qs = q_start[b];
   const int rows_total = qlen * heads;
-  if (rt * 16 >= rows_total) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  uint8_t* sQ = smem;                                   // 16 x 576 bf16 = 18432 B
-  uint8_t* sK[2] = {smem + 18432, smem + 18432 + PAGE * LD * 2};
+  if (blockIdx.x * 32 >= rows_total) return;
+  const int tile = threadIdx.x >> 7;                    // 0 / 1
+  const int rt = blockIdx.x * 2 + tile;
+  const int tid = threadIdx.x & 127;                    // thread within the tile's four warps
+  const int warp = tid >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  uint8_t* sQ = smem + tile * 18432;                    // 16 x 576 bf16 = 18432 B per tile
+  uint8_t* sK[2] = {smem + 2 * 18432, smem + 2 * 18432 + PAGE * LD * 2};
   const int past = ctx - qlen;
 
   // Q tile -> shared memory (zero rows beyond the sequence's rows)
-  for (int i = threadIdx.x; i < 16 * CH; i += 128) {
+  for (int i = tid; i < 16 * CH; i += 128) {
     const int r = i / CH, c = i % CH;
     const int rg = rt * 16 + r;
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -75,13 +80,23 @@ mla_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     const int rg = rt * 16 + g + e * 8;
     lim[e] = rg < rows_total ? past + rg / heads : -1;
   }
-  const int last_row = min(rows_total, rt * 16 + 16) - 1;
+  const int last_row = min(rows_total, blockIdx.x * 32 + 32) - 1;     // both tiles walk the same pages
   const int last_key = past + last_row / heads;
   const int pages = last_key / PAGE + 1;
   const int per = (pages + nsplit - 1) / nsplit;
   const int p0 = split * per, p1 = min(pages, p0 + per);
 
-  float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
+  // score tile, probabilities and the soft-max state of the 16 rows live in shared memory: every warp computes the
+  // scores of its own 16 keys of a page (no redundant Q K^T), the rows' state is updated once, and every warp then
+  // accumulates its 128-wide slice of P V
+  constexpr int TILE_AUX = 16 * PAGE * 4 + 16 * PAGE * 2 + 3 * 16 * 4;
+  uint8_t* aux = smem + 2 * 18432 + 2 * PAGE * LD * 2 + tile * TILE_AUX;
+  float* sS = reinterpret_cast<float*>(aux);                                       // [16][64] f32
+  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sS + 16 * PAGE);            // [16][64] bf16, chunk-swizzled
+  float* sM = reinterpret_cast<float*>(sP + 16 * PAGE);                            // [16] running max
+  float* sL = sM + 16;                                                             // [16] running sum
+  float* sR = sL + 16;                                                             // [16] rescale of this page
+  if (tid < 16) { sM[tid] = NEG_BIG; sL[tid] = 0.f; }
   float o[16][4];
 #pragma unroll
   for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -90,88 +105,96 @@ mla_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     int blk = block_table[(size_t)b * max_blocks + page];
     if (blk < 0 || blk >= num_blocks) { bad = true; blk = 0; }
     const __nv_bfloat16* src = cache + (size_t)blk * PAGE * LD;
-    for (int i = threadIdx.x; i < PAGE * CH; i += 128) {
+    for (int i = threadIdx.x; i < PAGE * CH; i += 256) {
       const int r = i / CH, c = i % CH;
       cp_async16(sK[buf] + toff(r, c), src + (size_t)r * LD + c * 8);
     }
     cp_commit();
   };
   if (p0 < p1) issue(p0, 0);
-  const uint32_t sQa = smem_u32(sQ);
+  const uint32_t sQa = smem_u32(sQ), sPa = smem_u32(sP);
   for (int p = p0; p < p1; ++p) {
     const int buf = (p - p0) & 1;
     if (p + 1 < p1) { issue(p + 1, buf ^ 1); cp_wait<1>(); } else { cp_wait<0>(); }
     __syncthreads();
     const uint32_t sKa = smem_u32(sK[buf]);
-    float s[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    // S[16 rows][16 keys of this warp]
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll 4
     for (int kk = 0; kk < LD / 16; ++kk) {
-      uint32_t a[4];
+      uint32_t a[4], b0, b1, b2, b3;
       ldsm4(sQa + toff((lane & 7) + (((lane >> 3) & 1) << 3), 2 * kk + (lane >> 4)), a[0], a[1], a[2], a[3]);
+      ldsm4(sKa + toff(warp * 16 + ((lane >> 4) << 3) + (lane & 7), 2 * kk + ((lane >> 3) & 1)), b0, b1, b2, b3);
+      mma(s[0], a, b0, b1);
+      mma(s[1], a, b2, b3);
+    }
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {
-        const int key = np * 16 + ((lane >> 4) << 3) + (lane & 7);
-        uint32_t b0, b1, b2, b3;
-        ldsm4(sKa + toff(key, 2 * kk + ((lane >> 3) & 1)), b0, b1, b2, b3);
-        mma(s[2 * np], a, b0, b1);
-        mma(s[2 * np + 1], a, b2, b3);
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kcol = warp * 16 + i * 8 + 2 * t + (j & 1), row = g + ((j >> 1) << 3);
+        const bool vis = p * PAGE + kcol <= ((j < 2) ? lim[0] : lim[1]);
+        sS[row * PAGE + kcol] = vis ? s[i][j] * scale_log2 : NEG_BIG;
+      }
+    __syncthreads();
+    {   // soft-max bookkeeping: 8 threads per row, 8 keys each
+      const int row = tid >> 3, part = tid & 7;
+      float sc8[8], mx = NEG_BIG;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { sc8[j] = sS[row * PAGE + part * 8 + j]; mx = fmaxf(mx, sc8[j]); }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1)); mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float mprev = sM[row], bmax = fmaxf(mprev, mx);
+      float bsum = 0.f;
+      uint32_t pw[4];
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        const float p0v = (sc8[j] <= NEG_BIG) ? 0.f : exp2f(sc8[j] - bmax);
+        const float p1v = (sc8[j + 1] <= NEG_BIG) ? 0.f : exp2f(sc8[j + 1] - bmax);
+        bsum += p0v + p1v;
+        pw[j >> 1] = pack_bf16x2(p0v, p1v);
+      }
+      bsum += __shfl_xor_sync(0xffffffffu, bsum, 1); bsum += __shfl_xor_sync(0xffffffffu, bsum, 2);
+      bsum += __shfl_xor_sync(0xffffffffu, bsum, 4);
+      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(sP) + ((row * 8 + (part ^ (row & 7))) * 16)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      __syncwarp();
+      if (part == 0) {
+        const float resc = exp2f(mprev - bmax);
+        sR[row] = resc;
+        sL[row] = sL[row] * resc + bsum;
+        sM[row] = bmax;
       }
     }
-    float mx0 = NEG_BIG, mx1 = NEG_BIG;
+    __syncthreads();
+    {   // O[16][128 dims of this warp] = O * rescale + P V
+      const float r0s = sR[g], r1s = sR[g + 8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < 16; ++i) { o[i][0] *= r0s; o[i][1] *= r0s; o[i][2] *= r1s; o[i][3] *= r1s; }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int key = p * PAGE + i * 8 + 2 * t + (j & 1);
-        const bool vis = key <= ((j < 2) ? lim[0] : lim[1]);
-        const float v = vis ? s[i][j] * scale_log2 : NEG_BIG;
-        s[i][j] = v;
-        if (j < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-      }
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
-    const float a0 = exp2f(m[0] - mn0), a1 = exp2f(m[1] - mn1);
-    m[0] = mn0; m[1] = mn1;
-    float rs0 = 0.f, rs1 = 0.f;
+      for (int ks = 0; ks < 4; ++ks) {
+        uint32_t pa[4];
+        {
+          const int prow = (lane & 7) + (((lane >> 3) & 1) << 3), pch = 2 * ks + (lane >> 4);
+          ldsm4(sPa + (uint32_t)((prow * 8 + (pch ^ (prow & 7))) * 16), pa[0], pa[1], pa[2], pa[3]);
+        }
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float pv = (s[i][j] <= NEG_BIG) ? 0.f : exp2f(s[i][j] - ((j < 2) ? mn0 : mn1));
-        s[i][j] = pv;
-        if (j < 2) rs0 += pv; else rs1 += pv;
-      }
-    l[0] = l[0] * a0 + rs0; l[1] = l[1] * a1 + rs1;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      uint32_t pa[4];
-      pa[0] = pack_bf16x2(s[2 * ks][0], s[2 * ks][1]);     pa[1] = pack_bf16x2(s[2 * ks][2], s[2 * ks][3]);
-      pa[2] = pack_bf16x2(s[2 * ks + 1][0], s[2 * ks + 1][1]); pa[3] = pack_bf16x2(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-#pragma unroll
-      for (int dp = 0; dp < 8; ++dp) {
-        const int key = ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
-        uint32_t b0, b1, b2, b3;
-        ldsm4t(sKa + toff(key, warp * 16 + dp * 2 + (lane >> 4)), b0, b1, b2, b3);
-        mma(o[2 * dp], pa, b0, b1);
-        mma(o[2 * dp + 1], pa, b2, b3);
+        for (int dp = 0; dp < 8; ++dp) {
+          const int key = ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+          uint32_t b0, b1, b2, b3;
+          ldsm4t(sKa + toff(key, warp * 16 + dp * 2 + (lane >> 4)), b0, b1, b2, b3);
+          mma(o[2 * dp], pa, b0, b1);
+          mma(o[2 * dp + 1], pa, b2, b3);
+        }
       }
     }
     __syncthreads();
   }
   if (bad) set_status(status, KID_MLA, FF_ERR_BOUNDS, b, rt);
-  float l0 = l[0], l1 = l[1];
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int rg = rt * 16 + g + e * 8;
     if (rg >= rows_total) continue;
-    const float L = e ? l1 : l0;
+    const float L = sL[g + 8 * e];
     if (nsplit == 1) {
       const float inv = L > 0.f ? 1.f / L : 0.f;
       __nv_bfloat16* dst = out + ((size_t)(qs + rg / heads) * heads + rg % heads) * LV + warp * 128;
@@ -183,7 +206,7 @@ mla_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
       float* dst = part_o + pr * LV + warp * 128;
 #pragma unroll
       for (int i = 0; i < 16; ++i) { dst[i * 8 + 2 * t] = o[i][2 * e]; dst[i * 8 + 2 * t + 1] = o[i][2 * e + 1]; }
-      if (warp == 0 && t == 0) { part_ml[pr * 2] = m[e]; part_ml[pr * 2 + 1] = L; }
+      if (warp == 0 && t == 0) { part_ml[pr * 2] = sM[g + 8 * e]; part_ml[pr * 2 + 1] = L; }
     }
   }
 }
@@ -229,10 +252,10 @@ __global__ void mla_cache_write_kernel(const __nv_bfloat16* __restrict__ c, cons
 }  // namespace ff
 using namespace ff;
 
-constexpr int MLA_SMEM = 18432 + 2 * mla::PAGE * mla::LD * 2;     // Q tile + two page stages = 165888 B
+constexpr int MLA_SMEM = 2 * 18432 + 2 * mla::PAGE * mla::LD * 2 + 2 * (16 * mla::PAGE * 4 + 16 * mla::PAGE * 2 + 3 * 16 * 4);   // two Q tiles + two page stages + per-tile score / probability tiles and row state
 
 FF_EXPORT int ff_mla_plan(int batch, int heads, int max_q, int max_ctx, long long* part_o_bytes, long long* part_ml_bytes) {
-  const int tiles = (max_q * heads + 15) / 16;
+  const int tiles = (max_q * heads + 31) / 32;        // a CTA owns two 16-row tiles
   const int ctas = batch * tiles;
   int nsplit = 1;
   if (ctas < 148) nsplit = (148 + ctas - 1) / ctas;
@@ -252,8 +275,8 @@ FF_EXPORT int ff_mla_attn(const void* q, const void* cache, const int* block_tab
   if (nsplit > 1 && (!part_o || !part_ml)) return FF_HOST_BAD_SHAPE;
   if (int r = opt_in_smem(mla::mla_attn_kernel, MLA_SMEM)) return r;
   const int max_rows = max_q * heads;
-  dim3 grid((max_rows + 15) / 16, nsplit, batch);
-  mla::mla_attn_kernel<<<grid, 128, MLA_SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table,
+  dim3 grid((max_rows + 31) / 32, nsplit, batch);
+  mla::mla_attn_kernel<<<grid, 256, MLA_SMEM, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table,
       q_start, q_lens, ctx_lens, (__nv_bfloat16*)out, part_o, part_ml, heads, max_blocks, num_blocks, nsplit, max_rows,
       scale * 1.4426950408889634f, status);
   if (int r = launch_result()) return r;
