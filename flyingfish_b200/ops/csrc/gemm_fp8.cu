@@ -74,7 +74,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 const float* __restrict__ w_scale, const float* __restrict__ x_scale, __nv_bfloat16* __restrict__ Y,
                 const int* __restrict__ seg_off, const int* __restrict__ counts, int M, int Nw, int K, int ldy,
                 int epi, int splits, int pipe_bytes, int stage_off, int tok_cap, float* __restrict__ scratch,
-                int* __restrict__ tile_counters, int* status) {
+                int* __restrict__ tile_counters, int* status, int xs_ld) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ Fp8Bars bars;
   const int tn = blockIdx.x, split = blockIdx.y, e = blockIdx.z;
@@ -201,7 +201,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           v[u] = 0.f;
           if (i < ntok * nkb) {
             const int t = i / nkb, kb = i - t * nkb;
-            if (t < real) v[u] = ws_row[kb0 + kb] * x_scale[(size_t)(grow0 + t) * kblocks_total + kb0 + kb];
+            if (t < real) v[u] = ws_row[kb0 + kb] * x_scale[(size_t)(grow0 + t) * xs_ld + kb0 + kb];
           }
         }
 #pragma unroll
@@ -354,9 +354,11 @@ FF_EXPORT int ff_gemm_fp8_plan(int M, int N, int K, long long* scratch_bytes, lo
 
 // Dense: seg_off = counts = null, experts = 1. Grouped: W is [experts*Nw, K], w_scale
 // [experts*ceil(Nw/128), K/128], X / x_scale are the 16-row padded sorted buffers, M = capacity.
-FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, const float* w_scale, void* y,
-                          const int* seg_off, const int* counts, int experts, int M, int Nw, int K, int ldy, int epi,
-                          int splits, float* scratch, int* tile_counters, int* status, cudaStream_t s) {
+static int gemm_fp8_launch(const void* xq, const float* x_scale, const void* wq, const float* w_scale, void* y,
+                           const int* seg_off, const int* counts, int experts, int M, int Nw, int K, int ldy, int epi,
+                           int splits, float* scratch, int* tile_counters, int* status, cudaStream_t s, long long ldxq,
+                           int xs_ld) {
+  if (ldxq < K || ldxq % 16 || xs_ld < K / 128) return FF_HOST_BAD_SHAPE;
   if (M <= 0 || Nw <= 0 || K <= 0 || K % 128 || experts < 1) return FF_HOST_BAD_SHAPE;
   if (experts > 1 && (!seg_off || !counts || Nw % 128)) return FF_HOST_BAD_SHAPE;
   if (splits < 1 || (splits > 1 && (!scratch || !tile_counters || experts > 1))) return FF_HOST_BAD_SHAPE;
@@ -370,7 +372,7 @@ FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, 
   CUtensorMap tmW, tmX;
   int r = make_tmap_2d(&tmW, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, (uint64_t)experts * Nw, (uint64_t)K, FBK, FBM);
   if (r) return r;
-  r = make_tmap_2d(&tmX, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, (uint64_t)K, FBK, 16);
+  r = make_tmap_2d(&tmX, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, (uint64_t)ldxq, FBK, 16);
   if (r) return r;
   const int staging = (tok_cap * FBM * 2 + per * tok_cap * 4 + 1023) / 1024 * 1024;
   const int budget = small ? 110 * 1024 : 224 * 1024;
@@ -381,12 +383,28 @@ FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, 
     r = opt_in_smem(gemm_fp8_kernel<32>, 111 * 1024); if (r) return r;
     if (int lr = launch_pdl(gemm_fp8_kernel<32>, grid, dim3(320), smem, s, 0, tmW, tmX, w_scale, x_scale, (__nv_bfloat16*)y,
                             seg_off, counts, M, Nw, K, ldy, epi, splits, pipe_bytes, staging, tok_cap, scratch, tile_counters,
-                            status)) return lr;
+                            status, xs_ld)) return lr;
     return launch_result();
   }
   r = opt_in_smem(gemm_fp8_kernel<F_TOK>, 225 * 1024); if (r) return r;
   if (int lr = launch_pdl(gemm_fp8_kernel<F_TOK>, grid, dim3(320), smem, s, 0, tmW, tmX, w_scale, x_scale, (__nv_bfloat16*)y,
                           seg_off, counts, M, Nw, K, ldy, epi, splits, pipe_bytes, staging, tok_cap, scratch, tile_counters,
-                          status)) return lr;
+                          status, xs_ld)) return lr;
   return launch_result();
+}
+
+FF_EXPORT int ff_gemm_fp8(const void* xq, const float* x_scale, const void* wq, const float* w_scale, void* y,
+                          const int* seg_off, const int* counts, int experts, int M, int Nw, int K, int ldy, int epi,
+                          int splits, float* scratch, int* tile_counters, int* status, cudaStream_t s) {
+  return gemm_fp8_launch(xq, x_scale, wq, w_scale, y, seg_off, counts, experts, M, Nw, K, ldy, epi, splits, scratch,
+                         tile_counters, status, s, (long long)K, K / 128);
+}
+
+// The same with strided activations: code rows ldxq bytes apart, scale rows xs_ld floats apart (packed records
+// [K codes | K / 128 scales] as they arrive from an expert-parallel dispatch: ldxq = K + K / 32, xs_ld = ldxq / 4).
+FF_EXPORT int ff_gemm_fp8_strided(const void* xq, const float* x_scale, long long ldxq, int xs_ld, const void* wq,
+                                  const float* w_scale, void* y, const int* seg_off, const int* counts, int experts, int M,
+                                  int Nw, int K, int ldy, int epi, int* status, cudaStream_t s) {
+  return gemm_fp8_launch(xq, x_scale, wq, w_scale, y, seg_off, counts, experts, M, Nw, K, ldy, epi, 1, nullptr, nullptr,
+                         status, s, ldxq, xs_ld);
 }

@@ -63,7 +63,8 @@ __global__ void ep_count_kernel(const int* __restrict__ ids, int n_assign, int E
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(EpArena a, const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
                    const int* __restrict__ my_counts, int* __restrict__ cursors, int* __restrict__ pos, int rows,
-                   int top_k, int ldx, int* __restrict__ seg_off_out, int* __restrict__ counts_out, int* status) {
+                   int top_k, int ldx, int* __restrict__ seg_off_out, int* __restrict__ counts_out, int* status,
+                   int row_vecs) {
   __shared__ int s_base[EP_MAX_E];     // first slot of (expert e, source = me) on the owner
   __shared__ int s_tot[EP_MAX_E];
   __shared__ int s_ok;
@@ -118,7 +119,9 @@ ep_dispatch_kernel(EpArena a, const __nv_bfloat16* __restrict__ x, const int* __
   // 4. scatter rows: one warp per token row. Lane j < top_k claims the slot of assignment j; the row is
   //    read once into registers (16 vectors per lane per pass) and stored to each of its k owners.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  const int nvec = a.hidden >> 3;
+  // 16-byte vectors of a travelling row: hidden / 8 for BF16 rows; packed FP8 records ([codes | 1x128 scales]) are
+  // about half of that
+  const int nvec = row_vecs;
   for (int r = blockIdx.x * wpb + warp; r < rows; r += gridDim.x * wpb) {
     int slot = -1, d = 0;
     if (lane < top_k) {
@@ -275,12 +278,13 @@ FF_EXPORT long long ff_ep_arena_layout(int world, int E, int hidden, int capacit
 
 // counts_scratch / cursors: int32[E] each (device, local). seg_off_out: int32[E_local+1],
 // counts_out: int32[E_local], pos: int32[rows*top_k].
-FF_EXPORT int ff_ep_dispatch(const EpArenaHost* h, const void* x, const int* ids, int rows, int top_k, int ldx,
-                             int* counts_scratch, int* cursors, int* pos, int* seg_off_out, int* counts_out,
-                             int* status, cudaStream_t s) {
+static int ep_dispatch_launch(const EpArenaHost* h, const void* x, const int* ids, int rows, int top_k, int ldx,
+                              int* counts_scratch, int* cursors, int* pos, int* seg_off_out, int* counts_out,
+                              int* status, cudaStream_t s, int row_vecs) {
   EpArena a;
   if (int r = to_arena(h, a)) return r;
   if (rows <= 0 || top_k < 1 || top_k > 16 || ldx % 8) return FF_HOST_BAD_SHAPE;
+  if (row_vecs <= 0 || row_vecs > (a.hidden >> 3) || ldx < row_vecs * 8) return FF_HOST_BAD_SHAPE;
   cudaError_t e = cudaMemsetAsync(counts_scratch, 0, (size_t)a.E * 4, s);
   if (e != cudaSuccess) return (int)e;
   e = cudaMemsetAsync(cursors, 0, (size_t)a.E * 4, s);
@@ -291,9 +295,26 @@ FF_EXPORT int ff_ep_dispatch(const EpArenaHost* h, const void* x, const int* ids
   if (ctas > 296) ctas = 296;
   if (ctas < 1) ctas = 1;
   ep_dispatch_kernel<<<ctas, 256, 0, s>>>(a, (const __nv_bfloat16*)x, ids, counts_scratch, cursors, pos, rows, top_k,
-                                          ldx, seg_off_out, counts_out, status);
+                                          ldx, seg_off_out, counts_out, status, row_vecs);
   ep_wait_kernel<<<1, 32, 0, s>>>(a, EP_FLAG_DISPATCH, status);
   return launch_result();
+}
+
+FF_EXPORT int ff_ep_dispatch(const EpArenaHost* h, const void* x, const int* ids, int rows, int top_k, int ldx,
+                             int* counts_scratch, int* cursors, int* pos, int* seg_off_out, int* counts_out,
+                             int* status, cudaStream_t s) {
+  return ep_dispatch_launch(h, x, ids, rows, top_k, ldx, counts_scratch, cursors, pos, seg_off_out, counts_out, status, s,
+                            h->hidden >> 3);
+}
+
+// Dispatch of packed records of `row_bytes` bytes (a multiple of 16, at most the arena's BF16 row): x rows are
+// `ld_bytes` apart. The receive buffer then holds records `row_bytes` apart (slot s at off_x + s * row_bytes).
+FF_EXPORT int ff_ep_dispatch_bytes(const EpArenaHost* h, const void* x, const int* ids, int rows, int top_k, int ld_bytes,
+                                   int row_bytes, int* counts_scratch, int* cursors, int* pos, int* seg_off_out,
+                                   int* counts_out, int* status, cudaStream_t s) {
+  if (row_bytes <= 0 || row_bytes % 16 || ld_bytes % 16 || ld_bytes < row_bytes) return FF_HOST_BAD_SHAPE;
+  return ep_dispatch_launch(h, x, ids, rows, top_k, ld_bytes / 2, counts_scratch, cursors, pos, seg_off_out, counts_out,
+                            status, s, row_bytes / 16);
 }
 
 FF_EXPORT int ff_ep_combine(const EpArenaHost* h, const int* pos, const int* ids, const float* w, void* out, int rows,

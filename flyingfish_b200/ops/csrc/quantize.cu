@@ -38,7 +38,8 @@ __device__ __forceinline__ uint32_t e2m1_code(float v) {
 
 // one warp per (row, 128-group): lane holds 4 consecutive elements
 __global__ void quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                                       float* __restrict__ scale, int rows, int K, int ldx, int ue8m0) {
+                                       float* __restrict__ scale, int rows, int K, int ldx, int ue8m0, long long ldq,
+                                       long long lds) {
   pdl_trigger();
   pdl_wait();
   const int groups = K >> 7;
@@ -56,8 +57,8 @@ __global__ void quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint
   // true division (not a reciprocal multiply) so the codes match the host codec bit for bit
   const uint32_t packed = (uint32_t)to_e4m3(__fdiv_rn(a.x, s)) | ((uint32_t)to_e4m3(__fdiv_rn(a.y, s)) << 8) |
                           ((uint32_t)to_e4m3(__fdiv_rn(b.x, s)) << 16) | ((uint32_t)to_e4m3(__fdiv_rn(b.y, s)) << 24);
-  *reinterpret_cast<uint32_t*>(q + (size_t)row * K + g * 128 + lane * 4) = packed;
-  if (lane == 0) scale[(size_t)row * groups + g] = s;
+  *reinterpret_cast<uint32_t*>(q + (size_t)row * ldq + g * 128 + lane * 4) = packed;
+  if (lane == 0) scale[(size_t)row * lds + g] = s;
 }
 
 __global__ void dequant_fp8_block_kernel(const uint8_t* __restrict__ q, const float* __restrict__ scale,
@@ -133,7 +134,20 @@ FF_EXPORT int ff_quant_fp8_1x128(const void* x, void* q, float* scale, int rows,
   if (rows <= 0 || K <= 0 || K % 128 || ldx % 4) return FF_HOST_BAD_SHAPE;
   const long long warps = (long long)rows * (K / 128);
   if (int lr = launch_pdl(quant_fp8_1x128_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, s, 0,
-                          (const __nv_bfloat16*)x, (uint8_t*)q, scale, rows, K, ldx, ue8m0)) return lr;
+                          (const __nv_bfloat16*)x, (uint8_t*)q, scale, rows, K, ldx, ue8m0, (long long)K,
+                          (long long)(K / 128))) return lr;
+  return launch_result();
+}
+
+// The same quantisation into strided outputs: code rows ldq bytes apart, scale rows lds floats apart. With
+// scale = (float*)(q + K), ldq = K + K / 32 and lds = ldq / 4 a row is one packed record [K codes | K / 128 scales]:
+// the form in which token rows travel to the ranks that own their experts.
+FF_EXPORT int ff_quant_fp8_1x128_strided(const void* x, void* q, float* scale, int rows, int K, int ldx, long long ldq,
+                                         long long lds, cudaStream_t s) {
+  if (rows <= 0 || K <= 0 || K % 128 || ldx % 4 || ldq < K || ldq % 4 || lds < K / 128) return FF_HOST_BAD_SHAPE;
+  const long long warps = (long long)rows * (K / 128);
+  if (int lr = launch_pdl(quant_fp8_1x128_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, s, 0,
+                          (const __nv_bfloat16*)x, (uint8_t*)q, scale, rows, K, ldx, 0, ldq, lds)) return lr;
   return launch_result();
 }
 

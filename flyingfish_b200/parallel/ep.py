@@ -13,6 +13,7 @@ layer's packet through pinned host memory (src/backend/cuda/engine_moe.rs:1643-1
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_longlong, c_ulonglong
 
 import torch
@@ -27,6 +28,10 @@ class EpArenaHost(ctypes.Structure):
     _fields_ = [("ptrs", c_ulonglong * 8), ("rank", c_int), ("world", c_int), ("E", c_int), ("E_local", c_int),
                 ("hidden", c_int), ("capacity", c_int), ("off_flags", c_longlong), ("off_counts", c_longlong),
                 ("off_x", c_longlong), ("off_y", c_longlong)]
+
+
+# FP8-resident experts: ship rows as packed E4M3 records (FLYINGFISH_EP_FP8_DISPATCH=0: BF16 rows, quantised on arrival)
+FP8_DISPATCH = os.environ.get("FLYINGFISH_EP_FP8_DISPATCH", "1") != "0"
 
 
 class EPComm:
@@ -91,6 +96,15 @@ class EPComm:
         return self._baseline(x, weights, ids, lw, mode)
 
     def _fused(self, x, weights, ids, lw, mode, layer: int = -1):
+        if self.provider is None and not isinstance(lw.experts_gu, torch.Tensor) and self.fp8_dispatch_ok():
+            # FP8-resident experts: rows are quantised 1x128 HERE and travel as packed records [codes | scales]
+            # (hidden + hidden / 32 bytes instead of 2 * hidden): the owners' W8A8 GEMMs read the records in place
+            pos = self.dispatch_fp8(x, ids)
+            self.experts_fp8_packed(lw)
+            out = self.combine(pos, ids, weights, x.shape[0])
+            self.stats["fused_calls"] += 1
+            self.stats["fp8_dispatch_calls"] = self.stats.get("fp8_dispatch_calls", 0) + 1
+            return out
         pos = self.dispatch(x, ids)
         if self.provider is not None:
             self.provider.ep_experts(layer, self.recv_x, self._seg_off, self._counts, self.capacity, self.out_y,
@@ -119,6 +133,53 @@ class EPComm:
         oplib.check(rc, "ff_ep_dispatch")
         ops._count(3)
         return pos
+
+    def fp8_dispatch_ok(self) -> bool:
+        rec = self.hidden + self.hidden // 32
+        return FP8_DISPATCH and self.hidden % 128 == 0 and rec % 16 == 0
+
+    def dispatch_fp8(self, x: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """Quantise the local rows (E4M3, one scale per 128) into packed records and scatter them to the owners."""
+        lib = oplib.kernels()
+        rows, top_k = ids.shape
+        E, El, h = self.E, self.El, self.hidden
+        rec = h + h // 32
+        counts_s, cursors = self.scratch[:E], self.scratch[E: 2 * E]
+        self._seg_off, self._counts = self.scratch[2 * E: 2 * E + El + 1], self.scratch[2 * E + El + 1:]
+        pos = torch.empty(rows * top_k, dtype=torch.int32, device=x.device)
+        self._rows_per_expert = rows * top_k / El
+        x = x.contiguous(); ids = ids.contiguous()
+        packed = torch.empty(rows, rec, dtype=torch.uint8, device=x.device)
+        rc = lib.ff_quant_fp8_1x128_strided(oplib.ptr(x), oplib.ptr(packed), ctypes.c_void_p(packed.data_ptr() + h), rows, h,
+                                            x.stride(0), ctypes.c_longlong(rec), ctypes.c_longlong(rec // 4),
+                                            oplib.stream_ptr())
+        oplib.check(rc, "ff_quant_fp8_1x128_strided")
+        rc = lib.ff_ep_dispatch_bytes(ctypes.byref(self.arena), oplib.ptr(packed), oplib.ptr(ids), rows, top_k, rec, rec,
+                                      oplib.ptr(counts_s), oplib.ptr(cursors), oplib.ptr(pos), oplib.ptr(self._seg_off),
+                                      oplib.ptr(self._counts), oplib.ptr(oplib.status_tensor(x.device)), oplib.stream_ptr())
+        oplib.check(rc, "ff_ep_dispatch_bytes")
+        ops._count(4)
+        return pos
+
+    def experts_fp8_packed(self, lw) -> None:
+        """W8A8 grouped GEMMs of this rank's experts over the packed records in the receive buffer."""
+        from ..ops import quant_ops
+        lib = oplib.kernels()
+        h = self.hidden
+        rec = h + h // 32
+        base = self.recv_x.data_ptr()
+        gu = lw.experts_gu
+        el, nw, _ = gu.codes.shape
+        mid = torch.empty(self.capacity, nw // 2, dtype=torch.bfloat16, device=self.recv_x.device)
+        rc = lib.ff_gemm_fp8_strided(ctypes.c_void_p(base), ctypes.c_void_p(base + h), ctypes.c_longlong(rec), rec // 4,
+                                     oplib.ptr(gu.codes), oplib.ptr(gu.scale), oplib.ptr(mid), oplib.ptr(self._seg_off),
+                                     oplib.ptr(self._counts), el, self.capacity, nw, h, nw // 2, 1,
+                                     oplib.ptr(oplib.status_tensor(mid.device)), oplib.stream_ptr())
+        oplib.check(rc, "ff_gemm_fp8_strided")
+        ops._count()
+        hq, hs = quant_ops.quant_fp8_act(mid)
+        quant_ops.grouped_gemm_fp8(hq, hs, lw.experts_down.codes, lw.experts_down.scale, self._seg_off, self._counts,
+                                   self.capacity, epi=0, out=self.out_y)
 
     def experts(self, lw) -> None:
         """Grouped gate/up (+SwiGLU) and down GEMMs of this rank's experts over the received rows."""

@@ -135,6 +135,7 @@ def test_ep2_fp8_experts_gpu(tmp_path):
     from flyingfish_b200.config import Settings
     res = _launch(2, "cuda", "ep", tmp_path, 29519, model="deepseek-v3-fp8-mini")
     assert res["stats"]["fused_calls"] > 0
+    assert res["stats"].get("fp8_dispatch_calls", 0) > 0          # rows travelled as packed E4M3 records
     m = Model.load("deepseek-v3-fp8-mini", Settings(capacity=256, max_batch=4, graph=False), device="cuda", seed=0)
     for r in res["per_rank"]:
         single = _single_moe("cuda", r["prompts"], "deepseek-v3-fp8-mini")
