@@ -122,7 +122,10 @@ class Model:
                 pass
         plan = plan_engine(spec, settings, device, weights_bytes=weights.nbytes(), tp=tp.size)
         log_json("prefill_memory_plan", verbose_only=True, **plan.to_json())
-        engine = Engine(net, spec, settings, plan.kv_blocks, device, max_prefill_rows=plan.prefill_chunk)
+        chunk = plan.prefill_chunk
+        if ep is not None and getattr(ep, "arena", None) is not None and getattr(ep, "max_rows", 0) > 0:
+            chunk = min(chunk, ep.max_rows)          # the expert-parallel receive buffers are sized for this many rows per call
+        engine = Engine(net, spec, settings, plan.kv_blocks, device, max_prefill_rows=chunk)
         m = cls(engine, spec, settings, tokenizer, name)
         if spec.extra.get("vision"):
             from .models.vision import VisionSpec, VisionTower

@@ -67,7 +67,8 @@ __device__ __forceinline__ bool next_tile(const GroupArgs& g, TileWalk& w, int t
     return true;
   }
   while (w.e < g.E) {
-    const int cnt = g.counts[w.e];
+    // a segment reaching past the row buffers (an overflowed dispatch, reported through the status word) is cut there
+    const int cnt = max(0, min(g.counts[w.e], M - g.seg_off[w.e]));
     const int tme = (cnt + BM - 1) / BM;
     const int n = tme * tiles_n;
     if (t < w.base + n) {

@@ -78,9 +78,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   __shared__ Fp8Bars bars;
   const int tn = blockIdx.x, split = blockIdx.y, e = blockIdx.z;
-  const int cnt = counts ? counts[e] : M;
-  if (cnt <= 0) return;
   const int row0 = seg_off ? seg_off[e] : 0;
+  // a segment that reaches past the row buffers (a dispatch that overflowed its capacity and said so through the status
+  // word) is cut at the buffer end: no row beyond M is read or written
+  const int cnt = counts ? min(counts[e], M - row0) : M;
+  if (cnt <= 0) return;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // staging is sized by the host for the tokens of this launch (tok_cap) and the k-blocks of one split: what it
   // does not take is pipeline depth, and the bytes in flight per SM are what bounds the weight stream

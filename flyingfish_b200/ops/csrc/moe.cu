@@ -190,12 +190,13 @@ __device__ __forceinline__ float bfr(float x) { return __bfloat162float(__float2
 __global__ void __launch_bounds__(192, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                         __nv_bfloat16* __restrict__ Y, const int* __restrict__ seg_off, const int* __restrict__ counts,
-                        int Nw, int K, int ldy, int epi, int pipe_bytes, int stage_off, int* status) {
+                        int Nw, int K, int ldy, int epi, int pipe_bytes, int stage_off, int* status, int capacity) {
   int stages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ GroupBars bars;
   const int e = blockIdx.y, tn = blockIdx.x;
-  const int cnt = counts[e];
+  // a segment reaching past the row buffers (an overflowed dispatch, reported through the status word) is cut there
+  const int cnt = min(counts[e], capacity - seg_off[e]);
   if (cnt <= 0) return;                                   // uniform for the CTA
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sT = reinterpret_cast<float*>(smem);             // staging [tok chunk of 64][128] fp32 = 32 KiB
@@ -433,7 +434,7 @@ FF_EXPORT int ff_moe_grouped_gemm(const void* xs, const void* w, void* y, const 
   r = opt_in_smem(moe_grouped_gemm_kernel, 200 * 1024); if (r) return r;
   dim3 grid(Nw / GBM, E_local);
   moe_grouped_gemm_kernel<<<grid, 192, smem, s>>>(tmW, tmX, (__nv_bfloat16*)y, seg_off, counts, Nw, K, ldy, epi,
-                                                  pipe_bytes, staging, status);
+                                                  pipe_bytes, staging, status, capacity);
   return launch_result();
 }
 

@@ -65,11 +65,12 @@ __global__ void __launch_bounds__(192, 2)
 moe_fp4_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ Wq,
                        const uint8_t* __restrict__ Wsc, const float* __restrict__ Wglobal, __nv_bfloat16* __restrict__ Y,
                        const int* __restrict__ seg_off, const int* __restrict__ counts, int Nw, int K, int ldy, int epi,
-                       int* status) {
+                       int* status, int capacity) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ Fp4Bars bars;
   const int e = blockIdx.y, tn = blockIdx.x;
-  const int cnt = counts[e];
+  // a segment reaching past the row buffers (an overflowed dispatch, reported through the status word) is cut there
+  const int cnt = min(counts[e], capacity - seg_off[e]);
   if (cnt <= 0) return;                                   // uniform for the CTA
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sT = reinterpret_cast<float*>(smem);             // epilogue staging [32 tokens][128] fp32
@@ -291,6 +292,6 @@ FF_EXPORT int ff_moe_grouped_gemm_nvfp4(const void* xs, const void* wq, const vo
   r = opt_in_smem(moe_fp4_grouped_kernel, smem); if (r) return r;
   dim3 grid(Nw / F4_BM, E_local);
   moe_fp4_grouped_kernel<<<grid, 192, smem, s>>>(tmX, (const uint8_t*)wq, (const uint8_t*)wsc, wglobal, (__nv_bfloat16*)y,
-                                                 seg_off, counts, Nw, K, ldy, epi, status);
+                                                 seg_off, counts, Nw, K, ldy, epi, status, capacity);
   return launch_result();
 }

@@ -45,6 +45,7 @@ class EPComm:
         self.stats = {"fused_calls": 0, "baseline_calls": 0}
         self.provider = None          # experts.provider.TieredExpertProvider when this rank tiers its own experts
         self.arena = None
+        self.max_rows = max_rows      # most local rows one layer call may dispatch (the engine caps its prefill chunk by it)
         if self.device.type == "cuda" and self.size > 1:
             self._setup_arena(max_rows, top_k)
 
