@@ -110,6 +110,12 @@ def _global_parser() -> argparse.ArgumentParser:
     cl.add_argument("--a", required=True)
     cl.add_argument("--b", required=True)
 
+    tr = sub.add_parser("transcribe")
+    tr.add_argument("input", help="RIFF/WAVE file (any rate and channel count; mixed down and resampled to 16 kHz)")
+    tr.add_argument("--format", choices=["txt", "json", "srt", "vtt"], default="txt")
+    tr.add_argument("--output", help="file to write instead of standard output")
+    tr.add_argument("--stream", action="store_true")
+
     for name in DSPARK_TOOLS:
         dp = sub.add_parser(name)
         dp.add_argument("--prompt-tokens", type=int, default=48)
@@ -186,6 +192,8 @@ def check_flags(args) -> None:
                              "(verification rows and shared prefixes read BF16 pages)")
     if args.tp < 1 or (args.tp > 1 and args.cpu):
         raise SystemExit("--tp needs one CUDA device per rank")
+    if args.command == "transcribe" and (args.draft_model or args.prefix_cache or args.kv_format != "bf16"):
+        raise SystemExit("transcribe takes none of the text-generation flags")
     if args.tp > 1 and args.command not in ("generate", "bench", "serve"):
         raise SystemExit(f"--tp applies to generate, bench and serve, not to {args.command}")
     if args.command in DSPARK_TOOLS and not args.draft_model:
@@ -440,6 +448,28 @@ def cmd_embed(args) -> dict:
     return {"dim": len(vec), "embedding": vec}
 
 
+def cmd_transcribe(args) -> None:
+    """Speech recognition of one audio file (src/main.rs:861-990 of the reference: same formats, output file guard)."""
+    from .speech import ParakeetModel, load_audio
+    if not args.model:
+        raise SystemExit("transcribe needs --model")
+    arch = json.loads((Path(args.model) / "config.json").read_text()).get("architectures", [None])[0]
+    if arch != "ParakeetForTDT":
+        raise SystemExit(f"unsupported transcription architecture {arch}")
+    if args.stream:
+        raise SystemExit("streaming transcription is not available for ParakeetForTDT")
+    out_path = check_output_path(args.output, args.model) if args.output else None
+    device = "cpu" if args.cpu else f"cuda:{args.device}"
+    model = ParakeetModel.load(args.model, device)
+    wave = load_audio(args.input, model.spec.mel.sampling_rate)
+    result = model.transcribe([wave])[0]
+    text = {"txt": result.text + "\n", "json": result.to_json() + "\n", "srt": result.to_srt(), "vtt": result.to_vtt()}[args.format]
+    if out_path is not None:
+        out_path.write_text(text)
+    else:
+        sys.stdout.write(text)
+
+
 def cmd_serve(args) -> None:
     from .loaders.tokenizer import read_chat_template
     from .serve.http import run
@@ -508,6 +538,9 @@ def main(argv: list[str] | None = None) -> int:
                 "bench-spec": cmd_spec, "profile-spec": cmd_spec, **{t: cmd_dspark for t in DSPARK_TOOLS}}
     if args.command == "serve":
         cmd_serve(args)
+        return 0
+    if args.command == "transcribe":
+        cmd_transcribe(args)
         return 0
     out = handlers[args.command](args)
     if _world()[1] == 0:

@@ -204,7 +204,7 @@ def save_safetensors(path: str | Path, tensors: dict[str, torch.Tensor], metadat
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _REV:
             raise CheckpointError(f"cannot store dtype {t.dtype}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool else t.to(torch.uint8).numpy().tobytes()
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool else t.to(torch.uint8).numpy().tobytes()
         header[name] = {"dtype": _REV[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)

@@ -104,6 +104,7 @@ __device__ __forceinline__ float act_apply(float x, int act) {
     case 2: return x / (1.f + __expf(-1.702f * x));
     case 3: return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
     case 4: return x / (1.f + __expf(-x));
+    case 5: return fmaxf(x, 0.f);
     default: return x;
   }
 }
@@ -315,7 +316,7 @@ FF_EXPORT int ff_layernorm(const void* x, const void* w, const void* b, void* y,
 }
 
 FF_EXPORT int ff_bias_act(void* x, const void* bias, long long rows, int n, int ldx, int act, cudaStream_t s) {
-  if (rows <= 0 || n <= 0 || n % 8 || ldx % 8 || act < 0 || act > 4) return FF_HOST_BAD_SHAPE;
+  if (rows <= 0 || n <= 0 || n % 8 || ldx % 8 || act < 0 || act > 5) return FF_HOST_BAD_SHAPE;
   const long long total = rows * (n / 8);
   if (int lr = launch_pdl(bias_act_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)x,
                           (const __nv_bfloat16*)bias, rows, n, ldx, act)) return lr;

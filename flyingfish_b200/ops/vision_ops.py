@@ -14,7 +14,7 @@ from . import _count, _require, linear
 from .lib import check, kernels, ptr, status_tensor, stream_ptr
 
 BF16 = torch.bfloat16
-ACTS = {"none": 0, "gelu_tanh": 1, "quick_gelu": 2, "gelu": 3, "silu": 4}
+ACTS = {"none": 0, "gelu_tanh": 1, "quick_gelu": 2, "gelu": 3, "silu": 4, "relu": 5}
 
 
 def _r(x: torch.Tensor) -> torch.Tensor:
@@ -51,6 +51,8 @@ def act_ref(x: torch.Tensor, act: str) -> torch.Tensor:
         return 0.5 * x * (1 + torch.erf(x * 0.7071067811865476))
     if act == "silu":
         return x * torch.sigmoid(x)
+    if act == "relu":
+        return torch.relu(x)
     return x
 
 

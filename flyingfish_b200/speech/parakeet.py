@@ -1,0 +1,352 @@
+"""Parakeet-style speech recognition: FastConformer encoder + token-and-duration transducer (TDT) decoder.
+
+Configuration and tensor contract follow the published ``ParakeetForTDT`` layout (src/parakeet.rs:295-577 of the
+reference); the greedy decode follows src/backend/cuda/engine_parakeet.rs:2550-2633. What differs is where the loop
+runs: the prediction-network state, the current frame, the last token and the trajectory live on the device, one decode
+step is a fixed sequence of launches replayed from a CUDA graph, and the host reads the state words once per
+``CHECK_EVERY`` steps instead of one selection per step."""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import torch
+
+from .. import ops
+from ..models.conformer import ConformerEncoder, ConformerSpec, random_tensors
+from ..ops import speech_ops, vision_ops
+from ..ops.speech_ops import (TS_ADVANCE, TS_CAP, TS_COUNT, TS_DONE, TS_ERROR, TS_FRAME, TS_MAXSYM, TS_TOKEN, TS_VALID,
+                              TS_WORDS)
+from .audio import LogMel, LogMelConfig
+from .transcript import Transcription, WORD_MARKER, tdt_cues
+
+BF16 = torch.bfloat16
+CHECK_EVERY = 32           # decode steps replayed between two reads of the device state
+
+
+@dataclass(frozen=True)
+class ParakeetSpec:
+    encoder: ConformerSpec = field(default_factory=ConformerSpec)
+    decoder_hidden: int = 640
+    decoder_layers: int = 2
+    vocab: int = 8193                  # tokens including the blank
+    blank: int = 8192
+    max_symbols: int = 10
+    eos: int = 3
+    pad: int = 2
+    durations: tuple[int, ...] = (0, 1, 2, 3, 4)
+    mel: LogMelConfig = field(default_factory=LogMelConfig)
+
+    @property
+    def joint_out(self) -> int:
+        return self.vocab + len(self.durations)
+
+    @property
+    def frame_seconds(self) -> float:
+        return 8 * self.mel.hop_length / self.mel.sampling_rate
+
+    def check(self) -> None:
+        self.encoder.check()
+        if not (0 <= self.blank < self.vocab and self.decoder_hidden % 8 == 0 and self.decoder_layers >= 1
+                and self.durations and self.max_symbols >= 1):
+            raise ValueError("unsupported transducer decoder geometry")
+
+    @classmethod
+    def from_json(cls, root: dict, processor: dict, generation: dict) -> "ParakeetSpec":
+        """``config.json``, ``processor_config.json`` and ``generation_config.json`` of a published checkpoint."""
+        if root.get("model_type") != "parakeet_tdt" or root.get("architectures") != ["ParakeetForTDT"]:
+            raise ValueError("not a Parakeet TDT configuration")
+        if root.get("hidden_act") != "relu":
+            raise ValueError("unsupported joint activation")
+        enc = root.get("encoder_config")
+        if not isinstance(enc, dict) or enc.get("model_type") != "parakeet_encoder":
+            raise ValueError("encoder_config missing")
+        for key, want in (("hidden_act", "silu"), ("scale_input", False), ("subsampling_conv_kernel_size", 3),
+                          ("subsampling_conv_stride", 2), ("subsampling_factor", 8)):
+            if enc.get(key) != want:
+                raise ValueError(f"unsupported encoder setting {key}={enc.get(key)!r}")
+        if enc.get("num_key_value_heads", enc["num_attention_heads"]) != enc["num_attention_heads"]:
+            raise ValueError("grouped-query encoders are not supported")
+        feats = processor.get("feature_extractor")
+        if not isinstance(feats, dict):
+            raise ValueError("feature_extractor missing")
+        if feats.get("padding_side", "right") != "right" or float(feats.get("padding_value", 0.0)) != 0.0:
+            raise ValueError("unsupported feature padding")
+        mel = LogMelConfig(sampling_rate=int(feats["sampling_rate"]), n_fft=int(feats["n_fft"]), win_length=int(feats["win_length"]),
+                           hop_length=int(feats["hop_length"]), mel_bins=int(feats["feature_size"]),
+                           preemphasis=float(feats["preemphasis"]))
+        if mel.mel_bins != int(enc["num_mel_bins"]):
+            raise ValueError("feature size and encoder mel bins differ")
+        encoder = ConformerSpec(layers=int(enc["num_hidden_layers"]), hidden=int(enc["hidden_size"]),
+                                heads=int(enc["num_attention_heads"]), intermediate=int(enc["intermediate_size"]),
+                                conv_kernel=int(enc["conv_kernel_size"]), mel_bins=mel.mel_bins,
+                                sub_channels=int(enc["subsampling_conv_channels"]), attention_bias=bool(enc["attention_bias"]),
+                                convolution_bias=bool(enc["convolution_bias"]), max_position=int(enc["max_position_embeddings"]))
+        spec = cls(encoder=encoder, decoder_hidden=int(root["decoder_hidden_size"]), decoder_layers=int(root["num_decoder_layers"]),
+                   vocab=int(root["vocab_size"]), blank=int(root["blank_token_id"]), max_symbols=int(root["max_symbols_per_step"]),
+                   eos=int(generation.get("eos_token_id", 3)), pad=int(root.get("pad_token_id", 2)),
+                   durations=tuple(int(d) for d in root["durations"]), mel=mel)
+        if generation.get("decoder_start_token_id", spec.blank) != spec.blank:
+            raise ValueError("decoder start token differs from the blank")
+        spec.check()
+        return spec
+
+    @classmethod
+    def read(cls, directory: str | Path) -> "ParakeetSpec":
+        d = Path(directory)
+        load = lambda n: json.loads((d / n).read_text())
+        return cls.from_json(load("config.json"), load("processor_config.json"), load("generation_config.json"))
+
+    def to_json(self) -> tuple[dict, dict, dict]:
+        """The three configuration files of this spec in the published layout."""
+        e = self.encoder
+        root = {"architectures": ["ParakeetForTDT"], "model_type": "parakeet_tdt", "dtype": "float32", "hidden_act": "relu",
+                "initializer_range": 0.02, "is_encoder_decoder": True, "pad_token_id": self.pad, "vocab_size": self.vocab,
+                "blank_token_id": self.blank, "durations": list(self.durations), "decoder_hidden_size": self.decoder_hidden,
+                "num_decoder_layers": self.decoder_layers, "max_symbols_per_step": self.max_symbols,
+                "encoder_config": {"model_type": "parakeet_encoder", "hidden_act": "silu", "scale_input": False,
+                                   "attention_bias": e.attention_bias, "convolution_bias": e.convolution_bias,
+                                   "conv_kernel_size": e.conv_kernel, "hidden_size": e.hidden, "intermediate_size": e.intermediate,
+                                   "max_position_embeddings": e.max_position, "num_attention_heads": e.heads,
+                                   "num_key_value_heads": e.heads, "num_hidden_layers": e.layers, "num_mel_bins": e.mel_bins,
+                                   "subsampling_conv_channels": e.sub_channels, "subsampling_conv_kernel_size": 3,
+                                   "subsampling_conv_stride": 2, "subsampling_factor": 8}}
+        m = self.mel
+        processor = {"processor_class": "ParakeetProcessor", "blank_token": "<blank>",
+                     "feature_extractor": {"feature_extractor_type": "ParakeetFeatureExtractor", "feature_size": m.mel_bins,
+                                           "hop_length": m.hop_length, "n_fft": m.n_fft, "padding_side": "right", "padding_value": 0.0,
+                                           "preemphasis": m.preemphasis, "return_attention_mask": True,
+                                           "sampling_rate": m.sampling_rate, "win_length": m.win_length}}
+        generation = {"decoder_start_token_id": self.blank, "eos_token_id": self.eos, "pad_token_id": self.pad}
+        return root, processor, generation
+
+    def expected_tensors(self) -> dict[str, tuple[str, tuple[int, ...]]]:
+        out = self.encoder.expected_tensors()
+        h, d = self.encoder.hidden, self.decoder_hidden
+        out["encoder_projector.weight"] = ("F32", (d, h))
+        out["encoder_projector.bias"] = ("F32", (d,))
+        out["decoder.embedding.weight"] = ("F32", (self.vocab, d))
+        out["decoder.decoder_projector.weight"] = ("F32", (d, d))
+        out["decoder.decoder_projector.bias"] = ("F32", (d,))
+        for layer in range(self.decoder_layers):
+            for kind in ("weight_ih", "weight_hh"):
+                out[f"decoder.lstm.{kind}_l{layer}"] = ("F32", (4 * d, d))
+            for kind in ("bias_ih", "bias_hh"):
+                out[f"decoder.lstm.{kind}_l{layer}"] = ("F32", (4 * d,))
+        out["joint.head.weight"] = ("F32", (self.joint_out, d))
+        out["joint.head.bias"] = ("F32", (self.joint_out,))
+        return out
+
+    def validate(self, names_shapes: dict[str, tuple[str, tuple[int, ...]]]) -> int:
+        """Checks a checkpoint's (dtype, shape) table against the contract; returns the tensor count."""
+        expected = self.expected_tensors()
+        for name in expected:
+            if name not in names_shapes:
+                raise ValueError(f"Parakeet tensor missing: {name}")
+        for name in names_shapes:
+            if name not in expected:
+                raise ValueError(f"Parakeet tensor unexpected: {name}")
+        for name, entry in expected.items():
+            if (names_shapes[name][0], tuple(names_shapes[name][1])) != entry:
+                raise ValueError(f"Parakeet tensor contract mismatch: {name}")
+        return len(expected)
+
+
+def parakeet_tiny() -> ParakeetSpec:
+    """A small random-init shape for tests: 2 layers, 128 hidden, two 64-wide heads, 32 mel bins."""
+    enc = ConformerSpec(layers=2, hidden=128, heads=2, intermediate=256, conv_kernel=9, mel_bins=32, sub_channels=32,
+                        max_position=512)
+    return ParakeetSpec(encoder=enc, decoder_hidden=64, decoder_layers=2, vocab=41, blank=40, max_symbols=10, eos=3,
+                        durations=(0, 1, 2, 3, 4), mel=LogMelConfig(mel_bins=32))
+
+
+SHAPES = {"parakeet-tdt-0.6b": ParakeetSpec, "parakeet-tiny": parakeet_tiny}
+
+
+@dataclass
+class TdtTrajectory:
+    tokens: list[int]
+    durations: list[int]
+    frames: list[int]
+    capacity: int
+    steps: int = 0
+    state_reads: int = 0
+
+
+class TdtDecoder:
+    """Prediction network (embedding + LSTM stack), joint network and the greedy TDT loop."""
+
+    def __init__(self, spec: ParakeetSpec, tensors: dict[str, torch.Tensor], device: torch.device | str, max_rows: int = 0):
+        self.spec, self.device = spec, torch.device(device)
+        dev, d = self.device, spec.decoder_hidden
+
+        def w16(t: torch.Tensor) -> torch.Tensor:
+            return t.float().to(BF16).contiguous().to(dev)
+
+        self.enc_proj = (w16(tensors["encoder_projector.weight"]), w16(tensors["encoder_projector.bias"]))
+        self.table = w16(tensors["decoder.embedding.weight"])
+        self.w_pred = w16(tensors["decoder.decoder_projector.weight"])
+        self.b_pred = tensors["decoder.decoder_projector.bias"].float().contiguous().to(dev)
+        self.lstm = []
+        for layer in range(spec.decoder_layers):
+            w = torch.cat([tensors[f"decoder.lstm.weight_ih_l{layer}"].float(), tensors[f"decoder.lstm.weight_hh_l{layer}"].float()], dim=1)
+            b = tensors[f"decoder.lstm.bias_ih_l{layer}"].float() + tensors[f"decoder.lstm.bias_hh_l{layer}"].float()
+            self.lstm.append((w16(w), b.contiguous().to(dev)))
+        n = spec.joint_out
+        n_pad = (n + 15) // 16 * 16
+        head = torch.zeros(n_pad, d)
+        head[:n] = tensors["joint.head.weight"].float()
+        self.w_head = w16(head)
+        self.b_head = tensors["joint.head.bias"].float().contiguous().to(dev)
+        self.durations = torch.tensor(spec.durations, dtype=torch.int32, device=dev)
+        # step buffers (fixed addresses: the step is captured once)
+        self.max_rows = max_rows or spec.encoder.max_position
+        self.enc = torch.zeros(self.max_rows, d, dtype=BF16, device=dev)
+        self.xh = [torch.zeros(2 * d, dtype=BF16, device=dev) for _ in range(spec.decoder_layers)]
+        self.cell = [torch.zeros(d, dtype=torch.float32, device=dev) for _ in range(spec.decoder_layers)]
+        self.top = torch.zeros(1, d, dtype=BF16, device=dev)
+        self.jh = torch.zeros(1, d, dtype=BF16, device=dev)
+        self.state = torch.zeros(TS_WORDS, dtype=torch.int32, device=dev)
+        cap = spec.max_symbols * self.max_rows + 1
+        self.traj = tuple(torch.zeros(cap, dtype=torch.int32, device=dev) for _ in range(3))
+        self._graph: torch.cuda.CUDAGraph | None = None
+        self.use_graph = self.device.type == "cuda"
+        self.graph_replays = 0
+
+    def project(self, encoded: torch.Tensor) -> torch.Tensor:
+        """[rows, hidden] BF16 encoder output -> [rows, decoder_hidden] BF16 in the joint space."""
+        return vision_ops.linear_bias_act(encoded, self.enc_proj[0], self.enc_proj[1], "none")
+
+    def reset(self, valid_rows: int) -> int:
+        spec = self.spec
+        for t in self.xh:
+            t.zero_()
+        for t in self.cell:
+            t.zero_()
+        capacity = min(spec.max_symbols * valid_rows + 1, self.traj[0].numel())
+        init = torch.zeros(TS_WORDS, dtype=torch.int32)
+        init[TS_TOKEN], init[TS_COUNT], init[TS_ADVANCE], init[TS_VALID], init[TS_CAP] = spec.blank, 1, 1, valid_rows, capacity
+        init[TS_MAXSYM] = spec.max_symbols
+        self.state.copy_(init)
+        first = torch.tensor([spec.blank, 0, 0], dtype=torch.int32)
+        for t, v in zip(self.traj, first):
+            t[:1] = v
+        return capacity
+
+    def step(self) -> None:
+        """One decode step on the current stream (the sequence a CUDA graph captures)."""
+        spec, d = self.spec, self.spec.decoder_hidden
+        speech_ops.tdt_embed(self.table, self.state, self.xh[0])
+        for layer, (w, b) in enumerate(self.lstm):
+            gates = ops.linear(self.xh[layer][None, :], w)
+            nxt = self.xh[layer + 1][:d] if layer + 1 < len(self.lstm) else self.top[0]
+            speech_ops.lstm_cell(gates[0], b, self.cell[layer], self.xh[layer][d:], nxt, self.state)
+        pred = ops.linear(self.top, self.w_pred)
+        speech_ops.tdt_joint_in(self.enc, pred, self.b_pred, self.state, self.jh)
+        logits = ops.linear(self.jh, self.w_head)
+        speech_ops.tdt_select(logits, self.b_head, self.durations, self.state, self.traj, spec.vocab, spec.blank, spec.eos)
+
+    def _capture(self) -> None:
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        saved = self.state.clone()
+        with torch.cuda.stream(side):
+            self.step()                                  # warm-up: workspaces and kernel attributes exist before capture
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+        self._graph = g
+        self.state.copy_(saved)
+
+    def decode(self, projected: torch.Tensor, valid_rows: int) -> TdtTrajectory:
+        """Greedy decode of one utterance from its projected encoder rows [rows, decoder_hidden]."""
+        rows = projected.shape[0]
+        if not (0 < valid_rows <= rows <= self.max_rows):
+            raise ValueError("decode valid encoder rows outside the projected extent")
+        self.enc[:rows].copy_(projected)
+        if self.use_graph and self._graph is None:
+            self.reset(valid_rows)
+            self._capture()
+        capacity = self.reset(valid_rows)
+        steps = reads = 0
+        while True:
+            if self.use_graph:
+                for _ in range(CHECK_EVERY):
+                    self._graph.replay()
+                self.graph_replays += CHECK_EVERY
+                steps += CHECK_EVERY
+            else:
+                self.step()
+                steps += 1
+            st = self.state.tolist()
+            reads += 1
+            if st[TS_ERROR]:
+                raise RuntimeError(f"decode capacity exceeded: capacity={capacity} frame={st[TS_FRAME]}")
+            if st[TS_DONE]:
+                break
+            if steps > capacity + CHECK_EVERY:
+                raise RuntimeError("decode did not finish within its capacity")
+        n = st[TS_COUNT]
+        tok, dur, frm = (t[:n].tolist() for t in self.traj)
+        return TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=capacity, steps=steps, state_reads=reads)
+
+
+class ParakeetModel:
+    """Log-mel front end + encoder + TDT decoder of one checkpoint (or of seeded random weights)."""
+
+    def __init__(self, spec: ParakeetSpec, tensors: dict[str, torch.Tensor], device: torch.device | str = "cpu",
+                 tokenizer=None, max_rows: int = 0):
+        spec.check()
+        self.spec, self.device, self.tokenizer = spec, torch.device(device), tokenizer
+        self.mel = LogMel(spec.mel, self.device)
+        self.encoder = ConformerEncoder(spec.encoder, tensors, self.device)
+        self.decoder = TdtDecoder(spec, tensors, self.device, max_rows)
+
+    @classmethod
+    def random(cls, spec: ParakeetSpec, device: torch.device | str = "cpu", seed: int = 0, **kw) -> "ParakeetModel":
+        return cls(spec, random_tensors(spec.expected_tensors(), seed), device, **kw)
+
+    @classmethod
+    def load(cls, directory: str | Path, device: torch.device | str = "cpu", **kw) -> "ParakeetModel":
+        from ..loaders.safetensors_io import MappedCheckpoint
+        from ..loaders.tokenizer import load_tokenizer
+        spec = ParakeetSpec.read(directory)
+        ckpt = MappedCheckpoint(directory)
+        table = {n: (ckpt.info(n).dtype, tuple(ckpt.info(n).shape)) for n in ckpt.names()}
+        spec.validate(table)
+        tensors = {n: ckpt.tensor(n) for n in ckpt.names()}
+        return cls(spec, tensors, device, tokenizer=load_tokenizer(directory), **kw)
+
+    def encode(self, waveforms: list[torch.Tensor]) -> tuple[torch.Tensor, list[int]]:
+        feat, valid = self.mel.extract(waveforms, normalize=True)
+        return self.encoder.encode(feat, valid.tolist())
+
+    def decode(self, waveforms: list[torch.Tensor]) -> list[TdtTrajectory]:
+        encoded, rows = self.encode(waveforms)
+        out = []
+        for b, n in enumerate(rows):
+            proj = self.decoder.project(encoded[b])
+            out.append(self.decoder.decode(proj, n))
+        return out
+
+    def transcription(self, traj: TdtTrajectory) -> Transcription:
+        tk = self.tokenizer
+        if tk is None:
+            raise RuntimeError("no tokenizer: the model directory holds no tokenizer.json")
+        pieces = {}
+        inner = getattr(tk, "tk", None)
+        if inner is not None:
+            pieces = {i: p for p, i in inner.get_vocab(False).items()}
+        return tdt_cues(traj.tokens, traj.durations, self.spec.blank, lambda ids: tk.decode(list(ids)),
+                        lambda t: pieces.get(t, "").startswith(WORD_MARKER), self.spec.frame_seconds, self.spec.pad)
+
+    def transcribe(self, waveforms: list[torch.Tensor]) -> list[Transcription]:
+        return [self.transcription(t) for t in self.decode(waveforms)]
+
+
+def transcribe(directory: str | Path, waveform: torch.Tensor, device: torch.device | str = "cpu") -> Transcription:
+    """Loads the checkpoint in ``directory`` and transcribes one 16 kHz mono waveform."""
+    return ParakeetModel.load(directory, device).transcribe([waveform])[0]

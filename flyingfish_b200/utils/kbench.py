@@ -247,10 +247,60 @@ def bench_gdn(args) -> dict:
             "chunked_us_per_chunk": chk["us_median"] / max(n // 64, 1)}
 
 
+def bench_speech(args) -> dict:
+    """Speech recognition at the published Parakeet-TDT geometry (random weights): log-mel, encoder and greedy
+    transducer decode of ``--batch`` utterances of ``--seconds`` each, and the relative-position attention kernel of one
+    layer alone with a library soft-max attention of the same shape (no position term) beside it."""
+    from ..ops import speech_ops
+    from ..speech import ParakeetModel, ParakeetSpec
+    dev = torch.device("cuda")
+    spec = ParakeetSpec()
+    model = ParakeetModel.random(spec, dev, seed=0)
+    g = torch.Generator().manual_seed(0)
+    waves = [0.1 * torch.randn(int(args.seconds * 16000), generator=g) for _ in range(args.batch)]
+    audio_s = args.seconds * args.batch
+
+    def front():
+        return model.mel.extract(waves)
+
+    feat, valid = front()
+    vl = valid.tolist()
+    mel = time_op(front, args.iters, args.warmup, None)
+    enc = time_op(lambda: model.encoder.encode(feat, vl), args.iters, args.warmup, None)
+    encoded, rows = model.encoder.encode(feat, vl)
+    proj = model.decoder.project(encoded[0])
+    model.decoder.decode(proj, rows[0])
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    traj = model.decoder.decode(proj, rows[0])
+    e1.record()
+    torch.cuda.synchronize()
+    dec_ms = e0.elapsed_time(e1)
+    t, h, d = encoded.shape[1], spec.encoder.heads, spec.encoder.head_dim
+    qkv = torch.randn(args.batch * t, 3 * h * d, device=dev).to(torch.bfloat16)
+    pos = torch.randn(2 * t - 1, h * d, device=dev).to(torch.bfloat16)
+    u, v = torch.randn(h, d, device=dev), torch.randn(h, d, device=dev)
+    lens = torch.tensor(rows, dtype=torch.int32, device=dev)
+    hd = h * d
+    att = time_op(lambda: speech_ops.relpos_attention(qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], pos, u, v, lens,
+                                                      args.batch, h), args.iters, args.warmup, None)
+    q4 = qkv.reshape(args.batch, t, 3, h, d).permute(2, 0, 3, 1, 4).contiguous()
+    lib = time_op(lambda: torch.nn.functional.scaled_dot_product_attention(q4[0], q4[1], q4[2]), args.iters, args.warmup, None)
+    flops = 3 * 2.0 * args.batch * h * t * t * d                  # content, position and PV products
+    total_ms = (mel["us_median"] + enc["us_median"]) / 1e3 + dec_ms * args.batch
+    return {"op": "speech", "batch": args.batch, "seconds": args.seconds, "encoder_rows": t,
+            "logmel_us": mel["us_median"], "encoder_ms": enc["us_median"] / 1e3, "decode_ms_per_utterance": dec_ms,
+            "decode_steps": traj.steps, "decode_state_reads": traj.state_reads, "decode_us_per_step": dec_ms * 1e3 / max(traj.steps, 1),
+            "audio_seconds_per_second_encoder": audio_s / (enc["us_median"] / 1e6),
+            "audio_seconds_per_second_total": audio_s / (total_ms / 1e3),
+            "relpos_attention_us": att["us_median"], "relpos_attention_tflops": flops / att["us_median"] / 1e6,
+            "library_sdpa_no_position_term_us": lib["us_median"]}
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="kbench")
     sub = ap.add_subparsers(dest="op", required=True)
-    for name in ("gemm", "attn_decode", "attn_prefill", "attn_mixed", "gdn", "moe"):
+    for name in ("gemm", "attn_decode", "attn_prefill", "attn_mixed", "gdn", "moe", "speech"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
@@ -262,6 +312,9 @@ def main(argv=None) -> None:
             p.add_argument("--torch", action="store_true", help="time torch.matmul (cuBLAS) instead, as the baseline")
             p.add_argument("--fp8", action="store_true", help="FP8-resident weight (E4M3, 128x128 scales), W8A8 kernel")
             p.add_argument("--graph", action="store_true", help="replay the operator from a CUDA graph (no host gaps)")
+        elif name == "speech":
+            p.add_argument("--batch", type=int, default=8)
+            p.add_argument("--seconds", type=float, default=30.0)
         elif name == "moe":
             p.add_argument("--rows", type=int, default=128)
             p.add_argument("--experts", type=int, default=128)
@@ -280,7 +333,7 @@ def main(argv=None) -> None:
                 p.add_argument("--recent", type=int, default=2048)
     args = ap.parse_args(argv)
     fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "attn_mixed": bench_attn_mixed, "gdn": bench_gdn,
-          "moe": bench_moe}[args.op]
+          "moe": bench_moe, "speech": bench_speech}[args.op]
     print(json.dumps(fn(args)))
     ops.check_status()
 
