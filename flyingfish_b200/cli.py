@@ -450,17 +450,17 @@ def cmd_embed(args) -> dict:
 
 def cmd_transcribe(args) -> None:
     """Speech recognition of one audio file (src/main.rs:861-990 of the reference: same formats, output file guard)."""
-    from .speech import ParakeetModel, load_audio
+    from .speech import load_audio, load_model
     if not args.model:
         raise SystemExit("transcribe needs --model")
     arch = json.loads((Path(args.model) / "config.json").read_text()).get("architectures", [None])[0]
-    if arch != "ParakeetForTDT":
+    if arch not in ("ParakeetForTDT", "ParakeetForCTC"):
         raise SystemExit(f"unsupported transcription architecture {arch}")
     if args.stream:
-        raise SystemExit("streaming transcription is not available for ParakeetForTDT")
+        raise SystemExit(f"streaming transcription is not available for {arch}")
     out_path = check_output_path(args.output, args.model) if args.output else None
     device = "cpu" if args.cpu else f"cuda:{args.device}"
-    model = ParakeetModel.load(args.model, device)
+    model = load_model(args.model, device)
     wave = load_audio(args.input, model.spec.mel.sampling_rate)
     result = model.transcribe([wave])[0]
     text = {"txt": result.text + "\n", "json": result.to_json() + "\n", "srt": result.to_srt(), "vtt": result.to_vtt()}[args.format]

@@ -626,9 +626,10 @@ tdt_select_kernel(const __nv_bfloat16* __restrict__ logits, const float* __restr
     if (x > dbest) { dbest = x; di = i; }
   }
   const int count = state[TS_COUNT], frame = state[TS_FRAME];
+  // n_dur == 0: a plain transducer (no duration head): tokens stay on the frame, blanks move one frame
   const int valid_rows = state[TS_VALID], capacity = min(state[TS_CAP], traj_len);
   if (count >= capacity) { state[TS_ERROR] = 1; state[TS_DONE] = 1; return; }
-  int dur = durations[di];
+  int dur = n_dur > 0 ? durations[di] : 0;
   if (bi == blank && dur == 0) dur = 1;
   int syms = state[TS_SYMS];
   if (bi != blank && dur == 0 && ++syms >= state[TS_MAXSYM]) dur = 1;
@@ -760,7 +761,7 @@ FF_EXPORT int ff_tdt_joint_in(const void* enc, const void* pred, const float* bi
 FF_EXPORT int ff_tdt_select(const void* logits, const float* out_bias, const int* durations, int* state, int* traj_tokens,
                             int* traj_durations, int* traj_frames, int n_tok, int n_dur, int blank, int eos,
                             int traj_len, cudaStream_t s) {
-  if (n_tok <= 0 || n_dur <= 0 || traj_len <= 0) return FF_HOST_BAD_SHAPE;
+  if (n_tok <= 0 || n_dur < 0 || traj_len <= 0) return FF_HOST_BAD_SHAPE;
   if (int lr = launch_pdl(tdt_select_kernel, dim3(1), dim3(256), 0, s, 0, (const __nv_bfloat16*)logits, out_bias,
                           durations, state, traj_tokens, traj_durations, traj_frames, n_tok, n_dur, blank, eos, traj_len))
     return lr;

@@ -347,7 +347,8 @@ def tdt_select(logits: torch.Tensor, out_bias: torch.Tensor | None, durations: t
     ``TS_MAXSYM``-th consecutive token that would stay on its frame; the
     (token, duration, frame) entry is appended to ``traj`` and the state moves to the next frame, or ``done`` is set on
     the end-of-sequence token or when the frames (state word ``TS_VALID``) are used up. A trajectory longer than
-    ``TS_CAP`` entries sets the error word."""
+    ``TS_CAP`` entries sets the error word. An empty ``durations`` selects the plain transducer rule: a token stays
+    on its frame, a blank moves one frame."""
     n_dur = durations.numel()
     traj_len = traj[0].numel()
     if not logits.is_cuda:
@@ -357,7 +358,7 @@ def tdt_select(logits: torch.Tensor, out_bias: torch.Tensor | None, durations: t
         if out_bias is not None:
             x = x + out_bias.float()[: n_tok + n_dur]
         tok = int(torch.argmax(x[:n_tok]))
-        dur = int(durations[int(torch.argmax(x[n_tok:n_tok + n_dur]))])
+        dur = int(durations[int(torch.argmax(x[n_tok:n_tok + n_dur]))]) if n_dur > 0 else 0
         count, frame = int(state[TS_COUNT]), int(state[TS_FRAME])
         valid_rows, capacity = int(state[TS_VALID]), min(int(state[TS_CAP]), traj_len)
         if count >= capacity:
@@ -384,3 +385,19 @@ def tdt_select(logits: torch.Tensor, out_bias: torch.Tensor | None, durations: t
                                  ptr(traj[2]), n_tok, n_dur, blank, eos, traj_len, stream_ptr())
     check(rc, "ff_tdt_select")
     _count()
+
+
+def ctc_collapse(ids: torch.Tensor, valid: int, blank: int) -> tuple[list[int], list[int], list[int]]:
+    """Greedy CTC path -> (tokens, first frame, frames held): repeats merge, blanks drop. ``ids``: [frames] arg-max ids."""
+    path = ids[:valid].tolist()
+    tokens, starts, runs = [], [], []
+    prev = None
+    for f, t in enumerate(path):
+        if t != prev and t != blank:
+            tokens.append(t)
+            starts.append(f)
+            runs.append(1)
+        elif t == prev and t != blank:
+            runs[-1] += 1
+        prev = t
+    return tokens, starts, runs

@@ -35,7 +35,7 @@ class ParakeetSpec:
     max_symbols: int = 10
     eos: int = 3
     pad: int = 2
-    durations: tuple[int, ...] = (0, 1, 2, 3, 4)
+    durations: tuple[int, ...] = (0, 1, 2, 3, 4)       # empty: a plain transducer (RNN-T) without a duration head
     mel: LogMelConfig = field(default_factory=LogMelConfig)
 
     @property
@@ -49,7 +49,7 @@ class ParakeetSpec:
     def check(self) -> None:
         self.encoder.check()
         if not (0 <= self.blank < self.vocab and self.decoder_hidden % 8 == 0 and self.decoder_layers >= 1
-                and self.durations and self.max_symbols >= 1):
+                and self.max_symbols >= 1):
             raise ValueError("unsupported transducer decoder geometry")
 
     @classmethod
@@ -199,7 +199,7 @@ class TdtDecoder:
         head[:n] = tensors["joint.head.weight"].float()
         self.w_head = w16(head)
         self.b_head = tensors["joint.head.bias"].float().contiguous().to(dev)
-        self.durations = torch.tensor(spec.durations, dtype=torch.int32, device=dev)
+        self.durations = torch.tensor(spec.durations or (0,), dtype=torch.int32, device=dev)[: len(spec.durations)]
         # step buffers (fixed addresses: the step is captured once)
         self.max_rows = max_rows or spec.encoder.max_position
         self.enc = torch.zeros(self.max_rows, d, dtype=BF16, device=dev)
@@ -347,6 +347,111 @@ class ParakeetModel:
         return [self.transcription(t) for t in self.decode(waveforms)]
 
 
+@dataclass(frozen=True)
+class ParakeetCtcSpec:
+    """FastConformer encoder with a CTC head (``ParakeetForCTC``: ``ctc_head`` is a kernel-1 convolution)."""
+    encoder: ConformerSpec = field(default_factory=ConformerSpec)
+    vocab: int = 1025                  # tokens including the blank
+    blank: int = 1024
+    pad: int = 2
+    mel: LogMelConfig = field(default_factory=lambda: LogMelConfig(mel_bins=80))
+
+    @property
+    def frame_seconds(self) -> float:
+        return 8 * self.mel.hop_length / self.mel.sampling_rate
+
+    def expected_tensors(self) -> dict[str, tuple[str, tuple[int, ...]]]:
+        out = self.encoder.expected_tensors()
+        out["ctc_head.weight"] = ("F32", (self.vocab, self.encoder.hidden, 1))
+        out["ctc_head.bias"] = ("F32", (self.vocab,))
+        return out
+
+    @classmethod
+    def read(cls, directory: str | Path) -> "ParakeetCtcSpec":
+        d = Path(directory)
+        root = json.loads((d / "config.json").read_text())
+        if root.get("architectures") != ["ParakeetForCTC"]:
+            raise ValueError("not a Parakeet CTC configuration")
+        proc = json.loads((d / "processor_config.json").read_text())
+        tdt_like = dict(root, architectures=["ParakeetForTDT"], model_type="parakeet_tdt", hidden_act="relu", durations=[0],
+                        decoder_hidden_size=8, num_decoder_layers=1, max_symbols_per_step=1,
+                        blank_token_id=root.get("blank_token_id", root.get("pad_token_id", root["vocab_size"] - 1)))
+        base = ParakeetSpec.from_json(tdt_like, proc, {})
+        return cls(encoder=base.encoder, vocab=base.vocab, blank=base.blank, pad=base.pad, mel=base.mel)
+
+
+class ParakeetCtcModel:
+    """Log-mel front end + encoder + CTC head; greedy decoding merges repeats and drops blanks."""
+
+    def __init__(self, spec: ParakeetCtcSpec, tensors: dict[str, torch.Tensor], device: torch.device | str = "cpu", tokenizer=None):
+        spec.encoder.check()
+        self.spec, self.device, self.tokenizer = spec, torch.device(device), tokenizer
+        self.mel = LogMel(spec.mel, self.device)
+        self.encoder = ConformerEncoder(spec.encoder, tensors, self.device)
+        n_pad = (spec.vocab + 15) // 16 * 16
+        head = torch.zeros(n_pad, spec.encoder.hidden)
+        head[: spec.vocab] = tensors["ctc_head.weight"].float().reshape(spec.vocab, spec.encoder.hidden)
+        bias = torch.full((n_pad,), -1.0e4)
+        bias[: spec.vocab] = tensors["ctc_head.bias"].float()
+        self.head = (head.to(BF16).contiguous().to(self.device), bias.to(BF16).contiguous().to(self.device))
+
+    @classmethod
+    def random(cls, spec: ParakeetCtcSpec, device: torch.device | str = "cpu", seed: int = 0, **kw) -> "ParakeetCtcModel":
+        return cls(spec, random_tensors(spec.expected_tensors(), seed), device, **kw)
+
+    @classmethod
+    def load(cls, directory: str | Path, device: torch.device | str = "cpu") -> "ParakeetCtcModel":
+        from ..loaders.safetensors_io import MappedCheckpoint
+        from ..loaders.tokenizer import load_tokenizer
+        spec = ParakeetCtcSpec.read(directory)
+        ckpt = MappedCheckpoint(directory)
+        expected = spec.expected_tensors()
+        for n in expected:
+            if not ckpt.has(n):
+                raise ValueError(f"Parakeet tensor missing: {n}")
+        return cls(spec, {n: ckpt.tensor(n) for n in expected}, device, tokenizer=load_tokenizer(directory))
+
+    def decode(self, waveforms: list[torch.Tensor]) -> list[tuple[list[int], list[int], list[int]]]:
+        """Per utterance: (tokens, first frame of each token, frames each token was held)."""
+        feat, valid = self.mel.extract(waveforms, normalize=True)
+        encoded, rows = self.encoder.encode(feat, valid.tolist())
+        b, t, h = encoded.shape
+        logits = vision_ops.linear_bias_act(encoded.reshape(b * t, h), self.head[0], self.head[1], "none")
+        ids = ops.argmax_rows(logits).reshape(b, t).cpu()
+        return [speech_ops.ctc_collapse(ids[i], rows[i], self.spec.blank) for i in range(b)]
+
+    def transcribe(self, waveforms: list[torch.Tensor]) -> list[Transcription]:
+        tk = self.tokenizer
+        if tk is None:
+            raise RuntimeError("no tokenizer: the model directory holds no tokenizer.json")
+        inner = getattr(tk, "tk", None)
+        pieces = {i: p for p, i in inner.get_vocab(False).items()} if inner is not None else {}
+        out = []
+        for tokens, starts, runs in self.decode(waveforms):
+            # the same cue rules as the transducer: blanks carry the gaps between emissions
+            traj_t, traj_d, frame = [], [], 0
+            for tok, f, r in zip(tokens, starts, runs):
+                if f > frame:
+                    traj_t.append(self.spec.blank)
+                    traj_d.append(f - frame)
+                traj_t.append(tok)
+                traj_d.append(r)
+                frame = f + r
+            out.append(tdt_cues(traj_t, traj_d, self.spec.blank, lambda ids: tk.decode([i for i in ids if i != self.spec.blank]),
+                                lambda t: pieces.get(t, "").startswith(WORD_MARKER), self.spec.frame_seconds, self.spec.pad))
+        return out
+
+
+def load_model(directory: str | Path, device: torch.device | str = "cpu"):
+    """The recognition model a checkpoint directory names in ``config.json``."""
+    arch = json.loads((Path(directory) / "config.json").read_text()).get("architectures", [None])[0]
+    if arch == "ParakeetForTDT":
+        return ParakeetModel.load(directory, device)
+    if arch == "ParakeetForCTC":
+        return ParakeetCtcModel.load(directory, device)
+    raise ValueError(f"unsupported transcription architecture {arch}")
+
+
 def transcribe(directory: str | Path, waveform: torch.Tensor, device: torch.device | str = "cpu") -> Transcription:
     """Loads the checkpoint in ``directory`` and transcribes one 16 kHz mono waveform."""
-    return ParakeetModel.load(directory, device).transcribe([waveform])[0]
+    return load_model(directory, device).transcribe([waveform])[0]

@@ -263,7 +263,8 @@ def _run_script(script, valid_rows, capacity, n_tok=6, blank=5, eos=3, durations
         advanced.append(int(state[TS_ADVANCE]))
         logits = torch.zeros(n_tok + len(durations))
         logits[tok] = 5.0
-        logits[n_tok + di] = 5.0
+        if durations:
+            logits[n_tok + di] = 5.0
         speech_ops.tdt_select(logits.to(torch.bfloat16), None, dur, state, traj, n_tok, blank, eos)
     n = int(state[TS_COUNT])
     return state, [t[:n].tolist() for t in traj], advanced
@@ -460,3 +461,37 @@ def test_transcribe_command(tmp_path, capsys):
     (d / "config.json").write_text(json.dumps(cfg))
     with pytest.raises(SystemExit, match="unsupported transcription architecture"):
         cli.main(["--cpu", "--model", str(d), "transcribe", str(tmp_path / "in.wav")])
+
+
+def test_plain_transducer_and_ctc_variants(tmp_path):
+    from dataclasses import replace
+    from flyingfish_b200.speech import ParakeetCtcModel, ParakeetCtcSpec, load_model
+    # RNN-T rule (no duration head): a token stays on its frame, a blank moves one frame
+    state, (tok, dur, frm), _ = _run_script([(1, 0), (5, 0), (2, 0), (2, 0), (5, 0)], valid_rows=3, capacity=60, durations=())
+    assert tok == [5, 1, 5, 2, 2, 5] and dur == [0, 0, 1, 0, 0, 1] and frm == [0, 0, 0, 1, 1, 1]
+    spec = replace(parakeet_tiny(), durations=())
+    assert spec.joint_out == spec.vocab
+    g = torch.Generator().manual_seed(21)
+    wave = 0.1 * torch.randn(12000, generator=g)
+    tr = ParakeetModel.random(spec, seed=5).decode([wave])[0]
+    assert all(d in (0, 1) for d in tr.durations) and tr.frames[-1] < spec.encoder.sub_len(75)
+    # CTC: repeats merge, blanks drop, first frames and run lengths are kept
+    ids = torch.tensor([4, 4, 9, 9, 9, 1, 1, 9, 2, 2, 4, 9])
+    assert speech_ops.ctc_collapse(ids, 11, 9) == ([4, 1, 2, 4], [0, 5, 8, 10], [2, 2, 2, 1])
+    cspec = ParakeetCtcSpec(encoder=parakeet_tiny().encoder, vocab=41, blank=40, mel=LogMelConfig(mel_bins=32))
+    model = ParakeetCtcModel.random(cspec, seed=6)
+    tokens, starts, runs = model.decode([wave])[0]
+    assert len(tokens) == len(starts) == len(runs) and all(0 <= t < 40 for t in tokens)
+    assert all(b >= a + r for a, r, b in zip(starts, runs, starts[1:]))
+    # through files and the architecture switch
+    d = tmp_path / "ctc"
+    _write_model_dir(d, parakeet_tiny(), 6)
+    cfg = json.loads((d / "config.json").read_text())
+    cfg["architectures"] = ["ParakeetForCTC"]
+    (d / "config.json").write_text(json.dumps(cfg))
+    (d / "model.safetensors").unlink()
+    save_safetensors(d / "model.safetensors", random_tensors(cspec.expected_tensors(), 6))
+    loaded = load_model(d)
+    assert isinstance(loaded, ParakeetCtcModel) and loaded.decode([wave])[0] == (tokens, starts, runs)
+    res = loaded.transcribe([wave])[0]
+    assert isinstance(res.text, str) and all(w.end >= w.start for w in res.words)
