@@ -57,15 +57,20 @@ class EPComm:
         # Real routers are skewed, so the receive buffers are sized for the worst case -- every rank sends all of its
         # assignments to this owner -- whenever that fits the byte budget (FF_EP_ARENA_MAX_GIB, default 4 GiB for the
         # two row buffers; decode batches and the benchmark prefill chunks do). Only beyond it the budget falls back
-        # to a multiple of the balanced share (at least 2x), and an overflow is reported through the status word.
+        # to a multiple of the balanced share (FF_EP_CAPACITY_FACTOR, default 2x); a layer call is then run in several
+        # passes over slices of the local rows, each small enough that even its worst case fits (``rows_fit``), so a
+        # skewed router costs extra passes instead of an overflow.
         import os
         budget = float(os.environ.get("FF_EP_ARENA_MAX_GIB", "4")) * (1 << 30)
+        factor = float(os.environ.get("FF_EP_CAPACITY_FACTOR", "2"))
         balanced = max_rows * top_k
         worst = self.size * balanced
         fit = int(budget // (2 * self.hidden * 2))
-        cap = max(256, min(worst, max(2 * balanced, fit)) + 16 * self.El)
+        cap = max(256, min(worst, max(int(factor * balanced), fit)) + 16 * self.El)
         cap = (cap + 15) // 16 * 16
         self.capacity_is_worst_case = cap >= worst + 16 * self.El
+        self.rows_fit = max(1, (cap - 16 * self.El) // (self.size * top_k))
+        self.passes = 1 if self.capacity_is_worst_case else -(-max_rows // self.rows_fit)
         offs = [c_longlong(0) for _ in range(4)]
         total = lib.ff_ep_arena_layout(self.size, self.E, self.hidden, cap, *[ctypes.byref(o) for o in offs])
         self.buf = symm.empty(int(total), dtype=torch.uint8, device=self.device)
@@ -91,7 +96,21 @@ class EPComm:
         """Routed-expert output for the local rows ``x`` (shared expert not included). ``layer``: the model's layer
         number, needed when this rank serves its experts from tiers."""
         if self.arena is not None and x.is_cuda:
-            return self._fused(x, weights, ids, lw, mode, layer)
+            if self.passes == 1:
+                return self._fused(x, weights, ids, lw, mode, layer)
+            # every rank runs the same number of passes (the phases are collective); a rank whose rows are used up
+            # sends one zero-weight row so that its kernels still take part
+            if x.shape[0] > self.passes * self.rows_fit:
+                raise ValueError(f"expert-parallel call of {x.shape[0]} rows exceeds max_rows={self.max_rows}")
+            out = torch.empty_like(x)
+            for p in range(self.passes):
+                lo, hi = p * self.rows_fit, min((p + 1) * self.rows_fit, x.shape[0])
+                if hi > lo:
+                    out[lo:hi] = self._fused(x[lo:hi], weights[lo:hi], ids[lo:hi], lw, mode, layer)
+                else:
+                    self._fused(torch.zeros_like(x[:1]), torch.zeros_like(weights[:1]), torch.zeros_like(ids[:1]), lw, mode, layer)
+            self.stats["multi_pass_calls"] = self.stats.get("multi_pass_calls", 0) + 1
+            return out
         if self.provider is not None:
             raise RuntimeError("tiered experts under expert parallelism need the CUDA peer-memory path")
         return self._baseline(x, weights, ids, lw, mode)

@@ -120,6 +120,36 @@ def main():
             torch.cuda.synchronize()
             ops.check_status(device)
         result.update(per_rank=gathered, stats=ep.stats)
+    elif args.mode == "ep_skew":
+        # receive buffers sized for the balanced share only, every row routed to rank 0's experts: the layer call runs
+        # in passes over row slices instead of overflowing
+        from types import SimpleNamespace
+        from flyingfish_b200.ops import ref
+        from flyingfish_b200.parallel.ep import EPComm
+        os.environ["FF_EP_ARENA_MAX_GIB"] = "0.00001"
+        os.environ["FF_EP_CAPACITY_FACTOR"] = "1"
+        E, hidden, inter, top_k, rows = 8, 256, 128, 2, 384
+        ep = EPComm(dist.group.WORLD, device, E, hidden, max_rows=rows, top_k=top_k)
+        g = torch.Generator().manual_seed(5)
+        w_gu = (0.05 * torch.randn(E, 2 * inter, hidden, generator=g)).to(torch.bfloat16)
+        w_dn = (0.05 * torch.randn(E, hidden, inter, generator=g)).to(torch.bfloat16)
+        gr = torch.Generator().manual_seed(50 + rank)
+        n = rows if rank == 0 else rows - 130                      # ranks hold different row counts
+        x = torch.randn(n, hidden, generator=gr).to(torch.bfloat16)
+        ids = torch.stack([torch.randint(0, 2, (n,), generator=gr), torch.randint(2, 4, (n,), generator=gr)], dim=1).to(torch.int32)
+        wts = torch.rand(n, top_k, generator=gr)
+        el = E // world
+        lw = SimpleNamespace(experts_gu=w_gu[rank * el:(rank + 1) * el].contiguous().to(device),
+                             experts_down=w_dn[rank * el:(rank + 1) * el].contiguous().to(device))
+        out = ep.dispatch_ffn_combine(x.to(device), wts.to(device), ids.to(device), lw, 0)
+        torch.cuda.synchronize()
+        ops.check_status(device)
+        want = ref.moe_forward(x, wts, ids, w_gu, w_dn, mode=0)
+        err = (out.float().cpu() - want.float()).abs().max().item()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, {"err": err, "scale": want.float().abs().max().item(), "passes": ep.passes,
+                                          "worst_case": ep.capacity_is_worst_case, "stats": dict(ep.stats)})
+        result.update(per_rank=gathered)
     elif args.mode == "ep_tier":
         # expert parallelism with every rank serving its own experts from tiers: half of them in GPU slots, the rest
         # through the host FFN
