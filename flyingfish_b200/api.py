@@ -79,6 +79,9 @@ class Model:
                 from .models.weights import DTYPES, synthetic_source
                 weights = build_v41_weights(spec, seed, device, synthetic_source(spec, seed, device, DTYPES[spec.dtype]),
                                             tp, epi)
+            elif spec.extra.get("hrm"):
+                from .models.hrm import random_hrm_weights
+                weights = random_hrm_weights(spec, seed, device)
             elif spec.mla is not None:
                 from .models.deepseek import build_deepseek_weights
                 from .models.weights import DTYPES, synthetic_source
@@ -98,6 +101,9 @@ class Model:
             from .models.deepseek_v41 import DeepseekV41Model
             net = DeepseekV41Model(weights, comm=comm, max_sequences=settings.max_batch, max_len=settings.capacity,
                                    max_chunk=min(settings.chunk or 256, 256), seed=seed)
+        elif spec.extra.get("hrm"):
+            from .models.hrm import HrmModel
+            net = HrmModel(weights, comm=comm)
         elif spec.extra.get("flint"):
             from .models.flint import FlintModel
             net = FlintModel(weights, comm=comm, seed=seed)

@@ -45,7 +45,7 @@ class MlaSpec:
 @dataclass
 class ModelSpec:
     name: str
-    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | deepseek_v41 | glm5_next | flint | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
+    arch: str                         # llama | qwen3 | qwen3_moe | deepseek_v3 | deepseek_v41 | glm5_next | flint | loop_vl | tiny_moe | qwen3_vl | embedding | diffusion_lm | qwen35_text | gemma
     layers: int
     hidden: int
     heads: int
@@ -251,6 +251,28 @@ def flint_tiny() -> ModelSpec:
         extra={"flint": {"window": 33, "no_rope_layers": [0, 1, 4]}})
 
 
+def _loop_spec(name: str, hidden: int, heads: int, ffn: int, vocab: int, per_stack: int, h_cycles: int, l_cycles: int,
+               original_max: int) -> ModelSpec:
+    return ModelSpec(
+        name=name, arch="loop_vl", layers=h_cycles * (l_cycles + 1) * per_stack, hidden=hidden, heads=heads, kv_heads=heads,
+        head_dim=128, ffn=ffn, vocab=vocab, rope_theta=1e4, rms_eps=1e-6,
+        extra={"hrm": {"layers_per_stack": per_stack, "h_cycles": h_cycles, "l_cycles": l_cycles,
+                       "embedding_scale": float(hidden) ** 0.5,
+                       "yarn": {"factor": 2.0, "original_max": original_max, "beta_fast": 32.0, "beta_slow": 1.0}}})
+
+
+def loop_tiny() -> ModelSpec:
+    """Small looped two-stack decoder: two weight stacks of 2 layers, 2 H cycles of 3 L calls + 1 H call = 16 cache
+    layers, gated full attention, YaRN positions."""
+    return _loop_spec("loop-tiny", 256, 2, 512, 2048, per_stack=2, h_cycles=2, l_cycles=3, original_max=64)
+
+
+def loopvl_text() -> ModelSpec:
+    """The published LoopVL text geometry: 1536 hidden, 12 heads, two stacks of 16 layers applied 2 x (3 + 1) times
+    (128 cache layers), vocabulary 65536."""
+    return _loop_spec("loopvl-text-shape", 1536, 12, 4096, 65536, per_stack=16, h_cycles=2, l_cycles=3, original_max=4096)
+
+
 def glm5_next_tiny() -> ModelSpec:
     """Small GLM-5-style shape: the hyper-connection program with every stage collapsing on its own pre-mix, top-k sparse
     attention with the pooled indexer in every layer, sigmoid routing with selection bias."""
@@ -265,6 +287,7 @@ NAMED_SHAPES = {
     "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini, "deepseek-v41-tiny": deepseek_v41_tiny, "glm5-next-tiny": glm5_next_tiny, "flint-tiny": flint_tiny,
+    "loop-tiny": loop_tiny, "loopvl-text-shape": loopvl_text,
     "qwen3-moe-235b-shape": qwen3_moe_235b, "qwen3-moe-tiny": qwen3_moe_tiny,
 }
 

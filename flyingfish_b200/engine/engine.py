@@ -93,6 +93,9 @@ class Engine:
         self.max_batch = max(settings.max_batch, 1)
         self.max_prefill_rows = max_prefill_rows
         self.take_limit = getattr(model, "prefill_take_limit", None) or max_prefill_rows   # rows of ONE sequence per chunk
+        # models that encode a prompt bidirectionally need all of it in one chunk: a prompt is never split, it waits
+        # for a chunk with room (and is refused when it is longer than a chunk)
+        self.whole_prompt = bool(getattr(model, "whole_prompt_prefill", False))
         self.prefill_batch = ForwardBatch(BatchLayout(self.max_batch, max(max_prefill_rows, self.max_batch),
                                                       self.max_blocks), self.device)
         self.graphs: dict[tuple[int, int], _Graph] = {}
@@ -182,6 +185,10 @@ class Engine:
                     if rows_left <= 0 or len(part) >= self.max_batch:
                         break
                     take = min(len(s.prompt) - s.prefilled, rows_left, self.take_limit)
+                    if self.whole_prompt and take < len(s.prompt) - s.prefilled:
+                        if not part and len(s.prompt) > min(chunk, self.take_limit):
+                            raise ValueError(f"prompt of {len(s.prompt)} tokens does not fit one prefill chunk of {chunk} rows")
+                        break
                     part.append((s, take))
                     rows_left -= take
                 toks = self._prefill_chunk(part)
@@ -211,6 +218,10 @@ class Engine:
             if rem <= 0:
                 continue
             take = min(rem, rows_left, self.take_limit)
+            if self.whole_prompt and take < rem:
+                if not part and rem > min(self.max_prefill_rows, self.take_limit):
+                    raise ValueError(f"prompt of {rem} tokens does not fit one prefill chunk of {self.max_prefill_rows} rows")
+                break
             part.append((s, take))
             rows_left -= take
         if not part:

@@ -133,6 +133,32 @@ bias_act_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__
   *p = v;
 }
 
+// y[row, c] = bf16(a[row, c] * sigmoid(gate[row, c])): the output gate of gated attention layers (the gate is a column
+// slice of the fused projection, hence its own leading dimension)
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ gate, __nv_bfloat16* __restrict__ y,
+                    long long rows, int n, int lda, int ldg, int ldy) {
+  pdl_trigger();
+  pdl_wait();
+  const int nvec = n >> 3;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= rows * nvec) return;
+  const long long row = gid / nvec;
+  const int c = (int)(gid - row * nvec);
+  const uint4 av = *(reinterpret_cast<const uint4*>(a + (size_t)row * lda) + c);
+  const uint4 gv = *(reinterpret_cast<const uint4*>(gate + (size_t)row * ldg) + c);
+  uint4 o;
+  const uint32_t* ap = reinterpret_cast<const uint32_t*>(&av);
+  const uint32_t* gp = reinterpret_cast<const uint32_t*>(&gv);
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 x = unpack_bf16x2(ap[j]), g = unpack_bf16x2(gp[j]);
+    op[j] = pack_bf16x2(x.x / (1.f + __expf(-g.x)), x.y / (1.f + __expf(-g.y)));
+  }
+  *(reinterpret_cast<uint4*>(y + (size_t)row * ldy) + c) = o;
+}
+
 // ------------------------------------------------------------------------------------------------
 // voxel hash table. key = (b:16 | x:16 | y:16 | z:16) of non-negative coordinates < 65536; slot value =
 // lowest row index with that key. Empty key = all ones.
@@ -320,6 +346,18 @@ FF_EXPORT int ff_bias_act(void* x, const void* bias, long long rows, int n, int 
   const long long total = rows * (n / 8);
   if (int lr = launch_pdl(bias_act_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0, (__nv_bfloat16*)x,
                           (const __nv_bfloat16*)bias, rows, n, ldx, act)) return lr;
+  return launch_result();
+}
+
+FF_EXPORT int ff_sigmoid_gate(const void* a, const void* gate, void* y, long long rows, int n, int lda, int ldg, int ldy,
+                              cudaStream_t s) {
+  if (rows <= 0 || n <= 0 || n % 8 || lda % 8 || ldg % 8 || ldy % 8) return FF_HOST_BAD_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(gate) & 15) || (reinterpret_cast<uintptr_t>(y) & 15))
+    return FF_HOST_BAD_ALIGN;
+  const long long total = rows * (n / 8);
+  if (int lr = launch_pdl(sigmoid_gate_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0,
+                          (const __nv_bfloat16*)a, (const __nv_bfloat16*)gate, (__nv_bfloat16*)y, rows, n, lda, ldg, ldy))
+    return lr;
   return launch_result();
 }
 

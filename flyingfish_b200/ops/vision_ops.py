@@ -70,6 +70,20 @@ def bias_act_(x: torch.Tensor, bias: torch.Tensor | None, act: str = "none") -> 
     return x
 
 
+def sigmoid_gate(a: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``bf16(a * sigmoid(gate))`` row-wise; ``gate`` may be a column slice of a wider projection."""
+    if not a.is_cuda:
+        return (a.float() * torch.sigmoid(gate.float())).to(a.dtype)
+    rows, n = a.shape
+    _require(a.dtype == BF16 and gate.dtype == BF16 and a.stride(1) == 1 and gate.stride(1) == 1 and gate.shape == a.shape,
+             "sigmoid_gate: bf16 rows")
+    y = torch.empty(rows, n, dtype=BF16, device=a.device)
+    rc = kernels().ff_sigmoid_gate(ptr(a), ptr(gate), ptr(y), c_longlong(rows), n, a.stride(0), gate.stride(0), n, stream_ptr())
+    check(rc, "ff_sigmoid_gate")
+    _count()
+    return y
+
+
 def linear_bias_act(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, act: str = "none") -> torch.Tensor:
     y = linear(x, w)
     if bias is None and act == "none":
@@ -100,7 +114,7 @@ def rope_table_apply_(qkv: torch.Tensor, table: torch.Tensor, heads: int, dim: i
     if not qkv.is_cuda:
         half = rot // 2
         nrot = heads + kv_heads
-        x = qkv[:, : nrot * dim].reshape(rows, nrot, dim).float()
+        x = qkv[:, : nrot * dim].reshape(rows, nrot, dim).to(torch.float32, copy=True)
         cs, sn = table[..., 0][:, None, :], table[..., 1][:, None, :]
         x1, x2 = x[..., :half].clone(), x[..., dim // 2: dim // 2 + half].clone()
         x[..., :half] = _r(_r(x1 * cs) - _r(x2 * sn))
