@@ -115,6 +115,9 @@ def _global_parser() -> argparse.ArgumentParser:
     tr.add_argument("--format", choices=["txt", "json", "srt", "vtt"], default="txt")
     tr.add_argument("--output", help="file to write instead of standard output")
     tr.add_argument("--stream", action="store_true")
+    tr.add_argument("--source-lang", default="en")
+    tr.add_argument("--target-lang", default="en")
+    tr.add_argument("--no-pnc", action="store_true", help="Canary: no punctuation and capitalisation")
 
     for name in DSPARK_TOOLS:
         dp = sub.add_parser(name)
@@ -454,7 +457,7 @@ def cmd_transcribe(args) -> None:
     if not args.model:
         raise SystemExit("transcribe needs --model")
     arch = json.loads((Path(args.model) / "config.json").read_text()).get("architectures", [None])[0]
-    if arch not in ("ParakeetForTDT", "ParakeetForCTC"):
+    if arch not in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration"):
         raise SystemExit(f"unsupported transcription architecture {arch}")
     if args.stream:
         raise SystemExit(f"streaming transcription is not available for {arch}")
@@ -462,7 +465,12 @@ def cmd_transcribe(args) -> None:
     device = "cpu" if args.cpu else f"cuda:{args.device}"
     model = load_model(args.model, device)
     wave = load_audio(args.input, model.spec.mel.sampling_rate)
-    result = model.transcribe([wave])[0]
+    if arch == "CanaryForConditionalGeneration":
+        result = model.transcribe([wave], args.source_lang, args.target_lang, not args.no_pnc)[0]
+    else:
+        if (args.source_lang, args.target_lang, args.no_pnc) != ("en", "en", False):
+            raise SystemExit(f"--source-lang / --target-lang / --no-pnc apply to Canary models, not to {arch}")
+        result = model.transcribe([wave])[0]
     text = {"txt": result.text + "\n", "json": result.to_json() + "\n", "srt": result.to_srt(), "vtt": result.to_vtt()}[args.format]
     if out_path is not None:
         out_path.write_text(text)

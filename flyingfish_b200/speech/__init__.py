@@ -3,3 +3,4 @@ from .audio import LogMel, LogMelConfig, load_audio, read_wav, resample, write_w
 from .parakeet import (ParakeetCtcModel, ParakeetCtcSpec, ParakeetModel, ParakeetSpec, TdtDecoder, TdtTrajectory,  # noqa: F401
                        load_model, parakeet_tiny, transcribe)
 from .transcript import TextSegment, Transcription, tdt_cues, word_segments  # noqa: F401
+from .canary import CanaryModel, CanarySpec, canary_prompt, canary_tiny  # noqa: F401

@@ -449,6 +449,9 @@ def load_model(directory: str | Path, device: torch.device | str = "cpu"):
         return ParakeetModel.load(directory, device)
     if arch == "ParakeetForCTC":
         return ParakeetCtcModel.load(directory, device)
+    if arch == "CanaryForConditionalGeneration":
+        from .canary import CanaryModel
+        return CanaryModel.load(directory, device)
     raise ValueError(f"unsupported transcription architecture {arch}")
 
 
