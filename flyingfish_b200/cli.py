@@ -459,12 +459,28 @@ def cmd_transcribe(args) -> None:
     arch = json.loads((Path(args.model) / "config.json").read_text()).get("architectures", [None])[0]
     if arch not in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration"):
         raise SystemExit(f"unsupported transcription architecture {arch}")
-    if args.stream:
-        raise SystemExit(f"streaming transcription is not available for {arch}")
     out_path = check_output_path(args.output, args.model) if args.output else None
     device = "cpu" if args.cpu else f"cuda:{args.device}"
     model = load_model(args.model, device)
     wave = load_audio(args.input, model.spec.mel.sampling_rate)
+    if args.stream:
+        # cache-aware streaming encoders only: audio goes in 320 ms pieces, one JSON line per piece that produced tokens
+        from .speech import ParakeetModel, StreamingRecognizer
+        enc = getattr(model.spec, "encoder", None)
+        if not isinstance(model, ParakeetModel) or enc is None or enc.chunk_size <= 0 or model.spec.mel.normalize:
+            raise SystemExit(f"streaming transcription is not available for this {arch} checkpoint (no chunk-wise encoder context)")
+        rec = StreamingRecognizer(model)
+        piece = model.spec.mel.sampling_rate * 32 // 100
+        for at in range(0, wave.numel(), piece):
+            nxt = min(wave.numel(), at + piece)
+            new = rec.push(wave[at:nxt], last=nxt == wave.numel())
+            if new and model.tokenizer is not None:
+                sys.stderr.write(json.dumps({"seconds": nxt / model.spec.mel.sampling_rate, "tokens": new,
+                                             "text": model.tokenizer.decode(new)}) + "\n")
+        result = rec.transcription()
+        text = {"txt": result.text + "\n", "json": result.to_json() + "\n", "srt": result.to_srt(), "vtt": result.to_vtt()}[args.format]
+        (out_path.write_text(text) if out_path is not None else sys.stdout.write(text))
+        return
     if arch == "CanaryForConditionalGeneration":
         result = model.transcribe([wave], args.source_lang, args.target_lang, not args.no_pnc)[0]
     else:

@@ -37,6 +37,10 @@ class ConformerSpec:
     max_position: int = 5000
     att_left: int = -1                 # attention context in frames on each side, -1 = unlimited
     att_right: int = -1
+    chunk_size: int = 0                # > 0: chunk-wise context (cache-aware streaming encoders): a query chunk sees
+    left_chunks: int = 0               #      ``left_chunks`` earlier chunks, itself and ``right_chunks`` later ones
+    right_chunks: int = 0
+    causal_conv: bool = False          # the conv module's depthwise taps look back only (left = kernel - 1)
     prefix: str = "encoder"
     conv_names: tuple[str, str, str] = ("subsampling.layers.0", "subsampling.layers.2", "subsampling.layers.5")
     pointwise_names: tuple[str, str] = ("subsampling.layers.3", "subsampling.layers.6")
@@ -45,6 +49,17 @@ class ConformerSpec:
     @property
     def head_dim(self) -> int:
         return self.hidden // self.heads
+
+    @property
+    def conv_left(self) -> int:
+        return self.conv_kernel - 1 if self.causal_conv else self.conv_kernel // 2
+
+    @property
+    def attention_window(self) -> tuple[int, int, int]:
+        """(left, right, chunk) as the attention operator takes them."""
+        if self.chunk_size > 0:
+            return self.left_chunks, self.right_chunks, self.chunk_size
+        return self.att_left, self.att_right, 0
 
     @property
     def pads(self) -> tuple[int, int]:
@@ -249,15 +264,15 @@ class ConformerEncoder:
         qkv = vision_ops.linear_bias_act(x, at["wqkv"], at["bqkv"], "none")
         rel = ops.linear(pos, at["wrel"])
         core = speech_ops.relpos_attention(qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], rel, at["u"], at["v"], lens, batch,
-                                           s.heads, s.att_left, s.att_right)
+                                           s.heads, *s.attention_window)
         d = ops.linear(core, at["wo"])
         cv = L["conv"]
         x = speech_ops.scale_add_layernorm(h, d, at["bo"], 1.0, *cv["norm"])
         e = ops.linear(x, cv["w1"])
         if cv["post"] is None:
-            cvd = speech_ops.glu_dwconv1d(e, cv["b1"], cv["dw"], cv["dwb"], lens, batch, s.conv_kernel // 2, silu=True)
+            cvd = speech_ops.glu_dwconv1d(e, cv["b1"], cv["dw"], cv["dwb"], lens, batch, s.conv_left, silu=True)
         else:
-            cvd = speech_ops.glu_dwconv1d(e, cv["b1"], cv["dw"], cv["dwb"], lens, batch, s.conv_kernel // 2, silu=False)
+            cvd = speech_ops.glu_dwconv1d(e, cv["b1"], cv["dw"], cv["dwb"], lens, batch, s.conv_left, silu=False)
             cvd = speech_ops.scale_add_layernorm(cvd, None, None, 0.0, *cv["post"])
             cvd = vision_ops.bias_act_(cvd, None, "silu")
         d = ops.linear(cvd, cv["w2"])
@@ -279,3 +294,101 @@ class ConformerEncoder:
             x = speech_ops.scale_add_layernorm(h, None, None, 0.0, *self.layers[li]["ff1"]["norm"])
             h = self.layer(li, h, x, lens, batch, pos)
         return h.reshape(batch, t, self.spec.hidden), rows
+
+
+class ConformerStream:
+    """Incremental encoding with a cache-aware streaming encoder (chunk-wise attention context, causal convolutions,
+    causal stem pads; src/backend/cuda/engine_parakeet.rs:1508-2010 of the reference keeps the same three caches).
+    Mel frames go in as they arrive, encoder rows come out chunk by chunk and equal the rows an offline ``encode`` of the
+    whole utterance produces: per layer the stream keeps the fused Q/K/V rows of the last ``left_chunks`` chunks and the
+    last ``kernel - 1`` rows entering the depthwise convolution; the stem is re-run over the few frames a chunk's rows
+    look back on."""
+
+    def __init__(self, encoder: ConformerEncoder):
+        s = encoder.spec
+        if not (s.chunk_size > 0 and s.right_chunks == 0 and s.causal_conv and s.pad_left == 2 and s.pad_right == 1):
+            raise ValueError("streaming needs chunk-wise attention without look-ahead, causal convolutions and causal stem pads")
+        self.enc, self.spec = encoder, s
+        self.frames = torch.zeros(0, s.mel_bins, dtype=torch.float32, device=encoder.device)
+        self.rows_out = 0                                   # encoder rows emitted so far
+        self.qkv = [None] * s.layers                        # [cached rows, 3 * hidden]
+        self.conv = [None] * s.layers                       # [cached rows, 2 * hidden]
+        self.finished = False
+
+    def _stem(self, first_row: int, n_rows: int, last: bool) -> torch.Tensor:
+        """Rows ``first_row .. first_row + n_rows`` of the stem's output from the buffered frames. A row looks back 14
+        frames; the window starts 16 frames (two rows) early so that stride phases line up, and those rows are dropped."""
+        s = self.spec
+        lead = min(2, first_row)
+        f0 = 8 * (first_row - lead)
+        f1 = self.frames.shape[0] if last else min(self.frames.shape[0], 8 * (first_row + n_rows - 1) + 1)
+        window = self.frames[f0:f1][None]
+        hid, rows = self.enc.subsample(window, [f1 - f0])
+        return hid[lead: lead + n_rows]
+
+    def _layers(self, h: torch.Tensor) -> torch.Tensor:
+        enc, s = self.enc, self.spec
+        n_new, hd = h.shape[0], s.hidden
+        keep = s.left_chunks * s.chunk_size
+        dev = enc.device
+        for li in range(s.layers):
+            L = enc.layers[li]
+            x = speech_ops.scale_add_layernorm(h, None, None, 0.0, *L["ff1"]["norm"])
+            ff = L["ff1"]
+            d = ops.linear(vision_ops.linear_bias_act(x, ff["w1"], ff["b1"], "silu"), ff["w2"])
+            at = L["attn"]
+            x = speech_ops.scale_add_layernorm(h, d, ff["b2"], 0.5, *at["norm"])
+            qkv_new = vision_ops.linear_bias_act(x, at["wqkv"], at["bqkv"], "none")
+            qkv = qkv_new if self.qkv[li] is None else torch.cat([self.qkv[li], qkv_new], dim=0)
+            t = qkv.shape[0]
+            rel = ops.linear(enc.positions(t), at["wrel"])
+            lens = torch.tensor([t], dtype=torch.int32, device=dev)
+            # the cached rows start on a chunk boundary, so local chunk indices differ from the absolute ones by a constant
+            core = speech_ops.relpos_attention(qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], rel, at["u"], at["v"], lens, 1,
+                                               s.heads, s.left_chunks, 0, s.chunk_size)[t - n_new:]
+            self.qkv[li] = qkv[max(0, t - keep):].contiguous()
+            cv = L["conv"]
+            x = speech_ops.scale_add_layernorm(h, ops.linear(core.contiguous(), at["wo"]), at["bo"], 1.0, *cv["norm"])
+            e_new = ops.linear(x, cv["w1"])
+            e = e_new if self.conv[li] is None else torch.cat([self.conv[li], e_new], dim=0)
+            te = e.shape[0]
+            lens_e = torch.tensor([te], dtype=torch.int32, device=dev)
+            cvd = speech_ops.glu_dwconv1d(e, cv["b1"], cv["dw"], cv["dwb"], lens_e, 1, s.conv_left, silu=cv["post"] is None)[te - n_new:]
+            self.conv[li] = e[max(0, te - (s.conv_kernel - 1)):].contiguous()
+            cvd = cvd.contiguous()
+            if cv["post"] is not None:
+                cvd = vision_ops.bias_act_(speech_ops.scale_add_layernorm(cvd, None, None, 0.0, *cv["post"]), None, "silu")
+            ff = L["ff2"]
+            x = speech_ops.scale_add_layernorm(h, ops.linear(cvd, cv["w2"]), cv["b2"], 1.0, *ff["norm"])
+            d = ops.linear(vision_ops.linear_bias_act(x, ff["w1"], ff["b1"], "silu"), ff["w2"])
+            h = speech_ops.scale_add_layernorm(h, d, ff["b2"], 0.5, *L["out"])
+        return h
+
+    def push(self, frames: torch.Tensor, last: bool = False) -> torch.Tensor:
+        """Appends mel frames [n, mel_bins] (FP32, un-normalised or normalised by the caller) and returns the encoder
+        rows [m, hidden] that became complete, whole chunks at a time; ``last`` flushes the tail of the utterance."""
+        if self.finished:
+            raise RuntimeError("the stream is finished")
+        s = self.spec
+        self.frames = torch.cat([self.frames, frames.to(self.frames.device, torch.float32)], dim=0)
+        n = self.frames.shape[0]
+        out = []
+        while True:
+            # row r is complete once frame 8r (its newest input) has arrived
+            complete = (n - 1) // 8 + 1 if n > 0 else 0
+            total = s.sub_len(n) if (last and n > 0) else complete
+            avail = total - self.rows_out
+            if avail >= s.chunk_size:
+                take = s.chunk_size
+            elif last and avail > 0:
+                take = avail
+            else:
+                break
+            h = self._stem(self.rows_out, take, last and take == avail)
+            out.append(self._layers(h.contiguous()))
+            self.rows_out += take
+        if last:
+            self.finished = True
+        if not out:
+            return torch.zeros(0, s.hidden, dtype=torch.bfloat16, device=self.enc.device)
+        return torch.cat(out, dim=0)

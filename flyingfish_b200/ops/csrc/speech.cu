@@ -345,7 +345,8 @@ scale_add_layernorm_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* _
 // q, k, v: rows b * T + i, head h at column h * D (leading dimensions ldq / ldk / ldv); pos: [2T - 1, heads * D], row c
 // holds the projected embedding of relative offset (T - 1 - c), so the score of query i and key j uses row
 // T - 1 - i + j. bias_u / bias_v: [heads, D] FP32. Keys j >= lens[b], j < i - left or j > i + right are masked
-// (left / right < 0: unlimited). out rows i >= lens[b] are zero.
+// (left / right < 0: unlimited); with chunk > 0 left / right count chunks of `chunk` rows instead: query chunk c sees
+// key chunks c - left .. c + right. out rows i >= lens[b] are zero.
 // grid (ceil(T / 64), heads, batch), 128 threads: warp w owns query rows i0 + 16w .. +15; key tiles of 64.
 constexpr int RA_Q = 64, RA_KEYS = 64, RA_WIN = 128, RA_RAW_LD = 81;
 
@@ -358,7 +359,7 @@ relpos_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ pos,
                         const float* __restrict__ bias_u, const float* __restrict__ bias_v, const int* __restrict__ lens,
                         __nv_bfloat16* __restrict__ out, int T, int ldq, int ldk, int ldv, int ldp, int ldo, int left,
-                        int right, float scale_log2) {
+                        int right, int chunk, float scale_log2) {
   pdl_trigger();
   pdl_wait();
   constexpr int CH = D / 8;
@@ -406,8 +407,14 @@ relpos_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int qi[2] = {i0 + warp * 16 + g, i0 + warp * 16 + g + 8};
 
   int j_begin = 0, j_end = len;
-  if (left >= 0) j_begin = max(0, i0 - left) / RA_KEYS * RA_KEYS;
-  if (right >= 0) j_end = min(len, i0 + RA_Q + right);
+  if (chunk > 0) {
+    // chunk-wise context: query chunk c sees key chunks c - left .. c + right (streaming encoders)
+    j_begin = max(0, (i0 / chunk - left) * chunk) / RA_KEYS * RA_KEYS;
+    j_end = min(len, ((i0 + RA_Q - 1) / chunk + right + 1) * chunk);
+  } else {
+    if (left >= 0) j_begin = max(0, i0 - left) / RA_KEYS * RA_KEYS;
+    if (right >= 0) j_end = min(len, i0 + RA_Q + right);
+  }
   for (int j0 = j_begin; j0 < j_end; j0 += RA_KEYS) {
     __syncthreads();                     // the previous tile's K, V and window are no longer read
     for (int i = tid; i < RA_KEYS * CH; i += 128) {
@@ -472,7 +479,9 @@ relpos_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const int rl = g + ((e >> 1) << 3), jl = n * 8 + 2 * t4 + (e & 1);
         const int i = qi[e >> 1], j = j0 + jl;
         float sc = (s[n][e] + raw[rl * RA_RAW_LD + jl + 15 - rl]) * scale_log2;
-        const bool ok = j < len && (left < 0 || j >= i - left) && (right < 0 || j <= i + right);
+        bool ok = j < len;
+        if (chunk > 0) { const int qc = i / chunk, kc = j / chunk; ok = ok && kc >= qc - left && kc <= qc + right; }
+        else ok = ok && (left < 0 || j >= i - left) && (right < 0 || j <= i + right);
         sc = ok ? sc : -3.0e38f;
         s[n][e] = sc;
         mx[e >> 1] = fmaxf(mx[e >> 1], sc);
@@ -637,10 +646,12 @@ tdt_select_kernel(const __nv_bfloat16* __restrict__ logits, const float* __restr
   traj_tokens[count] = bi; traj_durations[count] = dur; traj_frames[count] = frame;
   state[TS_COUNT] = count + 1;
   const int next = frame + dur;
-  if (bi == eos || next >= valid_rows) { state[TS_DONE] = 1; return; }
+  // the next (frame, token) is written even when the rows run out: a streaming decode resumes from it when more rows
+  // arrive
   state[TS_FRAME] = next;
   state[TS_TOKEN] = bi;
   state[TS_ADVANCE] = bi != blank;
+  if (bi == eos || next >= valid_rows) state[TS_DONE] = 1;
 }
 
 }  // namespace ff
@@ -712,8 +723,9 @@ FF_EXPORT int ff_scale_add_layernorm(void* h, const void* delta, const float* db
 FF_EXPORT int ff_relpos_attention(const void* q, const void* k, const void* v, const void* pos, const float* bias_u,
                                   const float* bias_v, const int* lens, void* out, int batch, int T, int heads,
                                   int head_dim, int ldq, int ldk, int ldv, int ldp, int ldo, int left, int right,
-                                  float scale, cudaStream_t s) {
+                                  int chunk, float scale, cudaStream_t s) {
   if (batch <= 0 || T <= 0 || heads <= 0 || (head_dim != 64 && head_dim != 128) || !(scale > 0.f)) return FF_HOST_BAD_SHAPE;
+  if (chunk < 0 || (chunk > 0 && (left < 0 || right < 0))) return FF_HOST_BAD_SHAPE;
   if (ldq % 8 || ldk % 8 || ldv % 8 || ldp % 8 || ldo % 2) return FF_HOST_BAD_ALIGN;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
       (reinterpret_cast<uintptr_t>(pos) & 15) || (reinterpret_cast<uintptr_t>(out) & 3)) return FF_HOST_BAD_ALIGN;
@@ -724,13 +736,13 @@ FF_EXPORT int ff_relpos_attention(const void* q, const void* k, const void* v, c
     if (int e = opt_in_smem(relpos_attention_kernel<128>, smem)) return e;
     if (int lr = launch_pdl(relpos_attention_kernel<128>, grid, dim3(128), smem, s, 0, (const __nv_bfloat16*)q,
                             (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)pos, bias_u, bias_v,
-                            lens, (__nv_bfloat16*)out, T, ldq, ldk, ldv, ldp, ldo, left, right, sl2)) return lr;
+                            lens, (__nv_bfloat16*)out, T, ldq, ldk, ldv, ldp, ldo, left, right, chunk, sl2)) return lr;
   } else {
     constexpr int smem = ra_smem_bytes<64>();
     if (int e = opt_in_smem(relpos_attention_kernel<64>, smem)) return e;
     if (int lr = launch_pdl(relpos_attention_kernel<64>, grid, dim3(128), smem, s, 0, (const __nv_bfloat16*)q,
                             (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)pos, bias_u, bias_v,
-                            lens, (__nv_bfloat16*)out, T, ldq, ldk, ldv, ldp, ldo, left, right, sl2)) return lr;
+                            lens, (__nv_bfloat16*)out, T, ldq, ldk, ldv, ldp, ldo, left, right, chunk, sl2)) return lr;
   }
   return launch_result();
 }

@@ -246,11 +246,13 @@ def relative_positions(rows: int, hidden: int, device=None) -> torch.Tensor:
 
 def relpos_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: torch.Tensor, bias_u: torch.Tensor,
                      bias_v: torch.Tensor, lens: torch.Tensor, batch: int, heads: int, left: int = -1,
-                     right: int = -1) -> torch.Tensor:
+                     right: int = -1, chunk: int = 0) -> torch.Tensor:
     """Relative-position self-attention. ``q``, ``k``, ``v``: [batch * T, heads * D] BF16 views (column slices of a
     packed projection are fine), ``pos``: [2T - 1, heads * D] BF16 projected position table (row ``T - 1 - i + j`` serves
     query i / key j), ``bias_u`` / ``bias_v``: [heads, D] FP32. score = ((q + u) . k + (q + v) . p) / sqrt(D); keys at or
-    beyond ``lens[b]`` and outside ``[i - left, i + right]`` are masked; rows at or beyond ``lens[b]`` come back zero."""
+    beyond ``lens[b]`` and outside ``[i - left, i + right]`` are masked; rows at or beyond ``lens[b]`` come back zero.
+    With ``chunk > 0`` the context is chunk-wise instead (streaming encoders): a query in chunk ``c = i // chunk`` sees the
+    keys of chunks ``c - left .. c + right``."""
     rows, width = q.shape
     t, d = rows // batch, width // heads
     if not q.is_cuda:
@@ -267,10 +269,14 @@ def relpos_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: tor
         bd = torch.gather(raw, 3, idx)
         sc = (ac + bd) / math.sqrt(d)
         ok = (j < lens[:, None, None, None])
-        if left >= 0:
-            ok = ok & (j >= i - left)
-        if right >= 0:
-            ok = ok & (j <= i + right)
+        if chunk > 0:
+            qc, kc = i // chunk, j // chunk
+            ok = ok & (kc >= qc - left) & (kc <= qc + right)
+        else:
+            if left >= 0:
+                ok = ok & (j >= i - left)
+            if right >= 0:
+                ok = ok & (j <= i + right)
         sc = sc.masked_fill(~ok, float("-inf"))
         p = torch.softmax(sc, dim=-1)
         o = torch.einsum("bhij,bjhd->bihd", p, vf)
@@ -282,7 +288,7 @@ def relpos_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: tor
     out = torch.empty(rows, width, dtype=BF16, device=q.device)
     rc = kernels().ff_relpos_attention(ptr(q), ptr(k), ptr(v), ptr(pos), ptr(bias_u), ptr(bias_v), ptr(lens), ptr(out),
                                        batch, t, heads, d, q.stride(0), k.stride(0), v.stride(0), pos.stride(0), width,
-                                       left, right, c_float(1.0 / math.sqrt(d)), stream_ptr())
+                                       left, right, chunk, c_float(1.0 / math.sqrt(d)), stream_ptr())
     check(rc, "ff_relpos_attention")
     _count()
     return out
@@ -376,10 +382,9 @@ def tdt_select(logits: torch.Tensor, out_bias: torch.Tensor | None, durations: t
         traj[0][count], traj[1][count], traj[2][count] = tok, dur, frame
         state[TS_COUNT] = count + 1
         nxt = frame + dur
+        state[TS_FRAME], state[TS_TOKEN], state[TS_ADVANCE] = nxt, tok, int(tok != blank)
         if tok == eos or nxt >= valid_rows:
             state[TS_DONE] = 1
-            return
-        state[TS_FRAME], state[TS_TOKEN], state[TS_ADVANCE] = nxt, tok, int(tok != blank)
         return
     rc = kernels().ff_tdt_select(ptr(logits), ptr(out_bias), ptr(durations), ptr(state), ptr(traj[0]), ptr(traj[1]),
                                  ptr(traj[2]), n_tok, n_dur, blank, eos, traj_len, stream_ptr())

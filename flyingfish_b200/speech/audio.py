@@ -128,6 +128,7 @@ class LogMelConfig:
     preemphasis: float = 0.97
     log_guard: float = 2.0 ** -24
     norm_eps: float = 1e-5
+    normalize: bool = True             # per-utterance, per-band normalisation (off for streaming models)
 
     def check(self) -> None:
         if not (self.sampling_rate > 0 and self.hop_length > 0 and self.mel_bins > 0 and 1 < self.win_length <= self.n_fft
@@ -181,3 +182,42 @@ class LogMel:
         feat = speech_ops.logmel(batch.to(self.device), lens.to(self.device), self.window, self.filters, self.ranges, hop,
                                  self.config.preemphasis, self.config.log_guard, normalize, self.config.norm_eps)
         return feat, (lens // hop).to(torch.int32)
+
+
+class StreamingLogMel:
+    """Log-mel frames of a growing waveform, un-normalised, identical to what ``LogMel.extract(normalize=False)`` gives
+    for the whole utterance. A frame is emitted once the samples under its window have arrived (``last`` flushes the
+    frames that look past the end, as the offline path computes them); every call re-runs the extractor over the new
+    frames plus two frames of lead-in so that windows and pre-emphasis see real samples on their left."""
+
+    def __init__(self, mel: LogMel):
+        self.mel = mel
+        self.buf = torch.zeros(0, dtype=torch.float32)
+        self.emitted = 0
+        self.finished = False
+
+    def push(self, samples: torch.Tensor, last: bool = False) -> torch.Tensor:
+        if self.finished:
+            raise RuntimeError("the stream is finished")
+        cfg = self.mel.config
+        hop, half = cfg.hop_length, cfg.n_fft // 2
+        self.buf = torch.cat([self.buf, samples.detach().float().cpu().reshape(-1)])
+        n = self.buf.numel()
+        ready = n // hop if last else (max(0, (n - half) // hop + 1) if n >= half else 0)
+        if last:
+            self.finished = True
+        t0 = self.emitted
+        empty = torch.zeros(0, cfg.mel_bins, dtype=torch.float32, device=self.mel.device)
+        if ready <= t0:
+            return empty
+        lead = min(2, t0)
+        s0 = (t0 - lead) * hop
+        end = n if last else min(n, (ready - 1) * hop + half + hop)
+        sub = self.buf[s0:end]
+        if sub.numel() < 2 * hop:
+            if not last:
+                return empty
+            sub = torch.nn.functional.pad(sub, (0, 2 * hop - sub.numel()))
+        feat, _ = self.mel.extract([sub], normalize=False)
+        self.emitted = ready
+        return feat[0, lead: lead + ready - t0]

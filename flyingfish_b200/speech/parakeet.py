@@ -78,11 +78,26 @@ class ParakeetSpec:
                            preemphasis=float(feats["preemphasis"]))
         if mel.mel_bins != int(enc["num_mel_bins"]):
             raise ValueError("feature size and encoder mel bins differ")
+        stream = {}
+        if "sliding_window" in enc:
+            # cache-aware streaming encoder (the layout of streaming RNN-T checkpoints): chunks of look-ahead + 1 rows,
+            # a left context of whole chunks, causal convolutions and stem pads, layer norm in the convolution module,
+            # un-normalised features
+            chunk = int(enc.get("default_num_lookahead_tokens", 0)) + 1
+            left = int(enc["sliding_window"])
+            if left % chunk:
+                raise ValueError(f"sliding-window left context {left} does not divide by chunk {chunk}")
+            stream = dict(chunk_size=chunk, left_chunks=left // chunk, causal_conv=True, pad_left=2, pad_right=1, conv_batch_norm=False,
+                          conv_names=("subsampling.conv_in", "subsampling.layers.0.depthwise_conv", "subsampling.layers.1.depthwise_conv"),
+                          pointwise_names=("subsampling.layers.0.pointwise_conv", "subsampling.layers.1.pointwise_conv"))
+            mel = LogMelConfig(sampling_rate=mel.sampling_rate, n_fft=mel.n_fft, win_length=mel.win_length, hop_length=mel.hop_length,
+                               mel_bins=mel.mel_bins, preemphasis=mel.preemphasis, normalize=False)
         encoder = ConformerSpec(layers=int(enc["num_hidden_layers"]), hidden=int(enc["hidden_size"]),
                                 heads=int(enc["num_attention_heads"]), intermediate=int(enc["intermediate_size"]),
                                 conv_kernel=int(enc["conv_kernel_size"]), mel_bins=mel.mel_bins,
                                 sub_channels=int(enc["subsampling_conv_channels"]), attention_bias=bool(enc["attention_bias"]),
-                                convolution_bias=bool(enc["convolution_bias"]), max_position=int(enc["max_position_embeddings"]))
+                                convolution_bias=bool(enc["convolution_bias"]), max_position=int(enc["max_position_embeddings"]),
+                                **stream)
         spec = cls(encoder=encoder, decoder_hidden=int(root["decoder_hidden_size"]), decoder_layers=int(root["num_decoder_layers"]),
                    vocab=int(root["vocab_size"]), blank=int(root["blank_token_id"]), max_symbols=int(root["max_symbols_per_step"]),
                    eos=int(generation.get("eos_token_id", 3)), pad=int(root.get("pad_token_id", 2)),
@@ -112,6 +127,8 @@ class ParakeetSpec:
                                    "num_key_value_heads": e.heads, "num_hidden_layers": e.layers, "num_mel_bins": e.mel_bins,
                                    "subsampling_conv_channels": e.sub_channels, "subsampling_conv_kernel_size": 3,
                                    "subsampling_conv_stride": 2, "subsampling_factor": 8}}
+        if e.chunk_size > 0:
+            root["encoder_config"].update(sliding_window=e.left_chunks * e.chunk_size, default_num_lookahead_tokens=e.chunk_size - 1)
         m = self.mel
         processor = {"processor_class": "ParakeetProcessor", "blank_token": "<blank>",
                      "feature_extractor": {"feature_extractor_type": "ParakeetFeatureExtractor", "feature_size": m.mel_bins,
@@ -261,6 +278,52 @@ class TdtDecoder:
         self._graph = g
         self.state.copy_(saved)
 
+    # -- streaming: rows arrive in pieces, the device state carries on ---------------------------------------
+    def begin_stream(self) -> None:
+        self.reset(1)
+        st = self.state.tolist()
+        st[TS_VALID], st[TS_CAP], st[TS_DONE] = 0, self.traj[0].numel(), 1
+        self.state.copy_(torch.tensor(st, dtype=torch.int32))
+        self._rows = 0
+        self._taken = 1                                  # trajectory entries already handed out (the initial blank)
+
+    def extend(self, projected: torch.Tensor) -> TdtTrajectory:
+        """Appends projected encoder rows and decodes as far as they reach; returns the new trajectory entries."""
+        n = projected.shape[0]
+        if self._rows + n > self.max_rows:
+            raise ValueError(f"stream longer than {self.max_rows} encoder rows")
+        if self.use_graph and self._graph is None:
+            saved_rows, saved_taken, saved_state = self._rows, self._taken, self.state.clone()
+            self._capture()
+            self._rows, self._taken = saved_rows, saved_taken
+            self.state.copy_(saved_state)
+        if n:
+            self.enc[self._rows: self._rows + n].copy_(projected)
+            self._rows += n
+        st = self.state.tolist()
+        stopped_on_eos = st[TS_DONE] and st[TS_COUNT] > 1 and int(self.traj[0][st[TS_COUNT] - 1]) == self.spec.eos
+        st[TS_VALID] = self._rows
+        st[TS_DONE] = int(stopped_on_eos or st[TS_FRAME] >= self._rows)
+        self.state.copy_(torch.tensor(st, dtype=torch.int32))
+        steps = reads = 0
+        while not st[TS_DONE]:
+            if self.use_graph:
+                for _ in range(CHECK_EVERY):
+                    self._graph.replay()
+                self.graph_replays += CHECK_EVERY
+                steps += CHECK_EVERY
+            else:
+                self.step()
+                steps += 1
+            st = self.state.tolist()
+            reads += 1
+            if st[TS_ERROR]:
+                raise RuntimeError(f"decode capacity exceeded at frame {st[TS_FRAME]}")
+        lo, hi = self._taken, st[TS_COUNT]
+        self._taken = hi
+        tok, dur, frm = (t[lo:hi].tolist() for t in self.traj)
+        return TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=self.traj[0].numel(), steps=steps, state_reads=reads)
+
     def decode(self, projected: torch.Tensor, valid_rows: int) -> TdtTrajectory:
         """Greedy decode of one utterance from its projected encoder rows [rows, decoder_hidden]."""
         rows = projected.shape[0]
@@ -321,7 +384,7 @@ class ParakeetModel:
         return cls(spec, tensors, device, tokenizer=load_tokenizer(directory), **kw)
 
     def encode(self, waveforms: list[torch.Tensor]) -> tuple[torch.Tensor, list[int]]:
-        feat, valid = self.mel.extract(waveforms, normalize=True)
+        feat, valid = self.mel.extract(waveforms, normalize=self.spec.mel.normalize)
         return self.encoder.encode(feat, valid.tolist())
 
     def decode(self, waveforms: list[torch.Tensor]) -> list[TdtTrajectory]:
@@ -458,3 +521,49 @@ def load_model(directory: str | Path, device: torch.device | str = "cpu"):
 def transcribe(directory: str | Path, waveform: torch.Tensor, device: torch.device | str = "cpu") -> Transcription:
     """Loads the checkpoint in ``directory`` and transcribes one 16 kHz mono waveform."""
     return load_model(directory, device).transcribe([waveform])[0]
+
+
+def streaming_tiny() -> ParakeetSpec:
+    """A small cache-aware streaming shape: chunks of 4 encoder rows seeing 3 earlier chunks, causal convolutions and
+    stem pads, layer-norm convolution module, plain RNN-T decoder, un-normalised features."""
+    enc = ConformerSpec(layers=2, hidden=128, heads=2, intermediate=256, conv_kernel=9, mel_bins=32, sub_channels=32,
+                        conv_batch_norm=False, pad_left=2, pad_right=1, max_position=512, chunk_size=4, left_chunks=3,
+                        causal_conv=True, conv_names=("subsampling.conv_in", "subsampling.layers.0.depthwise_conv",
+                                                      "subsampling.layers.1.depthwise_conv"),
+                        pointwise_names=("subsampling.layers.0.pointwise_conv", "subsampling.layers.1.pointwise_conv"))
+    return ParakeetSpec(encoder=enc, decoder_hidden=64, decoder_layers=1, vocab=41, blank=40, max_symbols=10, eos=3, durations=(),
+                        mel=LogMelConfig(mel_bins=32, normalize=False))
+
+
+class StreamingRecognizer:
+    """Incremental recognition with a streaming-capable model: audio in pieces, tokens out as soon as the encoder rows
+    they depend on are complete (front end, encoder stream and transducer state all carry on between calls)."""
+
+    def __init__(self, model: ParakeetModel):
+        from ..models.conformer import ConformerStream
+        from .audio import StreamingLogMel
+        if model.spec.mel.normalize:
+            raise ValueError("streaming needs un-normalised features (per-utterance statistics are not causal)")
+        self.model = model
+        self.front = StreamingLogMel(model.mel)
+        self.stream = ConformerStream(model.encoder)
+        model.decoder.begin_stream()
+        self.tokens: list[int] = [model.spec.blank]
+        self.durations: list[int] = [0]
+        self.frames: list[int] = [0]
+
+    def push(self, samples: torch.Tensor, last: bool = False) -> list[int]:
+        """Feeds samples; returns the non-blank tokens recognised by this call."""
+        frames = self.front.push(samples, last)
+        rows = self.stream.push(frames, last)
+        new = self.model.decoder.extend(self.model.decoder.project(rows) if rows.shape[0] else rows[:, : self.model.spec.decoder_hidden])
+        self.tokens += new.tokens
+        self.durations += new.durations
+        self.frames += new.frames
+        return [t for t in new.tokens if t != self.model.spec.blank]
+
+    def trajectory(self) -> TdtTrajectory:
+        return TdtTrajectory(self.tokens, self.durations, self.frames, self.model.decoder.traj[0].numel())
+
+    def transcription(self) -> Transcription:
+        return self.model.transcription(self.trajectory())

@@ -454,7 +454,7 @@ def test_transcribe_command(tmp_path, capsys):
     assert target.read_text() == direct.to_srt()
     with pytest.raises(SystemExit, match="refusing to overwrite"):
         cli.main(["--cpu", "--model", str(d), "transcribe", str(tmp_path / "in.wav"), "--output", str(target)])
-    with pytest.raises(SystemExit, match="streaming"):
+    with pytest.raises(SystemExit, match="streaming transcription is not available"):
         cli.main(["--cpu", "--model", str(d), "transcribe", str(tmp_path / "in.wav"), "--stream"])
     cfg = json.loads((d / "config.json").read_text())
     cfg["architectures"] = ["WhisperForConditionalGeneration"]
