@@ -278,7 +278,7 @@ def relpos_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: tor
             if right >= 0:
                 ok = ok & (j <= i + right)
         sc = sc.masked_fill(~ok, float("-inf"))
-        p = torch.softmax(sc, dim=-1)
+        p = torch.nan_to_num(torch.softmax(sc, dim=-1))       # a row without any visible key (padding rows) is zero
         o = torch.einsum("bhij,bjhd->bihd", p, vf)
         o = o * (torch.arange(t)[None, :, None, None] < lens[:, None, None, None])
         return o.reshape(rows, width).to(BF16)
