@@ -456,6 +456,15 @@ def cmd_transcribe(args) -> None:
     from .speech import load_audio, load_model
     if not args.model:
         raise SystemExit("transcribe needs --model")
+    if str(args.model).endswith(".nemo"):
+        # NeMo archive of a streaming RNN-T (end-of-utterance models): --stream cuts the text into timed utterances
+        from .speech.nemo import transcribe_nemo
+        out_path = check_output_path(args.output, None) if args.output else None
+        wave = load_audio(args.input, 16000)
+        result = transcribe_nemo(args.model, wave, "cpu" if args.cpu else f"cuda:{args.device}", stream=args.stream)
+        text = {"txt": result.text + "\n", "json": result.to_json() + "\n", "srt": result.to_srt(), "vtt": result.to_vtt()}[args.format]
+        (out_path.write_text(text) if out_path is not None else sys.stdout.write(text))
+        return
     arch = json.loads((Path(args.model) / "config.json").read_text()).get("architectures", [None])[0]
     if arch not in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration"):
         raise SystemExit(f"unsupported transcription architecture {arch}")

@@ -246,3 +246,17 @@ def read_nemo(path: str | Path) -> tuple[str, PthFile]:
     if cfg is None or weights is None:
         raise ValueError("not a .nemo archive (model_config.yaml / model_weights.ckpt missing)")
     return cfg, PthFile(path, weights[0], weights[1])
+
+
+def read_nemo_member(path: str | Path, suffix: str) -> bytes:
+    """Bytes of the one archive member whose name ends in ``suffix`` (tokenizer vocabularies carry a hash prefix)."""
+    hits = []
+    with tarfile.open(Path(path), "r:") as tar:
+        for m in tar:
+            if ".." in m.name.split("/") or m.name.startswith("/"):
+                raise ValueError(f"tar member {m.name} escapes the archive")
+            if m.isfile() and m.name.endswith(suffix):
+                hits.append(tar.extractfile(m).read())
+    if len(hits) != 1:
+        raise ValueError(f"{len(hits)} archive members end in {suffix!r}; one is expected")
+    return hits[0]

@@ -45,6 +45,9 @@ class ConformerSpec:
     conv_names: tuple[str, str, str] = ("subsampling.layers.0", "subsampling.layers.2", "subsampling.layers.5")
     pointwise_names: tuple[str, str] = ("subsampling.layers.3", "subsampling.layers.6")
     linear_name: str = "subsampling.linear"
+    # q, k, v, output, position projection, the two position biases; the norm inside the convolution module
+    attention_names: tuple[str, ...] = ("q_proj", "k_proj", "v_proj", "o_proj", "relative_k_proj", "bias_u", "bias_v")
+    conv_norm_name: str = "norm"
 
     @property
     def head_dim(self) -> int:
@@ -102,13 +105,14 @@ class ConformerSpec:
             for norm in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
                 out[f"{p}.{norm}.weight"] = ("F32", (h,))
                 out[f"{p}.{norm}.bias"] = ("F32", (h,))
-            for proj in ("q_proj", "k_proj", "v_proj", "o_proj", "relative_k_proj"):
+            an = self.attention_names
+            for proj in an[:5]:
                 out[f"{p}.self_attn.{proj}.weight"] = ("F32", (h, h))
             if self.attention_bias:
-                for proj in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                for proj in an[:4]:
                     out[f"{p}.self_attn.{proj}.bias"] = ("F32", (h,))
-            out[f"{p}.self_attn.bias_u"] = ("F32", (self.heads, self.head_dim))
-            out[f"{p}.self_attn.bias_v"] = ("F32", (self.heads, self.head_dim))
+            out[f"{p}.self_attn.{an[5]}"] = ("F32", (self.heads, self.head_dim))
+            out[f"{p}.self_attn.{an[6]}"] = ("F32", (self.heads, self.head_dim))
             out[f"{p}.conv.pointwise_conv1.weight"] = ("F32", (2 * h, h, 1))
             out[f"{p}.conv.pointwise_conv2.weight"] = ("F32", (h, h, 1))
             out[f"{p}.conv.depthwise_conv.weight"] = ("F32", (h, 1, k))
@@ -118,9 +122,9 @@ class ConformerSpec:
                 out[f"{p}.conv.depthwise_conv.bias"] = ("F32", (h,))
             names = ("weight", "bias", "running_mean", "running_var") if self.conv_batch_norm else ("weight", "bias")
             for n in names:
-                out[f"{p}.conv.norm.{n}"] = ("F32", (h,))
+                out[f"{p}.conv.{self.conv_norm_name}.{n}"] = ("F32", (h,))
             if self.conv_batch_norm:
-                out[f"{p}.conv.norm.num_batches_tracked"] = ("I64", ())
+                out[f"{p}.conv.{self.conv_norm_name}.num_batches_tracked"] = ("I64", ())
         for n in self.conv_names:
             out[f"{self.prefix}.{n}.weight"] = ("F32", (c, 1, 3, 3))
             out[f"{self.prefix}.{n}.bias"] = ("F32", (c,))
@@ -193,23 +197,25 @@ class ConformerEncoder:
                               w2=w16(tensors[f"{q}.{branch}.linear2.weight"].float()),
                               b2=opt32(f"{q}.{branch}.linear2.bias"))
             a = f"{q}.self_attn"
-            wqkv = torch.cat([tensors[f"{a}.{n}.weight"].float() for n in ("q_proj", "k_proj", "v_proj")], dim=0)
+            an = spec.attention_names
+            wqkv = torch.cat([tensors[f"{a}.{n}.weight"].float() for n in an[:3]], dim=0)
             bqkv = None
-            if f"{a}.q_proj.bias" in tensors:
-                bqkv = w16(torch.cat([tensors[f"{a}.{n}.bias"].float() for n in ("q_proj", "k_proj", "v_proj")]))
+            if f"{a}.{an[0]}.bias" in tensors:
+                bqkv = w16(torch.cat([tensors[f"{a}.{n}.bias"].float() for n in an[:3]]))
             L["attn"] = dict(norm=(f32(f"{q}.norm_self_att.weight"), f32(f"{q}.norm_self_att.bias")), wqkv=w16(wqkv), bqkv=bqkv,
-                             wrel=w16(tensors[f"{a}.relative_k_proj.weight"].float()), wo=w16(tensors[f"{a}.o_proj.weight"].float()),
-                             bo=opt32(f"{a}.o_proj.bias"), u=f32(f"{a}.bias_u"), v=f32(f"{a}.bias_v"))
+                             wrel=w16(tensors[f"{a}.{an[4]}.weight"].float()), wo=w16(tensors[f"{a}.{an[3]}.weight"].float()),
+                             bo=opt32(f"{a}.{an[3]}.bias"), u=f32(f"{a}.{an[5]}"), v=f32(f"{a}.{an[6]}"))
             cv = f"{q}.conv"
             dw = tensors[f"{cv}.depthwise_conv.weight"].float().reshape(h, spec.conv_kernel)
             dwb = tensors[f"{cv}.depthwise_conv.bias"].float() if f"{cv}.depthwise_conv.bias" in tensors else torch.zeros(h)
             post = None
+            cn = f"{cv}.{spec.conv_norm_name}"
             if spec.conv_batch_norm:
-                g = tensors[f"{cv}.norm.weight"].float() * torch.rsqrt(tensors[f"{cv}.norm.running_var"].float() + 1e-5)
+                g = tensors[f"{cn}.weight"].float() * torch.rsqrt(tensors[f"{cn}.running_var"].float() + 1e-5)
                 dw = dw * g[:, None]
-                dwb = (dwb - tensors[f"{cv}.norm.running_mean"].float()) * g + tensors[f"{cv}.norm.bias"].float()
+                dwb = (dwb - tensors[f"{cn}.running_mean"].float()) * g + tensors[f"{cn}.bias"].float()
             else:
-                post = (f32(f"{cv}.norm.weight"), f32(f"{cv}.norm.bias"))
+                post = (f32(f"{cn}.weight"), f32(f"{cn}.bias"))
             L["conv"] = dict(norm=(f32(f"{q}.norm_conv.weight"), f32(f"{q}.norm_conv.bias")),
                              w1=w16(tensors[f"{cv}.pointwise_conv1.weight"].float().reshape(2 * h, h)),
                              b1=opt32(f"{cv}.pointwise_conv1.bias"), dw=dw.t().contiguous().to(dev), dwb=dwb.contiguous().to(dev),

@@ -191,3 +191,117 @@ def test_transcribe_stream_command(tmp_path, capsys):
     updates = [json.loads(l) for l in io.err.splitlines() if l.startswith("{")]
     assert all(u["tokens"] and u["seconds"] <= 20000 / 16000 + 1e-9 for u in updates)
     assert [u["seconds"] for u in updates] == sorted(u["seconds"] for u in updates)
+
+
+NEMO_YAML = """\
+token_init_method: constant
+sample_rate: 16000
+preprocessor:
+  sample_rate: 16000
+  normalize: NA
+  window_size: 0.025
+  window_stride: 0.01
+  features: 32
+  n_fft: 512
+  frame_splicing: 1
+  dither: 1.0e-05
+  pad_to: 0
+encoder:
+  feat_in: 32
+  n_layers: 2
+  d_model: 128
+  use_bias: false
+  subsampling: dw_striding
+  subsampling_factor: 8
+  subsampling_conv_channels: 32
+  causal_downsampling: true
+  ff_expansion_factor: 2
+  self_attention_model: rel_pos
+  n_heads: 2
+  att_context_size:
+  - 6
+  - 1
+  att_context_style: chunked_limited
+  xscaling: false
+  pos_emb_max_len: 512
+  conv_kernel_size: 9
+  conv_norm_type: layer_norm
+  conv_context_size: causal
+decoder:
+  vocab_size: 30
+  blank_as_pad: true
+  prednet:
+    pred_hidden: 64
+    pred_rnn_layers: 1
+joint:
+  num_classes: 30
+  jointnet:
+    joint_hidden: 64
+    activation: relu
+    encoder_hidden: 128
+    pred_hidden: 64
+"""
+
+
+def _write_nemo(path, spec, seed):
+    import io
+    import tarfile
+    from flyingfish_b200.speech.nemo import canonical_tensors
+    canon = random_tensors(spec.expected_tensors(), seed)
+    # NeMo spellings of the decoder / joint tensors (the encoder's are carried by the spec)
+    back = {"decoder.embedding.weight": "decoder.prediction.embed.weight", "decoder.decoder_projector.weight": "joint.pred.weight",
+            "decoder.decoder_projector.bias": "joint.pred.bias", "encoder_projector.weight": "joint.enc.weight",
+            "encoder_projector.bias": "joint.enc.bias", "joint.head.weight": "joint.joint_net.2.weight", "joint.head.bias": "joint.joint_net.2.bias"}
+    for kind in ("weight_ih", "weight_hh", "bias_ih", "bias_hh"):
+        back[f"decoder.lstm.{kind}_l0"] = f"decoder.prediction.dec_rnn.lstm.{kind}_l0"
+    nemo = {back.get(n, n): t for n, t in canon.items()}
+    assert set(canonical_tensors(spec, nemo)) == set(canon)
+    buf = io.BytesIO()
+    torch.save(nemo, buf)
+    vocab = "\n".join(["<unk>\t0.0"] + [f"{'▁' if i % 2 else ''}p{i}\t-{i}.0" for i in range(1, 28)] + ["<EOU>\t-1.0", "<EOB>\t-1.0"])
+    with tarfile.open(path, "w") as tar:
+        for name, data in (("./model_config.yaml", NEMO_YAML.encode()), ("./model_weights.ckpt", buf.getvalue()),
+                           ("./abc123_tokenizer.vocab", vocab.encode())):
+            info = tarfile.TarInfo(name)
+            info.size = len(data)
+            tar.addfile(info, io.BytesIO(data))
+    return canon
+
+
+def test_nemo_archive_streams_and_cuts_utterances(tmp_path):
+    from flyingfish_b200.speech.nemo import UnigramVocab, load_nemo, spec_from_yaml, split_utterances, transcribe_nemo
+    spec = spec_from_yaml(NEMO_YAML)
+    e = spec.encoder
+    assert (e.chunk_size, e.left_chunks, e.right_chunks, e.causal_conv, e.conv_batch_norm) == (2, 3, 0, True, False)
+    assert spec.blank == 30 and spec.vocab == 31 and spec.durations == () and not spec.mel.normalize and spec.mel.win_length == 400
+    assert "encoder.layers.0.self_attn.linear_pos.weight" in spec.expected_tensors()
+    assert "encoder.layers.1.conv.batch_norm.weight" in spec.expected_tensors() and "encoder.pre_encode.out.bias" in spec.expected_tensors()
+    with pytest.raises(ValueError, match="architecture variant"):
+        spec_from_yaml(NEMO_YAML.replace("chunked_limited", "regular"))
+    with pytest.raises(ValueError, match="lacks"):
+        spec_from_yaml(NEMO_YAML.replace("  n_heads: 2\n", ""))
+    arc = tmp_path / "m.nemo"
+    canon = _write_nemo(arc, spec, 21)
+    model = load_nemo(arc)
+    direct = ParakeetModel(spec, canon)
+    g = torch.Generator().manual_seed(22)
+    wave = 0.2 * torch.randn(16000, generator=g)
+    a, b = StreamingRecognizer(model), StreamingRecognizer(direct)
+    a.push(wave, last=True); b.push(wave, last=True)
+    assert a.tokens == b.tokens and a.frames == b.frames
+    assert UnigramVocab("<unk>\t0.0\n▁hello\t-1.0\n▁world\t-2.0\n▁again\t-3.0").decode([1, 2]) == "hello world"
+    # utterances end where the marker is emitted
+    utt = split_utterances([30, 5, 6, 28, 30, 7, 28, 9], [0, 1, 1, 3, 3, 6, 8, 9], [0, 0, 0, 0, 1, 0, 0, 0], blank=30, eou=28)
+    assert [(u[0], round(u[1], 2), round(u[2], 2)) for u in utt] == [([5, 6], 0.0, 0.24), ([7], 0.24, 0.64), ([9], 0.64, 0.72)]
+    res = transcribe_nemo(arc, wave)
+    assert isinstance(res.text, str) and all(s.end >= s.start for s in res.segments)
+    whole = transcribe_nemo(arc, wave, stream=False)
+    assert len(whole.segments) <= 1
+    from flyingfish_b200 import cli
+    from flyingfish_b200.speech import write_wav
+    write_wav(tmp_path / "w.wav", wave, 16000)
+    import contextlib, io as _io, json as _json
+    buf = _io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert cli.main(["--cpu", "--model", str(arc), "transcribe", str(tmp_path / "w.wav"), "--stream", "--format", "json"]) == 0
+    assert _json.loads(buf.getvalue())["text"] == res.text
