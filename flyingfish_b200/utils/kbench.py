@@ -115,10 +115,17 @@ def bench_attn_decode(args) -> dict:
     cl = torch.full((b,), ctx, dtype=torch.int32, device=dev)
     q = torch.randn(b, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16)
     fn = lambda: ops.attn_decode(q, kc, vc, bt, cl, hq, hkv, d, 1 / math.sqrt(d), max_ctx=ctx)
+    if args.torch:
+        # the library arm: torch's fused attention over contiguous K / V of the same sizes (no paging, no packed Q)
+        q4 = q[:, : hq * d].reshape(b, hq, 1, d).contiguous()
+        k4 = kc.view(b, blocks_per, hkv, 64, d).permute(0, 2, 1, 3, 4).reshape(b, hkv, blocks_per * 64, d)[:, :, :ctx].contiguous()
+        v4 = vc.view(b, blocks_per, hkv, 64, d).permute(0, 2, 1, 3, 4).reshape(b, hkv, blocks_per * 64, d)[:, :, :ctx].contiguous()
+        fn = lambda: torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, enable_gqa=True)
     byts = 2 * b * ctx * hkv * d * 2
     r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
     pk = peaks()
-    r.update(op="attn_decode", batch=b, ctx=ctx, hq=hq, hkv=hkv, gbs=byts / (r["us_median"] * 1e-6) / 1e9)
+    r.update(op="attn_decode", impl="torch_sdpa" if args.torch else "own", batch=b, ctx=ctx, hq=hq, hkv=hkv,
+             gbs=byts / (r["us_median"] * 1e-6) / 1e9)
     r["frac_hbm"] = r["gbs"] / pk["hbm_gbs"]
     r["peaks"] = pk["source"]
     return r
@@ -136,10 +143,15 @@ def bench_attn_prefill(args) -> dict:
     qs = (torch.arange(b, dtype=torch.int32, device=dev) * ctx)
     q = torch.randn(b * ctx, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16)
     fn = lambda: ops.attn_prefill(q, kc, vc, bt, qs, ql, ql, ctx, hq, hkv, d, 1 / math.sqrt(d))
+    if args.torch:
+        q4 = q[:, : hq * d].reshape(b, ctx, hq, d).transpose(1, 2).contiguous()
+        k4 = kc.view(b, blocks_per, hkv, 64, d).permute(0, 2, 1, 3, 4).reshape(b, hkv, blocks_per * 64, d)[:, :, :ctx].contiguous()
+        v4 = vc.view(b, blocks_per, hkv, 64, d).permute(0, 2, 1, 3, 4).reshape(b, hkv, blocks_per * 64, d)[:, :, :ctx].contiguous()
+        fn = lambda: torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=True)
     flops = 4.0 * b * hq * d * ctx * (ctx + 1) / 2
     r = time_op(fn, args.iters, args.warmup, None)
     pk = peaks()
-    r.update(op="attn_prefill", batch=b, ctx=ctx, hq=hq, hkv=hkv, tflops=flops / (r["us_median"] * 1e-6) / 1e12)
+    r.update(op="attn_prefill", impl="torch_sdpa" if args.torch else "own", batch=b, ctx=ctx, hq=hq, hkv=hkv, tflops=flops / (r["us_median"] * 1e-6) / 1e12)
     r["frac_tensor"] = r["tflops"] / pk["bf16_tflops"]
     r["peaks"] = pk["source"]
     return r
@@ -255,6 +267,18 @@ def bench_speech(args) -> dict:
     from ..speech import ParakeetModel, ParakeetSpec
     dev = torch.device("cuda")
     spec = ParakeetSpec()
+    if args.attention_only:
+        t, h, d = spec.encoder.sub_len(int(args.seconds * 100)), spec.encoder.heads, spec.encoder.head_dim
+        qkv = torch.randn(args.batch * t, 3 * h * d, device=dev).to(torch.bfloat16)
+        pos = torch.randn(2 * t - 1, h * d, device=dev).to(torch.bfloat16)
+        u, v = torch.randn(h, d, device=dev), torch.randn(h, d, device=dev)
+        lens = torch.full((args.batch,), t, dtype=torch.int32, device=dev)
+        hd = h * d
+        att = time_op(lambda: speech_ops.relpos_attention(qkv[:, :hd], qkv[:, hd:2 * hd], qkv[:, 2 * hd:], pos, u, v, lens,
+                                                          args.batch, h), args.iters, args.warmup, None)
+        flops = 3 * 2.0 * args.batch * h * t * t * d
+        return {"op": "relpos_attention", "batch": args.batch, "rows": t, "heads": h, "head_dim": d, "us": att["us_median"],
+                "tflops": flops / att["us_median"] / 1e6}
     model = ParakeetModel.random(spec, dev, seed=0)
     g = torch.Generator().manual_seed(0)
     waves = [0.1 * torch.randn(int(args.seconds * 16000), generator=g) for _ in range(args.batch)]
@@ -315,6 +339,7 @@ def main(argv=None) -> None:
         elif name == "speech":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--seconds", type=float, default=30.0)
+            p.add_argument("--attention-only", action="store_true", help="only the relative-position attention kernel of one layer")
         elif name == "moe":
             p.add_argument("--rows", type=int, default=128)
             p.add_argument("--experts", type=int, default=128)
@@ -331,6 +356,8 @@ def main(argv=None) -> None:
             p.add_argument("--hkv", type=int, default=8)
             if name == "attn_mixed":
                 p.add_argument("--recent", type=int, default=2048)
+            if name in ("attn_decode", "attn_prefill"):
+                p.add_argument("--torch", action="store_true", help="time torch's fused attention on contiguous K / V instead")
     args = ap.parse_args(argv)
     fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "attn_mixed": bench_attn_mixed, "gdn": bench_gdn,
           "moe": bench_moe, "speech": bench_speech}[args.op]
