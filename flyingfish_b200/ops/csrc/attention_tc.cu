@@ -15,7 +15,8 @@
 //
 // Warp roles: warp 0 = TMA producer (Q once, then K/V tiles through a ring of stages, block ids read from the
 // block table), warp 1 = MMA issuer, warps 2-5 = softmax: thread t owns query row t (TMEM lane t), reads its S
-// row with tcgen05.ld, applies scale and mask, keeps the running maximum and sum in the base-2 domain, and
+// row with tcgen05.ld, applies the mask where a tile needs one, keeps the running maximum and sum in the base-2 domain
+// (scale folded into the exponent's FMA, ex2.approx straight on the MUFU), and
 // rescales O in TMEM only when the maximum has moved by more than 2^8 (the stale maximum stays exact: P and
 // the sum use the same reference, the final division cancels it).
 //
@@ -27,6 +28,12 @@
 #include "host_util.h"
 
 namespace ff {
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 constexpr int TC_HD = 128, TC_PAGE = 64, TC_BM = 128, TC_BN = 128;
 constexpr int TC_STAGES = 2;
@@ -180,31 +187,47 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     const uint32_t lane_base = (uint32_t(q * 32) << 16);
+    // key range common to all live rows of the tile: [largest lower bound, smallest upper bound]
+    const int tile_hi_min = causal ? past + r0 : ctx - 1;
+    const int tile_lo_max = window > 0 ? max(0, past + r0 + real - window) : 0;
     for (int j = 0; j < ntiles && ok; ++j) {
       const int sb = j & 1; const uint32_t sph = (j >> 1) & 1;
       if (!mbar_wait(&bars.s_full[sb], sph, abort_flag, status, KID_ATTN_PREFILL, 6)) { ok = false; break; }
       tc_fence_after();
       float sv[TC_BN];
+      {
+        // all four loads are issued before the one wait
+        uint32_t r[TC_BN];
 #pragma unroll
-      for (int c = 0; c < TC_BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_x32(tmem_base + lane_base + sb * TC_BN + c, r);
+        for (int c = 0; c < TC_BN; c += 32) tmem_ld_x32(tmem_base + lane_base + sb * TC_BN + c, r + c);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(r[i]);
+        for (int i = 0; i < TC_BN; ++i) sv[i] = __uint_as_float(r[i]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
       const int k0 = (t0 + j) * TC_BN;
-      float mx = -INFINITY;
+      // sv stays in raw score units: the scale is folded into the exponent's FMA below. A tile that lies inside the key
+      // range of every live row of this query tile (most tiles of a long context) skips the mask altogether.
+      // eight independent maxima / sums: one 128-long dependent chain would leave the single warp of a scheduler waiting
+      float mx8[8];
 #pragma unroll
-      for (int i = 0; i < TC_BN; ++i) {
-        const int key = k0 + i;
-        const float t = (key >= lo && key <= hi) ? sv[i] * scale_log2 : -INFINITY;
-        sv[i] = t;
-        mx = fmaxf(mx, t);
+      for (int u = 0; u < 8; ++u) mx8[u] = -INFINITY;
+      if (k0 >= tile_lo_max && k0 + TC_BN - 1 <= tile_hi_min) {
+#pragma unroll
+        for (int i = 0; i < TC_BN; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], sv[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < TC_BN; ++i) {
+          const int key = k0 + i;
+          const float t = (key >= lo && key <= hi) ? sv[i] : -INFINITY;
+          sv[i] = t;
+          mx8[i & 7] = fmaxf(mx8[i & 7], t);
+        }
       }
+      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      mx *= scale_log2;                          // scale > 0: the maximum commutes with it (-inf stays -inf)
       // the previous P V must be done before P is overwritten or O is rescaled
       if (!mbar_wait(&bars.p_empty, (j & 1) ^ 1, abort_flag, status, KID_ATTN_PREFILL, 7)) { ok = false; break; }
       tc_fence_after();
@@ -233,19 +256,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // block kb at (row / 8) * 1024 + (row % 8) * 128 + ((c ^ (row % 8)) * 16)
       const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
       uint8_t* prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
         uint32_t pk[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = exp2f(sv[c * 8 + 2 * i] - mr), p1 = exp2f(sv[c * 8 + 2 * i + 1] - mr);
+          // 2^(s * scale - m): one FMA and one MUFU per value; a masked score is -inf and gives exactly 0
+          const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * i], scale_log2, -mr));
+          const float p1 = ex2_approx(fmaf(sv[c * 8 + 2 * i + 1], scale_log2, -mr));
           pk[i] = pack_bf16x2(p0, p1);
-          const float2 back = unpack_bf16x2(pk[i]);          // the sum uses the rounded values the MMA will see
-          l_sum += back.x + back.y;
+          ls4[i] += p0 + p1;
         }
         const int kb = c >> 3, cc = c & 7;
         *reinterpret_cast<uint4*>(prow + kb * 16384 + ((cc ^ (row & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
+      l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
       asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -115,7 +115,7 @@ def bench_attn_decode(args) -> dict:
     cl = torch.full((b,), ctx, dtype=torch.int32, device=dev)
     q = torch.randn(b, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16)
     fn = lambda: ops.attn_decode(q, kc, vc, bt, cl, hq, hkv, d, 1 / math.sqrt(d), max_ctx=ctx)
-    if args.torch:
+    if getattr(args, "torch", False):
         # the library arm: torch's fused attention over contiguous K / V of the same sizes (no paging, no packed Q)
         q4 = q[:, : hq * d].reshape(b, hq, 1, d).contiguous()
         k4 = kc.view(b, blocks_per, hkv, 64, d).permute(0, 2, 1, 3, 4).reshape(b, hkv, blocks_per * 64, d)[:, :, :ctx].contiguous()
@@ -124,7 +124,7 @@ def bench_attn_decode(args) -> dict:
     byts = 2 * b * ctx * hkv * d * 2
     r = time_op(fn, args.iters, args.warmup, Flusher(dev) if not args.no_flush else None)
     pk = peaks()
-    r.update(op="attn_decode", impl="torch_sdpa" if args.torch else "own", batch=b, ctx=ctx, hq=hq, hkv=hkv,
+    r.update(op="attn_decode", impl="torch_sdpa" if getattr(args, "torch", False) else "own", batch=b, ctx=ctx, hq=hq, hkv=hkv,
              gbs=byts / (r["us_median"] * 1e-6) / 1e9)
     r["frac_hbm"] = r["gbs"] / pk["hbm_gbs"]
     r["peaks"] = pk["source"]
@@ -143,7 +143,7 @@ def bench_attn_prefill(args) -> dict:
     qs = (torch.arange(b, dtype=torch.int32, device=dev) * ctx)
     q = torch.randn(b * ctx, (hq + 2 * hkv) * d, device=dev).to(torch.bfloat16)
     fn = lambda: ops.attn_prefill(q, kc, vc, bt, qs, ql, ql, ctx, hq, hkv, d, 1 / math.sqrt(d))
-    if args.torch:
+    if getattr(args, "torch", False):
         q4 = q[:, : hq * d].reshape(b, ctx, hq, d).transpose(1, 2).contiguous()
         k4 = kc.view(b, blocks_per, hkv, 64, d).permute(0, 2, 1, 3, 4).reshape(b, hkv, blocks_per * 64, d)[:, :, :ctx].contiguous()
         v4 = vc.view(b, blocks_per, hkv, 64, d).permute(0, 2, 1, 3, 4).reshape(b, hkv, blocks_per * 64, d)[:, :, :ctx].contiguous()
@@ -151,7 +151,7 @@ def bench_attn_prefill(args) -> dict:
     flops = 4.0 * b * hq * d * ctx * (ctx + 1) / 2
     r = time_op(fn, args.iters, args.warmup, None)
     pk = peaks()
-    r.update(op="attn_prefill", impl="torch_sdpa" if args.torch else "own", batch=b, ctx=ctx, hq=hq, hkv=hkv, tflops=flops / (r["us_median"] * 1e-6) / 1e12)
+    r.update(op="attn_prefill", impl="torch_sdpa" if getattr(args, "torch", False) else "own", batch=b, ctx=ctx, hq=hq, hkv=hkv, tflops=flops / (r["us_median"] * 1e-6) / 1e12)
     r["frac_tensor"] = r["tflops"] / pk["bf16_tflops"]
     r["peaks"] = pk["source"]
     return r
