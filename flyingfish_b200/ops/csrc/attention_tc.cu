@@ -13,7 +13,8 @@
 //                 B = V tile  [128 keys x 128 d]    exactly as the cache stores it: d contiguous = MN-major
 //                 D = O       TMEM, 128 lanes x 128 columns, lives across all KV tiles
 //
-// Warp roles: warp 0 = TMA producer (Q once, then K/V tiles through a ring of stages, block ids read from the
+// Warp roles: warp 0 = TMA producer (Q once, then K tiles through a ring of two and V tiles through a ring of three
+// stages -- a K tile is released right after its Q Kᵀ, so the loads run two tiles ahead; block ids read from the
 // block table), warp 1 = MMA issuer, warps 2-5 = softmax: thread t owns query row t (TMEM lane t), reads its S
 // row with tcgen05.ld, applies the mask where a tile needs one, keeps the running maximum and sum in the base-2 domain
 // (scale folded into the exponent's FMA, ex2.approx straight on the MUFU), and
@@ -36,17 +37,19 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 constexpr int TC_HD = 128, TC_PAGE = 64, TC_BM = 128, TC_BN = 128;
-constexpr int TC_STAGES = 2;
+constexpr int TC_KSTAGES = 2, TC_VSTAGES = 3;             // K is done with after Q Kᵀ, V only after P V: separate rings
 constexpr int TC_Q_BYTES = TC_BM * TC_HD * 2;             // 32 KiB
 constexpr int TC_P_BYTES = TC_BM * TC_BN * 2;             // 32 KiB
 constexpr int TC_KV_BYTES = TC_BN * TC_HD * 2;            // 32 KiB per operand per stage
-constexpr int TC_SMEM = TC_Q_BYTES + TC_P_BYTES + TC_STAGES * 2 * TC_KV_BYTES + 1024;
+constexpr int TC_SMEM = TC_Q_BYTES + TC_P_BYTES + (TC_KSTAGES + TC_VSTAGES) * TC_KV_BYTES + 1024;   // 225 KiB
 constexpr float TC_RESCALE_THRESHOLD = 8.0f;              // log2 units
 
 struct alignas(8) TcBars {
   uint64_t q_full;
-  uint64_t kv_full[TC_STAGES];
-  uint64_t kv_empty[TC_STAGES];
+  uint64_t k_full[TC_KSTAGES];
+  uint64_t k_empty[TC_KSTAGES];
+  uint64_t v_full[TC_VSTAGES];
+  uint64_t v_empty[TC_VSTAGES];
   uint64_t s_full[2];
   uint64_t s_empty[2];
   uint64_t p_full;
@@ -73,7 +76,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sP = smem + TC_Q_BYTES;
-  uint8_t* sKV = smem + TC_Q_BYTES + TC_P_BYTES;          // stage s: K at s*64K, V at s*64K + 32K
+  uint8_t* sKr = smem + TC_Q_BYTES + TC_P_BYTES;          // K ring, then V ring: 32 KiB tiles
+  uint8_t* sVr = sKr + TC_KSTAGES * TC_KV_BYTES;
   const int ctx = ctx_lens[b], qs = q_start[b];
   const int kvh = h / (hq / hkv);
   const int past = ctx - qlen;
@@ -88,7 +92,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
     mbar_init(&bars.q_full, 1);
-    for (int i = 0; i < TC_STAGES; ++i) { mbar_init(&bars.kv_full[i], 1); mbar_init(&bars.kv_empty[i], 1); }
+    for (int i = 0; i < TC_KSTAGES; ++i) { mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_empty[i], 1); }
+    for (int i = 0; i < TC_VSTAGES; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 4); }
     mbar_init(&bars.p_full, 1); mbar_init(&bars.p_empty, 1); mbar_init(&bars.o_done, 1);
     bars.abort_flag = 0;
@@ -113,22 +118,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       bool ok = true, bad = false;
       const int nblk = (ctx + TC_PAGE - 1) / TC_PAGE;
       for (int j = 0; j < ntiles && ok; ++j) {
-        const int s = j % TC_STAGES; const uint32_t ph = (j / TC_STAGES) & 1;
-        if (!mbar_wait(&bars.kv_empty[s], ph ^ 1, abort_flag, status, KID_ATTN_PREFILL, 1)) { ok = false; break; }
-        mbar_expect_tx(&bars.kv_full[s], 2 * TC_KV_BYTES);
-        uint8_t* sK = sKV + s * 2 * TC_KV_BYTES;
-        uint8_t* sV = sK + TC_KV_BYTES;
+        const int ks = j % TC_KSTAGES, vs = j % TC_VSTAGES;
+        int rows[2];
         for (int pg = 0; pg < 2; ++pg) {
           int page = (t0 + j) * 2 + pg;
           if (page >= nblk) page = nblk - 1;                 // past the context: any valid page, its keys are masked
           int blk = block_table[(size_t)b * max_blocks + page];
           if (blk < 0 || blk >= num_blocks) { bad = true; blk = 0; }
-          const int row = (blk * hkv + kvh) * TC_PAGE;
-          // layout of a tile: block d0 = [128 keys x 64 d] (16 KiB), then block d1; a page is 64 keys of each
-          tma_load_2d(sK + pg * 8192, &tmK, &bars.kv_full[s], 0, row);
-          tma_load_2d(sK + 16384 + pg * 8192, &tmK, &bars.kv_full[s], 64, row);
-          tma_load_2d(sV + pg * 8192, &tmV, &bars.kv_full[s], 0, row);
-          tma_load_2d(sV + 16384 + pg * 8192, &tmV, &bars.kv_full[s], 64, row);
+          rows[pg] = (blk * hkv + kvh) * TC_PAGE;
+        }
+        // layout of a tile: block d0 = [128 keys x 64 d] (16 KiB), then block d1; a page is 64 keys of each
+        if (!mbar_wait(&bars.k_empty[ks], ((j / TC_KSTAGES) & 1) ^ 1, abort_flag, status, KID_ATTN_PREFILL, 1)) { ok = false; break; }
+        mbar_expect_tx(&bars.k_full[ks], TC_KV_BYTES);
+        uint8_t* sK = sKr + ks * TC_KV_BYTES;
+        for (int pg = 0; pg < 2; ++pg) {
+          tma_load_2d(sK + pg * 8192, &tmK, &bars.k_full[ks], 0, rows[pg]);
+          tma_load_2d(sK + 16384 + pg * 8192, &tmK, &bars.k_full[ks], 64, rows[pg]);
+        }
+        if (!mbar_wait(&bars.v_empty[vs], ((j / TC_VSTAGES) & 1) ^ 1, abort_flag, status, KID_ATTN_PREFILL, 10)) { ok = false; break; }
+        mbar_expect_tx(&bars.v_full[vs], TC_KV_BYTES);
+        uint8_t* sV = sVr + vs * TC_KV_BYTES;
+        for (int pg = 0; pg < 2; ++pg) {
+          tma_load_2d(sV + pg * 8192, &tmV, &bars.v_full[vs], 0, rows[pg]);
+          tma_load_2d(sV + 16384 + pg * 8192, &tmV, &bars.v_full[vs], 64, rows[pg]);
         }
       }
       if (bad) set_status(status, KID_ATTN_PREFILL, FF_ERR_BOUNDS, b, r0 / TC_BM);
@@ -141,12 +153,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       bool ok = mbar_wait(&bars.q_full, 0, abort_flag, status, KID_ATTN_PREFILL, 2);
       auto issue_s = [&](int j) -> bool {
-        const int s = j % TC_STAGES; const uint32_t ph = (j / TC_STAGES) & 1;
+        const int ks = j % TC_KSTAGES; const uint32_t ph = (j / TC_KSTAGES) & 1;
         const int sb = j & 1; const uint32_t sph = (j >> 1) & 1;
-        if (!mbar_wait(&bars.kv_full[s], ph, abort_flag, status, KID_ATTN_PREFILL, 3)) return false;
+        if (!mbar_wait(&bars.k_full[ks], ph, abort_flag, status, KID_ATTN_PREFILL, 3)) return false;
         if (!mbar_wait(&bars.s_empty[sb], sph ^ 1, abort_flag, status, KID_ATTN_PREFILL, 4)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sKV + s * 2 * TC_KV_BYTES);
+        const uint32_t k_addr = smem_u32(sKr + ks * TC_KV_BYTES);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
@@ -154,15 +166,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                    idesc_s, k != 0);
         }
         umma_commit(&bars.s_full[sb]);
+        umma_commit(&bars.k_empty[ks]);            // the K tile is free as soon as this product has read it
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < ntiles && ok; ++j) {
         if (j + 1 < ntiles) { ok = issue_s(j + 1); if (!ok) break; }
         if (!mbar_wait(&bars.p_full, j & 1, abort_flag, status, KID_ATTN_PREFILL, 5)) { ok = false; break; }
+        const int vs = j % TC_VSTAGES;
+        if (!mbar_wait(&bars.v_full[vs], (j / TC_VSTAGES) & 1, abort_flag, status, KID_ATTN_PREFILL, 11)) { ok = false; break; }
         tc_fence_after();
-        const int s = j % TC_STAGES;
-        const uint32_t v_addr = smem_u32(sKV + s * 2 * TC_KV_BYTES + TC_KV_BYTES);
+        const uint32_t v_addr = smem_u32(sVr + vs * TC_KV_BYTES);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           // P: 16 keys of k-step k sit in 64-key block k/4 at byte (k%4)*32 of each row; V: 16 key rows = 2 KiB
@@ -171,7 +185,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           umma_f16(tmem_o, da, db, idesc_o, (j > 0) || (k != 0));
         }
         umma_commit(&bars.p_empty);
-        umma_commit(&bars.kv_empty[s]);
+        umma_commit(&bars.v_empty[vs]);
       }
       if (ok) umma_commit(&bars.o_done);
     }
