@@ -15,7 +15,8 @@
 //
 // Warp roles: warp 0 = TMA producer (Q once, then K tiles through a ring of two and V tiles through a ring of three
 // stages -- a K tile is released right after its Q Kᵀ, so the loads run two tiles ahead; block ids read from the
-// block table), warp 1 = MMA issuer, warps 2-5 = softmax: thread t owns query row t (TMEM lane t), reads its S
+// block table), warp 1 = MMA issuer, warps 2-9 = softmax: two threads share query row t (TMEM lane t) and split its
+// key columns in halves (two warps per lane quadrant, so each scheduler has two warps to interleave); a thread reads its S
 // row with tcgen05.ld, applies the mask where a tile needs one, keeps the running maximum and sum in the base-2 domain
 // (scale folded into the exponent's FMA, ex2.approx straight on the MUFU), and
 // rescales O in TMEM only when the maximum has moved by more than 2^8 (the stale maximum stays exact: P and
@@ -57,9 +58,10 @@ struct alignas(8) TcBars {
   uint64_t o_done;
   uint32_t tmem_base;
   int abort_flag;
+  float xmax[2][TC_BM];      // row maxima (and, at the end, row sums) exchanged between the two warps of a quadrant
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const int* __restrict__ block_table,
                        const int* __restrict__ q_start, const int* __restrict__ q_lens,
@@ -94,7 +96,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     mbar_init(&bars.q_full, 1);
     for (int i = 0; i < TC_KSTAGES; ++i) { mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_empty[i], 1); }
     for (int i = 0; i < TC_VSTAGES; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 4); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 8); }
     mbar_init(&bars.p_full, 1); mbar_init(&bars.p_empty, 1); mbar_init(&bars.o_done, 1);
     bars.abort_flag = 0;
     mbar_fence_init();
@@ -190,8 +192,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (ok) umma_commit(&bars.o_done);
     }
   } else {
-    // ================================ softmax warps 2..5 ================================
+    // ================================ softmax warps 2..9 ================================
+    // Two warps per 32-lane quadrant of tensor memory (a warp may only touch the lanes of quadrant warp % 4): the pair
+    // shares the rows of its quadrant and splits a tile's 128 key columns (and O's 128 columns, when it is rescaled)
+    // in halves, so every scheduler has two warps to interleave. Row maxima cross the pair through shared memory.
     const int q = warp & 3;
+    const int hf = (warp - 2) >> 2;               // which 64-column half this warp owns
     const int row = q * 32 + lane;                // query row of the tile = TMEM lane
     const int e = (warp - 2) * 32 + lane;
     const bool live = row < real;
@@ -204,44 +210,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     // key range common to all live rows of the tile: [largest lower bound, smallest upper bound]
     const int tile_hi_min = causal ? past + r0 : ctx - 1;
     const int tile_lo_max = window > 0 ? max(0, past + r0 + real - window) : 0;
+    constexpr int HB = TC_BN / 2;                 // columns per warp
     for (int j = 0; j < ntiles && ok; ++j) {
       const int sb = j & 1; const uint32_t sph = (j >> 1) & 1;
       if (!mbar_wait(&bars.s_full[sb], sph, abort_flag, status, KID_ATTN_PREFILL, 6)) { ok = false; break; }
       tc_fence_after();
-      float sv[TC_BN];
+      float sv[HB];
       {
-        // all four loads are issued before the one wait
-        uint32_t r[TC_BN];
+        uint32_t r[HB];
 #pragma unroll
-        for (int c = 0; c < TC_BN; c += 32) tmem_ld_x32(tmem_base + lane_base + sb * TC_BN + c, r + c);
+        for (int c = 0; c < HB; c += 32) tmem_ld_x32(tmem_base + lane_base + sb * TC_BN + hf * HB + c, r + c);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < TC_BN; ++i) sv[i] = __uint_as_float(r[i]);
+        for (int i = 0; i < HB; ++i) sv[i] = __uint_as_float(r[i]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
-      const int k0 = (t0 + j) * TC_BN;
+      const int k0 = (t0 + j) * TC_BN + hf * HB;
       // sv stays in raw score units: the scale is folded into the exponent's FMA below. A tile that lies inside the key
       // range of every live row of this query tile (most tiles of a long context) skips the mask altogether.
-      // eight independent maxima / sums: one 128-long dependent chain would leave the single warp of a scheduler waiting
-      float mx8[8];
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if ((t0 + j) * TC_BN >= tile_lo_max && (t0 + j) * TC_BN + TC_BN - 1 <= tile_hi_min) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) mx8[u] = -INFINITY;
-      if (k0 >= tile_lo_max && k0 + TC_BN - 1 <= tile_hi_min) {
-#pragma unroll
-        for (int i = 0; i < TC_BN; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], sv[i]);
+        for (int i = 0; i < HB; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < TC_BN; ++i) {
+        for (int i = 0; i < HB; ++i) {
           const int key = k0 + i;
           const float t = (key >= lo && key <= hi) ? sv[i] : -INFINITY;
           sv[i] = t;
-          mx8[i & 7] = fmaxf(mx8[i & 7], t);
+          mx4[i & 3] = fmaxf(mx4[i & 3], t);
         }
       }
-      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-      mx *= scale_log2;                          // scale > 0: the maximum commutes with it (-inf stays -inf)
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 commutes with the maximum
+      // the row's maximum over both halves: through shared memory, one 64-thread barrier per quadrant pair
+      bars.xmax[hf][row] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+      mx = fmaxf(mx, bars.xmax[hf ^ 1][row]);
       // the previous P V must be done before P is overwritten or O is rescaled
       if (!mbar_wait(&bars.p_empty, (j & 1) ^ 1, abort_flag, status, KID_ATTN_PREFILL, 7)) { ok = false; break; }
       tc_fence_after();
@@ -253,55 +259,58 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         need = j > 0;                              // O holds nothing before the first P V
       }
       if (__any_sync(0xffffffffu, need)) {
-        // rescale this warp's 32 lanes of O (lanes that did not move keep alpha = 1)
+        // rescale this warp's half of the 32 lanes of O (lanes that did not move keep alpha = 1)
 #pragma unroll
-        for (int c = 0; c < TC_HD; c += 16) {
+        for (int c = 0; c < TC_HD / 2; c += 16) {
           uint32_t r[16];
-          tmem_ld_x16(tmem_o + lane_base + c, r);
+          tmem_ld_x16(tmem_o + lane_base + hf * (TC_HD / 2) + c, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_x16(tmem_o + lane_base + c, r);
+          tmem_st_x16(tmem_o + lane_base + hf * (TC_HD / 2) + c, r);
         }
         tmem_st_wait();
       }
       l_sum *= alpha;
-      // P = 2^(t - m_ref), BF16, into 128-byte-swizzled K-major shared memory: row `row`, 16-byte chunk c of 64-key
-      // block kb at (row / 8) * 1024 + (row % 8) * 128 + ((c ^ (row % 8)) * 16)
+      // P = 2^(s * scale - m_ref), BF16, into 128-byte-swizzled K-major shared memory: row `row`, 16-byte chunk c of 64-key
+      // block kb (= this warp's half) at (row / 8) * 1024 + (row % 8) * 128 + ((c ^ (row % 8)) * 16)
       const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
-      uint8_t* prow = sP + (row >> 3) * 1024 + (row & 7) * 128;
+      uint8_t* prow = sP + hf * 16384 + (row >> 3) * 1024 + (row & 7) * 128;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < 8; ++c) {
         uint32_t pk[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          // 2^(s * scale - m): one FMA and one MUFU per value; a masked score is -inf and gives exactly 0
+          // one FMA and one MUFU per value; a masked score is -inf and gives exactly 0
           const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * i], scale_log2, -mr));
           const float p1 = ex2_approx(fmaf(sv[c * 8 + 2 * i + 1], scale_log2, -mr));
           pk[i] = pack_bf16x2(p0, p1);
           ls4[i] += p0 + p1;
         }
-        const int kb = c >> 3, cc = c & 7;
-        *reinterpret_cast<uint4*>(prow + kb * 16384 + ((cc ^ (row & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (e == 0) mbar_arrive(&bars.p_full);
     }
     if (ok) ok = mbar_wait(&bars.o_done, 0, abort_flag, status, KID_ATTN_PREFILL, 8);
     if (ok) {
       tc_fence_after();
+      // the row's sum over both halves
+      bars.xmax[hf][row] = l_sum;
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+      l_sum += bars.xmax[hf ^ 1][row];
       // learnable soft-max: one extra logit per head that enters the denominator only
       if (sinks != nullptr) l_sum += (m_ref == -INFINITY) ? 1.f : exp2f(sinks[h] * 1.4426950408889634f - m_ref);
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-      __nv_bfloat16* orow = out + (size_t)(qs + r0 + row) * ldo + (size_t)h * TC_HD;
+      __nv_bfloat16* orow = out + (size_t)(qs + r0 + row) * ldo + (size_t)h * TC_HD + hf * (TC_HD / 2);
 #pragma unroll
-      for (int c = 0; c < TC_HD; c += 16) {
+      for (int c = 0; c < TC_HD / 2; c += 16) {
         uint32_t r[16];
-        tmem_ld_x16(tmem_o + lane_base + c, r);
+        tmem_ld_x16(tmem_o + lane_base + hf * (TC_HD / 2) + c, r);
         tmem_ld_wait();
         if (live) {
           uint4 o0, o1;
@@ -349,7 +358,7 @@ FF_EXPORT int ff_attn_prefill_tc(const void* q, const void* kcache, const void* 
   if (int r = opt_in_smem(attn_prefill_tc_kernel, TC_SMEM)) return r;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid((max_q_len + TC_BM - 1) / TC_BM, hq, batch);
-  attn_prefill_tc_kernel<<<grid, 192, TC_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
+  attn_prefill_tc_kernel<<<grid, 320, TC_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
                                                     (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
                                                     window < 0 ? 0 : window, window < 0 ? 0 : 1, status, sinks);
   return launch_result();
