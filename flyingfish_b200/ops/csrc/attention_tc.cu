@@ -38,11 +38,10 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 constexpr int TC_HD = 128, TC_PAGE = 64, TC_BM = 128, TC_BN = 128;
-constexpr int TC_KSTAGES = 2, TC_VSTAGES = 3;             // K is done with after Q Kᵀ, V only after P V: separate rings
+constexpr int TC_KSTAGES = 3, TC_VSTAGES = 3;             // K is done with after Q Kᵀ, V only after P V: separate rings
 constexpr int TC_Q_BYTES = TC_BM * TC_HD * 2;             // 32 KiB
-constexpr int TC_P_BYTES = TC_BM * TC_BN * 2;             // 32 KiB
 constexpr int TC_KV_BYTES = TC_BN * TC_HD * 2;            // 32 KiB per operand per stage
-constexpr int TC_SMEM = TC_Q_BYTES + TC_P_BYTES + (TC_KSTAGES + TC_VSTAGES) * TC_KV_BYTES + 1024;   // 225 KiB
+constexpr int TC_SMEM = TC_Q_BYTES + (TC_KSTAGES + TC_VSTAGES) * TC_KV_BYTES + 1024;   // 225 KiB
 constexpr float TC_RESCALE_THRESHOLD = 8.0f;              // log2 units
 
 struct alignas(8) TcBars {
@@ -77,8 +76,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __shared__ TcBars bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sP = smem + TC_Q_BYTES;
-  uint8_t* sKr = smem + TC_Q_BYTES + TC_P_BYTES;          // K ring, then V ring: 32 KiB tiles
+  uint8_t* sKr = smem + TC_Q_BYTES;                       // K ring, then V ring: 32 KiB tiles
   uint8_t* sVr = sKr + TC_KSTAGES * TC_KV_BYTES;
   const int ctx = ctx_lens[b], qs = q_start[b];
   const int kvh = h / (hq / hkv);
@@ -107,6 +105,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = bars.tmem_base;
   const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_p = tmem_base + 384;       // P: 128 keys as 64 columns of packed BF16 pairs
   volatile int* abort_flag = &bars.abort_flag;
 
   if (warp == 0) {
@@ -152,7 +151,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(1, 1, 0, 0, TC_BM, TC_BN);      // Q (K-major) x K (K-major)
       const uint32_t idesc_o = umma_idesc(1, 1, 0, 1, TC_BM, TC_HD);      // P (K-major) x V (MN-major)
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      const uint32_t q_addr = smem_u32(sQ);
       bool ok = mbar_wait(&bars.q_full, 0, abort_flag, status, KID_ATTN_PREFILL, 2);
       auto issue_s = [&](int j) -> bool {
         const int ks = j % TC_KSTAGES; const uint32_t ph = (j / TC_KSTAGES) & 1;
@@ -181,10 +180,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const uint32_t v_addr = smem_u32(sVr + vs * TC_KV_BYTES);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          // P: 16 keys of k-step k sit in 64-key block k/4 at byte (k%4)*32 of each row; V: 16 key rows = 2 KiB
-          const uint64_t da = umma_desc_sw128(p_addr + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          // P: the 16 keys of k-step k are 8 columns of the P region of tensor memory; V: 16 key rows = 2 KiB
           const uint64_t db = umma_desc_sw128(v_addr + (k >> 2) * 8192 + (k & 3) * 2048, 16384, 1024);
-          umma_f16(tmem_o, da, db, idesc_o, (j > 0) || (k != 0));
+          umma_f16_ts(tmem_o, tmem_p + k * 8, db, idesc_o, (j > 0) || (k != 0));
         }
         umma_commit(&bars.p_empty);
         umma_commit(&bars.v_empty[vs]);
@@ -275,23 +273,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // P = 2^(s * scale - m_ref), BF16, into 128-byte-swizzled K-major shared memory: row `row`, 16-byte chunk c of 64-key
       // block kb (= this warp's half) at (row / 8) * 1024 + (row % 8) * 128 + ((c ^ (row % 8)) * 16)
       const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
-      uint8_t* prow = sP + hf * 16384 + (row >> 3) * 1024 + (row & 7) * 128;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[HB / 2];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          // one FMA and one MUFU per value; a masked score is -inf and gives exactly 0
-          const float p0 = ex2_approx(fmaf(sv[c * 8 + 2 * i], scale_log2, -mr));
-          const float p1 = ex2_approx(fmaf(sv[c * 8 + 2 * i + 1], scale_log2, -mr));
-          pk[i] = pack_bf16x2(p0, p1);
-          ls4[i] += p0 + p1;
-        }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      for (int i = 0; i < HB / 2; ++i) {
+        // one FMA and one MUFU per value; a masked score is -inf and gives exactly 0
+        const float p0 = ex2_approx(fmaf(sv[2 * i], scale_log2, -mr));
+        const float p1 = ex2_approx(fmaf(sv[2 * i + 1], scale_log2, -mr));
+        pk[i] = pack_bf16x2(p0, p1);
+        ls4[i & 3] += p0 + p1;
       }
+      // P stays in tensor memory: row = lane, two BF16 keys per 32-bit column, this warp's 64 keys = 32 columns; the second
+      // product reads it from there as its A operand (no trip through shared memory, whose bandwidth the two products'
+      // operand reads already use up)
+      tmem_st_x16(tmem_p + lane_base + hf * (HB / 2), pk);
+      tmem_st_x16(tmem_p + lane_base + hf * (HB / 2) + 16, pk + 16);
+      tmem_st_wait();
       l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-      fence_proxy_async_smem();
       tc_fence_before();
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (e == 0) mbar_arrive(&bars.p_full);
