@@ -160,6 +160,154 @@ sigmoid_gate_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __
 }
 
 // ------------------------------------------------------------------------------------------------
+// group norm over channels-last activations [n, positions, C] and dense 3-D convolution as im2col + GEMM
+// (kernels/vision_ops.cu group-norm / im2col families of the reference, there channels-first)
+// ------------------------------------------------------------------------------------------------
+constexpr int GN_CHUNKS = 64;
+
+// partial sums of one (sample, group, chunk of positions): part[((n * G + g) * GN_CHUNKS + chunk) * 2 + {0, 1}]
+__global__ void __launch_bounds__(256)
+group_norm_stats_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, int positions, int C, int G) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float s_a[8], s_b[8];
+  const int chunk = blockIdx.x, g = blockIdx.y, n = blockIdx.z;
+  const int cg = C / G;
+  const int per = (positions + GN_CHUNKS - 1) / GN_CHUNKS;
+  const int p0 = chunk * per, p1 = min(positions, p0 + per);
+  const __nv_bfloat16* base = x + ((size_t)n * positions) * C + (size_t)g * cg;
+  float sum = 0.f, sq = 0.f;
+  const long long total = (long long)max(p1 - p0, 0) * cg;
+  for (long long i = threadIdx.x; i < total; i += 256) {
+    const int p = p0 + (int)(i / cg), c = (int)(i % cg);
+    const float v = __bfloat162float(base[(size_t)p * C + c]);
+    sum += v; sq = fmaf(v, v, sq);
+  }
+  sum = warp_sum(sum); sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) { s_a[threadIdx.x >> 5] = sum; s_b[threadIdx.x >> 5] = sq; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int w = 0; w < 8; ++w) { a += s_a[w]; b += s_b[w]; }
+    float* dst = part + (((size_t)n * G + g) * GN_CHUNKS + chunk) * 2;
+    dst[0] = a; dst[1] = b;
+  }
+}
+
+// y = act((x - mean) * rstd * w + b); the chunk partials are summed in chunk order by every thread that needs them
+__global__ void __launch_bounds__(256)
+group_norm_apply_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ part, const float* __restrict__ w,
+                        const float* __restrict__ b, __nv_bfloat16* __restrict__ y, int positions, int C, int G, float eps,
+                        int act, long long total8) {
+  pdl_trigger();
+  pdl_wait();
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (gid >= total8) return;
+  const int cv = C >> 3;
+  const int c0 = (int)(gid % cv) * 8;
+  const long long row = gid / cv;
+  const int n = (int)(row / positions);
+  const int cg = C / G;
+  uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)row * C + c0);
+  uint32_t* vp = reinterpret_cast<uint32_t*>(&v);
+  float mean = 0.f, rstd = 0.f;
+  int cur = -1;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 f = unpack_bf16x2(vp[j]);
+    float o[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = c0 + 2 * j + h;
+      const int g = c / cg;
+      if (g != cur) {
+        const float* src = part + ((size_t)n * G + g) * GN_CHUNKS * 2;
+        float a = 0.f, q = 0.f;
+        for (int k = 0; k < GN_CHUNKS; ++k) { a += src[2 * k]; q += src[2 * k + 1]; }
+        const float cnt = (float)positions * (float)cg;
+        mean = a / cnt;
+        rstd = rsqrtf(fmaxf(q / cnt - mean * mean, 0.f) + eps);
+        cur = g;
+      }
+      const float xv = h == 0 ? f.x : f.y;
+      o[h] = act_apply(fmaf((xv - mean) * rstd, w[c], b ? b[c] : 0.f), act);
+    }
+    vp[j] = pack_bf16x2(o[0], o[1]);
+  }
+  *reinterpret_cast<uint4*>(y + (size_t)row * C + c0) = v;
+}
+
+// cols[((n, d, h, w), tap, c)] = x[n, d + kd - pad, h + kh - pad, w + kw - pad, c] (zero outside), taps in (kd, kh, kw)
+// order; one thread per (output position, tap, 8 channels)
+__global__ void __launch_bounds__(256)
+im2col3d_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ cols, int D, int H, int W, int C, int k,
+                int pad, long long total8) {
+  pdl_trigger();
+  pdl_wait();
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (gid >= total8) return;
+  const int cv = C >> 3, taps = k * k * k;
+  const int c0 = (int)(gid % cv) * 8;
+  long long r = gid / cv;
+  const int tap = (int)(r % taps); r /= taps;
+  const int w = (int)(r % W); r /= W;
+  const int h = (int)(r % H); r /= H;
+  const int d = (int)(r % D);
+  const long long n = r / D;
+  const int kd = tap / (k * k), kh = (tap / k) % k, kw = tap % k;
+  const int sd = d + kd - pad, sh = h + kh - pad, sw = w + kw - pad;
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (sd >= 0 && sd < D && sh >= 0 && sh < H && sw >= 0 && sw < W)
+    v = *reinterpret_cast<const uint4*>(x + ((((size_t)n * D + sd) * H + sh) * W + sw) * C + c0);
+  *reinterpret_cast<uint4*>(cols + (size_t)gid * 8) = v;
+}
+
+// Neighbourhood attention over a 2-D grid: the query at (i, j) attends to the ks x ks keys of the window centred on it,
+// shifted inwards at the borders so that it always holds ks x ks positions. q, k, v, out: [n, H, W, heads, d] BF16.
+// One warp per (query, head): lanes split the head dimension (d <= 256, d % 32 == 0), online soft-max over the window.
+__global__ void __launch_bounds__(256)
+neighborhood_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                         const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out, int H, int W, int heads, int d,
+                         int ks, float scale_log2, long long total) {
+  pdl_trigger();
+  pdl_wait();
+  const long long wid = ((long long)blockIdx.x * 256 + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= total) return;
+  const int hd = (int)(wid % heads);
+  long long r = wid / heads;
+  const int j = (int)(r % W); r /= W;
+  const int i = (int)(r % H);
+  const long long n = r / H;
+  const int per = d >> 5;                              // dims per lane (1..8)
+  const int i0 = min(max(i - ks / 2, 0), H - ks), j0 = min(max(j - ks / 2, 0), W - ks);
+  const size_t stride = (size_t)heads * d;
+  const __nv_bfloat16* qp = q + (((size_t)n * H + i) * W + j) * stride + (size_t)hd * d + lane * per;
+  float qv[8], acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { qv[e] = e < per ? __bfloat162float(qp[e]) : 0.f; acc[e] = 0.f; }
+  float m = -INFINITY, l = 0.f;
+  for (int a = 0; a < ks; ++a)
+    for (int b = 0; b < ks; ++b) {
+      const size_t off = (((size_t)n * H + i0 + a) * W + j0 + b) * stride + (size_t)hd * d + lane * per;
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) if (e < per) dot = fmaf(qv[e], __bfloat162float(k[off + e]), dot);
+      dot = warp_sum(dot) * scale_log2;
+      const float mn = fmaxf(m, dot);
+      const float corr = exp2f(m - mn), p = exp2f(dot - mn);
+      l = l * corr + p;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) if (e < per) acc[e] = fmaf(p, __bfloat162float(v[off + e]), acc[e] * corr);
+      m = mn;
+    }
+  const float inv = 1.f / l;
+  __nv_bfloat16* op = out + (((size_t)n * H + i) * W + j) * stride + (size_t)hd * d + lane * per;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) if (e < per) op[e] = __float2bfloat16(acc[e] * inv);
+}
+
+// ------------------------------------------------------------------------------------------------
 // voxel hash table. key = (b:16 | x:16 | y:16 | z:16) of non-negative coordinates < 65536; slot value =
 // lowest row index with that key. Empty key = all ones.
 // ------------------------------------------------------------------------------------------------
@@ -358,6 +506,38 @@ FF_EXPORT int ff_sigmoid_gate(const void* a, const void* gate, void* y, long lon
   if (int lr = launch_pdl(sigmoid_gate_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, 0,
                           (const __nv_bfloat16*)a, (const __nv_bfloat16*)gate, (__nv_bfloat16*)y, rows, n, lda, ldg, ldy))
     return lr;
+  return launch_result();
+}
+
+// x, y: [n, positions, C] BF16; w, b: [C] FP32; part: FP32 scratch of n * G * 64 * 2 floats. act as in ff_bias_act.
+FF_EXPORT int ff_group_norm(const void* x, const float* w, const float* b, void* y, float* part, int n, int positions, int C,
+                            int G, float eps, int act, cudaStream_t s) {
+  if (n <= 0 || positions <= 0 || C <= 0 || G <= 0 || C % G || C % 8 || act < 0 || act > 5) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(group_norm_stats_kernel, dim3(GN_CHUNKS, G, n), dim3(256), 0, s, 0, (const __nv_bfloat16*)x, part,
+                          positions, C, G)) return lr;
+  const long long total8 = (long long)n * positions * (C / 8);
+  if (int lr = launch_pdl(group_norm_apply_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, s, 0,
+                          (const __nv_bfloat16*)x, (const float*)part, w, b, (__nv_bfloat16*)y, positions, C, G, eps, act,
+                          total8)) return lr;
+  return launch_result();
+}
+
+FF_EXPORT int ff_neighborhood_attn(const void* q, const void* k, const void* v, void* out, int n, int H, int W, int heads,
+                                   int d, int ks, float scale, cudaStream_t s) {
+  if (n <= 0 || H <= 0 || W <= 0 || heads <= 0 || d <= 0 || d % 32 || d > 256 || ks < 1 || ks % 2 == 0 || ks > H || ks > W || !(scale > 0.f))
+    return FF_HOST_BAD_SHAPE;
+  const long long total = (long long)n * H * W * heads;
+  if (int lr = launch_pdl(neighborhood_attn_kernel, dim3((unsigned)((total * 32 + 255) / 256)), dim3(256), 0, s, 0,
+                          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, H, W,
+                          heads, d, ks, scale * 1.4426950408889634f, total)) return lr;
+  return launch_result();
+}
+
+FF_EXPORT int ff_im2col3d(const void* x, void* cols, int n, int D, int H, int W, int C, int k, int pad, cudaStream_t s) {
+  if (n <= 0 || D <= 0 || H <= 0 || W <= 0 || C <= 0 || C % 8 || k < 1 || k > 7 || pad < 0) return FF_HOST_BAD_SHAPE;
+  const long long total8 = (long long)n * D * H * W * k * k * k * (C / 8);
+  if (int lr = launch_pdl(im2col3d_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, s, 0,
+                          (const __nv_bfloat16*)x, (__nv_bfloat16*)cols, D, H, W, C, k, pad, total8)) return lr;
   return launch_result();
 }
 

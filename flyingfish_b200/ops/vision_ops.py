@@ -84,6 +84,76 @@ def sigmoid_gate(a: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def group_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, groups: int, eps: float = 1e-5, act: str = "none") -> torch.Tensor:
+    """Group normalisation of channels-last activations ``x`` [n, positions, C] (BF16): statistics over the positions and
+    the ``C / groups`` channels of a group, per sample; then ``act(y * w + b)``. ``w`` / ``b``: [C] FP32."""
+    n, positions, c = x.shape
+    if not x.is_cuda:
+        xf = x.float().reshape(n, positions, groups, c // groups)
+        mean = xf.mean(dim=(1, 3), keepdim=True)
+        var = ((xf - mean) ** 2).mean(dim=(1, 3), keepdim=True)
+        y = ((xf - mean) * torch.rsqrt(var + eps)).reshape(n, positions, c) * w.float() + (b.float() if b is not None else 0.0)
+        return act_ref(y, act).to(x.dtype)
+    _require(x.dtype == BF16 and x.is_contiguous() and w.dtype == torch.float32 and c % groups == 0 and c % 8 == 0, "group_norm: layout")
+    y = torch.empty_like(x)
+    part = torch.empty(n * groups * 64 * 2, dtype=torch.float32, device=x.device)
+    rc = kernels().ff_group_norm(ptr(x), ptr(w), ptr(b), ptr(y), ptr(part), n, positions, c, groups, c_float(eps), ACTS[act], stream_ptr())
+    check(rc, "ff_group_norm")
+    _count(2)
+    return y
+
+
+def conv3d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, act: str = "none") -> torch.Tensor:
+    """Dense 3-D convolution, stride 1, "same" padding, channels-last: ``x`` [n, D, H, W, C] BF16, ``weight``
+    [C_out, C, k, k, k] -> [n, D, H, W, C_out]. CUDA: the taps are gathered into rows (im2col) and one tensor-core GEMM
+    against the weight in (tap, channel) order does the rest; the bias and activation follow in one pass."""
+    n, d, h, w_, c = x.shape
+    co, ci, k = weight.shape[0], weight.shape[1], weight.shape[2]
+    _require(ci == c and weight.shape[3] == k and weight.shape[4] == k and k % 2 == 1, "conv3d: weight [C_out, C, k, k, k], odd k")
+    pad = k // 2
+    if not x.is_cuda:
+        y = torch.nn.functional.conv3d(x.float().permute(0, 4, 1, 2, 3), weight.float(), None, padding=pad).permute(0, 2, 3, 4, 1)
+        y = _r(y)
+        if bias is not None or act != "none":
+            y = act_ref(_r(y + (bias.float() if bias is not None else 0.0)), act)
+        return y.to(x.dtype)
+    _require(x.dtype == BF16 and x.is_contiguous() and c % 8 == 0, "conv3d: bf16 channels-last input, C % 8 == 0")
+    rows = n * d * h * w_
+    cols = torch.empty(rows, k * k * k * c, dtype=BF16, device=x.device)
+    rc = kernels().ff_im2col3d(ptr(x), ptr(cols), n, d, h, w_, c, k, pad, stream_ptr())
+    check(rc, "ff_im2col3d")
+    _count()
+    wmat = weight.permute(0, 2, 3, 4, 1).reshape(co, k * k * k * c).to(BF16).contiguous()
+    y = linear_bias_act(cols, wmat, bias.to(BF16).contiguous() if bias is not None else None, act)
+    return y.reshape(n, d, h, w_, co)
+
+
+def neighborhood_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: int) -> torch.Tensor:
+    """2-D neighbourhood attention: ``q``, ``k``, ``v`` [n, H, W, heads, d] BF16; the query at (i, j) attends to the
+    ``kernel x kernel`` keys of the window centred on it, shifted inwards at the borders (always ``kernel ** 2`` keys)."""
+    n, h, w, heads, d = q.shape
+    _require(kernel % 2 == 1 and kernel <= h and kernel <= w, "neighborhood_attention: odd window inside the grid")
+    if not q.is_cuda:
+        qf, kf, vf = q.float(), k.float(), v.float()
+        out = torch.empty_like(qf)
+        i0 = (torch.arange(h) - kernel // 2).clamp(0, h - kernel)
+        j0 = (torch.arange(w) - kernel // 2).clamp(0, w - kernel)
+        for i in range(h):
+            for j in range(w):
+                kk = kf[:, i0[i]: i0[i] + kernel, j0[j]: j0[j] + kernel].reshape(n, kernel * kernel, heads, d)
+                vv = vf[:, i0[i]: i0[i] + kernel, j0[j]: j0[j] + kernel].reshape(n, kernel * kernel, heads, d)
+                sc = torch.einsum("nhd,nkhd->nhk", qf[:, i, j], kk) / math.sqrt(d)
+                out[:, i, j] = torch.einsum("nhk,nkhd->nhd", torch.softmax(sc, -1), vv)
+        return out.to(q.dtype)
+    _require(q.dtype == BF16 and q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and d % 32 == 0 and d <= 256,
+             "neighborhood_attention: contiguous bf16, head width a multiple of 32 up to 256")
+    out = torch.empty_like(q)
+    rc = kernels().ff_neighborhood_attn(ptr(q), ptr(k), ptr(v), ptr(out), n, h, w, heads, d, kernel, c_float(1.0 / math.sqrt(d)), stream_ptr())
+    check(rc, "ff_neighborhood_attn")
+    _count()
+    return out
+
+
 def linear_bias_act(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, act: str = "none") -> torch.Tensor:
     y = linear(x, w)
     if bias is None and act == "none":

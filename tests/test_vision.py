@@ -267,3 +267,65 @@ def test_multimodal_gpu():
     assert (la - lb).abs().max() > 1e-3
     from flyingfish_b200 import ops
     ops.check_status()
+
+
+def test_group_norm_and_conv3d_oracles():
+    from flyingfish_b200.ops import vision_ops
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(2, 50, 32, generator=g).to(torch.bfloat16)
+    w, b = 1 + 0.1 * torch.randn(32, generator=g), 0.1 * torch.randn(32, generator=g)
+    got = vision_ops.group_norm(x, w, b, groups=4, act="silu").float()
+    ref = torch.nn.functional.silu(torch.nn.functional.group_norm(x.float().transpose(1, 2), 4, w, b, 1e-5).transpose(1, 2))
+    assert (got - ref).abs().max() < 3e-2
+    v = torch.randn(1, 5, 6, 7, 16, generator=g).to(torch.bfloat16)
+    wt = 0.1 * torch.randn(24, 16, 3, 3, 3, generator=g)
+    bias = 0.1 * torch.randn(24, generator=g)
+    got = vision_ops.conv3d(v, wt, bias, act="relu").float()
+    ref = torch.relu(torch.nn.functional.conv3d(v.float().permute(0, 4, 1, 2, 3), wt, bias, padding=1).permute(0, 2, 3, 4, 1))
+    assert got.shape == (1, 5, 6, 7, 24) and (got - ref).abs().max() < 5e-2
+
+
+@pytest.mark.gpu
+def test_group_norm_and_conv3d_kernels(cuda):
+    from flyingfish_b200.ops import vision_ops
+    g = torch.Generator().manual_seed(42)
+    for n, positions, c, groups in ((2, 777, 64, 8), (1, 4096, 128, 32), (3, 10, 16, 2)):
+        x = torch.randn(n, positions, c, generator=g).to(torch.bfloat16)
+        w, b = 1 + 0.1 * torch.randn(c, generator=g), 0.1 * torch.randn(c, generator=g)
+        for act in ("none", "silu"):
+            want = vision_ops.group_norm(x, w, b, groups, act=act).float()
+            got = vision_ops.group_norm(x.to(cuda), w.to(cuda), b.to(cuda), groups, act=act).float().cpu()
+            assert (got - want).abs().max() < 4e-2, (n, positions, c, groups, act)
+    v = torch.randn(2, 6, 7, 9, 32, generator=g).to(torch.bfloat16)
+    wt = 0.05 * torch.randn(40, 32, 3, 3, 3, generator=g)
+    bias = 0.1 * torch.randn(40, generator=g)
+    want = vision_ops.conv3d(v, wt, bias, act="silu").float()
+    got = vision_ops.conv3d(v.to(cuda), wt.to(cuda), bias.to(cuda), act="silu").float().cpu()
+    assert got.shape == want.shape and (got - want).abs().max() < 6e-2
+
+
+def test_neighborhood_attention_window_rule():
+    from flyingfish_b200.ops import vision_ops
+    g = torch.Generator().manual_seed(43)
+    q, k, v = (torch.randn(1, 5, 6, 2, 32, generator=g).to(torch.bfloat16) for _ in range(3))
+    out = vision_ops.neighborhood_attention(q, k, v, 3).float()
+    # corner query: the window is shifted inwards and still holds 9 keys
+    kk, vv = k.float()[0, :3, :3].reshape(9, 2, 32), v.float()[0, :3, :3].reshape(9, 2, 32)
+    sc = torch.einsum("hd,khd->hk", q.float()[0, 0, 0], kk) / 32 ** 0.5
+    assert (out[0, 0, 0] - torch.einsum("hk,khd->hd", torch.softmax(sc, -1), vv)).abs().max() < 2e-2
+    # a full-size window is plain attention over the grid
+    full = vision_ops.neighborhood_attention(q[:, :5, :5].contiguous(), k[:, :5, :5].contiguous(), v[:, :5, :5].contiguous(), 5).float()
+    kk, vv = k.float()[0, :5, :5].reshape(25, 2, 32), v.float()[0, :5, :5].reshape(25, 2, 32)
+    sc = torch.einsum("ijhd,khd->ijhk", q.float()[0, :5, :5], kk) / 32 ** 0.5
+    assert (full[0] - torch.einsum("ijhk,khd->ijhd", torch.softmax(sc, -1), vv)).abs().max() < 2e-2
+
+
+@pytest.mark.gpu
+def test_neighborhood_attention_kernel(cuda):
+    from flyingfish_b200.ops import vision_ops
+    g = torch.Generator().manual_seed(44)
+    for shape, ks in (((2, 9, 11, 3, 64), 7), ((1, 8, 8, 2, 128), 3), ((1, 5, 5, 1, 32), 5)):
+        q, k, v = (torch.randn(*shape, generator=g).to(torch.bfloat16) for _ in range(3))
+        want = vision_ops.neighborhood_attention(q, k, v, ks).float()
+        got = vision_ops.neighborhood_attention(q.to(cuda), k.to(cuda), v.to(cuda), ks).float().cpu()
+        assert (got - want).abs().max() < 3e-2, (shape, ks)
