@@ -209,11 +209,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int tile_hi_min = causal ? past + r0 : ctx - 1;
     const int tile_lo_max = window > 0 ? max(0, past + r0 + real - window) : 0;
     constexpr int HB = TC_BN / 2;                 // columns per warp
-    for (int j = 0; j < ntiles && ok; ++j) {
+    // A wait that gives up clears `ok` for the whole warp; the warp then skips the work of the remaining tiles but still
+    // takes part in every barrier, so that no other warp is left waiting for it.
+    for (int j = 0; j < ntiles; ++j) {
       const int sb = j & 1; const uint32_t sph = (j >> 1) & 1;
-      if (!mbar_wait(&bars.s_full[sb], sph, abort_flag, status, KID_ATTN_PREFILL, 6)) { ok = false; break; }
-      tc_fence_after();
+      if (ok && !mbar_wait(&bars.s_full[sb], sph, abort_flag, status, KID_ATTN_PREFILL, 6)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
       float sv[HB];
+      float mx = -INFINITY;
+      if (ok) {
+      tc_fence_after();
       {
         uint32_t r[HB];
 #pragma unroll
@@ -241,13 +246,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           mx4[i & 3] = fmaxf(mx4[i & 3], t);
         }
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 commutes with the maximum
+      mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale > 0 commutes with the maximum
+      }
       // the row's maximum over both halves: through shared memory, one 64-thread barrier per quadrant pair
       bars.xmax[hf][row] = mx;
       asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
       mx = fmaxf(mx, bars.xmax[hf ^ 1][row]);
       // the previous P V must be done before P is overwritten or O is rescaled
-      if (!mbar_wait(&bars.p_empty, (j & 1) ^ 1, abort_flag, status, KID_ATTN_PREFILL, 7)) { ok = false; break; }
+      if (ok && !mbar_wait(&bars.p_empty, (j & 1) ^ 1, abort_flag, status, KID_ATTN_PREFILL, 7)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
       tc_fence_after();
       float alpha = 1.f;
       bool need = false;
@@ -291,15 +299,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tmem_st_wait();
       l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       tc_fence_before();
+      }
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (e == 0) mbar_arrive(&bars.p_full);
+      if (e == 0 && ok) mbar_arrive(&bars.p_full);
     }
     if (ok) ok = mbar_wait(&bars.o_done, 0, abort_flag, status, KID_ATTN_PREFILL, 8);
+    ok = __all_sync(0xffffffffu, ok);
+    // the row's sum over both halves
+    bars.xmax[hf][row] = l_sum;
+    asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
     if (ok) {
       tc_fence_after();
-      // the row's sum over both halves
-      bars.xmax[hf][row] = l_sum;
-      asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
       l_sum += bars.xmax[hf ^ 1][row];
       // learnable soft-max: one extra logit per head that enters the denominator only
       if (sinks != nullptr) l_sum += (m_ref == -INFINITY) ? 1.f : exp2f(sinks[h] * 1.4426950408889634f - m_ref);
