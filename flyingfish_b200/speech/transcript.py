@@ -118,3 +118,41 @@ def tdt_cues(tokens: Sequence[int], durations: Sequence[int], blank: int, decode
         frame += duration
     words, segments = word_segments(cues)
     return Transcription(text=full_text, segments=segments, words=words)
+
+
+def speaker_segments(logits, speakers: int, attention_mask=None, threshold: float = 0.5, frame_seconds: float = 0.08) -> list[TextSegment]:
+    """Frame-level speaker activity logits ``[frames, speakers]`` (row-major sequence or tensor) -> one segment per run
+    of frames whose sigmoid exceeds ``threshold`` (masked frames are inactive), labelled ``speaker_<n>``, times rounded to
+    hundredths (ties to even), sorted by start then speaker (src/diarization.rs:54-112 of the reference)."""
+    import math
+    flat = [float(v) for v in (logits.reshape(-1).tolist() if hasattr(logits, "reshape") else logits)]
+    if speakers <= 0:
+        raise ValueError("speaker count must be positive")
+    if not flat or len(flat) % speakers:
+        raise ValueError("diarization logits extent")
+    if not all(math.isfinite(v) for v in flat):
+        raise ValueError("non-finite logit")
+    if not (math.isfinite(threshold) and 0.0 <= threshold <= 1.0):
+        raise ValueError("invalid diarization threshold")
+    if not (math.isfinite(frame_seconds) and frame_seconds > 0.0):
+        raise ValueError("invalid frame duration")
+    frames = len(flat) // speakers
+    mask = None if attention_mask is None else [bool(m) for m in attention_mask]
+    if mask is not None and len(mask) != frames:
+        raise ValueError("diarization mask extent")
+
+    def stamp(frame: int) -> float:
+        return round(frame * frame_seconds * 100.0) / 100.0          # Python rounds ties to even
+
+    found = []
+    for spk in range(speakers):
+        start = None
+        for idx in range(frames + 1):
+            active = idx < frames and (mask is None or mask[idx]) and 1.0 / (1.0 + math.exp(-flat[idx * speakers + spk])) > threshold
+            if start is None and active:
+                start = idx
+            elif start is not None and not active:
+                found.append((stamp(start), spk, stamp(idx)))
+                start = None
+    found.sort(key=lambda t: (t[0], t[1]))
+    return [TextSegment(a, b, f"speaker_{spk}") for a, spk, b in found]

@@ -495,3 +495,20 @@ def test_plain_transducer_and_ctc_variants(tmp_path):
     assert isinstance(loaded, ParakeetCtcModel) and loaded.decode([wave])[0] == (tokens, starts, runs)
     res = loaded.transcribe([wave])[0]
     assert isinstance(res.text, str) and all(w.end >= w.start for w in res.words)
+
+
+def test_speaker_segments_from_frame_logits():
+    from flyingfish_b200.speech import speaker_segments
+    hi, lo = 4.0, -4.0
+    # frames x 2 speakers: speaker 0 active on frames 0-2 and 5; speaker 1 on frames 2-4
+    rows = [[hi, lo], [hi, lo], [hi, hi], [lo, hi], [lo, hi], [hi, lo]]
+    segs = speaker_segments(torch.tensor(rows), 2)
+    assert [(s.text, s.start, s.end) for s in segs] == [("speaker_0", 0.0, 0.24), ("speaker_1", 0.16, 0.4), ("speaker_0", 0.4, 0.48)]
+    masked = speaker_segments(torch.tensor(rows), 2, attention_mask=[True, True, False, True, True, True])
+    assert [(s.text, s.start, s.end) for s in masked] == [("speaker_0", 0.0, 0.16), ("speaker_1", 0.24, 0.4), ("speaker_0", 0.4, 0.48)]
+    assert speaker_segments([0.0, 0.0], 2, threshold=0.5) == []            # sigmoid(0) is not above the threshold
+    for bad in (dict(logits=[1.0, 2.0, 3.0], speakers=2), dict(logits=[float("nan")], speakers=1), dict(logits=[1.0], speakers=0),
+                dict(logits=[1.0], speakers=1, threshold=1.5), dict(logits=[1.0], speakers=1, frame_seconds=0.0),
+                dict(logits=[1.0, 1.0], speakers=1, attention_mask=[True])):
+        with pytest.raises(ValueError):
+            speaker_segments(**bad)
