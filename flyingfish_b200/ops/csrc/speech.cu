@@ -552,65 +552,83 @@ relpos_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 enum { TS_FRAME = 0, TS_TOKEN = 1, TS_COUNT = 2, TS_DONE = 3, TS_ADVANCE = 4, TS_ERROR = 5, TS_VALID = 6, TS_CAP = 7,
        TS_SYMS = 8, TS_MAXSYM = 9, TS_WORDS = 16 };
 
-// xh0[0:Hd] = table[state.token] when the prediction network advances this step
+// Every decoder kernel serves a batch of utterances that step together: blockIdx.y is the utterance, its state words are
+// state + b * TS_WORDS, its rows of the step buffers are `ld*` elements apart.
+
+// xh0[b, 0:Hd] = table[state[b].token] when the prediction network of utterance b advances this step
 __global__ void tdt_embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ state,
-                                 __nv_bfloat16* __restrict__ xh0, int Hd, int rows) {
+                                 __nv_bfloat16* __restrict__ xh0, int Hd, int rows, int ldx) {
   pdl_trigger();
   pdl_wait();
-  if (state[TS_DONE] || !state[TS_ADVANCE]) return;
-  const int tok = min(max(state[TS_TOKEN], 0), rows - 1);
-  for (int i = threadIdx.x; i < Hd; i += blockDim.x) xh0[i] = table[(size_t)tok * Hd + i];
+  const int* st = state + (size_t)blockIdx.y * TS_WORDS;
+  if (st[TS_DONE] || !st[TS_ADVANCE]) return;
+  const int tok = min(max(st[TS_TOKEN], 0), rows - 1);
+  __nv_bfloat16* dst = xh0 + (size_t)blockIdx.y * ldx;
+  for (int i = threadIdx.x; i < Hd; i += blockDim.x) dst[i] = table[(size_t)tok * Hd + i];
 }
 
-// gates: [4 Hd] BF16 pre-activations in i, f, g, o order (W [x; h]); bias: [4 Hd] FP32 (b_ih + b_hh).
-// c: FP32 cell state. The new hidden state goes to h_self (the recurrent half of this layer's input) and h_next (the
-// input half of the next layer, or the top output). Nothing is written when the step does not advance.
+// gates: [batch, 4 Hd] BF16 pre-activations in i, f, g, o order (W [x; h]); bias: [4 Hd] FP32 (b_ih + b_hh).
+// c: [batch, Hd] FP32 cell state. The new hidden state goes to h_self (the recurrent half of this layer's input) and
+// h_next (the input half of the next layer, or the top output). Nothing is written when the step does not advance.
 __global__ void lstm_cell_kernel(const __nv_bfloat16* __restrict__ gates, const float* __restrict__ bias,
                                  float* __restrict__ c, __nv_bfloat16* __restrict__ h_self,
-                                 __nv_bfloat16* __restrict__ h_next, const int* __restrict__ state, int Hd) {
+                                 __nv_bfloat16* __restrict__ h_next, const int* __restrict__ state, int Hd, int ldg, int lds,
+                                 int ldn) {
   pdl_trigger();
   pdl_wait();
-  if (state != nullptr && (state[TS_DONE] || !state[TS_ADVANCE])) return;
+  const int b = blockIdx.y;
+  if (state != nullptr) {
+    const int* st = state + (size_t)b * TS_WORDS;
+    if (st[TS_DONE] || !st[TS_ADVANCE]) return;
+  }
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= Hd) return;
-  const float gi = __bfloat162float(gates[i]) + bias[i];
-  const float gf = __bfloat162float(gates[Hd + i]) + bias[Hd + i];
-  const float gg = __bfloat162float(gates[2 * Hd + i]) + bias[2 * Hd + i];
-  const float go = __bfloat162float(gates[3 * Hd + i]) + bias[3 * Hd + i];
-  const float cn = sigmoidf_(gf) * c[i] + sigmoidf_(gi) * tanhf(gg);
+  const __nv_bfloat16* g = gates + (size_t)b * ldg;
+  float* cb = c + (size_t)b * Hd;
+  const float gi = __bfloat162float(g[i]) + bias[i];
+  const float gf = __bfloat162float(g[Hd + i]) + bias[Hd + i];
+  const float gg = __bfloat162float(g[2 * Hd + i]) + bias[2 * Hd + i];
+  const float go = __bfloat162float(g[3 * Hd + i]) + bias[3 * Hd + i];
+  const float cn = sigmoidf_(gf) * cb[i] + sigmoidf_(gi) * tanhf(gg);
   const float hn = sigmoidf_(go) * tanhf(cn);
-  c[i] = cn;
+  cb[i] = cn;
   const __nv_bfloat16 hb = __float2bfloat16(hn);
-  h_self[i] = hb;
-  if (h_next) h_next[i] = hb;
+  h_self[(size_t)b * lds + i] = hb;
+  if (h_next) h_next[(size_t)b * ldn + i] = hb;
 }
 
-// out[j] = relu(enc[frame, j] + pred[j] + bias[j]) in BF16 (enc and pred are the two projections into the joint space)
+// out[b, j] = relu(enc[b, frame_b, j] + pred[b, j] + bias[j]) in BF16 (enc and pred are the two projections into the
+// joint space; enc holds `frames` rows per utterance)
 __global__ void tdt_joint_in_kernel(const __nv_bfloat16* __restrict__ enc, const __nv_bfloat16* __restrict__ pred,
                                     const float* __restrict__ bias, const int* __restrict__ state,
-                                    __nv_bfloat16* __restrict__ out, int J, int frames) {
+                                    __nv_bfloat16* __restrict__ out, int J, int frames, int ldp, int ldo) {
   pdl_trigger();
   pdl_wait();
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
   if (j >= J) return;
-  const int f = min(max(state[TS_FRAME], 0), frames - 1);
-  const float x = __bfloat162float(enc[(size_t)f * J + j]) + __bfloat162float(pred[j]) + (bias ? bias[j] : 0.f);
-  out[j] = __float2bfloat16(fmaxf(x, 0.f));
+  const int f = min(max(state[(size_t)b * TS_WORDS + TS_FRAME], 0), frames - 1);
+  const float x = __bfloat162float(enc[((size_t)b * frames + f) * J + j]) + __bfloat162float(pred[(size_t)b * ldp + j]) +
+                  (bias ? bias[j] : 0.f);
+  out[(size_t)b * ldo + j] = __float2bfloat16(fmaxf(x, 0.f));
 }
 
-// One greedy step: token = argmax logits[0 .. vocab] (index vocab is blank), duration = durations[argmax of the
-// n_dur logits after it]; a blank with duration 0 moves one frame, and so does the TS_MAXSYM-th token in a row that
+// One greedy step per utterance: token = argmax logits[0 .. vocab] (index vocab is blank), duration = durations[argmax of
+// the n_dur logits after it]; a blank with duration 0 moves one frame, and so does the TS_MAXSYM-th token in a row that
 // would stay on its frame (the transducer's symbols-per-step limit). The trajectory entry and the next
-// (frame, token) are written on the device. Lowest index wins ties. 256 threads, one CTA.
+// (frame, token) are written on the device. Lowest index wins ties. 256 threads, one CTA per utterance.
 __global__ void __launch_bounds__(256)
-tdt_select_kernel(const __nv_bfloat16* __restrict__ logits, const float* __restrict__ out_bias,
-                  const int* __restrict__ durations, int* __restrict__ state, int* __restrict__ traj_tokens,
+tdt_select_kernel(const __nv_bfloat16* __restrict__ logits_all, const float* __restrict__ out_bias,
+                  const int* __restrict__ durations, int* __restrict__ state_all, int* __restrict__ traj_tokens,
                   int* __restrict__ traj_durations, int* __restrict__ traj_frames, int n_tok, int n_dur, int blank, int eos,
-                  int traj_len) {
+                  int traj_len, int ldl) {
   pdl_trigger();
   pdl_wait();
   __shared__ float s_val[8];
   __shared__ int s_idx[8];
+  const int ub = blockIdx.y;
+  int* state = state_all + (size_t)ub * TS_WORDS;
+  const __nv_bfloat16* logits = logits_all + (size_t)ub * ldl;
+  traj_tokens += (size_t)ub * traj_len; traj_durations += (size_t)ub * traj_len; traj_frames += (size_t)ub * traj_len;
   if (state[TS_DONE]) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float best = -3.0e38f; int bi = 0x7fffffff;
@@ -747,35 +765,36 @@ FF_EXPORT int ff_relpos_attention(const void* q, const void* k, const void* v, c
   return launch_result();
 }
 
-FF_EXPORT int ff_tdt_embed(const void* table, const int* state, void* xh0, int Hd, int rows, cudaStream_t s) {
-  if (Hd <= 0 || rows <= 0) return FF_HOST_BAD_SHAPE;
-  if (int lr = launch_pdl(tdt_embed_kernel, dim3(1), dim3(256), 0, s, 0, (const __nv_bfloat16*)table, state,
-                          (__nv_bfloat16*)xh0, Hd, rows)) return lr;
+FF_EXPORT int ff_tdt_embed(const void* table, const int* state, void* xh0, int batch, int Hd, int rows, int ldx,
+                           cudaStream_t s) {
+  if (batch <= 0 || Hd <= 0 || rows <= 0 || ldx < Hd) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(tdt_embed_kernel, dim3(1, batch), dim3(256), 0, s, 0, (const __nv_bfloat16*)table, state,
+                          (__nv_bfloat16*)xh0, Hd, rows, ldx)) return lr;
   return launch_result();
 }
 
 FF_EXPORT int ff_lstm_cell(const void* gates, const float* bias, float* c, void* h_self, void* h_next, const int* state,
-                           int Hd, cudaStream_t s) {
-  if (Hd <= 0) return FF_HOST_BAD_SHAPE;
-  if (int lr = launch_pdl(lstm_cell_kernel, dim3((Hd + 127) / 128), dim3(128), 0, s, 0, (const __nv_bfloat16*)gates, bias,
-                          c, (__nv_bfloat16*)h_self, (__nv_bfloat16*)h_next, state, Hd)) return lr;
+                           int batch, int Hd, int ldg, int lds, int ldn, cudaStream_t s) {
+  if (batch <= 0 || Hd <= 0 || ldg < 4 * Hd || lds < Hd) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(lstm_cell_kernel, dim3((Hd + 127) / 128, batch), dim3(128), 0, s, 0, (const __nv_bfloat16*)gates,
+                          bias, c, (__nv_bfloat16*)h_self, (__nv_bfloat16*)h_next, state, Hd, ldg, lds, ldn)) return lr;
   return launch_result();
 }
 
-FF_EXPORT int ff_tdt_joint_in(const void* enc, const void* pred, const float* bias, const int* state, void* out, int J,
-                              int frames, cudaStream_t s) {
-  if (J <= 0 || frames <= 0) return FF_HOST_BAD_SHAPE;
-  if (int lr = launch_pdl(tdt_joint_in_kernel, dim3((J + 127) / 128), dim3(128), 0, s, 0, (const __nv_bfloat16*)enc,
-                          (const __nv_bfloat16*)pred, bias, state, (__nv_bfloat16*)out, J, frames)) return lr;
+FF_EXPORT int ff_tdt_joint_in(const void* enc, const void* pred, const float* bias, const int* state, void* out, int batch,
+                              int J, int frames, int ldp, int ldo, cudaStream_t s) {
+  if (batch <= 0 || J <= 0 || frames <= 0 || ldp < J || ldo < J) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(tdt_joint_in_kernel, dim3((J + 127) / 128, batch), dim3(128), 0, s, 0, (const __nv_bfloat16*)enc,
+                          (const __nv_bfloat16*)pred, bias, state, (__nv_bfloat16*)out, J, frames, ldp, ldo)) return lr;
   return launch_result();
 }
 
 FF_EXPORT int ff_tdt_select(const void* logits, const float* out_bias, const int* durations, int* state, int* traj_tokens,
-                            int* traj_durations, int* traj_frames, int n_tok, int n_dur, int blank, int eos,
-                            int traj_len, cudaStream_t s) {
-  if (n_tok <= 0 || n_dur < 0 || traj_len <= 0) return FF_HOST_BAD_SHAPE;
-  if (int lr = launch_pdl(tdt_select_kernel, dim3(1), dim3(256), 0, s, 0, (const __nv_bfloat16*)logits, out_bias,
-                          durations, state, traj_tokens, traj_durations, traj_frames, n_tok, n_dur, blank, eos, traj_len))
+                            int* traj_durations, int* traj_frames, int batch, int n_tok, int n_dur, int blank, int eos,
+                            int traj_len, int ldl, cudaStream_t s) {
+  if (batch <= 0 || n_tok <= 0 || n_dur < 0 || traj_len <= 0 || ldl < n_tok + n_dur) return FF_HOST_BAD_SHAPE;
+  if (int lr = launch_pdl(tdt_select_kernel, dim3(1, batch), dim3(256), 0, s, 0, (const __nv_bfloat16*)logits, out_bias,
+                          durations, state, traj_tokens, traj_durations, traj_frames, n_tok, n_dur, blank, eos, traj_len, ldl))
     return lr;
   return launch_result();
 }

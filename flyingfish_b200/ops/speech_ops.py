@@ -297,97 +297,122 @@ def relpos_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: tor
 # ------------------------------------------------------------------------------------------------
 # transducer decoder steps (device-resident state)
 # ------------------------------------------------------------------------------------------------
+def _rows(t: torch.Tensor | None) -> torch.Tensor | None:
+    """Decoder step buffers are [batch, width]; a 1-D tensor is the batch of one."""
+    return None if t is None else (t if t.dim() >= 2 else t[None])
+
+
 def tdt_embed(table: torch.Tensor, state: torch.Tensor, xh0: torch.Tensor) -> None:
-    """``xh0[:Hd] = table[state.token]`` when the step advances the prediction network."""
+    """``xh0[b, :Hd] = table[state[b].token]`` for every utterance whose step advances the prediction network.
+    ``state``: [batch, TS_WORDS] int32, ``xh0``: [batch, >= Hd] (rows may be wider: the input half of ``[x; h]``)."""
     hd = table.shape[1]
+    st, x = _rows(state), _rows(xh0)
     if not table.is_cuda:
-        if int(state[TS_DONE]) or not int(state[TS_ADVANCE]):
-            return
-        xh0[:hd] = table[min(max(int(state[TS_TOKEN]), 0), table.shape[0] - 1)]
+        for b in range(st.shape[0]):
+            if int(st[b, TS_DONE]) or not int(st[b, TS_ADVANCE]):
+                continue
+            x[b, :hd] = table[min(max(int(st[b, TS_TOKEN]), 0), table.shape[0] - 1)]
         return
-    rc = kernels().ff_tdt_embed(ptr(table), ptr(state), ptr(xh0), hd, table.shape[0], stream_ptr())
+    _require(st.is_contiguous() and x.stride(1) == 1, "tdt_embed: layout")
+    rc = kernels().ff_tdt_embed(ptr(table), ptr(st), ptr(x), st.shape[0], hd, table.shape[0], x.stride(0), stream_ptr())
     check(rc, "ff_tdt_embed")
     _count()
 
 
 def lstm_cell(gates: torch.Tensor, bias: torch.Tensor, c: torch.Tensor, h_self: torch.Tensor,
               h_next: torch.Tensor | None, state: torch.Tensor | None) -> None:
-    """One LSTM cell update from the gate pre-activations ``gates`` [4 Hd] BF16 (i, f, g, o; ``W [x; h]``) and
-    ``bias`` [4 Hd] FP32. ``c`` (FP32) is updated in place, the new hidden state is written (BF16) to ``h_self`` and
-    ``h_next``. With ``state`` the update only happens when the decode step advances."""
-    hd = c.numel()
-    if not gates.is_cuda:
-        if state is not None and (int(state[TS_DONE]) or not int(state[TS_ADVANCE])):
-            return
-        g = gates.float().reshape(4, hd) + bias.float().reshape(4, hd)
-        cn = torch.sigmoid(g[1]) * c + torch.sigmoid(g[0]) * torch.tanh(g[2])
-        hn = torch.sigmoid(g[3]) * torch.tanh(cn)
-        c.copy_(cn)
-        h_self.copy_(hn.to(h_self.dtype))
-        if h_next is not None:
-            h_next.copy_(hn.to(h_next.dtype))
+    """One LSTM cell update per utterance from the gate pre-activations ``gates`` [batch, 4 Hd] BF16 (i, f, g, o;
+    ``W [x; h]``) and ``bias`` [4 Hd] FP32. ``c`` [batch, Hd] (FP32) is updated in place, the new hidden state is written
+    (BF16) to ``h_self`` and ``h_next`` (row views of wider buffers are fine). With ``state`` an utterance is only updated
+    when its decode step advances."""
+    g, cc, hs, hn, st = _rows(gates), _rows(c), _rows(h_self), _rows(h_next), _rows(state)
+    batch, hd = cc.shape
+    if not g.is_cuda:
+        for b in range(batch):
+            if st is not None and (int(st[b, TS_DONE]) or not int(st[b, TS_ADVANCE])):
+                continue
+            z = g[b].float().reshape(4, hd) + bias.float().reshape(4, hd)
+            cn = torch.sigmoid(z[1]) * cc[b] + torch.sigmoid(z[0]) * torch.tanh(z[2])
+            hv = torch.sigmoid(z[3]) * torch.tanh(cn)
+            cc[b].copy_(cn)
+            hs[b].copy_(hv.to(hs.dtype))
+            if hn is not None:
+                hn[b].copy_(hv.to(hn.dtype))
         return
-    rc = kernels().ff_lstm_cell(ptr(gates), ptr(bias), ptr(c), ptr(h_self), ptr(h_next), ptr(state), hd, stream_ptr())
+    _require(cc.is_contiguous() and g.stride(1) == 1 and hs.stride(1) == 1 and (hn is None or hn.stride(1) == 1)
+             and (st is None or st.is_contiguous()), "lstm_cell: layout")
+    rc = kernels().ff_lstm_cell(ptr(g), ptr(bias), ptr(cc), ptr(hs), ptr(hn), ptr(st), batch, hd, g.stride(0), hs.stride(0),
+                                hn.stride(0) if hn is not None else hd, stream_ptr())
     check(rc, "ff_lstm_cell")
     _count()
 
 
 def tdt_joint_in(enc: torch.Tensor, pred: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
                  out: torch.Tensor) -> None:
-    """``out = bf16(relu(enc[state.frame] + pred + bias))``: the joint network's hidden vector of this step."""
-    frames, j = enc.shape
-    if not enc.is_cuda:
-        f = min(max(int(state[TS_FRAME]), 0), frames - 1)
-        x = enc[f].float() + pred.float().reshape(-1) + (bias.float() if bias is not None else 0.0)
-        out.copy_(torch.relu(x).to(out.dtype).reshape(out.shape))
+    """``out[b] = bf16(relu(enc[b, state[b].frame] + pred[b] + bias))``: the joint network's hidden vector of this step.
+    ``enc``: [batch, frames, J] (or [frames, J] for one utterance)."""
+    e = enc if enc.dim() == 3 else enc[None]
+    pr, st, o = _rows(pred), _rows(state), _rows(out)
+    batch, frames, j = e.shape
+    if not e.is_cuda:
+        for b in range(batch):
+            f = min(max(int(st[b, TS_FRAME]), 0), frames - 1)
+            x = e[b, f].float() + pr[b].float() + (bias.float() if bias is not None else 0.0)
+            o[b].copy_(torch.relu(x).to(o.dtype))
         return
-    rc = kernels().ff_tdt_joint_in(ptr(enc), ptr(pred), ptr(bias), ptr(state), ptr(out), j, frames, stream_ptr())
+    _require(e.is_contiguous() and pr.stride(1) == 1 and o.stride(1) == 1 and st.is_contiguous(), "tdt_joint_in: layout")
+    rc = kernels().ff_tdt_joint_in(ptr(e), ptr(pr), ptr(bias), ptr(st), ptr(o), batch, j, frames, pr.stride(0), o.stride(0), stream_ptr())
     check(rc, "ff_tdt_joint_in")
     _count()
 
 
 def tdt_select(logits: torch.Tensor, out_bias: torch.Tensor | None, durations: torch.Tensor, state: torch.Tensor,
                traj: tuple[torch.Tensor, torch.Tensor, torch.Tensor], n_tok: int, blank: int, eos: int) -> None:
-    """Greedy selection of one step and the state update: token = argmax of the first ``n_tok`` logits (lowest index
-    on ties), duration = ``durations[argmax of the rest]``, a blank with duration 0 advances one frame and so does the
-    ``TS_MAXSYM``-th consecutive token that would stay on its frame; the
-    (token, duration, frame) entry is appended to ``traj`` and the state moves to the next frame, or ``done`` is set on
-    the end-of-sequence token or when the frames (state word ``TS_VALID``) are used up. A trajectory longer than
-    ``TS_CAP`` entries sets the error word. An empty ``durations`` selects the plain transducer rule: a token stays
-    on its frame, a blank moves one frame."""
+    """Greedy selection of one step per utterance and the state update: token = argmax of the first ``n_tok`` logits
+    (lowest index on ties), duration = ``durations[argmax of the rest]``, a blank with duration 0 advances one frame and
+    so does the ``TS_MAXSYM``-th consecutive token that would stay on its frame; the (token, duration, frame) entry is
+    appended to ``traj`` (three [batch, capacity] int32 tensors) and the state moves to the next frame, or ``done`` is set
+    on the end-of-sequence token or when the frames (state word ``TS_VALID``) are used up. A trajectory longer than
+    ``TS_CAP`` entries sets the error word. An empty ``durations`` selects the plain transducer rule: a token stays on its
+    frame, a blank moves one frame."""
     n_dur = durations.numel()
-    traj_len = traj[0].numel()
-    if not logits.is_cuda:
-        if int(state[TS_DONE]):
-            return
-        x = logits.float().reshape(-1)[: n_tok + n_dur]
-        if out_bias is not None:
-            x = x + out_bias.float()[: n_tok + n_dur]
-        tok = int(torch.argmax(x[:n_tok]))
-        dur = int(durations[int(torch.argmax(x[n_tok:n_tok + n_dur]))]) if n_dur > 0 else 0
-        count, frame = int(state[TS_COUNT]), int(state[TS_FRAME])
-        valid_rows, capacity = int(state[TS_VALID]), min(int(state[TS_CAP]), traj_len)
-        if count >= capacity:
-            state[TS_ERROR] = 1
-            state[TS_DONE] = 1
-            return
-        if tok == blank and dur == 0:
-            dur = 1
-        syms = int(state[TS_SYMS])
-        if tok != blank and dur == 0:
-            syms += 1
-            if syms >= int(state[TS_MAXSYM]):
+    lg, st = _rows(logits), _rows(state)
+    tr = tuple(_rows(t) for t in traj)
+    traj_len = tr[0].shape[1]
+    if not lg.is_cuda:
+        for b in range(st.shape[0]):
+            s1 = st[b]
+            if int(s1[TS_DONE]):
+                continue
+            x = lg[b].float().reshape(-1)[: n_tok + n_dur]
+            if out_bias is not None:
+                x = x + out_bias.float()[: n_tok + n_dur]
+            tok = int(torch.argmax(x[:n_tok]))
+            dur = int(durations[int(torch.argmax(x[n_tok:n_tok + n_dur]))]) if n_dur > 0 else 0
+            count, frame = int(s1[TS_COUNT]), int(s1[TS_FRAME])
+            valid_rows, capacity = int(s1[TS_VALID]), min(int(s1[TS_CAP]), traj_len)
+            if count >= capacity:
+                s1[TS_ERROR] = 1
+                s1[TS_DONE] = 1
+                continue
+            if tok == blank and dur == 0:
                 dur = 1
-        state[TS_SYMS] = 0 if dur > 0 else syms
-        traj[0][count], traj[1][count], traj[2][count] = tok, dur, frame
-        state[TS_COUNT] = count + 1
-        nxt = frame + dur
-        state[TS_FRAME], state[TS_TOKEN], state[TS_ADVANCE] = nxt, tok, int(tok != blank)
-        if tok == eos or nxt >= valid_rows:
-            state[TS_DONE] = 1
+            syms = int(s1[TS_SYMS])
+            if tok != blank and dur == 0:
+                syms += 1
+                if syms >= int(s1[TS_MAXSYM]):
+                    dur = 1
+            s1[TS_SYMS] = 0 if dur > 0 else syms
+            tr[0][b, count], tr[1][b, count], tr[2][b, count] = tok, dur, frame
+            s1[TS_COUNT] = count + 1
+            nxt = frame + dur
+            s1[TS_FRAME], s1[TS_TOKEN], s1[TS_ADVANCE] = nxt, tok, int(tok != blank)
+            if tok == eos or nxt >= valid_rows:
+                s1[TS_DONE] = 1
         return
-    rc = kernels().ff_tdt_select(ptr(logits), ptr(out_bias), ptr(durations), ptr(state), ptr(traj[0]), ptr(traj[1]),
-                                 ptr(traj[2]), n_tok, n_dur, blank, eos, traj_len, stream_ptr())
+    _require(st.is_contiguous() and lg.stride(1) == 1 and all(t.is_contiguous() for t in tr), "tdt_select: layout")
+    rc = kernels().ff_tdt_select(ptr(lg), ptr(out_bias), ptr(durations), ptr(st), ptr(tr[0]), ptr(tr[1]), ptr(tr[2]), st.shape[0],
+                                 n_tok, n_dur, blank, eos, traj_len, lg.stride(0), stream_ptr())
     check(rc, "ff_tdt_select")
     _count()
 

@@ -192,9 +192,11 @@ class TdtTrajectory:
 
 
 class TdtDecoder:
-    """Prediction network (embedding + LSTM stack), joint network and the greedy TDT loop."""
+    """Prediction network (embedding + LSTM stack), joint network and the greedy TDT loop, for up to ``max_batch``
+    utterances stepping together (their states, frames and trajectories are separate rows of the device buffers)."""
 
-    def __init__(self, spec: ParakeetSpec, tensors: dict[str, torch.Tensor], device: torch.device | str, max_rows: int = 0):
+    def __init__(self, spec: ParakeetSpec, tensors: dict[str, torch.Tensor], device: torch.device | str, max_rows: int = 0,
+                 max_batch: int = 8):
         self.spec, self.device = spec, torch.device(device)
         dev, d = self.device, spec.decoder_hidden
 
@@ -217,16 +219,17 @@ class TdtDecoder:
         self.w_head = w16(head)
         self.b_head = tensors["joint.head.bias"].float().contiguous().to(dev)
         self.durations = torch.tensor(spec.durations or (0,), dtype=torch.int32, device=dev)[: len(spec.durations)]
-        # step buffers (fixed addresses: the step is captured once)
+        # step buffers (fixed addresses: the step is captured once); one row per utterance
         self.max_rows = max_rows or spec.encoder.max_position
-        self.enc = torch.zeros(self.max_rows, d, dtype=BF16, device=dev)
-        self.xh = [torch.zeros(2 * d, dtype=BF16, device=dev) for _ in range(spec.decoder_layers)]
-        self.cell = [torch.zeros(d, dtype=torch.float32, device=dev) for _ in range(spec.decoder_layers)]
-        self.top = torch.zeros(1, d, dtype=BF16, device=dev)
-        self.jh = torch.zeros(1, d, dtype=BF16, device=dev)
-        self.state = torch.zeros(TS_WORDS, dtype=torch.int32, device=dev)
+        self.max_batch = nb = max(1, max_batch)
+        self.enc = torch.zeros(nb, self.max_rows, d, dtype=BF16, device=dev)
+        self.xh = [torch.zeros(nb, 2 * d, dtype=BF16, device=dev) for _ in range(spec.decoder_layers)]
+        self.cell = [torch.zeros(nb, d, dtype=torch.float32, device=dev) for _ in range(spec.decoder_layers)]
+        self.top = torch.zeros(nb, d, dtype=BF16, device=dev)
+        self.jh = torch.zeros(nb, d, dtype=BF16, device=dev)
+        self.state = torch.zeros(nb, TS_WORDS, dtype=torch.int32, device=dev)
         cap = spec.max_symbols * self.max_rows + 1
-        self.traj = tuple(torch.zeros(cap, dtype=torch.int32, device=dev) for _ in range(3))
+        self.traj = tuple(torch.zeros(nb, cap, dtype=torch.int32, device=dev) for _ in range(3))
         self._graph: torch.cuda.CUDAGraph | None = None
         self.use_graph = self.device.type == "cuda"
         self.graph_replays = 0
@@ -235,30 +238,37 @@ class TdtDecoder:
         """[rows, hidden] BF16 encoder output -> [rows, decoder_hidden] BF16 in the joint space."""
         return vision_ops.linear_bias_act(encoded, self.enc_proj[0], self.enc_proj[1], "none")
 
-    def reset(self, valid_rows: int) -> int:
+    def reset(self, valid_rows: list[int] | int) -> list[int]:
+        """Fresh decode state for ``len(valid_rows)`` utterances (the other rows of the batch are parked as done)."""
         spec = self.spec
+        valid = [valid_rows] if isinstance(valid_rows, int) else list(valid_rows)
         for t in self.xh:
             t.zero_()
         for t in self.cell:
             t.zero_()
-        capacity = min(spec.max_symbols * valid_rows + 1, self.traj[0].numel())
-        init = torch.zeros(TS_WORDS, dtype=torch.int32)
-        init[TS_TOKEN], init[TS_COUNT], init[TS_ADVANCE], init[TS_VALID], init[TS_CAP] = spec.blank, 1, 1, valid_rows, capacity
-        init[TS_MAXSYM] = spec.max_symbols
+        cap_len = self.traj[0].shape[1]
+        init = torch.zeros(self.max_batch, TS_WORDS, dtype=torch.int32)
+        init[:, TS_DONE] = 1
+        caps = []
+        for b, rows in enumerate(valid):
+            cap = min(spec.max_symbols * rows + 1, cap_len)
+            caps.append(cap)
+            init[b, TS_TOKEN], init[b, TS_COUNT], init[b, TS_ADVANCE], init[b, TS_VALID], init[b, TS_CAP] = spec.blank, 1, 1, rows, cap
+            init[b, TS_MAXSYM], init[b, TS_DONE] = spec.max_symbols, 0
         self.state.copy_(init)
         first = torch.tensor([spec.blank, 0, 0], dtype=torch.int32)
         for t, v in zip(self.traj, first):
-            t[:1] = v
-        return capacity
+            t[:, :1] = v
+        return caps
 
     def step(self) -> None:
-        """One decode step on the current stream (the sequence a CUDA graph captures)."""
+        """One decode step of every utterance on the current stream (the sequence a CUDA graph captures)."""
         spec, d = self.spec, self.spec.decoder_hidden
         speech_ops.tdt_embed(self.table, self.state, self.xh[0])
         for layer, (w, b) in enumerate(self.lstm):
-            gates = ops.linear(self.xh[layer][None, :], w)
-            nxt = self.xh[layer + 1][:d] if layer + 1 < len(self.lstm) else self.top[0]
-            speech_ops.lstm_cell(gates[0], b, self.cell[layer], self.xh[layer][d:], nxt, self.state)
+            gates = ops.linear(self.xh[layer], w)
+            nxt = self.xh[layer + 1][:, :d] if layer + 1 < len(self.lstm) else self.top
+            speech_ops.lstm_cell(gates, b, self.cell[layer], self.xh[layer][:, d:], nxt, self.state)
         pred = ops.linear(self.top, self.w_pred)
         speech_ops.tdt_joint_in(self.enc, pred, self.b_pred, self.state, self.jh)
         logits = ops.linear(self.jh, self.w_head)
@@ -278,62 +288,7 @@ class TdtDecoder:
         self._graph = g
         self.state.copy_(saved)
 
-    # -- streaming: rows arrive in pieces, the device state carries on ---------------------------------------
-    def begin_stream(self) -> None:
-        self.reset(1)
-        st = self.state.tolist()
-        st[TS_VALID], st[TS_CAP], st[TS_DONE] = 0, self.traj[0].numel(), 1
-        self.state.copy_(torch.tensor(st, dtype=torch.int32))
-        self._rows = 0
-        self._taken = 1                                  # trajectory entries already handed out (the initial blank)
-
-    def extend(self, projected: torch.Tensor) -> TdtTrajectory:
-        """Appends projected encoder rows and decodes as far as they reach; returns the new trajectory entries."""
-        n = projected.shape[0]
-        if self._rows + n > self.max_rows:
-            raise ValueError(f"stream longer than {self.max_rows} encoder rows")
-        if self.use_graph and self._graph is None:
-            saved_rows, saved_taken, saved_state = self._rows, self._taken, self.state.clone()
-            self._capture()
-            self._rows, self._taken = saved_rows, saved_taken
-            self.state.copy_(saved_state)
-        if n:
-            self.enc[self._rows: self._rows + n].copy_(projected)
-            self._rows += n
-        st = self.state.tolist()
-        stopped_on_eos = st[TS_DONE] and st[TS_COUNT] > 1 and int(self.traj[0][st[TS_COUNT] - 1]) == self.spec.eos
-        st[TS_VALID] = self._rows
-        st[TS_DONE] = int(stopped_on_eos or st[TS_FRAME] >= self._rows)
-        self.state.copy_(torch.tensor(st, dtype=torch.int32))
-        steps = reads = 0
-        while not st[TS_DONE]:
-            if self.use_graph:
-                for _ in range(CHECK_EVERY):
-                    self._graph.replay()
-                self.graph_replays += CHECK_EVERY
-                steps += CHECK_EVERY
-            else:
-                self.step()
-                steps += 1
-            st = self.state.tolist()
-            reads += 1
-            if st[TS_ERROR]:
-                raise RuntimeError(f"decode capacity exceeded at frame {st[TS_FRAME]}")
-        lo, hi = self._taken, st[TS_COUNT]
-        self._taken = hi
-        tok, dur, frm = (t[lo:hi].tolist() for t in self.traj)
-        return TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=self.traj[0].numel(), steps=steps, state_reads=reads)
-
-    def decode(self, projected: torch.Tensor, valid_rows: int) -> TdtTrajectory:
-        """Greedy decode of one utterance from its projected encoder rows [rows, decoder_hidden]."""
-        rows = projected.shape[0]
-        if not (0 < valid_rows <= rows <= self.max_rows):
-            raise ValueError("decode valid encoder rows outside the projected extent")
-        self.enc[:rows].copy_(projected)
-        if self.use_graph and self._graph is None:
-            self.reset(valid_rows)
-            self._capture()
-        capacity = self.reset(valid_rows)
+    def _run_until_done(self, limit: int) -> tuple[list[list[int]], int, int]:
         steps = reads = 0
         while True:
             if self.use_graph:
@@ -346,27 +301,83 @@ class TdtDecoder:
                 steps += 1
             st = self.state.tolist()
             reads += 1
-            if st[TS_ERROR]:
-                raise RuntimeError(f"decode capacity exceeded: capacity={capacity} frame={st[TS_FRAME]}")
-            if st[TS_DONE]:
-                break
-            if steps > capacity + CHECK_EVERY:
+            for b, row in enumerate(st):
+                if row[TS_ERROR]:
+                    raise RuntimeError(f"decode capacity exceeded: utterance {b}, capacity={row[TS_CAP]} frame={row[TS_FRAME]}")
+            if all(row[TS_DONE] for row in st):
+                return st, steps, reads
+            if steps > limit + CHECK_EVERY:
                 raise RuntimeError("decode did not finish within its capacity")
-        n = st[TS_COUNT]
-        tok, dur, frm = (t[:n].tolist() for t in self.traj)
-        return TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=capacity, steps=steps, state_reads=reads)
+
+    # -- streaming: rows arrive in pieces, the device state carries on (utterance row 0) ---------------------
+    def begin_stream(self) -> None:
+        self.reset([1])
+        st = self.state.tolist()
+        st[0][TS_VALID], st[0][TS_CAP], st[0][TS_DONE] = 0, self.traj[0].shape[1], 1
+        self.state.copy_(torch.tensor(st, dtype=torch.int32))
+        self._rows = 0
+        self._taken = 1                                  # trajectory entries already handed out (the initial blank)
+
+    def extend(self, projected: torch.Tensor) -> TdtTrajectory:
+        """Appends projected encoder rows and decodes as far as they reach; returns the new trajectory entries."""
+        n = projected.shape[0]
+        if self._rows + n > self.max_rows:
+            raise ValueError(f"stream longer than {self.max_rows} encoder rows")
+        if self.use_graph and self._graph is None:
+            self._capture()                              # the capture leaves the state as it found it
+        if n:
+            self.enc[0, self._rows: self._rows + n].copy_(projected)
+            self._rows += n
+        st = self.state.tolist()
+        s0 = st[0]
+        stopped_on_eos = s0[TS_DONE] and s0[TS_COUNT] > 1 and int(self.traj[0][0, s0[TS_COUNT] - 1]) == self.spec.eos
+        s0[TS_VALID] = self._rows
+        s0[TS_DONE] = int(stopped_on_eos or s0[TS_FRAME] >= self._rows)
+        self.state.copy_(torch.tensor(st, dtype=torch.int32))
+        steps = reads = 0
+        if not s0[TS_DONE]:
+            st, steps, reads = self._run_until_done(self.traj[0].shape[1])
+        lo, hi = self._taken, st[0][TS_COUNT]
+        self._taken = hi
+        tok, dur, frm = (t[0, lo:hi].tolist() for t in self.traj)
+        return TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=self.traj[0].shape[1], steps=steps, state_reads=reads)
+
+    def decode_batch(self, projected: list[torch.Tensor], valid_rows: list[int]) -> list[TdtTrajectory]:
+        """Greedy decode of up to ``max_batch`` utterances at once from their projected encoder rows
+        ([rows, decoder_hidden] each); all of them step together until the last one is done."""
+        if not (0 < len(projected) <= self.max_batch) or len(projected) != len(valid_rows):
+            raise ValueError(f"decode takes 1..{self.max_batch} utterances")
+        for b, (p, v) in enumerate(zip(projected, valid_rows)):
+            if not (0 < v <= p.shape[0] <= self.max_rows):
+                raise ValueError("decode valid encoder rows outside the projected extent")
+            self.enc[b, : p.shape[0]].copy_(p)
+        if self.use_graph and self._graph is None:
+            self.reset(valid_rows)
+            self._capture()
+        caps = self.reset(valid_rows)
+        st, steps, reads = self._run_until_done(max(caps))
+        out = []
+        for b, cap in enumerate(caps):
+            n = st[b][TS_COUNT]
+            tok, dur, frm = (t[b, :n].tolist() for t in self.traj)
+            out.append(TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=cap, steps=steps, state_reads=reads))
+        return out
+
+    def decode(self, projected: torch.Tensor, valid_rows: int) -> TdtTrajectory:
+        """Greedy decode of one utterance from its projected encoder rows [rows, decoder_hidden]."""
+        return self.decode_batch([projected], [valid_rows])[0]
 
 
 class ParakeetModel:
     """Log-mel front end + encoder + TDT decoder of one checkpoint (or of seeded random weights)."""
 
     def __init__(self, spec: ParakeetSpec, tensors: dict[str, torch.Tensor], device: torch.device | str = "cpu",
-                 tokenizer=None, max_rows: int = 0):
+                 tokenizer=None, max_rows: int = 0, max_batch: int = 8):
         spec.check()
         self.spec, self.device, self.tokenizer = spec, torch.device(device), tokenizer
         self.mel = LogMel(spec.mel, self.device)
         self.encoder = ConformerEncoder(spec.encoder, tensors, self.device)
-        self.decoder = TdtDecoder(spec, tensors, self.device, max_rows)
+        self.decoder = TdtDecoder(spec, tensors, self.device, max_rows, max_batch)
 
     @classmethod
     def random(cls, spec: ParakeetSpec, device: torch.device | str = "cpu", seed: int = 0, **kw) -> "ParakeetModel":
@@ -389,10 +400,13 @@ class ParakeetModel:
 
     def decode(self, waveforms: list[torch.Tensor]) -> list[TdtTrajectory]:
         encoded, rows = self.encode(waveforms)
+        batch, t, h = encoded.shape
+        proj = self.decoder.project(encoded.reshape(batch * t, h)).reshape(batch, t, -1)
         out = []
-        for b, n in enumerate(rows):
-            proj = self.decoder.project(encoded[b])
-            out.append(self.decoder.decode(proj, n))
+        nb = self.decoder.max_batch
+        for lo in range(0, batch, nb):                    # the decoder steps up to max_batch utterances together
+            hi = min(batch, lo + nb)
+            out += self.decoder.decode_batch([proj[b] for b in range(lo, hi)], rows[lo:hi])
         return out
 
     def transcription(self, traj: TdtTrajectory) -> Transcription:

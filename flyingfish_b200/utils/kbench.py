@@ -279,7 +279,7 @@ def bench_speech(args) -> dict:
         flops = 3 * 2.0 * args.batch * h * t * t * d
         return {"op": "relpos_attention", "batch": args.batch, "rows": t, "heads": h, "head_dim": d, "us": att["us_median"],
                 "tflops": flops / att["us_median"] / 1e6}
-    model = ParakeetModel.random(spec, dev, seed=0)
+    model = ParakeetModel.random(spec, dev, seed=0, max_batch=min(args.batch, 32))
     g = torch.Generator().manual_seed(0)
     waves = [0.1 * torch.randn(int(args.seconds * 16000), generator=g) for _ in range(args.batch)]
     audio_s = args.seconds * args.batch
@@ -292,14 +292,15 @@ def bench_speech(args) -> dict:
     mel = time_op(front, args.iters, args.warmup, None)
     enc = time_op(lambda: model.encoder.encode(feat, vl), args.iters, args.warmup, None)
     encoded, rows = model.encoder.encode(feat, vl)
-    proj = model.decoder.project(encoded[0])
-    model.decoder.decode(proj, rows[0])
+    nb = min(args.batch, model.decoder.max_batch)
+    projs = [model.decoder.project(encoded[b]) for b in range(nb)]
+    model.decoder.decode_batch(projs, rows[:nb])
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    traj = model.decoder.decode(proj, rows[0])
+    traj = model.decoder.decode_batch(projs, rows[:nb])[0]
     e1.record()
     torch.cuda.synchronize()
-    dec_ms = e0.elapsed_time(e1)
+    dec_ms = e0.elapsed_time(e1) / nb                       # the utterances of a batch step together
     t, h, d = encoded.shape[1], spec.encoder.heads, spec.encoder.head_dim
     qkv = torch.randn(args.batch * t, 3 * h * d, device=dev).to(torch.bfloat16)
     pos = torch.randn(2 * t - 1, h * d, device=dev).to(torch.bfloat16)

@@ -512,3 +512,22 @@ def test_speaker_segments_from_frame_logits():
                 dict(logits=[1.0, 1.0], speakers=1, attention_mask=[True])):
         with pytest.raises(ValueError):
             speaker_segments(**bad)
+
+
+def test_batched_decode_equals_one_by_one():
+    spec = parakeet_tiny()
+    model = ParakeetModel.random(spec, seed=15, max_batch=3)
+    g = torch.Generator().manual_seed(16)
+    rows = [torch.randn(n, spec.decoder_hidden, generator=g).to(torch.bfloat16) for n in (31, 12, 20, 7)]
+    valid = [31, 9, 20, 7]
+    dec = model.decoder
+    together = dec.decode_batch(rows[:3], valid[:3])
+    alone = [dec.decode(r, v) for r, v in zip(rows, valid)]
+    for a, b in zip(together, alone):
+        assert (a.tokens, a.durations, a.frames) == (b.tokens, b.durations, b.frames)
+    with pytest.raises(ValueError):
+        dec.decode_batch(rows, valid)                       # more utterances than the decoder's batch
+    # the model batches by itself
+    waves = [0.1 * torch.randn(n, generator=g) for n in (8000, 5000, 9000, 6000)]
+    outs = model.decode(waves)
+    assert len(outs) == 4 and all(o.tokens[0] == spec.blank for o in outs)

@@ -190,3 +190,17 @@ def test_model_decode_on_device(cuda):
     enc, rows = dev_model.encode(waves)
     proj = dev_model.decoder.project(enc[0, : rows[0]])
     _close(proj, cpu_model.decoder.project(enc[0, : rows[0]].cpu()), 3e-2, 2e-2)
+
+
+def test_batched_decode_on_device(cuda):
+    spec = parakeet_tiny()
+    model = ParakeetModel.random(spec, cuda, seed=15, max_batch=3)
+    g = torch.Generator().manual_seed(16)
+    rows = [torch.randn(n, spec.decoder_hidden, generator=g).to(BF16).to(cuda) for n in (31, 12, 20)]
+    valid = [31, 9, 20]
+    dec = model.decoder
+    together = dec.decode_batch(rows, valid)
+    alone = [dec.decode(r, v) for r, v in zip(rows, valid)]
+    for a, b in zip(together, alone):
+        assert (a.tokens, a.durations, a.frames) == (b.tokens, b.durations, b.frames)
+    assert dec.graph_replays > 0
