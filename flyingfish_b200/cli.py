@@ -418,8 +418,29 @@ def cmd_inspect(args) -> dict:
         return {"shapes": {k: f().to_json() for k, f in NAMED_SHAPES.items()}}
     from .config import named_shape, read_model_spec
     p = Path(args.model or "")
+    if p.is_file() and p.suffix == ".nemo":
+        # NeMo archive of a streaming RNN-T: the spec its YAML maps to and the tensor table of the pickled weights
+        from dataclasses import asdict
+        import torch
+        from .loaders.pth import read_nemo
+        from .speech.nemo import spec_from_yaml
+        text, weights = read_nemo(p)
+        try:
+            nbytes = sum(r.storage.numel * torch.empty(0, dtype=r.dtype).element_size() for r in weights.records.values())
+            return {"family": "speech", "architecture": "nemo_rnnt", "spec": asdict(spec_from_yaml(text)),
+                    "tensors": len(weights.records), "bytes": nbytes}
+        finally:
+            weights.close()
     if p.is_dir():
         from .loaders.checkpoint import inspect_checkpoint
+        arch = json.loads((p / "config.json").read_text()).get("architectures", [None])[0] if (p / "config.json").exists() else None
+        if arch in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration"):
+            # speech checkpoints: their own spec classes, contract check included
+            from dataclasses import asdict
+            from .speech import CanarySpec, ParakeetCtcSpec, ParakeetSpec
+            sp = {"ParakeetForTDT": ParakeetSpec, "ParakeetForCTC": ParakeetCtcSpec, "CanaryForConditionalGeneration": CanarySpec}[arch].read(p)
+            info = inspect_checkpoint(p)
+            return {"family": "speech", "architecture": arch, "spec": asdict(sp), "expected_tensors": len(sp.expected_tensors()), **info}
         spec = read_model_spec(p)
         return {"spec": spec.to_json(), **inspect_checkpoint(p)}
     return {"spec": named_shape(args.model).to_json()}

@@ -531,3 +531,14 @@ def test_batched_decode_equals_one_by_one():
     waves = [0.1 * torch.randn(n, generator=g) for n in (8000, 5000, 9000, 6000)]
     outs = model.decode(waves)
     assert len(outs) == 4 and all(o.tokens[0] == spec.blank for o in outs)
+
+
+def test_inspect_reports_speech_checkpoints(tmp_path, capsys):
+    from flyingfish_b200 import cli
+    spec = parakeet_tiny()
+    d = tmp_path / "asr"
+    _write_model_dir(d, spec, 3)
+    assert cli.main(["--model", str(d), "inspect"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["family"] == "speech" and out["architecture"] == "ParakeetForTDT" and out["tensors"] == out["expected_tensors"]
+    assert out["spec"]["encoder"]["hidden"] == 128 and out["spec"]["durations"] == [0, 1, 2, 3, 4]

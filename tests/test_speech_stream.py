@@ -305,3 +305,8 @@ def test_nemo_archive_streams_and_cuts_utterances(tmp_path):
     with contextlib.redirect_stdout(buf):
         assert cli.main(["--cpu", "--model", str(arc), "transcribe", str(tmp_path / "w.wav"), "--stream", "--format", "json"]) == 0
     assert _json.loads(buf.getvalue())["text"] == res.text
+    buf = _io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert cli.main(["--model", str(arc), "inspect"]) == 0
+    info = _json.loads(buf.getvalue())
+    assert info["architecture"] == "nemo_rnnt" and info["spec"]["encoder"]["chunk_size"] == 2 and info["tensors"] > 50 and info["bytes"] > 0
