@@ -434,11 +434,12 @@ def cmd_inspect(args) -> dict:
     if p.is_dir():
         from .loaders.checkpoint import inspect_checkpoint
         arch = json.loads((p / "config.json").read_text()).get("architectures", [None])[0] if (p / "config.json").exists() else None
-        if arch in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration"):
+        if arch in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration", "Nemotron3_5AsrForRNNT"):
             # speech checkpoints: their own spec classes, contract check included
             from dataclasses import asdict
             from .speech import CanarySpec, ParakeetCtcSpec, ParakeetSpec
-            sp = {"ParakeetForTDT": ParakeetSpec, "ParakeetForCTC": ParakeetCtcSpec, "CanaryForConditionalGeneration": CanarySpec}[arch].read(p)
+            sp = {"ParakeetForTDT": ParakeetSpec, "Nemotron3_5AsrForRNNT": ParakeetSpec, "ParakeetForCTC": ParakeetCtcSpec,
+                  "CanaryForConditionalGeneration": CanarySpec}[arch].read(p)
             info = inspect_checkpoint(p)
             return {"family": "speech", "architecture": arch, "spec": asdict(sp), "expected_tensors": len(sp.expected_tensors()), **info}
         spec = read_model_spec(p)
@@ -487,12 +488,20 @@ def cmd_transcribe(args) -> None:
         (out_path.write_text(text) if out_path is not None else sys.stdout.write(text))
         return
     arch = json.loads((Path(args.model) / "config.json").read_text()).get("architectures", [None])[0]
-    if arch not in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration"):
+    if arch not in ("ParakeetForTDT", "ParakeetForCTC", "CanaryForConditionalGeneration", "Nemotron3_5AsrForRNNT"):
         raise SystemExit(f"unsupported transcription architecture {arch}")
     out_path = check_output_path(args.output, args.model) if args.output else None
     device = "cpu" if args.cpu else f"cuda:{args.device}"
     model = load_model(args.model, device)
     wave = load_audio(args.input, model.spec.mel.sampling_rate)
+    if arch == "Nemotron3_5AsrForRNNT":
+        # the prompt id conditions the encoder rows on a language: --source-lang names an entry of the prompt dictionary
+        table = dict(model.spec.prompt_dictionary)
+        if args.source_lang in table:
+            model.decoder.prompt_id = table[args.source_lang]
+        elif args.source_lang != "en":
+            raise SystemExit(f"--source-lang {args.source_lang} is not in the prompt dictionary ({', '.join(sorted(table))})")
+        args.source_lang = "en"
     if args.stream:
         # cache-aware streaming encoders only: audio goes in 320 ms pieces, one JSON line per piece that produced tokens
         from .speech import ParakeetModel, StreamingRecognizer

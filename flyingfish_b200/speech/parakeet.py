@@ -37,6 +37,12 @@ class ParakeetSpec:
     pad: int = 2
     durations: tuple[int, ...] = (0, 1, 2, 3, 4)       # empty: a plain transducer (RNN-T) without a duration head
     mel: LogMelConfig = field(default_factory=LogMelConfig)
+    # prompt-conditioned streaming RNN-T (``Nemotron3_5AsrForRNNT``): every encoder row, extended by the one-hot of a
+    # prompt id (a language), goes through a two-layer ReLU adapter before the joint projection
+    prompts: int = 0
+    prompt_intermediate: int = 0
+    default_prompt: int = 0
+    prompt_dictionary: tuple[tuple[str, int], ...] = ()
 
     @property
     def joint_out(self) -> int:
@@ -55,13 +61,16 @@ class ParakeetSpec:
     @classmethod
     def from_json(cls, root: dict, processor: dict, generation: dict) -> "ParakeetSpec":
         """``config.json``, ``processor_config.json`` and ``generation_config.json`` of a published checkpoint."""
-        if root.get("model_type") != "parakeet_tdt" or root.get("architectures") != ["ParakeetForTDT"]:
-            raise ValueError("not a Parakeet TDT configuration")
+        nemotron = root.get("model_type") == "nemotron3_5_asr" and root.get("architectures") == ["Nemotron3_5AsrForRNNT"]
+        if not nemotron and (root.get("model_type") != "parakeet_tdt" or root.get("architectures") != ["ParakeetForTDT"]):
+            raise ValueError("not a Parakeet TDT / Nemotron RNN-T configuration")
         if root.get("hidden_act") != "relu":
             raise ValueError("unsupported joint activation")
         enc = root.get("encoder_config")
-        if not isinstance(enc, dict) or enc.get("model_type") != "parakeet_encoder":
+        if not isinstance(enc, dict) or enc.get("model_type") != ("nemotron_asr_streaming_encoder" if nemotron else "parakeet_encoder"):
             raise ValueError("encoder_config missing")
+        if nemotron and (list(root.get("durations", [])) != [] or "sliding_window" not in enc):
+            raise ValueError("the prompt-conditioned RNN-T has no duration head and a streaming encoder")
         for key, want in (("hidden_act", "silu"), ("scale_input", False), ("subsampling_conv_kernel_size", 3),
                           ("subsampling_conv_stride", 2), ("subsampling_factor", 8)):
             if enc.get(key) != want:
@@ -98,10 +107,19 @@ class ParakeetSpec:
                                 sub_channels=int(enc["subsampling_conv_channels"]), attention_bias=bool(enc["attention_bias"]),
                                 convolution_bias=bool(enc["convolution_bias"]), max_position=int(enc["max_position_embeddings"]),
                                 **stream)
+        extra = {}
+        if nemotron:
+            table = processor.get("prompt_dictionary") or {}
+            if not isinstance(table, dict) or any(not (0 <= int(v) < int(root["num_prompts"])) for v in table.values()):
+                raise ValueError("prompt_dictionary is not a map of names to prompt ids")
+            extra = dict(prompts=int(root["num_prompts"]), prompt_intermediate=int(root["prompt_intermediate_size"]),
+                         default_prompt=int(root["default_prompt_id"]), prompt_dictionary=tuple(sorted((str(k), int(v)) for k, v in table.items())))
+            if not (0 <= extra["default_prompt"] < extra["prompts"]):
+                raise ValueError("default_prompt_id outside the prompt table")
         spec = cls(encoder=encoder, decoder_hidden=int(root["decoder_hidden_size"]), decoder_layers=int(root["num_decoder_layers"]),
                    vocab=int(root["vocab_size"]), blank=int(root["blank_token_id"]), max_symbols=int(root["max_symbols_per_step"]),
-                   eos=int(generation.get("eos_token_id", 3)), pad=int(root.get("pad_token_id", 2)),
-                   durations=tuple(int(d) for d in root["durations"]), mel=mel)
+                   eos=int(generation.get("eos_token_id", -1 if nemotron else 3)), pad=int(root.get("pad_token_id", 2)),
+                   durations=tuple(int(d) for d in root["durations"]), mel=mel, **extra)
         if generation.get("decoder_start_token_id", spec.blank) != spec.blank:
             raise ValueError("decoder start token differs from the blank")
         spec.check()
@@ -130,17 +148,28 @@ class ParakeetSpec:
         if e.chunk_size > 0:
             root["encoder_config"].update(sliding_window=e.left_chunks * e.chunk_size, default_num_lookahead_tokens=e.chunk_size - 1)
         m = self.mel
+        if self.prompts > 0:
+            root.update(architectures=["Nemotron3_5AsrForRNNT"], model_type="nemotron3_5_asr", num_prompts=self.prompts,
+                        prompt_intermediate_size=self.prompt_intermediate, default_prompt_id=self.default_prompt)
+            root["encoder_config"]["model_type"] = "nemotron_asr_streaming_encoder"
         processor = {"processor_class": "ParakeetProcessor", "blank_token": "<blank>",
                      "feature_extractor": {"feature_extractor_type": "ParakeetFeatureExtractor", "feature_size": m.mel_bins,
                                            "hop_length": m.hop_length, "n_fft": m.n_fft, "padding_side": "right", "padding_value": 0.0,
                                            "preemphasis": m.preemphasis, "return_attention_mask": True,
                                            "sampling_rate": m.sampling_rate, "win_length": m.win_length}}
         generation = {"decoder_start_token_id": self.blank, "eos_token_id": self.eos, "pad_token_id": self.pad}
+        if self.prompts > 0:
+            processor["prompt_dictionary"] = dict(self.prompt_dictionary)
         return root, processor, generation
 
     def expected_tensors(self) -> dict[str, tuple[str, tuple[int, ...]]]:
         out = self.encoder.expected_tensors()
         h, d = self.encoder.hidden, self.decoder_hidden
+        if self.prompts > 0:
+            out["prompt_projector.linear_1.weight"] = ("F32", (self.prompt_intermediate, h + self.prompts))
+            out["prompt_projector.linear_1.bias"] = ("F32", (self.prompt_intermediate,))
+            out["prompt_projector.linear_2.weight"] = ("F32", (h, self.prompt_intermediate))
+            out["prompt_projector.linear_2.bias"] = ("F32", (h,))
         out["encoder_projector.weight"] = ("F32", (d, h))
         out["encoder_projector.bias"] = ("F32", (d,))
         out["decoder.embedding.weight"] = ("F32", (self.vocab, d))
@@ -204,6 +233,15 @@ class TdtDecoder:
             return t.float().to(BF16).contiguous().to(dev)
 
         self.enc_proj = (w16(tensors["encoder_projector.weight"]), w16(tensors["encoder_projector.bias"]))
+        self.adapter = None
+        self.prompt_id = spec.default_prompt
+        if spec.prompts > 0:
+            # the one-hot prompt columns of the first layer are folded into one bias row per prompt id
+            h = spec.encoder.hidden
+            w1 = tensors["prompt_projector.linear_1.weight"].float()
+            bias_rows = tensors["prompt_projector.linear_1.bias"].float()[None, :] + w1[:, h:].t()
+            self.adapter = (w16(w1[:, :h]), w16(bias_rows), w16(tensors["prompt_projector.linear_2.weight"]),
+                            w16(tensors["prompt_projector.linear_2.bias"]))
         self.table = w16(tensors["decoder.embedding.weight"])
         self.w_pred = w16(tensors["decoder.decoder_projector.weight"])
         self.b_pred = tensors["decoder.decoder_projector.bias"].float().contiguous().to(dev)
@@ -235,7 +273,12 @@ class TdtDecoder:
         self.graph_replays = 0
 
     def project(self, encoded: torch.Tensor) -> torch.Tensor:
-        """[rows, hidden] BF16 encoder output -> [rows, decoder_hidden] BF16 in the joint space."""
+        """[rows, hidden] BF16 encoder output -> [rows, decoder_hidden] BF16 in the joint space (through the prompt
+        adapter of prompt-conditioned models: ``relu(W1 [row; onehot(prompt)] + b1)``, then ``W2 . + b2``)."""
+        if self.adapter is not None:
+            w1, bias_rows, w2, b2 = self.adapter
+            u = vision_ops.linear_bias_act(encoded, w1, bias_rows[self.prompt_id].contiguous(), "relu")
+            encoded = vision_ops.linear_bias_act(u, w2, b2, "none")
         return vision_ops.linear_bias_act(encoded, self.enc_proj[0], self.enc_proj[1], "none")
 
     def reset(self, valid_rows: list[int] | int) -> list[int]:
@@ -522,7 +565,7 @@ class ParakeetCtcModel:
 def load_model(directory: str | Path, device: torch.device | str = "cpu"):
     """The recognition model a checkpoint directory names in ``config.json``."""
     arch = json.loads((Path(directory) / "config.json").read_text()).get("architectures", [None])[0]
-    if arch == "ParakeetForTDT":
+    if arch in ("ParakeetForTDT", "Nemotron3_5AsrForRNNT"):
         return ParakeetModel.load(directory, device)
     if arch == "ParakeetForCTC":
         return ParakeetCtcModel.load(directory, device)
@@ -581,3 +624,10 @@ class StreamingRecognizer:
 
     def transcription(self) -> Transcription:
         return self.model.transcription(self.trajectory())
+
+
+def nemotron_tiny() -> ParakeetSpec:
+    """The streaming test shape with a prompt adapter: 6 prompt ids, 96-wide adapter, "auto" = id 4."""
+    from dataclasses import replace
+    return replace(streaming_tiny(), eos=-1, prompts=6, prompt_intermediate=96, default_prompt=4,
+                   prompt_dictionary=(("auto", 4), ("de", 2), ("en", 1)))

@@ -310,3 +310,44 @@ def test_nemo_archive_streams_and_cuts_utterances(tmp_path):
         assert cli.main(["--model", str(arc), "inspect"]) == 0
     info = _json.loads(buf.getvalue())
     assert info["architecture"] == "nemo_rnnt" and info["spec"]["encoder"]["chunk_size"] == 2 and info["tensors"] > 50 and info["bytes"] > 0
+
+
+def test_prompt_conditioned_rnnt(tmp_path, capsys):
+    import json
+    from test_speech import _write_model_dir
+    from flyingfish_b200 import cli
+    from flyingfish_b200.speech import ParakeetSpec, load_model, nemotron_tiny, write_wav
+    spec = nemotron_tiny()
+    root, processor, generation = spec.to_json()
+    assert root["architectures"] == ["Nemotron3_5AsrForRNNT"] and root["durations"] == [] and processor["prompt_dictionary"]["auto"] == 4
+    assert ParakeetSpec.from_json(root, processor, generation) == spec
+    exp = spec.expected_tensors()
+    assert exp["prompt_projector.linear_1.weight"] == ("F32", (96, 128 + 6)) and exp["prompt_projector.linear_2.weight"] == ("F32", (128, 96))
+    bad = dict(root, durations=[0, 1])
+    with pytest.raises(ValueError):
+        ParakeetSpec.from_json(bad, processor, generation)
+    # the adapter is the published arithmetic: relu(W1 [row; one-hot] + b1), W2 . + b2, then the joint projection
+    tensors = random_tensors(spec.expected_tensors(), 17)
+    model = ParakeetModel(spec, tensors)
+    g = torch.Generator().manual_seed(18)
+    rows = torch.randn(5, 128, generator=g).to(torch.bfloat16)
+    r = lambda t: t.to(torch.bfloat16).float()
+    for pid in (4, 1):
+        model.decoder.prompt_id = pid
+        got = model.decoder.project(rows).float()
+        onehot = torch.zeros(5, 6); onehot[:, pid] = 1.0
+        w1 = r(tensors["prompt_projector.linear_1.weight"])
+        u = torch.relu(torch.cat([rows.float(), onehot], 1) @ w1.t() + tensors["prompt_projector.linear_1.bias"])
+        c = r(u) @ r(tensors["prompt_projector.linear_2.weight"]).t() + tensors["prompt_projector.linear_2.bias"]
+        want = r(c) @ r(tensors["encoder_projector.weight"]).t() + tensors["encoder_projector.bias"]
+        assert (got - want).abs().max() < 3e-2, pid
+    # through files, the architecture switch, streaming and the prompt dictionary
+    d = tmp_path / "nemotron"
+    _write_model_dir(d, spec, 17)
+    loaded = load_model(d)
+    assert loaded.spec == spec and loaded.decoder.adapter is not None
+    write_wav(tmp_path / "in.wav", 0.2 * torch.randn(16000, generator=g), 16000)
+    assert cli.main(["--cpu", "--model", str(d), "transcribe", str(tmp_path / "in.wav"), "--stream", "--source-lang", "de", "--format", "json"]) == 0
+    assert set(json.loads(capsys.readouterr().out)) == {"text", "segments", "words"}
+    with pytest.raises(SystemExit, match="prompt dictionary"):
+        cli.main(["--cpu", "--model", str(d), "transcribe", str(tmp_path / "in.wav"), "--source-lang", "xx"])
