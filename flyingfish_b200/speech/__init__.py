@@ -2,5 +2,5 @@
 from .audio import LogMel, LogMelConfig, StreamingLogMel, load_audio, read_wav, resample, write_wav  # noqa: F401
 from .parakeet import (ParakeetCtcModel, ParakeetCtcSpec, ParakeetModel, ParakeetSpec, TdtDecoder, TdtTrajectory,  # noqa: F401
                        load_model, parakeet_tiny, transcribe, StreamingRecognizer, nemotron_tiny, streaming_tiny)
-from .transcript import TextSegment, Transcription, speaker_segments, tdt_cues, word_segments  # noqa: F401
+from .transcript import TextSegment, Transcription, speaker_segments, tdt_cues, to_rttm, word_segments  # noqa: F401
 from .canary import CanaryModel, CanarySpec, canary_prompt, canary_tiny  # noqa: F401

@@ -156,3 +156,17 @@ def speaker_segments(logits, speakers: int, attention_mask=None, threshold: floa
                 start = None
     found.sort(key=lambda t: (t[0], t[1]))
     return [TextSegment(a, b, f"speaker_{spk}") for a, spk, b in found]
+
+
+def to_rttm(file_id: str, segments: Sequence[TextSegment]) -> str:
+    """Speaker segments as RTTM lines (``SPEAKER <file> 1 <start> <duration> <NA> <NA> <label> <NA> <NA>``)."""
+    if not file_id or any(c.isspace() for c in file_id):
+        raise ValueError("RTTM file id must be one token")
+    out = []
+    for seg in segments:
+        if not (seg.start >= 0.0 and seg.end >= seg.start):
+            raise ValueError("segment times are not ordered")
+        if not seg.text or any(c.isspace() for c in seg.text):
+            raise ValueError("RTTM speaker label must be one token")
+        out.append(f"SPEAKER {file_id} 1 {seg.start:.3f} {seg.end - seg.start:.3f} <NA> <NA> {seg.text} <NA> <NA>\n")
+    return "".join(out)

@@ -542,3 +542,16 @@ def test_inspect_reports_speech_checkpoints(tmp_path, capsys):
     out = json.loads(capsys.readouterr().out)
     assert out["family"] == "speech" and out["architecture"] == "ParakeetForTDT" and out["tensors"] == out["expected_tensors"]
     assert out["spec"]["encoder"]["hidden"] == 128 and out["spec"]["durations"] == [0, 1, 2, 3, 4]
+
+
+def test_rttm_lines():
+    from flyingfish_b200.speech import speaker_segments, to_rttm
+    # frames x 2 speakers at 10 ms: speaker 0 on frames 0-1, speaker 1 on frames 1-2, the last frame masked out
+    logits = [4.0, -4.0, 4.0, 4.0, -4.0, 4.0, 4.0, 4.0]
+    segs = speaker_segments(logits, 2, attention_mask=[True, True, True, False], threshold=0.5, frame_seconds=0.01)
+    assert [(s.start, s.end, s.text) for s in segs] == [(0.0, 0.02, "speaker_0"), (0.01, 0.03, "speaker_1")]
+    assert to_rttm("clip", segs) == ("SPEAKER clip 1 0.000 0.020 <NA> <NA> speaker_0 <NA> <NA>\n"
+                                     "SPEAKER clip 1 0.010 0.020 <NA> <NA> speaker_1 <NA> <NA>\n")
+    assert speaker_segments([0.0], 1, frame_seconds=0.01) == []
+    with pytest.raises(ValueError):
+        to_rttm("two words", segs)
