@@ -43,6 +43,7 @@ constexpr int TC_Q_BYTES = TC_BM * TC_HD * 2;             // 32 KiB
 constexpr int TC_KV_BYTES = TC_BN * TC_HD * 2;            // 32 KiB per operand per stage
 constexpr int TC_SMEM = TC_Q_BYTES + (TC_KSTAGES + TC_VSTAGES) * TC_KV_BYTES + 1024;   // 225 KiB
 constexpr float TC_RESCALE_THRESHOLD = 8.0f;              // log2 units
+constexpr int TC_TWO_CTAS_DEFAULT = 1;
 
 struct alignas(8) TcBars {
   uint64_t q_full;
@@ -345,6 +346,255 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Two CTAs per SM. The same products and masks, arranged so that two CTAs fit one SM and fill each other's gaps: while
+// one CTA's softmax warps work through a tile, the other CTA's products own the tensor pipe. Per CTA: 97 KB of shared
+// memory (Q, ONE K tile, ONE V tile -- the K tile is free again right after Q Kᵀ, so the next one loads during the
+// softmax), 256 columns of tensor memory (S, single-buffered, and O; P is written over the first 64 columns of S by
+// the thread that owns the row, after it has taken its whole S row into registers), 6 warps (TMA, MMA, one softmax warp
+// per lane quadrant, a thread owning a full 128-column row). Inside a CTA the tile is a strict sequence
+// Q Kᵀ -> softmax -> P V -> next Q Kᵀ (the MMA warp waits for P V to finish before it lets the next product write S).
+// ------------------------------------------------------------------------------------------------
+constexpr int TC2_SMEM = TC_Q_BYTES + 2 * TC_KV_BYTES + 1024;       // 97 KiB
+
+struct alignas(8) Tc2Bars {
+  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, pv_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(192, 2)
+attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const int* __restrict__ block_table,
+                        const int* __restrict__ q_start, const int* __restrict__ q_lens,
+                        const int* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out, int hq, int hkv, int ldo,
+                        int max_blocks, int num_blocks, float scale_log2, int window, int causal, int* status,
+                        const float* __restrict__ sinks) {
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qlen = q_lens[b];
+  const int r0 = (gridDim.x - 1 - blockIdx.x) * TC_BM;            // long (late) query tiles first
+  if (r0 >= qlen) return;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Tc2Bars bars;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TC_Q_BYTES;
+  uint8_t* sV = sK + TC_KV_BYTES;
+  const int ctx = ctx_lens[b], qs = q_start[b];
+  const int kvh = h / (hq / hkv);
+  const int past = ctx - qlen;
+  const int real = min(TC_BM, qlen - r0);
+  const int last_key = causal ? past + r0 + real - 1 : ctx - 1;
+  const int first_key = window > 0 ? max(0, past + r0 - window + 1) : 0;
+  const int t0 = first_key / TC_BN, t1 = last_key / TC_BN + 1;
+  const int ntiles = t1 - t0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    mbar_init(&bars.q_full, 1); mbar_init(&bars.k_full, 1); mbar_init(&bars.k_empty, 1);
+    mbar_init(&bars.v_full, 1); mbar_init(&bars.v_empty, 1); mbar_init(&bars.s_full, 1);
+    mbar_init(&bars.p_full, 1); mbar_init(&bars.pv_done, 1);
+    bars.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars.tmem_base, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = bars.tmem_base;          // S: columns 0..127; P (packed BF16 pairs) over columns 0..63
+  const uint32_t tmem_o = bars.tmem_base + 128;
+  volatile int* abort_flag = &bars.abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars.q_full, TC_Q_BYTES);
+      tma_load_2d(sQ, &tmQ, &bars.q_full, h * TC_HD, qs + r0);
+      tma_load_2d(sQ + TC_BM * 128, &tmQ, &bars.q_full, h * TC_HD + 64, qs + r0);
+      bool ok = true, bad = false;
+      const int nblk = (ctx + TC_PAGE - 1) / TC_PAGE;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        int rows[2];
+        for (int pg = 0; pg < 2; ++pg) {
+          int page = (t0 + j) * 2 + pg;
+          if (page >= nblk) page = nblk - 1;                 // past the context: any valid page, its keys are masked
+          int blk = block_table[(size_t)b * max_blocks + page];
+          if (blk < 0 || blk >= num_blocks) { bad = true; blk = 0; }
+          rows[pg] = (blk * hkv + kvh) * TC_PAGE;
+        }
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(&bars.k_empty, ph ^ 1, abort_flag, status, KID_ATTN_PREFILL, 21)) { ok = false; break; }
+        mbar_expect_tx(&bars.k_full, TC_KV_BYTES);
+        for (int pg = 0; pg < 2; ++pg) {
+          tma_load_2d(sK + pg * 8192, &tmK, &bars.k_full, 0, rows[pg]);
+          tma_load_2d(sK + 16384 + pg * 8192, &tmK, &bars.k_full, 64, rows[pg]);
+        }
+        if (!mbar_wait(&bars.v_empty, ph ^ 1, abort_flag, status, KID_ATTN_PREFILL, 22)) { ok = false; break; }
+        mbar_expect_tx(&bars.v_full, TC_KV_BYTES);
+        for (int pg = 0; pg < 2; ++pg) {
+          tma_load_2d(sV + pg * 8192, &tmV, &bars.v_full, 0, rows[pg]);
+          tma_load_2d(sV + 16384 + pg * 8192, &tmV, &bars.v_full, 64, rows[pg]);
+        }
+      }
+      if (bad) set_status(status, KID_ATTN_PREFILL, FF_ERR_BOUNDS, b, r0 / TC_BM);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc(1, 1, 0, 0, TC_BM, TC_BN);
+      const uint32_t idesc_o = umma_idesc(1, 1, 0, 1, TC_BM, TC_HD);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool ok = mbar_wait(&bars.q_full, 0, abort_flag, status, KID_ATTN_PREFILL, 23);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(&bars.k_full, ph, abort_flag, status, KID_ATTN_PREFILL, 24)) { ok = false; break; }
+        // S is written over the P of the previous tile: that tile's P V has to be complete
+        if (j > 0 && !mbar_wait(&bars.pv_done, ph ^ 1, abort_flag, status, KID_ATTN_PREFILL, 25)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_f16(tmem_s, umma_desc_sw128(q_addr + off, 16, 1024), umma_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(&bars.s_full);
+        umma_commit(&bars.k_empty);
+        if (!mbar_wait(&bars.p_full, ph, abort_flag, status, KID_ATTN_PREFILL, 26)) { ok = false; break; }
+        if (!mbar_wait(&bars.v_full, ph, abort_flag, status, KID_ATTN_PREFILL, 27)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t db = umma_desc_sw128(v_addr + (k >> 2) * 8192 + (k & 3) * 2048, 16384, 1024);
+          umma_f16_ts(tmem_o, tmem_s + k * 8, db, idesc_o, (j > 0) || (k != 0));
+        }
+        umma_commit(&bars.pv_done);
+        umma_commit(&bars.v_empty);
+      }
+    }
+  } else {
+    // softmax: warp w owns the 32 lanes of quadrant w % 4; thread = one query row, all 128 columns
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int e = (warp - 2) * 32 + lane;
+    const bool live = row < real;
+    const int pos = past + r0 + row;
+    const int hi = live ? (causal ? pos : ctx - 1) : -1;
+    const int lo = (live && window > 0) ? max(0, pos - window + 1) : 0;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    const uint32_t lane_base = (uint32_t(q * 32) << 16);
+    const int tile_hi_min = causal ? past + r0 : ctx - 1;
+    const int tile_lo_max = window > 0 ? max(0, past + r0 + real - window) : 0;
+    for (int j = 0; j < ntiles; ++j) {
+      if (ok && !mbar_wait(&bars.s_full, j & 1, abort_flag, status, KID_ATTN_PREFILL, 28)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        float sv[TC_BN];
+        {
+          uint32_t r[TC_BN];
+#pragma unroll
+          for (int c = 0; c < TC_BN; c += 32) tmem_ld_x32(tmem_s + lane_base + c, r + c);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < TC_BN; ++i) sv[i] = __uint_as_float(r[i]);
+        }
+        const int k0 = (t0 + j) * TC_BN;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (k0 >= tile_lo_max && k0 + TC_BN - 1 <= tile_hi_min) {
+#pragma unroll
+          for (int i = 0; i < TC_BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < TC_BN; ++i) {
+            const int key = k0 + i;
+            const float t = (key >= lo && key <= hi) ? sv[i] : -INFINITY;
+            sv[i] = t;
+            mx4[i & 3] = fmaxf(mx4[i & 3], t);
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        // the previous P V is complete (the MMA warp waited for it before it let this tile's Q Kᵀ write S), so O may be
+        // rescaled and P written without a further wait
+        float alpha = 1.f;
+        bool need = false;
+        if (mx > m_ref + TC_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx > -INFINITY)) {
+          alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mx);
+          m_ref = mx;
+          need = j > 0;
+        }
+        if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+          for (int c = 0; c < TC_HD; c += 16) {
+            uint32_t r[16];
+            tmem_ld_x16(tmem_o + lane_base + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_x16(tmem_o + lane_base + c, r);
+          }
+          tmem_st_wait();
+        }
+        l_sum *= alpha;
+        const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
+        float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < TC_BN / 2; c += 16) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2_approx(fmaf(sv[2 * (c + i)], scale_log2, -mr));
+            const float p1 = ex2_approx(fmaf(sv[2 * (c + i) + 1], scale_log2, -mr));
+            pk[i] = pack_bf16x2(p0, p1);
+            ls4[i & 3] += p0 + p1;
+          }
+          // P over the first 64 columns of S: this thread's own lane, whose S values are all in registers by now
+          tmem_st_x16(tmem_s + lane_base + c, pk);
+        }
+        tmem_st_wait();
+        l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        tc_fence_before();
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (e == 0 && ok) mbar_arrive(&bars.p_full);
+    }
+    // the last P V
+    if (ok && !mbar_wait(&bars.pv_done, (ntiles - 1) & 1, abort_flag, status, KID_ATTN_PREFILL, 29)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      if (sinks != nullptr) l_sum += (m_ref == -INFINITY) ? 1.f : exp2f(sinks[h] * 1.4426950408889634f - m_ref);
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      __nv_bfloat16* orow = out + (size_t)(qs + r0 + row) * ldo + (size_t)h * TC_HD;
+#pragma unroll
+      for (int c = 0; c < TC_HD; c += 16) {
+        uint32_t r[16];
+        tmem_ld_x16(tmem_o + lane_base + c, r);
+        tmem_ld_wait();
+        if (live) {
+          uint4 o0, o1;
+          o0.x = pack_bf16x2(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          o0.y = pack_bf16x2(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          o0.z = pack_bf16x2(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          o0.w = pack_bf16x2(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          o1.x = pack_bf16x2(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+          o1.y = pack_bf16x2(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+          o1.z = pack_bf16x2(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+          o1.w = pack_bf16x2(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+          *reinterpret_cast<uint4*>(orow + c) = o0;
+          *reinterpret_cast<uint4*>(orow + c + 8) = o1;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (bars.abort_flag) {
+    const uint64_t t0w = globaltimer_ns();
+    while (globaltimer_ns() - t0w < 200000ull) { __nanosleep(1000); }
+  }
+  if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(bars.tmem_base, 256); }
+}
+
 }  // namespace ff
 using namespace ff;
 
@@ -363,9 +613,20 @@ FF_EXPORT int ff_attn_prefill_tc(const void* q, const void* kcache, const void* 
   const uint64_t cache_rows = (uint64_t)num_blocks * hkv * TC_PAGE;
   if (int r = make_tmap_2d(&tmK, kcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, TC_HD, cache_rows, TC_HD * 2, 64, TC_PAGE)) return r;
   if (int r = make_tmap_2d(&tmV, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, TC_HD, cache_rows, TC_HD * 2, 64, TC_PAGE)) return r;
-  if (int r = opt_in_smem(attn_prefill_tc_kernel, TC_SMEM)) return r;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid((max_q_len + TC_BM - 1) / TC_BM, hq, batch);
+  // FF_ATTN_PREFILL_CTAS = 1 selects the one-CTA-per-SM kernel (deep K / V rings, eight softmax warps); the default is the
+  // two-CTAs-per-SM kernel
+  static int two = -1;
+  if (two < 0) { const char* e = getenv("FF_ATTN_PREFILL_CTAS"); two = (e != nullptr && e[0] == '1') ? 0 : TC_TWO_CTAS_DEFAULT; }
+  if (two) {
+    if (int r = opt_in_smem(attn_prefill_tc2_kernel, TC2_SMEM)) return r;
+    attn_prefill_tc2_kernel<<<grid, 192, TC2_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
+                                                        (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
+                                                        window < 0 ? 0 : window, window < 0 ? 0 : 1, status, sinks);
+    return launch_result();
+  }
+  if (int r = opt_in_smem(attn_prefill_tc_kernel, TC_SMEM)) return r;
   attn_prefill_tc_kernel<<<grid, 320, TC_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
                                                     (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
                                                     window < 0 ? 0 : window, window < 0 ? 0 : 1, status, sinks);
