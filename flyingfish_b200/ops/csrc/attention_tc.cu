@@ -44,6 +44,7 @@ constexpr int TC_KV_BYTES = TC_BN * TC_HD * 2;            // 32 KiB per operand 
 constexpr int TC_SMEM = TC_Q_BYTES + (TC_KSTAGES + TC_VSTAGES) * TC_KV_BYTES + 1024;   // 225 KiB
 constexpr float TC_RESCALE_THRESHOLD = 8.0f;              // log2 units
 constexpr int TC_TWO_CTAS_DEFAULT = 1;
+constexpr int TC2_SPLIT_DEFAULT = 1;
 
 struct alignas(8) TcBars {
   uint64_t q_full;
@@ -362,9 +363,11 @@ struct alignas(8) Tc2Bars {
   uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, pv_done;
   uint32_t tmem_base;
   int abort_flag;
+  float xmax[2][TC_BM];
 };
 
-__global__ void __launch_bounds__(192, 2)
+template <int SPLIT>
+__global__ void __launch_bounds__(64 + 128 * SPLIT, 2)
 attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const int* __restrict__ block_table,
                         const int* __restrict__ q_start, const int* __restrict__ q_lens,
@@ -471,8 +474,12 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       }
     }
   } else {
-    // softmax: warp w owns the 32 lanes of quadrant w % 4; thread = one query row, all 128 columns
+    // softmax: warp w owns the 32 lanes of quadrant w % 4. SPLIT = 1: a thread = one query row, all 128 columns.
+    // SPLIT = 2: two warps per quadrant, each owning 64 of the columns (row maxima and sums cross the pair through
+    // shared memory), so that four softmax warps per scheduler interleave over the two resident CTAs.
+    constexpr int HB = TC_BN / SPLIT;
     const int q = warp & 3;
+    const int hf = (warp - 2) >> 2;
     const int row = q * 32 + lane;
     const int e = (warp - 2) * 32 + lane;
     const bool live = row < real;
@@ -487,32 +494,41 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     for (int j = 0; j < ntiles; ++j) {
       if (ok && !mbar_wait(&bars.s_full, j & 1, abort_flag, status, KID_ATTN_PREFILL, 28)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
+      float sv[HB];
+      float mx = -INFINITY;
       if (ok) {
         tc_fence_after();
-        float sv[TC_BN];
         {
-          uint32_t r[TC_BN];
+          uint32_t r[HB];
 #pragma unroll
-          for (int c = 0; c < TC_BN; c += 32) tmem_ld_x32(tmem_s + lane_base + c, r + c);
+          for (int c = 0; c < HB; c += 32) tmem_ld_x32(tmem_s + lane_base + hf * HB + c, r + c);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < TC_BN; ++i) sv[i] = __uint_as_float(r[i]);
+          for (int i = 0; i < HB; ++i) sv[i] = __uint_as_float(r[i]);
         }
-        const int k0 = (t0 + j) * TC_BN;
+        const int k0 = (t0 + j) * TC_BN + hf * HB;
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if (k0 >= tile_lo_max && k0 + TC_BN - 1 <= tile_hi_min) {
+        if ((t0 + j) * TC_BN >= tile_lo_max && (t0 + j) * TC_BN + TC_BN - 1 <= tile_hi_min) {
 #pragma unroll
-          for (int i = 0; i < TC_BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+          for (int i = 0; i < HB; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
         } else {
 #pragma unroll
-          for (int i = 0; i < TC_BN; ++i) {
+          for (int i = 0; i < HB; ++i) {
             const int key = k0 + i;
             const float t = (key >= lo && key <= hi) ? sv[i] : -INFINITY;
             sv[i] = t;
             mx4[i & 3] = fmaxf(mx4[i & 3], t);
           }
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      }
+      if (SPLIT == 2) {
+        // both warps of the pair have their S columns in registers after this barrier: P may overwrite S
+        bars.xmax[hf][row] = mx;
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+        mx = fmaxf(mx, bars.xmax[hf ^ 1][row]);
+      }
+      if (ok) {
         // the previous P V is complete (the MMA warp waited for it before it let this tile's Q Kᵀ write S), so O may be
         // rescaled and P written without a further wait
         float alpha = 1.f;
@@ -524,13 +540,13 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
-          for (int c = 0; c < TC_HD; c += 16) {
+          for (int c = 0; c < TC_HD / SPLIT; c += 16) {
             uint32_t r[16];
-            tmem_ld_x16(tmem_o + lane_base + c, r);
+            tmem_ld_x16(tmem_o + lane_base + hf * (TC_HD / SPLIT) + c, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_x16(tmem_o + lane_base + c, r);
+            tmem_st_x16(tmem_o + lane_base + hf * (TC_HD / SPLIT) + c, r);
           }
           tmem_st_wait();
         }
@@ -538,7 +554,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         const float mr = (m_ref == -INFINITY) ? 0.f : m_ref;
         float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < TC_BN / 2; c += 16) {
+        for (int c = 0; c < HB / 2; c += 16) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -547,28 +563,34 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             pk[i] = pack_bf16x2(p0, p1);
             ls4[i & 3] += p0 + p1;
           }
-          // P over the first 64 columns of S: this thread's own lane, whose S values are all in registers by now
-          tmem_st_x16(tmem_s + lane_base + c, pk);
+          // P over the first 64 columns of S: this thread's own lane; every S value of the lane is in registers by now
+          tmem_st_x16(tmem_s + lane_base + hf * (HB / 2) + c, pk);
         }
         tmem_st_wait();
         l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         tc_fence_before();
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (SPLIT == 2) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 1, 128;" ::: "memory");
       if (e == 0 && ok) mbar_arrive(&bars.p_full);
     }
     // the last P V
     if (ok && !mbar_wait(&bars.pv_done, (ntiles - 1) & 1, abort_flag, status, KID_ATTN_PREFILL, 29)) ok = false;
     ok = __all_sync(0xffffffffu, ok);
+    if (SPLIT == 2) {
+      bars.xmax[hf][row] = l_sum;
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory");
+      l_sum += bars.xmax[hf ^ 1][row];
+    }
     if (ok) {
       tc_fence_after();
       if (sinks != nullptr) l_sum += (m_ref == -INFINITY) ? 1.f : exp2f(sinks[h] * 1.4426950408889634f - m_ref);
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-      __nv_bfloat16* orow = out + (size_t)(qs + r0 + row) * ldo + (size_t)h * TC_HD;
+      __nv_bfloat16* orow = out + (size_t)(qs + r0 + row) * ldo + (size_t)h * TC_HD + hf * (TC_HD / SPLIT);
 #pragma unroll
-      for (int c = 0; c < TC_HD; c += 16) {
+      for (int c = 0; c < TC_HD / SPLIT; c += 16) {
         uint32_t r[16];
-        tmem_ld_x16(tmem_o + lane_base + c, r);
+        tmem_ld_x16(tmem_o + lane_base + hf * (TC_HD / SPLIT) + c, r);
         tmem_ld_wait();
         if (live) {
           uint4 o0, o1;
@@ -620,10 +642,20 @@ FF_EXPORT int ff_attn_prefill_tc(const void* q, const void* kcache, const void* 
   static int two = -1;
   if (two < 0) { const char* e = getenv("FF_ATTN_PREFILL_CTAS"); two = (e != nullptr && e[0] == '1') ? 0 : TC_TWO_CTAS_DEFAULT; }
   if (two) {
-    if (int r = opt_in_smem(attn_prefill_tc2_kernel, TC2_SMEM)) return r;
-    attn_prefill_tc2_kernel<<<grid, 192, TC2_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
-                                                        (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
-                                                        window < 0 ? 0 : window, window < 0 ? 0 : 1, status, sinks);
+    // FF_ATTN_PREFILL_SPLIT = 2: two softmax warps per lane quadrant (64 columns each) instead of one
+    static int split = -1;
+    if (split < 0) { const char* e = getenv("FF_ATTN_PREFILL_SPLIT"); split = (e != nullptr && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : TC2_SPLIT_DEFAULT; }
+    if (split == 2) {
+      if (int r = opt_in_smem(attn_prefill_tc2_kernel<2>, TC2_SMEM)) return r;
+      attn_prefill_tc2_kernel<2><<<grid, 320, TC2_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
+                                                             (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
+                                                             window < 0 ? 0 : window, window < 0 ? 0 : 1, status, sinks);
+      return launch_result();
+    }
+    if (int r = opt_in_smem(attn_prefill_tc2_kernel<1>, TC2_SMEM)) return r;
+    attn_prefill_tc2_kernel<1><<<grid, 192, TC2_SMEM, s>>>(tmQ, tmK, tmV, block_table, q_start, q_lens, ctx_lens,
+                                                           (__nv_bfloat16*)out, hq, hkv, ldo, max_blocks, num_blocks, scale_log2,
+                                                           window < 0 ? 0 : window, window < 0 ? 0 : 1, status, sinks);
     return launch_result();
   }
   if (int r = opt_in_smem(attn_prefill_tc_kernel, TC_SMEM)) return r;
