@@ -119,6 +119,14 @@ def _global_parser() -> argparse.ArgumentParser:
     tr.add_argument("--target-lang", default="en")
     tr.add_argument("--no-pnc", action="store_true", help="Canary: no punctuation and capitalisation")
 
+    dz = sub.add_parser("diarize")
+    dz.add_argument("input", help="RIFF/WAVE file (mixed down and resampled to the model's rate)")
+    dz.add_argument("--format", choices=["rttm", "json"], default="rttm")
+    dz.add_argument("--output", help="file to write instead of standard output")
+    dz.add_argument("--stream", action="store_true", help="chunk-wise with look-ahead, as live audio would arrive")
+    dz.add_argument("--mode", help="streaming latency mode named in the processor configuration")
+    dz.add_argument("--threshold", type=float, default=0.5, help="speaker activity probability that counts as speech")
+
     for name in DSPARK_TOOLS:
         dp = sub.add_parser(name)
         dp.add_argument("--prompt-tokens", type=int, default=48)
@@ -195,8 +203,8 @@ def check_flags(args) -> None:
                              "(verification rows and shared prefixes read BF16 pages)")
     if args.tp < 1 or (args.tp > 1 and args.cpu):
         raise SystemExit("--tp needs one CUDA device per rank")
-    if args.command == "transcribe" and (args.draft_model or args.prefix_cache or args.kv_format != "bf16"):
-        raise SystemExit("transcribe takes none of the text-generation flags")
+    if args.command in ("transcribe", "diarize") and (args.draft_model or args.prefix_cache or args.kv_format != "bf16"):
+        raise SystemExit(f"{args.command} takes none of the text-generation flags")
     if args.tp > 1 and args.command not in ("generate", "bench", "serve"):
         raise SystemExit(f"--tp applies to generate, bench and serve, not to {args.command}")
     if args.command in DSPARK_TOOLS and not args.draft_model:
@@ -533,6 +541,35 @@ def cmd_transcribe(args) -> None:
         sys.stdout.write(text)
 
 
+def cmd_diarize(args) -> None:
+    """Who spoke when, for one audio file (src/main.rs `diarize` of the reference: RTTM or JSON segments)."""
+    from .speech import load_audio
+    from .speech.diarization import ARCHITECTURE, load_model
+    from .speech.transcript import to_rttm
+    if not args.model:
+        raise SystemExit("diarize needs --model")
+    arch = json.loads((Path(args.model) / "config.json").read_text()).get("architectures", [None])[0]
+    if arch != ARCHITECTURE:
+        raise SystemExit(f"unsupported diarization architecture {arch}")
+    if not (0.0 <= args.threshold <= 1.0):
+        raise SystemExit("--threshold must lie in [0, 1]")
+    out_path = check_output_path(args.output, args.model) if args.output else None
+    model = load_model(args.model, "cpu" if args.cpu else f"cuda:{args.device}")
+    if args.mode is not None and not args.stream:
+        raise SystemExit("--mode applies to --stream")
+    wave = load_audio(args.input, model.spec.mel.sampling_rate)
+    segments = model.diarize(wave, stream=args.stream, threshold=args.threshold, mode=args.mode)
+    if args.format == "rttm":
+        stem = "".join(c if not c.isspace() else "_" for c in Path(args.input).stem) or "audio"
+        text = to_rttm(stem, segments)
+    else:
+        text = json.dumps([{"start": s.start, "end": s.end, "speaker": s.text} for s in segments]) + "\n"
+    if out_path is not None:
+        out_path.write_text(text)
+    else:
+        sys.stdout.write(text)
+
+
 def cmd_serve(args) -> None:
     from .loaders.tokenizer import read_chat_template
     from .serve.http import run
@@ -604,6 +641,9 @@ def main(argv: list[str] | None = None) -> int:
         return 0
     if args.command == "transcribe":
         cmd_transcribe(args)
+        return 0
+    if args.command == "diarize":
+        cmd_diarize(args)
         return 0
     out = handlers[args.command](args)
     if _world()[1] == 0:

@@ -4,3 +4,4 @@ from .parakeet import (ParakeetCtcModel, ParakeetCtcSpec, ParakeetModel, Parakee
                        load_model, parakeet_tiny, transcribe, StreamingRecognizer, nemotron_tiny, streaming_tiny)
 from .transcript import TextSegment, Transcription, speaker_segments, tdt_cues, to_rttm, word_segments  # noqa: F401
 from .canary import CanaryModel, CanarySpec, canary_prompt, canary_tiny  # noqa: F401
+from .diarization import DiarizationModel, DiarizationSpec, DiarizationStream, diarization_tiny, select_cache_rows  # noqa: F401
