@@ -118,6 +118,7 @@ def _global_parser() -> argparse.ArgumentParser:
     tr.add_argument("--source-lang", default="en")
     tr.add_argument("--target-lang", default="en")
     tr.add_argument("--no-pnc", action="store_true", help="Canary: no punctuation and capitalisation")
+    tr.add_argument("--diarization-model", help="multitalker archives: diarization checkpoint whose speaker activity selects the lanes")
 
     dz = sub.add_parser("diarize")
     dz.add_argument("input", help="RIFF/WAVE file (mixed down and resampled to the model's rate)")
@@ -488,9 +489,24 @@ def cmd_transcribe(args) -> None:
         raise SystemExit("transcribe needs --model")
     if str(args.model).endswith(".nemo"):
         # NeMo archive of a streaming RNN-T (end-of-utterance models): --stream cuts the text into timed utterances
+        from .loaders.pth import read_nemo_member
         from .speech.nemo import transcribe_nemo
         out_path = check_output_path(args.output, None) if args.output else None
         wave = load_audio(args.input, 16000)
+        if b"spk_kernel_type" in read_nemo_member(args.model, "model_config.yaml"):
+            # speaker-attributed recognition: one transcript per speaker the diarizer hears
+            from .speech.multitalker import transcribe_multitalker
+            if not args.diarization_model:
+                raise SystemExit("a multitalker archive needs --diarization-model (speaker activity selects its lanes)")
+            if args.format not in ("txt", "json"):
+                raise SystemExit("speaker-attributed transcripts come as txt or json")
+            res = transcribe_multitalker(args.model, args.diarization_model, wave, "cpu" if args.cpu else f"cuda:{args.device}",
+                                         stream_diarizer=args.stream)
+            text = res.to_text() if args.format == "txt" else res.to_json() + "\n"
+            (out_path.write_text(text) if out_path is not None else sys.stdout.write(text))
+            return
+        if args.diarization_model:
+            raise SystemExit("--diarization-model applies to multitalker archives")
         result = transcribe_nemo(args.model, wave, "cpu" if args.cpu else f"cuda:{args.device}", stream=args.stream)
         text = {"txt": result.text + "\n", "json": result.to_json() + "\n", "srt": result.to_srt(), "vtt": result.to_vtt()}[args.format]
         (out_path.write_text(text) if out_path is not None else sys.stdout.write(text))

@@ -375,10 +375,23 @@ class ConformerStream:
         rows [m, hidden] that became complete, whole chunks at a time; ``last`` flushes the tail of the utterance."""
         if self.finished:
             raise RuntimeError("the stream is finished")
+        out = [self._layers(h) for _, h in self.stem_chunks(frames, last)]
+        if not out:
+            return torch.zeros(0, self.spec.hidden, dtype=torch.bfloat16, device=self.enc.device)
+        return torch.cat(out, dim=0)
+
+    def stem_chunks(self, frames: torch.Tensor, last: bool = False):
+        """Appends mel frames and yields ``(first_row, stem rows)`` for every chunk that became complete: the rows as
+        they enter the first layer. ``push`` runs them through this stream's layers; a caller that conditions the
+        rows first (several lanes over one audio stream, each with layer caches of its own) drives ``_layers`` of
+        other streams with them."""
+        if self.finished:
+            raise RuntimeError("the stream is finished")
         s = self.spec
         self.frames = torch.cat([self.frames, frames.to(self.frames.device, torch.float32)], dim=0)
         n = self.frames.shape[0]
-        out = []
+        if last:
+            self.finished = True
         while True:
             # row r is complete once frame 8r (its newest input) has arrived
             complete = (n - 1) // 8 + 1 if n > 0 else 0
@@ -391,10 +404,6 @@ class ConformerStream:
             else:
                 break
             h = self._stem(self.rows_out, take, last and take == avail)
-            out.append(self._layers(h.contiguous()))
+            first = self.rows_out
             self.rows_out += take
-        if last:
-            self.finished = True
-        if not out:
-            return torch.zeros(0, s.hidden, dtype=torch.bfloat16, device=self.enc.device)
-        return torch.cat(out, dim=0)
+            yield first, h.contiguous()

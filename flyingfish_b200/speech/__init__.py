@@ -5,3 +5,4 @@ from .parakeet import (ParakeetCtcModel, ParakeetCtcSpec, ParakeetModel, Parakee
 from .transcript import TextSegment, Transcription, speaker_segments, tdt_cues, to_rttm, word_segments  # noqa: F401
 from .canary import CanaryModel, CanarySpec, canary_prompt, canary_tiny  # noqa: F401
 from .diarization import DiarizationModel, DiarizationSpec, DiarizationStream, diarization_tiny, select_cache_rows  # noqa: F401
+from .multitalker import MultitalkerModel, MultitalkerSpec, MultitalkerStream, transcribe_multitalker  # noqa: F401

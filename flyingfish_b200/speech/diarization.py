@@ -564,9 +564,10 @@ class DiarizationModel:
     def stream(self, mode: str | None = None) -> "DiarizationStream":
         return DiarizationStream(self, self.spec.stream_config(mode))
 
-    def diarize(self, waveform: torch.Tensor, stream: bool = False, threshold: float = DEFAULT_THRESHOLD,
-                mode: str | None = None, block_samples: int | None = None) -> list[TextSegment]:
-        """A mono waveform at the model's sampling rate -> speaker segments ``speaker_<slot>``."""
+    def clip_logits(self, waveform: torch.Tensor, stream: bool = False, mode: str | None = None,
+                    block_samples: int | None = None) -> torch.Tensor:
+        """A mono waveform at the model's sampling rate -> frame logits [frames, speakers]: through the offline chunking,
+        or chunk by chunk with look-ahead as live audio would arrive (``stream``; samples go in blocks of one second)."""
         s = self.spec
         if stream:
             st = self.stream(mode)
@@ -574,16 +575,29 @@ class DiarizationModel:
             pieces = []
             for off in range(0, waveform.numel(), block):
                 pieces.append(st.push(waveform[off:off + block], last=off + block >= waveform.numel()))
-            logits = torch.cat(pieces, 0)
-            valid = [True] * logits.shape[0]
-        else:
-            feat, lens = self.mel.extract([waveform], normalize=False)
-            n = int(lens[0])
-            logits = self.offline(feat[0, :n])
-            valid = [True] * n
+            return torch.cat(pieces, 0)
+        feat, lens = self.mel.extract([waveform], normalize=False)
+        return self.offline(feat[0, : int(lens[0])])
+
+    def diarize(self, waveform: torch.Tensor, stream: bool = False, threshold: float = DEFAULT_THRESHOLD,
+                mode: str | None = None, block_samples: int | None = None) -> list[TextSegment]:
+        """A mono waveform at the model's sampling rate -> speaker segments ``speaker_<slot>``."""
+        logits = self.clip_logits(waveform, stream, mode, block_samples)
         if logits.shape[0] == 0:
             return []
-        return speaker_segments(logits.cpu(), s.speakers, valid, threshold, s.frame_seconds)
+        return speaker_segments(logits.cpu(), self.spec.speakers, [True] * logits.shape[0], threshold, self.spec.frame_seconds)
+
+
+def speaker_masks(model: DiarizationModel, waveform: torch.Tensor, stream: bool = False, threshold: float = DEFAULT_THRESHOLD,
+                  mode: str | None = None) -> tuple[torch.Tensor, float]:
+    """Binarised speaker activity at the encoder's row grid, pooled as the speaker cache pools it: the mean sigmoid over
+    each ``factor`` consecutive frames against the threshold (a trailing partial group is dropped). Returns
+    ``([rows, speakers] bool, seconds per row)`` (src/diarization.rs ``speaker_masks`` of the reference)."""
+    s = model.spec
+    logits = model.clip_logits(waveform, stream, mode).float().cpu()
+    rows = logits.shape[0] // s.factor
+    pooled = torch.sigmoid(logits[: rows * s.factor].double()).reshape(rows, s.factor, s.speakers).mean(dim=1)
+    return pooled > threshold, s.frame_seconds * s.factor
 
 
 class DiarizationStream:

@@ -34,7 +34,13 @@ def spec_from_yaml(text: str) -> ParakeetSpec:
             raise ValueError("unsupported decoder / joint variant")
         if int(enc["subsampling_factor"]) != 8 or int(pre.get("frame_splicing", 1)) != 1:
             raise ValueError("unsupported sub-sampling")
-        left, right = (int(v) for v in enc["att_context_size"])
+        context = enc["att_context_size"]
+        if context and isinstance(context[0], (list, tuple)):
+            # several training-time context modes: inference runs the first one, and all share the left context
+            if any(len(pair) != 2 or int(pair[0]) != int(context[0][0]) for pair in context):
+                raise ValueError("att_context_size modes differ in their left context")
+            context = context[0]
+        left, right = (int(v) for v in context)
         chunk = right + 1
         if left % chunk:
             raise ValueError(f"left context {left} does not divide by the chunk of {chunk} rows")

@@ -352,38 +352,61 @@ class TdtDecoder:
             if steps > limit + CHECK_EVERY:
                 raise RuntimeError("decode did not finish within its capacity")
 
-    # -- streaming: rows arrive in pieces, the device state carries on (utterance row 0) ---------------------
-    def begin_stream(self) -> None:
-        self.reset([1])
+    # -- streaming: rows arrive in pieces, the device state carries on (one utterance row per lane) ----------
+    def begin_stream(self, lanes: int = 1) -> None:
+        """Opens ``lanes`` independent streams (batch rows 0 .. lanes - 1): separate prediction-network states, encoder
+        row buffers and trajectories, stepping together whenever more than one has rows to decode."""
+        if not (0 < lanes <= self.max_batch):
+            raise ValueError(f"streams take 1..{self.max_batch} lanes")
+        self.reset([1] * lanes)
         st = self.state.tolist()
-        st[0][TS_VALID], st[0][TS_CAP], st[0][TS_DONE] = 0, self.traj[0].shape[1], 1
+        for lane in range(lanes):
+            st[lane][TS_VALID], st[lane][TS_CAP], st[lane][TS_DONE] = 0, self.traj[0].shape[1], 1
         self.state.copy_(torch.tensor(st, dtype=torch.int32))
-        self._rows = 0
-        self._taken = 1                                  # trajectory entries already handed out (the initial blank)
+        self._lanes = lanes
+        self._rows = [0] * lanes
+        self._taken = [1] * lanes                        # trajectory entries already handed out (the initial blank)
 
     def extend(self, projected: torch.Tensor) -> TdtTrajectory:
         """Appends projected encoder rows and decodes as far as they reach; returns the new trajectory entries."""
-        n = projected.shape[0]
-        if self._rows + n > self.max_rows:
-            raise ValueError(f"stream longer than {self.max_rows} encoder rows")
+        return self.extend_lanes({0: projected})[0]
+
+    def extend_lanes(self, projected: dict[int, torch.Tensor]) -> dict[int, TdtTrajectory]:
+        """Appends projected encoder rows to the named lanes and decodes them together as far as their rows reach; the
+        other lanes stay parked with their state untouched. Returns the new trajectory entries per named lane (frames
+        count the lane's own rows)."""
+        for lane, rows in projected.items():
+            if not (0 <= lane < self._lanes):
+                raise ValueError(f"lane {lane} outside the {self._lanes} open streams")
+            if self._rows[lane] + rows.shape[0] > self.max_rows:
+                raise ValueError(f"stream longer than {self.max_rows} encoder rows")
         if self.use_graph and self._graph is None:
             self._capture()                              # the capture leaves the state as it found it
-        if n:
-            self.enc[0, self._rows: self._rows + n].copy_(projected)
-            self._rows += n
+        for lane, rows in projected.items():
+            n = rows.shape[0]
+            if n:
+                self.enc[lane, self._rows[lane]: self._rows[lane] + n].copy_(rows)
+                self._rows[lane] += n
         st = self.state.tolist()
-        s0 = st[0]
-        stopped_on_eos = s0[TS_DONE] and s0[TS_COUNT] > 1 and int(self.traj[0][0, s0[TS_COUNT] - 1]) == self.spec.eos
-        s0[TS_VALID] = self._rows
-        s0[TS_DONE] = int(stopped_on_eos or s0[TS_FRAME] >= self._rows)
+        for lane in range(self._lanes):
+            s0 = st[lane]
+            if lane not in projected:
+                s0[TS_DONE] = 1
+                continue
+            stopped_on_eos = s0[TS_DONE] and s0[TS_COUNT] > 1 and int(self.traj[0][lane, s0[TS_COUNT] - 1]) == self.spec.eos
+            s0[TS_VALID] = self._rows[lane]
+            s0[TS_DONE] = int(stopped_on_eos or s0[TS_FRAME] >= self._rows[lane])
         self.state.copy_(torch.tensor(st, dtype=torch.int32))
         steps = reads = 0
-        if not s0[TS_DONE]:
+        if not all(st[lane][TS_DONE] for lane in range(self._lanes)):
             st, steps, reads = self._run_until_done(self.traj[0].shape[1])
-        lo, hi = self._taken, st[0][TS_COUNT]
-        self._taken = hi
-        tok, dur, frm = (t[0, lo:hi].tolist() for t in self.traj)
-        return TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=self.traj[0].shape[1], steps=steps, state_reads=reads)
+        out = {}
+        for lane in projected:
+            lo, hi = self._taken[lane], st[lane][TS_COUNT]
+            self._taken[lane] = hi
+            tok, dur, frm = (t[lane, lo:hi].tolist() for t in self.traj)
+            out[lane] = TdtTrajectory(tokens=tok, durations=dur, frames=frm, capacity=self.traj[0].shape[1], steps=steps, state_reads=reads)
+        return out
 
     def decode_batch(self, projected: list[torch.Tensor], valid_rows: list[int]) -> list[TdtTrajectory]:
         """Greedy decode of up to ``max_batch`` utterances at once from their projected encoder rows
