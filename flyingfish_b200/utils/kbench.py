@@ -322,10 +322,41 @@ def bench_speech(args) -> dict:
             "library_sdpa_no_position_term_us": lib["us_median"]}
 
 
+def bench_diarize(args) -> dict:
+    """Speaker diarization at the published geometry (31 layers, hidden 512, 8 heads of 64, random weights): one full
+    offline window (speaker cache + FIFO + chunk + look-ahead = 684 rows) through encoder and head, one low-latency
+    streaming window (264 + 264 + 9 + 4 rows), and a whole clip of ``--seconds`` through the offline chunking with the
+    cache policy on the host."""
+    from ..speech import diarization as dz
+    dev = torch.device("cuda")
+    spec = dz.DiarizationSpec()
+    model = dz.DiarizationModel.random(spec, dev, seed=0)
+    out = {"op": "diarize", "seconds": args.seconds}
+    for name, rows in (("offline_window", spec.max_encoder_rows()), ("stream_window", spec.cache.frames + spec.cache.fifo + 13)):
+        emb = (torch.randn(rows, spec.hidden, device=dev) * 0.5).to(torch.bfloat16)
+        t = time_op(lambda: model.classify(model.encode(emb, rows)), args.iters, args.warmup, None)
+        flops = spec.layers * (2.0 * rows * spec.hidden * (4 * spec.hidden + 2 * spec.intermediate) + 4.0 * rows * rows * spec.hidden)
+        out[name] = {"rows": rows, "us": t["us_median"], "tflops": flops / t["us_median"] / 1e6}
+    frames = int(args.seconds * 100)
+    feat = torch.randn(frames, spec.mel.mel_bins, device=dev)
+    model.offline(feat)                                            # warm-up
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    calls = model.encoder_calls
+    model.offline(feat)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    out.update({"clip_ms": ms, "clip_windows": model.encoder_calls - calls, "audio_seconds_per_second": args.seconds / (ms / 1e3),
+                "cache_compressions": model.last_state.updates})
+    return out
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="kbench")
     sub = ap.add_subparsers(dest="op", required=True)
-    for name in ("gemm", "attn_decode", "attn_prefill", "attn_mixed", "gdn", "moe", "speech"):
+    for name in ("gemm", "attn_decode", "attn_prefill", "attn_mixed", "gdn", "moe", "speech", "diarize"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
@@ -341,6 +372,8 @@ def main(argv=None) -> None:
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--seconds", type=float, default=30.0)
             p.add_argument("--attention-only", action="store_true", help="only the relative-position attention kernel of one layer")
+        elif name == "diarize":
+            p.add_argument("--seconds", type=float, default=120.0)
         elif name == "moe":
             p.add_argument("--rows", type=int, default=128)
             p.add_argument("--experts", type=int, default=128)
@@ -361,7 +394,7 @@ def main(argv=None) -> None:
                 p.add_argument("--torch", action="store_true", help="time torch's fused attention on contiguous K / V instead")
     args = ap.parse_args(argv)
     fn = {"gemm": bench_gemm, "attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "attn_mixed": bench_attn_mixed, "gdn": bench_gdn,
-          "moe": bench_moe, "speech": bench_speech}[args.op]
+          "moe": bench_moe, "speech": bench_speech, "diarize": bench_diarize}[args.op]
     print(json.dumps(fn(args)))
     ops.check_status()
 
