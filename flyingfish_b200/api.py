@@ -133,7 +133,17 @@ class Model:
             chunk = min(chunk, ep.max_rows)          # the expert-parallel receive buffers are sized for this many rows per call
         engine = Engine(net, spec, settings, plan.kv_blocks, device, max_prefill_rows=chunk)
         m = cls(engine, spec, settings, tokenizer, name)
-        if spec.extra.get("vision"):
+        if spec.extra.get("vision") and spec.extra["vision"].get("kind") == "minicpm":
+            from .models.minicpm_vision import MiniCpmVisionSpec, MiniCpmVisionTower
+            vspec = MiniCpmVisionSpec(**{k: v for k, v in spec.extra["vision"].items() if k != "kind"})
+            if path.is_dir() and not random_init:
+                from .loaders.safetensors_io import MappedCheckpoint
+                ckpt = MappedCheckpoint(path)
+                m.vision = MiniCpmVisionTower(vspec, {n: ckpt.tensor(n) for n in vspec.expected_tensors() if ckpt.has(n)}, device)
+            else:
+                m.vision = MiniCpmVisionTower.random(vspec, device, seed + 1)
+            engine.mm_encoder = m.encode_images
+        elif spec.extra.get("vision"):
             from .models.vision import VisionSpec, VisionTower
             vspec = VisionSpec(**spec.extra["vision"])
             if path.is_dir() and not random_init:
@@ -182,6 +192,8 @@ class Model:
         if self.vision is None:
             raise ValueError("this model has no vision tower")
         vs = self.vision.spec
+        if self.spec.extra["vision"].get("kind") == "minicpm":
+            return self._encode_sliced_images(ids, images)
         packed = [pack_patches(im, patch=vs.patch, merge=vs.merge, temporal=vs.temporal) for im in images]
         patches = [torch.from_numpy(p) for p, _ in packed]
         grids = [g for _, g in packed]
@@ -189,6 +201,30 @@ class Model:
         token = int(self.spec.extra["image_token_id"])
         out = expand_image_tokens(ids, token, [image_token_count(g, vs.merge) for g in grids])
         positions = [i for i, t in enumerate(out) if t == token]
+        return out, positions, embeds
+
+    def _encode_sliced_images(self, ids: list[int], images: list) -> tuple[list[int], list[int], torch.Tensor]:
+        """MiniCPM-V style: every image is shown whole (about ``slice_scale`` pixels a side) and, when it is large, as a
+        grid of tiles; all views of all images go through the tower together, and an image's placeholder becomes
+        ``start thumb end`` followed by ``slice_start tile slice_end`` per tile with a newline token between tile rows."""
+        from .models.minicpm_vision import expand_view_tokens
+        from .serve.image import pack_slices
+        vs, ex = self.vision.spec, self.spec.extra
+        patches, grids, plans = [], [], []
+        for im in images:
+            views, plan = pack_slices(im, patch=vs.patch, max_slices=int(ex.get("max_slices", 9)), scale=int(ex.get("slice_scale", 448)))
+            vg = [(g[1], g[2]) for g in plan.grids(vs.patch)]
+            patches += [torch.from_numpy(v) for v in views]
+            grids += vg
+            per = vs.patches_per_token
+            plans.append((vg[0][0] * vg[0][1] // per, plan.rows, plan.cols, vg[1][0] * vg[1][1] // per if plan.rows else 0))
+        embeds = torch.cat(self.vision.forward(patches, grids), 0)
+        token = int(ex["image_token_id"])
+        out = expand_view_tokens(ids, token, plans, int(ex["image_start_id"]), int(ex["image_end_id"]), int(ex["slice_start_id"]),
+                                 int(ex["slice_end_id"]), int(ex["newline_id"]))
+        positions = [i for i, t in enumerate(out) if t == token]
+        if len(positions) != embeds.shape[0]:
+            raise RuntimeError(f"{len(positions)} image rows in the prompt for {embeds.shape[0]} rows from the tower")
         return out, positions, embeds
 
     def prefill_multimodal(self, ids: list[int], images: list) -> int:

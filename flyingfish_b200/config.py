@@ -184,6 +184,19 @@ def tiny_vl() -> ModelSpec:
     return spec
 
 
+def tiny_minicpm() -> ModelSpec:
+    """Small sliced-image vision-language shape: the tiny dense decoder plus a MiniCPM-V style tower
+    (``extra["vision"]``: ``kind`` "minicpm" and the fields of ``models.minicpm_vision.MiniCpmVisionSpec``); a large
+    image is shown whole and as tiles, each view wrapped in marker tokens."""
+    spec = tiny_llama()
+    spec.name, spec.arch = "tiny-minicpm", "qwen3_vl"
+    spec.extra = {"image_token_id": 2047, "image_start_id": 2040, "image_end_id": 2041, "slice_start_id": 2042, "slice_end_id": 2043,
+                  "newline_id": 10, "max_slices": 4, "slice_scale": 32,
+                  "vision": {"kind": "minicpm", "hidden": 64, "heads": 2, "depth": 3, "intermediate": 96, "patch": 2, "channels": 3,
+                             "image_size": 32, "insert_layer": 0, "out_hidden": spec.hidden}}
+    return spec
+
+
 def tiny_embed() -> ModelSpec:
     """Small bidirectional text encoder (embedding model): mean pooling, optional dense head, L2 normalisation."""
     spec = tiny_llama()
@@ -284,7 +297,7 @@ def glm5_next_tiny() -> ModelSpec:
 
 
 NAMED_SHAPES = {
-    "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
+    "tiny-gemma": tiny_gemma, "qwen3-moe-fp4-tiny": qwen3_moe_fp4_tiny, "tiny-hybrid": tiny_hybrid, "tiny-embed": tiny_embed, "tiny-diffusion": tiny_diffusion, "tiny-vl": tiny_vl, "tiny-minicpm": tiny_minicpm, "tiny-moe": tiny_moe, "tiny-llama": tiny_llama, "llama3-8b-shape": llama3_8b, "llama3-70b-shape": llama3_70b,
     "deepseek-v3-shape": deepseek_v3, "deepseek-v3-tiny": deepseek_v3_tiny, "deepseek-v3-mini": deepseek_v3_mini,
     "deepseek-v3-fp8-mini": deepseek_v3_fp8_mini, "deepseek-v41-tiny": deepseek_v41_tiny, "glm5-next-tiny": glm5_next_tiny, "flint-tiny": flint_tiny,
     "loop-tiny": loop_tiny, "loopvl-text-shape": loopvl_text,

@@ -322,10 +322,10 @@ def slice_image(img: Image, patch: int = 14, max_slices: int = 9, scale: int = S
     return plan, views
 
 
-def pack_slices(img: Image, patch: int = 14, max_slices: int = 9, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5)
-                ) -> tuple[list[np.ndarray], SlicePlan]:
+def pack_slices(img: Image, patch: int = 14, max_slices: int = 9, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5),
+                scale: int = SCALE_RESOLUTION) -> tuple[list[np.ndarray], SlicePlan]:
     """Every view as patches [grid_h * grid_w, 3 * patch * patch] float32, row-major patch order, normalised."""
-    plan, views = slice_image(img, patch, max_slices)
+    plan, views = slice_image(img, patch, max_slices, scale)
     out = []
     for v in views:
         x = ((v / 255.0 - np.asarray(mean)) / np.asarray(std)).astype(np.float32).transpose(2, 0, 1)
