@@ -119,6 +119,7 @@ def _global_parser() -> argparse.ArgumentParser:
     tr.add_argument("--target-lang", default="en")
     tr.add_argument("--no-pnc", action="store_true", help="Canary: no punctuation and capitalisation")
     tr.add_argument("--diarization-model", help="multitalker archives: diarization checkpoint whose speaker activity selects the lanes")
+    tr.add_argument("--masked-asr", action="store_true", help="multitalker archives: mask each lane's log-mel input instead of conditioning layer 0")
 
     dz = sub.add_parser("diarize")
     dz.add_argument("input", help="RIFF/WAVE file (mixed down and resampled to the model's rate)")
@@ -501,12 +502,12 @@ def cmd_transcribe(args) -> None:
             if args.format not in ("txt", "json"):
                 raise SystemExit("speaker-attributed transcripts come as txt or json")
             res = transcribe_multitalker(args.model, args.diarization_model, wave, "cpu" if args.cpu else f"cuda:{args.device}",
-                                         stream_diarizer=args.stream)
+                                         stream_diarizer=args.stream, masked=args.masked_asr)
             text = res.to_text() if args.format == "txt" else res.to_json() + "\n"
             (out_path.write_text(text) if out_path is not None else sys.stdout.write(text))
             return
-        if args.diarization_model:
-            raise SystemExit("--diarization-model applies to multitalker archives")
+        if args.diarization_model or args.masked_asr:
+            raise SystemExit("--diarization-model / --masked-asr apply to multitalker archives")
         result = transcribe_nemo(args.model, wave, "cpu" if args.cpu else f"cuda:{args.device}", stream=args.stream)
         text = {"txt": result.text + "\n", "json": result.to_json() + "\n", "srt": result.to_srt(), "vtt": result.to_vtt()}[args.format]
         (out_path.write_text(text) if out_path is not None else sys.stdout.write(text))

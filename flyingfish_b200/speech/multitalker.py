@@ -171,13 +171,13 @@ class MultitalkerModel(ParakeetModel):
             h = (h.float() + vision_ops.linear_bias_act(mid, down[0], down[1], "none").float()).to(BF16)
         return h
 
-    def stream(self, activity: torch.Tensor, gating: bool = True) -> "MultitalkerStream":
-        return MultitalkerStream(self, activity, gating)
+    def stream(self, activity: torch.Tensor, gating: bool = True, masked: bool = False) -> "MultitalkerStream":
+        return MultitalkerStream(self, activity, gating, masked)
 
     def transcribe_speakers(self, waveform: torch.Tensor, activity: torch.Tensor, gating: bool = True,
-                            piece_seconds: float = 1.12) -> MultitalkerTranscription:
+                            piece_seconds: float = 1.12, masked: bool = False) -> MultitalkerTranscription:
         """One clip with its speaker activity ``[rows, lanes]`` at the 80 ms grid -> one transcript per active speaker."""
-        st = self.stream(activity, gating)
+        st = self.stream(activity, gating, masked)
         piece = max(1, int(piece_seconds * self.spec.mel.sampling_rate))
         for at in range(0, waveform.numel(), piece):
             nxt = min(waveform.numel(), at + piece)
@@ -189,14 +189,18 @@ class MultitalkerStream:
     """Audio in pieces, tokens per speaker lane out. ``activity`` [rows, lanes] (values above 0.5 = speaking) covers the
     clip at the encoder's row grid; rows beyond its end count as "own speaker active, nobody else"."""
 
-    def __init__(self, model: MultitalkerModel, activity: torch.Tensor, gating: bool = True):
+    def __init__(self, model: MultitalkerModel, activity: torch.Tensor, gating: bool = True, masked: bool = False):
+        """``masked``: the feature-masking variant -- instead of conditioning layer 0, every lane gets its own log-mel
+        input in which the frames of rows where its speaker is silent are zeroed (frames that are exactly zero take the
+        log floor), the kernels run with "own speaker active, nobody else", and every lane runs its own stem."""
         spec = model.spec
         if spec.mel.normalize:
             raise ValueError("streaming needs un-normalised features")
         act = activity.detach().float().cpu()
         if act.dim() != 2 or not (1 <= act.shape[1] <= model.mt.speakers):
             raise ValueError(f"speaker activity must be [rows, 1..{model.mt.speakers}]")
-        self.model, self.activity, self.gating = model, act, gating
+        self.model, self.activity, self.gating, self.masked = model, act, gating, masked
+        self.frames_seen = 0
         self.lanes = act.shape[1]
         self.front = StreamingLogMel(model.mel)
         self.stem = ConformerStream(model.encoder)              # frames and stem only; its layer caches stay empty
@@ -227,20 +231,41 @@ class MultitalkerStream:
                 others[:have] = (rest > 0.5).any(dim=1).float()
         return own, others
 
+    def masked_frames(self, frames: torch.Tensor, lane: int) -> torch.Tensor:
+        """The new log-mel frames as lane ``lane`` sees them in the feature-masking variant: a frame belongs to row
+        ``frame // 8``; rows where the lane's speaker is silent are zeroed, rows beyond the activity count as active, and
+        values that are exactly zero become the log floor (src/backend/cuda/engine_multitalker.rs:414-438 of the
+        reference)."""
+        n = frames.shape[0]
+        rows = (torch.arange(n) + self.frames_seen) // 8
+        inside = rows < self.activity.shape[0]
+        keep = torch.ones(n)
+        keep[inside] = (self.activity[rows[inside], lane] > 0.5).float()
+        floor = float(torch.log(torch.tensor(self.model.spec.mel.log_guard)))
+        f = frames.float()
+        return torch.where(f == 0.0, torch.full_like(f, floor), f * keep.to(f.device)[:, None])
+
     def push(self, samples: torch.Tensor, last: bool = False) -> dict[int, list[int]]:
         """Feeds samples; returns the tokens each lane recognised in this call."""
         model, dec = self.model, self.model.decoder
         new: dict[int, list[int]] = {}
-        for first, h in self.stem.stem_chunks(self.front.push(samples, last), last):
-            n = h.shape[0]
+        frames = self.front.push(samples, last)
+        if self.masked:
+            per_lane = [list(self.lane_streams[lane].stem_chunks(self.masked_frames(frames, lane), last)) for lane in range(self.lanes)]
+            chunks = [(per_lane[0][i][0], [per_lane[lane][i][1] for lane in range(self.lanes)]) for i in range(len(per_lane[0]))]
+            self.frames_seen += frames.shape[0]
+        else:
+            chunks = [(first, [h] * self.lanes) for first, h in self.stem.stem_chunks(frames, last)]
+        for first, hs in chunks:
+            n = hs[0].shape[0]
             live = self.live_lanes(first + n)
             self.steps += 1
             if not live:
                 continue
             projected = {}
             for lane in live:
-                own, others = self.masks(first, n, lane)
-                rows = self.lane_streams[lane]._layers(model.speaker_kernels(h, own, others))
+                own, others = (torch.ones(n), torch.zeros(n)) if self.masked else self.masks(first, n, lane)
+                rows = self.lane_streams[lane]._layers(model.speaker_kernels(hs[lane], own, others))
                 projected[lane] = dec.project(rows)
                 self.row_map[lane] += list(range(first, first + n))
                 self.lane_steps[lane] += 1
@@ -269,7 +294,8 @@ class MultitalkerStream:
 
 
 def transcribe_multitalker(nemo_path: str | Path, diarization_dir: str | Path, waveform: torch.Tensor,
-                           device: torch.device | str = "cpu", threshold: float = 0.5, stream_diarizer: bool = True) -> MultitalkerTranscription:
+                           device: torch.device | str = "cpu", threshold: float = 0.5, stream_diarizer: bool = True,
+                           masked: bool = False) -> MultitalkerTranscription:
     """The whole pipeline on one 16 kHz mono clip: the diarizer's pooled speaker activity selects the lanes, the
     multitalker model transcribes each of them. A diarizer channel beyond the model's lanes that is ever active is an
     error (src/multitalker.rs ``transcribe`` of the reference)."""
@@ -283,4 +309,4 @@ def transcribe_multitalker(nemo_path: str | Path, diarization_dir: str | Path, w
     beyond = [c for c in range(lanes, masks.shape[1]) if bool(masks[:, c].any())]
     if beyond:
         raise ValueError(f"diarization activates speaker channels {beyond} beyond the {lanes} lanes the model serves")
-    return model.transcribe_speakers(waveform, masks[:, :lanes].float())
+    return model.transcribe_speakers(waveform, masks[:, :lanes].float(), masked=masked)

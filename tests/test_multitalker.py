@@ -210,6 +210,36 @@ def test_masks_steer_lanes_and_gating_parks_them():
         assert all(w.end > w.start for w in sp.words)
 
 
+def test_feature_masking_variant():
+    spec = mt.MultitalkerSpec.from_yaml(YAML)
+    tensors = _tensors(spec, 7, kernel_std=0.0)
+    model = mt.MultitalkerModel(spec, tensors)
+    wave = _wave(8, 2.4)
+    plain = StreamingRecognizer(ParakeetModel(spec.asr, {n: t for n, t in tensors.items() if n in spec.asr.expected_tensors()}))
+    plain.push(wave, last=True)
+    want = [(t, f) for t, f in zip(plain.tokens, plain.frames) if t != spec.asr.blank]
+    rows = spec.asr.encoder.sub_len(len(wave) // spec.asr.mel.hop_length)
+    act = torch.ones(rows, 2)
+    act[rows // 3: 2 * rows // 3, 1] = 0.0                       # speaker 1 pauses in the middle third
+    st = model.stream(act, gating=False, masked=True)
+    for at in range(0, wave.numel(), 5000):
+        st.push(wave[at:at + 5000], last=at + 5000 >= wave.numel())
+    # a lane whose speaker never pauses sees the unmasked features: the plain recogniser's tokens
+    assert list(zip(st.tokens[0], st.token_rows[0])) == want
+    # the paused lane heard silence in the middle third: its second layer's attention cache (rows that looked back on
+    # the silent stretch) differs from the other lane's, the stem rows of the last chunk (all audible again) do not
+    assert not torch.equal(st.lane_streams[1].qkv[1], st.lane_streams[0].qkv[1])
+    assert torch.equal(st.lane_streams[1].qkv[0][-2:], st.lane_streams[0].qkv[0][-2:])
+    # the mask itself: frames of silent rows are zero, exact zeros take the log floor
+    probe = model.stream(act, masked=True)
+    frames = torch.ones(8 * rows, spec.asr.mel.mel_bins)
+    frames[0, 0] = 0.0
+    got = probe.masked_frames(frames, 1)
+    lo, hi = 8 * (rows // 3), 8 * (2 * rows // 3)
+    assert (got[lo:hi] == 0).all() and (got[hi:] == 1).all() and (got[1:lo] == 1).all()
+    assert got[0, 0].item() == pytest.approx(-16.6355, abs=1e-3) and got[0, 1].item() == 1.0
+
+
 def test_speaker_words():
     pieces = ["<unk>", "▁he", "llo", "▁", "wor", "ld", "▁again", "<EOU>"]
     text, words = mt.speaker_words([1, 2, 3, 4, 5, 7, 6], [2, 3, 9, 9, 11, 12, 20], lambda t: pieces[t], 0.08)
