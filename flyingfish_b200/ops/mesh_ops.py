@@ -364,3 +364,95 @@ def dual_contour_mesh_reference(coords: torch.Tensor, cubes: torch.Tensor, posit
                 faces += [[q[0], q[1], q[2]], [q[2], q[1], q[3]]]
     v = torch.stack(verts) if verts else torch.zeros(0, 3)
     return v, torch.tensor(faces, dtype=torch.int32).reshape(-1, 3)
+
+
+# ------------------------------------------------------------------------------------------------
+# triangles -> voxels
+# ------------------------------------------------------------------------------------------------
+def _dot3(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    # the summation order of the scalar kernel: fma(a2, b2, fma(a0, b0, a1 * b1))
+    return a[..., 2] * b[..., 2] + (a[..., 0] * b[..., 0] + a[..., 1] * b[..., 1])
+
+
+def triangle_voxels(vertices: torch.Tensor, faces: torch.Tensor, resolution: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Every (voxel, triangle) pair that overlaps, for triangles given in voxel units over the grid ``[0, resolution)^3``
+    (kernels/vision_ops.cu ``triangle_box_count`` / ``triangle_box_emit`` of the reference: the separating-axis test of a
+    triangle against a unit cube -- three box axes, nine edge cross products, the triangle's plane). Returns
+    (voxels [m, 3] int32, owners [m] int32), triangles in order and the voxels of a triangle in x, y, z order. All
+    candidate cells of all triangles are tested at once."""
+    if vertices.dim() != 2 or vertices.shape[1] != 3 or faces.dim() != 2 or faces.shape[1] != 3 or resolution <= 0:
+        raise ValueError("triangle_voxels: vertices [n, 3], faces [f, 3], positive resolution")
+    if not torch.isfinite(vertices).all():
+        raise ValueError("non-finite vertex")
+    dev = vertices.device
+    pts = vertices.float()[faces.long()]                                 # [f, 3 vertices, 3 axes]
+    lower = torch.floor(pts.min(dim=1).values).clamp(min=0).long()
+    upper = torch.floor(pts.max(dim=1).values).clamp(max=resolution - 1).long()
+    size = (upper - lower + 1).clamp(min=0)
+    count = size.prod(dim=1)
+    total = int(count.sum())
+    if total == 0:
+        return torch.zeros(0, 3, dtype=torch.int32, device=dev), torch.zeros(0, dtype=torch.int32, device=dev)
+    owner = torch.repeat_interleave(torch.arange(faces.shape[0], device=dev), count)
+    local = torch.arange(total, device=dev) - torch.repeat_interleave(torch.cumsum(count, 0) - count, count)
+    sz = size[owner]
+    z = local % sz[:, 2]
+    y = (local // sz[:, 2]) % sz[:, 1]
+    x = local // (sz[:, 2] * sz[:, 1])
+    cell = torch.stack([x, y, z], dim=1) + lower[owner]
+    p = pts[owner] - (cell.float() + 0.5)[:, None, :]                    # triangle relative to the cell centre
+    edges = p[:, [1, 2, 0]] - p
+    ok = ~((p.min(dim=1).values > 0.5) | (p.max(dim=1).values < -0.5)).any(dim=1)
+    for e in range(3):
+        for a in range(3):
+            axis = torch.zeros_like(p[:, 0])
+            axis[:, (a + 1) % 3] = edges[:, e, (a + 2) % 3]
+            axis[:, (a + 2) % 3] = -edges[:, e, (a + 1) % 3]
+            proj = torch.stack([_dot3(p[:, v], axis) for v in range(3)], dim=1)
+            radius = 0.5 * ((axis[:, 0].abs() + axis[:, 1].abs()) + axis[:, 2].abs())
+            ok &= (proj.min(dim=1).values <= radius) & (proj.max(dim=1).values >= -radius)
+    normal = torch.stack([edges[:, 0, (a + 1) % 3] * edges[:, 1, (a + 2) % 3] - edges[:, 0, (a + 2) % 3] * edges[:, 1, (a + 1) % 3]
+                          for a in range(3)], dim=1)
+    radius = 0.5 * ((normal[:, 0].abs() + normal[:, 1].abs()) + normal[:, 2].abs())
+    ok &= _dot3(p[:, 0], normal).abs() <= radius
+    return cell[ok].to(torch.int32), owner[ok].to(torch.int32)
+
+
+def triangle_voxels_reference(vertices: torch.Tensor, faces: torch.Tensor, resolution: int):
+    """Per-triangle, per-cell restatement of :func:`triangle_voxels`."""
+    v = vertices.float().cpu()
+    cells, owners = [], []
+    f32 = lambda t: torch.tensor(t, dtype=torch.float32)
+    for fi, face in enumerate(faces.cpu().tolist()):
+        tri = v[face]
+        lo = [max(0, int(math.floor(float(tri[:, a].min())))) for a in range(3)]
+        hi = [min(resolution - 1, int(math.floor(float(tri[:, a].max())))) for a in range(3)]
+        for x in range(lo[0], hi[0] + 1):
+            for y in range(lo[1], hi[1] + 1):
+                for z in range(lo[2], hi[2] + 1):
+                    p = tri - (f32([x, y, z]) + 0.5)
+                    e = p[[1, 2, 0]] - p
+                    hit = not any(float(p[:, a].min()) > 0.5 or float(p[:, a].max()) < -0.5 for a in range(3))
+                    for k in range(3):
+                        for a in range(3):
+                            ax = torch.zeros(3)
+                            ax[(a + 1) % 3] = e[k, (a + 2) % 3]
+                            ax[(a + 2) % 3] = -e[k, (a + 1) % 3]
+                            proj = _dot3(p, ax[None, :])
+                            rad = 0.5 * ((ax[0].abs() + ax[1].abs()) + ax[2].abs())
+                            hit = hit and bool(proj.min() <= rad) and bool(proj.max() >= -rad)
+                    n = torch.stack([e[0, (a + 1) % 3] * e[1, (a + 2) % 3] - e[0, (a + 2) % 3] * e[1, (a + 1) % 3] for a in range(3)])
+                    rad = 0.5 * ((n[0].abs() + n[1].abs()) + n[2].abs())
+                    hit = hit and bool(_dot3(p[0], n).abs() <= rad)
+                    if hit:
+                        cells.append([x, y, z])
+                        owners.append(fi)
+    return torch.tensor(cells, dtype=torch.int32).reshape(-1, 3), torch.tensor(owners, dtype=torch.int32)
+
+
+def occupied_voxels(voxels: torch.Tensor, resolution: int) -> torch.Tensor:
+    """Unique voxels of a (voxel, triangle) list in x, y, z order, as sparse coordinates [m, 4] int32 of batch 0."""
+    key = (voxels[:, 0].long() * resolution + voxels[:, 1].long()) * resolution + voxels[:, 2].long()
+    u = torch.unique(key)
+    xyz = torch.stack([u // (resolution * resolution), (u // resolution) % resolution, u % resolution], dim=1)
+    return torch.cat([torch.zeros(u.shape[0], 1, dtype=torch.long, device=u.device), xyz], dim=1).to(torch.int32)

@@ -143,3 +143,39 @@ def test_mesh_builders_on_the_device():
     v, f = mo.dual_contour_mesh(coords.cuda(), cubes.cuda(), positions.cuda(), scalar.cuda())
     rv, rf = mo.dual_contour_mesh_reference(coords, cubes, positions, scalar)
     assert torch.allclose(v.cpu(), rv, atol=1e-4) and torch.equal(f.cpu(), rf)
+    cells, owners = mo.triangle_voxels(v, f, g)
+    rc, ro = mo.triangle_voxels(v.cpu(), f.cpu(), g)
+    # touching cases may differ in the last bit between devices: compare the bulk
+    assert abs(cells.shape[0] - rc.shape[0]) <= 0.01 * rc.shape[0] + 2
+
+
+def test_triangle_voxels():
+    # a triangle in the plane z = 0.5 over a 4 x 4 x 4 grid: exactly the cells of layer z = 0 its area touches
+    v = torch.tensor([[0.2, 0.2, 0.5], [3.7, 0.2, 0.5], [0.2, 3.7, 0.5]])
+    f = torch.tensor([[0, 1, 2]])
+    cells, owners = mo.triangle_voxels(v, f, 4)
+    assert (cells[:, 2] == 0).all() and (owners == 0).all()
+    got = {tuple(c) for c in cells[:, :2].tolist()}
+    assert got == {(x, y) for x in range(4) for y in range(4) if x + y <= 3}
+    # random triangles, some partly outside the grid: the batched test equals the per-cell restatement, order included
+    gen = torch.Generator().manual_seed(4)
+    v = torch.rand(30, 3, generator=gen) * 8.0 - 1.0
+    f = torch.randint(0, 30, (25, 3), generator=gen)
+    cells, owners = mo.triangle_voxels(v, f, 6)
+    rc, ro = mo.triangle_voxels_reference(v, f, 6)
+    assert torch.equal(cells, rc) and torch.equal(owners, ro) and cells.shape[0] > 50
+    assert (cells >= 0).all() and (cells < 6).all()
+    # a triangle outside the grid gives nothing
+    out = mo.triangle_voxels(torch.tensor([[9.0, 9, 9], [10, 9, 9], [9, 10, 9]]), f[:1] * 0 + torch.tensor([[0, 1, 2]]), 4)
+    assert out[0].shape == (0, 3)
+    # the voxels of an extracted sphere contain every vertex of its mesh
+    coords, cubes, positions = _dense_block(8)
+    scalar = (positions - torch.tensor([3.9, 4.1, 4.05])).norm(dim=1) - 2.7
+    mv, mf = mo.dual_contour_mesh(coords, cubes, positions, scalar)
+    cells, _ = mo.triangle_voxels(mv, mf, 8)
+    occ = mo.occupied_voxels(cells, 8)
+    assert occ.shape[1] == 4 and occ.shape[0] == len({tuple(c) for c in cells.tolist()})
+    have = {tuple(c[1:]) for c in occ.tolist()}
+    assert all(tuple(int(t) for t in p.floor().tolist()) in have for p in mv)
+    with pytest.raises(ValueError):
+        mo.triangle_voxels(v, f, 0)
