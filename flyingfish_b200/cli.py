@@ -437,6 +437,13 @@ def cmd_inspect(args) -> dict:
         text, weights = read_nemo(p)
         try:
             nbytes = sum(r.storage.numel * torch.empty(0, dtype=r.dtype).element_size() for r in weights.records.values())
+            if "spk_kernel_type" in text:
+                # speaker-attributed recognition: the same encoder / transducer plus the speaker kernels
+                from .speech.multitalker import KERNEL_TENSORS, MultitalkerSpec
+                mt = MultitalkerSpec.from_yaml(text)
+                return {"family": "speech", "architecture": "nemo_multitalker_rnnt", "speakers": mt.speakers, "spec": asdict(mt.asr),
+                        "speaker_kernels": [k for k in KERNEL_TENSORS if k + ".weight" in weights.records],
+                        "tensors": len(weights.records), "bytes": nbytes}
             return {"family": "speech", "architecture": "nemo_rnnt", "spec": asdict(spec_from_yaml(text)),
                     "tensors": len(weights.records), "bytes": nbytes}
         finally:
@@ -452,6 +459,12 @@ def cmd_inspect(args) -> dict:
                   "CanaryForConditionalGeneration": CanarySpec}[arch].read(p)
             info = inspect_checkpoint(p)
             return {"family": "speech", "architecture": arch, "spec": asdict(sp), "expected_tensors": len(sp.expected_tensors()), **info}
+        if arch == "Nemotron3DiarizationForAudioFrameClassification":
+            from dataclasses import asdict
+            from .speech.diarization import DiarizationSpec
+            sp = DiarizationSpec.from_json(json.loads((p / "config.json").read_text()), json.loads((p / "processor_config.json").read_text()))
+            return {"family": "speech", "architecture": arch, "spec": asdict(sp), "expected_tensors": len(sp.expected_tensors()),
+                    "max_encoder_rows": sp.max_encoder_rows(), **inspect_checkpoint(p)}
         spec = read_model_spec(p)
         return {"spec": spec.to_json(), **inspect_checkpoint(p)}
     return {"spec": named_shape(args.model).to_json()}

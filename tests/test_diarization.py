@@ -249,6 +249,11 @@ def test_save_load_and_command_line(tmp_path, capsys):
     assert segs and all(set(s) == {"start", "end", "speaker"} for s in segs)
     with pytest.raises(SystemExit):
         cli.main(["--model", str(tmp_path / "model"), "--cpu", "diarize", "--mode", "low_latency", str(tmp_path / "two words.wav")])
+    capsys.readouterr()
+    assert cli.main(["--model", str(tmp_path / "model"), "inspect"]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert info["architecture"] == "Nemotron3DiarizationForAudioFrameClassification" and info["expected_tensors"] == len(spec.expected_tensors())
+    assert info["spec"]["speakers"] == 4 and info["max_encoder_rows"] == spec.max_encoder_rows()
 
 
 @pytest.mark.gpu

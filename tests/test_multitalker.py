@@ -302,6 +302,10 @@ def test_archive_and_pipeline_with_a_diarizer(tmp_path, capsys):
                      "--format", "json"]) == 0
     got = json.loads(capsys.readouterr().out)
     assert [s["speaker"] for s in got["speakers"]] == [s.speaker for s in mt.transcribe_multitalker(arc, tmp_path / "diar", wave).speakers]
+    capsys.readouterr()
+    assert cli.main(["--model", str(arc), "inspect"]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert info["architecture"] == "nemo_multitalker_rnnt" and info["speakers"] == 3 and len(info["speaker_kernels"]) == 4
     # a multitalker archive without a diarizer is refused, and so is activity for more lanes than the model serves
     with pytest.raises(SystemExit):
         cli.main(["--cpu", "--model", str(arc), "transcribe", str(tmp_path / "w.wav")])
