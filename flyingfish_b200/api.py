@@ -106,7 +106,7 @@ class Model:
             net = HrmModel(weights, comm=comm)
         elif spec.extra.get("flint"):
             from .models.flint import FlintModel
-            net = FlintModel(weights, comm=comm, seed=seed)
+            net = FlintModel(weights, comm=comm, seed=seed, state=weights.extra.get("state"))
         elif spec.extra.get("gemma"):
             from .models.gemma import GemmaModel
             net = GemmaModel(weights, comm=comm, seed=seed)

@@ -321,8 +321,54 @@ class ConfigError(ValueError):
 _ARCH_MAP = {
     "LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "Qwen2ForCausalLM": "qwen3",
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "DeepseekV3ForCausalLM": "deepseek_v3",
-    "DeepseekV2ForCausalLM": "deepseek_v3",
+    "DeepseekV2ForCausalLM": "deepseek_v3", "FlintForCausalLM": "flint",
 }
+
+
+def _flint_spec(cfg: dict[str, Any], name: str) -> ModelSpec:
+    """``FlintForCausalLM`` (src/model_spec.rs:2723-2905 of the reference): sliding-window layers with rotary positions,
+    the listed layers global and without positions, QK-norm, a learnable soft-max offset per head, dense FFNs in the
+    ``mlp_only_layers`` prefix and sigmoid-routed experts with one shared expert after it."""
+    for key, want in (("hidden_act", "silu"), ("attention_bias", False), ("router_score_function", "sigmoid"),
+                      ("softmax_type", "learnable"), ("norm_topk_prob", True), ("use_sliding_window", True), ("decoder_sparse_step", 1)):
+        if cfg.get(key, want) != want:
+            raise ConfigError(f"unsupported Flint setting {key}={cfg.get(key)!r}")
+    layers = int(cfg["num_hidden_layers"])
+    no_rope = sorted(int(i) for i in cfg["no_rope_layer_indices"])
+    if any(not (0 <= i < layers) for i in no_rope) or len(set(no_rope)) != len(no_rope):
+        raise ConfigError("no_rope_layer_indices outside the layer range")
+    types = cfg.get("layer_types")
+    if types is not None:
+        want = ["full_attention" if i in set(no_rope) else "sliding_attention" for i in range(layers)]
+        if list(types) != want:
+            raise ConfigError("layer_types disagree with no_rope_layer_indices (global layers carry no positions)")
+    dense = sorted(int(i) for i in cfg.get("mlp_only_layers", []))
+    if dense != list(range(len(dense))):
+        raise ConfigError("mlp_only_layers must be a prefix of the layers")
+    if int(cfg["head_dim"]) != 128:
+        raise ConfigError("Flint heads are 128 wide")
+    td = cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))
+    dtype = {"bfloat16": "bf16", "float16": "f16", "float32": "fp32"}.get(td)
+    if dtype is None:
+        raise ConfigError(f"unsupported torch_dtype {td!r}")
+    eos = cfg.get("eos_token_id")
+    extra: dict[str, Any] = {"flint": {"window": int(cfg["sliding_window"]), "no_rope_layers": no_rope}}
+    if isinstance(eos, list):
+        extra["eos_token_ids"] = eos
+        eos = eos[0] if eos else None
+    heads, kv_heads = int(cfg["num_attention_heads"]), int(cfg["num_key_value_heads"])
+    if heads % kv_heads:
+        raise ConfigError("num_attention_heads must be a multiple of num_key_value_heads")
+    return ModelSpec(
+        name=name, arch="flint", layers=layers, hidden=int(cfg["hidden_size"]), heads=heads, kv_heads=kv_heads, head_dim=128,
+        ffn=int(cfg["intermediate_size"]), vocab=int(cfg["vocab_size"]), rope_theta=float(cfg.get("rope_theta", 10000.0)),
+        rms_eps=float(cfg.get("rms_norm_eps", 1e-6)), dtype=dtype, tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+        qk_norm=True, max_position=int(cfg.get("max_position_embeddings", 262144)), eos_token_id=eos,
+        moe=MoeSpec(num_experts=int(cfg["num_experts"]), top_k=int(cfg["num_experts_per_tok"]),
+                    expert_ffn=int(cfg["moe_intermediate_size"]), score="sigmoid", n_shared=1,
+                    shared_ffn=int(cfg["shared_expert_intermediate_size"]), first_dense_layers=len(dense),
+                    dense_ffn=int(cfg["intermediate_size"])),
+        extra=extra)
 
 
 def spec_from_hf_config(cfg: dict[str, Any], name: str = "model") -> ModelSpec:
@@ -332,6 +378,8 @@ def spec_from_hf_config(cfg: dict[str, Any], name: str = "model") -> ModelSpec:
     arch = next((_ARCH_MAP[a] for a in archs if a in _ARCH_MAP), None)
     if arch is None:
         raise ConfigError(f"unsupported architectures {archs}")
+    if arch == "flint":
+        return _flint_spec(cfg, name)
     act = cfg.get("hidden_act", "silu")
     if act not in ("silu", "swish"):
         raise ConfigError(f"unsupported activation {act!r}")

@@ -92,12 +92,24 @@ def manifest(spec: ModelSpec, policy: LoadPolicy = LoadPolicy.TEXT_ONLY) -> dict
                 sf = moe.shared_ffn
                 for nm, (o, k) in {"gate_proj": (sf, h), "up_proj": (sf, h), "down_proj": (h, sf)}.items():
                     m.update(_linear_entries(p + "mlp.shared_experts." + nm, o, k, lf))
+        if spec.arch == "flint":
+            m[p + "self_attn.softmax_offset"] = ((spec.heads,), "float")
         if i >= spec.layers:   # MTP module extras
             m[p + "enorm.weight"] = ((h,), "float")
             m[p + "hnorm.weight"] = ((h,), "float")
             m[p + "eh_proj.weight"] = ((h, 2 * h), "float")
             m[p + "shared_head.norm.weight"] = ((h,), "float")
+    if spec.arch == "flint":
+        # published Flint checkpoints name the shared expert in the singular
+        m = {k.replace(".mlp.shared_experts.", ".mlp.shared_expert."): v for k, v in m.items()}
     return m
+
+
+def published_name(spec: ModelSpec, name: str) -> str:
+    """The tensor name a published checkpoint of ``spec.arch`` uses for the canonical ``name``."""
+    if spec.arch == "flint":
+        return name.replace(".mlp.shared_experts.", ".mlp.shared_expert.")
+    return name
 
 
 _CLASS = {"float": ("BF16", "F16", "F32"), "f32": ("F32",), "fp8": ("F8_E4M3",), "u8": ("U8",)}
@@ -180,6 +192,7 @@ def load_decoder_weights(model_dir: str | Path, spec: ModelSpec | None, device: 
     dtype = DTYPES["bf16" if spec.dtype == "f16" and device.type == "cuda" else spec.dtype]
 
     def source(name: str, shape: tuple[int, ...]) -> torch.Tensor:
+        name = published_name(spec, name)
         if not ck.has(name):
             raise CheckpointError(f"missing tensor {name}")
         info = ck.info(name)
@@ -205,6 +218,10 @@ def load_decoder_weights(model_dir: str | Path, spec: ModelSpec | None, device: 
                 nm = f"model.layers.{i}.mlp.gate.e_score_correction_bias"
                 if lw.router is not None and ck.has(nm):
                     lw.router_bias = ck.tensor(nm).to(device=device, dtype=torch.float32)
+        if spec.arch == "flint":
+            # the learnable soft-max offsets ride along for the model class (one logit per query head and layer)
+            w.extra["state"] = {f"model.layers.{i}.self_attn.sinks": ck.tensor(f"model.layers.{i}.self_attn.softmax_offset").float().clone()
+                                for i in range(spec.layers)}
         return w
     finally:
         ck.close()
