@@ -69,7 +69,17 @@ class Model:
             from .loaders.checkpoint import load_decoder_weights
             from .loaders.tokenizer import load_tokenizer
             spec = read_model_spec(path)
-            weights = load_decoder_weights(path, spec, device, tp, epi)
+            if spec.extra.get("hrm"):
+                # looped two-stack decoder: its own weight assembly over the published tensor names (text side only)
+                from .loaders.checkpoint import checkpoint_source
+                from .models.hrm import build_hrm_weights
+                source, close = checkpoint_source(path, spec, device)
+                try:
+                    weights = build_hrm_weights(spec, source, device)
+                finally:
+                    close()
+            else:
+                weights = load_decoder_weights(path, spec, device, tp, epi)
             tokenizer = load_tokenizer(path)
             name = path.name
         else:

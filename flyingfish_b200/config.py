@@ -321,8 +321,45 @@ class ConfigError(ValueError):
 _ARCH_MAP = {
     "LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "Qwen2ForCausalLM": "qwen3",
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe", "DeepseekV3ForCausalLM": "deepseek_v3",
-    "DeepseekV2ForCausalLM": "deepseek_v3", "FlintForCausalLM": "flint",
+    "DeepseekV2ForCausalLM": "deepseek_v3", "FlintForCausalLM": "flint", "LoopVLForConditionalGeneration": "loop_vl",
 }
+
+
+def _loopvl_spec(cfg: dict[str, Any], name: str) -> ModelSpec:
+    """``LoopVLForConditionalGeneration`` (src/model_spec.rs:2273-2400 of the reference), text side: the looped two-stack
+    decoder described by ``text_config`` (``hrm_text``); the vision encoder and projector of the checkpoint are not
+    loaded."""
+    t = cfg.get("text_config")
+    if not isinstance(t, dict) or t.get("model_type") != "hrm_text":
+        raise ConfigError("LoopVL text_config (hrm_text) missing")
+    if cfg.get("quantization_config") is not None:
+        raise ConfigError("LoopVL checkpoints are BF16 / F32")
+    for key, want in (("hidden_act", "silu"), ("prefix_lm", True), ("tie_word_embeddings", False), ("attention_bias", False),
+                      ("mlp_bias", False)):
+        if t.get(key, want) != want:
+            raise ConfigError(f"unsupported LoopVL setting {key}={t.get(key)!r}")
+    rope = t.get("rope_parameters") or {}
+    if rope.get("rope_type") != "yarn":
+        raise ConfigError("LoopVL positions are YaRN-scaled")
+    language = (cfg.get("loopvl_config") or {}).get("language") or {}
+    for key in ("hidden_size", "num_attention_heads", "head_dim", "H_cycles", "L_cycles", "max_position_embeddings"):
+        if key in language and language[key] != t.get(key):
+            raise ConfigError(f"LoopVL language / text_config mismatch: {key}")
+    if int(t["head_dim"]) != 128 or int(t["num_key_value_heads"]) != int(t["num_attention_heads"]):
+        raise ConfigError("LoopVL heads are 128 wide without grouping")
+    per, hc, lc = int(t["num_layers_per_stack"]), int(t["H_cycles"]), int(t["L_cycles"])
+    if int(t.get("num_hidden_layers", hc * (lc + 1) * per)) != hc * (lc + 1) * per:
+        raise ConfigError("num_hidden_layers differs from H_cycles * (L_cycles + 1) * num_layers_per_stack")
+    spec = _loop_spec(name, int(t["hidden_size"]), int(t["num_attention_heads"]), int(t["intermediate_size"]), int(t["vocab_size"]),
+                      per_stack=per, h_cycles=hc, l_cycles=lc, original_max=int(rope["original_max_position_embeddings"]))
+    spec.rope_theta, spec.rms_eps = float(t.get("rope_theta", 10000.0)), float(t.get("rms_norm_eps", 1e-6))
+    spec.max_position = int(t["max_position_embeddings"])
+    spec.eos_token_id = t.get("eos_token_id")
+    hrm = spec.extra["hrm"]
+    hrm["embedding_scale"] = float(t.get("embedding_scale", hrm["embedding_scale"]))
+    hrm["yarn"] = {"factor": float(rope["factor"]), "original_max": int(rope["original_max_position_embeddings"]),
+                   "beta_fast": float(rope.get("beta_fast", 32.0)), "beta_slow": float(rope.get("beta_slow", 1.0))}
+    return spec
 
 
 def _flint_spec(cfg: dict[str, Any], name: str) -> ModelSpec:
@@ -380,6 +417,8 @@ def spec_from_hf_config(cfg: dict[str, Any], name: str = "model") -> ModelSpec:
         raise ConfigError(f"unsupported architectures {archs}")
     if arch == "flint":
         return _flint_spec(cfg, name)
+    if arch == "loop_vl":
+        return _loopvl_spec(cfg, name)
     act = cfg.get("hidden_act", "silu")
     if act not in ("silu", "swish"):
         raise ConfigError(f"unsupported activation {act!r}")

@@ -227,6 +227,25 @@ def load_decoder_weights(model_dir: str | Path, spec: ModelSpec | None, device: 
         ck.close()
 
 
+def checkpoint_source(model_dir: str | Path, spec: ModelSpec, device: torch.device | str):
+    """(source, close): ``source(name, shape)`` reads one 16/32-bit float tensor of the directory, checks its shape and
+    casts it to the model's compute dtype on ``device`` -- for model classes that assemble their own weight sets."""
+    ck = MappedCheckpoint(Path(model_dir))
+    device = torch.device(device)
+    dtype = DTYPES["bf16" if spec.dtype == "f16" and device.type == "cuda" else spec.dtype]
+
+    def source(name: str, shape: tuple[int, ...]) -> torch.Tensor:
+        if not ck.has(name):
+            raise CheckpointError(f"missing tensor {name}")
+        t = ck.tensor(name)
+        if tuple(t.shape) != tuple(shape):
+            raise CheckpointError(f"{name}: shape {tuple(t.shape)} != expected {tuple(shape)}")
+        if ck.info(name).dtype not in ("BF16", "F16", "F32"):
+            raise CheckpointError(f"{name}: dtype {ck.info(name).dtype} is not a float tensor")
+        return t.to(device=device, dtype=dtype)
+    return source, ck.close
+
+
 def save_decoder_checkpoint(model_dir: str | Path, spec: ModelSpec, tensors: dict[str, torch.Tensor],
                             hf_config: dict, shards: int = 1) -> None:
     """Write a model directory (config.json + safetensors, optionally sharded with an index) --

@@ -64,3 +64,66 @@ def test_flint_config_and_checkpoint(tmp_path):
     save_decoder_checkpoint(d3, spec, wrong, FLINT_CONFIG)
     with pytest.raises(CheckpointError):
         Model.load(str(d3), Settings(capacity=256, max_batch=2, graph=False), device="cpu")
+
+
+LOOPVL_TEXT = {
+    "model_type": "hrm_text", "architectures": ["HrmTextForCausalLM"], "dtype": "bfloat16", "hidden_act": "silu", "prefix_lm": True,
+    "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False, "use_cache": False, "hidden_size": 256,
+    "intermediate_size": 512, "vocab_size": 2048, "num_attention_heads": 2, "num_key_value_heads": 2, "head_dim": 128, "H_cycles": 2,
+    "L_cycles": 3, "num_layers_per_stack": 2, "num_hidden_layers": 16, "max_position_embeddings": 128, "bos_token_id": 6,
+    "eos_token_id": 11, "pad_token_id": 5, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "embedding_scale": 16.0,
+    "attention_dropout": 0.0,
+    "rope_parameters": {"rope_type": "yarn", "rope_theta": 10000, "factor": 2, "original_max_position_embeddings": 64,
+                        "beta_fast": 32, "beta_slow": 1},
+}
+LOOPVL_CONFIG = {"model_type": "loopvl", "architectures": ["LoopVLForConditionalGeneration"], "format_version": 2,
+                 "text_config": LOOPVL_TEXT, "loopvl_config": {"language": {k: LOOPVL_TEXT[k] for k in ("hidden_size", "num_attention_heads", "H_cycles")}},
+                 "vision_config": {"model_type": "penguinvl_vision_encoder"}}
+
+
+def test_loopvl_text_config_and_checkpoint(tmp_path):
+    from flyingfish_b200.config import loop_tiny
+    spec = spec_from_hf_config(LOOPVL_CONFIG, "loop-test")
+    tiny = loop_tiny()
+    assert spec.arch == "loop_vl" and spec.layers == 16 and spec.extra["hrm"]["layers_per_stack"] == 2
+    assert spec.extra["hrm"]["yarn"] == {"factor": 2.0, "original_max": 64, "beta_fast": 32.0, "beta_slow": 1.0}
+    assert spec.extra["hrm"]["embedding_scale"] == 16.0 and spec.eos_token_id == 11 and spec.max_position == 128
+    assert (spec.hidden, spec.heads, spec.ffn, spec.vocab) == (tiny.hidden, tiny.heads, tiny.ffn, tiny.vocab)
+    bad = json.loads(json.dumps(LOOPVL_CONFIG))
+    bad["text_config"]["num_hidden_layers"] = 12
+    with pytest.raises(ConfigError):
+        spec_from_hf_config(bad, "x")
+    bad = json.loads(json.dumps(LOOPVL_CONFIG))
+    bad["loopvl_config"]["language"]["H_cycles"] = 3
+    with pytest.raises(ConfigError):
+        spec_from_hf_config(bad, "x")
+    g = torch.Generator().manual_seed(1)
+    h, f = spec.hidden, spec.ffn
+    tensors = {"language_model.model.embed_tokens.weight": torch.randn(spec.vocab, h, generator=g) * 0.05,
+               "language_model.lm_head.weight": torch.randn(spec.vocab, h, generator=g) * 0.05,
+               "language_model.model.z_L_init": torch.randn(h, generator=g) * 0.05,
+               "projector.fc1.bias": torch.zeros(8)}                         # vision-side tensors are left alone
+    for stack in ("L", "H"):
+        for i in range(2):
+            p = f"language_model.model.{stack}_module.layers.{i}"
+            for r in ("q", "k", "v", "o", "gate"):
+                tensors[f"{p}.self_attn.{r}_proj.weight"] = torch.randn(h, h, generator=g) * 0.05
+            tensors[f"{p}.mlp.gate_proj.weight"] = torch.randn(f, h, generator=g) * 0.05
+            tensors[f"{p}.mlp.up_proj.weight"] = torch.randn(f, h, generator=g) * 0.05
+            tensors[f"{p}.mlp.down_proj.weight"] = torch.randn(h, f, generator=g) * 0.05
+    tensors = {k: v.to(torch.bfloat16) for k, v in tensors.items()}
+    d = tmp_path / "loopvl"
+    save_decoder_checkpoint(d, spec, tensors, LOOPVL_CONFIG)
+    model = Model.load(str(d), Settings(capacity=128, max_batch=2, graph=False), device="cpu")
+    w = model.engine.model.w
+    assert torch.equal(w.embed.cpu(), tensors["language_model.model.embed_tokens.weight"])
+    assert torch.equal(w.layers[0].wqkv[:h].cpu(), tensors["language_model.model.L_module.layers.0.self_attn.q_proj.weight"])
+    assert torch.equal(w.layers[2].wo.cpu(), tensors["language_model.model.H_module.layers.0.self_attn.o_proj.weight"])
+    ids = [6, 20, 21, 22, 23]
+    first = model.prefill(ids)
+    assert first == model.prefill(ids) and isinstance(model.decode(), int)
+    del tensors["language_model.model.z_L_init"]
+    d2 = tmp_path / "loopvl2"
+    save_decoder_checkpoint(d2, spec, tensors, LOOPVL_CONFIG)
+    with pytest.raises(CheckpointError):
+        Model.load(str(d2), Settings(capacity=128, max_batch=2, graph=False), device="cpu")
