@@ -129,6 +129,16 @@ def _global_parser() -> argparse.ArgumentParser:
     dz.add_argument("--mode", help="streaming latency mode named in the processor configuration")
     dz.add_argument("--threshold", type=float, default=0.5, help="speaker activity probability that counts as speech")
 
+    t3 = sub.add_parser("to-3d")
+    t3.add_argument("input", help="safetensors file with the shape decoder's output: `coords` [n, 4] int32 and either `fields` [n, 7] "
+                                  "(dual grid) or `cubes` [n, 8], `positions` [c, 3], `scalar` [c] (corner field)")
+    t3.add_argument("--output", required=True, help="mesh file to write (.ply or .obj)")
+    t3.add_argument("--resolution", type=int, default=0, help="grid side of the dual-grid fields")
+    t3.add_argument("--min-component", type=float, default=0.0, help="drop components below this share of the faces")
+    t3.add_argument("--fill-holes", type=int, default=0, help="close boundary loops of at most this many edges")
+    t3.add_argument("--faces", type=int, default=0, help="simplify to at most this many faces")
+    t3.add_argument("--unit-ball", action="store_true", help="centre the mesh and scale it into the unit ball")
+
     for name in DSPARK_TOOLS:
         dp = sub.add_parser(name)
         dp.add_argument("--prompt-tokens", type=int, default=48)
@@ -205,7 +215,7 @@ def check_flags(args) -> None:
                              "(verification rows and shared prefixes read BF16 pages)")
     if args.tp < 1 or (args.tp > 1 and args.cpu):
         raise SystemExit("--tp needs one CUDA device per rank")
-    if args.command in ("transcribe", "diarize") and (args.draft_model or args.prefix_cache or args.kv_format != "bf16"):
+    if args.command in ("transcribe", "diarize", "to-3d") and (args.draft_model or args.prefix_cache or args.kv_format != "bf16"):
         raise SystemExit(f"{args.command} takes none of the text-generation flags")
     if args.tp > 1 and args.command not in ("generate", "bench", "serve"):
         raise SystemExit(f"--tp applies to generate, bench and serve, not to {args.command}")
@@ -600,6 +610,44 @@ def cmd_diarize(args) -> None:
         sys.stdout.write(text)
 
 
+def cmd_to_3d(args) -> dict:
+    """The decode tail of image-to-3D: the shape decoder's sparse output -> surface -> post-processing -> mesh file
+    (src/main.rs `to-3d` of the reference ends the same way; the generator in front of it is not part of this build,
+    so the command starts from the decoder's saved output)."""
+    import torch
+    from .loaders.safetensors_io import SafetensorsFile
+    from .ops import mesh_ops
+    from .utils import media, mesh_post
+    if args.model:
+        raise SystemExit("to-3d starts from saved decoder output (the image-to-3D generator is not built): pass no --model")
+    out = check_output_path(args.output, None)
+    if out.suffix not in (".ply", ".obj"):
+        raise SystemExit("--output must end in .ply or .obj")
+    sf = SafetensorsFile(args.input)
+    try:
+        t = {n: sf.tensor(n).clone() for n in sf.tensors}
+    finally:
+        sf.close()
+    dev = "cpu" if args.cpu else f"cuda:{args.device}"
+    if "coords" not in t:
+        raise SystemExit("the input holds no `coords` tensor")
+    coords = t["coords"].to(torch.int32).to(dev)
+    if "fields" in t:
+        if args.resolution <= 0:
+            raise SystemExit("dual-grid fields need --resolution")
+        v, f = mesh_ops.dual_grid_mesh(coords, t["fields"].float().to(dev), args.resolution)
+        kind = "dual_grid"
+    elif all(k in t for k in ("cubes", "positions", "scalar")):
+        v, f = mesh_ops.dual_contour_mesh(coords, t["cubes"].to(dev), t["positions"].float().to(dev), t["scalar"].float().to(dev))
+        kind = "dual_contour"
+    else:
+        raise SystemExit("the input holds neither `fields` nor `cubes` / `positions` / `scalar`")
+    v, f, report = mesh_post.finish_mesh(v, f, args.min_component, args.fill_holes, args.faces, args.unit_ball)
+    with open(out, "wb") as fh:
+        (media.write_ply if out.suffix == ".ply" else media.write_obj)(fh, media.Mesh(v, f))
+    return {"surface": kind, "output": str(out), **report}
+
+
 def cmd_serve(args) -> None:
     from .loaders.tokenizer import read_chat_template
     from .serve.http import run
@@ -665,7 +713,7 @@ def main(argv: list[str] | None = None) -> int:
     handlers = {"generate": cmd_generate, "bench": cmd_bench, "profile": cmd_profile, "inspect": cmd_inspect,
                 "tokenize": cmd_tokenize, "calibrate": cmd_calibrate, "embed": cmd_embed, "verify": cmd_verify,
                 "compare-prefill": cmd_verify, "compare-log": cmd_compare_log, "verify-spec": cmd_spec,
-                "bench-spec": cmd_spec, "profile-spec": cmd_spec, **{t: cmd_dspark for t in DSPARK_TOOLS}}
+                "bench-spec": cmd_spec, "profile-spec": cmd_spec, "to-3d": cmd_to_3d, **{t: cmd_dspark for t in DSPARK_TOOLS}}
     if args.command == "serve":
         cmd_serve(args)
         return 0

@@ -146,3 +146,26 @@ def fill_holes(vertices: torch.Tensor, faces: torch.Tensor, capacity: int) -> tu
     if not new:
         return faces.to(torch.int32), 0
     return torch.cat([faces.to(torch.int32).cpu(), torch.tensor(new, dtype=torch.int32)], dim=0), closed
+
+
+def finish_mesh(vertices: torch.Tensor, faces: torch.Tensor, minimum_face_ratio: float = 0.0, hole_capacity: int = 0,
+                target_faces: int = 0, unit_ball: bool = False) -> tuple[torch.Tensor, torch.Tensor, dict]:
+    """The tail of the image-to-3D pipeline on an extracted mesh, each stage optional: drop small components, close
+    small holes, simplify to a face budget, normalise into the unit ball. Returns (vertices, faces, what each stage did)."""
+    report: dict = {"input": {"vertices": int(vertices.shape[0]), "faces": int(faces.shape[0])}}
+    v, f = vertices.detach().float().cpu(), faces.detach().to(torch.int32).cpu()
+    if f.shape[0] == 0:
+        raise ValueError("the extracted surface has no faces")
+    if minimum_face_ratio > 0.0:
+        v, f, kept_faces, _ = filter_components(v, f, minimum_face_ratio)
+        report["components"] = {"faces_kept": int(kept_faces.shape[0])}
+    if hole_capacity >= 3:
+        f, closed = fill_holes(v, f, hole_capacity)
+        report["holes"] = {"closed": closed}
+    if target_faces > 0:
+        v, f, _, _ = simplify(v, f, target_faces)
+        report["simplify"] = {"faces": int(f.shape[0])}
+    if unit_ball:
+        v = normalize(v)
+    report["output"] = {"vertices": int(v.shape[0]), "faces": int(f.shape[0])}
+    return v, f, report

@@ -108,3 +108,45 @@ def test_holes_are_found_and_closed():
     assert mp.fill_holes(v, f, 8)[1] == 0
     with pytest.raises(ValueError):
         mp.fill_holes(v, f, 2)
+
+
+def test_to_3d_command_runs_the_decode_tail(tmp_path, capsys):
+    import json
+    from flyingfish_b200 import cli
+    from flyingfish_b200.loaders.safetensors_io import save_safetensors
+    from flyingfish_b200.utils import media
+    # a corner field of a sphere with a small stray blob, saved as the shape decoder would leave it
+    g = 10
+    idx = torch.stack(torch.meshgrid(torch.arange(g), torch.arange(g), torch.arange(g), indexing="ij"), -1).reshape(-1, 3)
+    coords = torch.cat([torch.zeros(idx.shape[0], 1, dtype=torch.long), idx], 1).to(torch.int32)
+    s = g + 1
+    corner = lambda x, y, z: x + s * (y + s * z)
+    cubes = torch.stack([corner(idx[:, 0] + (c & 1), idx[:, 1] + ((c >> 1) & 1), idx[:, 2] + ((c >> 2) & 1)) for c in range(8)], 1)
+    lat = torch.stack(torch.meshgrid(torch.arange(s), torch.arange(s), torch.arange(s), indexing="ij"), -1).reshape(-1, 3)
+    positions = torch.zeros(s ** 3, 3)
+    positions[corner(lat[:, 0], lat[:, 1], lat[:, 2])] = lat.float()
+    big = (positions - torch.tensor([4.4, 4.6, 4.5])).norm(dim=1) - 3.1
+    blob = (positions - torch.tensor([8.6, 8.5, 8.4])).norm(dim=1) - 0.8
+    scalar = torch.minimum(big, blob)
+    src = tmp_path / "decoder.safetensors"
+    save_safetensors(src, {"coords": coords, "cubes": cubes.to(torch.int32), "positions": positions, "scalar": scalar})
+    out = tmp_path / "shape.ply"
+    assert cli.main(["--cpu", "to-3d", str(src), "--output", str(out), "--min-component", "0.2", "--faces", "120", "--unit-ball"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report["surface"] == "dual_contour" and report["output"]["faces"] <= 120
+    assert report["components"]["faces_kept"] < report["input"]["faces"]                # the blob is gone
+    mesh = media.read_mesh(out.read_bytes(), "ply")
+    assert mesh.triangles.shape[0] == report["output"]["faces"] and _closed(mesh.positions, mesh.triangles)
+    assert mesh.positions.norm(dim=1).max().item() == pytest.approx(1.0, abs=1e-5)
+    # dual-grid fields go the other way in, OBJ comes out; existing outputs are not overwritten
+    fields = torch.randn(coords.shape[0], 7, generator=torch.Generator().manual_seed(0))
+    src2 = tmp_path / "fields.safetensors"
+    save_safetensors(src2, {"coords": coords, "fields": fields})
+    assert cli.main(["--cpu", "to-3d", str(src2), "--output", str(tmp_path / "grid.obj"), "--resolution", "10"]) == 0
+    assert json.loads(capsys.readouterr().out)["surface"] == "dual_grid" and (tmp_path / "grid.obj").read_text().startswith("v ")
+    with pytest.raises(SystemExit):
+        cli.main(["--cpu", "to-3d", str(src2), "--output", str(out), "--resolution", "10"])
+    with pytest.raises(SystemExit):
+        cli.main(["--cpu", "to-3d", str(src2), "--output", str(tmp_path / "x.ply")])                  # no --resolution
+    with pytest.raises(SystemExit):
+        cli.main(["--cpu", "to-3d", str(src2), "--output", str(tmp_path / "x.stl"), "--resolution", "10"])
