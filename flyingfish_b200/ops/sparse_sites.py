@@ -97,3 +97,57 @@ def round_unique(coords: torch.Tensor, source_grid: int, target_grid: int) -> to
     """Sites re-quantised onto another grid (ties to even), duplicates merged, lexicographic order."""
     scaled = torch.round(scaled_coordinates(coords, source_grid, target_grid)).to(torch.int32)
     return deduplicate(torch.cat([coords[:, :1].to(torch.int32), scaled], dim=1))[0]
+
+
+def morton_keys(coords: torch.Tensor, swap_xy: bool = False) -> torch.Tensor:
+    """Z-order keys [n] int64: the bits of (x, y, z) -- or (y, x, z) -- interleaved with the first axis most significant
+    inside every triple, the batch index above them."""
+    c = coords.long()
+    top = int(c[:, 1:].max())
+    depth = max(top.bit_length(), 0)
+    batches = int(c[:, 0].max()) + 1
+    if depth > 16 or 3 * depth + batches.bit_length() > 63:
+        raise ValueError("serialized coordinate or batch exceeds Morton capacity")
+    axes = [c[:, 2], c[:, 1], c[:, 3]] if swap_xy else [c[:, 1], c[:, 2], c[:, 3]]
+    key = c[:, 0] << (3 * depth)
+    for bit in range(depth):
+        for axis, value in enumerate(axes):
+            key = key | (((value >> bit) & 1) << (3 * bit + 2 - axis))
+    return key
+
+
+def serialized_windows(coords: torch.Tensor, window: int) -> dict[str, torch.Tensor | list[torch.Tensor]]:
+    """Orders for windowed attention over sparse sites (src/sparse.rs:1411-1502 of the reference): two space-filling
+    orders (z-order over x y z and over y x z) with their inverse permutations, and a padding plan that makes every
+    sample's row count a multiple of ``window`` by repeating rows of its last full window: ``pad`` lists the source row
+    of every padded slot, ``unpad`` the slot of every real row, ``offsets`` the window boundaries (cumulative)."""
+    check_sites(coords)
+    if window <= 0:
+        raise ValueError("invalid serialized window size")
+    n = coords.shape[0]
+    keys = [morton_keys(coords, False), morton_keys(coords, True)]
+    order = [torch.sort(k, stable=True).indices for k in keys]
+    inverse = []
+    for o in order:
+        inv = torch.empty_like(o)
+        inv[o] = torch.arange(n, device=o.device)
+        inverse.append(inv)
+    counts = torch.bincount(coords[:, 0].long()).tolist()
+    pad, unpad, offsets, first = [], [], [0], 0
+    for count in counts:
+        if count == 0:
+            continue
+        padded = -(-count // window) * window if count > window else count
+        base = len(pad)
+        unpad += list(range(base, base + count))
+        pad += list(range(first, first + count))
+        if padded > count:
+            tail = count % window
+            pad += list(range(first + count - window, first + count - tail))
+        for start in range(base, base + padded, window):
+            offsets.append(start + min(window, base + padded - start))
+        first += count
+    dev = coords.device
+    as_t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    return {"keys": keys, "order": [o.to(torch.int32) for o in order], "inverse": [i.to(torch.int32) for i in inverse],
+            "pad": as_t(pad), "unpad": as_t(unpad), "offsets": as_t(offsets)}

@@ -71,3 +71,26 @@ def test_parents_children_and_rescaling():
         ss.scaled_coordinates(_sites([[0, 4, 0, 0]]), 4, 9)
     with pytest.raises(ValueError):
         ss.downsample(c, 0)
+
+
+def test_serialized_windows():
+    c = _sites([[0, 0, 0, 0], [0, 1, 0, 0], [0, 0, 1, 0], [0, 0, 0, 1], [0, 3, 2, 1], [1, 1, 1, 1], [1, 0, 0, 0]])
+    k = ss.morton_keys(c)
+    # depth 2 (largest coordinate 3): x y z bits interleaved, x most significant inside a triple
+    assert k[:4].tolist() == [0, 4, 2, 1]
+    assert k[4].item() == ((1 << 5) | (1 << 4)) | ((1 << 2) | (1 << 0))        # x = 0b11, y = 0b10, z = 0b01
+    assert k[5].item() == (1 << 6) | 7 and k[6].item() == (1 << 6)
+    assert ss.morton_keys(c, swap_xy=True)[:3].tolist() == [0, 2, 4]
+    w = ss.serialized_windows(c, window=2)
+    assert w["order"][0].tolist() == [0, 3, 2, 1, 4, 6, 5] and w["order"][1].tolist() == [0, 3, 1, 2, 4, 6, 5]
+    for o, inv in zip(w["order"], w["inverse"]):
+        assert inv[o.long()].tolist() == list(range(7))
+    # sample 0 has 5 rows -> 6 slots (the odd row's window is filled from the last full window), sample 1 has 2
+    assert w["pad"].tolist() == [0, 1, 2, 3, 4, 3, 5, 6] and w["unpad"].tolist() == [0, 1, 2, 3, 4, 6, 7]
+    assert w["offsets"].tolist() == [0, 2, 4, 6, 8]
+    small = ss.serialized_windows(c, window=8)                                  # samples shorter than a window are not padded
+    assert small["pad"].tolist() == list(range(7)) and small["offsets"].tolist() == [0, 5, 7]
+    with pytest.raises(ValueError):
+        ss.serialized_windows(c, 0)
+    with pytest.raises(ValueError):
+        ss.morton_keys(_sites([[0, 1 << 17, 0, 0]]))
