@@ -165,3 +165,12 @@ def project_bilinear(features: torch.Tensor, camera: torch.Tensor, grid_side: in
     val = val + f[y0, x1] * (dx * (1.0 - dy))
     val = val + f[y1, x0] * ((1.0 - dx) * dy)
     return val + f[y1, x1] * (dx * dy)
+
+
+def adaptive_avg_pool2d(x: torch.Tensor, out_h: int, out_w: int) -> torch.Tensor:
+    """Channels-last adaptive average pooling [h, w, c] -> [out_h, out_w, c]: output cell (y, x) averages rows
+    ``floor(y h / out_h) .. ceil((y + 1) h / out_h)`` and the matching columns (the windows of PyTorch's operator)."""
+    h, w, c = x.shape
+    if out_h <= 0 or out_w <= 0:
+        raise ValueError("adaptive pooling needs a positive output size")
+    return torch.nn.functional.adaptive_avg_pool2d(x.float().permute(2, 0, 1)[None], (out_h, out_w))[0].permute(1, 2, 0).contiguous()

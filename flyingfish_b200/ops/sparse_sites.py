@@ -151,3 +151,22 @@ def serialized_windows(coords: torch.Tensor, window: int) -> dict[str, torch.Ten
     as_t = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     return {"keys": keys, "order": [o.to(torch.int32) for o in order], "inverse": [i.to(torch.int32) for i in inverse],
             "pad": as_t(pad), "unpad": as_t(unpad), "offsets": as_t(offsets)}
+
+
+def unit_ball_frame(coords: torch.Tensor) -> torch.Tensor:
+    """4 x 4 affine frame (FP32) that moves the sites' centroid to the origin and the farthest site to radius 1
+    (src/sparse.rs:1265-1301 of the reference); the sites must belong to one sample."""
+    if bool((coords[:, 0] != coords[0, 0]).any()):
+        raise ValueError("unit-ball frame requires one sample")
+    xyz = coords[:, 1:].long()
+    center = xyz.sum(dim=0).float() * (1.0 / float(coords.shape[0]))
+    d = xyz.float() - center
+    radius = float(torch.sqrt((d[:, 0] * d[:, 0] + d[:, 2] * d[:, 2]) + d[:, 1] * d[:, 1]).max()) + 1e-8
+    if not (radius > 0.0 and radius < float("inf")):
+        raise ValueError("invalid unit-ball radius")
+    frame = torch.zeros(4, 4)
+    for a in range(3):
+        frame[a, a] = 1.0 / radius
+        frame[a, 3] = -float(center[a]) / radius
+    frame[3, 3] = 1.0
+    return frame

@@ -94,3 +94,23 @@ def test_serialized_windows():
         ss.serialized_windows(c, 0)
     with pytest.raises(ValueError):
         ss.morton_keys(_sites([[0, 1 << 17, 0, 0]]))
+
+
+def test_unit_ball_frame_and_adaptive_pool():
+    c = _sites([[2, 0, 0, 0], [2, 4, 0, 0], [2, 2, 6, 2]])
+    f = ss.unit_ball_frame(c)
+    centre = torch.tensor([2.0, 2.0, 2.0 / 3.0])
+    pts = torch.cat([c[:, 1:].float(), torch.ones(3, 1)], 1) @ f.t()
+    assert torch.allclose(pts[:, :3].mean(0), torch.zeros(3), atol=1e-6) and pts[:, 3].tolist() == [1.0, 1.0, 1.0]
+    assert pts[:, :3].norm(dim=1).max().item() == pytest.approx(1.0, abs=1e-6)
+    assert torch.allclose(f[:3, 3] / f[0, 0], -centre, atol=1e-6)
+    with pytest.raises(ValueError):
+        ss.unit_ball_frame(_sites([[0, 0, 0, 0], [1, 1, 1, 1]]))
+    from flyingfish_b200.ops import media_ops
+    x = torch.arange(5 * 7 * 2, dtype=torch.float32).reshape(5, 7, 2)
+    y = media_ops.adaptive_avg_pool2d(x, 2, 3)
+    for oy in range(2):
+        for ox in range(3):
+            y0, y1 = oy * 5 // 2, ((oy + 1) * 5 + 1) // 2
+            x0, x1 = ox * 7 // 3, ((ox + 1) * 7 + 2) // 3
+            assert torch.allclose(y[oy, ox], x[y0:y1, x0:x1].reshape(-1, 2).mean(0))
