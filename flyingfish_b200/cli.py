@@ -131,7 +131,8 @@ def _global_parser() -> argparse.ArgumentParser:
 
     t3 = sub.add_parser("to-3d")
     t3.add_argument("input", help="safetensors file with the shape decoder's output: `coords` [n, 4] int32 and either `fields` [n, 7] "
-                                  "(dual grid) or `cubes` [n, 8], `positions` [c, 3], `scalar` [c] (corner field)")
+                                  "(dual grid), or `scalar` [c] on the cubes' shared corners (lexicographic corner order), or "
+                                  "`cubes` [n, 8], `positions` [c, 3], `scalar` [c] (explicit corner field)")
     t3.add_argument("--output", required=True, help="mesh file to write (.ply or .obj)")
     t3.add_argument("--resolution", type=int, default=0, help="grid side of the dual-grid fields")
     t3.add_argument("--min-component", type=float, default=0.0, help="drop components below this share of the faces")
@@ -640,8 +641,16 @@ def cmd_to_3d(args) -> dict:
     elif all(k in t for k in ("cubes", "positions", "scalar")):
         v, f = mesh_ops.dual_contour_mesh(coords, t["cubes"].to(dev), t["positions"].float().to(dev), t["scalar"].float().to(dev))
         kind = "dual_contour"
+    elif "scalar" in t:
+        # values on the shared corner lattice of the cubes, in the lexicographic corner order
+        from .ops import sparse_sites
+        corners, cubes, _, _ = sparse_sites.cube_corners(coords)
+        if t["scalar"].numel() != corners.shape[0]:
+            raise SystemExit(f"`scalar` has {t['scalar'].numel()} values for {corners.shape[0]} cube corners")
+        v, f = mesh_ops.dual_contour_mesh(coords, cubes, corners[:, 1:].float(), t["scalar"].float().reshape(-1).to(dev))
+        kind = "dual_contour"
     else:
-        raise SystemExit("the input holds neither `fields` nor `cubes` / `positions` / `scalar`")
+        raise SystemExit("the input holds neither `fields` nor `scalar` (with or without `cubes` / `positions`)")
     v, f, report = mesh_post.finish_mesh(v, f, args.min_component, args.fill_holes, args.faces, args.unit_ball)
     with open(out, "wb") as fh:
         (media.write_ply if out.suffix == ".ply" else media.write_obj)(fh, media.Mesh(v, f))

@@ -144,6 +144,19 @@ def test_to_3d_command_runs_the_decode_tail(tmp_path, capsys):
     save_safetensors(src2, {"coords": coords, "fields": fields})
     assert cli.main(["--cpu", "to-3d", str(src2), "--output", str(tmp_path / "grid.obj"), "--resolution", "10"]) == 0
     assert json.loads(capsys.readouterr().out)["surface"] == "dual_grid" and (tmp_path / "grid.obj").read_text().startswith("v ")
+    # a corner field without explicit cubes: values in the order of the shared corner lattice
+    from flyingfish_b200.ops import sparse_sites
+    corners, _, _, _ = sparse_sites.cube_corners(coords)
+    field = (corners[:, 1:].float() - torch.tensor([4.4, 4.6, 4.5])).norm(dim=1) - 3.1
+    src3 = tmp_path / "corners.safetensors"
+    save_safetensors(src3, {"coords": coords, "scalar": field})
+    assert cli.main(["--cpu", "to-3d", str(src3), "--output", str(tmp_path / "ball.ply")]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    ball = media.read_mesh((tmp_path / "ball.ply").read_bytes(), "ply")
+    assert rep["surface"] == "dual_contour" and _closed(ball.positions, ball.triangles)
+    save_safetensors(tmp_path / "short.safetensors", {"coords": coords, "scalar": field[:-1]})
+    with pytest.raises(SystemExit):
+        cli.main(["--cpu", "to-3d", str(tmp_path / "short.safetensors"), "--output", str(tmp_path / "y.ply")])
     with pytest.raises(SystemExit):
         cli.main(["--cpu", "to-3d", str(src2), "--output", str(out), "--resolution", "10"])
     with pytest.raises(SystemExit):
