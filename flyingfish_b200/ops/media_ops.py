@@ -174,3 +174,27 @@ def adaptive_avg_pool2d(x: torch.Tensor, out_h: int, out_w: int) -> torch.Tensor
     if out_h <= 0 or out_w <= 0:
         raise ValueError("adaptive pooling needs a positive output size")
     return torch.nn.functional.adaptive_avg_pool2d(x.float().permute(2, 0, 1)[None], (out_h, out_w))[0].permute(1, 2, 0).contiguous()
+
+
+def axial_rotary_table(height: int, width: int, dim: int, theta: float = 10000.0) -> torch.Tensor:
+    """[height * width, dim] table for :func:`rotary_spatial`: cos in the first half, sin in the second; the first
+    quarter of the frequencies turns with the row index, the second with the column index."""
+    if dim % 4:
+        raise ValueError("axial rotary needs a head width that is a multiple of 4")
+    q = dim // 4
+    inv = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), torch.arange(q, dtype=torch.float32) / q)
+    ys, xs = torch.meshgrid(torch.arange(height, dtype=torch.float32), torch.arange(width, dtype=torch.float32), indexing="ij")
+    ang = torch.cat([ys.reshape(-1, 1) * inv[None], xs.reshape(-1, 1) * inv[None]], dim=1)          # [pixels, dim / 2]
+    return torch.cat([torch.cos(ang), torch.sin(ang)], dim=1)
+
+
+def rotary_spatial(x: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """Split-half rotary embedding of channels-last activations: x [pixels, heads, dim] with a per-pixel table
+    [pixels, dim] (cos | sin); pairs are (d, d + dim / 2)."""
+    pixels, heads, dim = x.shape
+    if dim % 4 or table.shape != (pixels, dim):
+        raise ValueError("rotary_spatial: x [pixels, heads, dim], table [pixels, dim], dim a multiple of 4")
+    half = dim // 2
+    c, s = table[:, None, :half].float(), table[:, None, half:].float()
+    a, b = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([a * c - b * s, b * c + a * s], dim=-1).to(x.dtype)

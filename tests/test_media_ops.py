@@ -128,3 +128,24 @@ def test_projection_samples_the_feature_map():
     assert torch.allclose(sub[0], out[centre]) and torch.allclose(sub[1], out[(0 * 3 + 2) * 3 + 1])
     with pytest.raises(ValueError):
         mo.project_bilinear(feats, cam, side, torch.tensor([[3, 0, 0]]))
+
+
+def test_spatial_rotary():
+    h, w, heads, dim = 3, 4, 2, 8
+    table = mo.axial_rotary_table(h, w, dim)
+    assert table.shape == (12, 8)
+    # pixel (0, 0) is the identity; a pixel in row 0 only turns the column frequencies
+    assert torch.allclose(table[0], torch.tensor([1.0, 1, 1, 1, 0, 0, 0, 0]))
+    assert torch.allclose(table[2, :2], torch.ones(2)) and not torch.allclose(table[2, 2:4], torch.ones(2))
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(12, heads, dim, generator=g)
+    y = mo.rotary_spatial(x, table)
+    for p in (0, 5, 11):
+        for hd in range(heads):
+            for d in range(4):
+                c, s = table[p, d], table[p, 4 + d]
+                assert y[p, hd, d] == pytest.approx(float(x[p, hd, d] * c - x[p, hd, 4 + d] * s), abs=1e-6)
+                assert y[p, hd, 4 + d] == pytest.approx(float(x[p, hd, 4 + d] * c + x[p, hd, d] * s), abs=1e-6)
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-5)           # a rotation
+    with pytest.raises(ValueError):
+        mo.rotary_spatial(x[..., :6], table[:, :6])
